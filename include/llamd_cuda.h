@@ -1,0 +1,202 @@
+/*
+ * llamd_cuda.h -- C ABI of libllamd_cuda.so, the B200 (sm_100a) backend for
+ * llamd's quantized decode/prefill hot path.
+ *
+ * The entry points mirror, one for one, the `extern "C"` surface that the
+ * reference's device backend crate binds (crates/llamd-rocm/src/lib.rs:73-136
+ * and crates/llamd-rocm/src/forward.rs:269-618), so a `llamd-cuda` crate can
+ * declare them with the same shapes. Each declaration cites the reference
+ * interface it replaces.
+ *
+ * Conventions (same as the reference's):
+ *   - `llamd_cuda_*` host-facing calls take HOST pointers unless a parameter
+ *     is named d_*, synchronise before returning, and return 0 / -1.
+ *   - `llamd_fwd_*` calls take DEVICE pointers, enqueue on the one stream the
+ *     library owns, never synchronise, and return void. A failure is sticky
+ *     and surfaces from llamd_fwd_sync() / llamd_fwd_last_error().
+ *   - The caller owns every buffer; the library owns the stream, the captured
+ *     graph and its grow-only scratch.
+ *   - Not re-entrant: one stream, one thread at a time.
+ *
+ * Q6_K weights live on the device in a tiled layout (see "weights" below); the
+ * bytes a caller uploads are always the reference's own 210-byte blocks.
+ */
+#ifndef LLAMD_CUDA_H
+#define LLAMD_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLAMD_QK_K 256
+#define LLAMD_Q6K_BLOCK_BYTES 210
+#define LLAMD_Q8_0_BLOCK_BYTES 34
+#define LLAMD_MAX_SEQ 8 /* crates/llamd-rocm/kernels/llamd_batch.hip:41 MAX_SEQ */
+
+/* ---- device discovery: crates/llamd-rocm/src/lib.rs:74-85 ------------- */
+int llamd_cuda_device_count(void);
+int llamd_cuda_device_info(int dev, char *name, int name_len, char *arch, int arch_len,
+                           size_t *total_mem, int *sm_count, int *warp_size);
+size_t llamd_cuda_free_mem(void);
+/* Message for the last failure on this thread's library state ("" if none). */
+const char *llamd_cuda_last_error_string(void);
+
+/* ---- raw device memory: crates/llamd-rocm/src/lib.rs:86-90,
+ *      crates/llamd-rocm/src/forward.rs:270-277 --------------------------- */
+void *llamd_cuda_upload(const void *host, size_t bytes); /* NULL on failure */
+void llamd_cuda_release(void *dev);
+void *llamd_fwd_alloc(size_t bytes);
+void llamd_fwd_free(void *p);
+int llamd_fwd_upload(void *dst, const void *src, size_t bytes);
+int llamd_fwd_download(void *dst, const void *src, size_t bytes);
+int llamd_fwd_memset(void *p, int value, size_t bytes);
+int llamd_fwd_sync(void);
+size_t llamd_fwd_free_mem(void);
+int llamd_fwd_last_error(void);
+int llamd_fwd_stream_init(void); /* forward.rs:552 */
+/* The library's stream as a cudaStream_t, for callers that time with events. */
+void *llamd_fwd_stream(void);
+
+/* ---- graph capture: crates/llamd-rocm/src/forward.rs:613-617 ----------- */
+int llamd_fwd_begin_capture(void);
+int llamd_fwd_end_capture(void);
+int llamd_fwd_graph_launch(void);
+int llamd_fwd_has_graph(void);
+void llamd_fwd_graph_destroy(void);
+
+/* ---- weights ----------------------------------------------------------
+ * Device layout "T32": blocks are taken in the reference's own order
+ * (row-major, `blocks` per row, experts on the slowest axis) and cut into
+ * tiles of 32 blocks; a tile is 6720 bytes (= 32 x 210, so the repack is a
+ * bit permutation): 12 x 32 x 16 B of 6-bit codes, 32 x 16 B of scales and
+ * 32 x 2 B of f16 d. It plays the role of the reference's planar repack
+ * (crates/llamd-quant/src/dot.rs:379-423, crates/llamd-rocm/src/lib.rs:685-695).
+ */
+size_t llamd_cuda_q6k_tiled_bytes(size_t n_blocks);
+/* d_src: n_blocks x 210 B in the reference layout, on the device. */
+void llamd_fwd_repack_q6k(const void *d_src, void *d_dst, size_t n_blocks);
+/* Host blocks in, tiled device buffer out (upload + repack + sync). NULL on failure. */
+void *llamd_cuda_upload_q6k(const void *host_blocks, size_t n_blocks);
+/* Inverse of the repack, for checking that no bit moved wrongly. */
+void llamd_fwd_unpack_q6k(const void *d_tiled, void *d_dst, size_t n_blocks);
+/* Dequantize blocks [first, first+n) of a tiled buffer to f32, with the
+ * reference's arithmetic d * sc * q (crates/llamd-quant/src/lib.rs:181-226). */
+void llamd_fwd_dequantize_q6k(const void *d_tiled, size_t first_block, size_t n_blocks, float *d_out);
+/* Q8_0: same idea, tiles of 32 rows x 1 block. rows must be what matvec gets. */
+size_t llamd_cuda_q8_0_tiled_bytes(size_t rows, size_t blocks_per_row);
+void llamd_fwd_repack_q8_0(const void *d_src, void *d_dst, size_t rows, size_t blocks_per_row);
+void *llamd_cuda_upload_q8_0(const void *host_blocks, size_t rows, size_t blocks_per_row);
+/* crates/llamd-quant/src/lib.rs:154-162, from the tiled buffer. */
+void llamd_fwd_dequantize_q8_0(const void *d_tiled, size_t rows, size_t blocks_per_row, float *d_out);
+
+/* ---- host-facing compute: crates/llamd-rocm/src/lib.rs:91-135 ---------- */
+/* d_w: tiled Q6_K, rows x blocks. aq/ad: one Q8_K activation (qs and d planes). */
+int llamd_cuda_matvec_q6k_resident(const void *d_w, const int8_t *aq, const float *ad, float *out,
+                                   int blocks, int rows);
+/* d_w holds n_expert matrices of `rows` rows; out is [n_used][rows]. */
+int llamd_cuda_matvec_grouped(const void *d_w, const int32_t *eid, const int8_t *aq, const float *ad,
+                              float *out, int blocks, int rows, int n_used);
+int llamd_cuda_matvec_bench(const void *d_w, const int8_t *aq, const float *ad, int blocks, int rows,
+                            int iters, float *ms_out);
+int llamd_cuda_matvec_grouped_bench(const void *d_w, const int32_t *eid, const int8_t *aq,
+                                    const float *ad, int blocks, int rows, int n_used, int iters,
+                                    float *ms_out);
+int llamd_cuda_quantize_q8k(const float *x, int nblocks, int8_t *qs, float *d, int16_t *bsums);
+/* f32 activations in, f32 out: quantize + matvec for `nseq` activations at
+ * once (Model::matvec_quant, crates/llamd-models/src/model.rs:241-276). The
+ * whole call is what a host caller pays: H2D, kernels, D2H. */
+int llamd_cuda_matvec_q6k_f32(const void *d_w, const float *x, float *out, int blocks, int rows, int nseq);
+/* Q8_0 weights: dequantize-then-f32-dot in the reference's order (model.rs:253-263). */
+int llamd_cuda_matvec_q8_0_f32(const void *d_w, const float *x, float *out, int blocks32, int rows, int nseq);
+
+/* ---- device-pointer ops: crates/llamd-rocm/src/forward.rs:279-612 ------ */
+void llamd_fwd_quantize(const float *x, int8_t *qs, float *d, int nblocks);              /* :375 */
+void llamd_fwd_quantize_bsums(const float *x, int8_t *qs, float *d, int16_t *bsums, int nblocks);
+void llamd_fwd_matvec(const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows); /* :347 */
+/* nseq activations [nseq][blocks*256] / [nseq][blocks] -> out [nseq][rows]
+ * (crates/llamd-rocm/src/batch.rs bop::matvec). */
+void llamd_fwd_matvec_batch(const void *w, const int8_t *aq, const float *ad, float *out, int blocks,
+                            int rows, int nseq);
+void llamd_fwd_matvec_x3(const void *w0, const void *w1, const void *w2, const int8_t *aq,
+                         const float *ad, float *o0, float *o1, float *o2, int blocks, int rows0,
+                         int rows1, int rows2); /* :524 */
+void llamd_fwd_matvec_x3_batch(const void *w0, const void *w1, const void *w2, const int8_t *aq,
+                               const float *ad, float *o0, float *o1, float *o2, int blocks, int rows0,
+                               int rows1, int rows2, int nseq);
+void llamd_fwd_matvec_grouped(const void *w, const int32_t *ids, const int8_t *aq, const float *ad,
+                              float *out, int blocks, int rows, int n_used); /* :355 */
+void llamd_fwd_matvec_grouped_x2(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq,
+                                 const float *ad, float *oa, float *ob, int blocks, int rows,
+                                 int n_used); /* :539 */
+/* per-expert activation aq[e], ad[e] (:365) */
+void llamd_fwd_matvec_grouped_pa(const void *w, const int32_t *ids, const int8_t *aq, const float *ad,
+                                 float *out, int blocks, int rows, int n_used);
+/* Batched grouped forms: ids [nseq][n_used]; activations [nseq][blocks*256]
+ * (x2) or [nseq][n_used][blocks*256] (pa); outputs [nseq][n_used][rows]. */
+void llamd_fwd_matvec_grouped_x2_batch(const void *wa, const void *wb, const int32_t *ids,
+                                       const int8_t *aq, const float *ad, float *oa, float *ob,
+                                       int blocks, int rows, int n_used, int nseq);
+void llamd_fwd_matvec_grouped_pa_batch(const void *w, const int32_t *ids, const int8_t *aq,
+                                       const float *ad, float *out, int blocks, int rows, int n_used,
+                                       int nseq);
+/* f32 weights [rows][k] (the router): sequential f32 dot per row (:340). wt is
+ * the transposed copy [k][rows] that llamd_fwd_transpose_f32 makes. */
+void llamd_fwd_transpose_f32(const float *w, float *wt, int rows, int k);
+void llamd_fwd_matvec_f32(const float *wt, const float *x, float *out, int k, int rows);
+void llamd_fwd_matvec_f32_batch(const float *wt, const float *x, float *out, int k, int rows, int nseq);
+void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq);
+
+void llamd_fwd_embed(const void *table, int token, float *out, int blocks);              /* :279 */
+void llamd_fwd_embed_meta(const void *table, const int32_t *meta, float *out, int blocks, int nseq); /* :594 */
+void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, float eps, int nseq); /* :280 */
+void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps); /* :287 */
+/* norm*w, then Q8_K of the result, one pass (:576). */
+void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n,
+                              float eps, int nseq);
+/* rope_tab: [max_pos][hd/2][2] (sin, cos) built by llamd_cuda_rope_table. */
+int llamd_cuda_rope_table(float *host_out, int max_pos, int hd, float freq_base);
+void llamd_fwd_rope(float *x, int pos, int n_head, int hd, const float *rope_tab);       /* :295 */
+void llamd_fwd_norm_rope(float *x, const float *w, int n_head, int hd, const int32_t *meta,
+                         const float *rope_tab, float eps, int nseq);                   /* :553 */
+void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float *kc, float *vc,
+                                 int n_head_kv, int hd, int kv_dim, const int32_t *meta,
+                                 const float *rope_tab, float eps, int nseq, int max_kv); /* :563 */
+void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, int pos, int kv_dim); /* :296 */
+void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float *out, float *scores,
+                         int n_head, int n_head_kv, int hd, int n_kv);                  /* :304 */
+void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out,
+                              float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                              int max_kv, int nseq);                                    /* :601 */
+void llamd_fwd_add(const float *a, const float *b, float *out, int n);                   /* :315 */
+void llamd_fwd_silu_mul(const float *gate, const float *up, float *out, int n);          /* :316 */
+/* silu(gate)*up, then Q8_K of the result (fuses :316 and :375). */
+void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, int8_t *qs, float *d, int n);
+void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *ids, float *weights,
+                      float *probs, int nseq);                                          /* :317 */
+void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd); /* :325 */
+void llamd_fwd_moe_combine_add(const float *down, const float *weights, const float *residual,
+                               float *out, int n_used, int n_embd, int nseq);           /* :586 */
+void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_i, int32_t *out,
+                      int nblocks, int nseq);                                           /* :332 */
+
+/* Expert scatter plan (crates/llamd-vulkan/shaders/moe_group.comp:40-82):
+ * counting sort of the nseq*n_used (token, slot) pairs by expert. Within an
+ * expert, pairs are in ascending pair order. */
+void llamd_fwd_moe_group(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart,
+                         int32_t *gcount, int32_t *ptoken, int32_t *pslot);
+/* Expert-major grouped matvec for many tokens (prefill): every expert with
+ * gcount>0 is read once for all its pairs. by_slot=0: activation of pair p is
+ * aq[ptoken[p]] (gate/up); by_slot=1: aq[pslot[p]] (down). Output row block
+ * pslot[p]: out[pslot[p]][rows]. Mirrors q6k_expert_major[_pa].comp. */
+void llamd_fwd_expert_major(const void *w, const int32_t *gstart, const int32_t *gcount,
+                            const int32_t *ptoken, const int32_t *pslot, const int8_t *aq,
+                            const float *ad, float *out, int blocks, int rows, int n_expert,
+                            int by_slot);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAMD_CUDA_H */

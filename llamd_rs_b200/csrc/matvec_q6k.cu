@@ -1,0 +1,287 @@
+// Q6_K x Q8_K matrix-vector product: the decode hot path.
+//
+// Arithmetic contract (crates/llamd-quant/src/dot.rs:138-196). For each row:
+//   per block b, eight integers  aux[r] = sum_g scale[g] * (a[16g+r]*w[16g+r] + a[16g+8+r]*w[16g+8+r])
+//   then  sums[r] += (f16(d_b) * ad_b) * (float)aux[r]   for b = 0, 1, ... in order
+//   then  y = ((((((s0+s1)+s2)+s3)+s4)+s5)+s6)+s7
+// The integers are exact in any order; the f32 tail is reproduced operation
+// for operation (separate multiply and add, no FMA), so y is bit-identical to
+// the reference's scalar loop.
+//
+// Mapping. One thread owns one (row, block) unit of the tiled weight layout
+// (q6k_layout.cuh): it streams 13 x 16 B + 2 B from HBM with fully coalesced
+// loads, unpacks residue by residue and forms its eight integers with dp4a
+// against activations staged in shared memory. A CTA of 256 threads covers
+// floor(256/blocks) whole rows. The per-unit f32 products go through shared
+// memory to the threads that walk the ordered sums.
+//
+// Activation staging: for block b and residue r the shared-memory image holds
+// eight word pairs (lo, hi): word j carries bytes a[e(r,j,0..3)] and lo / hi
+// keep bytes 0-1 / 2-3 only, so dp4a(W4_j, lo) and dp4a(W4_j, hi) are the two
+// per-group pair products (times 4, since W4 = 4*(q-32)).
+#include "q6k_layout.cuh"
+
+namespace llamd {
+
+constexpr int kThreads = 256;
+constexpr int kActBlockWords = 132;  // 128 + 4 padding words: conflict-free 16-byte reads across blocks
+constexpr int kExStride = 257;
+
+struct MatvecJob {
+    const uint8_t *w;  // tiled Q6_K
+    float *out;
+    int rows;          // rows per matrix (per expert)
+    int cta_begin;     // first CTA (within one slot) that works on this job
+};
+
+struct MatvecParams {
+    MatvecJob job[3];
+    int njobs;
+    int ctas_per_slot;     // sum over jobs of ceil(rows / rows_per_cta)
+    int nb;                // blocks per row
+    int rows_per_cta;
+    const int32_t *ids;    // [n_slots] expert ids, or null (ungrouped)
+    int n_slots;           // 1 when ids is null; nseq*n_used for a batched grouped launch
+    int n_expert;          // for the device-side id check
+    long long expert_units;  // blocks between consecutive experts in w
+    const int8_t *aq;      // activations: [nseq][nb*256] ungrouped, else indexed by slot / act_div
+    const float *ad;
+    int act_div;           // grouped: activation index = slot / act_div
+};
+
+// Unpack the four W4 words of quad m of residue r from the three stored words.
+__device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t w[4]) {
+    w[0] = s0 & 0xFCFCFCFCu;
+    w[1] = s1 & 0xFCFCFCFCu;
+    w[2] = s2 & 0xFCFCFCFCu;
+    const uint32_t u = ((s0 << 6) & 0xC0C0C0C0u) | ((s1 << 4) & 0x30303030u);
+    w[3] = u | ((s2 << 2) & 0x0C0C0C0Cu);
+}
+
+template <int NSEQ>
+__global__ void __launch_bounds__(kThreads) matvec_q6k_kernel(const MatvecParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int nb = p.nb;
+    // shared memory: [act: NSEQ*nb*132 words][ex: NSEQ*8*257 floats, aliased with the natural-order staging]
+    uint32_t *s_act = reinterpret_cast<uint32_t *>(smem);
+    float *s_ex = reinterpret_cast<float *>(smem + (size_t)NSEQ * nb * kActBlockWords * 4);
+    int8_t *s_nat = reinterpret_cast<int8_t *>(s_ex);
+
+    // ---- which job / slot / rows -------------------------------------
+    const int slot = blockIdx.x / p.ctas_per_slot;
+    const int cta = blockIdx.x - slot * p.ctas_per_slot;
+    int j = 0;
+    if (p.njobs > 1 && cta >= p.job[1].cta_begin) j = 1;
+    if (p.njobs > 2 && cta >= p.job[2].cta_begin) j = 2;
+    const MatvecJob job = p.job[j];
+    const int row0 = (cta - job.cta_begin) * p.rows_per_cta;
+    const int rows_here = min(p.rows_per_cta, job.rows - row0);
+    const int tid = threadIdx.x;
+    const bool active = tid < rows_here * nb;
+    const int row_l = tid / nb, b = tid - row_l * nb;
+
+    // expert id of this slot (grouped forms); an id outside the tensor reads
+    // expert 0: the host wrappers refuse such ids before any launch.
+    long long expert_off = 0;
+    if (p.ids) {
+        int e = p.ids[slot];
+        if (e < 0 || e >= p.n_expert) e = 0;
+        expert_off = (long long)e * p.expert_units;
+    }
+
+    // ---- issue the weight loads first: they stay in flight across the staging barrier
+    uint32_t S[48];
+    uint4 scw = make_uint4(0, 0, 0, 0);
+    uint16_t dbits = 0;
+    if (active) {
+        const size_t unit = (size_t)expert_off + (size_t)(row0 + row_l) * nb + b;
+        const uint8_t *tile = job.w + (unit >> 5) * kTileBytes;
+        const int sl = (int)(unit & 31);
+        const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl;
+#pragma unroll
+        for (int c = 0; c < 12; c++) {
+            const uint4 v = __ldg(cp + c * 32);
+            S[4 * c + 0] = v.x;
+            S[4 * c + 1] = v.y;
+            S[4 * c + 2] = v.z;
+            S[4 * c + 3] = v.w;
+        }
+        scw = __ldg(reinterpret_cast<const uint4 *>(tile + kTileScaleOff) + sl);
+        dbits = __ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl);
+    }
+
+    // ---- stage the activations ----------------------------------------
+    // natural order bytes first (coalesced 16-byte copies) ...
+    {
+        const int n16 = NSEQ * nb * 16;
+        for (int i = tid; i < n16; i += kThreads) {
+            const int s = i / (nb * 16), o = i - s * nb * 16;
+            const long long a_idx = p.ids ? slot / p.act_div : s;
+            reinterpret_cast<uint4 *>(s_nat)[i] = __ldg(reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o);
+        }
+    }
+    __syncthreads();
+    // ... then the residue-major (lo, hi) image
+    {
+        const int nitems = NSEQ * nb * 64;  // (s, b, r, j)
+        for (int i = tid; i < nitems; i += kThreads) {
+            const int jj = i & 7, r = (i >> 3) & 7, sb = i >> 6;
+            const int8_t *src = s_nat + sb * 256;
+            const uint32_t b0 = (uint8_t)src[t32_element(r, jj, 0)], b1 = (uint8_t)src[t32_element(r, jj, 1)];
+            const uint32_t b2 = (uint8_t)src[t32_element(r, jj, 2)], b3 = (uint8_t)src[t32_element(r, jj, 3)];
+            uint32_t *dst = s_act + sb * kActBlockWords + r * 16 + jj * 2;
+            dst[0] = b0 | (b1 << 8);
+            dst[1] = (b2 << 16) | (b3 << 24);
+        }
+    }
+    __syncthreads();  // s_nat is dead from here: s_ex may be written
+
+    // ---- integer core -----------------------------------------------------
+    if (active) {
+        int sc[16];
+        {
+            const uint32_t ws[4] = {scw.x, scw.y, scw.z, scw.w};
+#pragma unroll
+            for (int i = 0; i < 16; i++) sc[i] = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+        }
+        int aux[NSEQ][8];
+#pragma unroll
+        for (int s = 0; s < NSEQ; s++)
+#pragma unroll
+            for (int r = 0; r < 8; r++) aux[s][r] = 0;
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+#pragma unroll
+            for (int m = 0; m < 2; m++) {
+                uint32_t w4[4];
+                unpack_quad(S[6 * r + 3 * m], S[6 * r + 3 * m + 1], S[6 * r + 3 * m + 2], w4);
+#pragma unroll
+                for (int s = 0; s < NSEQ; s++) {
+                    const uint4 *ap = reinterpret_cast<const uint4 *>(s_act + (s * nb + b) * kActBlockWords + r * 16 + m * 8);
+                    const uint4 a01 = ap[0], a23 = ap[1];
+                    int acc = aux[s][r];
+                    acc += sc[8 * m + 0] * __dp4a((int)w4[0], (int)a01.x, 0);
+                    acc += sc[8 * m + 1] * __dp4a((int)w4[0], (int)a01.y, 0);
+                    acc += sc[8 * m + 2] * __dp4a((int)w4[1], (int)a01.z, 0);
+                    acc += sc[8 * m + 3] * __dp4a((int)w4[1], (int)a01.w, 0);
+                    acc += sc[8 * m + 4] * __dp4a((int)w4[2], (int)a23.x, 0);
+                    acc += sc[8 * m + 5] * __dp4a((int)w4[2], (int)a23.y, 0);
+                    acc += sc[8 * m + 6] * __dp4a((int)w4[3], (int)a23.z, 0);
+                    acc += sc[8 * m + 7] * __dp4a((int)w4[3], (int)a23.w, 0);
+                    aux[s][r] = acc;
+                }
+            }
+        }
+        const float dw = f16_bits_to_f32(dbits);
+#pragma unroll
+        for (int s = 0; s < NSEQ; s++) {
+            const long long a_idx = p.ids ? slot / p.act_div : s;
+            const float dsc = __fmul_rn(dw, __ldg(p.ad + a_idx * nb + b));
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+                s_ex[(s * 8 + r) * kExStride + tid] = __fmul_rn(dsc, (float)(aux[s][r] >> 2));
+        }
+    }
+    __syncthreads();
+
+    // ---- ordered f32 tail ---------------------------------------------------
+    // thread (row_l, r) adds the blocks in order; then the eight residues are
+    // added in order across the 8 adjacent lanes.
+    const int n_out = rows_here * 8;
+    for (int base = 0; base < n_out; base += kThreads) {
+        const int idx = base + tid;
+        const bool on = idx < n_out;
+        const int rl = idx >> 3, r = idx & 7;
+#pragma unroll
+        for (int s = 0; s < NSEQ; s++) {
+            float acc = 0.0f;
+            if (on) {
+                const float *ex = s_ex + (s * 8 + r) * kExStride + rl * nb;
+                for (int bb = 0; bb < nb; bb++) acc = __fadd_rn(acc, ex[bb]);
+            }
+            const int lane0 = (tid & 31) & ~7;
+            float total = __shfl_sync(0xffffffffu, acc, lane0);
+#pragma unroll
+            for (int rr = 1; rr < 8; rr++) total = __fadd_rn(total, __shfl_sync(0xffffffffu, acc, lane0 + rr));
+            // ungrouped: out[seq][rows]; grouped: out[slot][rows]
+            if (on && r == 0) job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
+        }
+    }
+}
+
+static size_t matvec_smem_bytes(int nseq, int nb) {
+    const size_t act = (size_t)nseq * nb * kActBlockWords * 4;
+    const size_t ex = (size_t)nseq * 8 * kExStride * 4;
+    const size_t nat = (size_t)nseq * nb * 256;
+    return act + (ex > nat ? ex : nat);
+}
+
+template <int NSEQ>
+static void launch_t(const MatvecParams &p, int grid) {
+    const size_t smem = matvec_smem_bytes(NSEQ, p.nb);
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(matvec_q6k_kernel<NSEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error(e, "matvec smem attribute");
+            return;
+        }
+        configured = smem;
+    }
+    matvec_q6k_kernel<NSEQ><<<grid, kThreads, smem, stream()>>>(p);
+    LLAMD_CHECK_LAUNCH("matvec_q6k");
+}
+
+// Build the launch. `rows[i]`/`w[i]`/`out[i]` describe up to three matrices
+// that share the activation (q,k,v or gate,up). Ungrouped (ids == null): nseq
+// activations, outputs [nseq][rows]. Grouped: n_slots expert ids, activation of
+// slot s is index s / act_div, outputs [n_slots][rows]; nseq must be 1.
+void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
+                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div) {
+    if (blocks <= 0 || blocks > kThreads || nseq < 1 || nseq > LLAMD_MAX_SEQ || njobs < 1 || njobs > 3 || (ids && nseq != 1) ||
+        (ids && (n_slots < 1 || act_div < 1))) {
+        set_error_msg("matvec: blocks must be 1..256, nseq 1..8, 1..3 matrices");
+        return;
+    }
+    if (matvec_smem_bytes(nseq, blocks) > 200 * 1024) {
+        set_error_msg("matvec: blocks x nseq does not fit shared memory");
+        return;
+    }
+    MatvecParams p = {};
+    p.njobs = njobs;
+    p.nb = blocks;
+    p.rows_per_cta = kThreads / blocks;
+    int cta = 0;
+    for (int i = 0; i < njobs; i++) {
+        if (rows[i] <= 0 || (ids && rows[i] != rows[0])) {
+            set_error_msg("matvec: rows must be positive (and equal across a grouped launch)");
+            return;
+        }
+        p.job[i].w = (const uint8_t *)w[i];
+        p.job[i].out = out[i];
+        p.job[i].rows = rows[i];
+        p.job[i].cta_begin = cta;
+        cta += (rows[i] + p.rows_per_cta - 1) / p.rows_per_cta;
+    }
+    p.ctas_per_slot = cta;
+    p.ids = ids;
+    p.n_slots = ids ? n_slots : 1;
+    p.n_expert = n_expert;
+    p.expert_units = (long long)rows[0] * blocks;  // experts are `rows` rows apart in the reference order
+    p.aq = aq;
+    p.ad = ad;
+    p.act_div = act_div < 1 ? 1 : act_div;
+    const int grid = p.ctas_per_slot * p.n_slots;
+    switch (nseq) {
+    case 1: launch_t<1>(p, grid); break;
+    case 2: launch_t<2>(p, grid); break;
+    case 3: launch_t<3>(p, grid); break;
+    case 4: launch_t<4>(p, grid); break;
+    case 5: launch_t<5>(p, grid); break;
+    case 6: launch_t<6>(p, grid); break;
+    case 7: launch_t<7>(p, grid); break;
+    default: launch_t<8>(p, grid); break;
+    }
+}
+
+}  // namespace llamd

@@ -1,0 +1,569 @@
+// The f32 ops around the quantized matvecs: router, f32 and Q8_0 matvec,
+// QK-norm + RoPE + KV store, attention, argmax and the expert scatter plan.
+//
+// Reductions whose order is observable in the reference (sequential f32 sums)
+// are walked in that order by one thread; everything that is order-free (max,
+// integer counts) is done in parallel.
+#include <math.h>
+
+#include <vector>
+
+#include "q6k_layout.cuh"
+
+namespace llamd {
+
+__device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
+
+#define WEIGHT_SUM_FLOOR 6.103515625e-5f  // 2^-14, crates/llamd-models/src/moe.rs:50
+
+// ---- f32 matvec: crates/llamd-models/src/model.rs:253-263 -----------------
+// y[row] = fold(-0.0, +) of w[row][t]*x[t], t ascending. wt is [k][rows] so a
+// warp reads one contiguous run per step. One thread per row.
+__device__ __forceinline__ float dot_sequential_t(const float *__restrict__ wt, const float *__restrict__ sx, int k, int rows, int row) {
+    float acc = -0.0f;
+#pragma unroll 8
+    for (int t = 0; t < k; t++) acc = __fadd_rn(acc, __fmul_rn(wt[(size_t)t * rows + row], sx[t]));
+    return acc;
+}
+
+__global__ void matvec_f32_kernel(const float *__restrict__ wt, const float *__restrict__ x, float *__restrict__ out, int k, int rows) {
+    extern __shared__ float sx[];
+    const int seq = blockIdx.y;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) sx[i] = x[(size_t)seq * k + i];
+    __syncthreads();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row < rows) out[(size_t)seq * rows + row] = dot_sequential_t(wt, sx, k, rows, row);
+}
+
+// ---- route: crates/llamd-models/src/moe.rs:73-113 --------------------------
+// One CTA per sequence, blockDim >= n_expert (<= 1024). s_p holds the logits
+// on entry and the probabilities on exit.
+__device__ void route_block(float *s_p, float *s_red, int *s_redi, int n_expert, int n_used, int32_t *__restrict__ ids,
+                            float *__restrict__ weights, float *__restrict__ probs) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
+    // max is order-free
+    float m = tid < n_expert ? s_p[tid] : -INFINITY;
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    m = s_red[0];
+    for (int w = 1; w < nwarps; w++) m = fmaxf(m, s_red[w]);
+    __syncthreads();
+    if (tid < n_expert) s_p[tid] = ref_expf(__fsub_rn(s_p[tid], m));
+    __syncthreads();
+    // probs.iter().sum(): left to right from -0.0
+    if (tid == 0) {
+        float total = -0.0f;
+        for (int i = 0; i < n_expert; i++) total = __fadd_rn(total, s_p[i]);
+        s_red[32] = total;
+    }
+    __syncthreads();
+    const float total = s_red[32];
+    float p = -INFINITY;
+    if (tid < n_expert) {
+        p = __fdiv_rn(s_p[tid], total);
+        s_p[tid] = p;
+        if (probs) probs[tid] = p;
+    }
+    __syncthreads();
+    // n_used rounds of arg-max: probability descending, index ascending
+    for (int k = 0; k < n_used; k++) {
+        float bv = p;
+        int bi = tid < n_expert ? tid : 0x7fffffff;
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            s_red[warp] = bv;
+            s_redi[warp] = bi;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float v = s_red[0];
+            int ix = s_redi[0];
+            for (int w = 1; w < nwarps; w++)
+                if (s_red[w] > v || (s_red[w] == v && s_redi[w] < ix)) {
+                    v = s_red[w];
+                    ix = s_redi[w];
+                }
+            s_redi[40 + k] = ix;
+            s_red[40 + k] = v;
+        }
+        __syncthreads();
+        if (tid == s_redi[40 + k]) p = -INFINITY;  // taken: cannot win again
+        __syncthreads();
+    }
+    if (tid == 0) {
+        float sum = -0.0f;
+        for (int k = 0; k < n_used; k++) sum = __fadd_rn(sum, s_red[40 + k]);
+        sum = fmaxf(sum, WEIGHT_SUM_FLOOR);
+        for (int k = 0; k < n_used; k++) {
+            ids[k] = s_redi[40 + k];
+            weights[k] = __fdiv_rn(s_red[40 + k], sum);
+        }
+    }
+}
+
+constexpr int kMaxUsed = 64;
+
+__global__ void router_kernel(const float *__restrict__ logits, int n_expert, int n_used, int32_t *__restrict__ ids,
+                              float *__restrict__ weights, float *__restrict__ probs) {
+    extern __shared__ float s_p[];
+    __shared__ float s_red[40 + kMaxUsed];
+    __shared__ int s_redi[40 + kMaxUsed];
+    const int seq = blockIdx.x;
+    if (threadIdx.x < n_expert) s_p[threadIdx.x] = logits[(size_t)seq * n_expert + threadIdx.x];
+    __syncthreads();
+    route_block(s_p, s_red, s_redi, n_expert, n_used, ids + (size_t)seq * n_used, weights + (size_t)seq * n_used,
+                probs ? probs + (size_t)seq * n_expert : nullptr);
+}
+
+// Router logits and routing in one launch: the f32 matvec above, then route.
+__global__ void router_matvec_kernel(const float *__restrict__ wt, const float *__restrict__ x, int k, int n_expert, int n_used,
+                                     float *__restrict__ logits_out, int32_t *__restrict__ ids, float *__restrict__ weights,
+                                     float *__restrict__ probs) {
+    extern __shared__ float sm[];
+    float *sx = sm, *s_p = sm + k;
+    __shared__ float s_red[40 + kMaxUsed];
+    __shared__ int s_redi[40 + kMaxUsed];
+    const int seq = blockIdx.x;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) sx[i] = x[(size_t)seq * k + i];
+    __syncthreads();
+    if (threadIdx.x < n_expert) {
+        const float l = dot_sequential_t(wt, sx, k, n_expert, threadIdx.x);
+        s_p[threadIdx.x] = l;
+        if (logits_out) logits_out[(size_t)seq * n_expert + threadIdx.x] = l;
+    }
+    __syncthreads();
+    route_block(s_p, s_red, s_redi, n_expert, n_used, ids + (size_t)seq * n_used, weights + (size_t)seq * n_used,
+                probs ? probs + (size_t)seq * n_expert : nullptr);
+}
+
+// ---- Q8_0 matvec: dequantize (d*q) then the sequential f32 dot -------------
+// (crates/llamd-quant/src/lib.rs:154-162 + crates/llamd-models/src/model.rs:253-263)
+template <int NSEQ>
+__global__ void __launch_bounds__(128) matvec_q8_0_kernel(const uint8_t *__restrict__ tiled, const float *__restrict__ x,
+                                                          float *__restrict__ out, int blocks, int rows) {
+    extern __shared__ float sx[];  // [NSEQ][k]
+    const int k = blocks * 32;
+    for (int i = threadIdx.x; i < NSEQ * k; i += blockDim.x) sx[i] = x[i];
+    __syncthreads();
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    const int lane = row & 31;
+    float acc[NSEQ];
+#pragma unroll
+    for (int s = 0; s < NSEQ; s++) acc[s] = -0.0f;
+    const uint8_t *t = tiled + q80_tile_offset(row, 0, blocks);
+    uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(t) + lane), q1 = __ldg(reinterpret_cast<const uint4 *>(t + 512) + lane);
+    uint16_t db = __ldg(reinterpret_cast<const uint16_t *>(t + 1024) + lane);
+    for (int b = 0; b < blocks; b++) {
+        const uint4 c0 = q0, c1 = q1;
+        const float d = f16_bits_to_f32(db);
+        if (b + 1 < blocks) {
+            t += kQ80TileBytes;
+            q0 = __ldg(reinterpret_cast<const uint4 *>(t) + lane);
+            q1 = __ldg(reinterpret_cast<const uint4 *>(t + 512) + lane);
+            db = __ldg(reinterpret_cast<const uint16_t *>(t + 1024) + lane);
+        }
+        const uint32_t ws[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float w = __fmul_rn(d, (float)(int8_t)(ws[j >> 2] >> (8 * (j & 3))));
+#pragma unroll
+            for (int s = 0; s < NSEQ; s++) acc[s] = __fadd_rn(acc[s], __fmul_rn(w, sx[s * k + b * 32 + j]));
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < NSEQ; s++) out[(size_t)s * rows + row] = acc[s];
+}
+
+// ---- QK-norm + RoPE (+ KV store) -----------------------------------------
+// crates/llamd-runtime/src/layer.rs:120-153, crates/llamd-cpu/src/lib.rs:158-209.
+// One CTA of hd/2 threads per head; thread 0 walks the sum of squares. The
+// sin/cos come from a table the host built with its own libm, which is what
+// the reference's CPU path calls (powf, sin, cos).
+__global__ void norm_rope_kernel(float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ v_src,
+                                 float *__restrict__ kc, float *__restrict__ vc, int n_head, int hd, const int32_t *__restrict__ meta,
+                                 int pos_imm, const float *__restrict__ rope_tab, float eps, int max_kv) {
+    extern __shared__ float sx[];
+    __shared__ float s_scale;
+    const int head = blockIdx.x, seq = blockIdx.y, half = hd / 2, i = threadIdx.x;
+    const int pos = meta ? meta[2 * seq + 1] : pos_imm;
+    float *xh = x + ((size_t)seq * n_head + head) * hd;
+    sx[i] = xh[i];
+    sx[i + half] = xh[i + half];
+    __syncthreads();
+    float scale = 1.0f;
+    if (w) {
+        if (i == 0) {
+            float sum = 0.0f;
+#pragma unroll 8
+            for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
+            s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), eps)));
+        }
+        __syncthreads();
+        scale = s_scale;
+    }
+    float a = sx[i], b = sx[i + half];
+    if (w) {
+        a = __fmul_rn(__fmul_rn(a, scale), w[i]);
+        b = __fmul_rn(__fmul_rn(b, scale), w[i + half]);
+    }
+    const float2 sc = *reinterpret_cast<const float2 *>(rope_tab + ((size_t)pos * half + i) * 2);
+    const float o0 = __fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x));
+    const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
+    xh[i] = o0;
+    xh[i + half] = o1;
+    if (kc) {
+        const int kv_dim = n_head * hd;
+        float *kdst = kc + ((size_t)seq * max_kv + pos) * kv_dim + (size_t)head * hd;
+        float *vdst = vc + ((size_t)seq * max_kv + pos) * kv_dim + (size_t)head * hd;
+        const float *vs = v_src + ((size_t)seq * n_head + head) * hd;
+        kdst[i] = o0;
+        kdst[i + half] = o1;
+        vdst[i] = vs[i];
+        vdst[i + half] = vs[i + half];
+    }
+}
+
+__global__ void kv_store_kernel(float *__restrict__ kc, float *__restrict__ vc, const float *__restrict__ k, const float *__restrict__ v,
+                                int pos, int kv_dim) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < kv_dim) {
+        kc[(size_t)pos * kv_dim + i] = k[i];
+        vc[(size_t)pos * kv_dim + i] = v[i];
+    }
+}
+
+// ---- attention: crates/llamd-runtime/src/attention.rs:62-125 ---------------
+// One CTA per (query head, sequence). Scores live in shared memory.
+//   logit[t] = (sum_d q[d]*k[t][d], d ascending) * scale      thread per t
+//   max (order-free), e[t] = exp(logit[t]-max), sum e[t] t ascending (thread 0)
+//   out[d] = sum_t (e[t]*inv) * v[t][d], t ascending            thread per d
+__global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+                                                        const float *__restrict__ vc, float *__restrict__ out, int n_head, int n_head_kv,
+                                                        int hd, const int32_t *__restrict__ meta, int n_kv_imm, int max_kv) {
+    extern __shared__ float sm[];
+    float *sq = sm, *sl = sm + hd;
+    __shared__ float s_red[8];
+    const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
+    const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
+    const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
+    const float *kb = kc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
+    const float *vb = vc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
+    const float *qh = q + ((size_t)seq * n_head + h) * hd;
+    for (int i = tid; i < hd; i += blockDim.x) sq[i] = qh[i];
+    __syncthreads();
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    float lmax = -INFINITY;
+    for (int t = tid; t < n_kv; t += blockDim.x) {
+        const float4 *kr = reinterpret_cast<const float4 *>(kb + (size_t)t * kv_dim);
+        float dot = 0.0f;
+        for (int d4 = 0; d4 < hd / 4; d4++) {
+            const float4 kv4 = __ldg(kr + d4);
+            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 0], kv4.x));
+            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 1], kv4.y));
+            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 2], kv4.z));
+            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 3], kv4.w));
+        }
+        const float l = __fmul_rn(dot, scale);
+        sl[t] = l;
+        lmax = fmaxf(lmax, l);
+    }
+    for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
+    if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
+    __syncthreads();
+    lmax = s_red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) lmax = fmaxf(lmax, s_red[w]);
+    for (int t = tid; t < n_kv; t += blockDim.x) sl[t] = ref_expf(__fsub_rn(sl[t], lmax));
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.0f;
+#pragma unroll 8
+        for (int t = 0; t < n_kv; t++) sum = __fadd_rn(sum, sl[t]);
+        s_red[4] = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    const float inv = s_red[4];
+    for (int d = tid; d < hd; d += blockDim.x) {
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int t = 0; t < n_kv; t++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t], inv), __ldg(vb + (size_t)t * kv_dim + d)));
+        out[((size_t)seq * n_head + h) * hd + d] = acc;
+    }
+}
+
+// ---- argmax, lowest index on a tie (llamd_forward.hip:353-389) -------------
+__device__ __forceinline__ void argmax_combine(float &v, int &i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) {
+        v = ov;
+        i = oi;
+    }
+}
+__global__ void argmax_partial_kernel(const float *__restrict__ x, int n, float *__restrict__ pv, int32_t *__restrict__ pi) {
+    const int seq = blockIdx.y;
+    x += (size_t)seq * n;
+    float v = -INFINITY;
+    int ix = 0x7fffffff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) argmax_combine(v, ix, x[i], i);
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    for (int off = 16; off > 0; off >>= 1) argmax_combine(v, ix, __shfl_xor_sync(0xffffffffu, v, off), __shfl_xor_sync(0xffffffffu, ix, off));
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = v;
+        si[threadIdx.x >> 5] = ix;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) argmax_combine(v, ix, sv[w], si[w]);
+        pv[(size_t)seq * gridDim.x + blockIdx.x] = v;
+        pi[(size_t)seq * gridDim.x + blockIdx.x] = ix;
+    }
+}
+__global__ void argmax_final_kernel(const float *__restrict__ pv, const int32_t *__restrict__ pi, int nblocks, int32_t *__restrict__ out) {
+    const int seq = blockIdx.x;
+    float v = -INFINITY;
+    int ix = 0x7fffffff;
+    for (int i = threadIdx.x; i < nblocks; i += blockDim.x) argmax_combine(v, ix, pv[(size_t)seq * nblocks + i], pi[(size_t)seq * nblocks + i]);
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    for (int off = 16; off > 0; off >>= 1) argmax_combine(v, ix, __shfl_xor_sync(0xffffffffu, v, off), __shfl_xor_sync(0xffffffffu, ix, off));
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = v;
+        si[threadIdx.x >> 5] = ix;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) argmax_combine(v, ix, sv[w], si[w]);
+        out[seq] = ix == 0x7fffffff ? 0 : ix;
+    }
+}
+
+// ---- expert scatter plan (crates/llamd-vulkan/shaders/moe_group.comp:40-82) --
+// Counting sort of the (token, slot) pairs by expert. Thread e scans the pair
+// list, so pairs of one expert come out in ascending pair order (the shader
+// leaves that order unspecified; a fixed order makes runs reproducible).
+// Also emits the work list the expert-major matvec walks: entries of up to 8
+// pairs of one expert, (expert, first, count), and their number.
+__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, int npair, int n_used, int32_t *__restrict__ gstart,
+                                 int32_t *__restrict__ gcount, int32_t *__restrict__ ptoken, int32_t *__restrict__ pslot,
+                                 int32_t *__restrict__ work, int32_t *__restrict__ n_work) {
+    extern __shared__ int s_ids[];
+    __shared__ int s_start[1024];
+    __shared__ int s_wstart[1024];
+    const int e = threadIdx.x;
+    for (int p = threadIdx.x; p < npair; p += blockDim.x) s_ids[p] = ids[p];
+    __syncthreads();
+    int count = 0;
+    if (e < n_expert)
+        for (int p = 0; p < npair; p++) count += (s_ids[p] == e);
+    if (e < n_expert) s_start[e] = count;
+    __syncthreads();
+    if (e == 0) {
+        int run = 0, wrun = 0;
+        for (int i = 0; i < n_expert; i++) {
+            const int c = s_start[i];
+            s_start[i] = run;
+            s_wstart[i] = wrun;
+            run += c;
+            wrun += (c + 7) / 8;
+        }
+        if (n_work) *n_work = wrun;
+    }
+    __syncthreads();
+    if (e < n_expert) {
+        const int start = s_start[e];
+        int at = start;
+        for (int p = 0; p < npair; p++)
+            if (s_ids[p] == e) {
+                ptoken[at] = p / n_used;
+                pslot[at] = p;
+                at++;
+            }
+        gstart[e] = start;
+        gcount[e] = count;
+        if (work) {
+            int wi = s_wstart[e];
+            for (int f = 0; f < count; f += 8, wi++) {
+                work[3 * wi + 0] = e;
+                work[3 * wi + 1] = start + f;
+                work[3 * wi + 2] = min(8, count - f);
+            }
+        }
+    }
+}
+
+}  // namespace llamd
+
+using namespace llamd;
+
+extern "C" {
+
+void llamd_fwd_matvec_f32_batch(const float *wt, const float *x, float *out, int k, int rows, int nseq) {
+    matvec_f32_kernel<<<dim3((rows + 127) / 128, nseq), 128, k * sizeof(float), stream()>>>(wt, x, out, k, rows);
+    LLAMD_CHECK_LAUNCH("matvec_f32");
+}
+void llamd_fwd_matvec_f32(const float *wt, const float *x, float *out, int k, int rows) {
+    llamd_fwd_matvec_f32_batch(wt, x, out, k, rows, 1);
+}
+
+void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *ids, float *weights, float *probs, int nseq) {
+    if (n_expert < 1 || n_expert > 1024 || n_used < 1 || n_used > n_expert || n_used > kMaxUsed) {
+        set_error_msg("router: n_expert must be 1..1024 and n_used 1..min(n_expert,64)");
+        return;
+    }
+    const int threads = ((n_expert + 31) / 32) * 32;
+    router_kernel<<<nseq, threads, n_expert * sizeof(float), stream()>>>(logits, n_expert, n_used, ids, weights, probs);
+    LLAMD_CHECK_LAUNCH("router");
+}
+// The router's f32 matvec (forward.rs:340) and routing (:317) in one launch.
+void llamd_fwd_router_matvec(const float *wt, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
+                             float *weights, float *probs, int nseq) {
+    if (n_expert < 1 || n_expert > 1024 || n_used < 1 || n_used > n_expert || n_used > kMaxUsed) {
+        set_error_msg("router: n_expert must be 1..1024 and n_used 1..min(n_expert,64)");
+        return;
+    }
+    const int threads = ((n_expert + 31) / 32) * 32;
+    router_matvec_kernel<<<nseq, threads, (k + n_expert) * sizeof(float), stream()>>>(wt, x, k, n_expert, n_used, logits, ids, weights, probs);
+    LLAMD_CHECK_LAUNCH("router_matvec");
+}
+
+void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq) {
+    const dim3 grid((rows + 127) / 128);
+    const size_t smem = (size_t)nseq * blocks32 * 32 * sizeof(float);
+    if (nseq < 1 || nseq > LLAMD_MAX_SEQ || smem > 200 * 1024) {
+        set_error_msg("matvec_q8_0: nseq 1..8 and nseq*k*4 <= 200 KiB");
+        return;
+    }
+    const uint8_t *t = (const uint8_t *)w;
+#define Q80_CASE(N)                                                                                                   \
+    case N: {                                                                                                          \
+        static size_t configured = 0;                                                                                  \
+        if (smem > 48 * 1024 && smem > configured) {                                                                   \
+            cudaFuncSetAttribute(matvec_q8_0_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+            configured = smem;                                                                                         \
+        }                                                                                                              \
+        matvec_q8_0_kernel<N><<<grid, 128, smem, stream()>>>(t, x, out, blocks32, rows);                               \
+    } break;
+    switch (nseq) {
+        Q80_CASE(1) Q80_CASE(2) Q80_CASE(3) Q80_CASE(4) Q80_CASE(5) Q80_CASE(6) Q80_CASE(7) Q80_CASE(8)
+    }
+#undef Q80_CASE
+    LLAMD_CHECK_LAUNCH("matvec_q8_0");
+}
+
+// sin/cos for every (pos, i), computed with the host libm exactly as the
+// reference's CPU rope does (crates/llamd-cpu/src/lib.rs:196-200).
+int llamd_cuda_rope_table(float *host_out, int max_pos, int hd, float freq_base) {
+    if (!host_out || max_pos <= 0 || hd <= 0 || hd % 2) return -1;
+    const int half = hd / 2;
+    for (int p = 0; p < max_pos; p++) {
+        const float pos = (float)(uint32_t)p * 1.0f;
+        for (int i = 0; i < half; i++) {
+            const float exponent = 2.0f * (float)i / (float)hd;
+            const float theta = pos / powf(freq_base, exponent);
+            host_out[((size_t)p * half + i) * 2 + 0] = sinf(theta);
+            host_out[((size_t)p * half + i) * 2 + 1] = cosf(theta);
+        }
+    }
+    return 0;
+}
+
+void llamd_fwd_rope(float *x, int pos, int n_head, int hd, const float *rope_tab) {
+    norm_rope_kernel<<<dim3(n_head, 1), hd / 2, hd * sizeof(float), stream()>>>(x, nullptr, nullptr, nullptr, nullptr, n_head, hd, nullptr,
+                                                                               pos, rope_tab, 0.0f, 0);
+    LLAMD_CHECK_LAUNCH("rope");
+}
+void llamd_fwd_norm_rope(float *x, const float *w, int n_head, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq) {
+    norm_rope_kernel<<<dim3(n_head, nseq), hd / 2, hd * sizeof(float), stream()>>>(x, w, nullptr, nullptr, nullptr, n_head, hd, meta, 0,
+                                                                                  rope_tab, eps, 0);
+    LLAMD_CHECK_LAUNCH("norm_rope");
+}
+void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float *kc, float *vc, int n_head_kv, int hd, int kv_dim,
+                                 const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv) {
+    if (kv_dim != n_head_kv * hd) {
+        set_error_msg("k_norm_rope_store: kv_dim != n_head_kv*hd");
+        return;
+    }
+    norm_rope_kernel<<<dim3(n_head_kv, nseq), hd / 2, hd * sizeof(float), stream()>>>(k, w, v, kc, vc, n_head_kv, hd, meta, 0, rope_tab, eps,
+                                                                                     max_kv);
+    LLAMD_CHECK_LAUNCH("k_norm_rope_store");
+}
+void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, int pos, int kv_dim) {
+    kv_store_kernel<<<(kv_dim + 255) / 256, 256, 0, stream()>>>(kc, vc, k, v, pos, kv_dim);
+    LLAMD_CHECK_LAUNCH("kv_store");
+}
+
+static void attention_launch(const float *q, const float *kc, const float *vc, float *out, int n_head, int n_head_kv, int hd,
+                             const int32_t *meta, int n_kv, int max_kv, int nseq) {
+    const size_t smem = (size_t)(hd + max_kv) * sizeof(float);
+    if (hd % 4 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
+        set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
+        return;
+    }
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error(e, "attention smem attribute");
+            return;
+        }
+        configured = smem;
+    }
+    attention_kernel<<<dim3(n_head, nseq), 128, smem, stream()>>>(q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
+    LLAMD_CHECK_LAUNCH("attention");
+}
+// `scores` is accepted for signature parity with the reference and unused:
+// the scores stay in shared memory.
+void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
+                         int n_kv) {
+    (void)scores;
+    attention_launch(q, kc, vc, out, n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1);
+}
+void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
+                              int hd, const int32_t *meta, int max_kv, int nseq) {
+    (void)scores;
+    attention_launch(q, kc, vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, nseq);
+}
+
+void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_i, int32_t *out, int nblocks, int nseq) {
+    if (nblocks < 1) nblocks = 1;
+    argmax_partial_kernel<<<dim3(nblocks, nseq), 256, 0, stream()>>>(x, n, scratch_v, scratch_i);
+    LLAMD_CHECK_LAUNCH("argmax_partial");
+    argmax_final_kernel<<<nseq, 256, 0, stream()>>>(scratch_v, scratch_i, nblocks, out);
+    LLAMD_CHECK_LAUNCH("argmax_final");
+}
+
+void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
+                              int32_t *ptoken, int32_t *pslot, int32_t *work, int32_t *n_work) {
+    const int npair = n_used * nseq;
+    if (n_expert < 1 || n_expert > 1024 || npair < 0 || (size_t)npair * 4 > 160 * 1024) {
+        set_error_msg("moe_group: n_expert 1..1024 and at most 40960 pairs per call");
+        return;
+    }
+    const int threads = ((n_expert + 31) / 32) * 32;
+    const size_t smem = (size_t)npair * sizeof(int);
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(moe_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error(e, "moe_group smem attribute");
+            return;
+        }
+        configured = smem;
+    }
+    moe_group_kernel<<<1, threads, smem, stream()>>>(ids, n_expert, npair, n_used, gstart, gcount, ptoken, pslot, work, n_work);
+    LLAMD_CHECK_LAUNCH("moe_group");
+}
+void llamd_fwd_moe_group(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount, int32_t *ptoken,
+                         int32_t *pslot) {
+    llamd_fwd_moe_group_work(ids, n_expert, n_used, nseq, gstart, gcount, ptoken, pslot, nullptr, nullptr);
+}
+
+}  // extern "C"

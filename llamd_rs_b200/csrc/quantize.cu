@@ -1,0 +1,262 @@
+// Q8_K activation quantizer and the small f32 ops that feed it.
+//
+// Everything here reproduces the reference's scalar f32 arithmetic in its
+// order (no FMA contraction, no reassociation), because each value ends up in
+// an int8 quant or a routing decision where the last bit is observable.
+#include "common.cuh"
+
+namespace llamd {
+
+// The reference calls Rust's f32::exp, i.e. the host libm's expf. Here the
+// exponential is evaluated in double and rounded once to f32.
+__device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
+
+// ---- Q8_K: crates/llamd-quant/src/dot.rs:88-128 ---------------------------
+// One warp per 256-element block; lane l owns elements 8l..8l+7.
+// Produces qs[256] (natural order), d and optionally bsums[16].
+__device__ __forceinline__ void q8k_quantize_block(const float v[8], int lane, int8_t *__restrict__ qs, float *__restrict__ d_out,
+                                                   int16_t *__restrict__ bsums) {
+    // the SIGNED value at the largest magnitude, first such element
+    float amax = 0.0f, mx = 0.0f;
+    int idx = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float a = fabsf(v[i]);
+        if (a > amax) {
+            amax = a;
+            mx = v[i];
+            idx = lane * 8 + i;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
+        const float om = __shfl_xor_sync(0xffffffffu, mx, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+        if (oa > amax || (oa == amax && oi < idx)) {
+            amax = oa;
+            mx = om;
+            idx = oi;
+        }
+    }
+    int q[8];
+    float dd = 0.0f;
+    if (amax == 0.0f) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) q[i] = 0;
+    } else {
+        const float iscale = __fdiv_rn(-127.0f, mx);
+#pragma unroll
+        for (int i = 0; i < 8; i++) q[i] = min(127, __float2int_rn(__fmul_rn(iscale, v[i])));
+        dd = __fdiv_rn(1.0f, iscale);
+    }
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        w0 |= ((uint32_t)q[i] & 0xFFu) << (8 * i);
+        w1 |= ((uint32_t)q[4 + i] & 0xFFu) << (8 * i);
+    }
+    *reinterpret_cast<uint2 *>(qs + lane * 8) = make_uint2(w0, w1);
+    if (lane == 0) *d_out = dd;
+    if (bsums) {
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) s += q[i];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if ((lane & 1) == 0) bsums[lane >> 1] = (int16_t)s;
+    }
+}
+
+__global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restrict__ x, int8_t *__restrict__ qs, float *__restrict__ d,
+                                                           int16_t *__restrict__ bsums, int nblocks) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= nblocks) return;
+    const float4 *p = reinterpret_cast<const float4 *>(x + (size_t)warp * 256 + lane * 8);
+    const float4 a = p[0], b = p[1];
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    q8k_quantize_block(v, lane, qs + (size_t)warp * 256, d + warp, bsums ? bsums + (size_t)warp * 16 : nullptr);
+}
+
+// ---- rms_norm: crates/llamd-cpu/src/lib.rs:55-75, then `* w` --------------
+// The sum of squares is a left-to-right f32 chain in the reference; thread 0
+// walks it from shared memory while the other threads wait. One CTA per row.
+__device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ sx, int n, float eps) {
+    float sum = 0.0f;
+#pragma unroll 8
+    for (int i = 0; i < n; i++) sum = __fadd_rn(sum, __fmul_rn(sx[i], sx[i]));
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+}
+
+// out = (x*scale)*w ; optionally Q8_K of out. Dynamic smem: n floats.
+// `residual`/`sum_out`: when given, x := x + residual first (the attention
+// residual, crates/llamd-runtime/src/layer.rs:170) and is written to sum_out.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
+                                                       float *__restrict__ sum_out, const float *__restrict__ w, float *__restrict__ out,
+                                                       int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps) {
+    extern __shared__ float sx[];
+    __shared__ float s_scale;
+    const int seq = blockIdx.x;
+    x += (size_t)seq * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = x[i];
+        if (residual) {
+            v = __fadd_rn(v, residual[(size_t)seq * n + i]);
+            sum_out[(size_t)seq * n + i] = v;
+        }
+        sx[i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_scale = rms_scale_sequential(sx, n, eps);
+    __syncthreads();
+    const float scale = s_scale;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float o = __fmul_rn(__fmul_rn(sx[i], scale), w[i]);
+        sx[i] = o;
+        if (out) out[(size_t)seq * n + i] = o;
+    }
+    if (!qs) return;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int b = warp; b < n / 256; b += nwarps) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = sx[b * 256 + lane * 8 + i];
+        q8k_quantize_block(v, lane, qs + (size_t)seq * n + (size_t)b * 256, d + (size_t)seq * (n / 256) + b, nullptr);
+    }
+}
+
+// Per-head norm (crates/llamd-runtime/src/layer.rs:62-79): one warp per head,
+// lane 0 walks the chain.
+__global__ void head_rms_norm_mul_kernel(const float *__restrict__ x, const float *__restrict__ w, float *__restrict__ out, int n_head,
+                                         int hd, float eps) {
+    const int head = blockIdx.x;
+    if (head >= n_head) return;
+    extern __shared__ float sx[];
+    __shared__ float s_scale;
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) sx[i] = x[(size_t)head * hd + i];
+    __syncthreads();
+    if (threadIdx.x == 0) s_scale = rms_scale_sequential(sx, hd, eps);
+    __syncthreads();
+    for (int i = threadIdx.x; i < hd; i += blockDim.x)
+        out[(size_t)head * hd + i] = __fmul_rn(__fmul_rn(sx[i], s_scale), w[i]);
+}
+
+__global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __fadd_rn(a[i], b[i]);
+}
+
+// silu(gate) * up (crates/llamd-cpu/src/lib.rs:103-114, layer.rs:252):
+// v / (1 + exp(-v)), then the elementwise product.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    const float s = __fdiv_rn(g, __fadd_rn(1.0f, ref_expf(-g)));
+    return __fmul_rn(s, u);
+}
+__global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = silu_mul(gate[i], up[i]);
+}
+// One warp per 256-element block: act = silu(gate)*up, then Q8_K of act.
+__global__ void __launch_bounds__(256) silu_mul_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                             float *__restrict__ out, int8_t *__restrict__ qs, float *__restrict__ d,
+                                                             int nblocks) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= nblocks) return;
+    const size_t base = (size_t)warp * 256 + lane * 8;
+    const float4 g0 = *reinterpret_cast<const float4 *>(gate + base), g1 = *reinterpret_cast<const float4 *>(gate + base + 4);
+    const float4 u0 = *reinterpret_cast<const float4 *>(up + base), u1 = *reinterpret_cast<const float4 *>(up + base + 4);
+    float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
+                  silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
+    if (out) {
+        *reinterpret_cast<float4 *>(out + base) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(out + base + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    q8k_quantize_block(v, lane, qs + (size_t)warp * 256, d + warp, nullptr);
+}
+
+// out[i] = residual[i] + sum_e w[e]*down[e][i], e in routing order
+// (crates/llamd-runtime/src/layer.rs:243-258 then :281-287): the expert sum
+// starts from 0 and the residual is added last.
+__global__ void moe_combine_kernel(const float *__restrict__ down, const float *__restrict__ weights, const float *__restrict__ residual,
+                                   float *__restrict__ out, int n_used, int n_embd) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int seq = blockIdx.y;
+    if (i >= n_embd) return;
+    down += (size_t)seq * n_used * n_embd;
+    weights += (size_t)seq * n_used;
+    float acc = 0.0f;
+    for (int e = 0; e < n_used; e++) acc = __fadd_rn(acc, __fmul_rn(weights[e], down[(size_t)e * n_embd + i]));
+    if (residual) acc = __fadd_rn(residual[(size_t)seq * n_embd + i], acc);
+    out[(size_t)seq * n_embd + i] = acc;
+}
+
+}  // namespace llamd
+
+using namespace llamd;
+
+extern "C" {
+
+void llamd_fwd_quantize_bsums(const float *x, int8_t *qs, float *d, int16_t *bsums, int nblocks) {
+    if (nblocks <= 0) return;
+    q8k_quantize_kernel<<<(nblocks + 7) / 8, 256, 0, stream()>>>(x, qs, d, bsums, nblocks);
+    LLAMD_CHECK_LAUNCH("q8k_quantize");
+}
+void llamd_fwd_quantize(const float *x, int8_t *qs, float *d, int nblocks) {
+    llamd_fwd_quantize_bsums(x, qs, d, nullptr, nblocks);
+}
+
+void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, float eps, int nseq) {
+    rms_norm_kernel<<<nseq, 256, n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, nullptr, nullptr, n, eps);
+    LLAMD_CHECK_LAUNCH("rms_norm_mul");
+}
+void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
+    if (n % 256) {
+        set_error_msg("rms_norm_quant: n must be a multiple of 256");
+        return;
+    }
+    rms_norm_kernel<<<nseq, 256, n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, qs, d, n, eps);
+    LLAMD_CHECK_LAUNCH("rms_norm_quant");
+}
+// x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
+// add of layer.rs:170 into the norm of :173-174.
+void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs,
+                                  float *d, int n, float eps, int nseq) {
+    if (n % 256) {
+        set_error_msg("add_rms_norm_quant: n must be a multiple of 256");
+        return;
+    }
+    rms_norm_kernel<<<nseq, 256, n * sizeof(float), stream()>>>(x, residual, sum_out, w, out, qs, d, n, eps);
+    LLAMD_CHECK_LAUNCH("add_rms_norm_quant");
+}
+void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
+    head_rms_norm_mul_kernel<<<n_head, 128, hd * sizeof(float), stream()>>>(x, w, out, n_head, hd, eps);
+    LLAMD_CHECK_LAUNCH("head_rms_norm_mul");
+}
+void llamd_fwd_add(const float *a, const float *b, float *out, int n) {
+    add_kernel<<<(n + 255) / 256, 256, 0, stream()>>>(a, b, out, n);
+    LLAMD_CHECK_LAUNCH("add");
+}
+void llamd_fwd_silu_mul(const float *gate, const float *up, float *out, int n) {
+    silu_mul_kernel<<<(n + 255) / 256, 256, 0, stream()>>>(gate, up, out, n);
+    LLAMD_CHECK_LAUNCH("silu_mul");
+}
+void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, int8_t *qs, float *d, int n) {
+    if (n % 256) {
+        set_error_msg("silu_mul_quant: n must be a multiple of 256");
+        return;
+    }
+    const int nblocks = n / 256;
+    silu_mul_quant_kernel<<<(nblocks + 7) / 8, 256, 0, stream()>>>(gate, up, out, qs, d, nblocks);
+    LLAMD_CHECK_LAUNCH("silu_mul_quant");
+}
+void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd) {
+    moe_combine_kernel<<<dim3((n_embd + 255) / 256, 1), 256, 0, stream()>>>(down, weights, nullptr, out, n_used, n_embd);
+    LLAMD_CHECK_LAUNCH("moe_combine");
+}
+void llamd_fwd_moe_combine_add(const float *down, const float *weights, const float *residual, float *out, int n_used, int n_embd,
+                               int nseq) {
+    moe_combine_kernel<<<dim3((n_embd + 255) / 256, nseq), 256, 0, stream()>>>(down, weights, residual, out, n_used, n_embd);
+    LLAMD_CHECK_LAUNCH("moe_combine_add");
+}
+
+}  // extern "C"

@@ -1,0 +1,198 @@
+// Device discovery, raw memory, the library stream, the sticky error and the
+// captured graph: the counterpart of the host side of
+// crates/llamd-rocm/kernels/llamd_forward.hip:701-916 and
+// crates/llamd-rocm/kernels/llamd.hip:1027-1100.
+#include <mutex>
+#include <string>
+
+#include "common.cuh"
+
+namespace llamd {
+
+static cudaStream_t g_stream = nullptr;
+static int g_err = 0;
+static std::string g_err_msg;
+static cudaGraph_t g_graph = nullptr;
+static cudaGraphExec_t g_graph_exec = nullptr;
+static void *g_scratch[8] = {};
+static size_t g_scratch_bytes[8] = {};
+
+cudaStream_t stream() {
+    if (!g_stream) {
+        cudaError_t e = cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            set_error(e, "cudaStreamCreate");
+            g_stream = nullptr;
+        }
+    }
+    return g_stream;
+}
+
+void set_error(cudaError_t e, const char *what) {
+    if (g_err == 0) {
+        g_err = (int)e;
+        g_err_msg = std::string(what) + ": " + cudaGetErrorString(e);
+    }
+}
+void set_error_msg(const char *what) {
+    if (g_err == 0) {
+        g_err = -1;
+        g_err_msg = what;
+    }
+}
+int error_code() { return g_err; }
+
+void *scratch(int slot, size_t bytes) {
+    if (bytes <= g_scratch_bytes[slot] && g_scratch[slot]) return g_scratch[slot];
+    if (g_scratch[slot]) {
+        cudaStreamSynchronize(stream());
+        cudaFree(g_scratch[slot]);
+        g_scratch[slot] = nullptr;
+        g_scratch_bytes[slot] = 0;
+    }
+    size_t want = bytes < 4096 ? 4096 : bytes;
+    cudaError_t e = cudaMalloc(&g_scratch[slot], want);
+    if (e != cudaSuccess) {
+        set_error(e, "scratch cudaMalloc");
+        return nullptr;
+    }
+    g_scratch_bytes[slot] = want;
+    return g_scratch[slot];
+}
+
+}  // namespace llamd
+
+using namespace llamd;
+
+extern "C" {
+
+int llamd_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int llamd_cuda_device_info(int dev, char *name, int name_len, char *arch, int arch_len,
+                           size_t *total_mem, int *sm_count, int *warp_size) {
+    cudaDeviceProp p;
+    if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    if (name && name_len > 0) snprintf(name, (size_t)name_len, "%s", p.name);
+    if (arch && arch_len > 0) snprintf(arch, (size_t)arch_len, "sm_%d%d", p.major, p.minor);
+    if (total_mem) *total_mem = p.totalGlobalMem;
+    if (sm_count) *sm_count = p.multiProcessorCount;
+    if (warp_size) *warp_size = p.warpSize;
+    return 0;
+}
+
+size_t llamd_cuda_free_mem(void) {
+    size_t f = 0, t = 0;
+    if (cudaMemGetInfo(&f, &t) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return f;
+}
+size_t llamd_fwd_free_mem(void) { return llamd_cuda_free_mem(); }
+
+const char *llamd_cuda_last_error_string(void) { return g_err_msg.c_str(); }
+
+void *llamd_cuda_upload(const void *host, size_t bytes) {
+    void *d = nullptr;
+    if (cudaMalloc(&d, bytes ? bytes : 1) != cudaSuccess) {
+        set_error(cudaGetLastError(), "upload cudaMalloc");
+        return nullptr;
+    }
+    if (bytes && cudaMemcpy(d, host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        set_error(cudaGetLastError(), "upload cudaMemcpy");
+        cudaFree(d);
+        return nullptr;
+    }
+    return d;
+}
+void llamd_cuda_release(void *dev) {
+    if (dev) cudaFree(dev);
+}
+
+void *llamd_fwd_alloc(size_t bytes) {
+    void *d = nullptr;
+    if (cudaMalloc(&d, bytes ? bytes : 1) != cudaSuccess) {
+        set_error(cudaGetLastError(), "alloc cudaMalloc");
+        return nullptr;
+    }
+    return d;
+}
+void llamd_fwd_free(void *p) {
+    if (p) cudaFree(p);
+}
+int llamd_fwd_upload(void *dst, const void *src, size_t bytes) {
+    LLAMD_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream()), "upload");
+    return 0;
+}
+int llamd_fwd_download(void *dst, const void *src, size_t bytes) {
+    LLAMD_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream()), "download");
+    LLAMD_TRY(cudaStreamSynchronize(stream()), "download sync");
+    return 0;
+}
+int llamd_fwd_memset(void *p, int value, size_t bytes) {
+    LLAMD_TRY(cudaMemsetAsync(p, value, bytes, stream()), "memset");
+    return 0;
+}
+int llamd_fwd_sync(void) {
+    cudaError_t e = cudaStreamSynchronize(stream());
+    if (e != cudaSuccess) set_error(e, "sync");
+    return g_err == 0 ? 0 : -1;
+}
+int llamd_fwd_last_error(void) {
+    int e = g_err;
+    g_err = 0;
+    return e;
+}
+int llamd_fwd_stream_init(void) { return stream() ? 0 : -1; }
+void *llamd_fwd_stream(void) { return (void *)stream(); }
+
+int llamd_fwd_begin_capture(void) {
+    llamd_fwd_graph_destroy();
+    LLAMD_TRY(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal), "begin capture");
+    return 0;
+}
+int llamd_fwd_end_capture(void) {
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(stream(), &g);
+    if (e != cudaSuccess || !g) {
+        set_error(e, "end capture");
+        return -1;
+    }
+    g_graph = g;
+    e = cudaGraphInstantiate(&g_graph_exec, g_graph, 0);
+    if (e != cudaSuccess) {
+        set_error(e, "graph instantiate");
+        cudaGraphDestroy(g_graph);
+        g_graph = nullptr;
+        g_graph_exec = nullptr;
+        return -1;
+    }
+    return 0;
+}
+int llamd_fwd_graph_launch(void) {
+    if (!g_graph_exec) {
+        set_error_msg("graph launch without a captured graph");
+        return -1;
+    }
+    LLAMD_TRY(cudaGraphLaunch(g_graph_exec, stream()), "graph launch");
+    return 0;
+}
+int llamd_fwd_has_graph(void) { return g_graph_exec ? 1 : 0; }
+void llamd_fwd_graph_destroy(void) {
+    if (g_graph_exec) cudaGraphExecDestroy(g_graph_exec);
+    if (g_graph) cudaGraphDestroy(g_graph);
+    g_graph_exec = nullptr;
+    g_graph = nullptr;
+}
+
+}  // extern "C"
