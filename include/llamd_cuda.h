@@ -78,6 +78,8 @@ void llamd_fwd_graph_destroy(void);
 size_t llamd_cuda_q6k_tiled_bytes(size_t n_blocks);
 /* d_src: n_blocks x 210 B in the reference layout, on the device. */
 void llamd_fwd_repack_q6k(const void *d_src, void *d_dst, size_t n_blocks);
+/* The same into blocks [dst_first, dst_first+n_blocks) of a larger tiled buffer that was zero-filled. */
+void llamd_fwd_repack_q6k_at(const void *d_src, void *d_dst, size_t n_blocks, size_t dst_first);
 /* Host blocks in, tiled device buffer out (upload + repack + sync). NULL on failure. */
 void *llamd_cuda_upload_q6k(const void *host_blocks, size_t n_blocks);
 /* Inverse of the repack, for checking that no bit moved wrongly. */
@@ -156,6 +158,11 @@ void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int
 /* norm*w, then Q8_K of the result, one pass (:576). */
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n,
                               float eps, int nseq);
+/* x + residual -> sum_out, then norm*w (f32 to out, may be NULL) and its Q8_K
+ * form: the residual add of crates/llamd-runtime/src/layer.rs:170 fused into
+ * the norm of :173-174. */
+void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w,
+                                  float *out, int8_t *qs, float *d, int n, float eps, int nseq);
 /* rope_tab: [max_pos][hd/2][2] (sin, cos) built by llamd_cuda_rope_table. */
 int llamd_cuda_rope_table(float *host_out, int max_pos, int hd, float freq_base);
 void llamd_fwd_rope(float *x, int pos, int n_head, int hd, const float *rope_tab);       /* :295 */
@@ -176,6 +183,10 @@ void llamd_fwd_silu_mul(const float *gate, const float *up, float *out, int n); 
 void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, int8_t *qs, float *d, int n);
 void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *ids, float *weights,
                       float *probs, int nseq);                                          /* :317 */
+/* The router's f32 matvec (:340) and the routing (:317) in one launch; wt is
+ * the transposed router matrix; logits and probs may be NULL. */
+void llamd_fwd_router_matvec(const float *wt, const float *x, int k, int n_expert, int n_used, float *logits,
+                             int32_t *ids, float *weights, float *probs, int nseq);
 void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd); /* :325 */
 void llamd_fwd_moe_combine_add(const float *down, const float *weights, const float *residual,
                                float *out, int n_used, int n_embd, int nseq);           /* :586 */
@@ -187,14 +198,11 @@ void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_
  * expert, pairs are in ascending pair order. */
 void llamd_fwd_moe_group(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart,
                          int32_t *gcount, int32_t *ptoken, int32_t *pslot);
-/* Expert-major grouped matvec for many tokens (prefill): every expert with
- * gcount>0 is read once for all its pairs. by_slot=0: activation of pair p is
- * aq[ptoken[p]] (gate/up); by_slot=1: aq[pslot[p]] (down). Output row block
- * pslot[p]: out[pslot[p]][rows]. Mirrors q6k_expert_major[_pa].comp. */
-void llamd_fwd_expert_major(const void *w, const int32_t *gstart, const int32_t *gcount,
-                            const int32_t *ptoken, const int32_t *pslot, const int8_t *aq,
-                            const float *ad, float *out, int blocks, int rows, int n_expert,
-                            int by_slot);
+/* The same plus a work list for the expert-major matvec: entries
+ * (expert, first pair, count <= 8), 3 ints each, and their number. */
+void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart,
+                              int32_t *gcount, int32_t *ptoken, int32_t *pslot, int32_t *work,
+                              int32_t *n_work);
 
 #ifdef __cplusplus
 }

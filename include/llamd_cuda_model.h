@@ -1,0 +1,88 @@
+/*
+ * llamd_cuda_model.h -- C ABI of the resident decode model in libllamd_cuda.so.
+ *
+ * The counterpart of `DeviceModel` (crates/llamd-runtime/src/device.rs:94-144):
+ * load once, then `forward(token, pos) -> token` with one synchronise per
+ * token. The reference loads from a GGUF-backed `Model`
+ * (device.rs:262-471); here tensors are handed over one at a time in the
+ * reference's own byte layouts, which also serves random-init weights that
+ * have no file.
+ */
+#ifndef LLAMD_CUDA_MODEL_H
+#define LLAMD_CUDA_MODEL_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* crates/llamd-models/src/hparams.rs:54-75 (the fields the decode loop reads) */
+typedef struct {
+    int32_t n_layer, n_embd, n_head, n_head_kv, head_dim;
+    int32_t n_expert, n_expert_used, n_ff_expert, n_vocab;
+    float rope_freq_base, rms_eps;
+} llamd_hparams;
+
+typedef struct llamd_model llamd_model;
+
+/* Tensor ids for llamd_model_set_tensor. Names follow
+ * crates/llamd-models/src/model.rs LayerNames. */
+enum {
+    LLAMD_T_TOK_EMBD = 0,   /* Q6_K [n_vocab x n_embd]                      */
+    LLAMD_T_OUTPUT_NORM,    /* f32  [n_embd]                                */
+    LLAMD_T_OUTPUT,         /* Q6_K [n_vocab x n_embd]; absent = tied       */
+    LLAMD_T_ATTN_NORM,      /* f32  [n_embd]                                */
+    LLAMD_T_ATTN_Q,         /* Q6_K [n_head*head_dim x n_embd]              */
+    LLAMD_T_ATTN_K,         /* Q6_K [n_head_kv*head_dim x n_embd]           */
+    LLAMD_T_ATTN_V,
+    LLAMD_T_ATTN_Q_NORM,    /* f32  [head_dim], optional                    */
+    LLAMD_T_ATTN_K_NORM,
+    LLAMD_T_ATTN_OUT,       /* Q6_K [n_embd x n_head*head_dim]              */
+    LLAMD_T_FFN_NORM,       /* f32  [n_embd]                                */
+    LLAMD_T_FFN_GATE_INP,   /* f32  [n_expert x n_embd]                     */
+    LLAMD_T_FFN_GATE_EXPS,  /* Q6_K [n_expert][n_ff_expert x n_embd]        */
+    LLAMD_T_FFN_UP_EXPS,
+    LLAMD_T_FFN_DOWN_EXPS   /* Q6_K [n_expert][n_embd x n_ff_expert]        */
+};
+
+/* DeviceModel::load_batched (device.rs:270): room for max_seq sequences of
+ * max_kv positions. NULL on failure (llamd_cuda_last_error_string says why). */
+llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq);
+void llamd_model_free(llamd_model *m);
+const char *llamd_model_error(llamd_model *m);
+
+/* Upload (part of) one tensor from host memory. For Q6_K tensors `host` holds
+ * `count` 210-byte blocks that land at blocks [first_block, first_block+count)
+ * of the tensor (so the 128 experts of a layer can be sent one by one); for
+ * f32 tensors `count` is the element count and first_block must be 0.
+ * layer is ignored for the three model-level tensors. 0 / -1. */
+int llamd_model_set_tensor(llamd_model *m, int layer, int which, size_t first_block, const void *host, size_t count);
+size_t llamd_model_weight_bytes(llamd_model *m); /* device.rs:473 */
+
+/* Public knobs of DeviceModel (device.rs:126-143): "use_graph" (default 1),
+ * "trace" (record per-layer hidden state and expert ids; disables the graph). */
+int llamd_model_set_option(llamd_model *m, const char *name, int value);
+
+/* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */
+int llamd_model_forward(llamd_model *m, int32_t token, int32_t pos, int32_t *out_token);
+/* DeviceModel::forward_batch (device.rs:741-962): nseq independent sequences. */
+int llamd_model_forward_batch(llamd_model *m, const int32_t *tokens, const int32_t *positions, int nseq,
+                              int32_t *out_tokens);
+/* VulkanModel::prefill (crates/llamd-runtime/src/vulkan_model.rs:877-907):
+ * consume n_tokens prompt ids at positions base_pos.., return the greedy token
+ * after the last one. */
+int llamd_model_prefill(llamd_model *m, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_token);
+/* Logits of the last pass, [nseq][n_vocab], to host memory (device.rs:966). */
+int llamd_model_logits(llamd_model *m, float *host_out, int nseq);
+/* With "trace" on: x after every layer [n_layer][max_seq][n_embd] and the
+ * routed expert ids [n_layer][max_seq][n_expert_used] of the last pass. */
+int llamd_model_read_trace(llamd_model *m, float *x_out, int32_t *ids_out);
+/* K and V of positions [0, n_pos) of one layer and sequence, to host memory. */
+int llamd_model_read_kv(llamd_model *m, int layer, int seq, int n_pos, float *k_out, float *v_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLAMD_CUDA_MODEL_H */

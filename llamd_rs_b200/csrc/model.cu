@@ -1,0 +1,453 @@
+// CudaModel: the resident decode model, the counterpart of DeviceModel
+// (crates/llamd-runtime/src/device.rs:94-144, 262-471, 486-722, 741-962).
+//
+// Weights are uploaded once (tensor by tensor, from the reference's byte
+// layouts) and stay on the device; a token is one queue of launches on the
+// library stream reading (token, pos) from a device-resident meta buffer, so
+// the captured CUDA graph is valid for every later token; the host pays 8 bytes
+// up and 4 bytes down per token and one synchronise.
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "../../include/llamd_cuda_model.h"
+
+extern "C" {
+void llamd_fwd_repack_q6k_at(const void *d_src, void *d_dst, size_t n_blocks, size_t dst_first);
+void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs,
+                                  float *d, int n, float eps, int nseq);
+void llamd_fwd_router_matvec(const float *wt, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
+                             float *weights, float *probs, int nseq);
+void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
+                              int32_t *ptoken, int32_t *pslot, int32_t *work, int32_t *n_work);
+}
+
+using namespace llamd;
+
+namespace {
+
+constexpr int kArgmaxBlocks = 512;  // crates/llamd-runtime/src/device.rs ARGMAX_BLOCKS
+
+struct Buf {
+    void *p = nullptr;
+    size_t bytes = 0;
+    bool alloc(size_t n) {
+        bytes = n ? n : 1;
+        if (cudaMalloc(&p, bytes) != cudaSuccess) {
+            set_error(cudaGetLastError(), "model cudaMalloc");
+            p = nullptr;
+            return false;
+        }
+        cudaMemsetAsync(p, 0, bytes, stream());
+        return true;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+    }
+    template <typename T>
+    T *as() const {
+        return (T *)p;
+    }
+};
+
+struct Layer {
+    Buf attn_norm, attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_out, ffn_norm, ffn_gate_inp_t;
+    Buf gate_exps, up_exps, down_exps;
+    bool has_q_norm = false, has_k_norm = false;
+    Buf kc, vc;
+};
+
+struct Model {
+    llamd_hparams hp;
+    int max_kv, max_seq;
+    std::vector<Layer> layers;
+    Buf tok_embd, output_norm, output, rope_tab;
+    // scratch (crates/llamd-runtime/src/device.rs:407-434)
+    Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, router_logits, router_probs, expert_ids, expert_w;
+    Buf e_gate, e_up, e_down, logits, amax_v, amax_i, out_token, meta;
+    Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
+    int32_t *h_meta = nullptr;  // pinned
+    int32_t *h_out = nullptr;   // pinned
+    size_t weight_bytes = 0;
+    int use_graph = 1, trace = 0;
+    int graph_nseq = 0;         // nseq the captured graph was recorded for
+    unsigned long long id = 0;
+    std::string err;
+};
+
+unsigned long long g_next_id = 1, g_graph_owner = 0;
+
+size_t q6k_blocks_for(size_t rows, size_t k) { return rows * (k / LLAMD_QK_K); }
+
+bool upload_q6k_slice(Buf &dst, size_t total_blocks, size_t first, const void *host, size_t n_blocks) {
+    if (!dst.p && !dst.alloc(llamd_cuda_q6k_tiled_bytes(total_blocks))) return false;
+    if (first + n_blocks > total_blocks) {
+        set_error_msg("set_tensor: slice outside the tensor");
+        return false;
+    }
+    const size_t bytes = n_blocks * LLAMD_Q6K_BLOCK_BYTES;
+    void *raw = scratch(6, bytes);
+    if (!raw) return false;
+    if (cudaMemcpyAsync(raw, host, bytes, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "set_tensor H2D");
+        return false;
+    }
+    llamd_fwd_repack_q6k_at(raw, dst.p, n_blocks, first);
+    // the staging buffer is reused by the next call and the host array may go away
+    return llamd_fwd_sync() == 0;
+}
+
+bool upload_f32(Buf &dst, const void *host, size_t n) {
+    if (!dst.p && !dst.alloc(n * sizeof(float))) return false;
+    if (cudaMemcpyAsync(dst.p, host, n * sizeof(float), cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "set_tensor H2D");
+        return false;
+    }
+    return llamd_fwd_sync() == 0;
+}
+
+// Queue one pass for `nseq` sequences. Does not synchronise.
+// The order is crates/llamd-runtime/src/device.rs:486-655 (itself the CPU
+// order of crates/llamd-runtime/src/layer.rs:85-203, 230-304).
+void queue_token(Model &m, int nseq) {
+    const llamd_hparams &hp = m.hp;
+    const int E = hp.n_embd, H = hp.n_head, HKV = hp.n_head_kv, hd = hp.head_dim;
+    const int kvd = HKV * hd, qd = H * hd, nu = hp.n_expert_used, ffe = hp.n_ff_expert;
+    const int eb = E / 256;
+    const int32_t *meta = m.meta.as<int32_t>();
+    float *x = m.x.as<float>();
+
+    llamd_fwd_embed_meta(m.tok_embd.p, meta, x, eb, nseq);
+    for (int il = 0; il < hp.n_layer; il++) {
+        Layer &l = m.layers[il];
+        // attention norm, f32 and Q8_K in one pass: Q, K and V read the same activation
+        llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+        llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
+                                  m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
+        llamd_fwd_norm_rope(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, H, hd, meta, m.rope_tab.as<float>(),
+                            hp.rms_eps, nseq);
+        llamd_fwd_k_norm_rope_store(m.k.as<float>(), l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(),
+                                    l.kc.as<float>(), l.vc.as<float>(), HKV, hd, kvd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq,
+                                    m.max_kv);
+        llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), nullptr, H, HKV, hd, meta,
+                                 m.max_kv, nseq);
+        llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+        llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
+        llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
+                                     m.ad.as<float>(), E, hp.rms_eps, nseq);
+        llamd_fwd_router_matvec(l.ffn_gate_inp_t.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
+                                m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), m.router_probs.as<float>(), nseq);
+        llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
+                                          m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+        llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                 nseq * nu * ffe);
+        llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                          m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+        llamd_fwd_moe_combine_add(m.e_down.as<float>(), m.expert_w.as<float>(), x, x, nu, E, nseq);
+        if (m.trace) {
+            cudaMemcpyAsync(m.trace_x.as<float>() + (size_t)il * m.max_seq * E, x, (size_t)nseq * E * sizeof(float),
+                            cudaMemcpyDeviceToDevice, stream());
+            cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
+                            cudaMemcpyDeviceToDevice, stream());
+        }
+    }
+    llamd_fwd_rms_norm_quant(x, m.output_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+    llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
+                           hp.n_vocab, nseq);
+    llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
+                     kArgmaxBlocks, nseq);
+}
+
+bool check_ready(Model &m) {
+    if (!m.tok_embd.p || !m.output_norm.p) {
+        m.err = "model: token_embd / output_norm not set";
+        return false;
+    }
+    for (size_t i = 0; i < m.layers.size(); i++) {
+        Layer &l = m.layers[i];
+        if (!l.attn_norm.p || !l.attn_q.p || !l.attn_k.p || !l.attn_v.p || !l.attn_out.p || !l.ffn_norm.p || !l.ffn_gate_inp_t.p ||
+            !l.gate_exps.p || !l.up_exps.p || !l.down_exps.p) {
+            m.err = "model: layer " + std::to_string(i) + " has tensors missing";
+            return false;
+        }
+    }
+    return true;
+}
+
+int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int32_t *out_tokens) {
+    const llamd_hparams &hp = m.hp;
+    if (nseq < 1 || nseq > m.max_seq) {
+        m.err = "forward: nseq outside 1..max_seq";
+        return -1;
+    }
+    for (int s = 0; s < nseq; s++) {
+        if (positions[s] < 0 || positions[s] >= m.max_kv) {
+            m.err = "forward: position " + std::to_string(positions[s]) + " beyond the " + std::to_string(m.max_kv) + " allocated";
+            return -1;
+        }
+        if (tokens[s] < 0 || tokens[s] >= hp.n_vocab) {
+            m.err = "forward: token id outside the vocabulary";
+            return -1;
+        }
+        m.h_meta[2 * s] = tokens[s];
+        m.h_meta[2 * s + 1] = positions[s];
+    }
+    if (!check_ready(m)) return -1;
+    // the only per-token host->device traffic: 8 bytes per sequence
+    if (cudaMemcpyAsync(m.meta.p, m.h_meta, (size_t)nseq * 8, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "meta H2D");
+        return -1;
+    }
+    if (m.use_graph && !m.trace) {
+        // a graph recorded for another model, or another nseq, points at the wrong buffers
+        if (!llamd_fwd_has_graph() || g_graph_owner != m.id || m.graph_nseq != nseq) {
+            llamd_fwd_graph_destroy();
+            if (llamd_fwd_begin_capture() != 0) return -1;
+            queue_token(m, nseq);
+            if (llamd_fwd_end_capture() != 0 || error_code() != 0) {
+                llamd_fwd_graph_destroy();
+                return -1;
+            }
+            g_graph_owner = m.id;
+            m.graph_nseq = nseq;
+        }
+        if (llamd_fwd_graph_launch() != 0) return -1;
+    } else {
+        queue_token(m, nseq);
+    }
+    if (cudaMemcpyAsync(m.h_out, m.out_token.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "token D2H");
+        return -1;
+    }
+    if (llamd_fwd_sync() != 0) return -1;  // THE ONE SYNCHRONISE
+    for (int s = 0; s < nseq; s++) {
+        if (m.h_out[s] < 0 || m.h_out[s] >= hp.n_vocab) {
+            m.err = "argmax returned " + std::to_string(m.h_out[s]);
+            return -1;
+        }
+        out_tokens[s] = m.h_out[s];
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq) {
+    if (!hp || max_kv <= 0 || max_seq < 1 || max_seq > LLAMD_MAX_SEQ) {
+        set_error_msg("model: max_kv of 0 or max_seq outside 1..8");
+        return nullptr;
+    }
+    if (hp->n_layer <= 0 || hp->n_embd % 256 || (hp->n_head * hp->head_dim) % 256 || hp->n_ff_expert % 256 || hp->head_dim % 4 ||
+        hp->n_head_kv <= 0 || hp->n_head % hp->n_head_kv || hp->n_expert <= 0 || hp->n_expert > 1024 || hp->n_expert_used <= 0 ||
+        hp->n_expert_used > hp->n_expert || hp->n_expert_used > 64 || hp->head_dim / 2 > 1024) {
+        set_error_msg("model: unsupported hyperparameters (widths must be multiples of 256, MoE only)");
+        return nullptr;
+    }
+    if (!stream()) return nullptr;
+    Model *m = new Model();
+    m->hp = *hp;
+    m->max_kv = max_kv;
+    m->max_seq = max_seq;
+    m->id = g_next_id++;
+    m->layers.resize(hp->n_layer);
+    const size_t E = hp->n_embd, qd = (size_t)hp->n_head * hp->head_dim, kvd = (size_t)hp->n_head_kv * hp->head_dim;
+    const size_t nu = hp->n_expert_used, ffe = hp->n_ff_expert, S = max_seq;
+    const size_t max_act = E > qd ? E : qd;
+    bool ok = true;
+    auto f = [&](Buf &b, size_t n) { ok = ok && b.alloc(n * S * sizeof(float)); };
+    f(m->x, E); f(m->xb, E); f(m->xb2, E); f(m->q, qd); f(m->k, kvd); f(m->v, kvd); f(m->attn, qd);
+    ok = ok && m->aq.alloc(max_act * S);
+    f(m->ad, max_act / 256);
+    ok = ok && m->aq2.alloc(nu * ffe * S);
+    f(m->ad2, nu * ffe / 256);
+    f(m->router_logits, hp->n_expert); f(m->router_probs, hp->n_expert);
+    ok = ok && m->expert_ids.alloc(nu * 4 * S);
+    f(m->expert_w, nu); f(m->e_gate, nu * ffe); f(m->e_up, nu * ffe); f(m->e_down, nu * E);
+    f(m->logits, hp->n_vocab); f(m->amax_v, kArgmaxBlocks);
+    ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
+    for (auto &l : m->layers) {
+        ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
+    }
+    // RoPE angles from the host libm
+    if (ok) {
+        std::vector<float> tab((size_t)max_kv * hp->head_dim);
+        llamd_cuda_rope_table(tab.data(), max_kv, hp->head_dim, hp->rope_freq_base);
+        ok = m->rope_tab.alloc(tab.size() * sizeof(float)) &&
+             cudaMemcpyAsync(m->rope_tab.p, tab.data(), tab.size() * sizeof(float), cudaMemcpyHostToDevice, stream()) == cudaSuccess &&
+             llamd_fwd_sync() == 0;
+    }
+    ok = ok && cudaMallocHost((void **)&m->h_meta, 8 * S) == cudaSuccess && cudaMallocHost((void **)&m->h_out, 4 * S) == cudaSuccess;
+    if (!ok) {
+        llamd_model_free((llamd_model *)m);
+        return nullptr;
+    }
+    return (llamd_model *)m;
+}
+
+void llamd_model_free(llamd_model *h) {
+    if (!h) return;
+    Model *m = (Model *)h;
+    cudaStreamSynchronize(stream());
+    if (g_graph_owner == m->id) {
+        // a captured graph must not outlive the buffers it points at
+        llamd_fwd_graph_destroy();
+        g_graph_owner = 0;
+    }
+    for (auto &l : m->layers)
+        for (Buf *b : {&l.attn_norm, &l.attn_q, &l.attn_k, &l.attn_v, &l.attn_q_norm, &l.attn_k_norm, &l.attn_out, &l.ffn_norm,
+                       &l.ffn_gate_inp_t, &l.gate_exps, &l.up_exps, &l.down_exps, &l.kc, &l.vc})
+            b->release();
+    for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
+                   &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
+                   &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids})
+        b->release();
+    if (m->h_meta) cudaFreeHost(m->h_meta);
+    if (m->h_out) cudaFreeHost(m->h_out);
+    delete m;
+}
+
+const char *llamd_model_error(llamd_model *h) {
+    Model *m = (Model *)h;
+    if (!m) return llamd_cuda_last_error_string();
+    if (m->err.empty()) return llamd_cuda_last_error_string();
+    return m->err.c_str();
+}
+
+int llamd_model_set_tensor(llamd_model *h, int layer, int which, size_t first_block, const void *host, size_t count) {
+    Model *m = (Model *)h;
+    if (!m || !host) return -1;
+    const llamd_hparams &hp = m->hp;
+    const size_t E = hp.n_embd, qd = (size_t)hp.n_head * hp.head_dim, kvd = (size_t)hp.n_head_kv * hp.head_dim;
+    const size_t ffe = hp.n_ff_expert, ne = hp.n_expert;
+    bool ok = false;
+    size_t total = 0;
+    if (which == LLAMD_T_TOK_EMBD || which == LLAMD_T_OUTPUT) {
+        total = q6k_blocks_for(hp.n_vocab, E);
+        ok = upload_q6k_slice(which == LLAMD_T_TOK_EMBD ? m->tok_embd : m->output, total, first_block, host, count);
+    } else if (which == LLAMD_T_OUTPUT_NORM) {
+        ok = count == E && upload_f32(m->output_norm, host, E);
+    } else {
+        if (layer < 0 || layer >= hp.n_layer) {
+            m->err = "set_tensor: layer out of range";
+            return -1;
+        }
+        Layer &l = m->layers[layer];
+        switch (which) {
+        case LLAMD_T_ATTN_NORM: ok = count == E && upload_f32(l.attn_norm, host, E); break;
+        case LLAMD_T_FFN_NORM: ok = count == E && upload_f32(l.ffn_norm, host, E); break;
+        case LLAMD_T_ATTN_Q_NORM: ok = count == (size_t)hp.head_dim && upload_f32(l.attn_q_norm, host, count); l.has_q_norm = ok; break;
+        case LLAMD_T_ATTN_K_NORM: ok = count == (size_t)hp.head_dim && upload_f32(l.attn_k_norm, host, count); l.has_k_norm = ok; break;
+        case LLAMD_T_ATTN_Q: total = q6k_blocks_for(qd, E); ok = upload_q6k_slice(l.attn_q, total, first_block, host, count); break;
+        case LLAMD_T_ATTN_K: total = q6k_blocks_for(kvd, E); ok = upload_q6k_slice(l.attn_k, total, first_block, host, count); break;
+        case LLAMD_T_ATTN_V: total = q6k_blocks_for(kvd, E); ok = upload_q6k_slice(l.attn_v, total, first_block, host, count); break;
+        case LLAMD_T_ATTN_OUT: total = q6k_blocks_for(E, qd); ok = upload_q6k_slice(l.attn_out, total, first_block, host, count); break;
+        case LLAMD_T_FFN_GATE_EXPS: total = ne * q6k_blocks_for(ffe, E); ok = upload_q6k_slice(l.gate_exps, total, first_block, host, count); break;
+        case LLAMD_T_FFN_UP_EXPS: total = ne * q6k_blocks_for(ffe, E); ok = upload_q6k_slice(l.up_exps, total, first_block, host, count); break;
+        case LLAMD_T_FFN_DOWN_EXPS: total = ne * q6k_blocks_for(E, ffe); ok = upload_q6k_slice(l.down_exps, total, first_block, host, count); break;
+        case LLAMD_T_FFN_GATE_INP: {
+            // f32 [n_expert][n_embd]; kept transposed so the sequential dot reads coalesced
+            if (count != ne * E) break;
+            float *raw = (float *)scratch(6, ne * E * sizeof(float));
+            if (!raw) break;
+            if (!l.ffn_gate_inp_t.p && !l.ffn_gate_inp_t.alloc(ne * E * sizeof(float))) break;
+            if (cudaMemcpyAsync(raw, host, ne * E * sizeof(float), cudaMemcpyHostToDevice, stream()) != cudaSuccess) break;
+            llamd_fwd_transpose_f32(raw, l.ffn_gate_inp_t.as<float>(), (int)ne, (int)E);
+            ok = llamd_fwd_sync() == 0;
+        } break;
+        default: m->err = "set_tensor: unknown tensor id"; return -1;
+        }
+    }
+    if (!ok) {
+        if (m->err.empty()) m->err = std::string("set_tensor failed: ") + llamd_cuda_last_error_string();
+        return -1;
+    }
+    if (total) m->weight_bytes += count * LLAMD_Q6K_BLOCK_BYTES;
+    else m->weight_bytes += count * sizeof(float);
+    return 0;
+}
+
+size_t llamd_model_weight_bytes(llamd_model *h) { return h ? ((Model *)h)->weight_bytes : 0; }
+
+int llamd_model_set_option(llamd_model *h, const char *name, int value) {
+    Model *m = (Model *)h;
+    if (!m || !name) return -1;
+    if (!strcmp(name, "use_graph")) {
+        m->use_graph = value;
+        return 0;
+    }
+    if (!strcmp(name, "trace")) {
+        if (value && !m->trace_x.p) {
+            if (!m->trace_x.alloc((size_t)m->hp.n_layer * m->max_seq * m->hp.n_embd * sizeof(float)) ||
+                !m->trace_ids.alloc((size_t)m->hp.n_layer * m->max_seq * m->hp.n_expert_used * sizeof(int32_t)))
+                return -1;
+        }
+        m->trace = value;
+        return 0;
+    }
+    m->err = "set_option: unknown option";
+    return -1;
+}
+
+int llamd_model_forward(llamd_model *h, int32_t token, int32_t pos, int32_t *out_token) {
+    Model *m = (Model *)h;
+    if (!m || !out_token) return -1;
+    m->err.clear();
+    return run(*m, &token, &pos, 1, out_token);
+}
+
+int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32_t *positions, int nseq, int32_t *out_tokens) {
+    Model *m = (Model *)h;
+    if (!m || !tokens || !positions || !out_tokens) return -1;
+    m->err.clear();
+    return run(*m, tokens, positions, nseq, out_tokens);
+}
+
+// VulkanModel::prefill (crates/llamd-runtime/src/vulkan_model.rs:877-907):
+// consume a prompt, return the greedy token after its last position. This
+// form walks the prompt one position at a time through the decode graph, which
+// is what the reference's CPU and ROCm paths do (crates/llamd-runtime/src/layer.rs:83-84).
+int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_token) {
+    Model *m = (Model *)h;
+    if (!m || !tokens || n_tokens <= 0 || !out_token) return -1;
+    m->err.clear();
+    int32_t out = -1;
+    for (int i = 0; i < n_tokens; i++) {
+        const int32_t pos = base_pos + i;
+        if (run(*m, &tokens[i], &pos, 1, &out) != 0) return -1;
+    }
+    *out_token = out;
+    return 0;
+}
+
+int llamd_model_logits(llamd_model *h, float *host_out, int nseq) {
+    Model *m = (Model *)h;
+    if (!m || !host_out || nseq < 1 || nseq > m->max_seq) return -1;
+    return llamd_fwd_download(host_out, m->logits.p, (size_t)nseq * m->hp.n_vocab * sizeof(float));
+}
+
+int llamd_model_read_trace(llamd_model *h, float *x_out, int32_t *ids_out) {
+    Model *m = (Model *)h;
+    if (!m || !m->trace_x.p) return -1;
+    if (x_out && llamd_fwd_download(x_out, m->trace_x.p, m->trace_x.bytes) != 0) return -1;
+    if (ids_out && llamd_fwd_download(ids_out, m->trace_ids.p, m->trace_ids.bytes) != 0) return -1;
+    return 0;
+}
+
+int llamd_model_read_kv(llamd_model *h, int layer, int seq, int n_pos, float *k_out, float *v_out) {
+    Model *m = (Model *)h;
+    if (!m || layer < 0 || layer >= m->hp.n_layer || seq < 0 || seq >= m->max_seq || n_pos < 0 || n_pos > m->max_kv) return -1;
+    const size_t kvd = (size_t)m->hp.n_head_kv * m->hp.head_dim;
+    const size_t off = (size_t)seq * m->max_kv * kvd;
+    if (k_out && llamd_fwd_download(k_out, m->layers[layer].kc.as<float>() + off, n_pos * kvd * sizeof(float)) != 0) return -1;
+    if (v_out && llamd_fwd_download(v_out, m->layers[layer].vc.as<float>() + off, n_pos * kvd * sizeof(float)) != 0) return -1;
+    return 0;
+}
+
+}  // extern "C"

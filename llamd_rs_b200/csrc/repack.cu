@@ -6,13 +6,14 @@
 namespace llamd {
 
 // One CTA of 64 threads per block.
-__global__ void repack_q6k_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t n_units) {
-    const size_t unit = blockIdx.x + (size_t)blockIdx.y * gridDim.x;
-    if (unit >= n_units) return;
+__global__ void repack_q6k_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t n_units, size_t dst_first) {
+    const size_t src_unit = blockIdx.x + (size_t)blockIdx.y * gridDim.x;
+    if (src_unit >= n_units) return;
     __shared__ uint8_t blk[LLAMD_Q6K_BLOCK_BYTES];
     for (int i = threadIdx.x; i < LLAMD_Q6K_BLOCK_BYTES; i += blockDim.x)
-        blk[i] = src[unit * LLAMD_Q6K_BLOCK_BYTES + i];
+        blk[i] = src[src_unit * LLAMD_Q6K_BLOCK_BYTES + i];
     __syncthreads();
+    const size_t unit = dst_first + src_unit;
     const int t = threadIdx.x;
     if (t < 48) {
         const int r = t / 6, m = (t % 6) / 3, i = t % 3;
@@ -148,8 +149,17 @@ void llamd_fwd_repack_q6k(const void *d_src, void *d_dst, size_t n_blocks) {
     if (n_blocks == 0) return;
     cudaError_t e = cudaMemsetAsync(d_dst, 0, llamd_cuda_q6k_tiled_bytes(n_blocks), stream());
     if (e != cudaSuccess) set_error(e, "repack memset");
-    repack_q6k_kernel<<<grid_2d(n_blocks), 64, 0, stream()>>>((const uint8_t *)d_src, (uint8_t *)d_dst, n_blocks);
+    repack_q6k_kernel<<<grid_2d(n_blocks), 64, 0, stream()>>>((const uint8_t *)d_src, (uint8_t *)d_dst, n_blocks, 0);
     LLAMD_CHECK_LAUNCH("repack_q6k");
+}
+
+// Repack n_blocks source blocks into blocks [dst_first, dst_first+n) of a tiled
+// buffer that was zeroed when it was allocated: lets a large tensor (all the
+// experts of a layer) be uploaded piece by piece.
+void llamd_fwd_repack_q6k_at(const void *d_src, void *d_dst, size_t n_blocks, size_t dst_first) {
+    if (n_blocks == 0) return;
+    repack_q6k_kernel<<<grid_2d(n_blocks), 64, 0, stream()>>>((const uint8_t *)d_src, (uint8_t *)d_dst, n_blocks, dst_first);
+    LLAMD_CHECK_LAUNCH("repack_q6k_at");
 }
 
 void *llamd_cuda_upload_q6k(const void *host_blocks, size_t n_blocks) {

@@ -1,0 +1,210 @@
+"""CudaModel: Python handle on the resident decode model in libllamd_cuda.so.
+
+Mirrors ``DeviceModel`` (crates/llamd-runtime/src/device.rs): ``load`` /
+``load_batched``, ``forward(token, pos) -> token``, ``forward_batch``,
+``logits``, ``weight_bytes``, ``hparams`` and the public knobs ``use_graph``.
+Weights come as a dict of numpy arrays in the reference's byte layouts (see
+``synth.make_model``), or are streamed expert by expert for models too large
+to hold on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import backend
+from ._lib import lib
+
+(T_TOK_EMBD, T_OUTPUT_NORM, T_OUTPUT, T_ATTN_NORM, T_ATTN_Q, T_ATTN_K, T_ATTN_V, T_ATTN_Q_NORM, T_ATTN_K_NORM,
+ T_ATTN_OUT, T_FFN_NORM, T_FFN_GATE_INP, T_FFN_GATE_EXPS, T_FFN_UP_EXPS, T_FFN_DOWN_EXPS) = range(15)
+
+_LAYER_TENSORS = dict(attn_norm=T_ATTN_NORM, attn_q=T_ATTN_Q, attn_k=T_ATTN_K, attn_v=T_ATTN_V,
+                      attn_q_norm=T_ATTN_Q_NORM, attn_k_norm=T_ATTN_K_NORM, attn_out=T_ATTN_OUT, ffn_norm=T_FFN_NORM,
+                      ffn_gate_inp=T_FFN_GATE_INP, ffn_gate_exps=T_FFN_GATE_EXPS, ffn_up_exps=T_FFN_UP_EXPS,
+                      ffn_down_exps=T_FFN_DOWN_EXPS)
+_F32 = {T_OUTPUT_NORM, T_ATTN_NORM, T_ATTN_Q_NORM, T_ATTN_K_NORM, T_FFN_NORM, T_FFN_GATE_INP}
+
+
+class _Hparams(C.Structure):
+    _fields_ = [(k, C.c_int32) for k in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_expert",
+                                         "n_expert_used", "n_ff_expert", "n_vocab")] + \
+               [("rope_freq_base", C.c_float), ("rms_eps", C.c_float)]
+
+
+def _bind():
+    L = lib()
+    if getattr(L, "_model_bound", False):
+        return L
+    vp, i32 = C.c_void_p, C.c_int
+    L.llamd_model_create.restype = vp
+    L.llamd_model_create.argtypes = [C.POINTER(_Hparams), i32, i32]
+    L.llamd_model_free.restype = None
+    L.llamd_model_free.argtypes = [vp]
+    L.llamd_model_error.restype = C.c_char_p
+    L.llamd_model_error.argtypes = [vp]
+    L.llamd_model_set_tensor.restype = i32
+    L.llamd_model_set_tensor.argtypes = [vp, i32, i32, C.c_size_t, vp, C.c_size_t]
+    L.llamd_model_weight_bytes.restype = C.c_size_t
+    L.llamd_model_weight_bytes.argtypes = [vp]
+    L.llamd_model_set_option.restype = i32
+    L.llamd_model_set_option.argtypes = [vp, C.c_char_p, i32]
+    L.llamd_model_forward.restype = i32
+    L.llamd_model_forward.argtypes = [vp, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
+    L.llamd_model_forward_batch.restype = i32
+    L.llamd_model_forward_batch.argtypes = [vp, vp, vp, i32, vp]
+    L.llamd_model_logits.restype = i32
+    L.llamd_model_logits.argtypes = [vp, vp, i32]
+    L.llamd_model_read_trace.restype = i32
+    L.llamd_model_read_trace.argtypes = [vp, vp, vp]
+    L.llamd_model_read_kv.restype = i32
+    L.llamd_model_read_kv.argtypes = [vp, i32, i32, i32, vp, vp]
+    L.llamd_model_prefill.restype = i32
+    L.llamd_model_prefill.argtypes = [vp, vp, i32, i32, C.POINTER(C.c_int32)]
+    L._model_bound = True
+    return L
+
+
+class CudaModel:
+    def __init__(self, hp: dict, max_kv: int, max_seq: int = 1):
+        if max_kv == 0:
+            raise backend.Malformed("device model: max_kv of 0")
+        if max_seq == 0 or max_seq > backend.MAX_SEQ:
+            raise backend.Malformed(f"device model: max_seq {max_seq} outside 1..={backend.MAX_SEQ}")
+        if not backend.available():
+            raise backend.Unsupported("cuda: no device present (there is no CPU fallback)")
+        self._L = _bind()
+        self.hp = dict(hp)
+        h = _Hparams()
+        for k, _ in _Hparams._fields_:
+            setattr(h, k, hp[k])
+        self.max_kv, self.max_seq = max_kv, max_seq
+        self._h = self._L.llamd_model_create(C.byref(h), max_kv, max_seq)
+        if not self._h:
+            raise backend.Other("model create failed: " + backend._last_error())
+        self._use_graph = True
+
+    # -- loading -----------------------------------------------------------
+    @classmethod
+    def load(cls, hp: dict, weights: dict, max_kv: int) -> "CudaModel":
+        return cls.load_batched(hp, weights, max_kv, 1)
+
+    @classmethod
+    def load_batched(cls, hp: dict, weights: dict, max_kv: int, max_seq: int) -> "CudaModel":
+        m = cls(hp, max_kv, max_seq)
+        m.set_tensor(-1, T_TOK_EMBD, weights["tok_embd"])
+        m.set_tensor(-1, T_OUTPUT_NORM, weights["output_norm"])
+        if weights.get("output") is not None:
+            m.set_tensor(-1, T_OUTPUT, weights["output"])
+        for il, lay in enumerate(weights["layers"]):
+            for name, tid in _LAYER_TENSORS.items():
+                if lay.get(name) is not None:
+                    m.set_tensor(il, tid, lay[name])
+        return m
+
+    def set_tensor(self, layer: int, which: int, data, first_block: int = 0) -> None:
+        if which in _F32:
+            a = np.ascontiguousarray(data, dtype=np.float32).ravel()
+            count = a.size
+        else:
+            a = np.ascontiguousarray(data, dtype=np.uint8).ravel()
+            if a.size % backend.Q6K_BLOCK_BYTES:
+                raise backend.Malformed(f"tensor of {a.size} bytes is not whole Q6_K blocks")
+            count = a.size // backend.Q6K_BLOCK_BYTES
+        rc = self._L.llamd_model_set_tensor(self._h, layer, which, first_block, a.ctypes.data_as(C.c_void_p), count)
+        if rc != 0:
+            raise backend.Malformed("set_tensor: " + self._err())
+
+    def set_expert(self, layer: int, which: int, expert: int, data) -> None:
+        """which: 0 gate, 1 up, 2 down. Expert e is a contiguous block range
+        (crates/llamd-models/src/model.rs:182-227)."""
+        per = self.hp["n_ff_expert"] * self.hp["n_embd"] // backend.QK_K
+        self.set_tensor(layer, (T_FFN_GATE_EXPS, T_FFN_UP_EXPS, T_FFN_DOWN_EXPS)[which], data, expert * per)
+
+    # -- running -----------------------------------------------------------
+    def _err(self) -> str:
+        return self._L.llamd_model_error(self._h).decode(errors="replace")
+
+    @property
+    def use_graph(self) -> bool:
+        return self._use_graph
+
+    @use_graph.setter
+    def use_graph(self, v: bool) -> None:
+        self._use_graph = bool(v)
+        self._L.llamd_model_set_option(self._h, b"use_graph", int(bool(v)))
+
+    def set_trace(self, on: bool) -> None:
+        if self._L.llamd_model_set_option(self._h, b"trace", int(on)) != 0:
+            raise backend.Other("trace buffers: " + self._err())
+
+    def forward(self, token: int, pos: int) -> int:
+        if pos >= self.max_kv:
+            raise backend.Malformed(f"device forward: position {pos} beyond the {self.max_kv} allocated")
+        out = C.c_int32(-1)
+        if self._L.llamd_model_forward(self._h, int(token), int(pos), C.byref(out)) != 0:
+            raise backend.Other("forward: " + self._err())
+        return int(out.value)
+
+    def forward_batch(self, tokens, positions) -> np.ndarray:
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        p = np.ascontiguousarray(positions, dtype=np.int32)
+        if t.size != p.size or t.size == 0 or t.size > self.max_seq:
+            raise backend.Malformed(f"forward_batch: {t.size} tokens, {p.size} positions, max_seq {self.max_seq}")
+        out = np.zeros(t.size, dtype=np.int32)
+        rc = self._L.llamd_model_forward_batch(self._h, t.ctypes.data_as(C.c_void_p), p.ctypes.data_as(C.c_void_p), t.size,
+                                               out.ctypes.data_as(C.c_void_p))
+        if rc != 0:
+            raise backend.Other("forward_batch: " + self._err())
+        return out
+
+    def prefill(self, tokens, base_pos: int = 0) -> int:
+        """VulkanModel::prefill (crates/llamd-runtime/src/vulkan_model.rs:877-907):
+        run a whole prompt, return the greedy token after its last position."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        if t.size == 0:
+            raise backend.Malformed("prefill: empty prompt")
+        out = C.c_int32(-1)
+        if self._L.llamd_model_prefill(self._h, t.ctypes.data_as(C.c_void_p), t.size, int(base_pos), C.byref(out)) != 0:
+            raise backend.Other("prefill: " + self._err())
+        return int(out.value)
+
+    def logits(self, nseq: int = 1) -> np.ndarray:
+        out = np.zeros((nseq, self.hp["n_vocab"]), dtype=np.float32)
+        if self._L.llamd_model_logits(self._h, out.ctypes.data_as(C.c_void_p), nseq) != 0:
+            raise backend.Other("logits: " + self._err())
+        return out
+
+    def read_trace(self):
+        """-> (x [n_layer][max_seq][n_embd], ids [n_layer][max_seq][n_used]) of the last traced pass"""
+        hp = self.hp
+        x = np.zeros((hp["n_layer"], self.max_seq, hp["n_embd"]), dtype=np.float32)
+        ids = np.zeros((hp["n_layer"], self.max_seq, hp["n_expert_used"]), dtype=np.int32)
+        if self._L.llamd_model_read_trace(self._h, x.ctypes.data_as(C.c_void_p), ids.ctypes.data_as(C.c_void_p)) != 0:
+            raise backend.Other("read_trace: tracing is off")
+        return x, ids
+
+    def read_kv(self, layer: int, n_pos: int, seq: int = 0):
+        kvd = self.hp["n_head_kv"] * self.hp["head_dim"]
+        k = np.zeros(n_pos * kvd, dtype=np.float32)
+        v = np.zeros(n_pos * kvd, dtype=np.float32)
+        if self._L.llamd_model_read_kv(self._h, layer, seq, n_pos, k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)) != 0:
+            raise backend.Malformed("read_kv: out of range")
+        return k, v
+
+    def weight_bytes(self) -> int:
+        return int(self._L.llamd_model_weight_bytes(self._h))
+
+    def hparams(self) -> dict:
+        return dict(self.hp)
+
+    def free(self) -> None:
+        if getattr(self, "_h", None):
+            self._L.llamd_model_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

@@ -1,0 +1,152 @@
+"""GPU parity of the resident decode model against the oracle's decode loop.
+
+A small Qwen3MoE-shaped model (2 layers, 8 experts, 2 active) is decoded token
+by token on both sides from the same seeded weights. Expert ids and greedy
+token ids must be identical; hidden states, K/V and logits are compared bit
+for bit where no exp() is upstream, and at the reference's named tolerances
+(crates/llamd-core/src/tolerance.rs) after one.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+LAYER = 1e-4      # tolerance.rs:100
+LOGITS = 2e-3     # tolerance.rs:109
+ATTENTION = 1e-5  # tolerance.rs:97
+
+
+def max_dev(a, b):
+    """llamd_core::tolerance::max_deviation (tolerance.rs:135-151)."""
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.max(np.abs(a - b) / np.maximum(np.maximum(np.abs(a), np.abs(b)), 1.0)))
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    from llamd_rs_b200 import backend, synth
+    from llamd_rs_b200.model import CudaModel
+    import oracle
+
+    if not backend.available():
+        pytest.fail("no CUDA device: the GPU tests must run on a GPU box")
+    hp = synth.TINY
+    w = synth.make_model(hp, seed=7)
+    gm = CudaModel.load_batched(hp, w, max_kv=64, max_seq=4)
+    om = oracle.Model(hp, w, threads=4)
+    yield hp, w, gm, om
+    gm.free()
+
+
+def test_bad_arguments_are_refused(tiny):
+    from llamd_rs_b200 import backend
+    from llamd_rs_b200.model import CudaModel
+
+    hp, w, gm, om = tiny
+    with pytest.raises(backend.Malformed):
+        CudaModel(hp, 0)
+    with pytest.raises(backend.Malformed):
+        CudaModel(hp, 16, 9)
+    with pytest.raises(backend.Malformed):
+        gm.forward(1, 64)
+    with pytest.raises(backend.Other):
+        gm.forward(hp["n_vocab"], 0)
+    assert gm.weight_bytes() > 0 and gm.hparams()["n_layer"] == 2
+
+
+def test_first_token_layer_by_layer(tiny):
+    """Position 0: softmax over one key is exactly 1, so nothing upstream of the
+    router depends on exp(); the routing itself does."""
+    hp, w, gm, om = tiny
+    om.kv_new(64)
+    gm.set_trace(True)
+    tok = 17
+    got_tok = gm.forward(tok, 0)
+    gx, gids = gm.read_trace()
+    gm.set_trace(False)
+    import oracle
+
+    x = oracle.dequantize(oracle.Q6K, w["tok_embd"][tok * hp["n_embd"] // 256 * 210:], hp["n_embd"])
+    for il in range(hp["n_layer"]):
+        x, tr = om.forward_layer(il, x, 0)
+        assert gids[il, 0].tolist() == tr["experts"].tolist(), f"layer {il} expert ids"
+        assert max_dev(gx[il, 0], x) <= LAYER, f"layer {il} hidden state"
+        gk, gv = gm.read_kv(il, 1)
+        ok, ov = om.kv_layer(il, 1)
+        assert np.array_equal(gv.view(np.uint32), ov.view(np.uint32)) or il > 0, "layer 0 V is exp-free: bit-exact"
+        assert max_dev(gk, ok) <= ATTENTION and max_dev(gv, ov) <= ATTENTION
+    om.kv_new(64)
+    logits = om.forward(tok, 0)
+    assert max_dev(gm.logits()[0], logits) <= LOGITS
+    assert got_tok == oracle.argmax(logits)
+
+
+def test_greedy_decode_matches_token_for_token(tiny):
+    """Prompt of 6 ids, then 10 greedy tokens: ids EXACT, logits at LOGITS."""
+    import oracle
+    from llamd_rs_b200 import synth
+
+    hp, w, gm, om = tiny
+    prompt = synth.token_ids(6, hp["n_vocab"], 3, "prompt").tolist()
+    om.kv_new(64)
+    want, got = [], []
+    worst = 0.0
+    tok_o = tok_g = None
+    for pos in range(16):
+        t_in_o = prompt[pos] if pos < len(prompt) else tok_o
+        t_in_g = prompt[pos] if pos < len(prompt) else tok_g
+        lo = om.forward(t_in_o, pos)
+        tok_o = oracle.argmax(lo)
+        tok_g = gm.forward(t_in_g, pos)
+        worst = max(worst, max_dev(gm.logits()[0], lo))
+        want.append(tok_o)
+        got.append(tok_g)
+        assert tok_g == tok_o, f"token {pos}: gpu {got} cpu {want}"
+    assert worst <= LOGITS, f"logits deviate by {worst}"
+
+
+def test_graph_replay_equals_plain_queueing(tiny):
+    hp, w, gm, om = tiny
+    gm.use_graph = False
+    a = [gm.forward(5 + p, p) for p in range(5)]
+    la = gm.logits()[0]
+    gm.use_graph = True
+    b = [gm.forward(5 + p, p) for p in range(5)]
+    lb = gm.logits()[0]
+    assert a == b and np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+
+
+def test_batch_equals_single(tiny):
+    """crates/llamd-testing/tests/batch_decode.rs:102-125: N sequences in one
+    pass give the tokens (and here the logits, bit for bit) of N single passes."""
+    hp, w, gm, om = tiny
+    seqs = [[3, 9, 27], [100, 200, 300], [7, 7, 7], [511, 0, 255]]
+    single_tokens, single_logits = [], []
+    for s in seqs:
+        toks = []
+        for pos, t in enumerate(s):
+            toks.append(gm.forward(t, pos))
+        single_tokens.append(toks)
+        single_logits.append(gm.logits()[0].copy())
+    # batched: all four sequences advance together (each in its own KV slot)
+    for pos in range(3):
+        out = gm.forward_batch([s[pos] for s in seqs], [pos] * 4)
+        assert out.tolist() == [st[pos] for st in single_tokens]
+    lb = gm.logits(4)
+    for i in range(4):
+        assert np.array_equal(lb[i].view(np.uint32), single_logits[i].view(np.uint32)), f"sequence {i} logits"
+
+
+def test_prefill_equals_sequential_decode(tiny):
+    """crates/llamd-testing/tests/vulkan_prefill.rs:48-136."""
+    from llamd_rs_b200 import synth
+
+    hp, w, gm, om = tiny
+    prompt = synth.token_ids(9, hp["n_vocab"], 5, "prefill").tolist()
+    seq = None
+    for pos, t in enumerate(prompt):
+        seq = gm.forward(t, pos)
+    ls = gm.logits()[0].copy()
+    pre = gm.prefill(prompt, 0)
+    assert pre == seq
+    assert np.array_equal(gm.logits()[0].view(np.uint32), ls.view(np.uint32))
