@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Headline benchmark: Q6_K MoE decode tokens/s (batch 1) on B200.
+
+Workload ("decode_qwen3moe_q6k_b1"): the Qwen3MoE-architecture model of the
+decode configuration -- 48 layers, hidden 2048, 32/4 heads of 128, 128 experts
+(8 active, FFN 768), vocab 151936, every linear weight Q6_K, f32 router,
+random-init from seed 0 -- after a prompt of `--prompt` uniform token ids. A
+step is one greedy decode pass (one token). Synthetic weights and ids stand in
+for the real checkpoint, which is not available.
+
+  value     tokens/s with everything resident: K passes queued back to back,
+            each token fed to the next on the device, timed with CUDA events on
+            the library stream.
+  e2e       tokens/s through the public call `CudaModel.forward(token, pos)`:
+            per step 8 bytes host->device, the pass, 4 bytes device->host and
+            one synchronise, timed on the host between synchronises.
+  roofline  the Q6_K matvec kernel: algorithmic bytes of one token's matvec
+            launches / their device time (events), against the measured HBM
+            copy bandwidth. Each token streams ~2.5 GB of weights out of a
+            24 GB model, so every launch reads HBM-cold data (inputs larger than L2).
+  cpu_baseline  the CPU oracle (a port of the reference's scalar CPU path) on
+            the host cores, on a bounded sample (see `sample`).
+
+`--impl reference` times that CPU port as the main line: the reference is Rust
+and cannot be built here, so the oracle port stands in for llamd-cpu.
+
+Multi-GPU (torchrun): one process per GPU, each decoding its own sequence on
+its own replica of the model (scaling "weak"); value is the sum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def matvec_bytes_per_token(hp):
+    """Algorithmic bytes of one token's Q6_K matvec launches: weights read once
+    plus the Q8_K activations in and the f32 rows out of every launch."""
+    E, qd, kvd = hp["n_embd"], hp["n_head"] * hp["head_dim"], hp["n_head_kv"] * hp["head_dim"]
+    ffe, nu, V, L = hp["n_ff_expert"], hp["n_expert_used"], hp["n_vocab"], hp["n_layer"]
+    q6 = lambda rows, k: rows * (k // 256) * 210
+    act = lambda k: k + (k // 256) * 4
+    w_layer = q6(qd, E) + 2 * q6(kvd, E) + q6(E, qd) + nu * (2 * q6(ffe, E) + q6(E, ffe))
+    io_layer = act(E) + (qd + 2 * kvd) * 4 + act(qd) + E * 4 + act(E) + 2 * nu * ffe * 4 + nu * act(ffe) + nu * E * 4
+    weights = L * w_layer + q6(V, E)
+    io = L * io_layer + act(E) + V * 4
+    return weights, io
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_port_sample(hp, seed, n_layers_sample, steps, threads, tokens):
+    """Time the oracle's decode pass on a bounded sample: `n_layers_sample`
+    full layers (all their experts pre-generated so generation is not timed)
+    plus the output norm and lm_head, extrapolated to hp['n_layer'] layers.
+    -> (tokens/s estimate, seconds per sampled step list)"""
+    import oracle
+    from llamd_rs_b200 import synth
+
+    t0 = time.time()
+    w = dict(tok_embd=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "tok_embd"),
+             output_norm=np.ones(hp["n_embd"], np.float32),
+             output=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "output"),
+             layers=[synth.layer_weights(hp, seed, il, with_experts=True) for il in range(n_layers_sample)])
+    hp_s = dict(hp, n_layer=n_layers_sample)
+    om = oracle.Model(hp_s, w, threads=threads)
+    om.kv_new(max(64, steps + 8))
+    log(f"[cpu] sample weights ready in {time.time() - t0:.1f}s")
+    per_layer, per_head = [], []
+    for pos in range(steps):
+        tok = int(tokens[pos % len(tokens)])
+        x = oracle.dequantize(oracle.Q6K, w["tok_embd"][tok * (hp["n_embd"] // 256) * 210:], hp["n_embd"])
+        t1 = time.perf_counter()
+        for il in range(n_layers_sample):
+            x, _ = om.forward_layer(il, x, pos)
+        t2 = time.perf_counter()
+        normed = oracle.mul(oracle.rms_norm(x, hp["rms_eps"]), w["output_norm"])
+        logits = oracle.matvec_q6k(w["output"], normed, hp["n_embd"], hp["n_vocab"], threads=threads)
+        oracle.argmax(logits)
+        t3 = time.perf_counter()
+        per_layer.append((t2 - t1) / n_layers_sample)
+        per_head.append(t3 - t2)
+    tok_s = [hp["n_layer"] * a + b for a, b in zip(per_layer, per_head)]
+    return tok_s
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU implementation of the path: the oracle port, all host threads."""
+    if rank != 0:
+        return
+    from llamd_rs_b200 import synth
+
+    hp = dict(synth.QWEN3MOE_30B)
+    threads = os.cpu_count() or 1
+    tokens = synth.token_ids(512, hp["n_vocab"], 0, "prompt")
+    n_sample = 2
+    total = args.warmup + args.steps
+    secs = cpu_port_sample(hp, 0, n_sample, total, threads, tokens)[args.warmup:]
+    sec_per_tok = float(np.mean(secs))
+    v = 1.0 / sec_per_tok
+    sample = (f"{args.steps} decode steps at positions {args.warmup}..{args.warmup + args.steps - 1}; each step runs {n_sample} "
+              f"of 48 layers (every expert resident) + output norm + lm_head on {threads} threads; token time = 48 x mean layer + head")
+    line = {"impl": "reference", "metric": "q6k_moe_decode_tok_s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sec_per_tok, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
+            "config": {"workload": "decode_qwen3moe_q6k_b1", "layers": 48, "experts": "128x8", "hidden": 2048, "vocab": 151936,
+                       "batch": 1, "weights": "Q6_K random-init seed 0"},
+            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt", type=int, default=512, help="prompt length consumed before the timed decode")
+    ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; the JSON line says so")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="queue every launch instead of replaying the captured graph "
+                    "(for a profiler's launch list; the timed numbers are then not the headline)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group(backend="gloo")  # host-side barrier / max only: the data path has no collective
+        dist = dist_mod
+
+    from llamd_rs_b200 import backend, synth
+    from llamd_rs_b200.model import CudaModel
+
+    if not backend.available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    backend.set_device(local)
+    backend.stream_init()
+    info = backend.device_info(local)
+
+    hp = dict(synth.QWEN3MOE_30B)
+    hp["n_layer"] = args.layers
+    K, W = args.steps, args.warmup
+    max_kv = args.prompt + 2 * (K + W) + 8
+    t0 = time.time()
+    m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=1)
+    log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
+    if args.no_graph:
+        m.use_graph = False
+
+    # each rank decodes its own sequence
+    prompt = synth.token_ids(args.prompt, hp["n_vocab"], 0, "prompt", rank)
+    t0 = time.time()
+    tok = m.prefill(prompt, 0)
+    log(f"[rank {rank}] prompt of {args.prompt} consumed in {time.time() - t0:.2f}s")
+    pos = args.prompt
+
+    def barrier():
+        backend.sync()
+        if dist:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if not dist:
+            return v
+        import torch
+
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- warm-up (both paths) ----
+    for _ in range(W):
+        tok = m.forward(tok, pos)
+        pos += 1
+
+    from llamd_rs_b200._lib import lib as _lib
+
+    log(f"[launch-index] timed region starts after {_lib().llamd_fwd_launch_count()} launches; "
+        f"{m.launches_per_pass()} launches per pass")
+    sampler = ClockSampler(local)
+    sampler.start()
+    # ---- e2e: the public per-token call, host token in / host token out ----
+    barrier()
+    t1 = time.perf_counter()
+    e2e_tokens = []
+    for _ in range(K):
+        tok = m.forward(tok, pos)
+        e2e_tokens.append(tok)
+        pos += 1
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t1)
+
+    # ---- value: resident loop, device-timed ----
+    barrier()
+    toks, ms = m.decode(tok, pos, K)
+    barrier()
+    dev_ms = max_over_ranks(ms)
+    pos += K
+    clocks = sampler.stop()
+
+    # ---- roofline of the dominant kernel ----
+    iters = max(4, min(K, 16))
+    mv_ms, mv_launches = m.bench_matvecs(iters)
+    wbytes, iobytes = matvec_bytes_per_token(hp)
+    achieved = (wbytes + iobytes) / (mv_ms / iters * 1e-3) / 1e9
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
+
+    line = {
+        "metric": "q6k_moe_decode_tok_s", "value": world * K / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
+        "config": {"workload": "decode_qwen3moe_q6k_b1", "layers": hp["n_layer"], "experts": "128x8", "hidden": 2048, "vocab": 151936,
+                   "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
+                   "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": f"replicas x{world}",
+                   "token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "arith": "exact (reference order)",
+                   "graph": not args.no_graph},
+        "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(m.launches_per_pass()) * K,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "kernel": "matvec_q6k_kernel<1>", "launches_per_token": mv_launches, "avg_launch_us": mv_ms / iters / mv_launches * 1e3,
+                     "algorithmic_bytes_per_token": wbytes + iobytes, "peak_source": peak_src,
+                     "frac_of_nominal_8tbs": achieved / 8000.0},
+        "clocks": clocks,
+    }
+    if rank == 0 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        n_sample, cpu_steps = 2, 3
+        secs = cpu_port_sample(dict(synth.QWEN3MOE_30B), 0, n_sample, cpu_steps, threads, synth.token_ids(512, hp["n_vocab"], 0, "prompt"))
+        line["cpu_baseline"] = {"value": 1.0 / float(np.mean(secs[1:])), "unit": "tok/s", "cores": threads, "kind": "port",
+                                "sample": f"{cpu_steps - 1} decode steps (after 1 warm) of {n_sample} of 48 layers + lm_head; token time = 48 x mean layer + head"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    m.free()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

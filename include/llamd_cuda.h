@@ -41,6 +41,8 @@ int llamd_cuda_device_count(void);
 int llamd_cuda_device_info(int dev, char *name, int name_len, char *arch, int arch_len,
                            size_t *total_mem, int *sm_count, int *warp_size);
 size_t llamd_cuda_free_mem(void);
+/* One process drives one GPU: pick it before anything else is called. */
+int llamd_cuda_set_device(int dev);
 /* Message for the last failure on this thread's library state ("" if none). */
 const char *llamd_cuda_last_error_string(void);
 
@@ -57,6 +59,8 @@ int llamd_fwd_sync(void);
 size_t llamd_fwd_free_mem(void);
 int llamd_fwd_last_error(void);
 int llamd_fwd_stream_init(void); /* forward.rs:552 */
+/* Kernel launches issued through the library since load (graph nodes count once, at capture). */
+unsigned long long llamd_fwd_launch_count(void);
 /* The library's stream as a cudaStream_t, for callers that time with events. */
 void *llamd_fwd_stream(void);
 

@@ -74,6 +74,18 @@ int llamd_model_forward_batch(llamd_model *m, const int32_t *tokens, const int32
  * consume n_tokens prompt ids at positions base_pos.., return the greedy token
  * after the last one. */
 int llamd_model_prefill(llamd_model *m, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_token);
+/* Resident greedy decode: n passes back to back, each pass's token fed to the
+ * next on the device, one synchronise at the end; the same tokens as n calls
+ * of llamd_model_forward. ms_out (may be NULL) gets the device time of the n
+ * passes. The kernel-only counterpart of the reference's tg64 loop
+ * (crates/llamd-testing/tests/device_forward.rs:136-279). */
+int llamd_model_decode(llamd_model *m, int32_t first_token, int32_t start_pos, int n, int32_t *out_tokens, float *ms_out);
+/* Device time of `iters` repetitions of only the Q6_K matvec launches of one
+ * pass (the kernel-only discipline of DeviceWeights::bench_kernel_only,
+ * crates/llamd-rocm/src/lib.rs:378-423, over a whole token's weights). */
+int llamd_model_bench_matvecs(llamd_model *m, int iters, int nseq, float *ms_out, int *launches_out);
+/* Kernel launches one pass queues (the nodes of its graph). */
+unsigned long long llamd_model_launches_per_pass(llamd_model *m);
 /* Logits of the last pass, [nseq][n_vocab], to host memory (device.rs:966). */
 int llamd_model_logits(llamd_model *m, float *host_out, int nseq);
 /* With "trace" on: x after every layer [n_layer][max_seq][n_embd] and the

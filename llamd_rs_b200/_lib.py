@@ -20,6 +20,7 @@ SIGNATURES = {
     "llamd_cuda_device_count": (i32, []),
     "llamd_cuda_device_info": (i32, [i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(sz), C.POINTER(i32), C.POINTER(i32)]),
     "llamd_cuda_free_mem": (sz, []),
+    "llamd_cuda_set_device": (i32, [i32]),
     "llamd_cuda_last_error_string": (C.c_char_p, []),
     "llamd_cuda_upload": (vp, [vp, sz]),
     "llamd_cuda_release": (None, [vp]),
@@ -33,6 +34,8 @@ SIGNATURES = {
     "llamd_fwd_last_error": (i32, []),
     "llamd_fwd_stream_init": (i32, []),
     "llamd_fwd_stream": (vp, []),
+    "llamd_fwd_launch_count": (C.c_ulonglong, []),
+    "llamd_fwd_repack_q6k_at": (None, [vp, vp, sz, sz]),
     "llamd_fwd_begin_capture": (i32, []),
     "llamd_fwd_end_capture": (i32, []),
     "llamd_fwd_graph_launch": (i32, []),

@@ -96,6 +96,14 @@ def device_info(index: int) -> DeviceInfo:
                       arch.value.decode())
 
 
+def set_device(index: int) -> None:
+    n = device_count()
+    if index < 0 or index >= n:
+        raise Malformed(f"cuda device: index {index} of {n} devices")
+    if lib().llamd_cuda_set_device(index) != 0:
+        raise Other("set_device: " + _last_error())
+
+
 def free_memory() -> int:
     return int(lib().llamd_fwd_free_mem())
 

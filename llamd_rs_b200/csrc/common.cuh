@@ -17,8 +17,13 @@ void set_error(cudaError_t e, const char *what);
 void set_error_msg(const char *what);
 int error_code();
 
+// Kernel launches issued through the library since it was loaded (a launch
+// recorded into a graph counts once, at capture).
+extern unsigned long long g_launches;
+
 #define LLAMD_CHECK_LAUNCH(what)                                   \
     do {                                                           \
+        ::llamd::g_launches++;                                     \
         cudaError_t e__ = cudaPeekAtLastError();                   \
         if (e__ != cudaSuccess) ::llamd::set_error(e__, what);     \
     } while (0)

@@ -69,6 +69,8 @@ struct Model {
     Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, router_logits, router_probs, expert_ids, expert_w;
     Buf e_gate, e_up, e_down, logits, amax_v, amax_i, out_token, meta;
     Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
+    Buf tok_log, tok_count;  // device-side record of emitted tokens, for the resident decode loop
+    unsigned long long launches_per_pass = 0;
     int32_t *h_meta = nullptr;  // pinned
     int32_t *h_out = nullptr;   // pinned
     size_t weight_bytes = 0;
@@ -79,6 +81,24 @@ struct Model {
 };
 
 unsigned long long g_next_id = 1, g_graph_owner = 0;
+
+// After the argmax: record the emitted tokens and make them the next pass's
+// input at pos+1, so passes can be queued back to back without the host.
+// forward() overwrites meta before every pass, so this only matters to the
+// resident decode loop.
+__global__ void advance_meta_kernel(int32_t *__restrict__ meta, const int32_t *__restrict__ out_token, int32_t *__restrict__ tok_log,
+                                    int32_t *__restrict__ tok_count, int nseq, int log_cap) {
+    const int s = threadIdx.x;
+    const int c = *tok_count;
+    __syncthreads();
+    if (s < nseq) {
+        const int t = out_token[s];
+        if ((c + 1) * nseq <= log_cap) tok_log[c * nseq + s] = t;
+        meta[2 * s] = t;
+        meta[2 * s + 1] += 1;
+    }
+    if (s == 0) *tok_count = c + 1;
+}
 
 size_t q6k_blocks_for(size_t rows, size_t k) { return rows * (k / LLAMD_QK_K); }
 
@@ -161,6 +181,30 @@ void queue_token(Model &m, int nseq) {
                            hp.n_vocab, nseq);
     llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
                      kArgmaxBlocks, nseq);
+    advance_meta_kernel<<<1, 32, 0, stream()>>>(m.meta.as<int32_t>(), m.out_token.as<int32_t>(), m.tok_log.as<int32_t>(),
+                                                m.tok_count.as<int32_t>(), nseq, m.max_kv * m.max_seq);
+    LLAMD_CHECK_LAUNCH("advance_meta");
+}
+
+// Only the Q6_K matvec launches of one pass, with whatever activations and
+// expert ids the last pass left in the scratch buffers: what the dominant
+// kernel costs per token, for the roofline figure.
+void queue_matvecs_only(Model &m, int nseq) {
+    const llamd_hparams &hp = m.hp;
+    const int E = hp.n_embd, kvd = hp.n_head_kv * hp.head_dim, qd = hp.n_head * hp.head_dim, nu = hp.n_expert_used, ffe = hp.n_ff_expert;
+    const int eb = E / 256;
+    for (int il = 0; il < hp.n_layer; il++) {
+        Layer &l = m.layers[il];
+        llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
+                                  m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
+                                          m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+        llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                          m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+    }
+    llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
+                           hp.n_vocab, nseq);
 }
 
 bool check_ready(Model &m) {
@@ -208,7 +252,9 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
         if (!llamd_fwd_has_graph() || g_graph_owner != m.id || m.graph_nseq != nseq) {
             llamd_fwd_graph_destroy();
             if (llamd_fwd_begin_capture() != 0) return -1;
+            const unsigned long long before = g_launches;
             queue_token(m, nseq);
+            m.launches_per_pass = g_launches - before;
             if (llamd_fwd_end_capture() != 0 || error_code() != 0) {
                 llamd_fwd_graph_destroy();
                 return -1;
@@ -218,7 +264,9 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
         }
         if (llamd_fwd_graph_launch() != 0) return -1;
     } else {
+        const unsigned long long before = g_launches;
         queue_token(m, nseq);
+        m.launches_per_pass = g_launches - before;
     }
     if (cudaMemcpyAsync(m.h_out, m.out_token.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) {
         set_error(cudaGetLastError(), "token D2H");
@@ -272,6 +320,7 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     f(m->expert_w, nu); f(m->e_gate, nu * ffe); f(m->e_up, nu * ffe); f(m->e_down, nu * E);
     f(m->logits, hp->n_vocab); f(m->amax_v, kArgmaxBlocks);
     ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
+    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4);
     for (auto &l : m->layers) {
         ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
     }
@@ -306,7 +355,8 @@ void llamd_model_free(llamd_model *h) {
             b->release();
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
-                   &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids})
+                   &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
+                   &m->tok_log, &m->tok_count})
         b->release();
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out) cudaFreeHost(m->h_out);
@@ -425,6 +475,82 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
     *out_token = out;
     return 0;
 }
+
+// Resident greedy decode: n passes queued back to back, each feeding its
+// token to the next on the device; one synchronise at the end. Equivalent to
+// n calls of llamd_model_forward with the returned token fed back.
+// ms_out (optional): device time of the n passes, from events on the library stream.
+int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, int n, int32_t *out_tokens, float *ms_out) {
+    Model *m = (Model *)h;
+    if (!m || n <= 0 || !out_tokens) return -1;
+    m->err.clear();
+    if (start_pos < 0 || start_pos + n > m->max_kv || first_token < 0 || first_token >= m->hp.n_vocab) {
+        m->err = "decode: positions beyond the allocated KV cache, or a bad token";
+        return -1;
+    }
+    if (!check_ready(*m)) return -1;
+    m->h_meta[0] = first_token;
+    m->h_meta[1] = start_pos;
+    cudaMemcpyAsync(m->meta.p, m->h_meta, 8, cudaMemcpyHostToDevice, stream());
+    cudaMemsetAsync(m->tok_count.p, 0, 4, stream());
+    if (m->use_graph && (!llamd_fwd_has_graph() || g_graph_owner != m->id || m->graph_nseq != 1)) {
+        llamd_fwd_graph_destroy();
+        if (llamd_fwd_begin_capture() != 0) return -1;
+        const unsigned long long before = g_launches;
+        queue_token(*m, 1);
+        m->launches_per_pass = g_launches - before;
+        if (llamd_fwd_end_capture() != 0 || error_code() != 0) {
+            llamd_fwd_graph_destroy();
+            return -1;
+        }
+        g_graph_owner = m->id;
+        m->graph_nseq = 1;
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, stream());
+    for (int i = 0; i < n; i++) {
+        if (m->use_graph) {
+            if (llamd_fwd_graph_launch() != 0) return -1;
+        } else {
+            queue_token(*m, 1);
+        }
+    }
+    cudaEventRecord(e1, stream());
+    if (cudaMemcpyAsync(out_tokens, m->tok_log.p, (size_t)n * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "decode D2H");
+        return -1;
+    }
+    const int rc = llamd_fwd_sync();
+    if (ms_out) cudaEventElapsedTime(ms_out, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return rc;
+}
+
+// Device time of `iters` repetitions of one pass's Q6_K matvec launches only.
+int llamd_model_bench_matvecs(llamd_model *h, int iters, int nseq, float *ms_out, int *launches_out) {
+    Model *m = (Model *)h;
+    if (!m || iters <= 0 || !ms_out || nseq < 1 || nseq > m->max_seq || !check_ready(*m)) return -1;
+    const unsigned long long before = g_launches;
+    queue_matvecs_only(*m, nseq);  // warm
+    if (launches_out) *launches_out = (int)(g_launches - before);
+    if (llamd_fwd_sync() != 0) return -1;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, stream());
+    for (int i = 0; i < iters; i++) queue_matvecs_only(*m, nseq);
+    cudaEventRecord(e1, stream());
+    const int rc = llamd_fwd_sync();
+    cudaEventElapsedTime(ms_out, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return rc;
+}
+
+unsigned long long llamd_model_launches_per_pass(llamd_model *h) { return h ? ((Model *)h)->launches_per_pass : 0; }
 
 int llamd_model_logits(llamd_model *h, float *host_out, int nseq) {
     Model *m = (Model *)h;

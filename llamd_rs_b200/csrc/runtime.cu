@@ -9,6 +9,7 @@
 
 namespace llamd {
 
+unsigned long long g_launches = 0;
 static cudaStream_t g_stream = nullptr;
 static int g_err = 0;
 static std::string g_err_msg;
@@ -90,6 +91,17 @@ int llamd_cuda_device_info(int dev, char *name, int name_len, char *arch, int ar
     return 0;
 }
 
+// Select the device every later call of this process uses. Must come before
+// the first allocation or launch (the stream is created on first use).
+int llamd_cuda_set_device(int dev) {
+    if (g_stream) {
+        set_error_msg("set_device after the stream was created");
+        return -1;
+    }
+    LLAMD_TRY(cudaSetDevice(dev), "cudaSetDevice");
+    return 0;
+}
+
 size_t llamd_cuda_free_mem(void) {
     size_t f = 0, t = 0;
     if (cudaMemGetInfo(&f, &t) != cudaSuccess) {
@@ -154,6 +166,7 @@ int llamd_fwd_last_error(void) {
     return e;
 }
 int llamd_fwd_stream_init(void) { return stream() ? 0 : -1; }
+unsigned long long llamd_fwd_launch_count(void) { return g_launches; }
 void *llamd_fwd_stream(void) { return (void *)stream(); }
 
 int llamd_fwd_begin_capture(void) {

@@ -61,6 +61,12 @@ def _bind():
     L.llamd_model_read_kv.argtypes = [vp, i32, i32, i32, vp, vp]
     L.llamd_model_prefill.restype = i32
     L.llamd_model_prefill.argtypes = [vp, vp, i32, i32, C.POINTER(C.c_int32)]
+    L.llamd_model_decode.restype = i32
+    L.llamd_model_decode.argtypes = [vp, C.c_int32, C.c_int32, i32, vp, C.POINTER(C.c_float)]
+    L.llamd_model_bench_matvecs.restype = i32
+    L.llamd_model_bench_matvecs.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i32)]
+    L.llamd_model_launches_per_pass.restype = C.c_ulonglong
+    L.llamd_model_launches_per_pass.argtypes = [vp]
     L._model_bound = True
     return L
 
@@ -100,6 +106,28 @@ class CudaModel:
             for name, tid in _LAYER_TENSORS.items():
                 if lay.get(name) is not None:
                     m.set_tensor(il, tid, lay[name])
+        return m
+
+    @classmethod
+    def load_synthetic(cls, hp: dict, seed: int, max_kv: int, max_seq: int = 1) -> "CudaModel":
+        """Random-init weights streamed tensor by tensor (expert by expert), so
+        a 24 GB model never has to sit in host memory. Byte-identical to
+        ``load_batched(hp, synth.make_model(hp, seed), ...)``."""
+        from . import synth
+
+        m = cls(hp, max_kv, max_seq)
+        E = hp["n_embd"]
+        m.set_tensor(-1, T_TOK_EMBD, synth.q6k_blocks(hp["n_vocab"] * E // backend.QK_K, seed, "tok_embd"))
+        m.set_tensor(-1, T_OUTPUT_NORM, np.ones(E, np.float32))
+        m.set_tensor(-1, T_OUTPUT, synth.q6k_blocks(hp["n_vocab"] * E // backend.QK_K, seed, "output"))
+        for il in range(hp["n_layer"]):
+            lay = synth.layer_weights(hp, seed, il, with_experts=False)
+            for name, tid in _LAYER_TENSORS.items():
+                if name in lay:
+                    m.set_tensor(il, tid, lay[name])
+            for which in range(3):
+                for e in range(hp["n_expert"]):
+                    m.set_expert(il, which, e, synth.expert_blocks(hp, seed, il, which, e))
         return m
 
     def set_tensor(self, layer: int, which: int, data, first_block: int = 0) -> None:
@@ -168,6 +196,25 @@ class CudaModel:
         if self._L.llamd_model_prefill(self._h, t.ctypes.data_as(C.c_void_p), t.size, int(base_pos), C.byref(out)) != 0:
             raise backend.Other("prefill: " + self._err())
         return int(out.value)
+
+    def decode(self, first_token: int, start_pos: int, n: int):
+        """Resident greedy decode of n tokens -> (tokens int32[n], device milliseconds)."""
+        out = np.zeros(n, dtype=np.int32)
+        ms = C.c_float(0)
+        rc = self._L.llamd_model_decode(self._h, int(first_token), int(start_pos), int(n), out.ctypes.data_as(C.c_void_p), C.byref(ms))
+        if rc != 0:
+            raise backend.Other("decode: " + self._err())
+        return out, float(ms.value)
+
+    def bench_matvecs(self, iters: int, nseq: int = 1):
+        """-> (device ms for iters passes of the matvec launches only, launches per pass)"""
+        ms, n = C.c_float(0), C.c_int(0)
+        if self._L.llamd_model_bench_matvecs(self._h, iters, nseq, C.byref(ms), C.byref(n)) != 0:
+            raise backend.Other("bench_matvecs: " + self._err())
+        return float(ms.value), int(n.value)
+
+    def launches_per_pass(self) -> int:
+        return int(self._L.llamd_model_launches_per_pass(self._h))
 
     def logits(self, nseq: int = 1) -> np.ndarray:
         out = np.zeros((nseq, self.hp["n_vocab"]), dtype=np.float32)
