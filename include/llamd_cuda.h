@@ -148,11 +148,10 @@ void llamd_fwd_matvec_grouped_x2_batch(const void *wa, const void *wb, const int
 void llamd_fwd_matvec_grouped_pa_batch(const void *w, const int32_t *ids, const int8_t *aq,
                                        const float *ad, float *out, int blocks, int rows, int n_used,
                                        int nseq);
-/* f32 weights [rows][k] (the router): sequential f32 dot per row (:340). wt is
- * the transposed copy [k][rows] that llamd_fwd_transpose_f32 makes. */
+/* f32 weights [rows][k] (the router): sequential f32 dot per row (:340). */
+void llamd_fwd_matvec_f32(const float *w, const float *x, float *out, int k, int rows);
+void llamd_fwd_matvec_f32_batch(const float *w, const float *x, float *out, int k, int rows, int nseq);
 void llamd_fwd_transpose_f32(const float *w, float *wt, int rows, int k);
-void llamd_fwd_matvec_f32(const float *wt, const float *x, float *out, int k, int rows);
-void llamd_fwd_matvec_f32_batch(const float *wt, const float *x, float *out, int k, int rows, int nseq);
 void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq);
 
 void llamd_fwd_embed(const void *table, int token, float *out, int blocks);              /* :279 */
@@ -187,10 +186,11 @@ void llamd_fwd_silu_mul(const float *gate, const float *up, float *out, int n); 
 void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, int8_t *qs, float *d, int n);
 void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *ids, float *weights,
                       float *probs, int nseq);                                          /* :317 */
-/* The router's f32 matvec (:340) and the routing (:317) in one launch; wt is
- * the transposed router matrix; logits and probs may be NULL. */
-void llamd_fwd_router_matvec(const float *wt, const float *x, int k, int n_expert, int n_used, float *logits,
-                             int32_t *ids, float *weights, float *probs, int nseq);
+/* The router's f32 matvec (:340) and the routing (:317) in one launch. w is
+ * [n_expert][k]; logits [nseq][n_expert] is required (the CTAs meet there);
+ * probs may be NULL; counter is nseq zeroed words, left zeroed. */
+void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits,
+                             int32_t *ids, float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd); /* :325 */
 void llamd_fwd_moe_combine_add(const float *down, const float *weights, const float *residual,
                                float *out, int n_used, int n_embd, int nseq);           /* :586 */

@@ -18,8 +18,8 @@ extern "C" {
 void llamd_fwd_repack_q6k_at(const void *d_src, void *d_dst, size_t n_blocks, size_t dst_first);
 void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs,
                                   float *d, int n, float eps, int nseq);
-void llamd_fwd_router_matvec(const float *wt, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
-                             float *weights, float *probs, int nseq);
+void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
+                             float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
                               int32_t *ptoken, int32_t *pslot, int32_t *work, int32_t *n_work);
 }
@@ -54,7 +54,7 @@ struct Buf {
 };
 
 struct Layer {
-    Buf attn_norm, attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_out, ffn_norm, ffn_gate_inp_t;
+    Buf attn_norm, attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_out, ffn_norm, ffn_gate_inp;
     Buf gate_exps, up_exps, down_exps;
     bool has_q_norm = false, has_k_norm = false;
     Buf kc, vc;
@@ -69,6 +69,7 @@ struct Model {
     Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, router_logits, router_probs, expert_ids, expert_w;
     Buf e_gate, e_up, e_down, logits, amax_v, amax_i, out_token, meta;
     Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
+    Buf router_counter;      // the router kernel's arrival counters, one per sequence
     Buf tok_log, tok_count;  // device-side record of emitted tokens, for the resident decode loop
     unsigned long long launches_per_pass = 0;
     int32_t *h_meta = nullptr;  // pinned
@@ -160,8 +161,8 @@ void queue_token(Model &m, int nseq) {
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
         llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
                                      m.ad.as<float>(), E, hp.rms_eps, nseq);
-        llamd_fwd_router_matvec(l.ffn_gate_inp_t.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
-                                m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), m.router_probs.as<float>(), nseq);
+        llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
+                                m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
         llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                           m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
         llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
@@ -214,7 +215,7 @@ bool check_ready(Model &m) {
     }
     for (size_t i = 0; i < m.layers.size(); i++) {
         Layer &l = m.layers[i];
-        if (!l.attn_norm.p || !l.attn_q.p || !l.attn_k.p || !l.attn_v.p || !l.attn_out.p || !l.ffn_norm.p || !l.ffn_gate_inp_t.p ||
+        if (!l.attn_norm.p || !l.attn_q.p || !l.attn_k.p || !l.attn_v.p || !l.attn_out.p || !l.ffn_norm.p || !l.ffn_gate_inp.p ||
             !l.gate_exps.p || !l.up_exps.p || !l.down_exps.p) {
             m.err = "model: layer " + std::to_string(i) + " has tensors missing";
             return false;
@@ -320,7 +321,7 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     f(m->expert_w, nu); f(m->e_gate, nu * ffe); f(m->e_up, nu * ffe); f(m->e_down, nu * E);
     f(m->logits, hp->n_vocab); f(m->amax_v, kArgmaxBlocks);
     ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
-    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4);
+    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4) && m->router_counter.alloc(4 * S);
     for (auto &l : m->layers) {
         ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
     }
@@ -351,12 +352,12 @@ void llamd_model_free(llamd_model *h) {
     }
     for (auto &l : m->layers)
         for (Buf *b : {&l.attn_norm, &l.attn_q, &l.attn_k, &l.attn_v, &l.attn_q_norm, &l.attn_k_norm, &l.attn_out, &l.ffn_norm,
-                       &l.ffn_gate_inp_t, &l.gate_exps, &l.up_exps, &l.down_exps, &l.kc, &l.vc})
+                       &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.kc, &l.vc})
             b->release();
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
-                   &m->tok_log, &m->tok_count})
+                   &m->tok_log, &m->tok_count, &m->router_counter})
         b->release();
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out) cudaFreeHost(m->h_out);
@@ -401,16 +402,7 @@ int llamd_model_set_tensor(llamd_model *h, int layer, int which, size_t first_bl
         case LLAMD_T_FFN_GATE_EXPS: total = ne * q6k_blocks_for(ffe, E); ok = upload_q6k_slice(l.gate_exps, total, first_block, host, count); break;
         case LLAMD_T_FFN_UP_EXPS: total = ne * q6k_blocks_for(ffe, E); ok = upload_q6k_slice(l.up_exps, total, first_block, host, count); break;
         case LLAMD_T_FFN_DOWN_EXPS: total = ne * q6k_blocks_for(E, ffe); ok = upload_q6k_slice(l.down_exps, total, first_block, host, count); break;
-        case LLAMD_T_FFN_GATE_INP: {
-            // f32 [n_expert][n_embd]; kept transposed so the sequential dot reads coalesced
-            if (count != ne * E) break;
-            float *raw = (float *)scratch(6, ne * E * sizeof(float));
-            if (!raw) break;
-            if (!l.ffn_gate_inp_t.p && !l.ffn_gate_inp_t.alloc(ne * E * sizeof(float))) break;
-            if (cudaMemcpyAsync(raw, host, ne * E * sizeof(float), cudaMemcpyHostToDevice, stream()) != cudaSuccess) break;
-            llamd_fwd_transpose_f32(raw, l.ffn_gate_inp_t.as<float>(), (int)ne, (int)E);
-            ok = llamd_fwd_sync() == 0;
-        } break;
+        case LLAMD_T_FFN_GATE_INP: ok = count == ne * E && upload_f32(l.ffn_gate_inp, host, ne * E); break;
         default: m->err = "set_tensor: unknown tensor id"; return -1;
         }
     }

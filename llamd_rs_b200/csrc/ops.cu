@@ -15,41 +15,61 @@ namespace llamd {
 __device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
 
 #define WEIGHT_SUM_FLOOR 6.103515625e-5f  // 2^-14, crates/llamd-models/src/moe.rs:50
+constexpr int kMaxUsed = 64;
 
 // ---- f32 matvec: crates/llamd-models/src/model.rs:253-263 -----------------
-// y[row] = fold(-0.0, +) of w[row][t]*x[t], t ascending. wt is [k][rows] so a
-// warp reads one contiguous run per step. One thread per row.
-__device__ __forceinline__ float dot_sequential_t(const float *__restrict__ wt, const float *__restrict__ sx, int k, int rows, int row) {
-    float acc = -0.0f;
-#pragma unroll 8
-    for (int t = 0; t < k; t++) acc = __fadd_rn(acc, __fmul_rn(wt[(size_t)t * rows + row], sx[t]));
+// y[row] = fold(-0.0, +) of w[row][t]*x[t], t ascending; w is [rows][k]. One
+// warp per row: the independent products go to shared memory with coalesced
+// loads, lane 0 walks the ordered sum from there.
+__device__ __forceinline__ float row_dot_sequential(const float *__restrict__ wrow, const float *__restrict__ x, int k, float *prod, int lane) {
+    const float4 *wr = reinterpret_cast<const float4 *>(wrow);
+    const float4 *xr = reinterpret_cast<const float4 *>(x);
+    for (int i = lane; i < k / 4; i += 32) {
+        const float4 a = __ldg(wr + i), b = __ldg(xr + i);
+        reinterpret_cast<float4 *>(prod)[i] = make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
+    }
+    __syncwarp();
+    float acc = -0.0f;  // Rust's f32 Sum folds from -0.0
+    if (lane == 0) {
+        const float4 *p4 = reinterpret_cast<const float4 *>(prod);
+#pragma unroll 4
+        for (int i = 0; i < k / 4; i++) {
+            const float4 v = p4[i];
+            acc = __fadd_rn(acc, v.x);
+            acc = __fadd_rn(acc, v.y);
+            acc = __fadd_rn(acc, v.z);
+            acc = __fadd_rn(acc, v.w);
+        }
+    }
     return acc;
 }
 
-__global__ void matvec_f32_kernel(const float *__restrict__ wt, const float *__restrict__ x, float *__restrict__ out, int k, int rows) {
-    extern __shared__ float sx[];
-    const int seq = blockIdx.y;
-    for (int i = threadIdx.x; i < k; i += blockDim.x) sx[i] = x[(size_t)seq * k + i];
-    __syncthreads();
-    const int row = blockIdx.x * blockDim.x + threadIdx.x;
-    if (row < rows) out[(size_t)seq * rows + row] = dot_sequential_t(wt, sx, k, rows, row);
+__global__ void __launch_bounds__(128) matvec_f32_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
+                                                         int k, int rows) {
+    extern __shared__ __align__(16) float sm[];  // [4][k]
+    const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    const float acc = row_dot_sequential(w + (size_t)row * k, x + (size_t)seq * k, k, sm + (size_t)warp * k, lane);
+    if (lane == 0) out[(size_t)seq * rows + row] = acc;
 }
 
 // ---- route: crates/llamd-models/src/moe.rs:73-113 --------------------------
-// One CTA per sequence, blockDim >= n_expert (<= 1024). s_p holds the logits
-// on entry and the probabilities on exit.
+// One CTA. s_p holds the n_expert logits on entry and the probabilities on
+// exit. Works for any blockDim that is a multiple of 32.
 __device__ void route_block(float *s_p, float *s_red, int *s_redi, int n_expert, int n_used, int32_t *__restrict__ ids,
                             float *__restrict__ weights, float *__restrict__ probs) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
     // max is order-free
-    float m = tid < n_expert ? s_p[tid] : -INFINITY;
+    float m = -INFINITY;
+    for (int i = tid; i < n_expert; i += blockDim.x) m = fmaxf(m, s_p[i]);
     for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
     if (lane == 0) s_red[warp] = m;
     __syncthreads();
     m = s_red[0];
     for (int w = 1; w < nwarps; w++) m = fmaxf(m, s_red[w]);
     __syncthreads();
-    if (tid < n_expert) s_p[tid] = ref_expf(__fsub_rn(s_p[tid], m));
+    for (int i = tid; i < n_expert; i += blockDim.x) s_p[i] = ref_expf(__fsub_rn(s_p[i], m));
     __syncthreads();
     // probs.iter().sum(): left to right from -0.0
     if (tid == 0) {
@@ -59,17 +79,24 @@ __device__ void route_block(float *s_p, float *s_red, int *s_redi, int n_expert,
     }
     __syncthreads();
     const float total = s_red[32];
-    float p = -INFINITY;
-    if (tid < n_expert) {
-        p = __fdiv_rn(s_p[tid], total);
-        s_p[tid] = p;
-        if (probs) probs[tid] = p;
+    for (int i = tid; i < n_expert; i += blockDim.x) {
+        const float p = __fdiv_rn(s_p[i], total);
+        s_p[i] = p;
+        if (probs) probs[i] = p;
     }
     __syncthreads();
-    // n_used rounds of arg-max: probability descending, index ascending
+    // n_used rounds of arg-max: probability descending, index ascending.
+    // A taken expert is marked with -1 (probabilities are never negative).
     for (int k = 0; k < n_used; k++) {
-        float bv = p;
-        int bi = tid < n_expert ? tid : 0x7fffffff;
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = tid; i < n_expert; i += blockDim.x) {
+            const float v = s_p[i];
+            if (v > bv || (v == bv && i < bi)) {
+                bv = v;
+                bi = i;
+            }
+        }
         for (int off = 16; off > 0; off >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
@@ -93,9 +120,8 @@ __device__ void route_block(float *s_p, float *s_red, int *s_redi, int n_expert,
                 }
             s_redi[40 + k] = ix;
             s_red[40 + k] = v;
+            s_p[ix] = -1.0f;  // taken: cannot win again
         }
-        __syncthreads();
-        if (tid == s_redi[40 + k]) p = -INFINITY;  // taken: cannot win again
         __syncthreads();
     }
     if (tid == 0) {
@@ -109,7 +135,6 @@ __device__ void route_block(float *s_p, float *s_red, int *s_redi, int n_expert,
     }
 }
 
-constexpr int kMaxUsed = 64;
 
 __global__ void router_kernel(const float *__restrict__ logits, int n_expert, int n_used, int32_t *__restrict__ ids,
                               float *__restrict__ weights, float *__restrict__ probs) {
@@ -117,28 +142,48 @@ __global__ void router_kernel(const float *__restrict__ logits, int n_expert, in
     __shared__ float s_red[40 + kMaxUsed];
     __shared__ int s_redi[40 + kMaxUsed];
     const int seq = blockIdx.x;
-    if (threadIdx.x < n_expert) s_p[threadIdx.x] = logits[(size_t)seq * n_expert + threadIdx.x];
+    for (int i = threadIdx.x; i < n_expert; i += blockDim.x) s_p[i] = logits[(size_t)seq * n_expert + i];
     __syncthreads();
     route_block(s_p, s_red, s_redi, n_expert, n_used, ids + (size_t)seq * n_used, weights + (size_t)seq * n_used,
                 probs ? probs + (size_t)seq * n_expert : nullptr);
 }
 
-// Router logits and routing in one launch: the f32 matvec above, then route.
-__global__ void router_matvec_kernel(const float *__restrict__ wt, const float *__restrict__ x, int k, int n_expert, int n_used,
-                                     float *__restrict__ logits_out, int32_t *__restrict__ ids, float *__restrict__ weights,
-                                     float *__restrict__ probs) {
-    extern __shared__ float sm[];
-    float *sx = sm, *s_p = sm + k;
+// Router logits and routing in one launch.
+//
+// The logit of expert e is a 2048-long left-to-right f32 sum, a chain no
+// reordering may touch. The products w[e][t]*x[t] are independent, so a warp
+// computes them for its row with coalesced loads and parks them in shared
+// memory; lane 0 then walks the chain from there at the speed of dependent
+// adds. Four rows per CTA run their chains side by side on different SMs. The
+// CTA that finishes last (device-wide counter) has every logit and routes.
+// w is the router matrix as the file holds it, [n_expert][k].
+__global__ void __launch_bounds__(128) router_rows_kernel(const float *__restrict__ w, const float *__restrict__ x, int k, int n_expert,
+                                                          int n_used, float *__restrict__ logits, int32_t *__restrict__ ids,
+                                                          float *__restrict__ weights, float *__restrict__ probs,
+                                                          unsigned int *__restrict__ done_counter) {
+    extern __shared__ __align__(16) float sm[];  // [4][k] products, reused as the route scratch
     __shared__ float s_red[40 + kMaxUsed];
     __shared__ int s_redi[40 + kMaxUsed];
-    const int seq = blockIdx.x;
-    for (int i = threadIdx.x; i < k; i += blockDim.x) sx[i] = x[(size_t)seq * k + i];
-    __syncthreads();
-    if (threadIdx.x < n_expert) {
-        const float l = dot_sequential_t(wt, sx, k, n_expert, threadIdx.x);
-        s_p[threadIdx.x] = l;
-        if (logits_out) logits_out[(size_t)seq * n_expert + threadIdx.x] = l;
+    __shared__ bool s_last;
+    const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row < n_expert) {
+        const float acc = row_dot_sequential(w + (size_t)row * k, x + (size_t)seq * k, k, sm + (size_t)warp * k, lane);
+        if (lane == 0) {
+            logits[(size_t)seq * n_expert + row] = acc;
+            __threadfence();
+        }
     }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicInc(done_counter + seq, gridDim.x - 1);  // wraps to 0 after the last CTA
+        s_last = prev == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float *s_p = sm;
+    for (int i = threadIdx.x; i < n_expert; i += blockDim.x) s_p[i] = __ldcg(logits + (size_t)seq * n_expert + i);
     __syncthreads();
     route_block(s_p, s_red, s_redi, n_expert, n_used, ids + (size_t)seq * n_used, weights + (size_t)seq * n_used,
                 probs ? probs + (size_t)seq * n_expert : nullptr);
@@ -242,16 +287,27 @@ __global__ void kv_store_kernel(float *__restrict__ kc, float *__restrict__ vc, 
 }
 
 // ---- attention: crates/llamd-runtime/src/attention.rs:62-125 ---------------
-// One CTA per (query head, sequence). Scores live in shared memory.
-//   logit[t] = (sum_d q[d]*k[t][d], d ascending) * scale      thread per t
-//   max (order-free), e[t] = exp(logit[t]-max), sum e[t] t ascending (thread 0)
-//   out[d] = sum_t (e[t]*inv) * v[t][d], t ascending            thread per d
-__global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q, const float *__restrict__ kc,
+// One CTA of 256 threads per (query head, sequence).
+//   logit[t] = (sum_d q[d]*k[t][d], d ascending) * scale
+//   max (order-free), e[t] = exp(logit[t]-max), sum e[t] t ascending
+//   out[d] = sum_t (e[t]*inv) * v[t][d], t ascending
+// The three sums are left-to-right chains. K and V are staged through shared
+// memory in tiles of 64 positions, fetched by all threads with many loads in
+// flight and prefetched one tile ahead, so the chains read shared memory only:
+// thread t walks d for its position (tile rows padded to hd+1 words, no bank
+// conflicts), thread d walks t for its output column.
+constexpr int kAttTile = 64;
+
+__global__ void __launch_bounds__(256) attention_kernel(const float *__restrict__ q, const float *__restrict__ kc,
                                                         const float *__restrict__ vc, float *__restrict__ out, int n_head, int n_head_kv,
                                                         int hd, const int32_t *__restrict__ meta, int n_kv_imm, int max_kv) {
-    extern __shared__ float sm[];
-    float *sq = sm, *sl = sm + hd;
-    __shared__ float s_red[8];
+    extern __shared__ __align__(16) float sm[];
+    const int stride = hd + 1;
+    float *sq = sm;                       // [hd]
+    float *sl = sm + hd;                  // [n_kv] scores
+    const int n_kv_cap = meta ? max_kv : n_kv_imm;
+    float *tile = sl + ((n_kv_cap + 3) & ~3);  // [2][kAttTile][stride]
+    __shared__ float s_red[16];
     const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
     const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
@@ -259,44 +315,90 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
     const float *vb = vc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
     const float *qh = q + ((size_t)seq * n_head + h) * hd;
     for (int i = tid; i < hd; i += blockDim.x) sq[i] = qh[i];
-    __syncthreads();
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-    float lmax = -INFINITY;
-    for (int t = tid; t < n_kv; t += blockDim.x) {
-        const float4 *kr = reinterpret_cast<const float4 *>(kb + (size_t)t * kv_dim);
-        float dot = 0.0f;
-        for (int d4 = 0; d4 < hd / 4; d4++) {
-            const float4 kv4 = __ldg(kr + d4);
-            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 0], kv4.x));
-            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 1], kv4.y));
-            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 2], kv4.z));
-            dot = __fadd_rn(dot, __fmul_rn(sq[4 * d4 + 3], kv4.w));
+    const int hd4 = hd / 4, per_tile4 = kAttTile * hd4;  // float4s per tile
+    const int n_tiles = (n_kv + kAttTile - 1) / kAttTile;
+    constexpr int kMaxLd = 8;  // float4 loads in flight per thread (hd 128: 64*32/256)
+
+    // fetch tile `ti` of `base` into registers
+    float4 reg[kMaxLd];
+    auto fetch = [&](const float *base, int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / hd4, c = idx - r * hd4;
+            const int t = ti * kAttTile + r;
+            reg[j] = (idx < per_tile4 && t < n_kv) ? __ldg(reinterpret_cast<const float4 *>(base + (size_t)t * kv_dim) + c)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const float l = __fmul_rn(dot, scale);
-        sl[t] = l;
-        lmax = fmaxf(lmax, l);
+    };
+    auto stash = [&](float *dst) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            if (idx < per_tile4) {
+                const int r = idx / hd4, c = idx - r * hd4;
+                float *p = dst + r * stride + 4 * c;
+                p[0] = reg[j].x;
+                p[1] = reg[j].y;
+                p[2] = reg[j].z;
+                p[3] = reg[j].w;
+            }
+        }
+    };
+
+    // ---- scores ----
+    fetch(kb, 0);
+    float lmax = -INFINITY;
+    for (int ti = 0; ti < n_tiles; ti++) {
+        float *cur = tile + (ti & 1) * kAttTile * stride;
+        stash(cur);
+        __syncthreads();
+        if (ti + 1 < n_tiles) fetch(kb, ti + 1);
+        const int t = ti * kAttTile + tid;
+        if (tid < kAttTile && t < n_kv) {
+            const float *kr = cur + tid * stride;
+            float dot = 0.0f;
+#pragma unroll 8
+            for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(sq[d], kr[d]));
+            const float l = __fmul_rn(dot, scale);
+            sl[t] = l;
+            lmax = fmaxf(lmax, l);
+        }
+        // the buffer written two iterations from now is this one: the barrier
+        // at the top of the next iteration orders those writes after this read
     }
     for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
     if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
     __syncthreads();
     lmax = s_red[0];
-    for (int w = 1; w < (int)(blockDim.x >> 5); w++) lmax = fmaxf(lmax, s_red[w]);
+    for (int w = 1; w < 8; w++) lmax = fmaxf(lmax, s_red[w]);
+    // ---- softmax ----
+    fetch(vb, 0);  // V tile 0 travels while the exponentials and the sum run
     for (int t = tid; t < n_kv; t += blockDim.x) sl[t] = ref_expf(__fsub_rn(sl[t], lmax));
     __syncthreads();
     if (tid == 0) {
         float sum = 0.0f;
 #pragma unroll 8
         for (int t = 0; t < n_kv; t++) sum = __fadd_rn(sum, sl[t]);
-        s_red[4] = __fdiv_rn(1.0f, sum);
+        s_red[8] = __fdiv_rn(1.0f, sum);
     }
     __syncthreads();
-    const float inv = s_red[4];
-    for (int d = tid; d < hd; d += blockDim.x) {
-        float acc = 0.0f;
+    const float inv = s_red[8];
+    // ---- weighted values ----
+    float acc = 0.0f;
+    for (int ti = 0; ti < n_tiles; ti++) {
+        float *cur = tile + (ti & 1) * kAttTile * stride;
+        stash(cur);
+        __syncthreads();
+        if (ti + 1 < n_tiles) fetch(vb, ti + 1);
+        if (tid < hd) {
+            const int t0 = ti * kAttTile, cnt = min(kAttTile, n_kv - t0);
 #pragma unroll 4
-        for (int t = 0; t < n_kv; t++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t], inv), __ldg(vb + (size_t)t * kv_dim + d)));
-        out[((size_t)seq * n_head + h) * hd + d] = acc;
+            for (int r = 0; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t0 + r], inv), cur[r * stride + tid]));
+        }
     }
+    if (tid < hd) out[((size_t)seq * n_head + h) * hd + tid] = acc;
 }
 
 // ---- argmax, lowest index on a tie (llamd_forward.hip:353-389) -------------
@@ -405,12 +507,22 @@ using namespace llamd;
 
 extern "C" {
 
-void llamd_fwd_matvec_f32_batch(const float *wt, const float *x, float *out, int k, int rows, int nseq) {
-    matvec_f32_kernel<<<dim3((rows + 127) / 128, nseq), 128, k * sizeof(float), stream()>>>(wt, x, out, k, rows);
+void llamd_fwd_matvec_f32_batch(const float *w, const float *x, float *out, int k, int rows, int nseq) {
+    const size_t smem = (size_t)4 * k * sizeof(float);
+    if (k % 4 || smem > 200 * 1024) {
+        set_error_msg("matvec_f32: k must be a multiple of 4 and at most 12800");
+        return;
+    }
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaFuncSetAttribute(matvec_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = smem;
+    }
+    matvec_f32_kernel<<<dim3((rows + 3) / 4, nseq), 128, smem, stream()>>>(w, x, out, k, rows);
     LLAMD_CHECK_LAUNCH("matvec_f32");
 }
-void llamd_fwd_matvec_f32(const float *wt, const float *x, float *out, int k, int rows) {
-    llamd_fwd_matvec_f32_batch(wt, x, out, k, rows, 1);
+void llamd_fwd_matvec_f32(const float *w, const float *x, float *out, int k, int rows) {
+    llamd_fwd_matvec_f32_batch(w, x, out, k, rows, 1);
 }
 
 void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *ids, float *weights, float *probs, int nseq) {
@@ -423,14 +535,25 @@ void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *id
     LLAMD_CHECK_LAUNCH("router");
 }
 // The router's f32 matvec (forward.rs:340) and routing (:317) in one launch.
-void llamd_fwd_router_matvec(const float *wt, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
-                             float *weights, float *probs, int nseq) {
-    if (n_expert < 1 || n_expert > 1024 || n_used < 1 || n_used > n_expert || n_used > kMaxUsed) {
-        set_error_msg("router: n_expert must be 1..1024 and n_used 1..min(n_expert,64)");
+// w is [n_expert][k] as uploaded; `counter` is nseq zero-initialised words the
+// kernel leaves at zero again.
+void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
+                             float *weights, float *probs, unsigned int *counter, int nseq) {
+    if (n_expert < 1 || n_expert > 1024 || n_used < 1 || n_used > n_expert || n_used > kMaxUsed || k % 4 || !logits || !counter) {
+        set_error_msg("router: n_expert must be 1..1024, n_used 1..min(n_expert,64), k a multiple of 4, logits and counter given");
         return;
     }
-    const int threads = ((n_expert + 31) / 32) * 32;
-    router_matvec_kernel<<<nseq, threads, (k + n_expert) * sizeof(float), stream()>>>(wt, x, k, n_expert, n_used, logits, ids, weights, probs);
+    const size_t smem = (size_t)4 * k * sizeof(float);
+    if (smem > 200 * 1024 || (size_t)n_expert * sizeof(float) > smem) {
+        set_error_msg("router: k too large (or smaller than n_expert/4) for the shared-memory staging");
+        return;
+    }
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = smem;
+    }
+    router_rows_kernel<<<dim3((n_expert + 3) / 4, nseq), 128, smem, stream()>>>(w, x, k, n_expert, n_used, logits, ids, weights, probs, counter);
     LLAMD_CHECK_LAUNCH("router_matvec");
 }
 
@@ -502,8 +625,8 @@ void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, in
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, int n_head, int n_head_kv, int hd,
                              const int32_t *meta, int n_kv, int max_kv, int nseq) {
-    const size_t smem = (size_t)(hd + max_kv) * sizeof(float);
-    if (hd % 4 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
+    const size_t smem = (size_t)(hd + ((max_kv + 3) & ~3) + 2 * kAttTile * (hd + 1)) * sizeof(float);
+    if (hd % 4 || hd > 256 || kAttTile * (hd / 4) > 8 * 256 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
         set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
         return;
     }
@@ -516,7 +639,7 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
         }
         configured = smem;
     }
-    attention_kernel<<<dim3(n_head, nseq), 128, smem, stream()>>>(q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
+    attention_kernel<<<dim3(n_head, nseq), 256, smem, stream()>>>(q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
     LLAMD_CHECK_LAUNCH("attention");
 }
 // `scores` is accepted for signature parity with the reference and unused:

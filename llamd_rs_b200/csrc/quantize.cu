@@ -80,10 +80,18 @@ __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restri
 // ---- rms_norm: crates/llamd-cpu/src/lib.rs:55-75, then `* w` --------------
 // The sum of squares is a left-to-right f32 chain in the reference; thread 0
 // walks it from shared memory while the other threads wait. One CTA per row.
-__device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ sx, int n, float eps) {
+// ssq holds the squares x[i]*x[i] (computed by all threads); n % 4 == 0.
+__device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ ssq, int n, float eps) {
     float sum = 0.0f;
-#pragma unroll 8
-    for (int i = 0; i < n; i++) sum = __fadd_rn(sum, __fmul_rn(sx[i], sx[i]));
+    const float4 *p4 = reinterpret_cast<const float4 *>(ssq);
+#pragma unroll 4
+    for (int i = 0; i < n / 4; i++) {
+        const float4 v = p4[i];
+        sum = __fadd_rn(sum, v.x);
+        sum = __fadd_rn(sum, v.y);
+        sum = __fadd_rn(sum, v.z);
+        sum = __fadd_rn(sum, v.w);
+    }
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
 }
 
@@ -93,7 +101,8 @@ __device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ 
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                                                        float *__restrict__ sum_out, const float *__restrict__ w, float *__restrict__ out,
                                                        int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps) {
-    extern __shared__ float sx[];
+    extern __shared__ __align__(16) float sx[];  // [n] values, then [n] squares
+    float *ssq = sx + n;
     __shared__ float s_scale;
     const int seq = blockIdx.x;
     x += (size_t)seq * n;
@@ -104,9 +113,10 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
             sum_out[(size_t)seq * n + i] = v;
         }
         sx[i] = v;
+        ssq[i] = __fmul_rn(v, v);
     }
     __syncthreads();
-    if (threadIdx.x == 0) s_scale = rms_scale_sequential(sx, n, eps);
+    if (threadIdx.x == 0) s_scale = rms_scale_sequential(ssq, n, eps);
     __syncthreads();
     const float scale = s_scale;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -131,11 +141,16 @@ __global__ void head_rms_norm_mul_kernel(const float *__restrict__ x, const floa
                                          int hd, float eps) {
     const int head = blockIdx.x;
     if (head >= n_head) return;
-    extern __shared__ float sx[];
+    extern __shared__ __align__(16) float sx[];
+    float *ssq = sx + hd;
     __shared__ float s_scale;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) sx[i] = x[(size_t)head * hd + i];
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+        const float v = x[(size_t)head * hd + i];
+        sx[i] = v;
+        ssq[i] = __fmul_rn(v, v);
+    }
     __syncthreads();
-    if (threadIdx.x == 0) s_scale = rms_scale_sequential(sx, hd, eps);
+    if (threadIdx.x == 0) s_scale = rms_scale_sequential(ssq, hd, eps);
     __syncthreads();
     for (int i = threadIdx.x; i < hd; i += blockDim.x)
         out[(size_t)head * hd + i] = __fmul_rn(__fmul_rn(sx[i], s_scale), w[i]);
@@ -206,30 +221,38 @@ void llamd_fwd_quantize(const float *x, int8_t *qs, float *d, int nblocks) {
 }
 
 void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, float eps, int nseq) {
-    rms_norm_kernel<<<nseq, 256, n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, nullptr, nullptr, n, eps);
+    if (n % 4 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("rms_norm: n must be a multiple of 4 and at most 6144");
+        return;
+    }
+    rms_norm_kernel<<<nseq, 256, 2 * n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, nullptr, nullptr, n, eps);
     LLAMD_CHECK_LAUNCH("rms_norm_mul");
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
-    if (n % 256) {
-        set_error_msg("rms_norm_quant: n must be a multiple of 256");
+    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    rms_norm_kernel<<<nseq, 256, n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, qs, d, n, eps);
+    rms_norm_kernel<<<nseq, 256, 2 * n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, qs, d, n, eps);
     LLAMD_CHECK_LAUNCH("rms_norm_quant");
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
 void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs,
                                   float *d, int n, float eps, int nseq) {
-    if (n % 256) {
-        set_error_msg("add_rms_norm_quant: n must be a multiple of 256");
+    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("add_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    rms_norm_kernel<<<nseq, 256, n * sizeof(float), stream()>>>(x, residual, sum_out, w, out, qs, d, n, eps);
+    rms_norm_kernel<<<nseq, 256, 2 * n * sizeof(float), stream()>>>(x, residual, sum_out, w, out, qs, d, n, eps);
     LLAMD_CHECK_LAUNCH("add_rms_norm_quant");
 }
 void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
-    head_rms_norm_mul_kernel<<<n_head, 128, hd * sizeof(float), stream()>>>(x, w, out, n_head, hd, eps);
+    if (hd % 4) {
+        set_error_msg("head_rms_norm: head_dim must be a multiple of 4");
+        return;
+    }
+    head_rms_norm_mul_kernel<<<n_head, 128, 2 * hd * sizeof(float), stream()>>>(x, w, out, n_head, hd, eps);
     LLAMD_CHECK_LAUNCH("head_rms_norm_mul");
 }
 void llamd_fwd_add(const float *a, const float *b, float *out, int n) {

@@ -1,0 +1,231 @@
+"""Device-pointer ops of the C ABI, wrapped for numpy in / numpy out.
+
+The counterpart of ``llamd_rocm::op`` (crates/llamd-rocm/src/forward.rs:733-1676):
+each function checks sizes before the FFI call, uploads its inputs, queues the
+op on the library stream, synchronises and downloads the result. Meant for
+tests and experiments; the resident model (``model.CudaModel``) chains the same
+entry points without leaving the device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import backend
+from ._lib import lib
+from .backend import DevBuf, Malformed, ShapeError
+
+QK_K = 256
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def quantize(x):
+    """f32 [n] -> (qs int8[n], d f32[n/256]) on the device (op::quantize)."""
+    x = _f32(x).ravel()
+    if x.size == 0 or x.size % QK_K:
+        raise Malformed(f"q8k input: {x.size} is not a multiple of {QK_K}")
+    nb = x.size // QK_K
+    dx, dq, dd = DevBuf.from_array(x), DevBuf(x.size), DevBuf(nb * 4)
+    lib().llamd_fwd_quantize(dx.ptr, dq.ptr, dd.ptr, nb)
+    backend.sync()
+    return dq.download(np.int8, x.size), dd.download_f32(nb)
+
+
+def rms_norm_mul(x, w, eps: float):
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    w = _f32(w).ravel()
+    if w.size != x2.shape[1]:
+        raise ShapeError(f"weight of {w.size} for rows of {x2.shape[1]}")
+    dx, dw, do = DevBuf.from_array(x2), DevBuf.from_array(w), DevBuf(x2.nbytes)
+    lib().llamd_fwd_rms_norm_mul(dx.ptr, dw.ptr, do.ptr, x2.shape[1], eps, x2.shape[0])
+    backend.sync()
+    return do.download_f32(x2.size).reshape(x.shape)
+
+
+def rms_norm_quant(x, w, eps: float, residual=None):
+    """-> (out f32, qs, d[, x+residual])"""
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    n, nseq = x2.shape[1], x2.shape[0]
+    w = _f32(w).ravel()
+    if w.size != n or n % QK_K:
+        raise ShapeError(f"weight of {w.size} for rows of {n}")
+    dx, dw, do = DevBuf.from_array(x2), DevBuf.from_array(w), DevBuf(x2.nbytes)
+    dq, dd = DevBuf(x2.size), DevBuf(nseq * (n // QK_K) * 4)
+    if residual is None:
+        lib().llamd_fwd_rms_norm_quant(dx.ptr, dw.ptr, do.ptr, dq.ptr, dd.ptr, n, eps, nseq)
+        backend.sync()
+        return do.download_f32(x2.size).reshape(x.shape), dq.download(np.int8, x2.size), dd.download_f32(nseq * (n // QK_K))
+    r = _f32(residual).reshape(x2.shape)
+    dr, ds = DevBuf.from_array(r), DevBuf(x2.nbytes)
+    lib().llamd_fwd_add_rms_norm_quant(dx.ptr, dr.ptr, ds.ptr, dw.ptr, do.ptr, dq.ptr, dd.ptr, n, eps, nseq)
+    backend.sync()
+    return (do.download_f32(x2.size).reshape(x.shape), dq.download(np.int8, x2.size), dd.download_f32(nseq * (n // QK_K)),
+            ds.download_f32(x2.size).reshape(x.shape))
+
+
+def head_rms_norm_mul(x, w, n_head: int, hd: int, eps: float):
+    x, w = _f32(x).ravel(), _f32(w).ravel()
+    if x.size != n_head * hd or w.size != hd:
+        raise ShapeError("head_rms_norm_mul sizes")
+    dx, dw, do = DevBuf.from_array(x), DevBuf.from_array(w), DevBuf(x.nbytes)
+    lib().llamd_fwd_head_rms_norm_mul(dx.ptr, dw.ptr, do.ptr, n_head, hd, eps)
+    backend.sync()
+    return do.download_f32(x.size)
+
+
+def rope_table(max_pos: int, hd: int, freq_base: float) -> np.ndarray:
+    tab = np.zeros((max_pos, hd // 2, 2), dtype=np.float32)
+    if lib().llamd_cuda_rope_table(tab.ctypes.data_as(C.c_void_p), max_pos, hd, freq_base) != 0:
+        raise Malformed("rope table arguments")
+    return tab
+
+
+def norm_rope(x, w, n_head: int, hd: int, pos: int, freq_base: float, eps: float):
+    """Per-head RMS norm (w may be None) then NeoX RoPE at `pos` (op::norm_rope)."""
+    x = _f32(x).ravel()
+    if x.size != n_head * hd:
+        raise ShapeError("norm_rope sizes")
+    tab = DevBuf.from_array(rope_table(pos + 1, hd, freq_base))
+    meta = DevBuf.from_array(np.array([0, pos], np.int32))
+    dx = DevBuf.from_array(x)
+    dw = DevBuf.from_array(_f32(w)) if w is not None else None
+    lib().llamd_fwd_norm_rope(dx.ptr, dw.ptr if dw else None, n_head, hd, meta.ptr, tab.ptr, eps, 1)
+    backend.sync()
+    return dx.download_f32(x.size)
+
+
+def attention(q, k, v, n_kv: int, n_head: int, n_head_kv: int, hd: int):
+    q, k, v = _f32(q).ravel(), _f32(k).ravel(), _f32(v).ravel()
+    # same order of checks as attend (crates/llamd-runtime/src/attention.rs:63-85)
+    if n_head_kv == 0 or n_head % n_head_kv:
+        raise Malformed(f"attention: {n_head} query heads do not group into {n_head_kv} kv heads")
+    if hd == 0:
+        raise Malformed("attention: head_dim is zero")
+    if q.size != n_head * hd or k.size != n_kv * n_head_kv * hd or v.size != k.size:
+        raise ShapeError("attention sizes")
+    if n_kv == 0:
+        raise Malformed("attention: nothing to attend to")
+    dq, dk, dv, do = DevBuf.from_array(q), DevBuf.from_array(k), DevBuf.from_array(v), DevBuf(q.nbytes)
+    lib().llamd_fwd_attention(dq.ptr, dk.ptr, dv.ptr, do.ptr, None, n_head, n_head_kv, hd, n_kv)
+    backend.sync()
+    return do.download_f32(q.size)
+
+
+def silu_mul_quant(gate, up):
+    gate, up = _f32(gate).ravel(), _f32(up).ravel()
+    if gate.size != up.size or gate.size % QK_K:
+        raise ShapeError("silu_mul_quant sizes")
+    n = gate.size
+    dg, du, do, dq, dd = DevBuf.from_array(gate), DevBuf.from_array(up), DevBuf(n * 4), DevBuf(n), DevBuf(n // QK_K * 4)
+    lib().llamd_fwd_silu_mul_quant(dg.ptr, du.ptr, do.ptr, dq.ptr, dd.ptr, n)
+    backend.sync()
+    return do.download_f32(n), dq.download(np.int8, n), dd.download_f32(n // QK_K)
+
+
+def silu_mul(gate, up):
+    gate, up = _f32(gate).ravel(), _f32(up).ravel()
+    if gate.size != up.size:
+        raise ShapeError("silu_mul sizes")
+    dg, du, do = DevBuf.from_array(gate), DevBuf.from_array(up), DevBuf(max(gate.nbytes, 4))
+    lib().llamd_fwd_silu_mul(dg.ptr, du.ptr, do.ptr, gate.size)
+    backend.sync()
+    return do.download_f32(gate.size)
+
+
+def router(logits, n_used: int):
+    """-> (ids int32 [nseq][n_used], weights, probs) (op::router)."""
+    logits = _f32(logits)
+    l2 = logits.reshape(-1, logits.shape[-1])
+    nseq, ne = l2.shape
+    if n_used == 0 or n_used > ne:
+        raise Malformed(f"moe routing: {n_used} experts requested of {ne}")
+    dl, di, dw, dp = DevBuf.from_array(l2), DevBuf(nseq * n_used * 4), DevBuf(nseq * n_used * 4), DevBuf(l2.nbytes)
+    lib().llamd_fwd_router(dl.ptr, ne, n_used, di.ptr, dw.ptr, dp.ptr, nseq)
+    backend.sync()
+    return (di.download_i32(nseq * n_used).reshape(nseq, n_used), dw.download_f32(nseq * n_used).reshape(nseq, n_used),
+            dp.download_f32(l2.size).reshape(nseq, ne))
+
+
+def router_matvec(w, x, n_used: int):
+    """Router matrix f32 [n_expert][k] and activations [nseq][k] -> (logits, ids, weights)."""
+    w, x = _f32(w), _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    ne, k = w.shape
+    nseq = x2.shape[0]
+    if x2.shape[1] != k:
+        raise ShapeError("router_matvec sizes")
+    if n_used == 0 or n_used > ne:
+        raise Malformed(f"moe routing: {n_used} experts requested of {ne}")
+    dw_, dx = DevBuf.from_array(w), DevBuf.from_array(x2)
+    dl, di, dwt, dc = DevBuf(nseq * ne * 4), DevBuf(nseq * n_used * 4), DevBuf(nseq * n_used * 4), DevBuf.zeroed(4 * nseq)
+    lib().llamd_fwd_router_matvec(dw_.ptr, dx.ptr, k, ne, n_used, dl.ptr, di.ptr, dwt.ptr, None, dc.ptr, nseq)
+    backend.sync()
+    assert not dc.download(np.uint32, nseq).any(), "arrival counters must return to zero"
+    return (dl.download_f32(nseq * ne).reshape(nseq, ne), di.download_i32(nseq * n_used).reshape(nseq, n_used),
+            dwt.download_f32(nseq * n_used).reshape(nseq, n_used))
+
+
+def matvec_f32(w, x):
+    w, x = _f32(w), _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, k = w.shape
+    if x2.shape[1] != k:
+        raise ShapeError("matvec_f32 sizes")
+    dw_, dx, do = DevBuf.from_array(w), DevBuf.from_array(x2), DevBuf(x2.shape[0] * rows * 4)
+    lib().llamd_fwd_matvec_f32_batch(dw_.ptr, dx.ptr, do.ptr, k, rows, x2.shape[0])
+    backend.sync()
+    return do.download_f32(x2.shape[0] * rows).reshape(x2.shape[0], rows)
+
+
+def moe_combine_add(down, weights, residual):
+    """down [nseq][n_used][n_embd], weights [nseq][n_used], residual [nseq][n_embd] or None."""
+    down, weights = _f32(down), _f32(weights)
+    nseq, nu, E = down.shape
+    if weights.shape != (nseq, nu):
+        raise ShapeError("moe_combine sizes")
+    dd, dw_, do = DevBuf.from_array(down), DevBuf.from_array(weights), DevBuf(nseq * E * 4)
+    dr = DevBuf.from_array(_f32(residual).reshape(nseq, E)) if residual is not None else None
+    lib().llamd_fwd_moe_combine_add(dd.ptr, dw_.ptr, dr.ptr if dr else None, do.ptr, nu, E, nseq)
+    backend.sync()
+    return do.download_f32(nseq * E).reshape(nseq, E)
+
+
+def argmax(x, nblocks: int = 512):
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    nseq, n = x2.shape
+    dx, sv, si, do = DevBuf.from_array(x2), DevBuf(nblocks * nseq * 4), DevBuf(nblocks * nseq * 4), DevBuf(4 * nseq)
+    lib().llamd_fwd_argmax(dx.ptr, n, sv.ptr, si.ptr, do.ptr, nblocks, nseq)
+    backend.sync()
+    return do.download_i32(nseq)
+
+
+def moe_group(ids, n_expert: int, n_used: int):
+    """ids int32 [nseq][n_used] -> dict(gstart, gcount, ptoken, pslot, work [n_work][3])."""
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    nseq = ids.size // n_used
+    npair = nseq * n_used
+    di = DevBuf.from_array(ids)
+    gs, gc = DevBuf(n_expert * 4), DevBuf(n_expert * 4)
+    pt, ps = DevBuf(max(npair, 1) * 4), DevBuf(max(npair, 1) * 4)
+    wk, nw = DevBuf((npair // 8 + n_expert + 1) * 12), DevBuf.zeroed(4)
+    lib().llamd_fwd_moe_group_work(di.ptr, n_expert, n_used, nseq, gs.ptr, gc.ptr, pt.ptr, ps.ptr, wk.ptr, nw.ptr)
+    backend.sync()
+    n_work = int(nw.download_i32(1)[0])
+    return dict(gstart=gs.download_i32(n_expert), gcount=gc.download_i32(n_expert), ptoken=pt.download_i32(npair),
+                pslot=ps.download_i32(npair), work=wk.download_i32(3 * n_work).reshape(n_work, 3))
+
+
+def embed(table: "backend.DeviceWeights", token: int) -> np.ndarray:
+    if token < 0 or token >= table.rows():
+        raise Malformed(f"get_rows: id {token} is outside a table of {table.rows()} rows")
+    do = DevBuf(table.blocks() * QK_K * 4)
+    lib().llamd_fwd_embed(table.ptr, token, do.ptr, table.blocks())
+    backend.sync()
+    return do.download_f32(table.blocks() * QK_K)
