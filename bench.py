@@ -184,6 +184,8 @@ def main():
     ap.add_argument("--prompt", type=int, default=512, help="prompt length consumed before the timed decode")
     ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; the JSON line says so")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
+    ap.add_argument("--pdl-sweep", default="", help="(experiment) comma list of PDL class masks to time, e.g. 0,1,5,15")
     ap.add_argument("--no-graph", action="store_true", help="queue every launch instead of replaying the captured graph "
                     "(for a profiler's launch list; the timed numbers are then not the headline)")
     args = ap.parse_args()
@@ -220,6 +222,10 @@ def main():
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
     if args.no_graph:
         m.use_graph = False
+    if args.no_pdl:
+        from llamd_rs_b200._lib import lib as _l
+
+        _l().llamd_fwd_set_pdl(0)
 
     # each rank decodes its own sequence
     prompt = synth.token_ids(args.prompt, hp["n_vocab"], 0, "prompt", rank)
@@ -241,6 +247,19 @@ def main():
         t = torch.tensor([v], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.pdl_sweep:
+        from llamd_rs_b200._lib import lib as _l
+
+        for mask in [int(v) for v in args.pdl_sweep.split(",")]:
+            _l().llamd_fwd_set_pdl(mask if mask != 1 else 1 | 0x100)
+            m._L.llamd_model_set_option(m._h, b"pdl", mask if mask != 1 else 0x101)
+            for _ in range(3):
+                m.decode(tok, pos, 8)
+            _, ms = m.decode(tok, pos, K)
+            mv, _n = m.bench_matvecs(8)
+            log(f"[pdl-sweep] mask {mask}: {ms / K:.3f} ms/token, matvec-only {mv / 8:.3f} ms")
+        return
 
     # ---- warm-up (both paths) ----
     for _ in range(W):
@@ -293,7 +312,7 @@ def main():
                    "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
                    "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": f"replicas x{world}",
                    "token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "arith": "exact (reference order)",
-                   "graph": not args.no_graph},
+                   "graph": not args.no_graph, "pdl": not args.no_pdl},
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(m.launches_per_pass()) * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,

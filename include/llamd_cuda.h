@@ -61,6 +61,9 @@ int llamd_fwd_last_error(void);
 int llamd_fwd_stream_init(void); /* forward.rs:552 */
 /* Kernel launches issued through the library since load (graph nodes count once, at capture). */
 unsigned long long llamd_fwd_launch_count(void);
+/* Programmatic dependent launch of the decode-path kernels: 1 (default) lets a
+ * kernel's weight prefetch overlap the previous kernel's tail; 0 serialises. */
+void llamd_fwd_set_pdl(int on);
 /* The library's stream as a cudaStream_t, for callers that time with events. */
 void *llamd_fwd_stream(void);
 
@@ -166,6 +169,12 @@ void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t
  * the norm of :173-174. */
 void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w,
                                   float *out, int8_t *qs, float *d, int n, float eps, int nseq);
+/* x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual, :586,
+ * e in routing order), then norm*w and its Q8_K form: a layer's tail fused
+ * with the next layer's attention norm (or the output norm). */
+void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const float *weights, int n_used,
+                                      float *sum_out, const float *w, float *out, int8_t *qs, float *d, int n,
+                                      float eps, int nseq);
 /* rope_tab: [max_pos][hd/2][2] (sin, cos) built by llamd_cuda_rope_table. */
 int llamd_cuda_rope_table(float *host_out, int max_pos, int hd, float freq_base);
 void llamd_fwd_rope(float *x, int pos, int n_head, int hd, const float *rope_tab);       /* :295 */
@@ -174,6 +183,10 @@ void llamd_fwd_norm_rope(float *x, const float *w, int n_head, int hd, const int
 void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float *kc, float *vc,
                                  int n_head_kv, int hd, int kv_dim, const int32_t *meta,
                                  const float *rope_tab, float eps, int nseq, int max_kv); /* :563 */
+/* :553 and :563 in one launch: query heads and key heads together. */
+void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc,
+                                  float *vc, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                                  const float *rope_tab, float eps, int nseq, int max_kv);
 void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, int pos, int kv_dim); /* :296 */
 void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float *out, float *scores,
                          int n_head, int n_head_kv, int hd, int n_kv);                  /* :304 */

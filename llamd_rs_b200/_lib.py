@@ -35,6 +35,7 @@ SIGNATURES = {
     "llamd_fwd_stream_init": (i32, []),
     "llamd_fwd_stream": (vp, []),
     "llamd_fwd_launch_count": (C.c_ulonglong, []),
+    "llamd_fwd_set_pdl": (None, [i32]),
     "llamd_fwd_repack_q6k_at": (None, [vp, vp, sz, sz]),
     "llamd_fwd_begin_capture": (i32, []),
     "llamd_fwd_end_capture": (i32, []),
@@ -78,6 +79,8 @@ SIGNATURES = {
     "llamd_fwd_head_rms_norm_mul": (None, [vp, vp, vp, i32, i32, f32]),
     "llamd_fwd_rms_norm_quant": (None, [vp, vp, vp, vp, vp, i32, f32, i32]),
     "llamd_fwd_add_rms_norm_quant": (None, [vp, vp, vp, vp, vp, vp, vp, i32, f32, i32]),
+    "llamd_fwd_combine_rms_norm_quant": (None, [vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, f32, i32]),
+    "llamd_fwd_qk_norm_rope_store": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32]),
     "llamd_cuda_rope_table": (i32, [vp, i32, i32, f32]),
     "llamd_fwd_rope": (None, [vp, i32, i32, i32, vp]),
     "llamd_fwd_norm_rope": (None, [vp, vp, i32, i32, vp, vp, f32, i32]),

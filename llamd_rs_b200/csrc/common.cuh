@@ -37,6 +37,42 @@ extern unsigned long long g_launches;
         }                                                          \
     } while (0)
 
+// Programmatic dependent launch. Every kernel on the decode path is launched
+// with the stream-serialization attribute relaxed, calls pdl_trigger() first
+// (so the next kernel in the stream may be scheduled while this one runs) and
+// pdl_wait() before it touches anything an earlier kernel wrote. What sits
+// between the two -- streaming read-only weights into registers -- overlaps
+// the tail of the previous kernel. pdl_wait() returns only when the preceding
+// kernel has completed and flushed, and every kernel calls it, so completion
+// is transitive along the stream. Without the attribute both are no-ops.
+extern int g_pdl;
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Kernel classes for the launch attribute (bits of g_pdl).
+enum { PDL_MATVEC = 1, PDL_GROUPED = 2, PDL_ROUTER = 4, PDL_OTHER = 8 };
+
+template <typename... KArgs, typename... Args>
+inline void launch_kc(int cls, const char *what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (g_pdl & cls) ? 1 : 0;
+    g_launches++;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) set_error(e, what);
+}
+template <typename... KArgs, typename... Args>
+inline void launch_k(const char *what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    launch_kc(PDL_OTHER, what, kernel, grid, block, smem, args...);
+}
+
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.
 void *scratch(int slot, size_t bytes);
@@ -50,6 +86,30 @@ constexpr int kTileDOff = 6656;        // 32 x 2 B
 // IEEE binary16 -> binary32, exact (crates/llamd-quant/src/lib.rs:104-108).
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
     return __half2float(__ushort_as_half(h));
+}
+
+// Left-to-right f32 sum of n values in shared memory, starting from `acc`:
+// acc = (...((acc + s[0]) + s[1]) + ...). The adds form one dependent chain, so
+// the loop is software-pipelined (the next 16 values are fetched while the
+// current 16 are added) to run at the latency of a dependent add.
+// s must be 16-byte aligned.
+__device__ __forceinline__ float chain_sum(const float *__restrict__ s, int n, float acc) {
+    const float4 *p = reinterpret_cast<const float4 *>(s);
+    const int nblk = n / 16;
+    if (nblk > 0) {
+        float4 a = p[0], b = p[1], c = p[2], d = p[3];
+        for (int i = 0; i < nblk; i++) {
+            const int j = (i + 1 < nblk) ? (i + 1) : i;
+            const float4 na = p[4 * j], nb = p[4 * j + 1], nc = p[4 * j + 2], nd = p[4 * j + 3];
+            acc = __fadd_rn(acc, a.x); acc = __fadd_rn(acc, a.y); acc = __fadd_rn(acc, a.z); acc = __fadd_rn(acc, a.w);
+            acc = __fadd_rn(acc, b.x); acc = __fadd_rn(acc, b.y); acc = __fadd_rn(acc, b.z); acc = __fadd_rn(acc, b.w);
+            acc = __fadd_rn(acc, c.x); acc = __fadd_rn(acc, c.y); acc = __fadd_rn(acc, c.z); acc = __fadd_rn(acc, c.w);
+            acc = __fadd_rn(acc, d.x); acc = __fadd_rn(acc, d.y); acc = __fadd_rn(acc, d.z); acc = __fadd_rn(acc, d.w);
+            a = na; b = nb; c = nc; d = nd;
+        }
+    }
+    for (int i = nblk * 16; i < n; i++) acc = __fadd_rn(acc, s[i]);
+    return acc;
 }
 
 }  // namespace llamd

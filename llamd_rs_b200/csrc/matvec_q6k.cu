@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(kThreads) matvec_q6k_kernel(const MatvecParams
     float *s_ex = reinterpret_cast<float *>(smem + (size_t)NSEQ * nb * kActBlockWords * 4);
     int8_t *s_nat = reinterpret_cast<int8_t *>(s_ex);
 
+    pdl_trigger();
     // ---- which job / slot / rows -------------------------------------
     const int slot = blockIdx.x / p.ctas_per_slot;
     const int cta = blockIdx.x - slot * p.ctas_per_slot;
@@ -84,6 +85,7 @@ __global__ void __launch_bounds__(kThreads) matvec_q6k_kernel(const MatvecParams
     // expert 0: the host wrappers refuse such ids before any launch.
     long long expert_off = 0;
     if (p.ids) {
+        pdl_wait();  // the ids come from the router kernel
         int e = p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
         expert_off = (long long)e * p.expert_units;
@@ -110,6 +112,9 @@ __global__ void __launch_bounds__(kThreads) matvec_q6k_kernel(const MatvecParams
         dbits = __ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl);
     }
 
+    // Ungrouped: the weight loads above do not depend on the previous kernel and
+    // are in flight while it finishes; the activations below do.
+    if (!p.ids) pdl_wait();
     // ---- stage the activations ----------------------------------------
     // natural order bytes first (coalesced 16-byte copies) ...
     {
@@ -228,8 +233,7 @@ static void launch_t(const MatvecParams &p, int grid) {
         }
         configured = smem;
     }
-    matvec_q6k_kernel<NSEQ><<<grid, kThreads, smem, stream()>>>(p);
-    LLAMD_CHECK_LAUNCH("matvec_q6k");
+    launch_kc(p.ids ? PDL_GROUPED : PDL_MATVEC, "matvec_q6k", matvec_q6k_kernel<NSEQ>, dim3(grid), dim3(kThreads), smem, p);
 }
 
 // Build the launch. `rows[i]`/`w[i]`/`out[i]` describe up to three matrices

@@ -18,6 +18,10 @@ extern "C" {
 void llamd_fwd_repack_q6k_at(const void *d_src, void *d_dst, size_t n_blocks, size_t dst_first);
 void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs,
                                   float *d, int n, float eps, int nseq);
+void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const float *weights, int n_used, float *sum_out,
+                                      const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq);
+void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc, int n_head,
+                                  int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv);
 void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
                              float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
@@ -89,6 +93,8 @@ unsigned long long g_next_id = 1, g_graph_owner = 0;
 // resident decode loop.
 __global__ void advance_meta_kernel(int32_t *__restrict__ meta, const int32_t *__restrict__ out_token, int32_t *__restrict__ tok_log,
                                     int32_t *__restrict__ tok_count, int nseq, int log_cap) {
+    pdl_trigger();
+    pdl_wait();
     const int s = threadIdx.x;
     const int c = *tok_count;
     __syncthreads();
@@ -142,18 +148,29 @@ void queue_token(Model &m, int nseq) {
     float *x = m.x.as<float>();
 
     llamd_fwd_embed_meta(m.tok_embd.p, meta, x, eb, nseq);
+    auto trace_x = [&](int il) {
+        if (m.trace)
+            cudaMemcpyAsync(m.trace_x.as<float>() + (size_t)il * m.max_seq * E, x, (size_t)nseq * E * sizeof(float), cudaMemcpyDeviceToDevice,
+                            stream());
+    };
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
-        // attention norm, f32 and Q8_K in one pass: Q, K and V read the same activation
-        llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+        // Attention norm, f32 and Q8_K in one pass (Q, K and V read the same
+        // activation). From the second layer on the same launch first finishes
+        // the previous layer: x += sum_e w_e * down_e.
+        if (il == 0) {
+            llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+        } else {
+            llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
+                                             m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+            trace_x(il - 1);
+        }
         llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
                                   m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
-        llamd_fwd_norm_rope(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, H, hd, meta, m.rope_tab.as<float>(),
-                            hp.rms_eps, nseq);
-        llamd_fwd_k_norm_rope_store(m.k.as<float>(), l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(),
-                                    l.kc.as<float>(), l.vc.as<float>(), HKV, hd, kvd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq,
-                                    m.max_kv);
+        llamd_fwd_qk_norm_rope_store(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
+                                     l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
+                                     l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
         llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), nullptr, H, HKV, hd, meta,
                                  m.max_kv, nseq);
         llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
@@ -169,22 +186,20 @@ void queue_token(Model &m, int nseq) {
                                  nseq * nu * ffe);
         llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                           m.e_down.as<float>(), ffe / 256, E, nu, nseq);
-        llamd_fwd_moe_combine_add(m.e_down.as<float>(), m.expert_w.as<float>(), x, x, nu, E, nseq);
-        if (m.trace) {
-            cudaMemcpyAsync(m.trace_x.as<float>() + (size_t)il * m.max_seq * E, x, (size_t)nseq * E * sizeof(float),
-                            cudaMemcpyDeviceToDevice, stream());
+        if (m.trace)
             cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
                             cudaMemcpyDeviceToDevice, stream());
-        }
     }
-    llamd_fwd_rms_norm_quant(x, m.output_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+    // the last layer's combine, fused with the output norm
+    llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
+                                     m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+    trace_x(hp.n_layer - 1);
     llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
                            hp.n_vocab, nseq);
     llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
                      kArgmaxBlocks, nseq);
-    advance_meta_kernel<<<1, 32, 0, stream()>>>(m.meta.as<int32_t>(), m.out_token.as<int32_t>(), m.tok_log.as<int32_t>(),
-                                                m.tok_count.as<int32_t>(), nseq, m.max_kv * m.max_seq);
-    LLAMD_CHECK_LAUNCH("advance_meta");
+    launch_k("advance_meta", advance_meta_kernel, dim3(1), dim3(32), 0, m.meta.as<int32_t>(), (const int32_t *)m.out_token.as<int32_t>(),
+             m.tok_log.as<int32_t>(), m.tok_count.as<int32_t>(), nseq, m.max_kv * m.max_seq);
 }
 
 // Only the Q6_K matvec launches of one pass, with whatever activations and
@@ -422,6 +437,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!m || !name) return -1;
     if (!strcmp(name, "use_graph")) {
         m->use_graph = value;
+        return 0;
+    }
+    if (!strcmp(name, "pdl")) {
+        llamd_fwd_set_pdl(value);
+        if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded in the other mode
         return 0;
     }
     if (!strcmp(name, "trace")) {

@@ -24,32 +24,30 @@ constexpr int kMaxUsed = 64;
 __device__ __forceinline__ float row_dot_sequential(const float *__restrict__ wrow, const float *__restrict__ x, int k, float *prod, int lane) {
     const float4 *wr = reinterpret_cast<const float4 *>(wrow);
     const float4 *xr = reinterpret_cast<const float4 *>(x);
+    // the weight row does not depend on the previous kernel: park it in shared
+    // memory before waiting for the activation
+    for (int i = lane; i < k / 4; i += 32) reinterpret_cast<float4 *>(prod)[i] = __ldg(wr + i);
+    pdl_wait();
     for (int i = lane; i < k / 4; i += 32) {
-        const float4 a = __ldg(wr + i), b = __ldg(xr + i);
+        const float4 a = reinterpret_cast<float4 *>(prod)[i], b = __ldg(xr + i);
         reinterpret_cast<float4 *>(prod)[i] = make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
     }
     __syncwarp();
     float acc = -0.0f;  // Rust's f32 Sum folds from -0.0
-    if (lane == 0) {
-        const float4 *p4 = reinterpret_cast<const float4 *>(prod);
-#pragma unroll 4
-        for (int i = 0; i < k / 4; i++) {
-            const float4 v = p4[i];
-            acc = __fadd_rn(acc, v.x);
-            acc = __fadd_rn(acc, v.y);
-            acc = __fadd_rn(acc, v.z);
-            acc = __fadd_rn(acc, v.w);
-        }
-    }
+    if (lane == 0) acc = chain_sum(prod, k, acc);
     return acc;
 }
 
 __global__ void __launch_bounds__(128) matvec_f32_kernel(const float *__restrict__ w, const float *__restrict__ x, float *__restrict__ out,
                                                          int k, int rows) {
     extern __shared__ __align__(16) float sm[];  // [4][k]
+    pdl_trigger();
     const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;
-    if (row >= rows) return;
+    if (row >= rows) {
+        pdl_wait();
+        return;
+    }
     const float acc = row_dot_sequential(w + (size_t)row * k, x + (size_t)seq * k, k, sm + (size_t)warp * k, lane);
     if (lane == 0) out[(size_t)seq * rows + row] = acc;
 }
@@ -72,11 +70,7 @@ __device__ void route_block(float *s_p, float *s_red, int *s_redi, int n_expert,
     for (int i = tid; i < n_expert; i += blockDim.x) s_p[i] = ref_expf(__fsub_rn(s_p[i], m));
     __syncthreads();
     // probs.iter().sum(): left to right from -0.0
-    if (tid == 0) {
-        float total = -0.0f;
-        for (int i = 0; i < n_expert; i++) total = __fadd_rn(total, s_p[i]);
-        s_red[32] = total;
-    }
+    if (tid == 0) s_red[32] = chain_sum(s_p, n_expert, -0.0f);
     __syncthreads();
     const float total = s_red[32];
     for (int i = tid; i < n_expert; i += blockDim.x) {
@@ -141,6 +135,8 @@ __global__ void router_kernel(const float *__restrict__ logits, int n_expert, in
     extern __shared__ float s_p[];
     __shared__ float s_red[40 + kMaxUsed];
     __shared__ int s_redi[40 + kMaxUsed];
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.x;
     for (int i = threadIdx.x; i < n_expert; i += blockDim.x) s_p[i] = logits[(size_t)seq * n_expert + i];
     __syncthreads();
@@ -165,6 +161,7 @@ __global__ void __launch_bounds__(128) router_rows_kernel(const float *__restric
     __shared__ float s_red[40 + kMaxUsed];
     __shared__ int s_redi[40 + kMaxUsed];
     __shared__ bool s_last;
+    pdl_trigger();
     const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;
     if (row < n_expert) {
@@ -173,6 +170,8 @@ __global__ void __launch_bounds__(128) router_rows_kernel(const float *__restric
             logits[(size_t)seq * n_expert + row] = acc;
             __threadfence();
         }
+    } else {
+        pdl_wait();
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -195,6 +194,8 @@ template <int NSEQ>
 __global__ void __launch_bounds__(128) matvec_q8_0_kernel(const uint8_t *__restrict__ tiled, const float *__restrict__ x,
                                                           float *__restrict__ out, int blocks, int rows) {
     extern __shared__ float sx[];  // [NSEQ][k]
+    pdl_trigger();
+    pdl_wait();
     const int k = blocks * 32;
     for (int i = threadIdx.x; i < NSEQ * k; i += blockDim.x) sx[i] = x[i];
     __syncthreads();
@@ -233,12 +234,21 @@ __global__ void __launch_bounds__(128) matvec_q8_0_kernel(const uint8_t *__restr
 // One CTA of hd/2 threads per head; thread 0 walks the sum of squares. The
 // sin/cos come from a table the host built with its own libm, which is what
 // the reference's CPU path calls (powf, sin, cos).
-__global__ void norm_rope_kernel(float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ v_src,
-                                 float *__restrict__ kc, float *__restrict__ vc, int n_head, int hd, const int32_t *__restrict__ meta,
-                                 int pos_imm, const float *__restrict__ rope_tab, float eps, int max_kv) {
+__global__ void norm_rope_kernel(float *__restrict__ xq, const float *__restrict__ wq, float *__restrict__ xk, const float *__restrict__ wk,
+                                 const float *__restrict__ v_src, float *__restrict__ kc, float *__restrict__ vc, int n_head_q,
+                                 int n_head_k, int hd, const int32_t *__restrict__ meta, int pos_imm, const float *__restrict__ rope_tab,
+                                 float eps, int max_kv) {
     extern __shared__ float sx[];
     __shared__ float s_scale;
-    const int head = blockIdx.x, seq = blockIdx.y, half = hd / 2, i = threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    // blocks [0, n_head_q) are query heads, [n_head_q, n_head_q + n_head_k) key heads
+    const bool is_k = (int)blockIdx.x >= n_head_q;
+    const int head = is_k ? blockIdx.x - n_head_q : blockIdx.x;
+    const int n_head = is_k ? n_head_k : n_head_q;
+    float *x = is_k ? xk : xq;
+    const float *w = is_k ? wk : wq;
+    const int seq = blockIdx.y, half = hd / 2, i = threadIdx.x;
     const int pos = meta ? meta[2 * seq + 1] : pos_imm;
     float *xh = x + ((size_t)seq * n_head + head) * hd;
     sx[i] = xh[i];
@@ -265,7 +275,7 @@ __global__ void norm_rope_kernel(float *__restrict__ x, const float *__restrict_
     const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
     xh[i] = o0;
     xh[i + half] = o1;
-    if (kc) {
+    if (is_k && kc) {
         const int kv_dim = n_head * hd;
         float *kdst = kc + ((size_t)seq * max_kv + pos) * kv_dim + (size_t)head * hd;
         float *vdst = vc + ((size_t)seq * max_kv + pos) * kv_dim + (size_t)head * hd;
@@ -279,6 +289,8 @@ __global__ void norm_rope_kernel(float *__restrict__ x, const float *__restrict_
 
 __global__ void kv_store_kernel(float *__restrict__ kc, float *__restrict__ vc, const float *__restrict__ k, const float *__restrict__ v,
                                 int pos, int kv_dim) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < kv_dim) {
         kc[(size_t)pos * kv_dim + i] = k[i];
@@ -308,6 +320,8 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
     const int n_kv_cap = meta ? max_kv : n_kv_imm;
     float *tile = sl + ((n_kv_cap + 3) & ~3);  // [2][kAttTile][stride]
     __shared__ float s_red[16];
+    pdl_trigger();
+    pdl_wait();
     const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
     const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
@@ -359,8 +373,23 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
         if (tid < kAttTile && t < n_kv) {
             const float *kr = cur + tid * stride;
             float dot = 0.0f;
-#pragma unroll 8
-            for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(sq[d], kr[d]));
+            if ((hd & 15) == 0) {
+                // blocks of 16 products, the next block fetched while this one is added
+                float pa[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(sq[i], kr[i]);
+                for (int d0 = 0; d0 < hd; d0 += 16) {
+                    const int dn = (d0 + 16 < hd) ? d0 + 16 : d0;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(sq[dn + i], kr[dn + i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) dot = __fadd_rn(dot, pa[i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pa[i] = pb[i];
+                }
+            } else {
+                for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(sq[d], kr[d]));
+            }
             const float l = __fmul_rn(dot, scale);
             sl[t] = l;
             lmax = fmaxf(lmax, l);
@@ -377,12 +406,7 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
     fetch(vb, 0);  // V tile 0 travels while the exponentials and the sum run
     for (int t = tid; t < n_kv; t += blockDim.x) sl[t] = ref_expf(__fsub_rn(sl[t], lmax));
     __syncthreads();
-    if (tid == 0) {
-        float sum = 0.0f;
-#pragma unroll 8
-        for (int t = 0; t < n_kv; t++) sum = __fadd_rn(sum, sl[t]);
-        s_red[8] = __fdiv_rn(1.0f, sum);
-    }
+    if (tid == 0) s_red[8] = __fdiv_rn(1.0f, chain_sum(sl, n_kv, 0.0f));
     __syncthreads();
     const float inv = s_red[8];
     // ---- weighted values ----
@@ -394,8 +418,24 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
         if (ti + 1 < n_tiles) fetch(vb, ti + 1);
         if (tid < hd) {
             const int t0 = ti * kAttTile, cnt = min(kAttTile, n_kv - t0);
+            if (cnt == kAttTile) {
+                float pa[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(__fmul_rn(sl[t0 + i], inv), cur[i * stride + tid]);
+#pragma unroll
+                for (int r0 = 0; r0 < kAttTile; r0 += 16) {
+                    const int rn = (r0 + 16 < kAttTile) ? r0 + 16 : r0;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(__fmul_rn(sl[t0 + rn + i], inv), cur[(rn + i) * stride + tid]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) acc = __fadd_rn(acc, pa[i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pa[i] = pb[i];
+                }
+            } else {
 #pragma unroll 4
-            for (int r = 0; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t0 + r], inv), cur[r * stride + tid]));
+                for (int r = 0; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t0 + r], inv), cur[r * stride + tid]));
+            }
         }
     }
     if (tid < hd) out[((size_t)seq * n_head + h) * hd + tid] = acc;
@@ -409,6 +449,8 @@ __device__ __forceinline__ void argmax_combine(float &v, int &i, float ov, int o
     }
 }
 __global__ void argmax_partial_kernel(const float *__restrict__ x, int n, float *__restrict__ pv, int32_t *__restrict__ pi) {
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.y;
     x += (size_t)seq * n;
     float v = -INFINITY;
@@ -429,6 +471,8 @@ __global__ void argmax_partial_kernel(const float *__restrict__ x, int n, float 
     }
 }
 __global__ void argmax_final_kernel(const float *__restrict__ pv, const int32_t *__restrict__ pi, int nblocks, int32_t *__restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.x;
     float v = -INFINITY;
     int ix = 0x7fffffff;
@@ -459,6 +503,8 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, 
     extern __shared__ int s_ids[];
     __shared__ int s_start[1024];
     __shared__ int s_wstart[1024];
+    pdl_trigger();
+    pdl_wait();
     const int e = threadIdx.x;
     for (int p = threadIdx.x; p < npair; p += blockDim.x) s_ids[p] = ids[p];
     __syncthreads();
@@ -518,8 +564,7 @@ void llamd_fwd_matvec_f32_batch(const float *w, const float *x, float *out, int 
         cudaFuncSetAttribute(matvec_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured = smem;
     }
-    matvec_f32_kernel<<<dim3((rows + 3) / 4, nseq), 128, smem, stream()>>>(w, x, out, k, rows);
-    LLAMD_CHECK_LAUNCH("matvec_f32");
+    launch_k("matvec_f32", matvec_f32_kernel, dim3((rows + 3) / 4, nseq), dim3(128), smem, w, x, out, k, rows);
 }
 void llamd_fwd_matvec_f32(const float *w, const float *x, float *out, int k, int rows) {
     llamd_fwd_matvec_f32_batch(w, x, out, k, rows, 1);
@@ -531,8 +576,7 @@ void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *id
         return;
     }
     const int threads = ((n_expert + 31) / 32) * 32;
-    router_kernel<<<nseq, threads, n_expert * sizeof(float), stream()>>>(logits, n_expert, n_used, ids, weights, probs);
-    LLAMD_CHECK_LAUNCH("router");
+    launch_k("router", router_kernel, dim3(nseq), dim3(threads), n_expert * sizeof(float), logits, n_expert, n_used, ids, weights, probs);
 }
 // The router's f32 matvec (forward.rs:340) and routing (:317) in one launch.
 // w is [n_expert][k] as uploaded; `counter` is nseq zero-initialised words the
@@ -553,8 +597,8 @@ void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert
         cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured = smem;
     }
-    router_rows_kernel<<<dim3((n_expert + 3) / 4, nseq), 128, smem, stream()>>>(w, x, k, n_expert, n_used, logits, ids, weights, probs, counter);
-    LLAMD_CHECK_LAUNCH("router_matvec");
+    launch_kc(PDL_ROUTER, "router_matvec", router_rows_kernel, dim3((n_expert + 3) / 4, nseq), dim3(128), smem, w, x, k, n_expert, n_used, logits, ids,
+             weights, probs, counter);
 }
 
 void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq) {
@@ -572,13 +616,13 @@ void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks
             cudaFuncSetAttribute(matvec_q8_0_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
             configured = smem;                                                                                         \
         }                                                                                                              \
-        matvec_q8_0_kernel<N><<<grid, 128, smem, stream()>>>(t, x, out, blocks32, rows);                               \
+        launch_k("matvec_q8_0", matvec_q8_0_kernel<N>, grid, dim3(128), smem, t, x, out, blocks32, rows);                \
     } break;
     switch (nseq) {
         Q80_CASE(1) Q80_CASE(2) Q80_CASE(3) Q80_CASE(4) Q80_CASE(5) Q80_CASE(6) Q80_CASE(7) Q80_CASE(8)
     }
 #undef Q80_CASE
-    LLAMD_CHECK_LAUNCH("matvec_q8_0");
+
 }
 
 // sin/cos for every (pos, i), computed with the host libm exactly as the
@@ -599,14 +643,12 @@ int llamd_cuda_rope_table(float *host_out, int max_pos, int hd, float freq_base)
 }
 
 void llamd_fwd_rope(float *x, int pos, int n_head, int hd, const float *rope_tab) {
-    norm_rope_kernel<<<dim3(n_head, 1), hd / 2, hd * sizeof(float), stream()>>>(x, nullptr, nullptr, nullptr, nullptr, n_head, hd, nullptr,
-                                                                               pos, rope_tab, 0.0f, 0);
-    LLAMD_CHECK_LAUNCH("rope");
+    launch_k("rope", norm_rope_kernel, dim3(n_head, 1), dim3(hd / 2), hd * sizeof(float), x, nullptr, nullptr, nullptr, nullptr, nullptr,
+             nullptr, n_head, 0, hd, nullptr, pos, rope_tab, 0.0f, 0);
 }
 void llamd_fwd_norm_rope(float *x, const float *w, int n_head, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq) {
-    norm_rope_kernel<<<dim3(n_head, nseq), hd / 2, hd * sizeof(float), stream()>>>(x, w, nullptr, nullptr, nullptr, n_head, hd, meta, 0,
-                                                                                  rope_tab, eps, 0);
-    LLAMD_CHECK_LAUNCH("norm_rope");
+    launch_k("norm_rope", norm_rope_kernel, dim3(n_head, nseq), dim3(hd / 2), hd * sizeof(float), x, w, nullptr, nullptr, nullptr, nullptr,
+             nullptr, n_head, 0, hd, meta, 0, rope_tab, eps, 0);
 }
 void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float *kc, float *vc, int n_head_kv, int hd, int kv_dim,
                                  const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv) {
@@ -614,13 +656,17 @@ void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float
         set_error_msg("k_norm_rope_store: kv_dim != n_head_kv*hd");
         return;
     }
-    norm_rope_kernel<<<dim3(n_head_kv, nseq), hd / 2, hd * sizeof(float), stream()>>>(k, w, v, kc, vc, n_head_kv, hd, meta, 0, rope_tab, eps,
-                                                                                     max_kv);
-    LLAMD_CHECK_LAUNCH("k_norm_rope_store");
+    launch_k("k_norm_rope_store", norm_rope_kernel, dim3(n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), nullptr, nullptr, k, w, v, kc,
+             vc, 0, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
+}
+// Query heads and key heads in one launch: QK-norm, RoPE, and the KV store.
+void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc, int n_head,
+                                  int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv) {
+    launch_k("qk_norm_rope_store", norm_rope_kernel, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc, vc,
+             n_head, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
 }
 void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, int pos, int kv_dim) {
-    kv_store_kernel<<<(kv_dim + 255) / 256, 256, 0, stream()>>>(kc, vc, k, v, pos, kv_dim);
-    LLAMD_CHECK_LAUNCH("kv_store");
+    launch_k("kv_store", kv_store_kernel, dim3((kv_dim + 255) / 256), dim3(256), 0, kc, vc, k, v, pos, kv_dim);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, int n_head, int n_head_kv, int hd,
@@ -639,8 +685,7 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
         }
         configured = smem;
     }
-    attention_kernel<<<dim3(n_head, nseq), 256, smem, stream()>>>(q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
-    LLAMD_CHECK_LAUNCH("attention");
+    launch_k("attention", attention_kernel, dim3(n_head, nseq), dim3(256), smem, q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
 }
 // `scores` is accepted for signature parity with the reference and unused:
 // the scores stay in shared memory.
@@ -657,10 +702,8 @@ void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, 
 
 void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_i, int32_t *out, int nblocks, int nseq) {
     if (nblocks < 1) nblocks = 1;
-    argmax_partial_kernel<<<dim3(nblocks, nseq), 256, 0, stream()>>>(x, n, scratch_v, scratch_i);
-    LLAMD_CHECK_LAUNCH("argmax_partial");
-    argmax_final_kernel<<<nseq, 256, 0, stream()>>>(scratch_v, scratch_i, nblocks, out);
-    LLAMD_CHECK_LAUNCH("argmax_final");
+    launch_k("argmax_partial", argmax_partial_kernel, dim3(nblocks, nseq), dim3(256), 0, x, n, scratch_v, scratch_i);
+    launch_k("argmax_final", argmax_final_kernel, dim3(nseq), dim3(256), 0, (const float *)scratch_v, (const int32_t *)scratch_i, nblocks, out);
 }
 
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
@@ -681,8 +724,8 @@ void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int 
         }
         configured = smem;
     }
-    moe_group_kernel<<<1, threads, smem, stream()>>>(ids, n_expert, npair, n_used, gstart, gcount, ptoken, pslot, work, n_work);
-    LLAMD_CHECK_LAUNCH("moe_group");
+    launch_k("moe_group", moe_group_kernel, dim3(1), dim3(threads), smem, ids, n_expert, npair, n_used, gstart, gcount, ptoken, pslot, work,
+             n_work);
 }
 void llamd_fwd_moe_group(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount, int32_t *ptoken,
                          int32_t *pslot) {

@@ -69,6 +69,8 @@ __device__ __forceinline__ void q8k_quantize_block(const float v[8], int lane, i
 
 __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restrict__ x, int8_t *__restrict__ qs, float *__restrict__ d,
                                                            int16_t *__restrict__ bsums, int nblocks) {
+    pdl_trigger();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= nblocks) return;
     const float4 *p = reinterpret_cast<const float4 *>(x + (size_t)warp * 256 + lane * 8);
@@ -82,33 +84,37 @@ __global__ void __launch_bounds__(256) q8k_quantize_kernel(const float *__restri
 // walks it from shared memory while the other threads wait. One CTA per row.
 // ssq holds the squares x[i]*x[i] (computed by all threads); n % 4 == 0.
 __device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ ssq, int n, float eps) {
-    float sum = 0.0f;
-    const float4 *p4 = reinterpret_cast<const float4 *>(ssq);
-#pragma unroll 4
-    for (int i = 0; i < n / 4; i++) {
-        const float4 v = p4[i];
-        sum = __fadd_rn(sum, v.x);
-        sum = __fadd_rn(sum, v.y);
-        sum = __fadd_rn(sum, v.z);
-        sum = __fadd_rn(sum, v.w);
-    }
+    const float sum = chain_sum(ssq, n, 0.0f);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
 }
 
-// out = (x*scale)*w ; optionally Q8_K of out. Dynamic smem: n floats.
-// `residual`/`sum_out`: when given, x := x + residual first (the attention
-// residual, crates/llamd-runtime/src/layer.rs:170) and is written to sum_out.
+// out = (x*scale)*w ; optionally Q8_K of out. Dynamic smem: 2n floats.
+// Before the norm, x may first receive
+//   - `residual`: x := x + residual (the attention residual,
+//     crates/llamd-runtime/src/layer.rs:170), or
+//   - `down`/`cw`: x := x + sum_e cw[e]*down[e] with e in routing order and the
+//     expert sum started from 0 (moe_ffn, layer.rs:243-258, then :281-287),
+// and the updated x is written to sum_out.
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
+                                                       const float *__restrict__ down, const float *__restrict__ cw, int n_used,
                                                        float *__restrict__ sum_out, const float *__restrict__ w, float *__restrict__ out,
                                                        int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps) {
     extern __shared__ __align__(16) float sx[];  // [n] values, then [n] squares
     float *ssq = sx + n;
     __shared__ float s_scale;
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.x;
     x += (size_t)seq * n;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = x[i];
-        if (residual) {
+        if (down) {
+            float acc = 0.0f;
+            for (int e = 0; e < n_used; e++)
+                acc = __fadd_rn(acc, __fmul_rn(cw[(size_t)seq * n_used + e], down[((size_t)seq * n_used + e) * n + i]));
+            v = __fadd_rn(v, acc);
+            sum_out[(size_t)seq * n + i] = v;
+        } else if (residual) {
             v = __fadd_rn(v, residual[(size_t)seq * n + i]);
             sum_out[(size_t)seq * n + i] = v;
         }
@@ -175,6 +181,8 @@ __global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__r
 __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                                                              float *__restrict__ out, int8_t *__restrict__ qs, float *__restrict__ d,
                                                              int nblocks) {
+    pdl_trigger();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= nblocks) return;
     const size_t base = (size_t)warp * 256 + lane * 8;
@@ -194,6 +202,8 @@ __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const float *__rest
 // starts from 0 and the residual is added last.
 __global__ void moe_combine_kernel(const float *__restrict__ down, const float *__restrict__ weights, const float *__restrict__ residual,
                                    float *__restrict__ out, int n_used, int n_embd) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int seq = blockIdx.y;
     if (i >= n_embd) return;
@@ -213,8 +223,7 @@ extern "C" {
 
 void llamd_fwd_quantize_bsums(const float *x, int8_t *qs, float *d, int16_t *bsums, int nblocks) {
     if (nblocks <= 0) return;
-    q8k_quantize_kernel<<<(nblocks + 7) / 8, 256, 0, stream()>>>(x, qs, d, bsums, nblocks);
-    LLAMD_CHECK_LAUNCH("q8k_quantize");
+    launch_k("q8k_quantize", q8k_quantize_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, x, qs, d, bsums, nblocks);
 }
 void llamd_fwd_quantize(const float *x, int8_t *qs, float *d, int nblocks) {
     llamd_fwd_quantize_bsums(x, qs, d, nullptr, nblocks);
@@ -225,16 +234,16 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         set_error_msg("rms_norm: n must be a multiple of 4 and at most 6144");
         return;
     }
-    rms_norm_kernel<<<nseq, 256, 2 * n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, nullptr, nullptr, n, eps);
-    LLAMD_CHECK_LAUNCH("rms_norm_mul");
+    launch_k("rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
+             nullptr, nullptr, n, eps);
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
     if (n % 256 || (size_t)n * 8 > 48 * 1024) {
         set_error_msg("rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    rms_norm_kernel<<<nseq, 256, 2 * n * sizeof(float), stream()>>>(x, nullptr, nullptr, w, out, qs, d, n, eps);
-    LLAMD_CHECK_LAUNCH("rms_norm_quant");
+    launch_k("rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
+             out, qs, d, n, eps);
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
@@ -244,8 +253,20 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
         set_error_msg("add_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    rms_norm_kernel<<<nseq, 256, 2 * n * sizeof(float), stream()>>>(x, residual, sum_out, w, out, qs, d, n, eps);
-    LLAMD_CHECK_LAUNCH("add_rms_norm_quant");
+    launch_k("add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
+             w, out, qs, d, n, eps);
+}
+// x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
+// forward.rs:586), then norm*w and its Q8_K form: the tail of one layer fused
+// with the attention norm of the next (or with the output norm).
+void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const float *weights, int n_used, float *sum_out,
+                                      const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
+    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
+        return;
+    }
+    launch_k("combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
+             sum_out, w, out, qs, d, n, eps);
 }
 void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
     if (hd % 4) {
@@ -269,8 +290,7 @@ void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, in
         return;
     }
     const int nblocks = n / 256;
-    silu_mul_quant_kernel<<<(nblocks + 7) / 8, 256, 0, stream()>>>(gate, up, out, qs, d, nblocks);
-    LLAMD_CHECK_LAUNCH("silu_mul_quant");
+    launch_k("silu_mul_quant", silu_mul_quant_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, gate, up, out, qs, d, nblocks);
 }
 void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd) {
     moe_combine_kernel<<<dim3((n_embd + 255) / 256, 1), 256, 0, stream()>>>(down, weights, nullptr, out, n_used, n_embd);
@@ -278,8 +298,8 @@ void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, 
 }
 void llamd_fwd_moe_combine_add(const float *down, const float *weights, const float *residual, float *out, int n_used, int n_embd,
                                int nseq) {
-    moe_combine_kernel<<<dim3((n_embd + 255) / 256, nseq), 256, 0, stream()>>>(down, weights, residual, out, n_used, n_embd);
-    LLAMD_CHECK_LAUNCH("moe_combine_add");
+    launch_k("moe_combine_add", moe_combine_kernel, dim3((n_embd + 255) / 256, nseq), dim3(256), 0, down, weights, residual, out, n_used,
+             n_embd);
 }
 
 }  // extern "C"

@@ -77,6 +77,8 @@ __global__ void dequantize_q6k_kernel(const uint8_t *__restrict__ tiled, size_t 
 // from a device-resident meta buffer, crates/llamd-rocm/src/forward.rs:594-599).
 __global__ void embed_meta_kernel(const uint8_t *__restrict__ tiled, const int32_t *__restrict__ meta, int token_imm,
                                   float *__restrict__ out, int blocks) {
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.y;
     const int token = meta ? meta[2 * seq] : token_imm;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -194,12 +196,12 @@ void llamd_fwd_dequantize_q6k(const void *d_tiled, size_t first_block, size_t n_
 }
 
 void llamd_fwd_embed(const void *table, int token, float *out, int blocks) {
-    embed_meta_kernel<<<dim3((blocks * LLAMD_QK_K + 255) / 256, 1), 256, 0, stream()>>>((const uint8_t *)table, nullptr, token, out, blocks);
-    LLAMD_CHECK_LAUNCH("embed");
+    launch_k("embed", embed_meta_kernel, dim3((blocks * LLAMD_QK_K + 255) / 256, 1), dim3(256), 0, (const uint8_t *)table, nullptr, token, out,
+             blocks);
 }
 void llamd_fwd_embed_meta(const void *table, const int32_t *meta, float *out, int blocks, int nseq) {
-    embed_meta_kernel<<<dim3((blocks * LLAMD_QK_K + 255) / 256, nseq), 256, 0, stream()>>>((const uint8_t *)table, meta, 0, out, blocks);
-    LLAMD_CHECK_LAUNCH("embed_meta");
+    launch_k("embed_meta", embed_meta_kernel, dim3((blocks * LLAMD_QK_K + 255) / 256, nseq), dim3(256), 0, (const uint8_t *)table, meta, 0,
+             out, blocks);
 }
 
 size_t llamd_cuda_q8_0_tiled_bytes(size_t rows, size_t blocks_per_row) {

@@ -10,6 +10,7 @@
 namespace llamd {
 
 unsigned long long g_launches = 0;
+int g_pdl = 7;  // matvec, grouped matvec and router launches: measured best
 static cudaStream_t g_stream = nullptr;
 static int g_err = 0;
 static std::string g_err_msg;
@@ -167,6 +168,9 @@ int llamd_fwd_last_error(void) {
 }
 int llamd_fwd_stream_init(void) { return stream() ? 0 : -1; }
 unsigned long long llamd_fwd_launch_count(void) { return g_launches; }
+// Programmatic dependent launch on (default) or off, for A/B runs. A captured
+// graph keeps the mode it was recorded in.
+void llamd_fwd_set_pdl(int on) { g_pdl = on == 1 ? 7 : on; }
 void *llamd_fwd_stream(void) { return (void *)stream(); }
 
 int llamd_fwd_begin_capture(void) {
