@@ -73,6 +73,7 @@ struct Model {
     Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, router_logits, router_probs, expert_ids, expert_w;
     Buf e_gate, e_up, e_down, logits, amax_v, amax_i, out_token, meta;
     Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
+    Buf scores;              // [max_seq][n_head][max_kv] scaled attention logits
     Buf router_counter;      // the router kernel's arrival counters, one per sequence
     Buf tok_log, tok_count;  // device-side record of emitted tokens, for the resident decode loop
     unsigned long long launches_per_pass = 0;
@@ -171,7 +172,7 @@ void queue_token(Model &m, int nseq) {
         llamd_fwd_qk_norm_rope_store(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
                                      l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
                                      l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
-        llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), nullptr, H, HKV, hd, meta,
+        llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
                                  m.max_kv, nseq);
         llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
         llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
@@ -336,7 +337,8 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     f(m->expert_w, nu); f(m->e_gate, nu * ffe); f(m->e_up, nu * ffe); f(m->e_down, nu * E);
     f(m->logits, hp->n_vocab); f(m->amax_v, kArgmaxBlocks);
     ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
-    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4) && m->router_counter.alloc(4 * S);
+    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4) && m->router_counter.alloc(4 * S) &&
+         m->scores.alloc((size_t)S * hp->n_head * max_kv * sizeof(float));
     for (auto &l : m->layers) {
         ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
     }
@@ -372,7 +374,7 @@ void llamd_model_free(llamd_model *h) {
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
-                   &m->tok_log, &m->tok_count, &m->router_counter})
+                   &m->tok_log, &m->tok_count, &m->router_counter, &m->scores})
         b->release();
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out) cudaFreeHost(m->h_out);

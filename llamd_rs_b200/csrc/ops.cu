@@ -441,6 +441,177 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
     if (tid < hd) out[((size_t)seq * n_head + h) * hd + tid] = acc;
 }
 
+// ---- attention, split over CTAs ---------------------------------------------
+// The same arithmetic as attention_kernel, cut so that more SMs pull K and V:
+//   attn_scores_kernel  grid (head, kSplit, seq): CTA c takes the 64-position
+//                       tiles ti with ti % kSplit == c and writes the scaled
+//                       logits to the global `scores` buffer;
+//   attn_out_kernel     grid (head, kSplit, seq): every CTA redoes the (cheap)
+//                       softmax over all positions, then walks t for its own
+//                       hd/kSplit output columns.
+// Each position's dot and each output column's sum is still one left-to-right
+// chain, so the result is bit-identical to the single-CTA kernel.
+constexpr int kSplit = 4;
+
+__global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restrict__ q, const float *__restrict__ kc, float *__restrict__ scores,
+                                                          int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta,
+                                                          int n_kv_imm, int max_kv) {
+    extern __shared__ __align__(16) float sm[];
+    const int stride = hd + 1;
+    float *sq = sm;          // [hd]
+    float *tile = sm + hd;   // [2][kAttTile][stride]
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+    const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
+    const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
+    const float *kb = kc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
+    const float *qh = q + ((size_t)seq * n_head + h) * hd;
+    float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
+    for (int i = tid; i < hd; i += blockDim.x) sq[i] = qh[i];
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    const int hd4 = hd / 4, per_tile4 = kAttTile * hd4;
+    const int n_tiles = (n_kv + kAttTile - 1) / kAttTile;
+    constexpr int kMaxLd = 8;
+    float4 reg[kMaxLd];
+    auto fetch = [&](int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / hd4, cc = idx - r * hd4;
+            const int t = ti * kAttTile + r;
+            reg[j] = (idx < per_tile4 && t < n_kv) ? __ldg(reinterpret_cast<const float4 *>(kb + (size_t)t * kv_dim) + cc)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](float *dst) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            if (idx < per_tile4) {
+                const int r = idx / hd4, cc = idx - r * hd4;
+                float *p = dst + r * stride + 4 * cc;
+                p[0] = reg[j].x; p[1] = reg[j].y; p[2] = reg[j].z; p[3] = reg[j].w;
+            }
+        }
+    };
+    if (c < n_tiles) fetch(c);
+    int buf = 0;
+    for (int ti = c; ti < n_tiles; ti += kSplit, buf ^= 1) {
+        float *cur = tile + buf * kAttTile * stride;
+        stash(cur);
+        __syncthreads();
+        if (ti + kSplit < n_tiles) fetch(ti + kSplit);
+        const int t = ti * kAttTile + tid;
+        if (tid < kAttTile && t < n_kv) {
+            const float *kr = cur + tid * stride;
+            float dot = 0.0f;
+            if ((hd & 15) == 0) {
+                float pa[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(sq[i], kr[i]);
+                for (int d0 = 0; d0 < hd; d0 += 16) {
+                    const int dn = (d0 + 16 < hd) ? d0 + 16 : d0;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(sq[dn + i], kr[dn + i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) dot = __fadd_rn(dot, pa[i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pa[i] = pb[i];
+                }
+            } else {
+                for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(sq[d], kr[d]));
+            }
+            sc[t] = __fmul_rn(dot, scale);
+        }
+    }
+}
+
+constexpr int kPvTile = 128;  // positions per V tile
+
+__global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const float *__restrict__ vc, float *__restrict__ out,
+                                                       int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int n_kv_imm,
+                                                       int max_kv) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float s_red[16];
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+    const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
+    const int n_kv_cap = meta ? max_kv : n_kv_imm;
+    const int cols = hd / kSplit, cols4 = cols / 4;  // this CTA's output columns [c*cols, (c+1)*cols)
+    float *sl = sm;                                  // [n_kv]
+    float *tile = sm + ((n_kv_cap + 3) & ~3);        // [2][kPvTile][cols]
+    const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
+    const float *vb = vc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd + (size_t)c * cols;
+    const float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
+    const int per_tile4 = kPvTile * cols4;
+    const int n_tiles = (n_kv + kPvTile - 1) / kPvTile;
+    constexpr int kMaxLd = 4;  // 128 rows x 32 cols / 4 / 256
+    float4 reg[kMaxLd];
+    auto fetch = [&](int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / cols4, cc = idx - r * cols4;
+            const int t = ti * kPvTile + r;
+            reg[j] = (idx < per_tile4 && t < n_kv) ? __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kv_dim) + cc)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](float *dst) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            if (idx < per_tile4) reinterpret_cast<float4 *>(dst)[idx] = reg[j];
+        }
+    };
+    fetch(0);  // V tile 0 travels while the softmax runs
+    float lmax = -INFINITY;
+    for (int t = tid; t < n_kv; t += blockDim.x) {
+        const float l = sc[t];
+        sl[t] = l;
+        lmax = fmaxf(lmax, l);
+    }
+    for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
+    if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
+    __syncthreads();
+    lmax = s_red[0];
+    for (int w = 1; w < 8; w++) lmax = fmaxf(lmax, s_red[w]);
+    for (int t = tid; t < n_kv; t += blockDim.x) sl[t] = ref_expf(__fsub_rn(sl[t], lmax));
+    __syncthreads();
+    if (tid == 0) s_red[8] = __fdiv_rn(1.0f, chain_sum(sl, n_kv, 0.0f));
+    __syncthreads();
+    const float inv = s_red[8];
+    float acc = 0.0f;
+    for (int ti = 0; ti < n_tiles; ti++) {
+        float *cur = tile + (ti & 1) * kPvTile * cols;
+        stash(cur);
+        __syncthreads();
+        if (ti + 1 < n_tiles) fetch(ti + 1);
+        if (tid < cols) {
+            const int t0 = ti * kPvTile, cnt = min(kPvTile, n_kv - t0);
+            int r = 0;
+            if (cnt >= 16) {
+                float pa[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(__fmul_rn(sl[t0 + i], inv), cur[i * cols + tid]);
+                for (; r + 16 <= cnt; r += 16) {
+                    const int rn = (r + 32 <= cnt) ? r + 16 : r;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(__fmul_rn(sl[t0 + rn + i], inv), cur[(rn + i) * cols + tid]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) acc = __fadd_rn(acc, pa[i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pa[i] = pb[i];
+                }
+            }
+            for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t0 + r], inv), cur[r * cols + tid]));
+        }
+    }
+    if (tid < cols) out[((size_t)seq * n_head + h) * hd + (size_t)c * cols + tid] = acc;
+}
+
 // ---- argmax, lowest index on a tie (llamd_forward.hip:353-389) -------------
 __device__ __forceinline__ void argmax_combine(float &v, int &i, float ov, int oi) {
     if (ov > v || (ov == v && oi < i)) {
@@ -669,11 +840,36 @@ void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, in
     launch_k("kv_store", kv_store_kernel, dim3((kv_dim + 255) / 256), dim3(256), 0, kc, vc, k, v, pos, kv_dim);
 }
 
-static void attention_launch(const float *q, const float *kc, const float *vc, float *out, int n_head, int n_head_kv, int hd,
+static void attention_split_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
+                                   int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq) {
+    const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1)) * sizeof(float);
+    const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
+    static size_t conf_a = 0, conf_b = 0;
+    if (smem_a > 48 * 1024 && smem_a > conf_a) {
+        cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        conf_a = smem_a;
+    }
+    if (smem_b > 48 * 1024 && smem_b > conf_b) {
+        cudaFuncSetAttribute(attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+        conf_b = smem_b;
+    }
+    launch_k("attn_scores", attn_scores_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
+             max_kv);
+    launch_k("attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
+             meta, n_kv, max_kv);
+}
+
+static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
                              const int32_t *meta, int n_kv, int max_kv, int nseq) {
     const size_t smem = (size_t)(hd + ((max_kv + 3) & ~3) + 2 * kAttTile * (hd + 1)) * sizeof(float);
     if (hd % 4 || hd > 256 || kAttTile * (hd / 4) > 8 * 256 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
         set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
+        return;
+    }
+    // With a scores buffer ([nseq][n_head][max_kv] floats) and a head_dim the
+    // column split divides, the work is cut over 4x more CTAs.
+    if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 4 * 256) {
+        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq);
         return;
     }
     static size_t configured = 0;
@@ -687,17 +883,16 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     }
     launch_k("attention", attention_kernel, dim3(n_head, nseq), dim3(256), smem, q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
 }
-// `scores` is accepted for signature parity with the reference and unused:
-// the scores stay in shared memory.
+// `scores` (as in the reference's signature) is scratch for the scaled logits,
+// [n_head][n_kv] floats; when it is NULL a single-CTA-per-head kernel keeps
+// them in shared memory instead.
 void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
                          int n_kv) {
-    (void)scores;
-    attention_launch(q, kc, vc, out, n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1);
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1);
 }
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int nseq) {
-    (void)scores;
-    attention_launch(q, kc, vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, nseq);
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq);
 }
 
 void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_i, int32_t *out, int nblocks, int nseq) {

@@ -103,40 +103,108 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
     float *ssq = sx + n;
     __shared__ float s_scale;
     pdl_trigger();
+    const int seq = blockIdx.x, tid = threadIdx.x;
+    // Thread t owns the float4 groups t, t+256, ...: every global load of the
+    // kernel is issued before anything waits on one.
+    constexpr int kMaxV = 6;  // n <= 6144
+    const int n4 = n / 4;
+    float4 wv[kMaxV], xv[kMaxV];
+#pragma unroll
+    for (int u = 0; u < kMaxV; u++) {
+        const int j = tid + u * 256;
+        wv[u] = j < n4 ? __ldg(reinterpret_cast<const float4 *>(w) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_wait();
-    const int seq = blockIdx.x;
-    x += (size_t)seq * n;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = x[i];
-        if (down) {
-            float acc = 0.0f;
-            for (int e = 0; e < n_used; e++)
-                acc = __fadd_rn(acc, __fmul_rn(cw[(size_t)seq * n_used + e], down[((size_t)seq * n_used + e) * n + i]));
-            v = __fadd_rn(v, acc);
-            sum_out[(size_t)seq * n + i] = v;
-        } else if (residual) {
-            v = __fadd_rn(v, residual[(size_t)seq * n + i]);
-            sum_out[(size_t)seq * n + i] = v;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + (size_t)seq * n);
+#pragma unroll
+    for (int u = 0; u < kMaxV; u++) {
+        const int j = tid + u * 256;
+        xv[u] = j < n4 ? x4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (down) {
+        float4 acc[kMaxV];
+#pragma unroll
+        for (int u = 0; u < kMaxV; u++) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float *cws = cw + (size_t)seq * n_used;
+        for (int e0 = 0; e0 < n_used; e0 += 4) {
+            float4 dv[4][kMaxV];
+            float we[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int e = e0 + q;
+                we[q] = e < n_used ? cws[e] : 0.0f;
+                const float4 *d4 = reinterpret_cast<const float4 *>(down + ((size_t)seq * n_used + (e < n_used ? e : 0)) * n);
+#pragma unroll
+                for (int u = 0; u < kMaxV; u++) {
+                    const int j = tid + u * 256;
+                    dv[q][u] = (j < n4 && e < n_used) ? d4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if (e0 + q < n_used) {
+#pragma unroll
+                    for (int u = 0; u < kMaxV; u++) {
+                        acc[u].x = __fadd_rn(acc[u].x, __fmul_rn(we[q], dv[q][u].x));
+                        acc[u].y = __fadd_rn(acc[u].y, __fmul_rn(we[q], dv[q][u].y));
+                        acc[u].z = __fadd_rn(acc[u].z, __fmul_rn(we[q], dv[q][u].z));
+                        acc[u].w = __fadd_rn(acc[u].w, __fmul_rn(we[q], dv[q][u].w));
+                    }
+                }
+            }
         }
-        sx[i] = v;
-        ssq[i] = __fmul_rn(v, v);
+#pragma unroll
+        for (int u = 0; u < kMaxV; u++) {
+            xv[u].x = __fadd_rn(xv[u].x, acc[u].x);
+            xv[u].y = __fadd_rn(xv[u].y, acc[u].y);
+            xv[u].z = __fadd_rn(xv[u].z, acc[u].z);
+            xv[u].w = __fadd_rn(xv[u].w, acc[u].w);
+        }
+    } else if (residual) {
+        const float4 *r4 = reinterpret_cast<const float4 *>(residual + (size_t)seq * n);
+#pragma unroll
+        for (int u = 0; u < kMaxV; u++) {
+            const int j = tid + u * 256;
+            if (j < n4) {
+                const float4 r = r4[j];
+                xv[u].x = __fadd_rn(xv[u].x, r.x);
+                xv[u].y = __fadd_rn(xv[u].y, r.y);
+                xv[u].z = __fadd_rn(xv[u].z, r.z);
+                xv[u].w = __fadd_rn(xv[u].w, r.w);
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kMaxV; u++) {
+        const int j = tid + u * 256;
+        if (j < n4) {
+            if (down || residual) reinterpret_cast<float4 *>(sum_out + (size_t)seq * n)[j] = xv[u];
+            reinterpret_cast<float4 *>(sx)[j] = xv[u];
+            reinterpret_cast<float4 *>(ssq)[j] =
+                make_float4(__fmul_rn(xv[u].x, xv[u].x), __fmul_rn(xv[u].y, xv[u].y), __fmul_rn(xv[u].z, xv[u].z), __fmul_rn(xv[u].w, xv[u].w));
+        }
     }
     __syncthreads();
-    if (threadIdx.x == 0) s_scale = rms_scale_sequential(ssq, n, eps);
+    if (tid == 0) s_scale = rms_scale_sequential(ssq, n, eps);
     __syncthreads();
     const float scale = s_scale;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float o = __fmul_rn(__fmul_rn(sx[i], scale), w[i]);
-        sx[i] = o;
-        if (out) out[(size_t)seq * n + i] = o;
+#pragma unroll
+    for (int u = 0; u < kMaxV; u++) {
+        const int j = tid + u * 256;
+        if (j < n4) {
+            const float4 o = make_float4(__fmul_rn(__fmul_rn(xv[u].x, scale), wv[u].x), __fmul_rn(__fmul_rn(xv[u].y, scale), wv[u].y),
+                                         __fmul_rn(__fmul_rn(xv[u].z, scale), wv[u].z), __fmul_rn(__fmul_rn(xv[u].w, scale), wv[u].w));
+            reinterpret_cast<float4 *>(sx)[j] = o;
+            if (out) reinterpret_cast<float4 *>(out + (size_t)seq * n)[j] = o;
+        }
     }
     if (!qs) return;
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
     for (int b = warp; b < n / 256; b += nwarps) {
         float v[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = sx[b * 256 + lane * 8 + i];
+        const float4 a = reinterpret_cast<const float4 *>(sx + b * 256 + lane * 8)[0], c = reinterpret_cast<const float4 *>(sx + b * 256 + lane * 8)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
         q8k_quantize_block(v, lane, qs + (size_t)seq * n + (size_t)b * 256, d + (size_t)seq * (n / 256) + b, nullptr);
     }
 }

@@ -100,7 +100,9 @@ def norm_rope(x, w, n_head: int, hd: int, pos: int, freq_base: float, eps: float
     return dx.download_f32(x.size)
 
 
-def attention(q, k, v, n_kv: int, n_head: int, n_head_kv: int, hd: int):
+def attention(q, k, v, n_kv: int, n_head: int, n_head_kv: int, hd: int, scores: bool = False):
+    """scores=True hands the kernel a scores scratch buffer, which selects the
+    variant that splits each head over several CTAs."""
     q, k, v = _f32(q).ravel(), _f32(k).ravel(), _f32(v).ravel()
     # same order of checks as attend (crates/llamd-runtime/src/attention.rs:63-85)
     if n_head_kv == 0 or n_head % n_head_kv:
@@ -112,7 +114,8 @@ def attention(q, k, v, n_kv: int, n_head: int, n_head_kv: int, hd: int):
     if n_kv == 0:
         raise Malformed("attention: nothing to attend to")
     dq, dk, dv, do = DevBuf.from_array(q), DevBuf.from_array(k), DevBuf.from_array(v), DevBuf(q.nbytes)
-    lib().llamd_fwd_attention(dq.ptr, dk.ptr, dv.ptr, do.ptr, None, n_head, n_head_kv, hd, n_kv)
+    ds = DevBuf(n_head * n_kv * 4) if scores else None
+    lib().llamd_fwd_attention(dq.ptr, dk.ptr, dv.ptr, do.ptr, ds.ptr if ds else None, n_head, n_head_kv, hd, n_kv)
     backend.sync()
     return do.download_f32(q.size)
 

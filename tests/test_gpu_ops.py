@@ -88,6 +88,8 @@ def test_attention_matches(ops, orc, synth, n_kv):
     if n_kv == 1:
         assert bit_equal(got, want), "a single key gives exactly its value"
     assert max_dev(got, want) <= ATTENTION
+    split = ops.attention(q, k, v, n_kv, n_head, n_head_kv, hd, scores=True)
+    assert bit_equal(split, got), "the split-over-CTAs variant keeps every sum in order"
 
 
 def test_attention_reference_kats(ops, orc):
