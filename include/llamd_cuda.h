@@ -67,6 +67,11 @@ void llamd_fwd_set_pdl(int on);
 /* The library's stream as a cudaStream_t, for callers that time with events. */
 void *llamd_fwd_stream(void);
 
+/* Device-time stopwatch: CUDA events on the library stream (the discipline of
+ * crates/llamd-rocm/kernels/llamd.hip:1120-1141). stop synchronises. */
+int llamd_fwd_timer_start(void);
+int llamd_fwd_timer_stop(float *ms_out);
+
 /* ---- graph capture: crates/llamd-rocm/src/forward.rs:613-617 ----------- */
 int llamd_fwd_begin_capture(void);
 int llamd_fwd_end_capture(void);

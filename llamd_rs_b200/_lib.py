@@ -37,6 +37,8 @@ SIGNATURES = {
     "llamd_fwd_launch_count": (C.c_ulonglong, []),
     "llamd_fwd_set_pdl": (None, [i32]),
     "llamd_fwd_repack_q6k_at": (None, [vp, vp, sz, sz]),
+    "llamd_fwd_timer_start": (i32, []),
+    "llamd_fwd_timer_stop": (i32, [C.POINTER(f32)]),
     "llamd_fwd_begin_capture": (i32, []),
     "llamd_fwd_end_capture": (i32, []),
     "llamd_fwd_graph_launch": (i32, []),

@@ -173,6 +173,24 @@ unsigned long long llamd_fwd_launch_count(void) { return g_launches; }
 void llamd_fwd_set_pdl(int on) { g_pdl = on == 1 ? 7 : on; }
 void *llamd_fwd_stream(void) { return (void *)stream(); }
 
+// Device-time stopwatch on the library stream (CUDA events).
+static cudaEvent_t g_t0 = nullptr, g_t1 = nullptr;
+int llamd_fwd_timer_start(void) {
+    if (!g_t0) {
+        LLAMD_TRY(cudaEventCreate(&g_t0), "event create");
+        LLAMD_TRY(cudaEventCreate(&g_t1), "event create");
+    }
+    LLAMD_TRY(cudaEventRecord(g_t0, stream()), "event record");
+    return 0;
+}
+int llamd_fwd_timer_stop(float *ms_out) {
+    if (!g_t0 || !ms_out) return -1;
+    LLAMD_TRY(cudaEventRecord(g_t1, stream()), "event record");
+    LLAMD_TRY(cudaEventSynchronize(g_t1), "event sync");
+    LLAMD_TRY(cudaEventElapsedTime(ms_out, g_t0, g_t1), "event elapsed");
+    return 0;
+}
+
 int llamd_fwd_begin_capture(void) {
     llamd_fwd_graph_destroy();
     LLAMD_TRY(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal), "begin capture");
