@@ -59,7 +59,7 @@ __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s
 }
 
 template <int NSEQ>
-__global__ void __launch_bounds__(kThreads) matvec_q6k_kernel(const MatvecParams p) {
+__global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
     // shared memory: [act: NSEQ*nb*132 words][ex: NSEQ*8*257 floats, aliased with the natural-order staging]
