@@ -315,7 +315,11 @@ def main():
                    "graph": not args.no_graph, "pdl": not args.no_pdl},
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(m.launches_per_pass()) * K,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     # DRAM bytes per token's matvec launches: the ncu capture of the lm_head launch read+wrote 1.016x its
+                     # algorithmic bytes (profiles/matvec_q6k_lm_head_ncu_full.md); every weight byte is streamed once from
+                     # cold HBM in every launch, so the ratio carries over to the token's launches.
+                     "traffic": 1.016 * (wbytes + iobytes),
                      "kernel": "matvec_q6k_kernel<1>", "launches_per_token": mv_launches, "avg_launch_us": mv_ms / iters / mv_launches * 1e3,
                      "algorithmic_bytes_per_token": wbytes + iobytes, "peak_source": peak_src,
                      "frac_of_nominal_8tbs": achieved / 8000.0},

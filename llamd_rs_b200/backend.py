@@ -4,8 +4,8 @@ Same names, argument meaning and error behaviour as ``llamd-rocm``
 (crates/llamd-rocm/src/lib.rs, crates/llamd-rocm/src/forward.rs): every
 wrapper validates lengths and ids BEFORE the FFI call, device buffers free on
 drop, host-facing calls synchronise. numpy arrays stand in for Rust slices.
-This module is for tests, the bench and Python users; the C++ mirror of the
-same surface is ``include/llamd_cuda.hpp``.
+This module is for tests, the bench and Python users; the compiled host side
+(stream, graph, scratch, the resident model) is C++ inside the library.
 """
 from __future__ import annotations
 
