@@ -198,6 +198,20 @@ void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out,
                               float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta,
                               int max_kv, int nseq);                                    /* :601 */
+/* No counterpart in the reference. llamd_fwd_attention for hosts that cannot
+ * allocate device memory when they call (a server whose own pool owns the whole
+ * GPU, a loop that must not hit the allocator's device synchronisation): the
+ * score scratch is a 1 MiB array built into the library, so this call and
+ * everything under it allocate nothing. q, kc, vc, out are device pointers as
+ * in llamd_fwd_attention; enqueues on the library stream, does not synchronise.
+ * Limit: n_head * n_kv <= 262144 (64 heads x 4096 positions); larger shapes are
+ * refused with -1 and a message in llamd_cuda_last_error_string(). The first
+ * call on a device looks up the array's device address (that device must be
+ * current); make that first call before any stream capture begins. All calls
+ * share the one array: two calls whose kernels overlap on the GPU (different
+ * streams or processes' threads) race on it. Returns 0 / -1. */
+int llamd_fwd_attention_noalloc(const float *q, const float *kc, const float *vc, float *out, int n_head,
+                                int n_head_kv, int hd, int n_kv);
 void llamd_fwd_add(const float *a, const float *b, float *out, int n);                   /* :315 */
 void llamd_fwd_silu_mul(const float *gate, const float *up, float *out, int n);          /* :316 */
 /* silu(gate)*up, then Q8_K of the result (fuses :316 and :375). */

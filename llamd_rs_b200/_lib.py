@@ -90,6 +90,7 @@ SIGNATURES = {
     "llamd_fwd_kv_store": (None, [vp, vp, vp, vp, i32, i32]),
     "llamd_fwd_attention": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32]),
     "llamd_fwd_attention_meta": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32]),
+    "llamd_fwd_attention_noalloc": (i32, [vp, vp, vp, vp, i32, i32, i32, i32]),
     "llamd_fwd_add": (None, [vp, vp, vp, i32]),
     "llamd_fwd_silu_mul": (None, [vp, vp, vp, i32]),
     "llamd_fwd_silu_mul_quant": (None, [vp, vp, vp, vp, vp, i32]),

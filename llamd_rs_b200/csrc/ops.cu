@@ -895,6 +895,56 @@ void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, 
     attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq);
 }
 
+// ---- attention for callers that must not allocate ---------------------------
+// Some hosts of this library cannot obtain device memory at call time: an
+// inference server that hands all of the GPU's memory to its own pool at
+// start-up and forbids any later cudaMalloc, or a real-time loop in which the
+// implicit device synchronisation of the CUDA allocator is not acceptable.
+// For them the score scratch that llamd_fwd_attention takes from its caller
+// lives in this array instead. Every GPU that loads the library carries it
+// (1 MiB) until the process exits.
+constexpr int kStaticScoreFloats = 64 * 4096;  // n_head * n_kv may not exceed this
+static __device__ __align__(256) float g_static_scores[kStaticScoreFloats];
+// In host code `g_static_scores` is only a handle for the runtime, not an
+// address a kernel can use: the device address is looked up once per device.
+constexpr int kMaxDevices = 64;
+static float *g_static_scores_dev[kMaxDevices] = {};
+
+int llamd_fwd_attention_noalloc(const float *q, const float *kc, const float *vc, float *out, int n_head, int n_head_kv, int hd,
+                                int n_kv) {
+    if (!q || !kc || !vc || !out || n_head <= 0 || hd <= 0 || n_kv <= 0) {
+        set_error_msg("attention_noalloc: null pointer or empty shape");
+        return -1;
+    }
+    if ((long long)n_head * n_kv > kStaticScoreFloats) {
+        set_error_msg("attention_noalloc: n_head * n_kv exceeds the built-in scratch of 262144 floats (64 heads x 4096 positions)");
+        return -1;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error(e == cudaSuccess ? cudaErrorInvalidDevice : e, "attention_noalloc: cudaGetDevice");
+        return -1;
+    }
+    if (!g_static_scores_dev[dev]) {
+        // first call on this device (it is the current one): resolve the symbol
+        float *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_static_scores);
+        if (e != cudaSuccess || !p) {
+            set_error(e == cudaSuccess ? cudaErrorInvalidSymbol : e, "attention_noalloc: cudaGetSymbolAddress");
+            return -1;
+        }
+        g_static_scores_dev[dev] = p;
+    }
+    if (!stream()) return -1;
+    const int before = error_code();
+    // Nothing in the scratch has to start at zero: each launch writes the
+    // n_head * n_kv scores it later reads, so the previous call's contents are
+    // simply overwritten.
+    attention_launch(q, kc, vc, out, g_static_scores_dev[dev], n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1);
+    return (before == 0 && error_code() != 0) ? -1 : 0;
+}
+
 void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_i, int32_t *out, int nblocks, int nseq) {
     if (nblocks < 1) nblocks = 1;
     launch_k("argmax_partial", argmax_partial_kernel, dim3(nblocks, nseq), dim3(256), 0, x, n, scratch_v, scratch_i);
