@@ -240,6 +240,29 @@ void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int 
                               int32_t *gcount, int32_t *ptoken, int32_t *pslot, int32_t *work,
                               int32_t *n_work);
 
+/* ---- many tokens at once: the prefill path of VulkanModel::run
+ *      (crates/llamd-runtime/src/vulkan_model.rs:378-853) ------------------- */
+/* Up to three matrices (w1/w2 may be NULL) against ntok activations
+ * [ntok][blocks*256]; outputs [ntok][rows_i]. Weights are reused for 8 tokens
+ * per CTA. */
+void llamd_fwd_matvec_tokens(const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad,
+                             float *o0, float *o1, float *o2, int blocks, int rows0, int rows1, int rows2, int ntok);
+/* Expert-major grouped matvec over the plan of llamd_fwd_moe_group_work
+ * (q6k_expert_major.comp / q6k_expert_major_pa.comp): pair p reads activation
+ * aq[act_map[p]] (ptoken for gate/up, pslot for down) and writes
+ * out[pslot[p]][rows]. wb/ob may be NULL; max_items >= npair/8 + n_expert. */
+void llamd_fwd_expert_major(const void *wa, const void *wb, const int32_t *work, const int32_t *n_work, int max_items,
+                            const int32_t *act_map, const int32_t *pslot, const int8_t *aq, const float *ad,
+                            float *oa, float *ob, int blocks, int rows, int n_expert);
+/* QK-norm/RoPE/KV-store and attention for the ntok tokens of one tile: every
+ * row is a position (meta[2i+1]) of ONE sequence whose cache is kc/vc.
+ * scores: [ntok][n_head][max_kv] floats. */
+void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc,
+                                       float *vc, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                                       const float *rope_tab, float eps, int ntok);
+void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
+                              int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+
 #ifdef __cplusplus
 }
 #endif

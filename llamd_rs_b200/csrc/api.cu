@@ -8,6 +8,9 @@
 namespace llamd {
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div);
+void launch_matvec_multi(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
+                         const float *ad, int n_tokens, const int32_t *work, const int32_t *n_work, int max_items, const int32_t *act_map,
+                         const int32_t *out_map, int n_expert);
 }
 using namespace llamd;
 
@@ -64,6 +67,31 @@ void llamd_fwd_matvec_grouped_pa_batch(const void *w, const int32_t *ids, const 
 void llamd_fwd_matvec_grouped_pa(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks, int rows,
                                  int n_used) {
     llamd_fwd_matvec_grouped_pa_batch(w, ids, aq, ad, out, blocks, rows, n_used, 1);
+}
+
+// ---- many tokens at once (prefill) -------------------------------------------
+// Up to three matrices that share ntok activations [ntok][blocks*256]; outputs [ntok][rows_i].
+void llamd_fwd_matvec_tokens(const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0, float *o1,
+                             float *o2, int blocks, int rows0, int rows1, int rows2, int ntok) {
+    const void *ws[3] = {w0, w1, w2};
+    float *os[3] = {o0, o1, o2};
+    const int rows[3] = {rows0, rows1, rows2};
+    const int njobs = w2 ? 3 : (w1 ? 2 : 1);
+    launch_matvec_multi(njobs, ws, os, rows, blocks, aq, ad, ntok, nullptr, nullptr, 0, nullptr, nullptr, 0);
+}
+// Expert-major grouped matvec over the scatter plan of llamd_fwd_moe_group_work
+// (crates/llamd-vulkan/shaders/q6k_expert_major.comp, q6k_expert_major_pa.comp):
+// for every work item (expert, first, count) the expert's rows are streamed once
+// for `count` pairs. Pair p reads activation aq[act_map[p]] (act_map = ptoken
+// for gate/up, pslot for down) and writes out[pslot[p]][rows]. wb/ob may be NULL.
+// max_items bounds the list length: npair/8 + n_expert always suffices.
+void llamd_fwd_expert_major(const void *wa, const void *wb, const int32_t *work, const int32_t *n_work, int max_items,
+                            const int32_t *act_map, const int32_t *pslot, const int8_t *aq, const float *ad, float *oa, float *ob,
+                            int blocks, int rows, int n_expert) {
+    const void *ws[2] = {wa, wb};
+    float *os[2] = {oa, ob};
+    const int r2[2] = {rows, rows};
+    launch_matvec_multi(wb ? 2 : 1, ws, os, r2, blocks, aq, ad, 0, work, n_work, max_items, act_map, pslot, n_expert);
 }
 
 // ---- host-facing -----------------------------------------------------------

@@ -47,6 +47,14 @@ struct MatvecParams {
     const int8_t *aq;      // activations: [nseq][nb*256] ungrouped, else indexed by slot / act_div
     const float *ad;
     int act_div;           // grouped: activation index = slot / act_div
+    // Many-token ("multi") launches, blockIdx.y = item, NSEQ sequences per item:
+    //   work == null: item g covers tokens g*NSEQ .. (of n_tokens), activation
+    //                 and output index = token;
+    //   work != null: item i = (expert, first, count) of the expert scatter plan;
+    //                 sequence s reads activation act_map[first+s] and writes output
+    //                 row block out_map[first+s]; items >= *n_work do nothing.
+    const int32_t *work, *n_work, *act_map, *out_map;
+    int n_tokens;
 };
 
 // Unpack the four W4 words of quad m of residue r from the three stored words.
@@ -58,7 +66,7 @@ __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s
     w[3] = u | ((s2 << 2) & 0x0C0C0C0Cu);
 }
 
-template <int NSEQ>
+template <int NSEQ, bool MULTI>
 __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
@@ -84,7 +92,30 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
     // expert id of this slot (grouped forms); an id outside the tensor reads
     // expert 0: the host wrappers refuse such ids before any launch.
     long long expert_off = 0;
-    if (p.ids) {
+    __shared__ int s_aidx[NSEQ], s_oidx[NSEQ];
+    int count = NSEQ;
+    if (MULTI) {
+        pdl_wait();
+        const int item = blockIdx.y;
+        int first;
+        if (p.work) {
+            if (item >= *p.n_work) return;
+            int e = p.work[3 * item];
+            if (e < 0 || e >= p.n_expert) e = 0;
+            expert_off = (long long)e * p.expert_units;
+            first = p.work[3 * item + 1];
+            count = min(NSEQ, p.work[3 * item + 2]);
+        } else {
+            first = item * NSEQ;
+            count = min(NSEQ, p.n_tokens - first);
+        }
+        if (tid < NSEQ) {
+            const int sidx = first + (tid < count ? tid : 0);  // unused sequences shadow the first (never stored)
+            s_aidx[tid] = p.act_map ? p.act_map[sidx] : sidx;
+            s_oidx[tid] = p.out_map ? p.out_map[sidx] : sidx;
+        }
+        __syncthreads();
+    } else if (p.ids) {
         pdl_wait();  // the ids come from the router kernel
         int e = p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
@@ -114,14 +145,14 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
 
     // Ungrouped: the weight loads above do not depend on the previous kernel and
     // are in flight while it finishes; the activations below do.
-    if (!p.ids) pdl_wait();
+    if (!MULTI && !p.ids) pdl_wait();
     // ---- stage the activations ----------------------------------------
     // natural order bytes first (coalesced 16-byte copies) ...
     {
         const int n16 = NSEQ * nb * 16;
         for (int i = tid; i < n16; i += kThreads) {
             const int s = i / (nb * 16), o = i - s * nb * 16;
-            const long long a_idx = p.ids ? slot / p.act_div : s;
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
             reinterpret_cast<uint4 *>(s_nat)[i] = __ldg(reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o);
         }
     }
@@ -180,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         const float dw = f16_bits_to_f32(dbits);
 #pragma unroll
         for (int s = 0; s < NSEQ; s++) {
-            const long long a_idx = p.ids ? slot / p.act_div : s;
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
             const float dsc = __fmul_rn(dw, __ldg(p.ad + a_idx * nb + b));
 #pragma unroll
             for (int r = 0; r < 8; r++)
@@ -209,7 +240,11 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
 #pragma unroll
             for (int rr = 1; rr < 8; rr++) total = __fadd_rn(total, __shfl_sync(0xffffffffu, acc, lane0 + rr));
             // ungrouped: out[seq][rows]; grouped: out[slot][rows]
-            if (on && r == 0) job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
+            if (MULTI) {
+                if (on && r == 0 && s < count) job.out[(long long)s_oidx[s] * job.rows + row0 + rl] = total;
+            } else if (on && r == 0) {
+                job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
+            }
         }
     }
 }
@@ -221,19 +256,19 @@ static size_t matvec_smem_bytes(int nseq, int nb) {
     return act + (ex > nat ? ex : nat);
 }
 
-template <int NSEQ>
-static void launch_t(const MatvecParams &p, int grid) {
+template <int NSEQ, bool MULTI = false>
+static void launch_t(const MatvecParams &p, dim3 grid) {
     const size_t smem = matvec_smem_bytes(NSEQ, p.nb);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(matvec_q6k_kernel<NSEQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(matvec_q6k_kernel<NSEQ, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             set_error(e, "matvec smem attribute");
             return;
         }
         configured = smem;
     }
-    launch_kc(p.ids ? PDL_GROUPED : PDL_MATVEC, "matvec_q6k", matvec_q6k_kernel<NSEQ>, dim3(grid), dim3(kThreads), smem, p);
+    launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI>, grid, dim3(kThreads), smem, p);
 }
 
 // Build the launch. `rows[i]`/`w[i]`/`out[i]` describe up to three matrices
@@ -275,7 +310,7 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
     p.aq = aq;
     p.ad = ad;
     p.act_div = act_div < 1 ? 1 : act_div;
-    const int grid = p.ctas_per_slot * p.n_slots;
+    const dim3 grid(p.ctas_per_slot * p.n_slots);
     switch (nseq) {
     case 1: launch_t<1>(p, grid); break;
     case 2: launch_t<2>(p, grid); break;
@@ -286,6 +321,59 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
     case 7: launch_t<7>(p, grid); break;
     default: launch_t<8>(p, grid); break;
     }
+}
+
+// Many tokens against shared weights, 8 at a time (the prefill path).
+//   work == null: every token 0..n_tokens-1 against the matrices w[i] (QKV, attn_out): out[i][token][rows];
+//   work != null: the expert scatter plan's work list (expert, first pair, count<=8): pair p reads activation
+//                 act_map[p] and writes out[out_map[p]][rows], expert-major, so an expert's rows are streamed once
+//                 for up to 8 of its pairs (crates/llamd-vulkan/shaders/q6k_expert_major[_pa].comp).
+void launch_matvec_multi(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
+                         const float *ad, int n_tokens, const int32_t *work, const int32_t *n_work, int max_items, const int32_t *act_map,
+                         const int32_t *out_map, int n_expert) {
+    constexpr int NS = 8;
+    if (blocks <= 0 || blocks > kThreads || njobs < 1 || njobs > 3 || (!work && n_tokens < 1) || (work && (!n_work || max_items < 1))) {
+        set_error_msg("matvec_multi: bad arguments");
+        return;
+    }
+    if (matvec_smem_bytes(NS, blocks) > 200 * 1024) {
+        set_error_msg("matvec_multi: blocks does not fit shared memory");
+        return;
+    }
+    MatvecParams p = {};
+    p.njobs = njobs;
+    p.nb = blocks;
+    p.rows_per_cta = kThreads / blocks;
+    int cta = 0;
+    for (int i = 0; i < njobs; i++) {
+        if (rows[i] <= 0 || (work && rows[i] != rows[0])) {
+            set_error_msg("matvec_multi: rows must be positive (and equal across an expert launch)");
+            return;
+        }
+        p.job[i].w = (const uint8_t *)w[i];
+        p.job[i].out = out[i];
+        p.job[i].rows = rows[i];
+        p.job[i].cta_begin = cta;
+        cta += (rows[i] + p.rows_per_cta - 1) / p.rows_per_cta;
+    }
+    p.ctas_per_slot = cta;
+    p.n_slots = 1;
+    p.n_expert = n_expert;
+    p.expert_units = (long long)rows[0] * blocks;
+    p.aq = aq;
+    p.ad = ad;
+    p.act_div = 1;
+    p.work = work;
+    p.n_work = n_work;
+    p.act_map = act_map;
+    p.out_map = out_map;
+    p.n_tokens = n_tokens;
+    const int items = work ? max_items : (n_tokens + NS - 1) / NS;
+    if (items > 65535) {
+        set_error_msg("matvec_multi: too many items for one launch");
+        return;
+    }
+    launch_t<NS, true>(p, dim3(cta, items));
 }
 
 }  // namespace llamd

@@ -22,6 +22,15 @@ void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const f
                                       const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq);
 void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc, int n_head,
                                   int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv);
+void llamd_fwd_matvec_tokens(const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0, float *o1,
+                             float *o2, int blocks, int rows0, int rows1, int rows2, int ntok);
+void llamd_fwd_expert_major(const void *wa, const void *wb, const int32_t *work, const int32_t *n_work, int max_items,
+                            const int32_t *act_map, const int32_t *pslot, const int8_t *aq, const float *ad, float *oa, float *ob,
+                            int blocks, int rows, int n_expert);
+void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc,
+                                       int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok);
+void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
+                              int hd, const int32_t *meta, int max_kv, int ntok);
 void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
                              float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
@@ -77,6 +86,14 @@ struct Model {
     Buf router_counter;      // the router kernel's arrival counters, one per sequence
     Buf tok_log, tok_count;  // device-side record of emitted tokens, for the resident decode loop
     unsigned long long launches_per_pass = 0;
+    // prefill tile buffers (allocated on first use), token dimension = prefill_tile
+    struct Prefill {
+        int tile = 0;
+        Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, ids, w, logits, counter, gate, up, down, scores, meta;
+        Buf gstart, gcount, ptoken, pslot, work, n_work;
+        int32_t *h_meta = nullptr;
+    } pf;
+    int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
     int32_t *h_meta = nullptr;  // pinned
     int32_t *h_out = nullptr;   // pinned
     size_t weight_bytes = 0;
@@ -376,6 +393,11 @@ void llamd_model_free(llamd_model *h) {
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->scores})
         b->release();
+    for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
+                   &m->pf.ids, &m->pf.w, &m->pf.logits, &m->pf.counter, &m->pf.gate, &m->pf.up, &m->pf.down, &m->pf.scores, &m->pf.meta,
+                   &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work})
+        b->release();
+    if (m->pf.h_meta) cudaFreeHost(m->pf.h_meta);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out) cudaFreeHost(m->h_out);
     delete m;
@@ -441,6 +463,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         m->use_graph = value;
         return 0;
     }
+    if (!strcmp(name, "prefill_tile")) {
+        if (value < 1 || value > 4096) return -1;
+        m->prefill_tile = value;
+        return 0;
+    }
     if (!strcmp(name, "pdl")) {
         llamd_fwd_set_pdl(value);
         if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded in the other mode
@@ -473,20 +500,127 @@ int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32
     return run(*m, tokens, positions, nseq, out_tokens);
 }
 
-// VulkanModel::prefill (crates/llamd-runtime/src/vulkan_model.rs:877-907):
-// consume a prompt, return the greedy token after its last position. This
-// form walks the prompt one position at a time through the decode graph, which
-// is what the reference's CPU and ROCm paths do (crates/llamd-runtime/src/layer.rs:83-84).
+// ---- prefill ------------------------------------------------------------------
+// VulkanModel::prefill / run (crates/llamd-runtime/src/vulkan_model.rs:378-907):
+// the prompt is cut into tiles of at most `prefill_tile` tokens; a tile runs the
+// layer graph once with a token dimension: weights are streamed once per 8
+// tokens, the routed experts go expert-major through the counting-sort plan
+// (moe_group), and attention needs no mask because every token of the tile has
+// stored its K and V before any query of the tile runs. Per token the
+// arithmetic is the decode pass's, so prefill == sequential decode exactly.
+static bool prefill_alloc(Model &m, int tile) {
+    Model::Prefill &p = m.pf;
+    if (p.tile >= tile) return true;
+    for (Buf *b : {&p.x, &p.xb, &p.xb2, &p.q, &p.k, &p.v, &p.attn, &p.aq, &p.ad, &p.aq2, &p.ad2, &p.ids, &p.w, &p.logits, &p.counter,
+                   &p.gate, &p.up, &p.down, &p.scores, &p.meta, &p.gstart, &p.gcount, &p.ptoken, &p.pslot, &p.work, &p.n_work})
+        b->release();
+    if (p.h_meta) cudaFreeHost(p.h_meta);
+    p.h_meta = nullptr;
+    const llamd_hparams &hp = m.hp;
+    const size_t T = tile, E = hp.n_embd, qd = (size_t)hp.n_head * hp.head_dim, kvd = (size_t)hp.n_head_kv * hp.head_dim;
+    const size_t nu = hp.n_expert_used, ffe = hp.n_ff_expert, ne = hp.n_expert, max_act = E > qd ? E : qd;
+    bool ok = p.x.alloc(T * E * 4) && p.xb.alloc(T * E * 4) && p.xb2.alloc(T * E * 4) && p.q.alloc(T * qd * 4) && p.k.alloc(T * kvd * 4) &&
+              p.v.alloc(T * kvd * 4) && p.attn.alloc(T * qd * 4) && p.aq.alloc(T * max_act) && p.ad.alloc(T * (max_act / 256) * 4) &&
+              p.aq2.alloc(T * nu * ffe) && p.ad2.alloc(T * nu * (ffe / 256) * 4) && p.ids.alloc(T * nu * 4) && p.w.alloc(T * nu * 4) &&
+              p.logits.alloc(T * ne * 4) && p.counter.alloc(T * 4) && p.gate.alloc(T * nu * ffe * 4) && p.up.alloc(T * nu * ffe * 4) &&
+              p.down.alloc(T * nu * E * 4) && p.scores.alloc(T * hp.n_head * (size_t)m.max_kv * 4) && p.meta.alloc(T * 8) &&
+              p.gstart.alloc(ne * 4) && p.gcount.alloc(ne * 4) && p.ptoken.alloc(T * nu * 4) && p.pslot.alloc(T * nu * 4) &&
+              p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && cudaMallocHost((void **)&p.h_meta, T * 8) == cudaSuccess;
+    if (!ok) {
+        m.err = std::string("prefill buffers: ") + llamd_cuda_last_error_string();
+        return false;
+    }
+    p.tile = tile;
+    return true;
+}
+
+static void queue_prefill_tile(Model &m, int T, bool last) {
+    const llamd_hparams &hp = m.hp;
+    Model::Prefill &p = m.pf;
+    const int E = hp.n_embd, H = hp.n_head, HKV = hp.n_head_kv, hd = hp.head_dim;
+    const int kvd = HKV * hd, qd = H * hd, nu = hp.n_expert_used, ffe = hp.n_ff_expert, ne = hp.n_expert, eb = E / 256;
+    const int32_t *meta = p.meta.as<int32_t>();
+    float *x = p.x.as<float>();
+    const int max_items = T * nu / 8 + ne;
+    llamd_fwd_embed_meta(m.tok_embd.p, meta, x, eb, T);
+    for (int il = 0; il < hp.n_layer; il++) {
+        Layer &l = m.layers[il];
+        if (il == 0)
+            llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, p.aq.as<int8_t>(), p.ad.as<float>(), E, hp.rms_eps, T);
+        else
+            llamd_fwd_combine_rms_norm_quant(x, p.down.as<float>(), p.w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
+                                             p.aq.as<int8_t>(), p.ad.as<float>(), E, hp.rms_eps, T);
+        llamd_fwd_matvec_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq.as<int8_t>(), p.ad.as<float>(), p.q.as<float>(), p.k.as<float>(),
+                                p.v.as<float>(), eb, qd, kvd, kvd, T);
+        llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
+                                          l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
+                                          l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
+        llamd_fwd_attention_tile(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd,
+                                 meta, m.max_kv, T);
+        llamd_fwd_quantize(p.attn.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(), T * (qd / 256));
+        llamd_fwd_matvec_tokens(l.attn_out.p, nullptr, nullptr, p.aq.as<int8_t>(), p.ad.as<float>(), p.xb2.as<float>(), nullptr, nullptr,
+                                qd / 256, E, 0, 0, T);
+        llamd_fwd_add_rms_norm_quant(x, p.xb2.as<float>(), x, l.ffn_norm.as<float>(), p.xb.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(),
+                                     E, hp.rms_eps, T);
+        llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), p.xb.as<float>(), E, ne, nu, p.logits.as<float>(), p.ids.as<int32_t>(),
+                                p.w.as<float>(), nullptr, p.counter.as<unsigned int>(), T);
+        // the expert scatter plan: (token, slot) pairs sorted by expert
+        llamd_fwd_moe_group_work(p.ids.as<int32_t>(), ne, nu, T, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
+                                 p.pslot.as<int32_t>(), p.work.as<int32_t>(), p.n_work.as<int32_t>());
+        llamd_fwd_expert_major(l.gate_exps.p, l.up_exps.p, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items, p.ptoken.as<int32_t>(),
+                               p.pslot.as<int32_t>(), p.aq.as<int8_t>(), p.ad.as<float>(), p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne);
+        llamd_fwd_silu_mul_quant(p.gate.as<float>(), p.up.as<float>(), nullptr, p.aq2.as<int8_t>(), p.ad2.as<float>(), T * nu * ffe);
+        llamd_fwd_expert_major(l.down_exps.p, nullptr, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items, p.pslot.as<int32_t>(),
+                               p.pslot.as<int32_t>(), p.aq2.as<int8_t>(), p.ad2.as<float>(), p.down.as<float>(), nullptr, ffe / 256, E, ne);
+    }
+    if (!last) return;
+    // logits for the tile's last token only (vulkan_model.rs:793-818)
+    const size_t r = (size_t)(T - 1);
+    llamd_fwd_combine_rms_norm_quant(x + r * E, p.down.as<float>() + r * nu * E, p.w.as<float>() + r * nu, nu, m.x.as<float>(),
+                                     m.output_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, 1);
+    llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb, hp.n_vocab,
+                           1);
+    llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(), kArgmaxBlocks,
+                     1);
+}
+
 int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_token) {
     Model *m = (Model *)h;
     if (!m || !tokens || n_tokens <= 0 || !out_token) return -1;
     m->err.clear();
-    int32_t out = -1;
-    for (int i = 0; i < n_tokens; i++) {
-        const int32_t pos = base_pos + i;
-        if (run(*m, &tokens[i], &pos, 1, &out) != 0) return -1;
+    if (base_pos < 0 || base_pos + n_tokens > m->max_kv) {
+        m->err = "prefill: positions beyond the " + std::to_string(m->max_kv) + " allocated";
+        return -1;
     }
-    *out_token = out;
+    for (int i = 0; i < n_tokens; i++)
+        if (tokens[i] < 0 || tokens[i] >= m->hp.n_vocab) {
+            m->err = "prefill: token id outside the vocabulary";
+            return -1;
+        }
+    if (!check_ready(*m)) return -1;
+    int tile = m->prefill_tile < 1 ? 1 : m->prefill_tile;
+    if (tile > n_tokens) tile = n_tokens;
+    if (!prefill_alloc(*m, tile)) return -1;
+    for (int t0 = 0; t0 < n_tokens; t0 += tile) {
+        const int T = n_tokens - t0 < tile ? n_tokens - t0 : tile;
+        if (llamd_fwd_sync() != 0) return -1;  // the pinned meta staging is reused per tile
+        for (int i = 0; i < T; i++) {
+            m->pf.h_meta[2 * i] = tokens[t0 + i];
+            m->pf.h_meta[2 * i + 1] = base_pos + t0 + i;
+        }
+        if (cudaMemcpyAsync(m->pf.meta.p, m->pf.h_meta, (size_t)T * 8, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
+            set_error(cudaGetLastError(), "prefill meta H2D");
+            return -1;
+        }
+        queue_prefill_tile(*m, T, t0 + T >= n_tokens);
+    }
+    if (cudaMemcpyAsync(m->h_out, m->out_token.p, 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
+    if (llamd_fwd_sync() != 0) return -1;
+    if (m->h_out[0] < 0 || m->h_out[0] >= m->hp.n_vocab) {
+        m->err = "argmax returned " + std::to_string(m->h_out[0]);
+        return -1;
+    }
+    *out_token = m->h_out[0];
     return 0;
 }
 

@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(128) matvec_q8_0_kernel(const uint8_t *__restr
 __global__ void norm_rope_kernel(float *__restrict__ xq, const float *__restrict__ wq, float *__restrict__ xk, const float *__restrict__ wk,
                                  const float *__restrict__ v_src, float *__restrict__ kc, float *__restrict__ vc, int n_head_q,
                                  int n_head_k, int hd, const int32_t *__restrict__ meta, int pos_imm, const float *__restrict__ rope_tab,
-                                 float eps, int max_kv) {
+                                 float eps, int kv_stride) {
     extern __shared__ float sx[];
     __shared__ float s_scale;
     pdl_trigger();
@@ -277,8 +277,10 @@ __global__ void norm_rope_kernel(float *__restrict__ xq, const float *__restrict
     xh[i + half] = o1;
     if (is_k && kc) {
         const int kv_dim = n_head * hd;
-        float *kdst = kc + ((size_t)seq * max_kv + pos) * kv_dim + (size_t)head * hd;
-        float *vdst = vc + ((size_t)seq * max_kv + pos) * kv_dim + (size_t)head * hd;
+        // kv_stride: positions between two sequences' caches; 0 when every row of
+        // the launch is a position of ONE sequence (a prefill tile)
+        float *kdst = kc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)head * hd;
+        float *vdst = vc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)head * hd;
         const float *vs = v_src + ((size_t)seq * n_head + head) * hd;
         kdst[i] = o0;
         kdst[i + half] = o1;
@@ -312,7 +314,7 @@ constexpr int kAttTile = 64;
 
 __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict__ q, const float *__restrict__ kc,
                                                         const float *__restrict__ vc, float *__restrict__ out, int n_head, int n_head_kv,
-                                                        int hd, const int32_t *__restrict__ meta, int n_kv_imm, int max_kv) {
+                                                        int hd, const int32_t *__restrict__ meta, int n_kv_imm, int max_kv, int kv_stride) {
     extern __shared__ __align__(16) float sm[];
     const int stride = hd + 1;
     float *sq = sm;                       // [hd]
@@ -325,8 +327,8 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
     const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
     const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
-    const float *kb = kc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
-    const float *vb = vc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
+    const float *kb = kc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
+    const float *vb = vc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
     const float *qh = q + ((size_t)seq * n_head + h) * hd;
     for (int i = tid; i < hd; i += blockDim.x) sq[i] = qh[i];
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
@@ -455,7 +457,7 @@ constexpr int kSplit = 4;
 
 __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restrict__ q, const float *__restrict__ kc, float *__restrict__ scores,
                                                           int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta,
-                                                          int n_kv_imm, int max_kv) {
+                                                          int n_kv_imm, int max_kv, int kv_stride) {
     extern __shared__ __align__(16) float sm[];
     const int stride = hd + 1;
     float *sq = sm;          // [hd]
@@ -465,7 +467,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
     const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
     const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
-    const float *kb = kc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd;
+    const float *kb = kc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
     const float *qh = q + ((size_t)seq * n_head + h) * hd;
     float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
     for (int i = tid; i < hd; i += blockDim.x) sq[i] = qh[i];
@@ -531,7 +533,7 @@ constexpr int kPvTile = 128;  // positions per V tile
 
 __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const float *__restrict__ vc, float *__restrict__ out,
                                                        int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int n_kv_imm,
-                                                       int max_kv) {
+                                                       int max_kv, int kv_stride) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float s_red[16];
     pdl_trigger();
@@ -543,7 +545,7 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     float *sl = sm;                                  // [n_kv]
     float *tile = sm + ((n_kv_cap + 3) & ~3);        // [2][kPvTile][cols]
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
-    const float *vb = vc + (size_t)seq * max_kv * kv_dim + (size_t)kvh * hd + (size_t)c * cols;
+    const float *vb = vc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd + (size_t)c * cols;
     const float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
     const int per_tile4 = kPvTile * cols4;
     const int n_tiles = (n_kv + kPvTile - 1) / kPvTile;
@@ -836,12 +838,18 @@ void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const flo
     launch_k("qk_norm_rope_store", norm_rope_kernel, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc, vc,
              n_head, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
 }
+// The same for the ntok tokens of a prefill tile: all rows go into ONE cache.
+void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc,
+                                       int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok) {
+    launch_k("qk_norm_rope_store_tile", norm_rope_kernel, dim3(n_head + n_head_kv, ntok), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc,
+             vc, n_head, n_head_kv, hd, meta, 0, rope_tab, eps, 0);
+}
 void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, int pos, int kv_dim) {
     launch_k("kv_store", kv_store_kernel, dim3((kv_dim + 255) / 256), dim3(256), 0, kc, vc, k, v, pos, kv_dim);
 }
 
 static void attention_split_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
-                                   int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq) {
+                                   int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride) {
     const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1)) * sizeof(float);
     const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
     static size_t conf_a = 0, conf_b = 0;
@@ -854,13 +862,13 @@ static void attention_split_launch(const float *q, const float *kc, const float 
         conf_b = smem_b;
     }
     launch_k("attn_scores", attn_scores_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
-             max_kv);
+             max_kv, kv_stride);
     launch_k("attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
-             meta, n_kv, max_kv);
+             meta, n_kv, max_kv, kv_stride);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
-                             const int32_t *meta, int n_kv, int max_kv, int nseq) {
+                             const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride) {
     const size_t smem = (size_t)(hd + ((max_kv + 3) & ~3) + 2 * kAttTile * (hd + 1)) * sizeof(float);
     if (hd % 4 || hd > 256 || kAttTile * (hd / 4) > 8 * 256 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
         set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
@@ -869,7 +877,7 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     // With a scores buffer ([nseq][n_head][max_kv] floats) and a head_dim the
     // column split divides, the work is cut over 4x more CTAs.
     if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 4 * 256) {
-        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq);
+        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride);
         return;
     }
     static size_t configured = 0;
@@ -881,18 +889,27 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
         }
         configured = smem;
     }
-    launch_k("attention", attention_kernel, dim3(n_head, nseq), dim3(256), smem, q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv);
+    launch_k("attention", attention_kernel, dim3(n_head, nseq), dim3(256), smem, q, kc, vc, out, n_head, n_head_kv, hd, meta, n_kv, max_kv,
+             kv_stride);
 }
 // `scores` (as in the reference's signature) is scratch for the scaled logits,
 // [n_head][n_kv] floats; when it is NULL a single-CTA-per-head kernel keeps
 // them in shared memory instead.
 void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
                          int n_kv) {
-    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1);
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1, n_kv);
+}
+// One query per token of a prefill tile: token i (meta[2i+1] = its position)
+// attends positions 0..pos_i of the ONE cache at kc/vc. No mask is needed:
+// every token of the tile has stored its K and V before this launch.
+// scores: [ntok][n_head][max_kv] floats.
+void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
+                              int hd, const int32_t *meta, int max_kv, int ntok) {
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, ntok, 0);
 }
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int nseq) {
-    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq);
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv);
 }
 
 // ---- attention for callers that must not allocate ---------------------------
@@ -941,7 +958,7 @@ int llamd_fwd_attention_noalloc(const float *q, const float *kc, const float *vc
     // Nothing in the scratch has to start at zero: each launch writes the
     // n_head * n_kv scores it later reads, so the previous call's contents are
     // simply overwritten.
-    attention_launch(q, kc, vc, out, g_static_scores_dev[dev], n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1);
+    attention_launch(q, kc, vc, out, g_static_scores_dev[dev], n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1, n_kv);
     return (before == 0 && error_code() != 0) ? -1 : 0;
 }
 

@@ -162,6 +162,16 @@ class CudaModel:
         self._use_graph = bool(v)
         self._L.llamd_model_set_option(self._h, b"use_graph", int(bool(v)))
 
+    @property
+    def prefill_tile(self) -> int:
+        return getattr(self, "_prefill_tile", 512)
+
+    @prefill_tile.setter
+    def prefill_tile(self, v: int) -> None:
+        if self._L.llamd_model_set_option(self._h, b"prefill_tile", int(v)) != 0:
+            raise backend.Malformed(f"prefill_tile {v} outside 1..4096")
+        self._prefill_tile = int(v)
+
     def set_trace(self, on: bool) -> None:
         if self._L.llamd_model_set_option(self._h, b"trace", int(on)) != 0:
             raise backend.Other("trace buffers: " + self._err())

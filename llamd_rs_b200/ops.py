@@ -232,3 +232,59 @@ def embed(table: "backend.DeviceWeights", token: int) -> np.ndarray:
     lib().llamd_fwd_embed(table.ptr, token, do.ptr, table.blocks())
     backend.sync()
     return do.download_f32(table.blocks() * QK_K)
+
+
+def matvec_tokens(weights, x):
+    """`weights`: 1-3 DeviceWeights sharing the column count; x f32 [ntok][k].
+    Quantizes on the device, then every token against every matrix.
+    -> list of [ntok][rows_i] (llamd_fwd_matvec_tokens)."""
+    x = _f32(x)
+    ntok, k = x.shape
+    ws = list(weights)
+    if not 1 <= len(ws) <= 3 or any(w.blocks() * QK_K != k for w in ws):
+        raise ShapeError("matvec_tokens: 1..3 matrices with k columns")
+    nb = k // QK_K
+    dx, dq, dd = DevBuf.from_array(x), DevBuf(ntok * k), DevBuf(ntok * nb * 4)
+    lib().llamd_fwd_quantize(dx.ptr, dq.ptr, dd.ptr, ntok * nb)
+    outs = [DevBuf(ntok * w.rows() * 4) for w in ws]
+    wp = [w.ptr for w in ws] + [None] * (3 - len(ws))
+    op = [o.ptr for o in outs] + [None] * (3 - len(ws))
+    rows = [w.rows() for w in ws] + [0] * (3 - len(ws))
+    lib().llamd_fwd_matvec_tokens(wp[0], wp[1], wp[2], dq.ptr, dd.ptr, op[0], op[1], op[2], nb, rows[0], rows[1], rows[2], ntok)
+    backend.sync()
+    return [o.download_f32(ntok * w.rows()).reshape(ntok, w.rows()) for o, w in zip(outs, ws)]
+
+
+def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False):
+    """Routed matvec for many tokens through the scatter plan.
+
+    `weights`: 1-2 DeviceWeights holding n_expert matrices of rows_per_expert
+    rows; ids int32 [ntok][n_used]. by_slot=False: x is [ntok][k] and pair
+    (t, s) reads x[t] (gate/up); by_slot=True: x is [ntok*n_used][k] and pair p
+    reads x[p] (down). -> list of [ntok*n_used][rows_per_expert], row block p =
+    expert ids[p] applied to its activation."""
+    x = _f32(x)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    ntok, n_used = ids.shape
+    ws = list(weights)
+    k = x.shape[1]
+    if not 1 <= len(ws) <= 2 or any(w.blocks() * QK_K != k or w.rows() % rows_per_expert for w in ws):
+        raise ShapeError("expert_major: 1..2 expert tensors with k columns")
+    n_expert = ws[0].rows() // rows_per_expert
+    if ids.size and (ids.min() < 0 or ids.max() >= n_expert):
+        raise Malformed(f"expert id outside 0..{n_expert}")
+    if x.shape[0] != (ntok * n_used if by_slot else ntok):
+        raise ShapeError("expert_major: activation rows")
+    nb, npair, nact = k // QK_K, ntok * n_used, x.shape[0]
+    dx, dq, dd = DevBuf.from_array(x), DevBuf(nact * k), DevBuf(nact * nb * 4)
+    lib().llamd_fwd_quantize(dx.ptr, dq.ptr, dd.ptr, nact * nb)
+    di = DevBuf.from_array(ids)
+    gs, gc, pt, ps = DevBuf(n_expert * 4), DevBuf(n_expert * 4), DevBuf(npair * 4), DevBuf(npair * 4)
+    max_items = npair // 8 + n_expert
+    wk, nw = DevBuf((max_items + 1) * 12), DevBuf.zeroed(4)
+    lib().llamd_fwd_moe_group_work(di.ptr, n_expert, n_used, ntok, gs.ptr, gc.ptr, pt.ptr, ps.ptr, wk.ptr, nw.ptr)
+    outs = [DevBuf.zeroed(npair * rows_per_expert * 4) for _ in ws]
+    lib().llamd_fwd_expert_major(ws[0].ptr, ws[1].ptr if len(ws) > 1 else None, wk.ptr, nw.ptr, max_items, ps.ptr if by_slot else pt.ptr,
+                                 ps.ptr, dq.ptr, dd.ptr, outs[0].ptr, outs[1].ptr if len(ws) > 1 else None, nb, rows_per_expert, n_expert)
+    backend.sync()
+    return [o.download_f32(npair * rows_per_expert).reshape(npair, rows_per_expert) for o in outs]

@@ -90,3 +90,19 @@ def test_full_model_graph_and_resident_loop_agree_with_forward(full):
     assert looped.tolist() == plain[1:], "resident loop == forward() fed back == un-graphed queueing"
     assert np.array_equal(gm.logits()[0].view(np.uint32), logits_plain.view(np.uint32))
     assert ms > 0
+
+
+def test_full_model_prefill_equals_sequential_decode(full):
+    """The tiled prefill (expert-major experts, 8 tokens per weight pass) against token-by-token decode."""
+    from llamd_rs_b200 import synth
+
+    hp, gm = full
+    prompt = synth.token_ids(40, hp["n_vocab"], 2, "prefill").tolist()
+    for pos, t in enumerate(prompt):
+        tok = gm.forward(t, pos)
+    logits = gm.logits()[0].copy()
+    for tile in (16, 512):
+        gm.prefill_tile = tile
+        assert gm.prefill(prompt, 0) == tok
+        assert np.array_equal(gm.logits()[0].view(np.uint32), logits.view(np.uint32)), f"tile {tile}"
+    gm.prefill_tile = 512

@@ -209,3 +209,51 @@ def test_q8_0_matvec_is_bit_exact(be, orc, synth, nseq):
     for s in range(nseq):
         want = orc.matvec_dequant(orc.Q8_0, w, x[s * k:(s + 1) * k], k, rows)
         assert_bit_equal(got[s], want, f"q8_0 sequence {s}")
+
+
+# ---- many tokens at once: the prefill kernels --------------------------------
+@pytest.mark.parametrize("ntok", [1, 7, 8, 9, 37])
+def test_matvec_tokens_equals_per_token_matvec(be, orc, synth, ntok):
+    from llamd_rs_b200 import ops
+
+    k, rows = 512, (70, 24, 24)
+    ws = [synth.q6k_blocks(r * k // 256, 61, "mt", i) for i, r in enumerate(rows)]
+    dws = [be.DeviceWeights.upload(w, r, k // 256) for w, r in zip(ws, rows)]
+    x = synth.normal_f32(ntok * k, 61, "mt.x", ntok).reshape(ntok, k)
+    got = ops.matvec_tokens(dws, x)
+    for w, r, g in zip(ws, rows, got):
+        for t in range(ntok):
+            assert_bit_equal(g[t], orc.matvec_q6k(w, x[t], k, r), f"token {t}")
+    assert_bit_equal(ops.matvec_tokens(dws[:1], x)[0], got[0], "one matrix alone")
+
+
+@pytest.mark.parametrize("ntok,n_used", [(1, 2), (5, 2), (40, 3), (64, 8)])
+def test_expert_major_equals_token_major(be, orc, synth, ntok, n_used):
+    """crates/llamd-testing/tests/vulkan_prefill.rs:268-330: the expert-major path gives exactly what the
+    per-token grouped matvec gives."""
+    from llamd_rs_b200 import ops
+
+    n_expert, rows, k = 16, 48, 512
+    per = rows * k // 256 * 210
+    wa = synth.q6k_blocks(n_expert * rows * k // 256, 62, "em.a")
+    wb = synth.q6k_blocks(n_expert * rows * k // 256, 62, "em.b")
+    da, db = be.DeviceWeights.upload(wa, n_expert * rows, k // 256), be.DeviceWeights.upload(wb, n_expert * rows, k // 256)
+    rng = np.random.default_rng(ntok)
+    ids = np.stack([rng.permutation(n_expert)[:n_used] for _ in range(ntok)]).astype(np.int32)
+    if ntok >= 40:
+        ids[:, 0] = 3  # one hot expert: more than 8 pairs, so its work is cut into several items
+    x = synth.normal_f32(ntok * k, 62, "em.x", ntok).reshape(ntok, k)
+    ga, gb = ops.expert_major([da, db], x, ids, rows)
+    for t in range(ntok):
+        for s_ in range(n_used):
+            e = int(ids[t, s_])
+            assert_bit_equal(ga[t * n_used + s_], orc.matvec_q6k(wa[e * per:(e + 1) * per], x[t], k, rows), f"gate pair ({t},{s_})")
+            assert_bit_equal(gb[t * n_used + s_], orc.matvec_q6k(wb[e * per:(e + 1) * per], x[t], k, rows), f"up pair ({t},{s_})")
+    # down: every pair has its own activation
+    xs = synth.normal_f32(ntok * n_used * k, 62, "em.xs", ntok).reshape(ntok * n_used, k)
+    (gd,) = ops.expert_major([da], xs, ids, rows, by_slot=True)
+    for p_ in range(ntok * n_used):
+        e = int(ids.ravel()[p_])
+        assert_bit_equal(gd[p_], orc.matvec_q6k(wa[e * per:(e + 1) * per], xs[p_], k, rows), f"down pair {p_}")
+    with pytest.raises(be.Malformed):
+        ops.expert_major([da], x, np.full((ntok, n_used), n_expert, np.int32), rows)

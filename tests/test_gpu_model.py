@@ -138,15 +138,33 @@ def test_batch_equals_single(tiny):
 
 
 def test_prefill_equals_sequential_decode(tiny):
-    """crates/llamd-testing/tests/vulkan_prefill.rs:48-136."""
-    from llamd_rs_b200 import synth
+    """crates/llamd-testing/tests/vulkan_prefill.rs:48-136: prefill gives the token (and here the logits and the
+    K/V cache, bit for bit) of sequential decode, for (tile, length) pairs that straddle tile and chunk boundaries."""
+    from llamd_rs_b200 import backend, synth
 
     hp, w, gm, om = tiny
-    prompt = synth.token_ids(9, hp["n_vocab"], 5, "prefill").tolist()
-    seq = None
+    prompt = synth.token_ids(37, hp["n_vocab"], 5, "prefill").tolist()
+    seq_tok, seq_logits = {}, {}
     for pos, t in enumerate(prompt):
-        seq = gm.forward(t, pos)
-    ls = gm.logits()[0].copy()
-    pre = gm.prefill(prompt, 0)
-    assert pre == seq
-    assert np.array_equal(gm.logits()[0].view(np.uint32), ls.view(np.uint32))
+        seq_tok[pos + 1] = gm.forward(t, pos)
+        seq_logits[pos + 1] = gm.logits()[0].copy()
+    kv_ref = [gm.read_kv(il, len(prompt)) for il in range(hp["n_layer"])]
+    for tile, length in [(1, 1), (1, 5), (2, 5), (4, 4), (4, 5), (8, 7), (8, 8), (8, 9), (8, 17), (16, 33), (16, 37), (64, 37), (512, 37)]:
+        gm.prefill_tile = tile
+        got = gm.prefill(prompt[:length], 0)
+        assert got == seq_tok[length], f"tile {tile} length {length}"
+        assert np.array_equal(gm.logits()[0].view(np.uint32), seq_logits[length].view(np.uint32)), f"tile {tile} length {length}: logits"
+    for il in range(hp["n_layer"]):
+        k, v = gm.read_kv(il, len(prompt))
+        assert np.array_equal(k.view(np.uint32), kv_ref[il][0].view(np.uint32)) and np.array_equal(v.view(np.uint32), kv_ref[il][1].view(np.uint32))
+    # chunked: a later call continues at base_pos, and decode continues after a prefill
+    gm.prefill_tile = 8
+    gm.prefill(prompt[:20], 0)
+    assert gm.prefill(prompt[20:], 20) == seq_tok[37]
+    gm.prefill(prompt[:12], 0)
+    assert gm.forward(prompt[12], 12) == seq_tok[13]
+    with pytest.raises(backend.Other):
+        gm.prefill(prompt, 40)  # runs past the 64 allocated positions
+    with pytest.raises(backend.Malformed):
+        gm.prefill([], 0)
+    gm.prefill_tile = 512
