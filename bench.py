@@ -175,6 +175,51 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
+    """Prompt throughput: K passes of the tiled prefill over the same prompt from position 0 (pp<prompt>)."""
+    import ctypes as C
+
+    from llamd_rs_b200._lib import lib as _lib
+
+    L = _lib()
+    K, W = args.steps, args.warmup
+    for _ in range(W):
+        m.prefill(prompt, 0)
+    backend.sync()
+    if dist:
+        dist.barrier()
+    launches0 = L.llamd_fwd_launch_count()
+    ms = C.c_float(0)
+    t1 = time.perf_counter()
+    L.llamd_fwd_timer_start()
+    for _ in range(K):
+        tok = m.prefill(prompt, 0)
+    L.llamd_fwd_timer_stop(C.byref(ms))
+    backend.sync()
+    wall = time.perf_counter() - t1
+    if dist:
+        import torch
+
+        t = torch.tensor([ms.value, wall], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms.value, wall = float(t[0]), float(t[1])
+    n = len(prompt)
+    wbytes = 48 * (15482880 + 128 * 3 * 1290240)  # a 512-token tile touches every expert of every layer
+    line = {"metric": "q6k_moe_prefill_tok_s", "value": world * n * K / (ms.value * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms.value / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
+            "config": {"workload": f"prefill_qwen3moe_q6k_pp{n}", "layers": hp["n_layer"], "tile": m.prefill_tile,
+                       "l2": "a tile streams every expert of every layer (23.8 GB): inputs larger than L2"},
+            "e2e": {"value": world * n * K / wall, "unit": "tok/s", "h2d_bytes_per_step": 8 * n, "d2h_bytes_per_step": 4},
+            "gpu_launches": int(L.llamd_fwd_launch_count() - launches0), "last_token": int(tok),
+            "roofline": {"bound": "hbm", "achieved": wbytes / (ms.value / K * 1e-3) / 1e9, "peak": 6541.5, "unit": "GB/s",
+                         "frac": wbytes / (ms.value / K * 1e-3) / 1e9 / 6541.5, "traffic": None,
+                         "note": "weight bytes of one pass / pass time; the pass is bound by the integer pipe, not HBM"}}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    m.free()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -183,6 +228,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt", type=int, default=512, help="prompt length consumed before the timed decode")
     ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; the JSON line says so")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline (one token per step). prefill: one pass over a --prompt token prompt per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--pdl-sweep", default="", help="(experiment) comma list of PDL class masks to time, e.g. 0,1,5,15")
@@ -227,8 +274,11 @@ def main():
 
         _l().llamd_fwd_set_pdl(0)
 
-    # each rank decodes its own sequence
     prompt = synth.token_ids(args.prompt, hp["n_vocab"], 0, "prompt", rank)
+    if args.workload == "prefill":
+        run_prefill(args, m, hp, prompt, rank, world, backend, dist)
+        return
+    # each rank decodes its own sequence
     t0 = time.time()
     tok = m.prefill(prompt, 0)
     log(f"[rank {rank}] prompt of {args.prompt} consumed in {time.time() - t0:.2f}s")

@@ -156,6 +156,13 @@ void llamd_fwd_matvec_grouped_x2_batch(const void *wa, const void *wb, const int
 void llamd_fwd_matvec_grouped_pa_batch(const void *w, const int32_t *ids, const int8_t *aq,
                                        const float *ad, float *out, int blocks, int rows, int n_used,
                                        int nseq);
+/* Fused forms: the activation's Q8_K quantization (:375), and for the down
+ * projection also silu(gate)*up (:316), happen inside the matvec. x is f32
+ * [nseq][blocks*256]; gate/up are f32 [nseq*n_used][blocks*256]. Same results
+ * as the separate launches. */
+void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq);
+void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up,
+                                      float *out, int blocks, int rows, int n_used, int nseq);
 /* f32 weights [rows][k] (the router): sequential f32 dot per row (:340). */
 void llamd_fwd_matvec_f32(const float *w, const float *x, float *out, int k, int rows);
 void llamd_fwd_matvec_f32_batch(const float *w, const float *x, float *out, int k, int rows, int nseq);

@@ -71,6 +71,8 @@ SIGNATURES = {
     "llamd_fwd_matvec_grouped_pa": (None, [vp, vp, vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_matvec_grouped_x2_batch": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]),
     "llamd_fwd_matvec_grouped_pa_batch": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32]),
+    "llamd_fwd_matvec_f32act": (None, [vp, vp, vp, i32, i32, i32]),
+    "llamd_fwd_matvec_grouped_pa_silu": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32]),
     "llamd_fwd_transpose_f32": (None, [vp, vp, i32, i32]),
     "llamd_fwd_matvec_f32": (None, [vp, vp, vp, i32, i32]),
     "llamd_fwd_matvec_f32_batch": (None, [vp, vp, vp, i32, i32, i32]),

@@ -7,7 +7,8 @@
 
 namespace llamd {
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
-                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div);
+                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode = 0,
+                   const float *xf = nullptr, const float *xu = nullptr);
 void launch_matvec_multi(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                          const float *ad, int n_tokens, const int32_t *work, const int32_t *n_work, int max_items, const int32_t *act_map,
                          const int32_t *out_map, int n_expert);
@@ -67,6 +68,22 @@ void llamd_fwd_matvec_grouped_pa_batch(const void *w, const int32_t *ids, const 
 void llamd_fwd_matvec_grouped_pa(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks, int rows,
                                  int n_used) {
     llamd_fwd_matvec_grouped_pa_batch(w, ids, aq, ad, out, blocks, rows, n_used, 1);
+}
+
+// f32 activations quantized inside the matvec (fuses the separate `quantize`
+// launch of crates/llamd-runtime/src/device.rs:580 into the attn_out projection).
+void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, nullptr, nullptr, nseq, nullptr, 1, 0, 1, 1, x, nullptr);
+}
+// The down projection with silu(gate)*up and its quantization inside
+// (fuses device.rs:615-618 into :622): gate/up are [nseq*n_used][blocks*256].
+void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
+                                      int rows, int n_used, int nseq) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, nullptr, nullptr, 1, ids, n_used * nseq, kAnyExpert, 1, 2, gate, up);
 }
 
 // ---- many tokens at once (prefill) -------------------------------------------

@@ -20,6 +20,7 @@
 // keep bytes 0-1 / 2-3 only, so dp4a(W4_j, lo) and dp4a(W4_j, hi) are the two
 // per-group pair products (times 4, since W4 = 4*(q-32)).
 #include "q6k_layout.cuh"
+#include "quant.cuh"
 
 namespace llamd {
 
@@ -55,7 +56,23 @@ struct MatvecParams {
     //                 row block out_map[first+s]; items >= *n_work do nothing.
     const int32_t *work, *n_work, *act_map, *out_map;
     int n_tokens;
+    // Activation source (template parameter ACT):
+    //   ACT_Q8K  aq/ad hold Q8_K activations;
+    //   ACT_F32  xf holds f32 activations [index][k], quantized by every CTA in its prologue
+    //            (fuses crates/llamd-rocm/src/forward.rs:375 `quantize` into the matvec);
+    //   ACT_SILU xf = gate, xu = up, f32 [index][k]: silu(gate)*up, then quantized (fuses :316 too).
+    const float *xf, *xu;
 };
+
+enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2 };
+
+// shared memory: [act image][exchange floats, aliased with the natural-order staging][activation block scales]
+__host__ __device__ inline size_t matvec_ad_offset(int nseq, int nb) {
+    const size_t act = (size_t)nseq * nb * kActBlockWords * 4;
+    const size_t ex = (size_t)nseq * 8 * kExStride * 4;
+    const size_t nat = (size_t)nseq * nb * 256;
+    return act + (((ex > nat ? ex : nat) + 15) & ~(size_t)15);
+}
 
 // Unpack the four W4 words of quad m of residue r from the three stored words.
 __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t w[4]) {
@@ -66,7 +83,7 @@ __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s
     w[3] = u | ((s2 << 2) & 0x0C0C0C0Cu);
 }
 
-template <int NSEQ, bool MULTI>
+template <int NSEQ, bool MULTI, int ACT>
 __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
@@ -74,6 +91,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
     uint32_t *s_act = reinterpret_cast<uint32_t *>(smem);
     float *s_ex = reinterpret_cast<float *>(smem + (size_t)NSEQ * nb * kActBlockWords * 4);
     int8_t *s_nat = reinterpret_cast<int8_t *>(s_ex);
+    float *s_ad = reinterpret_cast<float *>(smem + matvec_ad_offset(NSEQ, nb));  // [NSEQ*nb] activation block scales
 
     pdl_trigger();
     // ---- which job / slot / rows -------------------------------------
@@ -147,13 +165,35 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
     // are in flight while it finishes; the activations below do.
     if (!MULTI && !p.ids) pdl_wait();
     // ---- stage the activations ----------------------------------------
-    // natural order bytes first (coalesced 16-byte copies) ...
-    {
+    // natural order bytes first ...
+    if (ACT == ACT_Q8K) {
         const int n16 = NSEQ * nb * 16;
         for (int i = tid; i < n16; i += kThreads) {
             const int s = i / (nb * 16), o = i - s * nb * 16;
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
             reinterpret_cast<uint4 *>(s_nat)[i] = __ldg(reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o);
+        }
+        for (int i = tid; i < NSEQ * nb; i += kThreads) {
+            const int s = i / nb, o = i - s * nb;
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
+            s_ad[i] = __ldg(p.ad + a_idx * nb + o);
+        }
+    } else {
+        // ... produced here: one warp per 256-element block quantizes the f32 activation
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int blk = warp; blk < NSEQ * nb; blk += kThreads / 32) {
+            const int s = blk / nb, o = blk - s * nb;
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
+            const size_t base = ((size_t)a_idx * nb + o) * 256 + lane * 8;
+            const float4 g0 = *reinterpret_cast<const float4 *>(p.xf + base), g1 = *reinterpret_cast<const float4 *>(p.xf + base + 4);
+            float v[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            if (ACT == ACT_SILU) {
+                const float4 u0 = *reinterpret_cast<const float4 *>(p.xu + base), u1 = *reinterpret_cast<const float4 *>(p.xu + base + 4);
+                const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = silu_mul(v[i], u[i]);
+            }
+            q8k_quantize_block(v, lane, s_nat + blk * 256, s_ad + blk, nullptr);
         }
     }
     __syncthreads();
@@ -211,8 +251,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         const float dw = f16_bits_to_f32(dbits);
 #pragma unroll
         for (int s = 0; s < NSEQ; s++) {
-            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
-            const float dsc = __fmul_rn(dw, __ldg(p.ad + a_idx * nb + b));
+            const float dsc = __fmul_rn(dw, s_ad[s * nb + b]);
 #pragma unroll
             for (int r = 0; r < 8; r++)
                 s_ex[(s * 8 + r) * kExStride + tid] = __fmul_rn(dsc, (float)(aux[s][r] >> 2));
@@ -249,26 +288,21 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
     }
 }
 
-static size_t matvec_smem_bytes(int nseq, int nb) {
-    const size_t act = (size_t)nseq * nb * kActBlockWords * 4;
-    const size_t ex = (size_t)nseq * 8 * kExStride * 4;
-    const size_t nat = (size_t)nseq * nb * 256;
-    return act + (ex > nat ? ex : nat);
-}
+static size_t matvec_smem_bytes(int nseq, int nb) { return matvec_ad_offset(nseq, nb) + (size_t)nseq * nb * 4; }
 
-template <int NSEQ, bool MULTI = false>
+template <int NSEQ, bool MULTI = false, int ACT = ACT_Q8K>
 static void launch_t(const MatvecParams &p, dim3 grid) {
     const size_t smem = matvec_smem_bytes(NSEQ, p.nb);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(matvec_q6k_kernel<NSEQ, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(matvec_q6k_kernel<NSEQ, MULTI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             set_error(e, "matvec smem attribute");
             return;
         }
         configured = smem;
     }
-    launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI>, grid, dim3(kThreads), smem, p);
+    launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI, ACT>, grid, dim3(kThreads), smem, p);
 }
 
 // Build the launch. `rows[i]`/`w[i]`/`out[i]` describe up to three matrices
@@ -276,7 +310,8 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
 // activations, outputs [nseq][rows]. Grouped: n_slots expert ids, activation of
 // slot s is index s / act_div, outputs [n_slots][rows]; nseq must be 1.
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
-                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div) {
+                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode, const float *xf,
+                   const float *xu) {
     if (blocks <= 0 || blocks > kThreads || nseq < 1 || nseq > LLAMD_MAX_SEQ || njobs < 1 || njobs > 3 || (ids && nseq != 1) ||
         (ids && (n_slots < 1 || act_div < 1))) {
         set_error_msg("matvec: blocks must be 1..256, nseq 1..8, 1..3 matrices");
@@ -310,7 +345,34 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
     p.aq = aq;
     p.ad = ad;
     p.act_div = act_div < 1 ? 1 : act_div;
+    p.xf = xf;
+    p.xu = xu;
     const dim3 grid(p.ctas_per_slot * p.n_slots);
+    if (act_mode == ACT_SILU) {
+        if (nseq != 1 || !xf || !xu) {
+            set_error_msg("matvec: the silu activation mode takes gate and up, one sequence per slot");
+            return;
+        }
+        launch_t<1, false, ACT_SILU>(p, grid);
+        return;
+    }
+    if (act_mode == ACT_F32) {
+        if (!xf) {
+            set_error_msg("matvec: f32 activation mode without activations");
+            return;
+        }
+        switch (nseq) {
+        case 1: launch_t<1, false, ACT_F32>(p, grid); break;
+        case 2: launch_t<2, false, ACT_F32>(p, grid); break;
+        case 3: launch_t<3, false, ACT_F32>(p, grid); break;
+        case 4: launch_t<4, false, ACT_F32>(p, grid); break;
+        case 5: launch_t<5, false, ACT_F32>(p, grid); break;
+        case 6: launch_t<6, false, ACT_F32>(p, grid); break;
+        case 7: launch_t<7, false, ACT_F32>(p, grid); break;
+        default: launch_t<8, false, ACT_F32>(p, grid); break;
+        }
+        return;
+    }
     switch (nseq) {
     case 1: launch_t<1>(p, grid); break;
     case 2: launch_t<2>(p, grid); break;

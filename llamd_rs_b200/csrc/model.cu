@@ -31,6 +31,9 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int ntok);
+void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq);
+void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
+                                      int rows, int n_used, int nseq);
 void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
                              float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
@@ -191,6 +194,7 @@ void queue_token(Model &m, int nseq) {
                                      l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
         llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
                                  m.max_kv, nseq);
+        // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
         llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
         llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
@@ -200,6 +204,7 @@ void queue_token(Model &m, int nseq) {
                                 m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
         llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                           m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+        // SiLU on the gate only, times up, quantized per expert; each expert's down projection reads its OWN activation
         llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                  nseq * nu * ffe);
         llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),

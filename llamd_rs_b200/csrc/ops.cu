@@ -9,10 +9,10 @@
 #include <vector>
 
 #include "q6k_layout.cuh"
+#include "quant.cuh"
 
 namespace llamd {
 
-__device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
 
 #define WEIGHT_SUM_FLOOR 6.103515625e-5f  // 2^-14, crates/llamd-models/src/moe.rs:50
 constexpr int kMaxUsed = 64;
@@ -26,11 +26,38 @@ __device__ __forceinline__ float row_dot_sequential(const float *__restrict__ wr
     const float4 *xr = reinterpret_cast<const float4 *>(x);
     // the weight row does not depend on the previous kernel: park it in shared
     // memory before waiting for the activation
-    for (int i = lane; i < k / 4; i += 32) reinterpret_cast<float4 *>(prod)[i] = __ldg(wr + i);
+    // (16 loads in flight per lane: the row comes from cold HBM)
+    const int k4 = k / 4;
+    for (int i0 = 0; i0 < k4; i0 += 512) {
+        float4 r[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int idx = i0 + j * 32 + lane;
+            r[j] = idx < k4 ? __ldg(wr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int idx = i0 + j * 32 + lane;
+            if (idx < k4) reinterpret_cast<float4 *>(prod)[idx] = r[j];
+        }
+    }
     pdl_wait();
-    for (int i = lane; i < k / 4; i += 32) {
-        const float4 a = reinterpret_cast<float4 *>(prod)[i], b = __ldg(xr + i);
-        reinterpret_cast<float4 *>(prod)[i] = make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
+    for (int i0 = 0; i0 < k4; i0 += 512) {
+        float4 r[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int idx = i0 + j * 32 + lane;
+            r[j] = idx < k4 ? __ldg(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int idx = i0 + j * 32 + lane;
+            if (idx < k4) {
+                const float4 a = reinterpret_cast<float4 *>(prod)[idx], b = r[j];
+                reinterpret_cast<float4 *>(prod)[idx] =
+                    make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
+            }
+        }
     }
     __syncwarp();
     float acc = -0.0f;  // Rust's f32 Sum folds from -0.0
@@ -445,15 +472,16 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
 
 // ---- attention, split over CTAs ---------------------------------------------
 // The same arithmetic as attention_kernel, cut so that more SMs pull K and V:
-//   attn_scores_kernel  grid (head, kSplit, seq): CTA c takes the 64-position
-//                       tiles ti with ti % kSplit == c and writes the scaled
+//   attn_scores_kernel  grid (head, kSplitT, seq): CTA c takes the 64-position
+//                       tiles ti with ti % kSplitT == c and writes the scaled
 //                       logits to the global `scores` buffer;
 //   attn_out_kernel     grid (head, kSplit, seq): every CTA redoes the (cheap)
 //                       softmax over all positions, then walks t for its own
 //                       hd/kSplit output columns.
 // Each position's dot and each output column's sum is still one left-to-right
 // chain, so the result is bit-identical to the single-CTA kernel.
-constexpr int kSplit = 4;
+constexpr int kSplit = 4;    // output-column split of attn_out_kernel
+constexpr int kSplitT = 8;   // position-tile split of attn_scores_kernel
 
 __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restrict__ q, const float *__restrict__ kc, float *__restrict__ scores,
                                                           int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta,
@@ -499,11 +527,11 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
     };
     if (c < n_tiles) fetch(c);
     int buf = 0;
-    for (int ti = c; ti < n_tiles; ti += kSplit, buf ^= 1) {
+    for (int ti = c; ti < n_tiles; ti += kSplitT, buf ^= 1) {
         float *cur = tile + buf * kAttTile * stride;
         stash(cur);
         __syncthreads();
-        if (ti + kSplit < n_tiles) fetch(ti + kSplit);
+        if (ti + kSplitT < n_tiles) fetch(ti + kSplitT);
         const int t = ti * kAttTile + tid;
         if (tid < kAttTile && t < n_kv) {
             const float *kr = cur + tid * stride;
@@ -529,7 +557,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
     }
 }
 
-constexpr int kPvTile = 128;  // positions per V tile
+constexpr int kPvTile = 256;  // positions per V tile
 
 __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const float *__restrict__ vc, float *__restrict__ out,
                                                        int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int n_kv_imm,
@@ -549,7 +577,7 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     const float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
     const int per_tile4 = kPvTile * cols4;
     const int n_tiles = (n_kv + kPvTile - 1) / kPvTile;
-    constexpr int kMaxLd = 4;  // 128 rows x 32 cols / 4 / 256
+    constexpr int kMaxLd = 8;  // 256 rows x 32 cols / 4 / 256
     float4 reg[kMaxLd];
     auto fetch = [&](int ti) {
 #pragma unroll
@@ -861,7 +889,7 @@ static void attention_split_launch(const float *q, const float *kc, const float 
         cudaFuncSetAttribute(attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
         conf_b = smem_b;
     }
-    launch_k("attn_scores", attn_scores_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
+    launch_k("attn_scores", attn_scores_kernel, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
              max_kv, kv_stride);
     launch_k("attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
              meta, n_kv, max_kv, kv_stride);
@@ -876,7 +904,7 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     }
     // With a scores buffer ([nseq][n_head][max_kv] floats) and a head_dim the
     // column split divides, the work is cut over 4x more CTAs.
-    if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 4 * 256) {
+    if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 8 * 256) {
         attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride);
         return;
     }

@@ -288,3 +288,31 @@ def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False):
                                  ps.ptr, dq.ptr, dd.ptr, outs[0].ptr, outs[1].ptr if len(ws) > 1 else None, nb, rows_per_expert, n_expert)
     backend.sync()
     return [o.download_f32(npair * rows_per_expert).reshape(npair, rows_per_expert) for o in outs]
+
+
+def matvec_f32act(w: "backend.DeviceWeights", x):
+    """f32 activations [nseq][k]; quantized inside the matvec (llamd_fwd_matvec_f32act)."""
+    x = _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.shape[1] != w.blocks() * QK_K or not 1 <= x2.shape[0] <= backend.MAX_SEQ:
+        raise ShapeError("matvec_f32act sizes")
+    dx, do = DevBuf.from_array(x2), DevBuf(x2.shape[0] * w.rows() * 4)
+    lib().llamd_fwd_matvec_f32act(w.ptr, dx.ptr, do.ptr, w.blocks(), w.rows(), x2.shape[0])
+    backend.sync()
+    return do.download_f32(x2.shape[0] * w.rows()).reshape(x2.shape[0], w.rows())
+
+
+def matvec_grouped_pa_silu(w: "backend.DeviceWeights", ids, gate, up, rows_per_expert: int):
+    """Down projection of routed experts with silu(gate)*up and its quantization fused in.
+    ids int32 [n_slots]; gate/up f32 [n_slots][k] -> [n_slots][rows_per_expert]."""
+    gate, up = _f32(gate), _f32(up)
+    ids = np.ascontiguousarray(ids, dtype=np.int32).ravel()
+    if gate.shape != up.shape or gate.shape[0] != ids.size or gate.shape[1] != w.blocks() * QK_K or w.rows() % rows_per_expert:
+        raise ShapeError("matvec_grouped_pa_silu sizes")
+    n_expert = w.rows() // rows_per_expert
+    if ids.size == 0 or ids.min() < 0 or ids.max() >= n_expert:
+        raise Malformed(f"expert id outside 0..{n_expert}")
+    dg, du, di, do = DevBuf.from_array(gate), DevBuf.from_array(up), DevBuf.from_array(ids), DevBuf(ids.size * rows_per_expert * 4)
+    lib().llamd_fwd_matvec_grouped_pa_silu(w.ptr, di.ptr, dg.ptr, du.ptr, do.ptr, w.blocks(), rows_per_expert, ids.size, 1)
+    backend.sync()
+    return do.download_f32(ids.size * rows_per_expert).reshape(ids.size, rows_per_expert)

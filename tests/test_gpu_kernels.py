@@ -257,3 +257,34 @@ def test_expert_major_equals_token_major(be, orc, synth, ntok, n_used):
         assert_bit_equal(gd[p_], orc.matvec_q6k(wa[e * per:(e + 1) * per], xs[p_], k, rows), f"down pair {p_}")
     with pytest.raises(be.Malformed):
         ops.expert_major([da], x, np.full((ntok, n_used), n_expert, np.int32), rows)
+
+
+# ---- matvecs with the activation's quantization (and SiLU) fused in -----------
+@pytest.mark.parametrize("nseq", [1, 3, 8])
+def test_matvec_f32act_equals_quantize_then_matvec(be, orc, synth, nseq):
+    from llamd_rs_b200 import ops
+
+    rows, k = 90, 1024
+    w = synth.q6k_blocks(rows * k // 256, 71, "f32act")
+    x = synth.normal_f32(nseq * k, 71, "f32act.x", nseq).reshape(nseq, k)
+    x[0, 256:512] = 0.0  # an all-zero block: d = 0
+    dw = be.DeviceWeights.upload(w, rows, k // 256)
+    got = ops.matvec_f32act(dw, x)
+    for s_ in range(nseq):
+        assert_bit_equal(got[s_], orc.matvec_q6k(w, x[s_], k, rows), f"sequence {s_}")
+
+
+def test_down_projection_with_fused_silu(be, orc, synth):
+    from llamd_rs_b200 import ops
+
+    n_expert, rows, k = 6, 64, 768
+    per = rows * k // 256 * 210
+    w = synth.q6k_blocks(n_expert * rows * k // 256, 72, "pasilu")
+    dw = be.DeviceWeights.upload(w, n_expert * rows, k // 256)
+    ids = [5, 0, 3, 3]
+    gate = synth.normal_f32(len(ids) * k, 72, "g").reshape(len(ids), k) * np.float32(2.0)
+    up = synth.normal_f32(len(ids) * k, 72, "u").reshape(len(ids), k)
+    got = ops.matvec_grouped_pa_silu(dw, ids, gate, up, rows)
+    act = ops.silu_mul(gate.ravel(), up.ravel()).reshape(len(ids), k)  # the device's own activation (exp differs from libm by <= 1 ulp)
+    for s_, e in enumerate(ids):
+        assert_bit_equal(got[s_], orc.matvec_q6k(w[e * per:(e + 1) * per], act[s_], k, rows), f"slot {s_}")
