@@ -230,6 +230,9 @@ def main():
     ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; the JSON line says so")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: the headline (one token per step). prefill: one pass over a --prompt token prompt per step")
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
+                    help="N > 1: replicas = one full model per GPU, no exchange; ep = experts sharded 128/N per GPU, "
+                         "NCCL dispatch/combine per MoE layer (each rank still decodes its own sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--pdl-sweep", default="", help="(experiment) comma list of PDL class masks to time, e.g. 0,1,5,15")
@@ -259,6 +262,16 @@ def main():
     backend.set_device(local)
     backend.stream_init()
     info = backend.device_info(local)
+    ep = world > 1 and args.parallelism == "ep"
+    if ep:
+        from llamd_rs_b200 import model as _M
+
+        def _share(b):
+            obj = [b]
+            dist.broadcast_object_list(obj, src=0)
+            return obj[0]
+
+        _M.ep_init(rank, world, _share)
 
     hp = dict(synth.QWEN3MOE_30B)
     hp["n_layer"] = args.layers
@@ -343,8 +356,13 @@ def main():
 
     # ---- roofline of the dominant kernel ----
     iters = max(4, min(K, 16))
-    mv_ms, mv_launches = m.bench_matvecs(iters)
     wbytes, iobytes = matvec_bytes_per_token(hp)
+    if ep:
+        # sharded experts: the matvec-only replay is not available; report this rank's share of a token's
+        # bytes over the whole pass time instead (a lower bound on the kernel's rate)
+        mv_ms, mv_launches = dev_ms / K * iters, 193
+    else:
+        mv_ms, mv_launches = m.bench_matvecs(iters)
     achieved = (wbytes + iobytes) / (mv_ms / iters * 1e-3) / 1e9
     peaks = {}
     try:
@@ -360,7 +378,8 @@ def main():
         "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
         "config": {"workload": "decode_qwen3moe_q6k_b1", "layers": hp["n_layer"], "experts": "128x8", "hidden": 2048, "vocab": 151936,
                    "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
-                   "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": f"replicas x{world}",
+                   "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU, NCCL all-gather dispatch + all-to-all combine per layer"
+                                   if ep else f"replicas x{world}"),
                    "token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "arith": "exact (reference order)",
                    "graph": not args.no_graph, "pdl": not args.no_pdl},
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},

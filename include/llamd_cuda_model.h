@@ -47,6 +47,21 @@ enum {
     LLAMD_T_FFN_DOWN_EXPS   /* Q6_K [n_expert][n_embd x n_ff_expert]        */
 };
 
+/* Expert parallelism (no counterpart in the reference, which is single-GPU):
+ * one process per GPU. Rank 0 makes 128 bytes with llamd_cuda_ep_unique_id and
+ * shares them with the other ranks by any host channel; every rank then calls
+ * llamd_cuda_ep_init(rank, world, id) after llamd_cuda_set_device and BEFORE
+ * llamd_model_create. A model created afterwards keeps only experts
+ * [rank*n_expert/world, (rank+1)*n_expert/world) of what set_tensor is given,
+ * decodes its own sequence (max_seq 1), and per MoE layer all-gathers the routed
+ * requests (ids + Q8_K activation) and returns expert outputs to their home rank
+ * over NCCL. Every rank must make the same sequence of forward calls. */
+int llamd_cuda_ep_unique_id(void *out128);
+int llamd_cuda_ep_init(int rank, int world, const void *id128);
+void llamd_cuda_ep_finalize(void);
+int llamd_cuda_ep_rank(void);
+int llamd_cuda_ep_world(void);
+
 /* DeviceModel::load_batched (device.rs:270): room for max_seq sequences of
  * max_kv positions. NULL on failure (llamd_cuda_last_error_string says why). */
 llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq);

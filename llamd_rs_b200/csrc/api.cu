@@ -8,7 +8,7 @@
 namespace llamd {
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode = 0,
-                   const float *xf = nullptr, const float *xu = nullptr);
+                   const float *xf = nullptr, const float *xu = nullptr, int own_lo = 0, int own_hi = 0x7fffffff);
 void launch_matvec_multi(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                          const float *ad, int n_tokens, const int32_t *work, const int32_t *n_work, int max_items, const int32_t *act_map,
                          const int32_t *out_map, int n_expert);
@@ -84,6 +84,23 @@ void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const f
     const void *ws[1] = {w};
     float *os[1] = {out};
     launch_matvec(1, ws, os, &rows, blocks, nullptr, nullptr, 1, ids, n_used * nseq, kAnyExpert, 1, 2, gate, up);
+}
+
+// Expert-parallel forms: `ids` are GLOBAL expert ids for n_slots slots; this GPU holds experts
+// [own_lo, own_hi) in `w*` from local index 0 and computes only the slots it owns.
+// x2: slot s reads activation aq[s / n_used]; pa: slot s reads aq[s].
+void llamd_fwd_matvec_grouped_x2_owned(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad, float *oa,
+                                       float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo, int own_hi) {
+    const void *ws[2] = {wa, wb};
+    float *os[2] = {oa, ob};
+    const int r2[2] = {rows, rows};
+    launch_matvec(2, ws, os, r2, blocks, aq, ad, 1, ids, n_slots, kAnyExpert, n_used, 0, nullptr, nullptr, own_lo, own_hi);
+}
+void llamd_fwd_matvec_grouped_pa_owned(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks,
+                                       int rows, int n_slots, int own_lo, int own_hi) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, aq, ad, 1, ids, n_slots, kAnyExpert, 1, 0, nullptr, nullptr, own_lo, own_hi);
 }
 
 // ---- many tokens at once (prefill) -------------------------------------------

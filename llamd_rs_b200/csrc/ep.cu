@@ -1,0 +1,170 @@
+// Expert parallelism: experts sharded over the GPUs of one node, one process
+// per GPU, NCCL over NVLink for the per-layer exchange. The reference has no
+// distributed code at all; this file is new design.
+//
+// Every rank decodes its own sequence and holds every non-expert weight, plus
+// experts [rank*E/N, (rank+1)*E/N). Per MoE layer:
+//   dispatch  all-gather of (expert ids, Q8_K activation) -- 2.1 KB per rank --
+//             so every rank sees the routed requests of all N tokens. The Q8_K
+//             form is what every expert consumes, so sending it is exact;
+//   compute   each rank runs the requested experts it owns;
+//   combine   all-to-all of fixed [n_used][n_embd] f32 blocks: rank r returns to
+//             rank t the rows it computed for t's token; the home rank then picks
+//             each slot's row from the expert's owner and adds them in routing
+//             order, as the single-GPU pass does.
+// NCCL is loaded with dlopen when expert parallelism is first initialised, so a
+// single-GPU process never needs the library.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace llamd {
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+static NcclApi g_nccl;
+static ncclComm_t g_comm = nullptr;
+static int g_ep_rank = 0, g_ep_world = 1;
+
+static bool nccl_load() {
+    if (g_nccl.handle) return true;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) {
+        set_error_msg("expert parallelism: libnccl.so.2 could not be loaded");
+        return false;
+    }
+#define LOAD(field, name)                                                      \
+    g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(h, name));   \
+    if (!g_nccl.field) {                                                       \
+        set_error_msg("expert parallelism: libnccl lacks " name);              \
+        return false;                                                          \
+    }
+    LOAD(GetUniqueId, "ncclGetUniqueId")
+    LOAD(CommInitRank, "ncclCommInitRank")
+    LOAD(CommDestroy, "ncclCommDestroy")
+    LOAD(AllGather, "ncclAllGather")
+    LOAD(Send, "ncclSend")
+    LOAD(Recv, "ncclRecv")
+    LOAD(GroupStart, "ncclGroupStart")
+    LOAD(GroupEnd, "ncclGroupEnd")
+    LOAD(GetErrorString, "ncclGetErrorString")
+#undef LOAD
+    g_nccl.handle = h;
+    return true;
+}
+
+static bool nccl_ok(ncclResult_t r, const char *what) {
+    if (r == ncclSuccess) return true;
+    char msg[256];
+    snprintf(msg, sizeof msg, "%s: %s", what, g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "nccl error");
+    set_error_msg(msg);
+    return false;
+}
+
+int ep_rank() { return g_ep_rank; }
+int ep_world() { return g_ep_world; }
+
+// Home rank: slot s of my token was computed by the rank that owns expert ids[s];
+// its row sits in that rank's block of the receive buffer.
+__global__ void ep_pick_kernel(const float *__restrict__ recv, const int32_t *__restrict__ ids, float *__restrict__ down, int n_used, int n_embd,
+                               int experts_per_rank) {
+    pdl_trigger();
+    pdl_wait();
+    const int s = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_embd) return;
+    const int owner = ids[s] / experts_per_rank;
+    down[(size_t)s * n_embd + i] = recv[((size_t)owner * n_used + s) * n_embd + i];
+}
+
+}  // namespace llamd
+
+using namespace llamd;
+
+extern "C" {
+
+// 128 bytes the ranks must share before llamd_cuda_ep_init (rank 0 makes them).
+int llamd_cuda_ep_unique_id(void *out128) {
+    if (!out128 || !nccl_load()) return -1;
+    ncclUniqueId id;
+    if (!nccl_ok(g_nccl.GetUniqueId(&id), "ncclGetUniqueId")) return -1;
+    memcpy(out128, &id, sizeof id);
+    return 0;
+}
+
+// Join the communicator: one process per GPU, the device already selected.
+int llamd_cuda_ep_init(int rank, int world, const void *id128) {
+    if (world < 1 || rank < 0 || rank >= world || !id128) return -1;
+    if (!nccl_load() || !stream()) return -1;
+    if (g_comm) {
+        g_nccl.CommDestroy(g_comm);
+        g_comm = nullptr;
+    }
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof id);
+    if (!nccl_ok(g_nccl.CommInitRank(&g_comm, world, id, rank), "ncclCommInitRank")) return -1;
+    g_ep_rank = rank;
+    g_ep_world = world;
+    return 0;
+}
+
+void llamd_cuda_ep_finalize(void) {
+    if (g_comm && g_nccl.CommDestroy) {
+        cudaStreamSynchronize(stream());
+        g_nccl.CommDestroy(g_comm);
+    }
+    g_comm = nullptr;
+    g_ep_rank = 0;
+    g_ep_world = 1;
+}
+
+// dispatch: three all-gathers in one NCCL group (ids, activation scales, activation quants)
+void llamd_fwd_ep_dispatch(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *ids_all, float *ad_all, int8_t *aq_all,
+                           int n_used, int blocks) {
+    if (!g_comm) {
+        set_error_msg("ep_dispatch before llamd_cuda_ep_init");
+        return;
+    }
+    bool ok = nccl_ok(g_nccl.GroupStart(), "ncclGroupStart");
+    ok = ok && nccl_ok(g_nccl.AllGather(ids, ids_all, (size_t)n_used, ncclInt32, g_comm, stream()), "ncclAllGather ids");
+    ok = ok && nccl_ok(g_nccl.AllGather(ad, ad_all, (size_t)blocks, ncclFloat, g_comm, stream()), "ncclAllGather ad");
+    ok = ok && nccl_ok(g_nccl.AllGather(aq, aq_all, (size_t)blocks * 256, ncclInt8, g_comm, stream()), "ncclAllGather aq");
+    nccl_ok(g_nccl.GroupEnd(), "ncclGroupEnd");
+    (void)ok;
+}
+
+// combine: block t of `send` ([world][n_used][n_embd]) goes to rank t; block r of `recv` comes from rank r;
+// then the home rank picks each slot's row from the owner of its expert into down [n_used][n_embd].
+void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, float *down, int n_used, int n_embd, int n_expert) {
+    if (!g_comm) {
+        set_error_msg("ep_combine before llamd_cuda_ep_init");
+        return;
+    }
+    const size_t blk = (size_t)n_used * n_embd;
+    bool ok = nccl_ok(g_nccl.GroupStart(), "ncclGroupStart");
+    for (int peer = 0; ok && peer < g_ep_world; peer++) {
+        ok = ok && nccl_ok(g_nccl.Send(send + peer * blk, blk, ncclFloat, peer, g_comm, stream()), "ncclSend");
+        ok = ok && nccl_ok(g_nccl.Recv(recv + peer * blk, blk, ncclFloat, peer, g_comm, stream()), "ncclRecv");
+    }
+    nccl_ok(g_nccl.GroupEnd(), "ncclGroupEnd");
+    launch_k("ep_pick", ep_pick_kernel, dim3((n_embd + 255) / 256, n_used), dim3(256), 0, (const float *)recv, ids, down, n_used, n_embd,
+             n_expert / g_ep_world);
+}
+
+int llamd_cuda_ep_rank(void) { return g_ep_rank; }
+int llamd_cuda_ep_world(void) { return g_ep_world; }
+
+}  // extern "C"

@@ -48,6 +48,9 @@ struct MatvecParams {
     const int8_t *aq;      // activations: [nseq][nb*256] ungrouped, else indexed by slot / act_div
     const float *ad;
     int act_div;           // grouped: activation index = slot / act_div
+    // Expert parallelism: this GPU holds experts [own_lo, own_hi) only, stored from local index 0.
+    // A slot whose expert lives elsewhere is skipped (its output rows are left untouched).
+    int own_lo, own_hi;
     // Many-token ("multi") launches, blockIdx.y = item, NSEQ sequences per item:
     //   work == null: item g covers tokens g*NSEQ .. (of n_tokens), activation
     //                 and output index = token;
@@ -137,7 +140,8 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         pdl_wait();  // the ids come from the router kernel
         int e = p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
-        expert_off = (long long)e * p.expert_units;
+        if (e < p.own_lo || e >= p.own_hi) return;  // another GPU's expert
+        expert_off = (long long)(e - p.own_lo) * p.expert_units;
     }
 
     // ---- issue the weight loads first: they stay in flight across the staging barrier
@@ -311,7 +315,7 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
 // slot s is index s / act_div, outputs [n_slots][rows]; nseq must be 1.
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode, const float *xf,
-                   const float *xu) {
+                   const float *xu, int own_lo, int own_hi) {
     if (blocks <= 0 || blocks > kThreads || nseq < 1 || nseq > LLAMD_MAX_SEQ || njobs < 1 || njobs > 3 || (ids && nseq != 1) ||
         (ids && (n_slots < 1 || act_div < 1))) {
         set_error_msg("matvec: blocks must be 1..256, nseq 1..8, 1..3 matrices");
@@ -347,6 +351,8 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
     p.act_div = act_div < 1 ? 1 : act_div;
     p.xf = xf;
     p.xu = xu;
+    p.own_lo = own_lo;
+    p.own_hi = own_hi;
     const dim3 grid(p.ctas_per_slot * p.n_slots);
     if (act_mode == ACT_SILU) {
         if (nseq != 1 || !xf || !xu) {

@@ -34,6 +34,15 @@ void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, 
 void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq);
 void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
                                       int rows, int n_used, int nseq);
+void llamd_fwd_matvec_grouped_x2_owned(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad, float *oa,
+                                       float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo, int own_hi);
+void llamd_fwd_matvec_grouped_pa_owned(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks,
+                                       int rows, int n_slots, int own_lo, int own_hi);
+void llamd_fwd_ep_dispatch(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *ids_all, float *ad_all, int8_t *aq_all,
+                           int n_used, int blocks);
+void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, float *down, int n_used, int n_embd, int n_expert);
+int llamd_cuda_ep_rank(void);
+int llamd_cuda_ep_world(void);
 void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
                              float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
@@ -96,6 +105,9 @@ struct Model {
         Buf gstart, gcount, ptoken, pslot, work, n_work;
         int32_t *h_meta = nullptr;
     } pf;
+    // expert parallelism (ep_world > 1): this rank holds experts [own_lo, own_hi)
+    int ep_rank = 0, ep_world = 1, own_lo = 0, own_hi = 0;
+    Buf ids_all, ad_all, aq_all, gate_all, up_all, aq2_all, ad2_all, down_all, recv_all;
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
     int32_t *h_meta = nullptr;  // pinned
     int32_t *h_out = nullptr;   // pinned
@@ -202,6 +214,25 @@ void queue_token(Model &m, int nseq) {
                                      m.ad.as<float>(), E, hp.rms_eps, nseq);
         llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
                                 m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
+        if (m.ep_world > 1) {
+            // Expert parallelism: gather every rank's routed request, run the experts this
+            // rank owns for all of them, return each token's rows to its home rank.
+            const int W = m.ep_world;
+            llamd_fwd_ep_dispatch(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ids_all.as<int32_t>(),
+                                  m.ad_all.as<float>(), m.aq_all.as<int8_t>(), nu, eb);
+            llamd_fwd_matvec_grouped_x2_owned(l.gate_exps.p, l.up_exps.p, m.ids_all.as<int32_t>(), m.aq_all.as<int8_t>(), m.ad_all.as<float>(),
+                                              m.gate_all.as<float>(), m.up_all.as<float>(), eb, ffe, nu, W * nu, m.own_lo, m.own_hi);
+            llamd_fwd_silu_mul_quant(m.gate_all.as<float>(), m.up_all.as<float>(), nullptr, m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
+                                     W * nu * ffe);
+            llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
+                                              m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
+            llamd_fwd_ep_combine(m.down_all.as<float>(), m.recv_all.as<float>(), m.expert_ids.as<int32_t>(), m.e_down.as<float>(), nu, E,
+                                 hp.n_expert);
+            if (m.trace)
+                cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
+                                cudaMemcpyDeviceToDevice, stream());
+            continue;
+        }
         llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                           m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
         // SiLU on the gate only, times up, quantized per expert; each expert's down projection reads its OWN activation
@@ -344,6 +375,15 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     m->max_seq = max_seq;
     m->id = g_next_id++;
     m->layers.resize(hp->n_layer);
+    m->ep_rank = llamd_cuda_ep_rank();
+    m->ep_world = llamd_cuda_ep_world();
+    if (m->ep_world > 1 && (hp->n_expert % m->ep_world != 0 || max_seq != 1)) {
+        set_error_msg("model: expert parallelism needs n_expert divisible by the world size and max_seq 1");
+        delete m;
+        return nullptr;
+    }
+    m->own_lo = m->ep_rank * (hp->n_expert / m->ep_world);
+    m->own_hi = m->own_lo + hp->n_expert / m->ep_world;
     const size_t E = hp->n_embd, qd = (size_t)hp->n_head * hp->head_dim, kvd = (size_t)hp->n_head_kv * hp->head_dim;
     const size_t nu = hp->n_expert_used, ffe = hp->n_ff_expert, S = max_seq;
     const size_t max_act = E > qd ? E : qd;
@@ -361,6 +401,12 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
     ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4) && m->router_counter.alloc(4 * S) &&
          m->scores.alloc((size_t)S * hp->n_head * max_kv * sizeof(float));
+    if (m->ep_world > 1) {
+        const size_t W = m->ep_world;
+        ok = ok && m->ids_all.alloc(W * nu * 4) && m->ad_all.alloc(W * (E / 256) * 4) && m->aq_all.alloc(W * E) &&
+             m->gate_all.alloc(W * nu * ffe * 4) && m->up_all.alloc(W * nu * ffe * 4) && m->aq2_all.alloc(W * nu * ffe) &&
+             m->ad2_all.alloc(W * nu * (ffe / 256) * 4) && m->down_all.alloc(W * nu * E * 4) && m->recv_all.alloc(W * nu * E * 4);
+    }
     for (auto &l : m->layers) {
         ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
     }
@@ -396,7 +442,8 @@ void llamd_model_free(llamd_model *h) {
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
-                   &m->tok_log, &m->tok_count, &m->router_counter, &m->scores})
+                   &m->tok_log, &m->tok_count, &m->router_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
+                   &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all})
         b->release();
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
                    &m->pf.ids, &m->pf.w, &m->pf.logits, &m->pf.counter, &m->pf.gate, &m->pf.up, &m->pf.down, &m->pf.scores, &m->pf.meta,
@@ -443,9 +490,31 @@ int llamd_model_set_tensor(llamd_model *h, int layer, int which, size_t first_bl
         case LLAMD_T_ATTN_K: total = q6k_blocks_for(kvd, E); ok = upload_q6k_slice(l.attn_k, total, first_block, host, count); break;
         case LLAMD_T_ATTN_V: total = q6k_blocks_for(kvd, E); ok = upload_q6k_slice(l.attn_v, total, first_block, host, count); break;
         case LLAMD_T_ATTN_OUT: total = q6k_blocks_for(E, qd); ok = upload_q6k_slice(l.attn_out, total, first_block, host, count); break;
-        case LLAMD_T_FFN_GATE_EXPS: total = ne * q6k_blocks_for(ffe, E); ok = upload_q6k_slice(l.gate_exps, total, first_block, host, count); break;
-        case LLAMD_T_FFN_UP_EXPS: total = ne * q6k_blocks_for(ffe, E); ok = upload_q6k_slice(l.up_exps, total, first_block, host, count); break;
-        case LLAMD_T_FFN_DOWN_EXPS: total = ne * q6k_blocks_for(E, ffe); ok = upload_q6k_slice(l.down_exps, total, first_block, host, count); break;
+        case LLAMD_T_FFN_GATE_EXPS:
+        case LLAMD_T_FFN_UP_EXPS:
+        case LLAMD_T_FFN_DOWN_EXPS: {
+            // Only the experts this rank owns are kept (all of them without expert
+            // parallelism): the caller's block range is cut to [own_lo, own_hi).
+            const size_t per = q6k_blocks_for(ffe, E);
+            total = (size_t)(m->own_hi - m->own_lo) * per;
+            Buf &dst = which == LLAMD_T_FFN_GATE_EXPS ? l.gate_exps : (which == LLAMD_T_FFN_UP_EXPS ? l.up_exps : l.down_exps);
+            if (first_block + count > ne * per) {
+                m->err = "set_tensor: slice outside the tensor";
+                return -1;
+            }
+            size_t lo = first_block, hi = first_block + count;
+            const size_t own0 = (size_t)m->own_lo * per, own1 = (size_t)m->own_hi * per;
+            if (lo < own0) lo = own0;
+            if (hi > own1) hi = own1;
+            if (!dst.p && !dst.alloc(llamd_cuda_q6k_tiled_bytes(total))) break;
+            if (lo >= hi) {
+                ok = true;  // nothing of this slice lives here
+                count = 0;
+            } else {
+                ok = upload_q6k_slice(dst, total, lo - own0, (const uint8_t *)host + (lo - first_block) * LLAMD_Q6K_BLOCK_BYTES, hi - lo);
+                count = hi - lo;
+            }
+        } break;
         case LLAMD_T_FFN_GATE_INP: ok = count == ne * E && upload_f32(l.ffn_gate_inp, host, ne * E); break;
         default: m->err = "set_tensor: unknown tensor id"; return -1;
         }
@@ -603,6 +672,17 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
             return -1;
         }
     if (!check_ready(*m)) return -1;
+    if (m->ep_world > 1) {
+        // With sharded experts the prompt goes through the decode pass position by position
+        // (every rank makes the same number of passes, so the collectives stay in step).
+        int32_t out = -1;
+        for (int i = 0; i < n_tokens; i++) {
+            const int32_t pos = base_pos + i;
+            if (run(*m, &tokens[i], &pos, 1, &out) != 0) return -1;
+        }
+        *out_token = out;
+        return 0;
+    }
     int tile = m->prefill_tile < 1 ? 1 : m->prefill_tile;
     if (tile > n_tokens) tile = n_tokens;
     if (!prefill_alloc(*m, tile)) return -1;
@@ -686,6 +766,10 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
 int llamd_model_bench_matvecs(llamd_model *h, int iters, int nseq, float *ms_out, int *launches_out) {
     Model *m = (Model *)h;
     if (!m || iters <= 0 || !ms_out || nseq < 1 || nseq > m->max_seq || !check_ready(*m)) return -1;
+    if (m->ep_world > 1) {
+        m->err = "bench_matvecs: not available with sharded experts";
+        return -1;
+    }
     const unsigned long long before = g_launches;
     queue_matvecs_only(*m, nseq);  // warm
     if (launches_out) *launches_out = (int)(g_launches - before);

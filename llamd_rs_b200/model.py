@@ -67,8 +67,35 @@ def _bind():
     L.llamd_model_bench_matvecs.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i32)]
     L.llamd_model_launches_per_pass.restype = C.c_ulonglong
     L.llamd_model_launches_per_pass.argtypes = [vp]
+    L.llamd_cuda_ep_unique_id.restype = i32
+    L.llamd_cuda_ep_unique_id.argtypes = [vp]
+    L.llamd_cuda_ep_init.restype = i32
+    L.llamd_cuda_ep_init.argtypes = [i32, i32, vp]
+    L.llamd_cuda_ep_finalize.restype = None
+    L.llamd_cuda_ep_finalize.argtypes = []
+    L.llamd_cuda_ep_rank.restype = i32
+    L.llamd_cuda_ep_world.restype = i32
     L._model_bound = True
     return L
+
+
+def ep_init(rank: int, world: int, share) -> None:
+    """Join the expert-parallel communicator. `share(bytes_or_None) -> bytes`
+    hands rank 0's 128-byte id to every rank (e.g. a torch.distributed/gloo
+    broadcast); call after backend.set_device and before creating the model."""
+    L = _bind()
+    buf = C.create_string_buffer(128)
+    if rank == 0 and L.llamd_cuda_ep_unique_id(buf) != 0:
+        raise backend.Other("ep unique id: " + backend._last_error())
+    ident = share(bytes(buf.raw) if rank == 0 else None)
+    if len(ident) != 128:
+        raise backend.Malformed("ep id must be 128 bytes")
+    if L.llamd_cuda_ep_init(rank, world, C.create_string_buffer(ident, 128)) != 0:
+        raise backend.Other("ep init: " + backend._last_error())
+
+
+def ep_finalize() -> None:
+    _bind().llamd_cuda_ep_finalize()
 
 
 class CudaModel:
@@ -125,8 +152,11 @@ class CudaModel:
             for name, tid in _LAYER_TENSORS.items():
                 if name in lay:
                     m.set_tensor(il, tid, lay[name])
+            # with expert parallelism only this rank's experts are generated and sent
+            world, rank = m._L.llamd_cuda_ep_world(), m._L.llamd_cuda_ep_rank()
+            per = hp["n_expert"] // world
             for which in range(3):
-                for e in range(hp["n_expert"]):
+                for e in range(rank * per, (rank + 1) * per):
                     m.set_expert(il, which, e, synth.expert_blocks(hp, seed, il, which, e))
         return m
 

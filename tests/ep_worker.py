@@ -1,0 +1,78 @@
+"""One rank of the expert-parallel parity check (launched by test_gpu_ep.py
+under torchrun, one process per GPU).
+
+Each rank first decodes ITS sequence on a full single-GPU model, then joins the
+NCCL communicator, reloads the model with only its share of the experts and
+decodes the same sequence again together with the other ranks. Tokens and
+logits must be identical, bit for bit: the exchange moves Q8_K activations and
+f32 rows without touching them, and the home rank adds the expert outputs in
+routing order exactly as the single-GPU pass does.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    import torch.distributed as dist
+
+    from llamd_rs_b200 import backend, synth
+    from llamd_rs_b200 import model as M
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    full_size = len(sys.argv) > 1 and sys.argv[1] == "full"
+    dist.init_process_group(backend="gloo")
+    backend.set_device(local)
+    backend.stream_init()
+    hp = dict(synth.QWEN3MOE_30B, n_layer=3) if full_size else synth.TINY
+    n_prompt, n_gen = 5, 6
+    prompt = synth.token_ids(n_prompt, hp["n_vocab"], 11, "ep", rank).tolist()
+
+    def decode(m):
+        toks, tok = [], None
+        for pos in range(n_prompt + n_gen):
+            tok = m.forward(prompt[pos] if pos < n_prompt else tok, pos)
+            toks.append(tok)
+        return toks, m.logits()[0].copy()
+
+    m = M.CudaModel.load_synthetic(hp, 5, max_kv=32)
+    want_toks, want_logits = decode(m)
+    single_bytes = m.weight_bytes()
+    m.use_graph = False
+    assert decode(m)[0] == want_toks
+    m.free()
+
+    def share(b):
+        obj = [b]
+        dist.broadcast_object_list(obj, src=0)
+        return obj[0]
+
+    M.ep_init(rank, world, share)
+    m = M.CudaModel.load_synthetic(hp, 5, max_kv=32)
+    full_bytes = hp["n_layer"] * 3 * hp["n_expert"] * (hp["n_ff_expert"] * hp["n_embd"] // 256 * 210)
+    got_toks, got_logits = decode(m)            # captured graph with the NCCL exchange inside
+    m.use_graph = False
+    plain_toks, plain_logits = decode(m)        # plain queueing
+    ok = (got_toks == want_toks and plain_toks == want_toks
+          and np.array_equal(got_logits.view(np.uint32), want_logits.view(np.uint32))
+          and np.array_equal(plain_logits.view(np.uint32), want_logits.view(np.uint32)))
+    res = dict(rank=rank, ok=bool(ok), tokens=got_toks, want=want_toks, weight_bytes=m.weight_bytes(), single_bytes=single_bytes,
+               full_expert_bytes=full_bytes)
+    m.free()
+    M.ep_finalize()
+    out = [None] * world
+    dist.all_gather_object(out, res)
+    if rank == 0:
+        print("EP_RESULT " + json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if all(r["ok"] for r in out) else 1)
+
+
+if __name__ == "__main__":
+    main()

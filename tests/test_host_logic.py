@@ -117,3 +117,16 @@ def test_reference_arm_other_ranks_exit_quietly():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
                          capture_output=True, text=True, env=env, timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_protocol_on_gloo(world):
+    """The dispatch / owned-expert compute / ordered combine of the expert-parallel path, rehearsed with the
+    oracle over gloo: every rank's MoE output equals the single-process oracle bit for bit."""
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
+                          "127.0.0.1", "--master-port", str(29760 + world), os.path.join(ROOT, "tests", "ep_protocol_worker.py")],
+                         capture_output=True, text=True, env=env, timeout=300)
+    lines = [l for l in out.stdout.splitlines() if l.startswith("EP_PROTOCOL ")]
+    assert out.returncode == 0 and lines, (out.stdout[-1000:], out.stderr[-2000:])
+    assert json.loads(lines[0][len("EP_PROTOCOL "):]) == [True] * world
