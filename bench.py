@@ -235,6 +235,9 @@ def main():
                          "NCCL dispatch/combine per MoE layer (each rank still decodes its own sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
+    ap.add_argument("--batch-sweep", default="", help="(secondary) comma list of batch sizes: time forward_batch over that many "
+                    "independent sequences (crates/llamd-runtime/src/device.rs:741-962) and print tok/s per batch size to stderr")
+    ap.add_argument("--phases", action="store_true", help="(diagnostic) print the per-phase time of an un-graphed pass and exit")
     ap.add_argument("--pdl-sweep", default="", help="(experiment) comma list of PDL class masks to time, e.g. 0,1,5,15")
     ap.add_argument("--no-graph", action="store_true", help="queue every launch instead of replaying the captured graph "
                     "(for a profiler's launch list; the timed numbers are then not the headline)")
@@ -276,9 +279,10 @@ def main():
     hp = dict(synth.QWEN3MOE_30B)
     hp["n_layer"] = args.layers
     K, W = args.steps, args.warmup
-    max_kv = args.prompt + 2 * (K + W) + 8
+    max_kv = args.prompt + 2 * (K + W) + 8 + (8 * (K + W) if args.batch_sweep else 0)
     t0 = time.time()
-    m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=1)
+    max_seq = max([int(b) for b in args.batch_sweep.split(",")]) if args.batch_sweep else 1
+    m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
     if args.no_graph:
         m.use_graph = False
@@ -311,6 +315,39 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if args.batch_sweep:
+        import numpy as _np
+
+        for B in [int(b) for b in args.batch_sweep.split(",")]:
+            toks = _np.array([int(t) for t in synth.token_ids(B, hp["n_vocab"], 3, "batch")], dtype=_np.int32)
+            p0 = 0
+            for _ in range(args.prompt if B > 1 else 0):  # fill each sequence's cache to the same depth as the headline
+                toks = m.forward_batch(toks, [p0] * B)
+                p0 += 1
+            p0 = max(p0, pos if B == 1 else p0)
+            for _ in range(W):
+                toks = m.forward_batch(toks, [p0] * B)
+                p0 += 1
+            backend.sync()
+            t1 = time.perf_counter()
+            for _ in range(K):
+                toks = m.forward_batch(toks, [p0] * B)
+                p0 += 1
+            backend.sync()
+            dt = time.perf_counter() - t1
+            log(f"[batch-sweep] batch {B}: {B * K / dt:.1f} tok/s aggregate, {dt / K * 1e3:.3f} ms/pass, position ~{p0}")
+        return
+    if args.phases:
+        m.forward(tok, pos)
+        acc = {}
+        for i in range(8):
+            for k, v in m.profile_pass(tok, pos).items():
+                acc[k] = acc.get(k, 0.0) + v / 8
+        tot = sum(acc.values())
+        for k, v in acc.items():
+            log(f"[phase] {k:10s} {v * 1e3:9.1f} us/token {v / hp['n_layer'] * 1e3:7.2f} us/layer {100 * v / tot:5.1f} %")
+        log(f"[phase] total {tot:.3f} ms (events between launches serialise the pass)")
+        return
     if args.pdl_sweep:
         from llamd_rs_b200._lib import lib as _l
 

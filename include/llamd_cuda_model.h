@@ -101,6 +101,16 @@ int llamd_model_decode(llamd_model *m, int32_t first_token, int32_t start_pos, i
 int llamd_model_bench_matvecs(llamd_model *m, int iters, int nseq, float *ms_out, int *launches_out);
 /* Kernel launches one pass queues (the nodes of its graph). */
 unsigned long long llamd_model_launches_per_pass(llamd_model *m);
+/* Phase profile of one pass (the counterpart of DeviceModel::profile,
+ * device.rs:136-199): an un-graphed pass with an event after every launch
+ * group; ms_out[LLAMD_PH_COUNT] gets each phase's time summed over the layers.
+ * A diagnostic: the events serialise the pass, the total is not a throughput. */
+enum {
+    LLAMD_PH_EMBED = 0, LLAMD_PH_ATTN_NORM, LLAMD_PH_QKV, LLAMD_PH_ROPE, LLAMD_PH_ATTENTION, LLAMD_PH_QUANT, LLAMD_PH_ATTN_OUT,
+    LLAMD_PH_FFN_NORM, LLAMD_PH_ROUTER, LLAMD_PH_GATE_UP, LLAMD_PH_SILU, LLAMD_PH_DOWN, LLAMD_PH_LM_HEAD, LLAMD_PH_ARGMAX,
+    LLAMD_PH_COUNT
+};
+int llamd_model_profile_pass(llamd_model *m, int32_t token, int32_t pos, float *ms_out);
 /* Logits of the last pass, [nseq][n_vocab], to host memory (device.rs:966). */
 int llamd_model_logits(llamd_model *m, float *host_out, int nseq);
 /* With "trace" on: x after every layer [n_layer][max_seq][n_embd] and the

@@ -50,7 +50,7 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Kernel classes for the launch attribute (bits of g_pdl).
-enum { PDL_MATVEC = 1, PDL_GROUPED = 2, PDL_ROUTER = 4, PDL_OTHER = 8 };
+enum { PDL_MATVEC = 1, PDL_GROUPED = 2, PDL_ROUTER = 4, PDL_OTHER = 8, PDL_NORM = 16, PDL_ATTN = 32, PDL_SMALL = 64 };
 
 template <typename... KArgs, typename... Args>
 inline void launch_kc(int cls, const char *what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {

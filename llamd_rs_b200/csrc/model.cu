@@ -108,6 +108,11 @@ struct Model {
     // expert parallelism (ep_world > 1): this rank holds experts [own_lo, own_hi)
     int ep_rank = 0, ep_world = 1, own_lo = 0, own_hi = 0;
     Buf ids_all, ad_all, aq_all, gate_all, up_all, aq2_all, ad2_all, down_all, recv_all;
+    // Opt-in phase profile (the counterpart of DeviceModel::profile, crates/llamd-runtime/src/device.rs:136-199):
+    // events between the launches of an un-graphed pass; totals are never a throughput figure.
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<int> prof_phase;
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
     int32_t *h_meta = nullptr;  // pinned
     int32_t *h_out = nullptr;   // pinned
@@ -180,7 +185,21 @@ void queue_token(Model &m, int nseq) {
     const int32_t *meta = m.meta.as<int32_t>();
     float *x = m.x.as<float>();
 
+    size_t n_marks = 0;
+    auto mark = [&](int phase) {
+        if (!m.profiling) return;
+        if (n_marks == m.prof_events.size()) {
+            cudaEvent_t e;
+            cudaEventCreate(&e);
+            m.prof_events.push_back(e);
+            m.prof_phase.push_back(0);
+        }
+        m.prof_phase[n_marks] = phase;
+        cudaEventRecord(m.prof_events[n_marks++], stream());
+    };
+    mark(-1);
     llamd_fwd_embed_meta(m.tok_embd.p, meta, x, eb, nseq);
+    mark(LLAMD_PH_EMBED);
     auto trace_x = [&](int il) {
         if (m.trace)
             cudaMemcpyAsync(m.trace_x.as<float>() + (size_t)il * m.max_seq * E, x, (size_t)nseq * E * sizeof(float), cudaMemcpyDeviceToDevice,
@@ -198,22 +217,30 @@ void queue_token(Model &m, int nseq) {
                                              m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
             trace_x(il - 1);
         }
+        mark(LLAMD_PH_ATTN_NORM);
         llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
                                   m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        mark(LLAMD_PH_QKV);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
         llamd_fwd_qk_norm_rope_store(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
                                      l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
                                      l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
+        mark(LLAMD_PH_ROPE);
         llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
                                  m.max_kv, nseq);
+        mark(LLAMD_PH_ATTENTION);
         // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
         llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+        mark(LLAMD_PH_QUANT);
         llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
         llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
                                      m.ad.as<float>(), E, hp.rms_eps, nseq);
+        mark(LLAMD_PH_FFN_NORM);
         llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
                                 m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
+        mark(LLAMD_PH_ROUTER);
         if (m.ep_world > 1) {
             // Expert parallelism: gather every rank's routed request, run the experts this
             // rank owns for all of them, return each token's rows to its home rank.
@@ -235,11 +262,14 @@ void queue_token(Model &m, int nseq) {
         }
         llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                           m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+        mark(LLAMD_PH_GATE_UP);
         // SiLU on the gate only, times up, quantized per expert; each expert's down projection reads its OWN activation
         llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                  nseq * nu * ffe);
+        mark(LLAMD_PH_SILU);
         llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                           m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+        mark(LLAMD_PH_DOWN);
         if (m.trace)
             cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
                             cudaMemcpyDeviceToDevice, stream());
@@ -248,10 +278,13 @@ void queue_token(Model &m, int nseq) {
     llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
                                      m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
     trace_x(hp.n_layer - 1);
+    mark(LLAMD_PH_ATTN_NORM);
     llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
                            hp.n_vocab, nseq);
+    mark(LLAMD_PH_LM_HEAD);
     llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
                      kArgmaxBlocks, nseq);
+    mark(LLAMD_PH_ARGMAX);
     launch_k("advance_meta", advance_meta_kernel, dim3(1), dim3(32), 0, m.meta.as<int32_t>(), (const int32_t *)m.out_token.as<int32_t>(),
              m.tok_log.as<int32_t>(), m.tok_count.as<int32_t>(), nseq, m.max_kv * m.max_seq);
 }
@@ -450,6 +483,7 @@ void llamd_model_free(llamd_model *h) {
                    &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work})
         b->release();
     if (m->pf.h_meta) cudaFreeHost(m->pf.h_meta);
+    for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out) cudaFreeHost(m->h_out);
     delete m;
@@ -788,6 +822,33 @@ int llamd_model_bench_matvecs(llamd_model *h, int iters, int nseq, float *ms_out
 }
 
 unsigned long long llamd_model_launches_per_pass(llamd_model *h) { return h ? ((Model *)h)->launches_per_pass : 0; }
+
+// One un-graphed pass with an event after every launch group; ms_out[LLAMD_PH_COUNT] receives the time
+// from the previous mark to each phase's mark, summed over the layers (so it includes the launch gap).
+int llamd_model_profile_pass(llamd_model *h, int32_t token, int32_t pos, float *ms_out) {
+    Model *m = (Model *)h;
+    if (!m || !ms_out || m->ep_world > 1) return -1;
+    m->err.clear();
+    const int saved_graph = m->use_graph;
+    m->use_graph = 0;
+    m->profiling = true;
+    int32_t out = 0;
+    const int rc = run(*m, &token, &pos, 1, &out);
+    m->profiling = false;
+    m->use_graph = saved_graph;
+    if (rc != 0) return -1;
+    for (int i = 0; i < LLAMD_PH_COUNT; i++) ms_out[i] = 0.0f;
+    for (size_t i = 1; i < m->prof_events.size(); i++) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, m->prof_events[i - 1], m->prof_events[i]) != cudaSuccess) {
+            cudaGetLastError();
+            break;
+        }
+        const int ph = m->prof_phase[i];
+        if (ph >= 0 && ph < LLAMD_PH_COUNT) ms_out[ph] += ms;
+    }
+    return 0;
+}
 
 int llamd_model_logits(llamd_model *h, float *host_out, int nseq) {
     Model *m = (Model *)h;

@@ -863,7 +863,7 @@ void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float
 // Query heads and key heads in one launch: QK-norm, RoPE, and the KV store.
 void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc, int n_head,
                                   int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv) {
-    launch_k("qk_norm_rope_store", norm_rope_kernel, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc, vc,
+    launch_kc(PDL_SMALL, "qk_norm_rope_store", norm_rope_kernel, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc, vc,
              n_head, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
 }
 // The same for the ntok tokens of a prefill tile: all rows go into ONE cache.
@@ -889,9 +889,9 @@ static void attention_split_launch(const float *q, const float *kc, const float 
         cudaFuncSetAttribute(attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
         conf_b = smem_b;
     }
-    launch_k("attn_scores", attn_scores_kernel, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
+    launch_kc(PDL_ATTN, "attn_scores", attn_scores_kernel, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
              max_kv, kv_stride);
-    launch_k("attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
+    launch_kc(PDL_ATTN, "attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
              meta, n_kv, max_kv, kv_stride);
 }
 

@@ -225,7 +225,7 @@ extern "C" {
 
 void llamd_fwd_quantize_bsums(const float *x, int8_t *qs, float *d, int16_t *bsums, int nblocks) {
     if (nblocks <= 0) return;
-    launch_k("q8k_quantize", q8k_quantize_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, x, qs, d, bsums, nblocks);
+    launch_kc(PDL_SMALL, "q8k_quantize", q8k_quantize_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, x, qs, d, bsums, nblocks);
 }
 void llamd_fwd_quantize(const float *x, int8_t *qs, float *d, int nblocks) {
     llamd_fwd_quantize_bsums(x, qs, d, nullptr, nblocks);
@@ -236,7 +236,7 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         set_error_msg("rms_norm: n must be a multiple of 4 and at most 6144");
         return;
     }
-    launch_k("rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
+    launch_kc(PDL_NORM, "rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
              nullptr, nullptr, n, eps);
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
@@ -244,7 +244,7 @@ void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t
         set_error_msg("rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    launch_k("rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
+    launch_kc(PDL_NORM, "rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
              out, qs, d, n, eps);
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
@@ -255,7 +255,7 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
         set_error_msg("add_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    launch_k("add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
+    launch_kc(PDL_NORM, "add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
              w, out, qs, d, n, eps);
 }
 // x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
@@ -267,7 +267,7 @@ void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const f
         set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    launch_k("combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
+    launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
              sum_out, w, out, qs, d, n, eps);
 }
 void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
@@ -292,7 +292,7 @@ void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, in
         return;
     }
     const int nblocks = n / 256;
-    launch_k("silu_mul_quant", silu_mul_quant_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, gate, up, out, qs, d, nblocks);
+    launch_kc(PDL_SMALL, "silu_mul_quant", silu_mul_quant_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, gate, up, out, qs, d, nblocks);
 }
 void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd) {
     moe_combine_kernel<<<dim3((n_embd + 255) / 256, 1), 256, 0, stream()>>>(down, weights, nullptr, out, n_used, n_embd);

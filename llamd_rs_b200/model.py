@@ -67,6 +67,8 @@ def _bind():
     L.llamd_model_bench_matvecs.argtypes = [vp, i32, i32, C.POINTER(C.c_float), C.POINTER(i32)]
     L.llamd_model_launches_per_pass.restype = C.c_ulonglong
     L.llamd_model_launches_per_pass.argtypes = [vp]
+    L.llamd_model_profile_pass.restype = i32
+    L.llamd_model_profile_pass.argtypes = [vp, C.c_int32, C.c_int32, vp]
     L.llamd_cuda_ep_unique_id.restype = i32
     L.llamd_cuda_ep_unique_id.argtypes = [vp]
     L.llamd_cuda_ep_init.restype = i32
@@ -255,6 +257,16 @@ class CudaModel:
 
     def launches_per_pass(self) -> int:
         return int(self._L.llamd_model_launches_per_pass(self._h))
+
+    PHASES = ("embed", "attn_norm", "qkv", "rope", "attention", "quant", "attn_out", "ffn_norm", "router", "gate_up", "silu", "down",
+              "lm_head", "argmax")
+
+    def profile_pass(self, token: int, pos: int) -> dict:
+        """Per-phase milliseconds of one un-graphed pass (summed over layers). A diagnostic, not a throughput."""
+        ms = np.zeros(len(self.PHASES), dtype=np.float32)
+        if self._L.llamd_model_profile_pass(self._h, int(token), int(pos), ms.ctypes.data_as(C.c_void_p)) != 0:
+            raise backend.Other("profile_pass: " + self._err())
+        return dict(zip(self.PHASES, ms.tolist()))
 
     def logits(self, nseq: int = 1) -> np.ndarray:
         out = np.zeros((nseq, self.hp["n_vocab"]), dtype=np.float32)
