@@ -261,6 +261,17 @@ void llamd_fwd_matvec_tokens(const void *w0, const void *w1, const void *w2, con
 void llamd_fwd_expert_major(const void *wa, const void *wb, const int32_t *work, const int32_t *n_work, int max_items,
                             const int32_t *act_map, const int32_t *pslot, const int8_t *aq, const float *ad,
                             float *oa, float *ob, int blocks, int rows, int n_expert);
+/* The same two on the integer tensor path (mma.sync s8 x s8 -> s32 per
+ * (block, residue) slice, f32 scaling per slice as crates/llamd-vulkan/shaders/
+ * q6k_expert_cm.comp:18-31 does per 16-K group); results identical to the two
+ * above. Activations are the residue-major words llamd_fwd_q8k_residue_major
+ * makes from Q8_K quants; the expert form takes gstart/gcount of the plan. */
+void llamd_fwd_q8k_residue_major(const int8_t *aq, void *aq_rm, size_t nblocks);
+void llamd_fwd_gemm_tokens(const void *w0, const void *w1, const void *w2, const void *aq_rm, const float *ad, float *o0,
+                           float *o1, float *o2, int blocks, int rows0, int rows1, int rows2, int ntok);
+void llamd_fwd_expert_gemm(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount,
+                           const int32_t *act_map, const int32_t *pslot, const void *aq_rm, const float *ad, float *oa,
+                           float *ob, int blocks, int rows, int n_expert);
 /* QK-norm/RoPE/KV-store and attention for the ntok tokens of one tile: every
  * row is a position (meta[2i+1]) of ONE sequence whose cache is kc/vc.
  * scores: [ntok][n_head][max_kv] floats. */

@@ -103,6 +103,9 @@ SIGNATURES = {
     "llamd_fwd_argmax": (None, [vp, i32, vp, vp, vp, i32, i32]),
     "llamd_fwd_matvec_tokens": (None, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
     "llamd_fwd_expert_major": (None, [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32]),
+    "llamd_fwd_q8k_residue_major": (None, [vp, vp, sz]),
+    "llamd_fwd_gemm_tokens": (None, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
+    "llamd_fwd_expert_gemm": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_qk_norm_rope_store_tile": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32]),
     "llamd_fwd_attention_tile": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32]),
     "llamd_fwd_moe_group": (None, [vp, i32, i32, i32, vp, vp, vp, vp]),

@@ -43,6 +43,12 @@ void llamd_fwd_ep_dispatch(const int32_t *ids, const float *ad, const int8_t *aq
 void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, float *down, int n_used, int n_embd, int n_expert);
 int llamd_cuda_ep_rank(void);
 int llamd_cuda_ep_world(void);
+void llamd_fwd_q8k_residue_major(const int8_t *aq, void *aq_rm, size_t nblocks);
+void llamd_fwd_gemm_tokens(const void *w0, const void *w1, const void *w2, const void *aq_rm, const float *ad, float *o0, float *o1,
+                           float *o2, int blocks, int rows0, int rows1, int rows2, int ntok);
+void llamd_fwd_expert_gemm(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
+                           const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows,
+                           int n_expert);
 void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits, int32_t *ids,
                              float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
@@ -103,6 +109,7 @@ struct Model {
         int tile = 0;
         Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, ids, w, logits, counter, gate, up, down, scores, meta;
         Buf gstart, gcount, ptoken, pslot, work, n_work;
+        Buf aq_rm, aq2_rm;  // residue-major copies of aq / aq2 for the tensor-path GEMM
         int32_t *h_meta = nullptr;
     } pf;
     // expert parallelism (ep_world > 1): this rank holds experts [own_lo, own_hi)
@@ -113,6 +120,7 @@ struct Model {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_phase;
+    int prefill_gemm = 1;    // 1: integer tensor path (mma.sync) for the tile's matmuls; 0: dp4a, 8 tokens per weight pass
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
     int32_t *h_meta = nullptr;  // pinned
     int32_t *h_out = nullptr;   // pinned
@@ -480,7 +488,7 @@ void llamd_model_free(llamd_model *h) {
         b->release();
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
                    &m->pf.ids, &m->pf.w, &m->pf.logits, &m->pf.counter, &m->pf.gate, &m->pf.up, &m->pf.down, &m->pf.scores, &m->pf.meta,
-                   &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work})
+                   &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work, &m->pf.aq_rm, &m->pf.aq2_rm})
         b->release();
     if (m->pf.h_meta) cudaFreeHost(m->pf.h_meta);
     for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
@@ -571,6 +579,10 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         m->use_graph = value;
         return 0;
     }
+    if (!strcmp(name, "prefill_gemm")) {
+        m->prefill_gemm = value;
+        return 0;
+    }
     if (!strcmp(name, "prefill_tile")) {
         if (value < 1 || value > 4096) return -1;
         m->prefill_tile = value;
@@ -620,7 +632,8 @@ static bool prefill_alloc(Model &m, int tile) {
     Model::Prefill &p = m.pf;
     if (p.tile >= tile) return true;
     for (Buf *b : {&p.x, &p.xb, &p.xb2, &p.q, &p.k, &p.v, &p.attn, &p.aq, &p.ad, &p.aq2, &p.ad2, &p.ids, &p.w, &p.logits, &p.counter,
-                   &p.gate, &p.up, &p.down, &p.scores, &p.meta, &p.gstart, &p.gcount, &p.ptoken, &p.pslot, &p.work, &p.n_work})
+                   &p.gate, &p.up, &p.down, &p.scores, &p.meta, &p.gstart, &p.gcount, &p.ptoken, &p.pslot, &p.work, &p.n_work, &p.aq_rm,
+                   &p.aq2_rm})
         b->release();
     if (p.h_meta) cudaFreeHost(p.h_meta);
     p.h_meta = nullptr;
@@ -633,7 +646,8 @@ static bool prefill_alloc(Model &m, int tile) {
               p.logits.alloc(T * ne * 4) && p.counter.alloc(T * 4) && p.gate.alloc(T * nu * ffe * 4) && p.up.alloc(T * nu * ffe * 4) &&
               p.down.alloc(T * nu * E * 4) && p.scores.alloc(T * hp.n_head * (size_t)m.max_kv * 4) && p.meta.alloc(T * 8) &&
               p.gstart.alloc(ne * 4) && p.gcount.alloc(ne * 4) && p.ptoken.alloc(T * nu * 4) && p.pslot.alloc(T * nu * 4) &&
-              p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && cudaMallocHost((void **)&p.h_meta, T * 8) == cudaSuccess;
+              p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && p.aq_rm.alloc(T * max_act) && p.aq2_rm.alloc(T * nu * ffe) &&
+              cudaMallocHost((void **)&p.h_meta, T * 8) == cudaSuccess;
     if (!ok) {
         m.err = std::string("prefill buffers: ") + llamd_cuda_last_error_string();
         return false;
@@ -658,16 +672,29 @@ static void queue_prefill_tile(Model &m, int T, bool last) {
         else
             llamd_fwd_combine_rms_norm_quant(x, p.down.as<float>(), p.w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
                                              p.aq.as<int8_t>(), p.ad.as<float>(), E, hp.rms_eps, T);
-        llamd_fwd_matvec_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq.as<int8_t>(), p.ad.as<float>(), p.q.as<float>(), p.k.as<float>(),
-                                p.v.as<float>(), eb, qd, kvd, kvd, T);
+        const bool gemm = m.prefill_gemm != 0;
+        if (gemm) {
+            llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * eb);
+            llamd_fwd_gemm_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq_rm.p, p.ad.as<float>(), p.q.as<float>(), p.k.as<float>(),
+                                  p.v.as<float>(), eb, qd, kvd, kvd, T);
+        } else {
+            llamd_fwd_matvec_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq.as<int8_t>(), p.ad.as<float>(), p.q.as<float>(),
+                                    p.k.as<float>(), p.v.as<float>(), eb, qd, kvd, kvd, T);
+        }
         llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
                                           l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
                                           l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
         llamd_fwd_attention_tile(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd,
                                  meta, m.max_kv, T);
         llamd_fwd_quantize(p.attn.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(), T * (qd / 256));
-        llamd_fwd_matvec_tokens(l.attn_out.p, nullptr, nullptr, p.aq.as<int8_t>(), p.ad.as<float>(), p.xb2.as<float>(), nullptr, nullptr,
-                                qd / 256, E, 0, 0, T);
+        if (gemm) {
+            llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * (qd / 256));
+            llamd_fwd_gemm_tokens(l.attn_out.p, nullptr, nullptr, p.aq_rm.p, p.ad.as<float>(), p.xb2.as<float>(), nullptr, nullptr, qd / 256,
+                                  E, 0, 0, T);
+        } else {
+            llamd_fwd_matvec_tokens(l.attn_out.p, nullptr, nullptr, p.aq.as<int8_t>(), p.ad.as<float>(), p.xb2.as<float>(), nullptr, nullptr,
+                                    qd / 256, E, 0, 0, T);
+        }
         llamd_fwd_add_rms_norm_quant(x, p.xb2.as<float>(), x, l.ffn_norm.as<float>(), p.xb.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(),
                                      E, hp.rms_eps, T);
         llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), p.xb.as<float>(), E, ne, nu, p.logits.as<float>(), p.ids.as<int32_t>(),
@@ -675,11 +702,23 @@ static void queue_prefill_tile(Model &m, int T, bool last) {
         // the expert scatter plan: (token, slot) pairs sorted by expert
         llamd_fwd_moe_group_work(p.ids.as<int32_t>(), ne, nu, T, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
                                  p.pslot.as<int32_t>(), p.work.as<int32_t>(), p.n_work.as<int32_t>());
-        llamd_fwd_expert_major(l.gate_exps.p, l.up_exps.p, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items, p.ptoken.as<int32_t>(),
-                               p.pslot.as<int32_t>(), p.aq.as<int8_t>(), p.ad.as<float>(), p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne);
-        llamd_fwd_silu_mul_quant(p.gate.as<float>(), p.up.as<float>(), nullptr, p.aq2.as<int8_t>(), p.ad2.as<float>(), T * nu * ffe);
-        llamd_fwd_expert_major(l.down_exps.p, nullptr, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items, p.pslot.as<int32_t>(),
-                               p.pslot.as<int32_t>(), p.aq2.as<int8_t>(), p.ad2.as<float>(), p.down.as<float>(), nullptr, ffe / 256, E, ne);
+        if (gemm) {
+            llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * eb);
+            llamd_fwd_expert_gemm(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
+                                  p.pslot.as<int32_t>(), p.aq_rm.p, p.ad.as<float>(), p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne);
+            llamd_fwd_silu_mul_quant(p.gate.as<float>(), p.up.as<float>(), nullptr, p.aq2.as<int8_t>(), p.ad2.as<float>(), T * nu * ffe);
+            llamd_fwd_q8k_residue_major(p.aq2.as<int8_t>(), p.aq2_rm.p, (size_t)T * nu * (ffe / 256));
+            llamd_fwd_expert_gemm(l.down_exps.p, nullptr, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.pslot.as<int32_t>(),
+                                  p.pslot.as<int32_t>(), p.aq2_rm.p, p.ad2.as<float>(), p.down.as<float>(), nullptr, ffe / 256, E, ne);
+        } else {
+            llamd_fwd_expert_major(l.gate_exps.p, l.up_exps.p, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items,
+                                   p.ptoken.as<int32_t>(), p.pslot.as<int32_t>(), p.aq.as<int8_t>(), p.ad.as<float>(), p.gate.as<float>(),
+                                   p.up.as<float>(), eb, ffe, ne);
+            llamd_fwd_silu_mul_quant(p.gate.as<float>(), p.up.as<float>(), nullptr, p.aq2.as<int8_t>(), p.ad2.as<float>(), T * nu * ffe);
+            llamd_fwd_expert_major(l.down_exps.p, nullptr, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items, p.pslot.as<int32_t>(),
+                                   p.pslot.as<int32_t>(), p.aq2.as<int8_t>(), p.ad2.as<float>(), p.down.as<float>(), nullptr, ffe / 256, E,
+                                   ne);
+        }
     }
     if (!last) return;
     // logits for the tile's last token only (vulkan_model.rs:793-818)

@@ -204,6 +204,10 @@ class CudaModel:
             raise backend.Malformed(f"prefill_tile {v} outside 1..4096")
         self._prefill_tile = int(v)
 
+    def set_prefill_gemm(self, on: bool) -> None:
+        """True (default): the prefill tile's matmuls run on the integer tensor path; False: dp4a, 8 tokens per pass."""
+        self._L.llamd_model_set_option(self._h, b"prefill_gemm", int(on))
+
     def set_trace(self, on: bool) -> None:
         if self._L.llamd_model_set_option(self._h, b"trace", int(on)) != 0:
             raise backend.Other("trace buffers: " + self._err())

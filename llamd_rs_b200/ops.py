@@ -234,10 +234,10 @@ def embed(table: "backend.DeviceWeights", token: int) -> np.ndarray:
     return do.download_f32(table.blocks() * QK_K)
 
 
-def matvec_tokens(weights, x):
+def matvec_tokens(weights, x, gemm: bool = False):
     """`weights`: 1-3 DeviceWeights sharing the column count; x f32 [ntok][k].
     Quantizes on the device, then every token against every matrix.
-    -> list of [ntok][rows_i] (llamd_fwd_matvec_tokens)."""
+    -> list of [ntok][rows_i] (llamd_fwd_matvec_tokens; gemm=True: llamd_fwd_gemm_tokens)."""
     x = _f32(x)
     ntok, k = x.shape
     ws = list(weights)
@@ -250,12 +250,17 @@ def matvec_tokens(weights, x):
     wp = [w.ptr for w in ws] + [None] * (3 - len(ws))
     op = [o.ptr for o in outs] + [None] * (3 - len(ws))
     rows = [w.rows() for w in ws] + [0] * (3 - len(ws))
-    lib().llamd_fwd_matvec_tokens(wp[0], wp[1], wp[2], dq.ptr, dd.ptr, op[0], op[1], op[2], nb, rows[0], rows[1], rows[2], ntok)
+    if gemm:
+        drm = DevBuf(ntok * k)
+        lib().llamd_fwd_q8k_residue_major(dq.ptr, drm.ptr, ntok * nb)
+        lib().llamd_fwd_gemm_tokens(wp[0], wp[1], wp[2], drm.ptr, dd.ptr, op[0], op[1], op[2], nb, rows[0], rows[1], rows[2], ntok)
+    else:
+        lib().llamd_fwd_matvec_tokens(wp[0], wp[1], wp[2], dq.ptr, dd.ptr, op[0], op[1], op[2], nb, rows[0], rows[1], rows[2], ntok)
     backend.sync()
     return [o.download_f32(ntok * w.rows()).reshape(ntok, w.rows()) for o, w in zip(outs, ws)]
 
 
-def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False):
+def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False, gemm: bool = False):
     """Routed matvec for many tokens through the scatter plan.
 
     `weights`: 1-2 DeviceWeights holding n_expert matrices of rows_per_expert
@@ -284,8 +289,14 @@ def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False):
     wk, nw = DevBuf((max_items + 1) * 12), DevBuf.zeroed(4)
     lib().llamd_fwd_moe_group_work(di.ptr, n_expert, n_used, ntok, gs.ptr, gc.ptr, pt.ptr, ps.ptr, wk.ptr, nw.ptr)
     outs = [DevBuf.zeroed(npair * rows_per_expert * 4) for _ in ws]
-    lib().llamd_fwd_expert_major(ws[0].ptr, ws[1].ptr if len(ws) > 1 else None, wk.ptr, nw.ptr, max_items, ps.ptr if by_slot else pt.ptr,
-                                 ps.ptr, dq.ptr, dd.ptr, outs[0].ptr, outs[1].ptr if len(ws) > 1 else None, nb, rows_per_expert, n_expert)
+    if gemm:
+        drm = DevBuf(nact * k)
+        lib().llamd_fwd_q8k_residue_major(dq.ptr, drm.ptr, nact * nb)
+        lib().llamd_fwd_expert_gemm(ws[0].ptr, ws[1].ptr if len(ws) > 1 else None, gs.ptr, gc.ptr, ps.ptr if by_slot else pt.ptr, ps.ptr,
+                                    drm.ptr, dd.ptr, outs[0].ptr, outs[1].ptr if len(ws) > 1 else None, nb, rows_per_expert, n_expert)
+    else:
+        lib().llamd_fwd_expert_major(ws[0].ptr, ws[1].ptr if len(ws) > 1 else None, wk.ptr, nw.ptr, max_items, ps.ptr if by_slot else pt.ptr,
+                                     ps.ptr, dq.ptr, dd.ptr, outs[0].ptr, outs[1].ptr if len(ws) > 1 else None, nb, rows_per_expert, n_expert)
     backend.sync()
     return [o.download_f32(npair * rows_per_expert).reshape(npair, rows_per_expert) for o in outs]
 

@@ -225,6 +225,8 @@ def test_matvec_tokens_equals_per_token_matvec(be, orc, synth, ntok):
         for t in range(ntok):
             assert_bit_equal(g[t], orc.matvec_q6k(w, x[t], k, r), f"token {t}")
     assert_bit_equal(ops.matvec_tokens(dws[:1], x)[0], got[0], "one matrix alone")
+    for a, b in zip(ops.matvec_tokens(dws, x, gemm=True), got):
+        assert_bit_equal(a, b, "tensor-path GEMM == dp4a matvec")
 
 
 @pytest.mark.parametrize("ntok,n_used", [(1, 2), (5, 2), (40, 3), (64, 8)])
@@ -255,6 +257,12 @@ def test_expert_major_equals_token_major(be, orc, synth, ntok, n_used):
     for p_ in range(ntok * n_used):
         e = int(ids.ravel()[p_])
         assert_bit_equal(gd[p_], orc.matvec_q6k(wa[e * per:(e + 1) * per], xs[p_], k, rows), f"down pair {p_}")
+    # the integer tensor path gives the same bits
+    ta, tb = ops.expert_major([da, db], x, ids, rows, gemm=True)
+    assert_bit_equal(ta, ga, "expert GEMM gate")
+    assert_bit_equal(tb, gb, "expert GEMM up")
+    (td,) = ops.expert_major([da], xs, ids, rows, by_slot=True, gemm=True)
+    assert_bit_equal(td, gd, "expert GEMM down")
     with pytest.raises(be.Malformed):
         ops.expert_major([da], x, np.full((ntok, n_used), n_expert, np.int32), rows)
 
@@ -288,3 +296,15 @@ def test_down_projection_with_fused_silu(be, orc, synth):
     act = ops.silu_mul(gate.ravel(), up.ravel()).reshape(len(ids), k)  # the device's own activation (exp differs from libm by <= 1 ulp)
     for s_, e in enumerate(ids):
         assert_bit_equal(got[s_], orc.matvec_q6k(w[e * per:(e + 1) * per], act[s_], k, rows), f"slot {s_}")
+
+
+def test_gemm_rows_not_a_multiple_of_16_and_odd_blocks(be, orc, synth):
+    from llamd_rs_b200 import ops
+
+    for rows, k, ntok in ((37, 768, 11), (5, 256, 3), (100, 4096, 9)):
+        w = synth.q6k_blocks(rows * k // 256, 81, "gemm", rows)
+        dw = be.DeviceWeights.upload(w, rows, k // 256)
+        x = synth.normal_f32(ntok * k, 81, "gemm.x", rows).reshape(ntok, k)
+        (got,) = ops.matvec_tokens([dw], x, gemm=True)
+        for t in range(ntok):
+            assert_bit_equal(got[t], orc.matvec_q6k(w, x[t], k, rows), f"{rows}x{k} token {t}")

@@ -151,9 +151,12 @@ def test_prefill_equals_sequential_decode(tiny):
     kv_ref = [gm.read_kv(il, len(prompt)) for il in range(hp["n_layer"])]
     for tile, length in [(1, 1), (1, 5), (2, 5), (4, 4), (4, 5), (8, 7), (8, 8), (8, 9), (8, 17), (16, 33), (16, 37), (64, 37), (512, 37)]:
         gm.prefill_tile = tile
-        got = gm.prefill(prompt[:length], 0)
-        assert got == seq_tok[length], f"tile {tile} length {length}"
-        assert np.array_equal(gm.logits()[0].view(np.uint32), seq_logits[length].view(np.uint32)), f"tile {tile} length {length}: logits"
+        for gemm in (True, False):  # integer tensor path and dp4a path
+            gm.set_prefill_gemm(gemm)
+            got = gm.prefill(prompt[:length], 0)
+            assert got == seq_tok[length], f"tile {tile} length {length} gemm {gemm}"
+            assert np.array_equal(gm.logits()[0].view(np.uint32), seq_logits[length].view(np.uint32)), f"tile {tile} length {length}: logits"
+    gm.set_prefill_gemm(True)
     for il in range(hp["n_layer"]):
         k, v = gm.read_kv(il, len(prompt))
         assert np.array_equal(k.view(np.uint32), kv_ref[il][0].view(np.uint32)) and np.array_equal(v.view(np.uint32), kv_ref[il][1].view(np.uint32))
