@@ -86,51 +86,65 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
     const size_t unit0 = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)row0 * nb;
 
     // ---- fold the scales into the weights, split hi/lo, store in fragment order ----
-    // task = (row, block, residue, quad m): three stored words -> four W4 words (j = 4m..4m+3)
-    const int ntask = kGemmRows * nb * 16;
-    for (int t = tid; t < ntask; t += kGemmThreads) {
-        const int m = t & 1, r = (t >> 1) & 7, rb = t >> 4;  // rb = row_local * nb + b
+    // One thread per (row, block): its 13 coalesced 16-byte loads fetch the whole block (as in the matvec
+    // kernel), all issued before any is used.
+    for (int rb = tid; rb < kGemmRows * nb; rb += kGemmThreads) {  // rb = row_local * nb + b
         const int row_l = rb / nb, b = rb - row_l * nb;
-        uint32_t hi[4] = {0, 0, 0, 0}, lo[4] = {0, 0, 0, 0};
-        if (row0 + row_l < rows) {
+        const bool live = row0 + row_l < rows;
+        uint32_t S[48];
+        uint4 scw = make_uint4(0, 0, 0, 0);
+        if (live) {
             const size_t unit = unit0 + rb;
-            const uint32_t s0 = __ldg(reinterpret_cast<const uint32_t *>(w + t32_word_offset(unit, 6 * r + 3 * m + 0)));
-            const uint32_t s1 = __ldg(reinterpret_cast<const uint32_t *>(w + t32_word_offset(unit, 6 * r + 3 * m + 1)));
-            const uint32_t s2 = __ldg(reinterpret_cast<const uint32_t *>(w + t32_word_offset(unit, 6 * r + 3 * m + 2)));
-            const uint2 scw = __ldg(reinterpret_cast<const uint2 *>(w + t32_scale_offset(unit) + 8 * m));  // scales of groups 8m..8m+7
-            uint32_t w4[4];
-            w4[0] = s0 & 0xFCFCFCFCu;
-            w4[1] = s1 & 0xFCFCFCFCu;
-            w4[2] = s2 & 0xFCFCFCFCu;
-            w4[3] = ((s0 << 6) & 0xC0C0C0C0u) | ((s1 << 4) & 0x30303030u) | ((s2 << 2) & 0x0C0C0C0Cu);
+            const uint8_t *tile = w + (unit >> 5) * kTileBytes;
+            const int sl = (int)(unit & 31);
+            const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int c = 0; c < 12; c++) {
+                const uint4 v = __ldg(cp + c * 32);
+                S[4 * c + 0] = v.x; S[4 * c + 1] = v.y; S[4 * c + 2] = v.z; S[4 * c + 3] = v.w;
+            }
+            scw = __ldg(reinterpret_cast<const uint4 *>(tile + kTileScaleOff) + sl);
+            s_d[rb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl));
+        } else {
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    // byte k of word 4m+i: weight (q-32) = the 6-bit field above bit 2; its group is 2(4m+i) + (k>>1)
-                    const int wv = ((int)(w4[i] << (24 - 8 * k))) >> 26;
-                    const int g = 2 * i + (k >> 1);  // within this quad's eight groups
-                    const int sc = (int)(int8_t)((g < 4 ? scw.x : scw.y) >> (8 * (g & 3)));
-                    const int u = wv * sc;  // 13 bits signed
-                    lo[i] |= (uint32_t)(u & 63) << (8 * k);
-                    hi[i] |= (uint32_t)((u >> 6) & 0xFF) << (8 * k);
+            for (int c = 0; c < 48; c++) S[c] = 0;
+            s_d[rb] = 0.0f;
+        }
+        int sc[16];
+        {
+            const uint32_t ws[4] = {scw.x, scw.y, scw.z, scw.w};
+#pragma unroll
+            for (int i = 0; i < 16; i++) sc[i] = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+        }
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+#pragma unroll
+            for (int m = 0; m < 2; m++) {
+                const uint32_t s0 = S[6 * r + 3 * m], s1 = S[6 * r + 3 * m + 1], s2 = S[6 * r + 3 * m + 2];
+                uint32_t w4[4];
+                w4[0] = s0 & 0xFCFCFCFCu;
+                w4[1] = s1 & 0xFCFCFCFCu;
+                w4[2] = s2 & 0xFCFCFCFCu;
+                w4[3] = ((s0 << 6) & 0xC0C0C0C0u) | ((s1 << 4) & 0x30303030u) | ((s2 << 2) & 0x0C0C0C0Cu);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    uint32_t hi = 0, lo = 0;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        // byte k of word jw = 4m+i: weight (q-32) = the 6-bit field above bit 2; its group is 2*jw + (k>>1)
+                        const int wv = ((int)(w4[i] << (24 - 8 * k))) >> 26;
+                        const int u = wv * sc[2 * (4 * m + i) + (k >> 1)];  // 13 bits signed
+                        lo |= (uint32_t)(u & 63) << (8 * k);
+                        hi |= (uint32_t)((u >> 6) & 0xFF) << (8 * k);
+                    }
+                    // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1)
+                    const int jw = 4 * m + i;
+                    const int L = (row_l & 7) * 4 + (jw & 3), q = (row_l >> 3) + 2 * (jw >> 2);
+                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + L)[q] = hi;
+                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 1) * 32 + L)[q] = lo;
                 }
             }
         }
-        // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1)
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int jw = 4 * m + i;
-            const int L = (row_l & 7) * 4 + (jw & 3), q = (row_l >> 3) + 2 * (jw >> 2);
-            uint32_t *fh = reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + L) + q;
-            uint32_t *fl = reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 1) * 32 + L) + q;
-            *fh = hi[i];
-            *fl = lo[i];
-        }
-    }
-    for (int t = tid; t < kGemmRows * nb; t += kGemmThreads) {
-        const int row_l = t / nb;
-        s_d[t] = (row0 + row_l < rows) ? f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(w + t32_d_offset(unit0 + t)))) : 0.0f;
     }
     __syncthreads();
 

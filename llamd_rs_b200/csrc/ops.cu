@@ -702,22 +702,29 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, 
                                  int32_t *__restrict__ gcount, int32_t *__restrict__ ptoken, int32_t *__restrict__ pslot,
                                  int32_t *__restrict__ work, int32_t *__restrict__ n_work) {
     extern __shared__ int s_ids[];
+    __shared__ int s_count[1024];
     __shared__ int s_start[1024];
     __shared__ int s_wstart[1024];
     pdl_trigger();
     pdl_wait();
-    const int e = threadIdx.x;
-    for (int p = threadIdx.x; p < npair; p += blockDim.x) s_ids[p] = ids[p];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int p = tid; p < npair; p += blockDim.x) s_ids[p] = ids[p];
     __syncthreads();
-    int count = 0;
-    if (e < n_expert)
-        for (int p = 0; p < npair; p++) count += (s_ids[p] == e);
-    if (e < n_expert) s_start[e] = count;
+    // A warp owns experts warp, warp+nwarps, ...: its lanes look at 32 pairs at a time, and the ballot keeps
+    // the pairs of an expert in ascending pair order.
+    for (int e = warp; e < n_expert; e += nwarps) {
+        int count = 0;
+        for (int p0 = 0; p0 < npair; p0 += 32) {
+            const int p = p0 + lane;
+            count += __popc(__ballot_sync(0xffffffffu, p < npair && s_ids[p] == e));
+        }
+        if (lane == 0) s_count[e] = count;
+    }
     __syncthreads();
-    if (e == 0) {
+    if (tid == 0) {
         int run = 0, wrun = 0;
         for (int i = 0; i < n_expert; i++) {
-            const int c = s_start[i];
+            const int c = s_count[i];
             s_start[i] = run;
             s_wstart[i] = wrun;
             run += c;
@@ -726,20 +733,28 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, 
         if (n_work) *n_work = wrun;
     }
     __syncthreads();
-    if (e < n_expert) {
-        const int start = s_start[e];
+    for (int e = warp; e < n_expert; e += nwarps) {
+        const int start = s_start[e], count = s_count[e];
         int at = start;
-        for (int p = 0; p < npair; p++)
-            if (s_ids[p] == e) {
-                ptoken[at] = p / n_used;
-                pslot[at] = p;
-                at++;
+        for (int p0 = 0; p0 < npair; p0 += 32) {
+            const int p = p0 + lane;
+            const bool mine = p < npair && s_ids[p] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int dst = at + __popc(mask & ((1u << lane) - 1u));
+                ptoken[dst] = p / n_used;
+                pslot[dst] = p;
             }
-        gstart[e] = start;
-        gcount[e] = count;
+            at += __popc(mask);
+        }
+        if (lane == 0) {
+            gstart[e] = start;
+            gcount[e] = count;
+        }
         if (work) {
-            int wi = s_wstart[e];
-            for (int f = 0; f < count; f += 8, wi++) {
+            const int wi0 = s_wstart[e];
+            for (int f = lane * 8; f < count; f += 256) {
+                const int wi = wi0 + f / 8;
                 work[3 * wi + 0] = e;
                 work[3 * wi + 1] = start + f;
                 work[3 * wi + 2] = min(8, count - f);
@@ -1003,10 +1018,10 @@ void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int 
         set_error_msg("moe_group: n_expert 1..1024 and at most 40960 pairs per call");
         return;
     }
-    const int threads = ((n_expert + 31) / 32) * 32;
+    const int threads = 1024;  // 32 warps, each owning n_expert/32 experts
     const size_t smem = (size_t)npair * sizeof(int);
     static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
+    if (smem > 36 * 1024 && smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(moe_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
             set_error(e, "moe_group smem attribute");
