@@ -280,6 +280,13 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
                               int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+/* The same result from register-tiled kernels (scores, softmax rows, weighted
+ * sum of V: each output element still one in-order chain of unfused multiply
+ * and add, as `attend` in crates/llamd-cpu/src/lib.rs computes it).
+ * n_kv_max bounds pos+1 over the tile's tokens. Shapes the tiled kernels do
+ * not cover fall through to llamd_fwd_attention_tile. */
+void llamd_fwd_attention_prefill(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
+                                 int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok, int n_kv_max);
 
 #ifdef __cplusplus
 }

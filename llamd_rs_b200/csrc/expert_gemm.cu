@@ -149,53 +149,72 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
     __syncthreads();
 
     // ---- token tiles of 8, one warp each ----
+    // Per block b the warp copies its 8 tokens' 256 activation bytes into its own double buffer with
+    // coalesced 16-byte loads (rows padded to 68 words so the fragment reads are conflict-free).
+    constexpr int kTokStride = 68;  // words
+    uint32_t *s_b = reinterpret_cast<uint32_t *>(smem + (size_t)nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * nb * 4) +
+                    (size_t)warp * 2 * 8 * kTokStride;
     const int g4 = lane >> 2, q4 = lane & 3;
     const int m0 = g4, m1 = g4 + 8;
     const int n_tiles = (count + 7) >> 3;
     for (int tn = warp; tn < n_tiles; tn += kGemmThreads / 32) {
         const int n0 = tn * 8;
-        // the token whose bytes this lane feeds as the B operand, and the two tokens whose outputs it owns
-        const int pb = first + min(n0 + g4, count - 1);
+        // the two tokens whose outputs this lane owns
         const int pa0 = first + min(n0 + 2 * q4, count - 1), pa1 = first + min(n0 + 2 * q4 + 1, count - 1);
-        const long long ib = p.act_map ? p.act_map[pb] : pb;
         const long long ia0 = p.act_map ? p.act_map[pa0] : pa0, ia1 = p.act_map ? p.act_map[pa1] : pa1;
-        const uint32_t *bsrc = p.aq_rm + (size_t)ib * nb * 64 + q4;
+        // staging: lane l copies 16-byte chunk (l & 15) + 16*i of token (l >> 4) + 2*i' ... 8 tokens x 16 chunks = 128 chunks, 4 per lane
+        const uint4 *src[4];
+        int dsto[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int chunk = lane + 32 * i;  // 0..127
+            const int tok = chunk >> 4, c16 = chunk & 15;
+            const int pt = first + min(n0 + tok, count - 1);
+            const long long it = p.act_map ? p.act_map[pt] : pt;
+            src[i] = reinterpret_cast<const uint4 *>(p.aq_rm + (size_t)it * nb * 64) + c16;
+            dsto[i] = tok * kTokStride + c16 * 4;
+        }
         float sums[4][8];
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
             for (int r = 0; r < 8; r++) sums[i][r] = 0.0f;
-        uint32_t bw[16];
+        uint4 st[4];
 #pragma unroll
-        for (int r = 0; r < 8; r++) {
-            bw[2 * r] = __ldg(bsrc + r * 8);
-            bw[2 * r + 1] = __ldg(bsrc + r * 8 + 4);
-        }
+        for (int i = 0; i < 4; i++) st[i] = __ldg(src[i]);
         for (int b = 0; b < nb; b++) {
-            uint32_t cur[16];
+            uint32_t *buf = s_b + (b & 1) * 8 * kTokStride;
 #pragma unroll
-            for (int i = 0; i < 16; i++) cur[i] = bw[i];
+            for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(buf + dsto[i]) = st[i];
+            __syncwarp();
             if (b + 1 < nb) {
-                const uint32_t *nx = bsrc + (size_t)(b + 1) * 64;
 #pragma unroll
-                for (int r = 0; r < 8; r++) {
-                    bw[2 * r] = __ldg(nx + r * 8);
-                    bw[2 * r + 1] = __ldg(nx + r * 8 + 4);
-                }
+                for (int i = 0; i < 4; i++) st[i] = __ldg(src[i] + (size_t)(b + 1) * 16);
             }
             const float a0 = __ldg(p.ad + ia0 * nb + b), a1 = __ldg(p.ad + ia1 * nb + b);
             const float d0 = s_d[m0 * nb + b], d1 = s_d[m1 * nb + b];
             const float dsc[4] = {__fmul_rn(d0, a0), __fmul_rn(d0, a1), __fmul_rn(d1, a0), __fmul_rn(d1, a1)};
             const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + lane;
+            const uint32_t *bt = buf + g4 * kTokStride + q4;
 #pragma unroll
             for (int r = 0; r < 8; r++) {
                 const uint4 ah = fr[(r * 2 + 0) * 32], al = fr[(r * 2 + 1) * 32];
+                const uint32_t b0 = bt[r * 8], b1 = bt[r * 8 + 4];
                 int ch[4], cl[4];
-                mma_s8(ch, ah, cur[2 * r], cur[2 * r + 1]);
-                mma_s8(cl, al, cur[2 * r], cur[2 * r + 1]);
+                mma_s8(ch, ah, b0, b1);
+                mma_s8(cl, al, b0, b1);
 #pragma unroll
-                for (int i = 0; i < 4; i++) sums[i][r] = __fadd_rn(sums[i][r], __fmul_rn(dsc[i], (float)(ch[i] * 64 + cl[i])));
+                for (int i = 0; i < 4; i++) {
+                    // (float)(64*hi + lo) without the slow int->float pipe: |hi|, |lo| < 2^22, so adding them to
+                    // 1.5*2^23 as integers and subtracting the constant as floats converts exactly; 64*fh + fl is
+                    // exact too because the sum (|aux| < 2^24) is representable.
+                    const float fh = __fsub_rn(__int_as_float(0x4B400000 + ch[i]), 12582912.0f);
+                    const float fl = __fsub_rn(__int_as_float(0x4B400000 + cl[i]), 12582912.0f);
+                    const float aux = __fmaf_rn(fh, 64.0f, fl);
+                    sums[i][r] = __fadd_rn(sums[i][r], __fmul_rn(dsc[i], aux));
+                }
             }
+            __syncwarp();
         }
         // y = ((((((s0+s1)+s2)+s3)+s4)+s5)+s6)+s7, then scatter
         float tot[4];
@@ -225,7 +244,7 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
 using namespace llamd;
 
 static void gemm_launch(GemmParams &p, int n_groups) {
-    const size_t smem = (size_t)p.nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * p.nb * 4;
+    const size_t smem = (size_t)p.nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * p.nb * 4 + (size_t)(kGemmThreads / 32) * 2 * 8 * 68 * 4;
     if (p.nb < 1 || smem > 200 * 1024) {
         set_error_msg("q6k gemm: blocks per row must be 1..24");
         return;

@@ -31,6 +31,8 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int ntok);
+void llamd_fwd_attention_prefill(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
+                                 int hd, const int32_t *meta, int max_kv, int ntok, int n_kv_max);
 void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq);
 void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
                                       int rows, int n_used, int nseq);
@@ -120,6 +122,7 @@ struct Model {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_phase;
+    int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int prefill_gemm = 1;    // 1: integer tensor path (mma.sync) for the tile's matmuls; 0: dp4a, 8 tokens per weight pass
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
     int32_t *h_meta = nullptr;  // pinned
@@ -579,6 +582,10 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         m->use_graph = value;
         return 0;
     }
+    if (!strcmp(name, "prefill_attn")) {
+        m->prefill_attn = value;
+        return 0;
+    }
     if (!strcmp(name, "prefill_gemm")) {
         m->prefill_gemm = value;
         return 0;
@@ -644,7 +651,7 @@ static bool prefill_alloc(Model &m, int tile) {
               p.v.alloc(T * kvd * 4) && p.attn.alloc(T * qd * 4) && p.aq.alloc(T * max_act) && p.ad.alloc(T * (max_act / 256) * 4) &&
               p.aq2.alloc(T * nu * ffe) && p.ad2.alloc(T * nu * (ffe / 256) * 4) && p.ids.alloc(T * nu * 4) && p.w.alloc(T * nu * 4) &&
               p.logits.alloc(T * ne * 4) && p.counter.alloc(T * 4) && p.gate.alloc(T * nu * ffe * 4) && p.up.alloc(T * nu * ffe * 4) &&
-              p.down.alloc(T * nu * E * 4) && p.scores.alloc(T * hp.n_head * (size_t)m.max_kv * 4) && p.meta.alloc(T * 8) &&
+              p.down.alloc(T * nu * E * 4) && p.scores.alloc(T * hp.n_head * (size_t)((m.max_kv + 3) & ~3) * 4) && p.meta.alloc(T * 8) &&
               p.gstart.alloc(ne * 4) && p.gcount.alloc(ne * 4) && p.ptoken.alloc(T * nu * 4) && p.pslot.alloc(T * nu * 4) &&
               p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && p.aq_rm.alloc(T * max_act) && p.aq2_rm.alloc(T * nu * ffe) &&
               cudaMallocHost((void **)&p.h_meta, T * 8) == cudaSuccess;
@@ -656,7 +663,7 @@ static bool prefill_alloc(Model &m, int tile) {
     return true;
 }
 
-static void queue_prefill_tile(Model &m, int T, bool last) {
+static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
     const llamd_hparams &hp = m.hp;
     Model::Prefill &p = m.pf;
     const int E = hp.n_embd, H = hp.n_head, HKV = hp.n_head_kv, hd = hp.head_dim;
@@ -684,8 +691,12 @@ static void queue_prefill_tile(Model &m, int T, bool last) {
         llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
                                           l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
                                           l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
-        llamd_fwd_attention_tile(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd,
-                                 meta, m.max_kv, T);
+        if (m.prefill_attn)
+            llamd_fwd_attention_prefill(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H,
+                                        HKV, hd, meta, (m.max_kv + 3) & ~3, T, n_kv_max);  // score rows padded to 16 bytes
+        else
+            llamd_fwd_attention_tile(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV,
+                                     hd, meta, m.max_kv, T);
         llamd_fwd_quantize(p.attn.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(), T * (qd / 256));
         if (gemm) {
             llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * (qd / 256));
@@ -770,7 +781,7 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
             set_error(cudaGetLastError(), "prefill meta H2D");
             return -1;
         }
-        queue_prefill_tile(*m, T, t0 + T >= n_tokens);
+        queue_prefill_tile(*m, T, base_pos + t0 + T, t0 + T >= n_tokens);
     }
     if (cudaMemcpyAsync(m->h_out, m->out_token.p, 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
     if (llamd_fwd_sync() != 0) return -1;

@@ -208,6 +208,10 @@ class CudaModel:
         """True (default): the prefill tile's matmuls run on the integer tensor path; False: dp4a, 8 tokens per pass."""
         self._L.llamd_model_set_option(self._h, b"prefill_gemm", int(on))
 
+    def set_prefill_attn(self, on: bool) -> None:
+        """True (default): a prefill tile's attention runs on the register-tiled kernels; False: the per-token ones."""
+        self._L.llamd_model_set_option(self._h, b"prefill_attn", int(on))
+
     def set_trace(self, on: bool) -> None:
         if self._L.llamd_model_set_option(self._h, b"trace", int(on)) != 0:
             raise backend.Other("trace buffers: " + self._err())

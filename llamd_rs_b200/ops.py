@@ -120,6 +120,31 @@ def attention(q, k, v, n_kv: int, n_head: int, n_head_kv: int, hd: int, scores: 
     return do.download_f32(q.size)
 
 
+def attention_prefill(q, k, v, positions, n_head: int, n_head_kv: int, hd: int, max_kv: int, tiled: bool = True):
+    """One query per tile token: token i (position positions[i]) attends rows 0..positions[i] of the ONE cache
+    k/v ([n_rows][n_head_kv*hd]). tiled=False runs the per-token kernels on the same inputs."""
+    q, k, v = _f32(q).ravel(), _f32(k).ravel(), _f32(v).ravel()
+    positions = np.ascontiguousarray(positions, dtype=np.int32).ravel()
+    ntok, kv_dim = positions.size, n_head_kv * hd
+    if n_head_kv == 0 or n_head % n_head_kv:
+        raise Malformed(f"attention: {n_head} query heads do not group into {n_head_kv} kv heads")
+    if q.size != ntok * n_head * hd or k.size != v.size or k.size % kv_dim or k.size // kv_dim > max_kv:
+        raise ShapeError("attention_prefill sizes")
+    if ntok == 0 or positions.min() < 0 or positions.max() >= k.size // kv_dim:
+        raise Malformed("attention_prefill: a position outside the cache")
+    meta = np.zeros((ntok, 2), dtype=np.int32)
+    meta[:, 1] = positions
+    dq, dk, dv, do = DevBuf.from_array(q), DevBuf.from_array(k), DevBuf.from_array(v), DevBuf(q.nbytes)
+    dm, ds = DevBuf.from_array(meta), DevBuf(ntok * n_head * max_kv * 4)
+    if tiled:
+        lib().llamd_fwd_attention_prefill(dq.ptr, dk.ptr, dv.ptr, do.ptr, ds.ptr, n_head, n_head_kv, hd, dm.ptr, max_kv, ntok,
+                                          int(positions.max()) + 1)
+    else:
+        lib().llamd_fwd_attention_tile(dq.ptr, dk.ptr, dv.ptr, do.ptr, ds.ptr, n_head, n_head_kv, hd, dm.ptr, max_kv, ntok)
+    backend.sync()
+    return do.download_f32(q.size).reshape(ntok, n_head * hd)
+
+
 def silu_mul_quant(gate, up):
     gate, up = _f32(gate).ravel(), _f32(up).ravel()
     if gate.size != up.size or gate.size % QK_K:

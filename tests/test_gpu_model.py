@@ -151,12 +151,14 @@ def test_prefill_equals_sequential_decode(tiny):
     kv_ref = [gm.read_kv(il, len(prompt)) for il in range(hp["n_layer"])]
     for tile, length in [(1, 1), (1, 5), (2, 5), (4, 4), (4, 5), (8, 7), (8, 8), (8, 9), (8, 17), (16, 33), (16, 37), (64, 37), (512, 37)]:
         gm.prefill_tile = tile
-        for gemm in (True, False):  # integer tensor path and dp4a path
+        for gemm, attn in ((True, True), (False, True), (True, False)):  # integer tensor path / dp4a; tiled / per-token attention
             gm.set_prefill_gemm(gemm)
+            gm.set_prefill_attn(attn)
             got = gm.prefill(prompt[:length], 0)
-            assert got == seq_tok[length], f"tile {tile} length {length} gemm {gemm}"
+            assert got == seq_tok[length], f"tile {tile} length {length} gemm {gemm} attn {attn}"
             assert np.array_equal(gm.logits()[0].view(np.uint32), seq_logits[length].view(np.uint32)), f"tile {tile} length {length}: logits"
     gm.set_prefill_gemm(True)
+    gm.set_prefill_attn(True)
     for il in range(hp["n_layer"]):
         k, v = gm.read_kv(il, len(prompt))
         assert np.array_equal(k.view(np.uint32), kv_ref[il][0].view(np.uint32)) and np.array_equal(v.view(np.uint32), kv_ref[il][1].view(np.uint32))

@@ -92,6 +92,35 @@ def test_attention_matches(ops, orc, synth, n_kv):
     assert bit_equal(split, got), "the split-over-CTAs variant keeps every sum in order"
 
 
+@pytest.mark.parametrize("n_head,n_head_kv,hd,base,ntok,max_kv", [
+    (8, 2, 128, 0, 70, 128),      # ragged token and position tiles, first tile of a prompt
+    (4, 2, 64, 37, 33, 96),       # a later tile: 37 positions of context before it
+    (4, 1, 128, 100, 1, 104),     # a single token with context
+    (4, 4, 64, 0, 96, 100),       # no grouping
+    (4, 2, 96, 0, 9, 16),         # a head_dim the tiled kernels do not cover: falls through
+    (4, 2, 64, 0, 9, 18),         # max_kv not a multiple of 4: falls through
+])
+def test_attention_prefill_tile(ops, orc, synth, n_head, n_head_kv, hd, base, ntok, max_kv):
+    """The register-tiled prefill attention equals the per-token kernels bit for bit and `attend` per token."""
+    n_rows = base + ntok
+    kv_dim = n_head_kv * hd
+    q = synth.normal_f32(ntok * n_head * hd, 5, "attp.q", hd, ntok).reshape(ntok, -1)
+    k = synth.normal_f32(n_rows * kv_dim, 5, "attp.k", hd, ntok)
+    v = synth.normal_f32(n_rows * kv_dim, 5, "attp.v", hd, ntok)
+    pos = np.arange(base, base + ntok, dtype=np.int32)
+    got = ops.attention_prefill(q, k, v, pos, n_head, n_head_kv, hd, max_kv)
+    per_token = ops.attention_prefill(q, k, v, pos, n_head, n_head_kv, hd, max_kv, tiled=False)
+    assert bit_equal(got, per_token)
+    for i in (0, ntok // 2, ntok - 1):
+        n_kv = int(pos[i]) + 1
+        want = orc.attend(q[i], k[: n_kv * kv_dim], v[: n_kv * kv_dim], n_kv, n_head, n_head_kv, hd)
+        assert max_dev(got[i], want) <= ATTENTION
+    # positions need not be consecutive or increasing
+    perm = np.random.default_rng(1).permutation(ntok)
+    got2 = ops.attention_prefill(q[perm], k, v, pos[perm], n_head, n_head_kv, hd, max_kv)
+    assert bit_equal(got2, got[perm])
+
+
 def test_attention_reference_kats(ops, orc):
     """crates/llamd-runtime/src/attention.rs:140-213"""
     out = ops.attention([0.5] * 4, [0.25] * 4, [7, 8, 9, 10], 1, 1, 1, 4)
