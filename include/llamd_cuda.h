@@ -280,6 +280,9 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
                               int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+/* llamd_fwd_matvec_f32 for the ntok tokens of a tile: out[t][row] = fold(-0.0, +) of w[row][i]*x[t][i], i
+ * ascending (crates/llamd-models/src/model.rs:253-263). w [rows][k] f32, x [ntok][k], out [ntok][rows]; k % 4 == 0. */
+void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int k, int rows, int ntok);
 /* The same result from register-tiled kernels (scores, softmax rows, weighted
  * sum of V: each output element still one in-order chain of unfused multiply
  * and add, as `attend` in crates/llamd-cpu/src/lib.rs computes it).

@@ -139,9 +139,13 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
                     }
                     // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1)
                     const int jw = 4 * m + i;
+                    // Lane L's 16 bytes sit in slot L ^ (L >> 3) ^ (b & 7): a warp here is 4 rows x 8 blocks writing the
+                    // same jw, and the swizzle spreads those over all eight 16-byte bank groups (the readers of one
+                    // fragment still touch 32 distinct slots).
                     const int L = (row_l & 7) * 4 + (jw & 3), q = (row_l >> 3) + 2 * (jw >> 2);
-                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + L)[q] = hi;
-                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 1) * 32 + L)[q] = lo;
+                    const int P = L ^ (L >> 3) ^ (b & 7);
+                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + P)[q] = hi;
+                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 1) * 32 + P)[q] = lo;
                 }
             }
         }
@@ -149,11 +153,12 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
     __syncthreads();
 
     // ---- token tiles of 8, one warp each ----
-    // Per block b the warp copies its 8 tokens' 256 activation bytes into its own double buffer with
-    // coalesced 16-byte loads (rows padded to 68 words so the fragment reads are conflict-free).
+    // Per block b the warp copies its 8 tokens' 256 activation bytes into its own buffer with coalesced
+    // 16-byte loads (rows padded to 68 words so the fragment reads are conflict-free); the next block's
+    // bytes wait in registers meanwhile.
     constexpr int kTokStride = 68;  // words
     uint32_t *s_b = reinterpret_cast<uint32_t *>(smem + (size_t)nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * nb * 4) +
-                    (size_t)warp * 2 * 8 * kTokStride;
+                    (size_t)warp * 8 * kTokStride;
     const int g4 = lane >> 2, q4 = lane & 3;
     const int m0 = g4, m1 = g4 + 8;
     const int n_tiles = (count + 7) >> 3;
@@ -183,7 +188,7 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
 #pragma unroll
         for (int i = 0; i < 4; i++) st[i] = __ldg(src[i]);
         for (int b = 0; b < nb; b++) {
-            uint32_t *buf = s_b + (b & 1) * 8 * kTokStride;
+            uint32_t *buf = s_b;
 #pragma unroll
             for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(buf + dsto[i]) = st[i];
             __syncwarp();
@@ -194,7 +199,7 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
             const float a0 = __ldg(p.ad + ia0 * nb + b), a1 = __ldg(p.ad + ia1 * nb + b);
             const float d0 = s_d[m0 * nb + b], d1 = s_d[m1 * nb + b];
             const float dsc[4] = {__fmul_rn(d0, a0), __fmul_rn(d0, a1), __fmul_rn(d1, a0), __fmul_rn(d1, a1)};
-            const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + lane;
+            const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + (lane ^ (lane >> 3) ^ (b & 7));
             const uint32_t *bt = buf + g4 * kTokStride + q4;
 #pragma unroll
             for (int r = 0; r < 8; r++) {
@@ -244,7 +249,7 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
 using namespace llamd;
 
 static void gemm_launch(GemmParams &p, int n_groups) {
-    const size_t smem = (size_t)p.nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * p.nb * 4 + (size_t)(kGemmThreads / 32) * 2 * 8 * 68 * 4;
+    const size_t smem = (size_t)p.nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * p.nb * 4 + (size_t)(kGemmThreads / 32) * 8 * 68 * 4;
     if (p.nb < 1 || smem > 200 * 1024) {
         set_error_msg("q6k gemm: blocks per row must be 1..24");
         return;

@@ -33,6 +33,7 @@ void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, 
                               int hd, const int32_t *meta, int max_kv, int ntok);
 void llamd_fwd_attention_prefill(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                                  int hd, const int32_t *meta, int max_kv, int ntok, int n_kv_max);
+void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int k, int rows, int ntok);
 void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq);
 void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
                                       int rows, int n_used, int nseq);
@@ -708,8 +709,13 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
         }
         llamd_fwd_add_rms_norm_quant(x, p.xb2.as<float>(), x, l.ffn_norm.as<float>(), p.xb.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(),
                                      E, hp.rms_eps, T);
-        llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), p.xb.as<float>(), E, ne, nu, p.logits.as<float>(), p.ids.as<int32_t>(),
-                                p.w.as<float>(), nullptr, p.counter.as<unsigned int>(), T);
+        if (m.prefill_attn && T > 1) {
+            llamd_fwd_matmul_f32_tokens(l.ffn_gate_inp.as<float>(), p.xb.as<float>(), p.logits.as<float>(), E, ne, T);
+            llamd_fwd_router(p.logits.as<float>(), ne, nu, p.ids.as<int32_t>(), p.w.as<float>(), nullptr, T);
+        } else {
+            llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), p.xb.as<float>(), E, ne, nu, p.logits.as<float>(), p.ids.as<int32_t>(),
+                                    p.w.as<float>(), nullptr, p.counter.as<unsigned int>(), T);
+        }
         // the expert scatter plan: (token, slot) pairs sorted by expert
         llamd_fwd_moe_group_work(p.ids.as<int32_t>(), ne, nu, T, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
                                  p.pslot.as<int32_t>(), p.work.as<int32_t>(), p.n_work.as<int32_t>());

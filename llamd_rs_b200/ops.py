@@ -211,6 +211,19 @@ def matvec_f32(w, x):
     return do.download_f32(x2.shape[0] * rows).reshape(x2.shape[0], rows)
 
 
+def matmul_f32_tokens(w, x):
+    """The f32 matvec for every token of a tile in one launch: w [rows][k], x [ntok][k] -> [ntok][rows]."""
+    w, x = _f32(w), _f32(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, k = w.shape
+    if x2.shape[1] != k or k % 4:
+        raise ShapeError("matmul_f32_tokens sizes")
+    dw_, dx, do = DevBuf.from_array(w), DevBuf.from_array(x2), DevBuf(x2.shape[0] * rows * 4)
+    lib().llamd_fwd_matmul_f32_tokens(dw_.ptr, dx.ptr, do.ptr, k, rows, x2.shape[0])
+    backend.sync()
+    return do.download_f32(x2.shape[0] * rows).reshape(x2.shape[0], rows)
+
+
 def moe_combine_add(down, weights, residual):
     """down [nseq][n_used][n_embd], weights [nseq][n_used], residual [nseq][n_embd] or None."""
     down, weights = _f32(down), _f32(weights)

@@ -186,6 +186,18 @@ def test_router_matvec_logits_are_bit_exact(ops, orc, synth):
     assert bit_equal(ops.matvec_f32(w, x), np.stack([orc.matvec_dequant(orc.F32, w, x[s], k, ne) for s in range(3)]))
 
 
+@pytest.mark.parametrize("rows,k,ntok", [(128, 2048, 37), (8, 256, 1), (50, 100, 19), (33, 68, 16)])
+def test_matmul_f32_tokens(ops, orc, synth, rows, k, ntok):
+    """The tile form of the f32 matvec: every output is the same -0.0-seeded left-to-right sum."""
+    w = synth.normal_f32(rows * k, 5, "mm.w", rows, k, std=0.02).reshape(rows, k)
+    x = synth.normal_f32(ntok * k, 5, "mm.x", rows, k).reshape(ntok, k)
+    got = ops.matmul_f32_tokens(w, x)
+    want = np.stack([orc.matvec_dequant(orc.F32, w, x[t], k, rows) for t in range(ntok)])
+    assert bit_equal(got, want)
+    z = ops.matmul_f32_tokens(-np.abs(w), np.zeros_like(x))
+    assert np.all(np.signbit(z)), "an all -0.0 sum keeps its sign: no padding term enters a chain"
+
+
 def test_silu_mul_and_quant(ops, orc, synth):
     g = synth.normal_f32(8 * 768, 6, "g") * np.float32(3.0)
     u = synth.normal_f32(8 * 768, 6, "u")
