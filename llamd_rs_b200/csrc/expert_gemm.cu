@@ -17,17 +17,21 @@
 // This mirrors the role of crates/llamd-vulkan/shaders/q6k_expert_cm.comp
 // (cooperative-matrix s8 GEMM with f32 scaling per 16-K group).
 //
-// A CTA (4 warps) owns 16 weight rows of one matrix/expert for all of that
-// expert's tokens: it folds and splits its rows once into shared memory in MMA
-// fragment order (amortised over every token tile), then each warp walks token
-// tiles of 8. Activations are read as residue-major words (one 32-bit word =
-// the four bytes of one MMA k-quad) prepared by q8k_residue_major_kernel.
+// A CTA owns 16 weight rows of one matrix/expert at a time: it folds and splits
+// those rows once into shared memory in MMA fragment order, then each warp walks
+// token tiles of 8. Activations are read as residue-major words (one 32-bit word
+// = the four bytes of one MMA k-quad) prepared by q8k_residue_major_kernel.
+// Two launch shapes share the code:
+//   grouped  grid (row tiles, experts), 4 warps: one fold, then all of the expert's tokens;
+//   dense    a fixed number of resident CTAs (8 warps) split the (row tile, 64-token chunk)
+//            items evenly; a CTA folds a row tile once for the consecutive chunks it owns.
 #include "q6k_layout.cuh"
 
 namespace llamd {
 
-constexpr int kGemmThreads = 128;
 constexpr int kGemmRows = 16;
+constexpr int kTokStride = 68;  // words per staged token row: 16-byte aligned, conflict-free fragment reads
+constexpr int kChunkTiles = 8;  // token tiles per dense work item
 
 struct GemmParams {
     const uint8_t *w[3];  // tiled Q6_K; up to three matrices that share the activations
@@ -64,84 +68,77 @@ __global__ void q8k_residue_major_kernel(const int8_t *__restrict__ aq, uint32_t
             ((uint32_t)src[t32_element(r, j, 3)] << 24);
 }
 
-__global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    const int nb = p.nb;
-    // [nb][8 residues][hi, lo][32 lanes] x 16 B of A fragments, then [16 rows][nb] f32 of d
-    uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
-    float *s_d = reinterpret_cast<float *>(smem + (size_t)nb * 8 * 2 * 32 * 16);
-    pdl_trigger();
-    pdl_wait();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int j = 0;
-    if (p.njobs > 1 && (int)blockIdx.x >= p.tile_begin[1]) j = 1;
-    if (p.njobs > 2 && (int)blockIdx.x >= p.tile_begin[2]) j = 2;
-    const int rows = p.rows[j];
-    const int row0 = ((int)blockIdx.x - p.tile_begin[j]) * kGemmRows;
-    const int e = blockIdx.y;
-    const int first = p.gstart ? p.gstart[e] : 0;
-    const int count = p.gstart ? p.gcount[e] : p.n_tokens;
-    if (count <= 0) return;
-    const uint8_t *w = p.w[j];
-    const size_t unit0 = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)row0 * nb;
-
-    // ---- fold the scales into the weights, split hi/lo, store in fragment order ----
-    // One thread per (row, block): its 13 coalesced 16-byte loads fetch the whole block (as in the matvec
-    // kernel), all issued before any is used.
-    for (int rb = tid; rb < kGemmRows * nb; rb += kGemmThreads) {  // rb = row_local * nb + b
+// ---- fold the scales into the weights, split hi/lo, store in fragment order ----
+// One thread per (row, block, half): residues 4h..4h+3 of the block are 6 of its 12 code chunks, fetched with
+// coalesced 16-byte loads (consecutive threads = consecutive blocks of the tile), all issued before any is used.
+//
+// Two weights of one scale group are folded by ONE 32-bit multiply-add: with q = w + 32 in [0, 63],
+//     (q0 | q1 << 16) * sc + (C | C << 16),  C = 16384 - 32*sc
+// is, as an integer, sum_i (sc*(q_i - 32) + 16384) << 16i, and every term lies in [12288, 20480], so the two 16-bit
+// fields hold V_i = U_i + 16384 with no carry between them. 16384 is a multiple of 64*256: V & 63 = U & 63 and the
+// low byte of V >> 6 is the two's-complement byte of U >> 6.
+template <int THREADS>
+__device__ __forceinline__ void fold_row_tile(const uint8_t *__restrict__ w, size_t unit0, int live_rows, int nb, uint4 *s_frag, float *s_d,
+                                              int tid) {
+    const int n_units = kGemmRows * nb;
+    for (int it = tid; it < 2 * n_units; it += THREADS) {
+        const int half = it >= n_units ? 1 : 0;
+        const int rb = it - half * n_units;  // row_local * nb + b
         const int row_l = rb / nb, b = rb - row_l * nb;
-        const bool live = row0 + row_l < rows;
-        uint32_t S[48];
+        uint32_t S[24];
         uint4 scw = make_uint4(0, 0, 0, 0);
-        if (live) {
+        float dval = 0.0f;
+        if (row_l < live_rows) {
             const size_t unit = unit0 + rb;
             const uint8_t *tile = w + (unit >> 5) * kTileBytes;
             const int sl = (int)(unit & 31);
-            const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl;
+            const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl + half * 6 * 32;
 #pragma unroll
-            for (int c = 0; c < 12; c++) {
+            for (int c = 0; c < 6; c++) {
                 const uint4 v = __ldg(cp + c * 32);
                 S[4 * c + 0] = v.x; S[4 * c + 1] = v.y; S[4 * c + 2] = v.z; S[4 * c + 3] = v.w;
             }
             scw = __ldg(reinterpret_cast<const uint4 *>(tile + kTileScaleOff) + sl);
-            s_d[rb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl));
+            dval = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl));
         } else {
+            // a row past the matrix: codes of q = 32 (w = 0) so that the fold below yields hi = lo = 0
 #pragma unroll
-            for (int c = 0; c < 48; c++) S[c] = 0;
-            s_d[rb] = 0.0f;
+            for (int c = 0; c < 24; c++) S[c] = 0;
         }
-        int sc[16];
+        if (half == 0) s_d[rb] = dval;
+        uint32_t sc[16], crep[16];
         {
             const uint32_t ws[4] = {scw.x, scw.y, scw.z, scw.w};
 #pragma unroll
-            for (int i = 0; i < 16; i++) sc[i] = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+            for (int i = 0; i < 16; i++) {
+                const int v = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+                sc[i] = (uint32_t)v;
+                crep[i] = (uint32_t)(16384 - 32 * v) * 0x00010001u;
+            }
         }
 #pragma unroll
-        for (int r = 0; r < 8; r++) {
+        for (int rl = 0; rl < 4; rl++) {
+            const int r = 4 * half + rl;
 #pragma unroll
             for (int m = 0; m < 2; m++) {
-                const uint32_t s0 = S[6 * r + 3 * m], s1 = S[6 * r + 3 * m + 1], s2 = S[6 * r + 3 * m + 2];
-                uint32_t w4[4];
-                w4[0] = s0 & 0xFCFCFCFCu;
-                w4[1] = s1 & 0xFCFCFCFCu;
-                w4[2] = s2 & 0xFCFCFCFCu;
-                w4[3] = ((s0 << 6) & 0xC0C0C0C0u) | ((s1 << 4) & 0x30303030u) | ((s2 << 2) & 0x0C0C0C0Cu);
+                const uint32_t s0 = S[6 * rl + 3 * m], s1 = S[6 * rl + 3 * m + 1], s2 = S[6 * rl + 3 * m + 2];
+                // the stored byte is (q ^ 0x20) << 2; the fourth word's codes are the low bit pairs of the other three
+                uint32_t qb[4];
+                qb[0] = ((s0 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
+                qb[1] = ((s1 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
+                qb[2] = ((s2 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
+                qb[3] = (((s0 << 4) & 0x30303030u) | ((s1 << 2) & 0x0C0C0C0Cu) | (s2 & 0x03030303u)) ^ 0x20202020u;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    uint32_t hi = 0, lo = 0;
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        // byte k of word jw = 4m+i: weight (q-32) = the 6-bit field above bit 2; its group is 2*jw + (k>>1)
-                        const int wv = ((int)(w4[i] << (24 - 8 * k))) >> 26;
-                        const int u = wv * sc[2 * (4 * m + i) + (k >> 1)];  // 13 bits signed
-                        lo |= (uint32_t)(u & 63) << (8 * k);
-                        hi |= (uint32_t)((u >> 6) & 0xFF) << (8 * k);
-                    }
-                    // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1)
-                    const int jw = 4 * m + i;
-                    // Lane L's 16 bytes sit in slot L ^ (L >> 3) ^ (b & 7): a warp here is 4 rows x 8 blocks writing the
-                    // same jw, and the swizzle spreads those over all eight 16-byte bank groups (the readers of one
-                    // fragment still touch 32 distinct slots).
+                    const int jw = 4 * m + i;  // bytes 0,1 of word jw belong to scale group 2jw, bytes 2,3 to 2jw+1
+                    const uint32_t v01 = __byte_perm(qb[i], 0u, 0x4140) * sc[2 * jw] + crep[2 * jw];
+                    const uint32_t v23 = __byte_perm(qb[i], 0u, 0x4342) * sc[2 * jw + 1] + crep[2 * jw + 1];
+                    const uint32_t lo = __byte_perm(v01, v23, 0x6420) & 0x3F3F3F3Fu;
+                    const uint32_t hi = __byte_perm(v01 >> 6, v23 >> 6, 0x6420);
+                    // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1).
+                    // Lane L's 16 bytes sit in slot L ^ (L >> 3) ^ (b & 7): the threads of a warp here write the same jw
+                    // of neighbouring rows and blocks, and the swizzle spreads them over all eight 16-byte bank groups
+                    // (the readers of one fragment still touch 32 distinct slots).
                     const int L = (row_l & 7) * 4 + (jw & 3), q = (row_l >> 3) + 2 * (jw >> 2);
                     const int P = L ^ (L >> 3) ^ (b & 7);
                     reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + P)[q] = hi;
@@ -150,29 +147,28 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
             }
         }
     }
-    __syncthreads();
+}
 
-    // ---- token tiles of 8, one warp each ----
-    // Per block b the warp copies its 8 tokens' 256 activation bytes into its own buffer with coalesced
-    // 16-byte loads (rows padded to 68 words so the fragment reads are conflict-free); the next block's
-    // bytes wait in registers meanwhile.
-    constexpr int kTokStride = 68;  // words
-    uint32_t *s_b = reinterpret_cast<uint32_t *>(smem + (size_t)nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * nb * 4) +
-                    (size_t)warp * 8 * kTokStride;
+// ---- token tiles of 8 against the folded row tile ----
+// Warp `warp` of `nwarps` takes tiles tile_lo + warp, + nwarps, ... below tile_hi. Per block b the warp copies its
+// 8 tokens' 256 activation bytes into its own buffer with coalesced 16-byte loads; the next block's bytes wait in
+// registers meanwhile.
+__device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int row0, int rows, int first, int count, int tile_lo, int tile_hi,
+                                                const uint4 *s_frag, const float *s_d, uint32_t *s_b, int warp, int nwarps, int lane) {
+    const int nb = p.nb;
     const int g4 = lane >> 2, q4 = lane & 3;
     const int m0 = g4, m1 = g4 + 8;
-    const int n_tiles = (count + 7) >> 3;
-    for (int tn = warp; tn < n_tiles; tn += kGemmThreads / 32) {
+    for (int tn = tile_lo + warp; tn < tile_hi; tn += nwarps) {
         const int n0 = tn * 8;
         // the two tokens whose outputs this lane owns
         const int pa0 = first + min(n0 + 2 * q4, count - 1), pa1 = first + min(n0 + 2 * q4 + 1, count - 1);
         const long long ia0 = p.act_map ? p.act_map[pa0] : pa0, ia1 = p.act_map ? p.act_map[pa1] : pa1;
-        // staging: lane l copies 16-byte chunk (l & 15) + 16*i of token (l >> 4) + 2*i' ... 8 tokens x 16 chunks = 128 chunks, 4 per lane
+        // staging: 8 tokens x 16 pieces of 16 bytes = 128 pieces, four per lane
         const uint4 *src[4];
         int dsto[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int chunk = lane + 32 * i;  // 0..127
+            const int chunk = lane + 32 * i;
             const int tok = chunk >> 4, c16 = chunk & 15;
             const int pt = first + min(n0 + tok, count - 1);
             const long long it = p.act_map ? p.act_map[pt] : pt;
@@ -188,9 +184,8 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
 #pragma unroll
         for (int i = 0; i < 4; i++) st[i] = __ldg(src[i]);
         for (int b = 0; b < nb; b++) {
-            uint32_t *buf = s_b;
 #pragma unroll
-            for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(buf + dsto[i]) = st[i];
+            for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(s_b + dsto[i]) = st[i];
             __syncwarp();
             if (b + 1 < nb) {
 #pragma unroll
@@ -200,7 +195,7 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
             const float d0 = s_d[m0 * nb + b], d1 = s_d[m1 * nb + b];
             const float dsc[4] = {__fmul_rn(d0, a0), __fmul_rn(d0, a1), __fmul_rn(d1, a0), __fmul_rn(d1, a1)};
             const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + (lane ^ (lane >> 3) ^ (b & 7));
-            const uint32_t *bt = buf + g4 * kTokStride + q4;
+            const uint32_t *bt = s_b + g4 * kTokStride + q4;
 #pragma unroll
             for (int r = 0; r < 8; r++) {
                 const uint4 ah = fr[(r * 2 + 0) * 32], al = fr[(r * 2 + 1) * 32];
@@ -244,31 +239,121 @@ __global__ void __launch_bounds__(kGemmThreads) q6k_gemm_kernel(const GemmParams
     }
 }
 
+// Shared memory: [nb][8 residues][hi, lo][32 lanes] x 16 B of A fragments, [16 rows][nb] f32 of d, one staging
+// buffer of 8 x kTokStride words per warp.
+__host__ __device__ inline size_t gemm_smem_bytes(int nb, int threads) {
+    return (size_t)nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * nb * 4 + (size_t)(threads / 32) * 8 * kTokStride * 4;
+}
+
+__device__ __forceinline__ int job_of_tile(const GemmParams &p, int rt) {
+    int j = 0;
+    if (p.njobs > 1 && rt >= p.tile_begin[1]) j = 1;
+    if (p.njobs > 2 && rt >= p.tile_begin[2]) j = 2;
+    return j;
+}
+
+// grid (row tiles of all jobs, groups)
+__global__ void __launch_bounds__(128) q6k_gemm_grouped_kernel(const GemmParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int nb = p.nb;
+    uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)nb * 8 * 2 * 32 * 16);
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int j = job_of_tile(p, blockIdx.x);
+    const int rows = p.rows[j];
+    const int row0 = ((int)blockIdx.x - p.tile_begin[j]) * kGemmRows;
+    const int e = blockIdx.y;
+    const int first = p.gstart ? p.gstart[e] : 0;
+    const int count = p.gstart ? p.gcount[e] : p.n_tokens;
+    if (count <= 0) return;
+    const size_t unit0 = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)row0 * nb;
+    fold_row_tile<128>(p.w[j], unit0, rows - row0, nb, s_frag, s_d, tid);
+    __syncthreads();
+    uint32_t *s_b = reinterpret_cast<uint32_t *>(s_d + kGemmRows * nb) + (size_t)warp * 8 * kTokStride;
+    mma_token_tiles(p, j, row0, rows, first, count, 0, (count + 7) >> 3, s_frag, s_d, s_b, warp, 4, lane);
+}
+
+// One group of n_tokens tokens; gridDim.x resident CTAs share the (row tile, chunk of kChunkTiles token tiles) items,
+// CTA c taking the contiguous range [c*items/grid, (c+1)*items/grid) in row-tile-major order.
+__global__ void __launch_bounds__(256) q6k_gemm_dense_kernel(const GemmParams p, int total_row_tiles) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int nb = p.nb;
+    uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)nb * 8 * 2 * 32 * 16);
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t *s_b = reinterpret_cast<uint32_t *>(s_d + kGemmRows * nb) + (size_t)warp * 8 * kTokStride;
+    const int n_tiles = (p.n_tokens + 7) >> 3;
+    const int n_chunks = (n_tiles + kChunkTiles - 1) / kChunkTiles;
+    const long long items = (long long)total_row_tiles * n_chunks;
+    const long long it_lo = items * blockIdx.x / gridDim.x, it_hi = items * (blockIdx.x + 1) / gridDim.x;
+    int cur_rt = -1, j = 0, row0 = 0;
+    for (long long it = it_lo; it < it_hi; it++) {
+        const int rt = (int)(it / n_chunks), ch = (int)(it - (long long)rt * n_chunks);
+        if (rt != cur_rt) {
+            __syncthreads();  // every warp is done with the previous row tile's fragments
+            cur_rt = rt;
+            j = job_of_tile(p, rt);
+            row0 = (rt - p.tile_begin[j]) * kGemmRows;
+            fold_row_tile<256>(p.w[j], (size_t)row0 * nb, p.rows[j] - row0, nb, s_frag, s_d, tid);
+            __syncthreads();
+        }
+        mma_token_tiles(p, j, row0, p.rows[j], 0, p.n_tokens, ch * kChunkTiles, min(n_tiles, (ch + 1) * kChunkTiles), s_frag, s_d, s_b, warp, 8,
+                        lane);
+    }
+}
+
 }  // namespace llamd
 
 using namespace llamd;
 
 static void gemm_launch(GemmParams &p, int n_groups) {
-    const size_t smem = (size_t)p.nb * 8 * 2 * 32 * 16 + (size_t)kGemmRows * p.nb * 4 + (size_t)(kGemmThreads / 32) * 8 * 68 * 4;
-    if (p.nb < 1 || smem > 200 * 1024) {
+    const int threads = n_groups > 1 || p.gstart ? 128 : 256;
+    const size_t smem = gemm_smem_bytes(p.nb, threads);
+    if (p.nb < 1 || smem > 220 * 1024) {
         set_error_msg("q6k gemm: blocks per row must be 1..24");
         return;
-    }
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaFuncSetAttribute(q6k_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured = smem;
     }
     int tiles = 0;
     for (int i = 0; i < p.njobs; i++) {
         p.tile_begin[i] = tiles;
         tiles += (p.rows[i] + kGemmRows - 1) / kGemmRows;
     }
-    if (n_groups > 65535) {
-        set_error_msg("q6k gemm: too many groups");
+    if (threads == 128) {
+        static size_t configured = 0;
+        if (smem > 48 * 1024 && smem > configured) {
+            cudaFuncSetAttribute(q6k_gemm_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured = smem;
+        }
+        if (n_groups > 65535) {
+            set_error_msg("q6k gemm: too many groups");
+            return;
+        }
+        launch_k("q6k_gemm_grouped", q6k_gemm_grouped_kernel, dim3(tiles, n_groups), dim3(128), smem, p);
         return;
     }
-    launch_k("q6k_gemm", q6k_gemm_kernel, dim3(tiles, n_groups), dim3(kGemmThreads), smem, p);
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaFuncSetAttribute(q6k_gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = smem;
+    }
+    // as many CTAs as stay resident at once (per shared-memory size: cached)
+    static int cached_nb = -1, cached_slots = 0;
+    if (cached_nb != p.nb) {
+        int dev = 0, sms = 0, per_sm = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, q6k_gemm_dense_kernel, 256, smem);
+        cached_slots = sms * (per_sm > 0 ? per_sm : 1);
+        cached_nb = p.nb;
+    }
+    const int n_tiles = (p.n_tokens + 7) / 8, n_chunks = (n_tiles + kChunkTiles - 1) / kChunkTiles;
+    const long long items = (long long)tiles * n_chunks;
+    const int grid = (int)(items < cached_slots ? items : cached_slots);
+    launch_k("q6k_gemm_dense", q6k_gemm_dense_kernel, dim3(grid), dim3(256), smem, p, tiles);
 }
 
 extern "C" {
