@@ -47,7 +47,16 @@ struct GemmParams {
     const int32_t *gstart, *gcount, *act_map, *out_map;
     int n_tokens;
     long long expert_units;  // blocks between consecutive experts in w
+    int prefetch_ahead;      // grouped kernel: CTA i asks L2 for the weights of CTA i + prefetch_ahead (0: off)
 };
+
+// Ask L2 for the tiles that hold the 16 x nb blocks starting at block `unit0` (a hint: nothing waits on it).
+__device__ __forceinline__ void prefetch_row_tile(const uint8_t *w, size_t unit0, int live_rows, int nb) {
+    const size_t t_lo = unit0 >> 5, t_hi = (unit0 + (size_t)min(live_rows, kGemmRows) * nb - 1) >> 5;
+    const uint8_t *src = w + t_lo * kTileBytes;
+    const uint32_t bytes = (uint32_t)((t_hi - t_lo + 1) * kTileBytes);  // 6720 = 16 * 420
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
@@ -259,8 +268,18 @@ __global__ void __launch_bounds__(128) q6k_gemm_grouped_kernel(const GemmParams 
     uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
     float *s_d = reinterpret_cast<float *>(smem + (size_t)nb * 8 * 2 * 32 * 16);
     pdl_trigger();
-    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0 && p.prefetch_ahead > 0) {
+        // the weights of the CTA that will take this one's place on the SM start their trip from HBM now
+        const long long lin = (long long)blockIdx.y * gridDim.x + blockIdx.x + p.prefetch_ahead;
+        if (lin < (long long)gridDim.x * gridDim.y) {
+            const int px = (int)(lin % gridDim.x), pe = (int)(lin / gridDim.x);
+            const int pj = job_of_tile(p, px);
+            const int prow0 = (px - p.tile_begin[pj]) * kGemmRows;
+            prefetch_row_tile(p.w[pj], (size_t)pe * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)prow0 * nb, p.rows[pj] - prow0, nb);
+        }
+    }
+    pdl_wait();
     const int j = job_of_tile(p, blockIdx.x);
     const int rows = p.rows[j];
     const int row0 = ((int)blockIdx.x - p.tile_begin[j]) * kGemmRows;
@@ -298,6 +317,11 @@ __global__ void __launch_bounds__(256) q6k_gemm_dense_kernel(const GemmParams p,
             cur_rt = rt;
             j = job_of_tile(p, rt);
             row0 = (rt - p.tile_begin[j]) * kGemmRows;
+            if (tid == 0 && (long long)(rt + 1) * n_chunks < it_hi) {  // this CTA's next row tile
+                const int nj = job_of_tile(p, rt + 1);
+                const int nrow0 = (rt + 1 - p.tile_begin[nj]) * kGemmRows;
+                prefetch_row_tile(p.w[nj], (size_t)nrow0 * nb, p.rows[nj] - nrow0, nb);
+            }
             fold_row_tile<256>(p.w[j], (size_t)row0 * nb, p.rows[j] - row0, nb, s_frag, s_d, tid);
             __syncthreads();
         }
@@ -332,6 +356,16 @@ static void gemm_launch(GemmParams &p, int n_groups) {
             set_error_msg("q6k gemm: too many groups");
             return;
         }
+        static int cached_nb = -1, cached_slots = 0;
+        if (cached_nb != p.nb) {
+            int dev = 0, sms = 0, per_sm = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, q6k_gemm_grouped_kernel, 128, smem);
+            cached_slots = sms * (per_sm > 0 ? per_sm : 1);
+            cached_nb = p.nb;
+        }
+        p.prefetch_ahead = cached_slots;
         launch_k("q6k_gemm_grouped", q6k_gemm_grouped_kernel, dim3(tiles, n_groups), dim3(128), smem, p);
         return;
     }

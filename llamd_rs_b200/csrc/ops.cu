@@ -693,66 +693,105 @@ __global__ void argmax_final_kernel(const float *__restrict__ pv, const int32_t 
 }
 
 // ---- expert scatter plan (crates/llamd-vulkan/shaders/moe_group.comp:40-82) --
-// Counting sort of the (token, slot) pairs by expert. Thread e scans the pair
-// list, so pairs of one expert come out in ascending pair order (the shader
-// leaves that order unspecified; a fixed order makes runs reproducible).
+// Counting sort of the (token, slot) pairs by expert, stable: pairs of one
+// expert come out in ascending pair order (the shader leaves that order
+// unspecified; a fixed order makes runs reproducible).
+// One CTA of 32 warps. Warp w owns the contiguous pairs [w*chunk, (w+1)*chunk):
+// it histograms them by expert into its own row of s_hist, each pair keeping
+// its rank among the warp's earlier pairs of the same expert (match_any finds
+// the lanes of a 32-pair step that share an expert). A scan over (expert, warp)
+// turns the counts into output positions.
 // Also emits the work list the expert-major matvec walks: entries of up to 8
 // pairs of one expert, (expert, first, count), and their number.
-__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, int npair, int n_used, int32_t *__restrict__ gstart,
-                                 int32_t *__restrict__ gcount, int32_t *__restrict__ ptoken, int32_t *__restrict__ pslot,
-                                 int32_t *__restrict__ work, int32_t *__restrict__ n_work) {
-    extern __shared__ int s_ids[];
+constexpr int kGroupMaxPerLane = 40;  // pairs per lane: 32 warps x 32 lanes x 40 = 40960 pairs
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, int npair, int n_used,
+                                                         int32_t *__restrict__ gstart, int32_t *__restrict__ gcount,
+                                                         int32_t *__restrict__ ptoken, int32_t *__restrict__ pslot, int32_t *__restrict__ work,
+                                                         int32_t *__restrict__ n_work) {
+    extern __shared__ int s_hist[];  // [32 warps][n_expert]
     __shared__ int s_count[1024];
     __shared__ int s_start[1024];
     __shared__ int s_wstart[1024];
+    __shared__ int s_warp_tot[32], s_warp_wtot[32];
     pdl_trigger();
     pdl_wait();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    for (int p = tid; p < npair; p += blockDim.x) s_ids[p] = ids[p];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < 32 * n_expert; i += 1024) s_hist[i] = 0;
     __syncthreads();
-    // A warp owns experts warp, warp+nwarps, ...: its lanes look at 32 pairs at a time, and the ballot keeps
-    // the pairs of an expert in ascending pair order.
-    for (int e = warp; e < n_expert; e += nwarps) {
-        int count = 0;
-        for (int p0 = 0; p0 < npair; p0 += 32) {
-            const int p = p0 + lane;
-            count += __popc(__ballot_sync(0xffffffffu, p < npair && s_ids[p] == e));
+    const int chunk = ((npair + 32 * 32 - 1) / (32 * 32)) * 32;  // pairs per warp, a multiple of 32
+    const int steps = chunk / 32;
+    int *hist = s_hist + warp * n_expert;
+    int my_rank[kGroupMaxPerLane];  // rank << 10 | expert
+#pragma unroll
+    for (int s = 0; s < kGroupMaxPerLane; s++) {
+        if (s < steps) {
+            const int p = warp * chunk + s * 32 + lane;
+            const bool live = p < npair;
+            const int e = live ? ids[p] : -1 - lane;  // dead lanes match nobody
+            const unsigned same = __match_any_sync(0xffffffffu, e);
+            const int before = __popc(same & ((1u << lane) - 1u));
+            int base = 0;
+            if (live) base = hist[e];
+            __syncwarp();
+            if (live && before == 0) hist[e] = base + __popc(same);
+            __syncwarp();
+            my_rank[s] = ((base + before) << 10) | (e & 1023);
         }
-        if (lane == 0) s_count[e] = count;
     }
     __syncthreads();
-    if (tid == 0) {
-        int run = 0, wrun = 0;
-        for (int i = 0; i < n_expert; i++) {
-            const int c = s_count[i];
-            s_start[i] = run;
-            s_wstart[i] = wrun;
-            run += c;
-            wrun += (c + 7) / 8;
+    // expert e: total, then its start among all experts, then each warp's first position
+    int total = 0;
+    for (int e = tid; e < n_expert; e += 1024) {  // n_expert <= 1024: at most one expert per thread
+        for (int w = 0; w < 32; w++) total += s_hist[w * n_expert + e];
+        s_count[e] = total;
+    }
+    int incl = total, wincl = (total + 7) / 8;
+    for (int off = 1; off < 32; off <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, incl, off), b = __shfl_up_sync(0xffffffffu, wincl, off);
+        if (lane >= off) {
+            incl += a;
+            wincl += b;
         }
-        if (n_work) *n_work = wrun;
+    }
+    if (lane == 31) {
+        s_warp_tot[warp] = incl;
+        s_warp_wtot[warp] = wincl;
     }
     __syncthreads();
-    for (int e = warp; e < n_expert; e += nwarps) {
-        const int start = s_start[e], count = s_count[e];
+    int run = 0, wrun = 0;
+    for (int w = 0; w < warp; w++) {
+        run += s_warp_tot[w];
+        wrun += s_warp_wtot[w];
+    }
+    if (tid < n_expert) {
+        const int start = run + incl - total, wstart = wrun + wincl - (total + 7) / 8;
+        s_start[tid] = start;
+        s_wstart[tid] = wstart;
         int at = start;
-        for (int p0 = 0; p0 < npair; p0 += 32) {
-            const int p = p0 + lane;
-            const bool mine = p < npair && s_ids[p] == e;
-            const unsigned mask = __ballot_sync(0xffffffffu, mine);
-            if (mine) {
-                const int dst = at + __popc(mask & ((1u << lane) - 1u));
+        for (int w = 0; w < 32; w++) {
+            const int c = s_hist[w * n_expert + tid];
+            s_hist[w * n_expert + tid] = at;
+            at += c;
+        }
+        gstart[tid] = start;
+        gcount[tid] = total;
+    }
+    if (tid == 1023 && n_work) *n_work = wrun + wincl;  // threads beyond n_expert carry zero totals
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < kGroupMaxPerLane; s++) {
+        if (s < steps) {
+            const int p = warp * chunk + s * 32 + lane;
+            if (p < npair) {
+                const int dst = hist[my_rank[s] & 1023] + (my_rank[s] >> 10);
                 ptoken[dst] = p / n_used;
                 pslot[dst] = p;
             }
-            at += __popc(mask);
         }
-        if (lane == 0) {
-            gstart[e] = start;
-            gcount[e] = count;
-        }
-        if (work) {
-            const int wi0 = s_wstart[e];
+    }
+    if (work) {
+        for (int e = warp; e < n_expert; e += 32) {
+            const int start = s_start[e], count = s_count[e], wi0 = s_wstart[e];
             for (int f = lane * 8; f < count; f += 256) {
                 const int wi = wi0 + f / 8;
                 work[3 * wi + 0] = e;
@@ -1014,12 +1053,12 @@ void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
                               int32_t *ptoken, int32_t *pslot, int32_t *work, int32_t *n_work) {
     const int npair = n_used * nseq;
-    if (n_expert < 1 || n_expert > 1024 || npair < 0 || (size_t)npair * 4 > 160 * 1024) {
+    if (n_expert < 1 || n_expert > 1024 || npair < 0 || npair > 32 * 32 * kGroupMaxPerLane) {
         set_error_msg("moe_group: n_expert 1..1024 and at most 40960 pairs per call");
         return;
     }
-    const int threads = 1024;  // 32 warps, each owning n_expert/32 experts
-    const size_t smem = (size_t)npair * sizeof(int);
+    const int threads = 1024;  // 32 warps, each owning a contiguous run of pairs
+    const size_t smem = (size_t)32 * n_expert * sizeof(int);
     static size_t configured = 0;
     if (smem > 36 * 1024 && smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(moe_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
