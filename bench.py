@@ -183,6 +183,8 @@ def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
 
     L = _lib()
     K, W = args.steps, args.warmup
+    # the library default (512) is the reference's; larger tiles fold each expert's weights for more tokens at once
+    m.prefill_tile = args.tile if args.tile > 0 else min(len(prompt), 2048)
     for _ in range(W):
         m.prefill(prompt, 0)
     backend.sync()
@@ -233,6 +235,7 @@ def main():
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
                     help="N > 1: replicas = one full model per GPU, no exchange; ep = experts sharded 128/N per GPU, "
                          "NCCL dispatch/combine per MoE layer (each rank still decodes its own sequence)")
+    ap.add_argument("--tile", type=int, default=0, help="prefill workload: tokens per prefill tile (0: min(prompt, 2048))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--batch-sweep", default="", help="(secondary) comma list of batch sizes: time forward_batch over that many "

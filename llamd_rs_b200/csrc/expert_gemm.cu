@@ -86,74 +86,104 @@ __global__ void q8k_residue_major_kernel(const int8_t *__restrict__ aq, uint32_t
 // is, as an integer, sum_i (sc*(q_i - 32) + 16384) << 16i, and every term lies in [12288, 20480], so the two 16-bit
 // fields hold V_i = U_i + 16384 with no carry between them. 16384 is a multiple of 64*256: V & 63 = U & 63 and the
 // low byte of V >> 6 is the two's-complement byte of U >> 6.
-template <int THREADS>
+struct FoldItem {
+    uint32_t S[24];  // six 16-byte code chunks: residues 4h..4h+3 of one block
+    uint4 scw;       // its 16 scales
+    float d;
+    int rb, half;    // row_local * nb + block, which half; rb < 0: nothing to do
+};
+
+__device__ __forceinline__ void fold_load(FoldItem &f, const uint8_t *__restrict__ w, size_t unit0, int live_rows, int nb, int it) {
+    const int n_units = kGemmRows * nb;
+    f.rb = -1;
+    if (it >= 2 * n_units) return;
+    f.half = it >= n_units ? 1 : 0;
+    f.rb = it - f.half * n_units;
+    f.scw = make_uint4(0, 0, 0, 0);
+    f.d = 0.0f;
+    if (f.rb / nb < live_rows) {
+        const size_t unit = unit0 + f.rb;
+        const uint8_t *tile = w + (unit >> 5) * kTileBytes;
+        const int sl = (int)(unit & 31);
+        const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl + f.half * 6 * 32;
+#pragma unroll
+        for (int c = 0; c < 6; c++) {
+            const uint4 v = __ldg(cp + c * 32);
+            f.S[4 * c + 0] = v.x; f.S[4 * c + 1] = v.y; f.S[4 * c + 2] = v.z; f.S[4 * c + 3] = v.w;
+        }
+        f.scw = __ldg(reinterpret_cast<const uint4 *>(tile + kTileScaleOff) + sl);
+        f.d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl));
+    } else {
+        // a row past the matrix: with zero scales the fold below yields hi = lo = 0 whatever the codes
+#pragma unroll
+        for (int c = 0; c < 24; c++) f.S[c] = 0;
+    }
+}
+
+__device__ __forceinline__ void fold_store(const FoldItem &f, int nb, uint4 *s_frag, float *s_d) {
+    if (f.rb < 0) return;
+    const int row_l = f.rb / nb, b = f.rb - row_l * nb;
+    if (f.half == 0) s_d[f.rb] = f.d;
+    uint32_t sc[16], crep[16];
+    {
+        const uint32_t ws[4] = {f.scw.x, f.scw.y, f.scw.z, f.scw.w};
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int v = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+            sc[i] = (uint32_t)v;
+            crep[i] = (uint32_t)(16384 - 32 * v) * 0x00010001u;
+        }
+    }
+#pragma unroll
+    for (int rl = 0; rl < 4; rl++) {
+        const int r = 4 * f.half + rl;
+#pragma unroll
+        for (int m = 0; m < 2; m++) {
+            const uint32_t s0 = f.S[6 * rl + 3 * m], s1 = f.S[6 * rl + 3 * m + 1], s2 = f.S[6 * rl + 3 * m + 2];
+            // the stored byte is (q ^ 0x20) << 2; the fourth word's codes are the low bit pairs of the other three
+            uint32_t qb[4];
+            qb[0] = ((s0 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
+            qb[1] = ((s1 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
+            qb[2] = ((s2 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
+            qb[3] = (((s0 << 4) & 0x30303030u) | ((s1 << 2) & 0x0C0C0C0Cu) | (s2 & 0x03030303u)) ^ 0x20202020u;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int jw = 4 * m + i;  // bytes 0,1 of word jw belong to scale group 2jw, bytes 2,3 to 2jw+1
+                const uint32_t v01 = __byte_perm(qb[i], 0u, 0x4140) * sc[2 * jw] + crep[2 * jw];
+                const uint32_t v23 = __byte_perm(qb[i], 0u, 0x4342) * sc[2 * jw + 1] + crep[2 * jw + 1];
+                const uint32_t lo = __byte_perm(v01, v23, 0x6420) & 0x3F3F3F3Fu;
+                const uint32_t hi = __byte_perm(v01 >> 6, v23 >> 6, 0x6420);
+                // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1).
+                // Lane L's 16 bytes sit in slot L ^ (L >> 3) ^ (b & 7): the threads of a warp here write the same jw
+                // of neighbouring rows and blocks, and the swizzle spreads them over all eight 16-byte bank groups
+                // (the readers of one fragment still touch 32 distinct slots).
+                const int L = (row_l & 7) * 4 + (jw & 3), q = (row_l >> 3) + 2 * (jw >> 2);
+                const int P = L ^ (L >> 3) ^ (b & 7);
+                reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + P)[q] = hi;
+                reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 1) * 32 + P)[q] = lo;
+            }
+        }
+    }
+}
+
+// HOIST: two items per thread and trip, the loads of both in flight before either is folded (more registers).
+template <int THREADS, bool HOIST>
 __device__ __forceinline__ void fold_row_tile(const uint8_t *__restrict__ w, size_t unit0, int live_rows, int nb, uint4 *s_frag, float *s_d,
                                               int tid) {
-    const int n_units = kGemmRows * nb;
-    for (int it = tid; it < 2 * n_units; it += THREADS) {
-        const int half = it >= n_units ? 1 : 0;
-        const int rb = it - half * n_units;  // row_local * nb + b
-        const int row_l = rb / nb, b = rb - row_l * nb;
-        uint32_t S[24];
-        uint4 scw = make_uint4(0, 0, 0, 0);
-        float dval = 0.0f;
-        if (row_l < live_rows) {
-            const size_t unit = unit0 + rb;
-            const uint8_t *tile = w + (unit >> 5) * kTileBytes;
-            const int sl = (int)(unit & 31);
-            const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl + half * 6 * 32;
-#pragma unroll
-            for (int c = 0; c < 6; c++) {
-                const uint4 v = __ldg(cp + c * 32);
-                S[4 * c + 0] = v.x; S[4 * c + 1] = v.y; S[4 * c + 2] = v.z; S[4 * c + 3] = v.w;
-            }
-            scw = __ldg(reinterpret_cast<const uint4 *>(tile + kTileScaleOff) + sl);
-            dval = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl));
-        } else {
-            // a row past the matrix: codes of q = 32 (w = 0) so that the fold below yields hi = lo = 0
-#pragma unroll
-            for (int c = 0; c < 24; c++) S[c] = 0;
+    const int n_items = 2 * kGemmRows * nb;
+    if (HOIST) {
+        for (int base = 0; base < n_items; base += 2 * THREADS) {
+            FoldItem fa, fb;
+            fold_load(fa, w, unit0, live_rows, nb, base + tid);
+            fold_load(fb, w, unit0, live_rows, nb, base + THREADS + tid);
+            fold_store(fa, nb, s_frag, s_d);
+            fold_store(fb, nb, s_frag, s_d);
         }
-        if (half == 0) s_d[rb] = dval;
-        uint32_t sc[16], crep[16];
-        {
-            const uint32_t ws[4] = {scw.x, scw.y, scw.z, scw.w};
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const int v = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
-                sc[i] = (uint32_t)v;
-                crep[i] = (uint32_t)(16384 - 32 * v) * 0x00010001u;
-            }
-        }
-#pragma unroll
-        for (int rl = 0; rl < 4; rl++) {
-            const int r = 4 * half + rl;
-#pragma unroll
-            for (int m = 0; m < 2; m++) {
-                const uint32_t s0 = S[6 * rl + 3 * m], s1 = S[6 * rl + 3 * m + 1], s2 = S[6 * rl + 3 * m + 2];
-                // the stored byte is (q ^ 0x20) << 2; the fourth word's codes are the low bit pairs of the other three
-                uint32_t qb[4];
-                qb[0] = ((s0 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
-                qb[1] = ((s1 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
-                qb[2] = ((s2 >> 2) & 0x3F3F3F3Fu) ^ 0x20202020u;
-                qb[3] = (((s0 << 4) & 0x30303030u) | ((s1 << 2) & 0x0C0C0C0Cu) | (s2 & 0x03030303u)) ^ 0x20202020u;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int jw = 4 * m + i;  // bytes 0,1 of word jw belong to scale group 2jw, bytes 2,3 to 2jw+1
-                    const uint32_t v01 = __byte_perm(qb[i], 0u, 0x4140) * sc[2 * jw] + crep[2 * jw];
-                    const uint32_t v23 = __byte_perm(qb[i], 0u, 0x4342) * sc[2 * jw + 1] + crep[2 * jw + 1];
-                    const uint32_t lo = __byte_perm(v01, v23, 0x6420) & 0x3F3F3F3Fu;
-                    const uint32_t hi = __byte_perm(v01 >> 6, v23 >> 6, 0x6420);
-                    // fragment word q of lane L: row = L/4 + 8(q&1), word jw = L%4 + 4(q>>1).
-                    // Lane L's 16 bytes sit in slot L ^ (L >> 3) ^ (b & 7): the threads of a warp here write the same jw
-                    // of neighbouring rows and blocks, and the swizzle spreads them over all eight 16-byte bank groups
-                    // (the readers of one fragment still touch 32 distinct slots).
-                    const int L = (row_l & 7) * 4 + (jw & 3), q = (row_l >> 3) + 2 * (jw >> 2);
-                    const int P = L ^ (L >> 3) ^ (b & 7);
-                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 0) * 32 + P)[q] = hi;
-                    reinterpret_cast<uint32_t *>(s_frag + ((size_t)(b * 8 + r) * 2 + 1) * 32 + P)[q] = lo;
-                }
-            }
+    } else {
+        for (int base = 0; base < n_items; base += THREADS) {
+            FoldItem fa;
+            fold_load(fa, w, unit0, live_rows, nb, base + tid);
+            fold_store(fa, nb, s_frag, s_d);
         }
     }
 }
@@ -192,6 +222,7 @@ __device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int 
         uint4 st[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) st[i] = __ldg(src[i]);
+        float a0n = __ldg(p.ad + ia0 * nb), a1n = __ldg(p.ad + ia1 * nb);
         for (int b = 0; b < nb; b++) {
 #pragma unroll
             for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(s_b + dsto[i]) = st[i];
@@ -200,7 +231,11 @@ __device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int 
 #pragma unroll
                 for (int i = 0; i < 4; i++) st[i] = __ldg(src[i] + (size_t)(b + 1) * 16);
             }
-            const float a0 = __ldg(p.ad + ia0 * nb + b), a1 = __ldg(p.ad + ia1 * nb + b);
+            const float a0 = a0n, a1 = a1n;
+            if (b + 1 < nb) {
+                a0n = __ldg(p.ad + ia0 * nb + b + 1);
+                a1n = __ldg(p.ad + ia1 * nb + b + 1);
+            }
             const float d0 = s_d[m0 * nb + b], d1 = s_d[m1 * nb + b];
             const float dsc[4] = {__fmul_rn(d0, a0), __fmul_rn(d0, a1), __fmul_rn(d1, a0), __fmul_rn(d1, a1)};
             const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + (lane ^ (lane >> 3) ^ (b & 7));
@@ -214,12 +249,18 @@ __device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int 
                 mma_s8(cl, al, b0, b1);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    // (float)(64*hi + lo) without the slow int->float pipe: |hi|, |lo| < 2^22, so adding them to
-                    // 1.5*2^23 as integers and subtracting the constant as floats converts exactly; 64*fh + fl is
-                    // exact too because the sum (|aux| < 2^24) is representable.
-                    const float fh = __fsub_rn(__int_as_float(0x4B400000 + ch[i]), 12582912.0f);
-                    const float fl = __fsub_rn(__int_as_float(0x4B400000 + cl[i]), 12582912.0f);
-                    const float aux = __fmaf_rn(fh, 64.0f, fl);
+                    // aux = 64*hi + lo as a float, exactly (|aux| < 2^24). Two routes share the work between pipes:
+                    // the int->float converter (a quarter-rate unit), and an arithmetic route for the fourth output:
+                    // |hi|, |lo| < 2^22, so adding them to 1.5*2^23 as integers and subtracting the constant as floats
+                    // converts each exactly, and 64*fh + fl is exact because the sum is representable.
+                    float aux;
+                    if (i < 3) {
+                        aux = (float)(ch[i] * 64 + cl[i]);
+                    } else {
+                        const float fh = __fsub_rn(__int_as_float(0x4B400000 + ch[i]), 12582912.0f);
+                        const float fl = __fsub_rn(__int_as_float(0x4B400000 + cl[i]), 12582912.0f);
+                        aux = __fmaf_rn(fh, 64.0f, fl);
+                    }
                     sums[i][r] = __fadd_rn(sums[i][r], __fmul_rn(dsc[i], aux));
                 }
             }
@@ -261,8 +302,10 @@ __device__ __forceinline__ int job_of_tile(const GemmParams &p, int rt) {
     return j;
 }
 
-// grid (row tiles of all jobs, groups)
-__global__ void __launch_bounds__(128) q6k_gemm_grouped_kernel(const GemmParams p) {
+// grid (row tiles of all jobs, groups). HOIST (long rows): three CTAs per SM fit anyway, spend registers on loads
+// in flight; short rows: keep registers low so that five CTAs fit.
+template <bool HOIST>
+__global__ void __launch_bounds__(128, HOIST ? 3 : 5) q6k_gemm_grouped_kernel(const GemmParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
     uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
@@ -288,7 +331,7 @@ __global__ void __launch_bounds__(128) q6k_gemm_grouped_kernel(const GemmParams 
     const int count = p.gstart ? p.gcount[e] : p.n_tokens;
     if (count <= 0) return;
     const size_t unit0 = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)row0 * nb;
-    fold_row_tile<128>(p.w[j], unit0, rows - row0, nb, s_frag, s_d, tid);
+    fold_row_tile<128, HOIST>(p.w[j], unit0, rows - row0, nb, s_frag, s_d, tid);
     __syncthreads();
     uint32_t *s_b = reinterpret_cast<uint32_t *>(s_d + kGemmRows * nb) + (size_t)warp * 8 * kTokStride;
     mma_token_tiles(p, j, row0, rows, first, count, 0, (count + 7) >> 3, s_frag, s_d, s_b, warp, 4, lane);
@@ -296,7 +339,7 @@ __global__ void __launch_bounds__(128) q6k_gemm_grouped_kernel(const GemmParams 
 
 // One group of n_tokens tokens; gridDim.x resident CTAs share the (row tile, chunk of kChunkTiles token tiles) items,
 // CTA c taking the contiguous range [c*items/grid, (c+1)*items/grid) in row-tile-major order.
-__global__ void __launch_bounds__(256) q6k_gemm_dense_kernel(const GemmParams p, int total_row_tiles) {
+__global__ void __launch_bounds__(256, 2) q6k_gemm_dense_kernel(const GemmParams p, int total_row_tiles) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
     uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
@@ -322,7 +365,7 @@ __global__ void __launch_bounds__(256) q6k_gemm_dense_kernel(const GemmParams p,
                 const int nrow0 = (rt + 1 - p.tile_begin[nj]) * kGemmRows;
                 prefetch_row_tile(p.w[nj], (size_t)nrow0 * nb, p.rows[nj] - nrow0, nb);
             }
-            fold_row_tile<256>(p.w[j], (size_t)row0 * nb, p.rows[j] - row0, nb, s_frag, s_d, tid);
+            fold_row_tile<256, false>(p.w[j], (size_t)row0 * nb, p.rows[j] - row0, nb, s_frag, s_d, tid);
             __syncthreads();
         }
         mma_token_tiles(p, j, row0, p.rows[j], 0, p.n_tokens, ch * kChunkTiles, min(n_tiles, (ch + 1) * kChunkTiles), s_frag, s_d, s_b, warp, 8,
@@ -347,26 +390,28 @@ static void gemm_launch(GemmParams &p, int n_groups) {
         tiles += (p.rows[i] + kGemmRows - 1) / kGemmRows;
     }
     if (threads == 128) {
-        static size_t configured = 0;
-        if (smem > 48 * 1024 && smem > configured) {
-            cudaFuncSetAttribute(q6k_gemm_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            configured = smem;
-        }
         if (n_groups > 65535) {
             set_error_msg("q6k gemm: too many groups");
             return;
+        }
+        const bool hoist = p.nb > 4;
+        auto kernel = hoist ? q6k_gemm_grouped_kernel<true> : q6k_gemm_grouped_kernel<false>;
+        static size_t configured[2] = {0, 0};
+        if (smem > 48 * 1024 && smem > configured[hoist]) {
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured[hoist] = smem;
         }
         static int cached_nb = -1, cached_slots = 0;
         if (cached_nb != p.nb) {
             int dev = 0, sms = 0, per_sm = 0;
             cudaGetDevice(&dev);
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, q6k_gemm_grouped_kernel, 128, smem);
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 128, smem);
             cached_slots = sms * (per_sm > 0 ? per_sm : 1);
             cached_nb = p.nb;
         }
         p.prefetch_ahead = cached_slots;
-        launch_k("q6k_gemm_grouped", q6k_gemm_grouped_kernel, dim3(tiles, n_groups), dim3(128), smem, p);
+        launch_k("q6k_gemm_grouped", kernel, dim3(tiles, n_groups), dim3(128), smem, p);
         return;
     }
     static size_t configured = 0;
