@@ -238,6 +238,7 @@ def main():
     ap.add_argument("--tile", type=int, default=0, help="prefill workload: tokens per prefill tile (0: min(prompt, 2048))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
+    ap.add_argument("--prefetch", action="store_true", help="(experiment) matvec launches ask L2 for the next matvec's weights; measured slightly slower")
     ap.add_argument("--batch-sweep", default="", help="(secondary) comma list of batch sizes: time forward_batch over that many "
                     "independent sequences (crates/llamd-runtime/src/device.rs:741-962) and print tok/s per batch size to stderr")
     ap.add_argument("--phases", action="store_true", help="(diagnostic) print the per-phase time of an un-graphed pass and exit")
@@ -270,6 +271,9 @@ def main():
     info = backend.device_info(local)
     ep = world > 1 and args.parallelism == "ep"
     if ep:
+        # NCCL's version banner goes to stdout, where the one JSON line lives
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         from llamd_rs_b200 import model as _M
 
         def _share(b):
@@ -293,6 +297,8 @@ def main():
         from llamd_rs_b200._lib import lib as _l
 
         _l().llamd_fwd_set_pdl(0)
+    if args.prefetch:
+        m.set_option("prefetch", 1)
 
     prompt = synth.token_ids(args.prompt, hp["n_vocab"], 0, "prompt", rank)
     if args.workload == "prefill":
@@ -421,7 +427,7 @@ def main():
                    "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU, NCCL all-gather dispatch + all-to-all combine per layer"
                                    if ep else f"replicas x{world}"),
                    "token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "arith": "exact (reference order)",
-                   "graph": not args.no_graph, "pdl": not args.no_pdl},
+                   "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch},
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(m.launches_per_pass()) * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -73,6 +73,37 @@ inline void launch_k(const char *what, void (*kernel)(KArgs...), dim3 grid, dim3
     launch_kc(PDL_OTHER, what, kernel, grid, block, smem, args...);
 }
 
+// What the next Q6_K matvec launch should ask L2 to fetch while it runs: the weights of the matvec that follows
+// it in the pass. A decode pass alternates short weight-streaming kernels with kernels that are bound by one long
+// chain of dependent adds and leave HBM idle; with the next weights already on their way, a matvec finds them in
+// L2 instead of starting its stream cold. The plan is a hint: nothing waits on it and it changes no result.
+struct PrefetchPlan {
+    const uint8_t *base[3];
+    unsigned long long bytes[3];  // multiples of 16; 0 = unused. With ids: bytes[0] is the size of ONE expert at base[0]
+    const int32_t *ids;           // expert ids on the device (read after the launch's dependency wait), or null
+    int n_ids, own_lo, own_hi;    // experts [own_lo, own_hi) are resident, stored from local index 0
+};
+extern PrefetchPlan g_next_prefetch;  // set by the model before a matvec launch; consumed and cleared by that launch
+
+// CTA `cta` of `n_cta` asks for its share of [base, base + bytes).
+__device__ __forceinline__ void l2_prefetch_slice(const uint8_t *base, unsigned long long bytes, int cta, int n_cta) {
+    unsigned long long slice = ((bytes / (unsigned long long)n_cta) + 15ull) & ~15ull;
+    if (slice == 0) slice = 16;
+    const unsigned long long off = slice * (unsigned long long)cta;
+    if (off >= bytes) return;
+    const unsigned long long n = bytes - off < slice ? bytes - off : slice;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"((uint32_t)n) : "memory");
+}
+__device__ __forceinline__ void prefetch_issue(const PrefetchPlan &pf, int cta, int n_cta) {
+    const int tid = threadIdx.x;
+    if (!pf.ids) {
+        if (tid < 3 && pf.bytes[tid]) l2_prefetch_slice(pf.base[tid], pf.bytes[tid], cta, n_cta);
+    } else if (tid < pf.n_ids) {
+        const int e = pf.ids[tid];
+        if (e >= pf.own_lo && e < pf.own_hi) l2_prefetch_slice(pf.base[0] + (unsigned long long)(e - pf.own_lo) * pf.bytes[0], pf.bytes[0], cta, n_cta);
+    }
+}
+
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.
 void *scratch(int slot, size_t bytes);

@@ -65,6 +65,7 @@ struct MatvecParams {
     //            (fuses crates/llamd-rocm/src/forward.rs:375 `quantize` into the matvec);
     //   ACT_SILU xf = gate, xu = up, f32 [index][k]: silu(gate)*up, then quantized (fuses :316 too).
     const float *xf, *xu;
+    PrefetchPlan pf;  // the weights of the matvec that follows this launch (a hint for L2)
 };
 
 enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2 };
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         __syncthreads();
     } else if (p.ids) {
         pdl_wait();  // the ids come from the router kernel
+        prefetch_issue(p.pf, blockIdx.x, gridDim.x);
         int e = p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
         if (e < p.own_lo || e >= p.own_hi) return;  // another GPU's expert
@@ -167,7 +169,11 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
 
     // Ungrouped: the weight loads above do not depend on the previous kernel and
     // are in flight while it finishes; the activations below do.
-    if (!MULTI && !p.ids) pdl_wait();
+    if (!MULTI && !p.ids) {
+        if (!p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
+        pdl_wait();
+        if (p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
+    }
     // ---- stage the activations ----------------------------------------
     // natural order bytes first ...
     if (ACT == ACT_Q8K) {
@@ -306,7 +312,10 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
         }
         configured = smem;
     }
-    launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI, ACT>, grid, dim3(kThreads), smem, p);
+    MatvecParams q = p;
+    q.pf = g_next_prefetch;
+    g_next_prefetch = PrefetchPlan{};
+    launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI, ACT>, grid, dim3(kThreads), smem, q);
 }
 
 // Build the launch. `rows[i]`/`w[i]`/`out[i]` describe up to three matrices

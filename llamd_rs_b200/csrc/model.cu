@@ -123,6 +123,7 @@ struct Model {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_phase;
+    int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int prefill_gemm = 1;    // 1: integer tensor path (mma.sync) for the tile's matmuls; 0: dp4a, 8 tokens per weight pass
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
@@ -186,6 +187,35 @@ bool upload_f32(Buf &dst, const void *host, size_t n) {
     return llamd_fwd_sync() == 0;
 }
 
+// ---- L2 prefetch plans (common.cuh: PrefetchPlan): set just before a matvec launch, naming what follows it ----
+static void plan_static(const Model &m, const Buf *a, const Buf *b = nullptr, const Buf *c = nullptr, size_t cap = 0) {
+    if (!m.prefetch) return;
+    PrefetchPlan pf = {};
+    const Buf *r[3] = {a, b, c};
+    for (int i = 0; i < 3; i++) {
+        if (!r[i] || !r[i]->p) continue;
+        size_t n = r[i]->bytes & ~(size_t)15;
+        if (cap && n > cap) n = cap;
+        pf.base[i] = (const uint8_t *)r[i]->p;
+        pf.bytes[i] = n;
+    }
+    g_next_prefetch = pf;
+}
+static void plan_experts(const Model &m, const Buf &w, const int32_t *ids, int n_ids) {
+    if (!m.prefetch || !w.p) return;
+    const int lo = m.ep_world > 1 ? m.own_lo : 0, hi = m.ep_world > 1 ? m.own_hi : m.hp.n_expert;
+    if (hi <= lo || n_ids > 256) return;
+    PrefetchPlan pf = {};
+    pf.base[0] = (const uint8_t *)w.p;
+    pf.bytes[0] = (w.bytes / (size_t)(hi - lo)) & ~(size_t)15;
+    pf.ids = ids;
+    pf.n_ids = n_ids;
+    pf.own_lo = lo;
+    pf.own_hi = hi;
+    g_next_prefetch = pf;
+}
+constexpr size_t kHeadPrefetchBytes = (size_t)48 << 20;  // of the 256 MB lm_head: what comfortably stays in L2
+
 // Queue one pass for `nseq` sequences. Does not synchronise.
 // The order is crates/llamd-runtime/src/device.rs:486-655 (itself the CPU
 // order of crates/llamd-runtime/src/layer.rs:85-203, 230-304).
@@ -217,6 +247,13 @@ void queue_token(Model &m, int nseq) {
             cudaMemcpyAsync(m.trace_x.as<float>() + (size_t)il * m.max_seq * E, x, (size_t)nseq * E * sizeof(float), cudaMemcpyDeviceToDevice,
                             stream());
     };
+    // what the down projection of layer il is followed by: the next layer's Q, K, V, or the head's first megabytes
+    auto plan_after_down = [&](int il) {
+        if (il + 1 < hp.n_layer)
+            plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v);
+        else
+            plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
+    };
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
         // Attention norm, f32 and Q8_K in one pass (Q, K and V read the same
@@ -230,6 +267,7 @@ void queue_token(Model &m, int nseq) {
             trace_x(il - 1);
         }
         mark(LLAMD_PH_ATTN_NORM);
+        plan_static(m, &l.attn_out);
         llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
                                   m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
         mark(LLAMD_PH_QKV);
@@ -244,6 +282,7 @@ void queue_token(Model &m, int nseq) {
         // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
         llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
         mark(LLAMD_PH_QUANT);
+        plan_static(m, &l.ffn_gate_inp);
         llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
         mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
@@ -259,10 +298,12 @@ void queue_token(Model &m, int nseq) {
             const int W = m.ep_world;
             llamd_fwd_ep_dispatch(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ids_all.as<int32_t>(),
                                   m.ad_all.as<float>(), m.aq_all.as<int8_t>(), nu, eb);
+            plan_experts(m, l.down_exps, m.ids_all.as<int32_t>(), W * nu);
             llamd_fwd_matvec_grouped_x2_owned(l.gate_exps.p, l.up_exps.p, m.ids_all.as<int32_t>(), m.aq_all.as<int8_t>(), m.ad_all.as<float>(),
                                               m.gate_all.as<float>(), m.up_all.as<float>(), eb, ffe, nu, W * nu, m.own_lo, m.own_hi);
             llamd_fwd_silu_mul_quant(m.gate_all.as<float>(), m.up_all.as<float>(), nullptr, m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
                                      W * nu * ffe);
+            plan_after_down(il);
             llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
                                               m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
             llamd_fwd_ep_combine(m.down_all.as<float>(), m.recv_all.as<float>(), m.expert_ids.as<int32_t>(), m.e_down.as<float>(), nu, E,
@@ -272,6 +313,7 @@ void queue_token(Model &m, int nseq) {
                                 cudaMemcpyDeviceToDevice, stream());
             continue;
         }
+        plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
         llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                           m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
         mark(LLAMD_PH_GATE_UP);
@@ -279,6 +321,7 @@ void queue_token(Model &m, int nseq) {
         llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                  nseq * nu * ffe);
         mark(LLAMD_PH_SILU);
+        plan_after_down(il);
         llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                           m.e_down.as<float>(), ffe / 256, E, nu, nseq);
         mark(LLAMD_PH_DOWN);
@@ -291,6 +334,7 @@ void queue_token(Model &m, int nseq) {
                                      m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
     trace_x(hp.n_layer - 1);
     mark(LLAMD_PH_ATTN_NORM);
+    plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v);  // the next token starts there
     llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
                            hp.n_vocab, nseq);
     mark(LLAMD_PH_LM_HEAD);
@@ -308,16 +352,25 @@ void queue_matvecs_only(Model &m, int nseq) {
     const llamd_hparams &hp = m.hp;
     const int E = hp.n_embd, kvd = hp.n_head_kv * hp.head_dim, qd = hp.n_head * hp.head_dim, nu = hp.n_expert_used, ffe = hp.n_ff_expert;
     const int eb = E / 256;
+    // the same prefetch plans as the full pass sets
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
+        plan_static(m, &l.attn_out);
         llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
                                   m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        plan_static(m, &l.ffn_gate_inp);
         llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
         llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                           m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+        if (il + 1 < hp.n_layer)
+            plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v);
+        else
+            plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
         llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                           m.e_down.as<float>(), ffe / 256, E, nu, nseq);
     }
+    plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v);
     llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
                            hp.n_vocab, nseq);
 }
@@ -581,6 +634,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!m || !name) return -1;
     if (!strcmp(name, "use_graph")) {
         m->use_graph = value;
+        return 0;
+    }
+    if (!strcmp(name, "prefetch")) {
+        if (m->prefetch != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->prefetch = value;
         return 0;
     }
     if (!strcmp(name, "prefill_attn")) {

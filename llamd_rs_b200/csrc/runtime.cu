@@ -10,6 +10,7 @@
 namespace llamd {
 
 unsigned long long g_launches = 0;
+PrefetchPlan g_next_prefetch = {};
 int g_pdl = 7;  // matvec, grouped matvec and router launches: measured best
 static cudaStream_t g_stream = nullptr;
 static int g_err = 0;

@@ -208,6 +208,11 @@ class CudaModel:
         """True (default): the prefill tile's matmuls run on the integer tensor path; False: dp4a, 8 tokens per pass."""
         self._L.llamd_model_set_option(self._h, b"prefill_gemm", int(on))
 
+    def set_option(self, name: str, value: int) -> None:
+        """llamd_model_set_option by name: use_graph, pdl, prefetch, trace, prefill_tile, prefill_gemm, prefill_attn."""
+        if self._L.llamd_model_set_option(self._h, name.encode(), int(value)) != 0:
+            raise backend.Malformed(f"set_option {name}={value}: " + self._err())
+
     def set_prefill_attn(self, on: bool) -> None:
         """True (default): a prefill tile's attention runs on the register-tiled kernels; False: the per-token ones."""
         self._L.llamd_model_set_option(self._h, b"prefill_attn", int(on))
