@@ -280,6 +280,25 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
                               int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+/* ---- expert parallelism (no counterpart in the reference, which has no multi-GPU path) ----
+ * After llamd_cuda_ep_init (llamd_cuda_model.h) this rank holds experts [own_lo, own_hi) of every expert tensor,
+ * stored from local index 0. The owned-range matvecs are llamd_fwd_matvec_grouped_x2 / _pa over n_slots flat
+ * slots (ids[n_slots], slot s reading activation s / n_used or its own): a slot whose expert is not owned is
+ * skipped and its output rows are left untouched.
+ * dispatch: all-gather of every rank's (ids[n_used], ad[blocks], aq[blocks*256]) into [world][...] buffers.
+ * combine: block t of send ([world][n_used][n_embd]) goes to rank t, block r of recv comes from rank r; then
+ * down[slot] = recv[owner(ids[slot])][slot]: the eight expert outputs in routing order, as on one GPU.
+ * Both enqueue NCCL calls on the library stream and may be captured into the graph. */
+void llamd_fwd_matvec_grouped_x2_owned(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                                       float *oa, float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo,
+                                       int own_hi);
+void llamd_fwd_matvec_grouped_pa_owned(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,
+                                       int blocks, int rows, int n_slots, int own_lo, int own_hi);
+void llamd_fwd_ep_dispatch(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *ids_all, float *ad_all,
+                           int8_t *aq_all, int n_used, int blocks);
+void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, float *down, int n_used, int n_embd,
+                          int n_expert);
+
 /* llamd_fwd_matvec_f32 for the ntok tokens of a tile: out[t][row] = fold(-0.0, +) of w[row][i]*x[t][i], i
  * ascending (crates/llamd-models/src/model.rs:253-263). w [rows][k] f32, x [ntok][k], out [ntok][rows]; k % 4 == 0. */
 void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int k, int rows, int ntok);

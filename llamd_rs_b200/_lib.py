@@ -108,6 +108,10 @@ SIGNATURES = {
     "llamd_fwd_expert_gemm": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_qk_norm_rope_store_tile": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32]),
     "llamd_fwd_attention_tile": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32]),
+    "llamd_fwd_matvec_grouped_x2_owned": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32]),
+    "llamd_fwd_matvec_grouped_pa_owned": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
+    "llamd_fwd_ep_dispatch": (None, [vp, vp, vp, vp, vp, vp, i32, i32]),
+    "llamd_fwd_ep_combine": (None, [vp, vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_matmul_f32_tokens": (None, [vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_attention_prefill": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32, i32]),
     "llamd_fwd_moe_group": (None, [vp, i32, i32, i32, vp, vp, vp, vp]),
