@@ -280,6 +280,20 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
                               int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+/* ---- the same matmuls at TOLERANCE level on tcgen05 (f16 tiles dequantized in shared memory, f32
+ * accumulators in TMEM, one accumulation over all of K). Outputs agree with llamd_fwd_gemm_tokens /
+ * llamd_fwd_expert_gemm within QUANTIZED_MATMUL = 1e-3 (crates/llamd-core/src/tolerance.rs:41-66), not bit for bit.
+ * act16: the activations as two f16 terms each, from llamd_fwd_act_f16_rm: blocks*256*4 bytes per index. max_count bounds the tokens of any one
+ * expert (the number of pairs always does). llamd_fwd_gemm_tc_status synchronises and returns 0 unless a wait
+ * inside a kernel ran out (outputs then incomplete). */
+void llamd_fwd_act_f16_rm(const int8_t *aq, const float *ad, void *act16, size_t nblocks);
+void llamd_fwd_gemm_tokens_tc(const void *w0, const void *w1, const void *w2, const void *act16, float *o0, float *o1,
+                              float *o2, int blocks, int rows0, int rows1, int rows2, int ntok);
+void llamd_fwd_expert_gemm_tc(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount,
+                              const int32_t *act_map, const int32_t *pslot, const void *act16, float *oa, float *ob,
+                              int blocks, int rows, int n_expert, int max_count);
+int llamd_fwd_gemm_tc_status(void);
+
 /* ---- expert parallelism (no counterpart in the reference, which has no multi-GPU path) ----
  * After llamd_cuda_ep_init (llamd_cuda_model.h) this rank holds experts [own_lo, own_hi) of every expert tensor,
  * stored from local index 0. The owned-range matvecs are llamd_fwd_matvec_grouped_x2 / _pa over n_slots flat

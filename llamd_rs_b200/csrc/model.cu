@@ -47,6 +47,13 @@ void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, fl
 int llamd_cuda_ep_rank(void);
 int llamd_cuda_ep_world(void);
 void llamd_fwd_q8k_residue_major(const int8_t *aq, void *aq_rm, size_t nblocks);
+void llamd_fwd_act_f16_rm(const int8_t *aq, const float *ad, void *act16, size_t nblocks);
+void llamd_fwd_gemm_tokens_tc(const void *w0, const void *w1, const void *w2, const void *act16, float *o0, float *o1, float *o2,
+                              int blocks, int rows0, int rows1, int rows2, int ntok);
+void llamd_fwd_expert_gemm_tc(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
+                              const int32_t *pslot, const void *act16, float *oa, float *ob, int blocks, int rows, int n_expert,
+                              int max_count);
+int llamd_fwd_gemm_tc_status(void);
 void llamd_fwd_gemm_tokens(const void *w0, const void *w1, const void *w2, const void *aq_rm, const float *ad, float *o0, float *o1,
                            float *o2, int blocks, int rows0, int rows1, int rows2, int ntok);
 void llamd_fwd_expert_gemm(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
@@ -112,7 +119,7 @@ struct Model {
         int tile = 0;
         Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, ids, w, logits, counter, gate, up, down, scores, meta;
         Buf gstart, gcount, ptoken, pslot, work, n_work;
-        Buf aq_rm, aq2_rm;  // residue-major copies of aq / aq2 for the tensor-path GEMM
+        Buf aq_rm, aq2_rm;  // the GEMMs' view of aq / aq2: residue-major bytes (integer path) or two f16 terms per element (tcgen05 path)
         int32_t *h_meta = nullptr;
     } pf;
     // expert parallelism (ep_world > 1): this rank holds experts [own_lo, own_hi)
@@ -125,7 +132,8 @@ struct Model {
     std::vector<int> prof_phase;
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
-    int prefill_gemm = 1;    // 1: integer tensor path (mma.sync) for the tile's matmuls; 0: dp4a, 8 tokens per weight pass
+    int prefill_gemm = 1;    // 1: integer tensor path (mma.sync), exact; 0: dp4a, 8 tokens per weight pass, exact;
+                             // 2: tcgen05 on f16 pairs, tolerance level (gemm_tc.cu)
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
     int32_t *h_meta = nullptr;  // pinned
     int32_t *h_out = nullptr;   // pinned
@@ -712,7 +720,7 @@ static bool prefill_alloc(Model &m, int tile) {
               p.logits.alloc(T * ne * 4) && p.counter.alloc(T * 4) && p.gate.alloc(T * nu * ffe * 4) && p.up.alloc(T * nu * ffe * 4) &&
               p.down.alloc(T * nu * E * 4) && p.scores.alloc(T * hp.n_head * (size_t)((m.max_kv + 3) & ~3) * 4) && p.meta.alloc(T * 8) &&
               p.gstart.alloc(ne * 4) && p.gcount.alloc(ne * 4) && p.ptoken.alloc(T * nu * 4) && p.pslot.alloc(T * nu * 4) &&
-              p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && p.aq_rm.alloc(T * max_act) && p.aq2_rm.alloc(T * nu * ffe) &&
+              p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && p.aq_rm.alloc(T * max_act * 4) && p.aq2_rm.alloc(T * nu * ffe * 4) &&
               cudaMallocHost((void **)&p.h_meta, T * 8) == cudaSuccess;
     if (!ok) {
         m.err = std::string("prefill buffers: ") + llamd_cuda_last_error_string();
@@ -738,8 +746,12 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
         else
             llamd_fwd_combine_rms_norm_quant(x, p.down.as<float>(), p.w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
                                              p.aq.as<int8_t>(), p.ad.as<float>(), E, hp.rms_eps, T);
-        const bool gemm = m.prefill_gemm != 0;
-        if (gemm) {
+        const bool gemm = m.prefill_gemm != 0, tc = m.prefill_gemm == 2;
+        if (tc) {
+            llamd_fwd_act_f16_rm(p.aq.as<int8_t>(), p.ad.as<float>(), p.aq_rm.p, (size_t)T * eb);
+            llamd_fwd_gemm_tokens_tc(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq_rm.p, p.q.as<float>(), p.k.as<float>(), p.v.as<float>(), eb, qd,
+                                     kvd, kvd, T);
+        } else if (gemm) {
             llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * eb);
             llamd_fwd_gemm_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq_rm.p, p.ad.as<float>(), p.q.as<float>(), p.k.as<float>(),
                                   p.v.as<float>(), eb, qd, kvd, kvd, T);
@@ -757,7 +769,10 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
             llamd_fwd_attention_tile(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV,
                                      hd, meta, m.max_kv, T);
         llamd_fwd_quantize(p.attn.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(), T * (qd / 256));
-        if (gemm) {
+        if (tc) {
+            llamd_fwd_act_f16_rm(p.aq.as<int8_t>(), p.ad.as<float>(), p.aq_rm.p, (size_t)T * (qd / 256));
+            llamd_fwd_gemm_tokens_tc(l.attn_out.p, nullptr, nullptr, p.aq_rm.p, p.xb2.as<float>(), nullptr, nullptr, qd / 256, E, 0, 0, T);
+        } else if (gemm) {
             llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * (qd / 256));
             llamd_fwd_gemm_tokens(l.attn_out.p, nullptr, nullptr, p.aq_rm.p, p.ad.as<float>(), p.xb2.as<float>(), nullptr, nullptr, qd / 256,
                                   E, 0, 0, T);
@@ -777,7 +792,15 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
         // the expert scatter plan: (token, slot) pairs sorted by expert
         llamd_fwd_moe_group_work(p.ids.as<int32_t>(), ne, nu, T, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
                                  p.pslot.as<int32_t>(), p.work.as<int32_t>(), p.n_work.as<int32_t>());
-        if (gemm) {
+        if (tc) {
+            llamd_fwd_act_f16_rm(p.aq.as<int8_t>(), p.ad.as<float>(), p.aq_rm.p, (size_t)T * eb);
+            llamd_fwd_expert_gemm_tc(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
+                                     p.pslot.as<int32_t>(), p.aq_rm.p, p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne, T);
+            llamd_fwd_silu_mul_quant(p.gate.as<float>(), p.up.as<float>(), nullptr, p.aq2.as<int8_t>(), p.ad2.as<float>(), T * nu * ffe);
+            llamd_fwd_act_f16_rm(p.aq2.as<int8_t>(), p.ad2.as<float>(), p.aq2_rm.p, (size_t)T * nu * (ffe / 256));
+            llamd_fwd_expert_gemm_tc(l.down_exps.p, nullptr, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.pslot.as<int32_t>(),
+                                     p.pslot.as<int32_t>(), p.aq2_rm.p, p.down.as<float>(), nullptr, ffe / 256, E, ne, T);
+        } else if (gemm) {
             llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * eb);
             llamd_fwd_expert_gemm(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
                                   p.pslot.as<int32_t>(), p.aq_rm.p, p.ad.as<float>(), p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne);
@@ -849,6 +872,10 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
     }
     if (cudaMemcpyAsync(m->h_out, m->out_token.p, 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
     if (llamd_fwd_sync() != 0) return -1;
+    if (m->prefill_gemm == 2 && llamd_fwd_gemm_tc_status() != 0) {
+        m->err = "prefill: a wait inside the tcgen05 GEMM ran out; the pass is incomplete";
+        return -1;
+    }
     if (m->h_out[0] < 0 || m->h_out[0] >= m->hp.n_vocab) {
         m->err = "argmax returned " + std::to_string(m->h_out[0]);
         return -1;

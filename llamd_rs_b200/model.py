@@ -204,8 +204,9 @@ class CudaModel:
             raise backend.Malformed(f"prefill_tile {v} outside 1..4096")
         self._prefill_tile = int(v)
 
-    def set_prefill_gemm(self, on: bool) -> None:
-        """True (default): the prefill tile's matmuls run on the integer tensor path; False: dp4a, 8 tokens per pass."""
+    def set_prefill_gemm(self, on) -> None:
+        """True / 1 (default): the prefill tile's matmuls run on the integer tensor path; False / 0: dp4a, 8 tokens
+        per pass (both bit-identical to decode); 2: tcgen05 on f16 pairs, tolerance level."""
         self._L.llamd_model_set_option(self._h, b"prefill_gemm", int(on))
 
     def set_option(self, name: str, value: int) -> None:

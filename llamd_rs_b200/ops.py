@@ -272,7 +272,13 @@ def embed(table: "backend.DeviceWeights", token: int) -> np.ndarray:
     return do.download_f32(table.blocks() * QK_K)
 
 
-def matvec_tokens(weights, x, gemm: bool = False):
+def _tc_check():
+    st = lib().llamd_fwd_gemm_tc_status()
+    if st != 0:
+        raise backend.Other(f"tcgen05 GEMM: a wait ran out (status {st})")
+
+
+def matvec_tokens(weights, x, gemm=False):
     """`weights`: 1-3 DeviceWeights sharing the column count; x f32 [ntok][k].
     Quantizes on the device, then every token against every matrix.
     -> list of [ntok][rows_i] (llamd_fwd_matvec_tokens; gemm=True: llamd_fwd_gemm_tokens)."""
@@ -288,7 +294,12 @@ def matvec_tokens(weights, x, gemm: bool = False):
     wp = [w.ptr for w in ws] + [None] * (3 - len(ws))
     op = [o.ptr for o in outs] + [None] * (3 - len(ws))
     rows = [w.rows() for w in ws] + [0] * (3 - len(ws))
-    if gemm:
+    if gemm == "tc":  # tolerance-level tcgen05 path
+        d16 = DevBuf(ntok * k * 4)  # two f16 terms per element
+        lib().llamd_fwd_act_f16_rm(dq.ptr, dd.ptr, d16.ptr, ntok * nb)
+        lib().llamd_fwd_gemm_tokens_tc(wp[0], wp[1], wp[2], d16.ptr, op[0], op[1], op[2], nb, rows[0], rows[1], rows[2], ntok)
+        _tc_check()
+    elif gemm:
         drm = DevBuf(ntok * k)
         lib().llamd_fwd_q8k_residue_major(dq.ptr, drm.ptr, ntok * nb)
         lib().llamd_fwd_gemm_tokens(wp[0], wp[1], wp[2], drm.ptr, dd.ptr, op[0], op[1], op[2], nb, rows[0], rows[1], rows[2], ntok)
@@ -298,7 +309,7 @@ def matvec_tokens(weights, x, gemm: bool = False):
     return [o.download_f32(ntok * w.rows()).reshape(ntok, w.rows()) for o, w in zip(outs, ws)]
 
 
-def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False, gemm: bool = False):
+def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False, gemm=False):
     """Routed matvec for many tokens through the scatter plan.
 
     `weights`: 1-2 DeviceWeights holding n_expert matrices of rows_per_expert
@@ -327,7 +338,13 @@ def expert_major(weights, x, ids, rows_per_expert: int, by_slot: bool = False, g
     wk, nw = DevBuf((max_items + 1) * 12), DevBuf.zeroed(4)
     lib().llamd_fwd_moe_group_work(di.ptr, n_expert, n_used, ntok, gs.ptr, gc.ptr, pt.ptr, ps.ptr, wk.ptr, nw.ptr)
     outs = [DevBuf.zeroed(npair * rows_per_expert * 4) for _ in ws]
-    if gemm:
+    if gemm == "tc":  # tolerance-level tcgen05 path
+        d16 = DevBuf(nact * k * 4)
+        lib().llamd_fwd_act_f16_rm(dq.ptr, dd.ptr, d16.ptr, nact * nb)
+        lib().llamd_fwd_expert_gemm_tc(ws[0].ptr, ws[1].ptr if len(ws) > 1 else None, gs.ptr, gc.ptr, ps.ptr if by_slot else pt.ptr, ps.ptr,
+                                       d16.ptr, outs[0].ptr, outs[1].ptr if len(ws) > 1 else None, nb, rows_per_expert, n_expert, npair)
+        _tc_check()
+    elif gemm:
         drm = DevBuf(nact * k)
         lib().llamd_fwd_q8k_residue_major(dq.ptr, drm.ptr, nact * nb)
         lib().llamd_fwd_expert_gemm(ws[0].ptr, ws[1].ptr if len(ws) > 1 else None, gs.ptr, gc.ptr, ps.ptr if by_slot else pt.ptr, ps.ptr,
