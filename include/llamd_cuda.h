@@ -280,6 +280,20 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
                               int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+/* ---- two decode launches fewer per layer: the producer's last CTA does the small follow-up op itself ----
+ * llamd_fwd_matvec_grouped_x2_silu_quant = llamd_fwd_matvec_grouped_x2 (crates/llamd-rocm/src/forward.rs: planar_grouped_x2)
+ * followed by llamd_fwd_silu_mul_quant of oa, ob: qs [slots][rows], d [slots][rows/256]; rows % 256 == 0.
+ * llamd_fwd_attention_meta_quant = llamd_fwd_attention_meta followed by llamd_fwd_quantize of out:
+ * qs [nseq][n_head*hd], d [nseq][n_head*hd/256]; needs the scores buffer.
+ * counter: one zero-initialised word per slot / per sequence; a launch leaves them at zero again. Same bits as the
+ * separate launches. */
+void llamd_fwd_matvec_grouped_x2_silu_quant(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq,
+                                            const float *ad, float *oa, float *ob, unsigned int *counter, int8_t *qs,
+                                            float *d, int blocks, int rows, int n_used, int nseq);
+void llamd_fwd_attention_meta_quant(const float *q, const float *kc, const float *vc, float *out, float *scores,
+                                    int n_head, int n_head_kv, int hd, const int32_t *meta, int max_kv, int nseq,
+                                    unsigned int *counter, int8_t *qs, float *d);
+
 /* ---- the same matmuls at TOLERANCE level on tcgen05 (f16 tiles dequantized in shared memory, f32
  * accumulators in TMEM, one accumulation over all of K). Outputs agree with llamd_fwd_gemm_tokens /
  * llamd_fwd_expert_gemm within QUANTIZED_MATMUL = 1e-3 (crates/llamd-core/src/tolerance.rs:41-66), not bit for bit.

@@ -112,6 +112,8 @@ SIGNATURES = {
     "llamd_fwd_matvec_grouped_pa_owned": (None, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
     "llamd_fwd_ep_dispatch": (None, [vp, vp, vp, vp, vp, vp, i32, i32]),
     "llamd_fwd_ep_combine": (None, [vp, vp, vp, vp, i32, i32, i32]),
+    "llamd_fwd_matvec_grouped_x2_silu_quant": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]),
+    "llamd_fwd_attention_meta_quant": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32, vp, vp, vp]),
     "llamd_fwd_act_f16_rm": (None, [vp, vp, vp, C.c_size_t]),
     "llamd_fwd_gemm_tokens_tc": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
     "llamd_fwd_expert_gemm_tc": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]),

@@ -55,6 +55,20 @@ void llamd_fwd_matvec_grouped_x2_batch(const void *wa, const void *wb, const int
     const int r2[2] = {rows, rows};
     launch_matvec(2, ws, os, r2, blocks, aq, ad, 1, ids, n_used * nseq, kAnyExpert, n_used);
 }
+// llamd_fwd_matvec_grouped_x2_batch followed by llamd_fwd_silu_mul_quant of its outputs, in one launch: the CTA
+// that completes a slot last writes act = silu(gate) * up as Q8_K into qs [slots][rows], d [slots][rows/256].
+// counter: n_used*nseq zero-initialised words the launch leaves at zero again. rows must be a multiple of 256.
+void llamd_fwd_matvec_grouped_x2_silu_quant(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                                            float *oa, float *ob, unsigned int *counter, int8_t *qs, float *d, int blocks, int rows,
+                                            int n_used, int nseq) {
+    if (!counter || !qs || !d || rows % 256) {
+        set_error_msg("matvec_grouped_x2_silu_quant: counter, qs, d must be given and rows a multiple of 256");
+        return;
+    }
+    g_next_tail = TailPlan{counter, qs, d};
+    llamd_fwd_matvec_grouped_x2_batch(wa, wb, ids, aq, ad, oa, ob, blocks, rows, n_used, nseq);
+    g_next_tail = TailPlan{};
+}
 void llamd_fwd_matvec_grouped_x2(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad, float *oa,
                                  float *ob, int blocks, int rows, int n_used) {
     llamd_fwd_matvec_grouped_x2_batch(wa, wb, ids, aq, ad, oa, ob, blocks, rows, n_used, 1);

@@ -104,6 +104,16 @@ __device__ __forceinline__ void prefetch_issue(const PrefetchPlan &pf, int cta, 
     }
 }
 
+// Work the next grouped gate+up matvec launch finishes itself instead of leaving it to a separate launch: the CTA
+// that completes a slot last (a self-resetting arrival counter per slot) computes act = silu(gate) * up for the
+// slot's rows and their Q8_K form, i.e. what llamd_fwd_silu_mul_quant would do one launch later.
+struct TailPlan {
+    unsigned int *counter;  // [n_slots] words, zero before the launch and zero again after it; null = no tail
+    int8_t *qs;             // [n_slots][rows]
+    float *d;               // [n_slots][rows / 256]
+};
+extern TailPlan g_next_tail;  // set by the model before a launch; consumed and cleared by that launch
+
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.
 void *scratch(int slot, size_t bytes);

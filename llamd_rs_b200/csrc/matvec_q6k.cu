@@ -66,6 +66,7 @@ struct MatvecParams {
     //   ACT_SILU xf = gate, xu = up, f32 [index][k]: silu(gate)*up, then quantized (fuses :316 too).
     const float *xf, *xu;
     PrefetchPlan pf;  // the weights of the matvec that follows this launch (a hint for L2)
+    TailPlan tail;    // gate+up launches: the slot's last CTA also produces the SiLU-gated, quantized activation
 };
 
 enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2 };
@@ -296,6 +297,27 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
             }
         }
     }
+    // ---- tail of a gate+up launch: silu(gate) * up and its Q8_K form, by the slot's last CTA ----
+    if (!MULTI && NSEQ == 1 && p.tail.counter) {  // uniform over the launch
+        __shared__ bool s_last;
+        __threadfence();  // this CTA's rows are visible before its arrival is
+        __syncthreads();
+        if (tid == 0) s_last = atomicInc(p.tail.counter + slot, p.ctas_per_slot - 1) == (unsigned)p.ctas_per_slot - 1;  // wraps to 0
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const int rows = p.job[0].rows, nblk = rows >> 8, lane = tid & 31;
+            const float *gate = p.job[0].out + (size_t)slot * rows, *up = p.job[1].out + (size_t)slot * rows;
+            for (int blk = tid >> 5; blk < nblk; blk += kThreads / 32) {
+                const size_t base = (size_t)blk * 256 + lane * 8;
+                const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(gate + base + 4));
+                const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(up + base + 4));
+                float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
+                              silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
+                q8k_quantize_block(v, lane, p.tail.qs + ((size_t)slot * nblk + blk) * 256, p.tail.d + (size_t)slot * nblk + blk, nullptr);
+            }
+        }
+    }
 }
 
 static size_t matvec_smem_bytes(int nseq, int nb) { return matvec_ad_offset(nseq, nb) + (size_t)nseq * nb * 4; }
@@ -315,6 +337,15 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
     MatvecParams q = p;
     q.pf = g_next_prefetch;
     g_next_prefetch = PrefetchPlan{};
+    q.tail = TailPlan{};
+    if (g_next_tail.counter) {
+        // only a grouped launch of two matrices whose rows are whole Q8_K blocks can take it
+        if (!MULTI && NSEQ == 1 && p.ids && p.njobs == 2 && p.job[0].rows % 256 == 0 && p.own_lo == 0 && p.own_hi >= p.n_expert)
+            q.tail = g_next_tail;
+        else
+            set_error_msg("matvec: a SiLU tail was planned for a launch that cannot carry it");
+        g_next_tail = TailPlan{};
+    }
     launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI, ACT>, grid, dim3(kThreads), smem, q);
 }
 

@@ -34,6 +34,11 @@ void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, 
 void llamd_fwd_attention_prefill(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                                  int hd, const int32_t *meta, int max_kv, int ntok, int n_kv_max);
 void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int k, int rows, int ntok);
+void llamd_fwd_matvec_grouped_x2_silu_quant(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                                            float *oa, float *ob, unsigned int *counter, int8_t *qs, float *d, int blocks, int rows,
+                                            int n_used, int nseq);
+void llamd_fwd_attention_meta_quant(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
+                                    int hd, const int32_t *meta, int max_kv, int nseq, unsigned int *counter, int8_t *qs, float *d);
 void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int blocks, int rows, int nseq);
 void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
                                       int rows, int n_used, int nseq);
@@ -112,6 +117,7 @@ struct Model {
     Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
     Buf scores;              // [max_seq][n_head][max_kv] scaled attention logits
     Buf router_counter;      // the router kernel's arrival counters, one per sequence
+    Buf tail_counter;        // arrival counters of the fused tails: [max_seq * n_expert_used] (also covers [max_seq])
     Buf tok_log, tok_count;  // device-side record of emitted tokens, for the resident decode loop
     unsigned long long launches_per_pass = 0;
     // prefill tile buffers (allocated on first use), token dimension = prefill_tile
@@ -130,6 +136,7 @@ struct Model {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_phase;
+    int fuse_tails = 1;      // 1: the attention output's and the gate/up outputs' follow-up ops run in the producer's last CTA
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int prefill_gemm = 1;    // 1: integer tensor path (mma.sync), exact; 0: dp4a, 8 tokens per weight pass, exact;
@@ -284,11 +291,20 @@ void queue_token(Model &m, int nseq) {
                                      l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
                                      l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
         mark(LLAMD_PH_ROPE);
-        llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
-                                 m.max_kv, nseq);
-        mark(LLAMD_PH_ATTENTION);
-        // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
-        llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+        const bool fuse = m.fuse_tails && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
+        if (fuse) {
+            // the CTA that finishes a sequence's attention last also writes its Q8_K form
+            llamd_fwd_attention_meta_quant(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
+                                           HKV, hd, meta, m.max_kv, nseq, m.tail_counter.as<unsigned int>(), m.aq.as<int8_t>(),
+                                           m.ad.as<float>());
+            mark(LLAMD_PH_ATTENTION);
+        } else {
+            llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV,
+                                     hd, meta, m.max_kv, nseq);
+            mark(LLAMD_PH_ATTENTION);
+            // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
+            llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+        }
         mark(LLAMD_PH_QUANT);
         plan_static(m, &l.ffn_gate_inp);
         llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
@@ -322,12 +338,19 @@ void queue_token(Model &m, int nseq) {
             continue;
         }
         plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
-        llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
-                                          m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
-        mark(LLAMD_PH_GATE_UP);
         // SiLU on the gate only, times up, quantized per expert; each expert's down projection reads its OWN activation
-        llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
-                                 nseq * nu * ffe);
+        if (fuse) {
+            llamd_fwd_matvec_grouped_x2_silu_quant(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
+                                                   m.e_gate.as<float>(), m.e_up.as<float>(), m.tail_counter.as<unsigned int>(),
+                                                   m.aq2.as<int8_t>(), m.ad2.as<float>(), eb, ffe, nu, nseq);
+            mark(LLAMD_PH_GATE_UP);
+        } else {
+            llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
+                                              m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+            mark(LLAMD_PH_GATE_UP);
+            llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                     nseq * nu * ffe);
+        }
         mark(LLAMD_PH_SILU);
         plan_after_down(il);
         llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
@@ -505,7 +528,7 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     f(m->expert_w, nu); f(m->e_gate, nu * ffe); f(m->e_up, nu * ffe); f(m->e_down, nu * E);
     f(m->logits, hp->n_vocab); f(m->amax_v, kArgmaxBlocks);
     ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
-    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4) && m->router_counter.alloc(4 * S) &&
+    ok = ok && m->tok_log.alloc((size_t)max_kv * 4 * S) && m->tok_count.alloc(4) && m->router_counter.alloc(4 * S) && m->tail_counter.alloc(4 * (size_t)S * hp->n_expert_used) &&
          m->scores.alloc((size_t)S * hp->n_head * max_kv * sizeof(float));
     if (m->ep_world > 1) {
         const size_t W = m->ep_world;
@@ -548,7 +571,7 @@ void llamd_model_free(llamd_model *h) {
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
-                   &m->tok_log, &m->tok_count, &m->router_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
+                   &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all})
         b->release();
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
@@ -642,6 +665,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!m || !name) return -1;
     if (!strcmp(name, "use_graph")) {
         m->use_graph = value;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_tails")) {
+        if (m->fuse_tails != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_tails = value;
         return 0;
     }
     if (!strcmp(name, "prefetch")) {

@@ -559,9 +559,11 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
 
 constexpr int kPvTile = 256;  // positions per V tile
 
+// With a TailPlan the CTA that finishes a sequence last also writes the Q8_K form of that sequence's whole
+// attention output (what llamd_fwd_quantize would do one launch later).
 __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const float *__restrict__ vc, float *__restrict__ out,
                                                        int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int n_kv_imm,
-                                                       int max_kv, int kv_stride) {
+                                                       int max_kv, int kv_stride, const TailPlan tail) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float s_red[16];
     pdl_trigger();
@@ -640,6 +642,24 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
         }
     }
     if (tid < cols) out[((size_t)seq * n_head + h) * hd + (size_t)c * cols + tid] = acc;
+    if (tail.counter) {  // uniform over the launch
+        __shared__ bool s_last;
+        const unsigned per_seq = gridDim.x * gridDim.y;
+        __threadfence();  // this CTA's columns are visible before its arrival is
+        __syncthreads();
+        if (tid == 0) s_last = atomicInc(tail.counter + seq, per_seq - 1) == per_seq - 1;  // wraps to 0
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const int n = n_head * hd, nblk = n >> 8, lane = tid & 31;
+            for (int blk = tid >> 5; blk < nblk; blk += 8) {
+                const float *src = out + (size_t)seq * n + (size_t)blk * 256 + lane * 8;
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(src)), b = __ldcg(reinterpret_cast<const float4 *>(src + 4));
+                float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                q8k_quantize_block(v, lane, tail.qs + ((size_t)seq * nblk + blk) * 256, tail.d + (size_t)seq * nblk + blk, nullptr);
+            }
+        }
+    }
 }
 
 // ---- argmax, lowest index on a tie (llamd_forward.hip:353-389) -------------
@@ -945,8 +965,16 @@ static void attention_split_launch(const float *q, const float *kc, const float 
     }
     launch_kc(PDL_ATTN, "attn_scores", attn_scores_kernel, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
              max_kv, kv_stride);
+    TailPlan tail = {};
+    if (g_next_tail.counter) {
+        if ((n_head * hd) % 256 == 0)
+            tail = g_next_tail;
+        else
+            set_error_msg("attention: a quantize tail needs n_head * head_dim to be whole Q8_K blocks");
+        g_next_tail = TailPlan{};
+    }
     launch_kc(PDL_ATTN, "attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
-             meta, n_kv, max_kv, kv_stride);
+             meta, n_kv, max_kv, kv_stride, tail);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
@@ -961,6 +989,10 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 8 * 256) {
         attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride);
         return;
+    }
+    if (g_next_tail.counter) {
+        set_error_msg("attention: a quantize tail was planned for the single-CTA kernel, which does not carry it");
+        g_next_tail = TailPlan{};
     }
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -988,6 +1020,19 @@ void llamd_fwd_attention(const float *q, const float *kc, const float *vc, float
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int ntok) {
     attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, ntok, 0);
+}
+// llamd_fwd_attention_meta followed by llamd_fwd_quantize of the result, in the attention's own two launches:
+// the CTA that finishes a sequence last writes qs [nseq][n_head*hd] and d [nseq][n_head*hd/256]. counter: nseq
+// zero-initialised words the launch leaves at zero again. Needs the scores buffer (the split kernels).
+void llamd_fwd_attention_meta_quant(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
+                                    int hd, const int32_t *meta, int max_kv, int nseq, unsigned int *counter, int8_t *qs, float *d) {
+    if (!scores || !counter || !qs || !d) {
+        set_error_msg("attention_meta_quant: scores, counter, qs and d must be given");
+        return;
+    }
+    g_next_tail = TailPlan{counter, qs, d};
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv);
+    g_next_tail = TailPlan{};
 }
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int nseq) {

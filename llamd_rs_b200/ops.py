@@ -382,3 +382,62 @@ def matvec_grouped_pa_silu(w: "backend.DeviceWeights", ids, gate, up, rows_per_e
     lib().llamd_fwd_matvec_grouped_pa_silu(w.ptr, di.ptr, dg.ptr, du.ptr, do.ptr, w.blocks(), rows_per_expert, ids.size, 1)
     backend.sync()
     return do.download_f32(ids.size * rows_per_expert).reshape(ids.size, rows_per_expert)
+
+
+def matvec_grouped_x2_silu_quant(wa: "backend.DeviceWeights", wb: "backend.DeviceWeights", ids, x, rows_per_expert: int, fused: bool = True):
+    """gate/up of routed experts for nseq sequences, then act = silu(gate)*up as Q8_K.
+    ids int32 [nseq][n_used]; x f32 [nseq][k]. fused=True: one launch (llamd_fwd_matvec_grouped_x2_silu_quant);
+    False: the two separate launches. -> (gate, up, qs int8 [slots][rows], d f32 [slots][rows/256])."""
+    x = _f32(x)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    nseq, n_used = ids.shape
+    k = x.shape[1]
+    if x.shape[0] != nseq or wa.blocks() * QK_K != k or wb.blocks() != wa.blocks() or rows_per_expert % QK_K:
+        raise ShapeError("matvec_grouped_x2_silu_quant sizes")
+    n_expert = wa.rows() // rows_per_expert
+    if ids.min() < 0 or ids.max() >= n_expert:
+        raise Malformed(f"expert id outside 0..{n_expert}")
+    nb, slots = k // QK_K, nseq * n_used
+    dx, dq, dd = DevBuf.from_array(x), DevBuf(nseq * k), DevBuf(nseq * nb * 4)
+    lib().llamd_fwd_quantize(dx.ptr, dq.ptr, dd.ptr, nseq * nb)
+    di = DevBuf.from_array(ids)
+    dg, du = DevBuf(slots * rows_per_expert * 4), DevBuf(slots * rows_per_expert * 4)
+    q2, d2 = DevBuf(slots * rows_per_expert), DevBuf(slots * (rows_per_expert // QK_K) * 4)
+    if fused:
+        dc = DevBuf.zeroed(slots * 4)
+        lib().llamd_fwd_matvec_grouped_x2_silu_quant(wa.ptr, wb.ptr, di.ptr, dq.ptr, dd.ptr, dg.ptr, du.ptr, dc.ptr, q2.ptr, d2.ptr, nb,
+                                                     rows_per_expert, n_used, nseq)
+        backend.sync()
+        assert not dc.download(np.uint32, slots).any(), "arrival counters must return to zero"
+    else:
+        lib().llamd_fwd_matvec_grouped_x2_batch(wa.ptr, wb.ptr, di.ptr, dq.ptr, dd.ptr, dg.ptr, du.ptr, nb, rows_per_expert, n_used, nseq)
+        lib().llamd_fwd_silu_mul_quant(dg.ptr, du.ptr, None, q2.ptr, d2.ptr, slots * rows_per_expert)
+        backend.sync()
+    return (dg.download_f32(slots * rows_per_expert).reshape(slots, -1), du.download_f32(slots * rows_per_expert).reshape(slots, -1),
+            q2.download(np.int8, slots * rows_per_expert).reshape(slots, -1), d2.download_f32(slots * (rows_per_expert // QK_K)).reshape(slots, -1))
+
+
+def attention_meta_quant(q, k, v, positions, n_head: int, n_head_kv: int, hd: int, max_kv: int, fused: bool = True):
+    """nseq sequences, each with its own cache k/v [nseq][max_kv][n_head_kv*hd] and position; the attention output and
+    its Q8_K form. fused=True: llamd_fwd_attention_meta_quant; False: attention_meta then quantize."""
+    q, k, v = _f32(q).ravel(), _f32(k).ravel(), _f32(v).ravel()
+    positions = np.ascontiguousarray(positions, dtype=np.int32).ravel()
+    nseq, n = positions.size, n_head * hd
+    if q.size != nseq * n or k.size != nseq * max_kv * n_head_kv * hd or v.size != k.size or n % QK_K:
+        raise ShapeError("attention_meta_quant sizes")
+    meta = np.zeros((nseq, 2), dtype=np.int32)
+    meta[:, 1] = positions
+    dq, dk, dv, do = DevBuf.from_array(q), DevBuf.from_array(k), DevBuf.from_array(v), DevBuf(q.nbytes)
+    dm, ds = DevBuf.from_array(meta), DevBuf(nseq * n_head * max_kv * 4)
+    qs, d = DevBuf(nseq * n), DevBuf(nseq * (n // QK_K) * 4)
+    if fused:
+        dc = DevBuf.zeroed(nseq * 4)
+        lib().llamd_fwd_attention_meta_quant(dq.ptr, dk.ptr, dv.ptr, do.ptr, ds.ptr, n_head, n_head_kv, hd, dm.ptr, max_kv, nseq, dc.ptr, qs.ptr,
+                                             d.ptr)
+        backend.sync()
+        assert not dc.download(np.uint32, nseq).any(), "arrival counters must return to zero"
+    else:
+        lib().llamd_fwd_attention_meta(dq.ptr, dk.ptr, dv.ptr, do.ptr, ds.ptr, n_head, n_head_kv, hd, dm.ptr, max_kv, nseq)
+        lib().llamd_fwd_quantize(do.ptr, qs.ptr, d.ptr, nseq * (n // QK_K))
+        backend.sync()
+    return do.download_f32(nseq * n).reshape(nseq, n), qs.download(np.int8, nseq * n).reshape(nseq, n), d.download_f32(nseq * (n // QK_K)).reshape(nseq, -1)

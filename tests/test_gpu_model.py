@@ -137,6 +137,24 @@ def test_batch_equals_single(tiny):
         assert np.array_equal(lb[i].view(np.uint32), single_logits[i].view(np.uint32)), f"sequence {i} logits"
 
 
+def test_fused_tails_change_nothing(tiny):
+    """The decode pass with the attention-quantize and SiLU-quantize tails inside their producers (default) and with
+    the separate launches: same tokens, same logits, bit for bit."""
+    hp, w, gm, om = tiny
+    runs = {}
+    for fuse in (1, 0, 1):
+        gm.set_option("fuse_tails", fuse)
+        toks, tok = [], 3
+        for pos in range(6):
+            tok = gm.forward(tok, pos)
+            toks.append(tok)
+        runs.setdefault(fuse, []).append((toks, gm.logits()[0].copy()))
+    gm.set_option("fuse_tails", 1)
+    ref_t, ref_l = runs[0][0]
+    for t, l in runs[1]:
+        assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
+
+
 def test_prefill_equals_sequential_decode(tiny):
     """crates/llamd-testing/tests/vulkan_prefill.rs:48-136: prefill gives the token (and here the logits and the
     K/V cache, bit for bit) of sequential decode, for (tile, length) pairs that straddle tile and chunk boundaries."""

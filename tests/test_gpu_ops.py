@@ -269,3 +269,36 @@ def test_embed_is_a_dequantized_row(ops, orc, synth):
         assert bit_equal(ops.embed(t, tok), full[tok])
     with pytest.raises(backend.Malformed):
         ops.embed(t, 50)
+
+
+@pytest.mark.parametrize("nseq", [1, 3])
+def test_gate_up_with_the_silu_quant_tail(ops, orc, synth, nseq):
+    """The slot's last CTA produces silu(gate)*up and its Q8_K form: same bits as the two separate launches."""
+    from llamd_rs_b200 import backend
+
+    n_expert, rows, k, n_used = 10, 512, 512, 4
+    wa = synth.q6k_blocks(n_expert * rows * k // 256, 94, "tail.a")
+    wb = synth.q6k_blocks(n_expert * rows * k // 256, 94, "tail.b")
+    da = backend.DeviceWeights.upload(wa, n_expert * rows, k // 256)
+    db = backend.DeviceWeights.upload(wb, n_expert * rows, k // 256)
+    rng = np.random.default_rng(nseq)
+    ids = np.stack([rng.permutation(n_expert)[:n_used] for _ in range(nseq)]).astype(np.int32)
+    x = synth.normal_f32(nseq * k, 94, "tail.x", nseq).reshape(nseq, k)
+    for _ in range(2):  # twice: the counters must be reusable
+        got = ops.matvec_grouped_x2_silu_quant(da, db, ids, x, rows)
+    want = ops.matvec_grouped_x2_silu_quant(da, db, ids, x, rows, fused=False)
+    assert bit_equal(got[0], want[0]) and bit_equal(got[1], want[1])
+    assert np.array_equal(got[2], want[2]) and bit_equal(got[3], want[3])
+
+
+def test_attention_with_the_quantize_tail(ops, synth):
+    n_head, n_head_kv, hd, max_kv = 8, 2, 64, 48
+    pos = np.array([5, 47, 0], dtype=np.int32)
+    kvd = n_head_kv * hd
+    q = synth.normal_f32(3 * n_head * hd, 95, "atq.q")
+    k = synth.normal_f32(3 * max_kv * kvd, 95, "atq.k")
+    v = synth.normal_f32(3 * max_kv * kvd, 95, "atq.v")
+    for _ in range(2):
+        got = ops.attention_meta_quant(q, k, v, pos, n_head, n_head_kv, hd, max_kv)
+    want = ops.attention_meta_quant(q, k, v, pos, n_head, n_head_kv, hd, max_kv, fused=False)
+    assert bit_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and bit_equal(got[2], want[2])
