@@ -136,7 +136,8 @@ struct Model {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_phase;
-    int fuse_tails = 1;      // 1: the attention output's and the gate/up outputs' follow-up ops run in the producer's last CTA
+    int fuse_tails = 0;      // 1: the attention output's and the gate/up outputs' follow-up ops run in the producer's last CTA
+                             // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int prefill_gemm = 1;    // 1: integer tensor path (mma.sync), exact; 0: dp4a, 8 tokens per weight pass, exact;
