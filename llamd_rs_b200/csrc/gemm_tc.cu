@@ -21,7 +21,8 @@
 //                   copy the B tile (cp.async); tiles are K-major, 128-byte rows [32 f16 | 32 f16], with the
 //                   128-byte swizzle the matrix descriptors name; the next stage's code words are already in flight
 //     one thread    8 x tcgen05.mma (M 128, N n_pad, K 16) accumulating into TMEM, tcgen05.commit -> mbarrier
-//   two stages of buffers: the fold of stage s+1 overlaps the MMAs of stage s
+//   two A buffers (the fold of stage s+1 overlaps the MMAs of stage s), a ring of four B buffers filled two stages
+//   ahead, code words loaded two stages ahead
 //   blocks alternate between two accumulator tiles in TMEM; one stage into the next block, the finished one is
 //   read back: tcgen05.ld (32 lanes x 32 columns per warp), acc += 64 d * D in registers
 //   at the end: scatter acc to out[token][row].
@@ -73,10 +74,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     }
     return false;
 }
-__device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
-}
-
 // K-major tile with 128-byte rows and the 128-byte swizzle; 8-row groups 1024 bytes apart (matrix descriptor
 // format of tcgen05.mma: start address, leading and stride byte offsets in 16-byte units, version 1 at bit 46,
 // layout type 2 = SWIZZLE_128B at bits 61-63).
@@ -150,7 +147,7 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_tc_kernel(const TcParams p) {
     const int first = first_all + t0, count = min(kTcN, count_all - t0);
     const int n_pad = max(16, (count + 15) & ~15);
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *sA = smem, *sB = smem + 2 * kTcStageBytes;  // two A stages of 128 rows, two B stages of kTcN rows
+    uint8_t *sA = smem, *sB = smem + 2 * kTcStageBytes;  // two A stages of 128 rows, a ring of four B stages of kTcN rows
 
     if (tid == 0) {
         mbar_init(&s_bar[0], 1);
@@ -208,119 +205,159 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_tc_kernel(const TcParams p) {
         for (int n = 0; n < 32; n++) acc[n] = fmaf(dscale, __uint_as_float(v[n]), acc[n]);
     };
 
-    // the loads of a stage: three code words, and at the first residue of a block its eight scales
-    auto load_stage = [&](int s, uint32_t (&S)[3], uint2 &scw) {
-        const int b = s >> 3, r = s & 7;
+    // ---- the stage loop: blocks outside, the eight residues of a block unrolled inside, so that every word offset,
+    // buffer index and barrier parity below is a compile-time constant ----
+    // byte offset of code word wdx inside a tile, for the block in slot 0 (chunk wdx/4 is 512 bytes, a word 4)
+#define TC_WOFF(wdx) ((((wdx) >> 2) * 512) + (((wdx) & 3) * 4))
+    const uint32_t sA_u = smem_u32(sA), sB_u = smem_u32(sB);
+    const int sw = row & 7;
+    // the four 16-byte pieces this thread writes in a stage's A tile: row = [U >> 6: words jw 0..7 | (U & 63)/64: words jw 0..7],
+    // 8 bytes per word; this thread owns jw = 4m .. 4m+3
+    const uint32_t a_off[4] = {(uint32_t)(row * 128 + (((2 * m + 0) ^ sw) << 4)), (uint32_t)(row * 128 + (((2 * m + 1) ^ sw) << 4)),
+                               (uint32_t)(row * 128 + (((4 + 2 * m + 0) ^ sw) << 4)), (uint32_t)(row * 128 + (((4 + 2 * m + 1) ^ sw) << 4))};
+    const bool bcopy[2] = {n_pad * 8 > tid, n_pad * 8 > tid + 256};
+    bool ok = true;
+    // where block b of this thread's row sits: tile base + its slot
+    auto block_ptr = [&](int b) -> const uint8_t * {
         const size_t unit = unit_row + b;
-        const uint8_t *tile = wj + (unit >> 5) * kTileBytes;
-        const int sl = (int)(unit & 31);
-        const int w0 = 6 * r + 3 * m;
+        return wj + (unit >> 5) * kTileBytes + (unit & 31) * 16;
+    };
+    const uint8_t *tb = live ? block_ptr(0) : wj;
+    // code words of the next stage (Sn) and of the one after it (Sn2): two stages of L2 latency are covered
+    uint32_t Sn[3] = {0, 0, 0}, Sn2[3] = {0, 0, 0};
+    uint2 scn = make_uint2(0, 0);
+    if (live) {
 #pragma unroll
         for (int x = 0; x < 3; x++) {
-            const int wdx = w0 + x;
-            S[x] = __ldg(reinterpret_cast<const uint32_t *>(tile + (wdx >> 2) * 512 + sl * 16 + (wdx & 3) * 4));
+            Sn[x] = __ldg(reinterpret_cast<const uint32_t *>(tb + (m ? TC_WOFF(3 + x) : TC_WOFF(x))));
+            Sn2[x] = __ldg(reinterpret_cast<const uint32_t *>(tb + (m ? TC_WOFF(6 + 3 + x) : TC_WOFF(6 + x))));
         }
-        if (r == 0) scw = __ldg(reinterpret_cast<const uint2 *>(tile + kTileScaleOff + sl * 16 + 8 * m));
+        scn = __ldg(reinterpret_cast<const uint2 *>(tb + kTileScaleOff + 8 * m));
+    }
+    // the B tiles of stages 0 and 1 start their trip now; stage s issues the copy for stage s+2
+    auto copy_b = [&](int ring) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            if (bcopy[i])
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sB_u + ring * (kTcN * 128) + bdst[i]), "l"(bsrc[i]), "r"(bbytes[i])
+                             : "memory");
+            bsrc[i] += 64;  // the next stage's 32 + 32 halves
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-
-    const int n_stages = 8 * nb;  // stage s = block s/8, residue s%8: a block's residues are consecutive
-    bool ok = true;
-    uint32_t Sn[3] = {0, 0, 0};
-    uint2 scn = make_uint2(0, 0);
-    if (live) load_stage(0, Sn, scn);
+    copy_b(0);
+    copy_b(1);
     int sc[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) sc[i] = 0;
-    for (int s = 0; s < n_stages; s++) {
-        const int buf = s & 1, b = s >> 3, r = s & 7;
-        if (s >= 2) {
-            if (!mbar_wait(&s_bar[buf], (uint32_t)((s >> 1) - 1) & 1)) ok = false;
-        }
-        if (r == 1 && b > 0) {
-            // The wait above covered stage s-2, the last of block b-1: its sum is complete. Block b accumulates into the
-            // other tile meanwhile, so nothing here waits for an MMA that was only just issued.
-            ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide: the warp reads together or not at all
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ok) drain_block(b - 1);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        }
+    for (int b = 0; b < nb; b++) {
+        const uint8_t *tb_next = (live && b + 1 < nb) ? block_ptr(b + 1) : tb;
 #pragma unroll
-        for (int i = 0; i < 2; i++)
-            if (n_pad * 8 > tid + 256 * i) cp_async16(sB + buf * (kTcN * 128) + bdst[i], bsrc[i] + (size_t)s * 64, bbytes[i]);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        for (int r = 0; r < 8; r++) {
+            const int buf = r & 1;
+            // the MMAs that read this buffer two stages ago: completion number (s >> 1) - 1 of its barrier, and s >> 1 = 4b + r/2
+            if (b > 0 || r >= 2) {
+                if (!mbar_wait(&s_bar[buf], (uint32_t)(((r >> 1) + 1) & 1))) ok = false;
+            }
+            if (r == 1 && b > 0) {
+                // The wait above covered stage s-2, the last of block b-1: its sum is complete. Block b accumulates into the
+                // other tile meanwhile, so nothing here waits for an MMA that was only just issued.
+                ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide: the warp reads together or not at all
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (ok) drain_block(b - 1);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            // ring slot (s+2)&3 was read by the MMAs of stage s-2, which the wait above covered
+            if (b + 1 < nb || r < 6) copy_b((r + 2) & 3);
+            else asm volatile("cp.async.commit_group;" ::: "memory");  // keep one group per stage so that the count below holds
 
-        // ---- this thread's 16 weights: MMA words jw = 4m .. 4m+3 of residue r of block (row, b) ----
-        uint32_t S[3] = {Sn[0], Sn[1], Sn[2]};
-        if (r == 0) {
-            const uint32_t ws[2] = {scn.x, scn.y};
+            // ---- this thread's 16 weights: MMA words jw = 4m .. 4m+3 of residue r of block (row, b) ----
+            const uint32_t S0 = Sn[0], S1 = Sn[1], S2 = Sn[2];
+            if (r == 0) {
+                const uint32_t ws[2] = {scn.x, scn.y};
 #pragma unroll
-            for (int i = 0; i < 8; i++) sc[i] = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
-        }
-        if (live && s + 1 < n_stages) load_stage(s + 1, Sn, scn);  // in flight while this stage is folded
-        uint32_t ahi[8], alo[8];
-        if (live) {
-            // The stored byte is 4*(q-32) mod 256; ^0x80 makes it 4q. The fourth word's codes are the low bit pairs of
-            // the other three.
-            uint32_t ub[4];
-            ub[0] = (S[0] & 0xFCFCFCFCu) ^ 0x80808080u;
-            ub[1] = (S[1] & 0xFCFCFCFCu) ^ 0x80808080u;
-            ub[2] = (S[2] & 0xFCFCFCFCu) ^ 0x80808080u;
-            ub[3] = (((S[0] << 6) & 0xC0C0C0C0u) | ((S[1] << 4) & 0x30303030u) | ((S[2] << 2) & 0x0C0C0C0Cu)) ^ 0x80808080u;
+                for (int i = 0; i < 8; i++) sc[i] = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+            }
+            Sn[0] = Sn2[0]; Sn[1] = Sn2[1]; Sn[2] = Sn2[2];
+            if (live) {  // the words of stage s+2: two stages of work hide their latency
+                if (r < 6) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                // Two weights per multiply-add. With the bytes spread into 16-bit fields, x - 0x00800080 is, as an integer,
-                // sum_i 4*(q_i - 32) << 16i, so sc*(x - 0x00800080) + 0x80008000 holds 4*U_i + 32768 (U = sc*(q-32), in
-                // [16512, 49152]) in each field with no carry between them: the high byte is (U >> 6) + 128, the low byte
-                // 4*(U & 63). Bytes 0,1 of word i belong to scale group 2i, bytes 2,3 to 2i+1.
+                    for (int x = 0; x < 3; x++)
+                        Sn2[x] = __ldg(reinterpret_cast<const uint32_t *>(tb + (m ? TC_WOFF(6 * (r + 2) + 3 + x) : TC_WOFF(6 * (r + 2) + x))));
+                } else if (b + 1 < nb) {
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const uint32_t x = __byte_perm(ub[i], 0u, h ? 0x4342 : 0x4140);
-                    const uint32_t v = (x - 0x00800080u) * (uint32_t)sc[2 * i + h] + 0x80008000u;
-                    // bytes under the exponent of 1024: (1024 + byte) as f16, two per register
-                    const uint32_t bh = __byte_perm(v, 0x64646464u, 0x4341), bl = __byte_perm(v, 0x64646464u, 0x4240);
-                    const __half2 hh = __hsub2(*reinterpret_cast<const __half2 *>(&bh), __half2half2(__ushort_as_half(0x6480)));  // - 1152: U >> 6
-                    const __half2 hl = __hfma2(*reinterpret_cast<const __half2 *>(&bl), __half2half2(__ushort_as_half(0x1C00)),  // * 1/256
-                                               __half2half2(__ushort_as_half(0xC400)));                                     // - 4: (U & 63) / 64
-                    ahi[2 * i + h] = *reinterpret_cast<const uint32_t *>(&hh);
-                    alo[2 * i + h] = *reinterpret_cast<const uint32_t *>(&hl);
+                    for (int x = 0; x < 3; x++)
+                        Sn2[x] = __ldg(reinterpret_cast<const uint32_t *>(tb_next + (m ? TC_WOFF(6 * (r - 6) + 3 + x) : TC_WOFF(6 * (r - 6) + x))));
+                    if (r == 7) scn = __ldg(reinterpret_cast<const uint2 *>(tb_next + kTileScaleOff + 8 * m));
                 }
             }
-        } else {
+            uint32_t ahi[8], alo[8];
+            if (live) {
+                // The stored byte is 4*(q-32) mod 256; ^0x80 makes it 4q. The fourth word's codes are the low bit pairs of
+                // the other three.
+                uint32_t ub[4];
+                ub[0] = (S0 & 0xFCFCFCFCu) ^ 0x80808080u;
+                ub[1] = (S1 & 0xFCFCFCFCu) ^ 0x80808080u;
+                ub[2] = (S2 & 0xFCFCFCFCu) ^ 0x80808080u;
+                ub[3] = (((S0 << 6) & 0xC0C0C0C0u) | ((S1 << 4) & 0x30303030u) | ((S2 << 2) & 0x0C0C0C0Cu)) ^ 0x80808080u;
 #pragma unroll
-            for (int q = 0; q < 8; q++) ahi[q] = alo[q] = 0;
-        }
-        {
-            // row = [U >> 6: words jw 0..7 | (U & 63)/64: words jw 0..7], 8 bytes per word; this thread owns jw = 4m .. 4m+3
-            uint8_t *arow = sA + buf * kTcStageBytes + row * 128;
-            const int sw = row & 7;
-            *reinterpret_cast<uint4 *>(arow + (((2 * m + 0) ^ sw) << 4)) = make_uint4(ahi[0], ahi[1], ahi[2], ahi[3]);
-            *reinterpret_cast<uint4 *>(arow + (((2 * m + 1) ^ sw) << 4)) = make_uint4(ahi[4], ahi[5], ahi[6], ahi[7]);
-            *reinterpret_cast<uint4 *>(arow + (((4 + 2 * m + 0) ^ sw) << 4)) = make_uint4(alo[0], alo[1], alo[2], alo[3]);
-            *reinterpret_cast<uint4 *>(arow + (((4 + 2 * m + 1) ^ sw) << 4)) = make_uint4(alo[4], alo[5], alo[6], alo[7]);
-        }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
-        __syncthreads();
-        if (tid == 0 && ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = tc_smem_desc(smem_u32(sA + buf * kTcStageBytes));
-            const uint64_t db = tc_smem_desc(smem_u32(sB + buf * (kTcN * 128)));
-            // 32-byte slices of a row (16 contraction elements each, +2 in 16-byte units). A: 0,1 = U >> 6; 2,3 = (U & 63)/64.
-            // B: 0,1 = first f16 term of the activation; 2,3 = second term. All four products, both halves of the residue.
-            const int sa[8] = {0, 1, 0, 1, 2, 3, 2, 3}, sb[8] = {0, 1, 2, 3, 0, 1, 2, 3};
+                for (int i = 0; i < 4; i++) {
+                    // Two weights per multiply-add. With the bytes spread into 16-bit fields, x - 0x00800080 is, as an
+                    // integer, sum_i 4*(q_i - 32) << 16i, so sc*(x - 0x00800080) + 0x80008000 holds 4*U_i + 32768
+                    // (U = sc*(q-32), in [16512, 49152]) in each field with no carry between them: the high byte is
+                    // (U >> 6) + 128, the low byte 4*(U & 63). Bytes 0,1 of word i belong to scale group 2i, bytes 2,3 to 2i+1.
 #pragma unroll
-            for (int kk = 0; kk < 8; kk++) {
-                const uint32_t accum = (r > 0 || kk > 0) ? 1u : 0u;  // a block starts its own sum
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\t"
-                    "setp.ne.b32 p, %4, 0;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                    ::"r"(tmem + (uint32_t)((b & 1) * kTcN)), "l"(da + (uint64_t)(2 * sa[kk])), "l"(db + (uint64_t)(2 * sb[kk])), "r"(idesc), "r"(accum)
-                    : "memory");
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t x = __byte_perm(ub[i], 0u, h ? 0x4342 : 0x4140);
+                        const uint32_t v = (x - 0x00800080u) * (uint32_t)sc[2 * i + h] + 0x80008000u;
+                        // bytes under the exponent of 1024: (1024 + byte) as f16, two per register
+                        const uint32_t bh = __byte_perm(v, 0x64646464u, 0x4341), bl = __byte_perm(v, 0x64646464u, 0x4240);
+                        const __half2 hh = __hsub2(*reinterpret_cast<const __half2 *>(&bh), __half2half2(__ushort_as_half(0x6480)));  // - 1152: U >> 6
+                        const __half2 hl = __hfma2(*reinterpret_cast<const __half2 *>(&bl), __half2half2(__ushort_as_half(0x1C00)),  // * 1/256
+                                                   __half2half2(__ushort_as_half(0xC400)));                                     // - 4: (U & 63) / 64
+                        ahi[2 * i + h] = *reinterpret_cast<const uint32_t *>(&hh);
+                        alo[2 * i + h] = *reinterpret_cast<const uint32_t *>(&hl);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; q++) ahi[q] = alo[q] = 0;
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s_bar[buf])) : "memory");
+            {
+                const uint32_t ab = sA_u + buf * kTcStageBytes;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ab + a_off[0]), "r"(ahi[0]), "r"(ahi[1]), "r"(ahi[2]), "r"(ahi[3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ab + a_off[1]), "r"(ahi[4]), "r"(ahi[5]), "r"(ahi[6]), "r"(ahi[7]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ab + a_off[2]), "r"(alo[0]), "r"(alo[1]), "r"(alo[2]), "r"(alo[3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ab + a_off[3]), "r"(alo[4]), "r"(alo[5]), "r"(alo[6]), "r"(alo[7]) : "memory");
+            }
+            asm volatile("cp.async.wait_group 2;" ::: "memory");  // all but the two newest copies: this stage's B tile has landed
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
+            __syncthreads();
+            if (tid == 0 && ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = tc_smem_desc(sA_u + buf * kTcStageBytes);
+                const uint64_t db = tc_smem_desc(sB_u + (r & 3) * (kTcN * 128));
+                // 32-byte slices of a row (16 contraction elements each, +2 in 16-byte units). A: 0,1 = U >> 6; 2,3 = (U & 63)/64.
+                // B: 0,1 = first f16 term of the activation; 2,3 = second term. All four products, both halves of the residue.
+                const int sa[8] = {0, 1, 0, 1, 2, 3, 2, 3}, sb[8] = {0, 1, 2, 3, 0, 1, 2, 3};
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {
+                    const uint32_t accum = (r > 0 || kk > 0) ? 1u : 0u;  // a block starts its own sum
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem + (uint32_t)((b & 1) * kTcN)), "l"(da + (uint64_t)(2 * sa[kk])), "l"(db + (uint64_t)(2 * sb[kk])), "r"(idesc),
+                        "r"(accum)
+                        : "memory");
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s_bar[buf])) : "memory");
+            }
         }
+        tb = tb_next;
     }
+#undef TC_WOFF
+    const int n_stages = 8 * nb;
     // the last block
     if (!mbar_wait(&s_bar[(n_stages - 1) & 1], (uint32_t)((n_stages - 1) >> 1) & 1)) ok = false;
     ok = __all_sync(0xffffffffu, ok);
@@ -373,7 +410,7 @@ static void tc_launch(TcParams &p, int n_groups, int max_count) {
         set_error_msg("q6k gemm (tcgen05): too many groups");
         return;
     }
-    const size_t smem = 2 * (size_t)kTcStageBytes + 2 * (size_t)kTcN * 128 + 1024;  // two A and two B stages, alignment slack
+    const size_t smem = 2 * (size_t)kTcStageBytes + 4 * (size_t)kTcN * 128 + 1024;  // two A and four B stages, alignment slack
     static size_t configured = 0;
     if (smem > configured) {
         cudaFuncSetAttribute(q6k_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
