@@ -167,6 +167,15 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_tc_kernel(const TcParams p) {
     // instruction descriptor: D f32 (bit 4), A and B f16 K-major, N >> 3 at bit 17, M >> 4 at bit 24
     const uint32_t idesc = (1u << 4) | ((uint32_t)(n_pad >> 3) << 17) | ((uint32_t)(kTcM >> 4) << 24);
 
+    if (tid == 0) {
+        // The CTA's 128 rows x nb blocks are whole consecutive tiles: ask L2 for all of them now, so that the word loads
+        // of the stage loop meet L2 latency, not HBM's (a hint; nothing waits on it).
+        const size_t u0 = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)row0 * nb;
+        const size_t u1 = u0 + (size_t)min(kTcM, rows - row0) * nb;
+        const size_t t_lo = u0 >> 5, t_hi = (u1 - 1) >> 5;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.w[j] + t_lo * kTileBytes), "r"((uint32_t)((t_hi - t_lo + 1) * kTileBytes))
+                     : "memory");
+    }
     const int row = tid & 127, m = tid >> 7;  // this thread folds words 3m..3m+2 of the stage's residue for its row
     const bool live = row0 + row < rows;
     const size_t unit_row = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)(row0 + row) * nb;
@@ -192,13 +201,17 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_tc_kernel(const TcParams p) {
 #pragma unroll
     for (int n = 0; n < 32; n++) acc[n] = 0.0f;
     // out += (64 * d[row][b]) * D for the block whose MMAs have completed
+    // d of (this thread's epilogue row, block b), requested several stages before the drain that uses it
+    uint32_t d_bits = 0;
+    auto load_d = [&](int b) {
+        if (col0 < n_pad && row0 + e_row < rows) {
+            const size_t unit = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)(row0 + e_row) * nb + b;
+            d_bits = __ldg(reinterpret_cast<const uint16_t *>(wj + (unit >> 5) * kTileBytes + kTileDOff) + (unit & 31));
+        }
+    };
     auto drain_block = [&](int b) {
         if (col0 >= n_pad) return;  // uniform per warp
-        float dscale = 0.0f;
-        if (row0 + e_row < rows) {
-            const size_t unit = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)(row0 + e_row) * nb + b;
-            dscale = 64.0f * f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(wj + (unit >> 5) * kTileBytes + kTileDOff) + (unit & 31)));
-        }
+        const float dscale = (row0 + e_row < rows) ? 64.0f * f16_bits_to_f32((uint16_t)d_bits) : 0.0f;
         uint32_t v[32];
         tmem_ld32(taddr + (uint32_t)((b & 1) * kTcN), v);  // blocks alternate between two accumulator tiles
 #pragma unroll
@@ -271,6 +284,7 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_tc_kernel(const TcParams p) {
             if (b + 1 < nb || r < 6) copy_b((r + 2) & 3);
             else asm volatile("cp.async.commit_group;" ::: "memory");  // keep one group per stage so that the count below holds
 
+            if (r == 3) load_d(b);  // the previous block's drain (at r == 1) is done with the old value
             // ---- this thread's 16 weights: MMA words jw = 4m .. 4m+3 of residue r of block (row, b) ----
             const uint32_t S0 = Sn[0], S1 = Sn[1], S2 = Sn[2];
             if (r == 0) {
@@ -288,8 +302,8 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_tc_kernel(const TcParams p) {
 #pragma unroll
                     for (int x = 0; x < 3; x++)
                         Sn2[x] = __ldg(reinterpret_cast<const uint32_t *>(tb_next + (m ? TC_WOFF(6 * (r - 6) + 3 + x) : TC_WOFF(6 * (r - 6) + x))));
-                    if (r == 7) scn = __ldg(reinterpret_cast<const uint2 *>(tb_next + kTileScaleOff + 8 * m));
                 }
+                if (r == 4 && b + 1 < nb) scn = __ldg(reinterpret_cast<const uint2 *>(tb_next + kTileScaleOff + 8 * m));  // used from the next block's r == 0
             }
             uint32_t ahi[8], alo[8];
             if (live) {

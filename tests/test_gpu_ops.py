@@ -258,6 +258,29 @@ def test_moe_group_is_a_stable_counting_sort(ops, synth):
     assert not empty["gcount"].any() and empty["work"].shape[0] == 0
 
 
+@pytest.mark.parametrize("n_expert,n_used,nseq,hot", [
+    (128, 8, 512, None),    # a full prefill tile
+    (128, 8, 5120, None),   # the largest tile one launch takes: 40960 pairs
+    (1024, 2, 33, None),    # the most experts, most of them empty
+    (8, 1, 1, None),        # a single pair
+    (16, 4, 300, 5),        # every token also picks expert 5: one group far longer than a warp's chunk
+])
+def test_moe_group_edges(ops, n_expert, n_used, nseq, hot):
+    rng = np.random.default_rng(n_expert + nseq)
+    ids = np.stack([rng.permutation(n_expert)[:n_used] for _ in range(nseq)]).astype(np.int32)
+    if hot is not None:
+        ids[:, 0] = hot
+    g = ops.moe_group(ids, n_expert, n_used)
+    flat = ids.ravel()
+    order = np.argsort(flat, kind="stable")
+    assert g["gcount"].tolist() == np.bincount(flat, minlength=n_expert).tolist()
+    assert g["gstart"].tolist() == (np.cumsum(g["gcount"]) - g["gcount"]).tolist()
+    assert np.array_equal(g["pslot"], order) and np.array_equal(g["ptoken"], order // n_used)
+    work = g["work"]
+    assert work.shape[0] == int(np.sum((g["gcount"] + 7) // 8))
+    assert int(work[:, 2].sum()) == flat.size and work[:, 2].min() >= 1 and work[:, 2].max() <= 8
+
+
 def test_embed_is_a_dequantized_row(ops, orc, synth):
     from llamd_rs_b200 import backend
 
