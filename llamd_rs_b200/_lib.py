@@ -114,6 +114,11 @@ SIGNATURES = {
     "llamd_fwd_ep_combine": (None, [vp, vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_matvec_grouped_x2_silu_quant": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]),
     "llamd_fwd_attention_meta_quant": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32, vp, vp, vp]),
+    "llamd_model_ep_p2p_export": (i32, [vp, vp]),
+    "llamd_model_ep_p2p_attach": (i32, [vp, vp, i32]),
+    "llamd_cuda_ep_ipc_export": (i32, [vp, vp]),
+    "llamd_cuda_ep_ipc_open": (vp, [vp]),
+    "llamd_cuda_ep_ipc_close": (None, [vp]),
     "llamd_fwd_act_f16_rm": (None, [vp, vp, vp, C.c_size_t]),
     "llamd_fwd_gemm_tokens_tc": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
     "llamd_fwd_expert_gemm_tc": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]),

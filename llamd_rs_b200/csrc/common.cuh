@@ -114,6 +114,25 @@ struct TailPlan {
 };
 extern TailPlan g_next_tail;  // set by the model before a launch; consumed and cleared by that launch
 
+// Expert parallelism without the return collective. Each rank maps the other ranks' expert-output buffers (CUDA IPC,
+// one process per GPU); the down projection of an owned expert then stores its rows straight into the HOME rank's
+// buffer over NVLink and bumps that rank's arrival counter, and the home rank's next kernel (the combine fused into the
+// following norm) waits for the expected number of arrivals instead of for an all-to-all.
+struct PeerOutPlan {
+    float *const *out_tab;            // device array [world]: each rank's [n_used][rows] output buffer
+    unsigned int *const *arrive_tab;  // device array [world]: each rank's arrival counter
+    int div;                          // slots per rank: slot s belongs to rank s / div, local slot s % div
+};
+extern PeerOutPlan g_next_peer_out;  // consumed and cleared by the next grouped matvec launch
+// What the next norm launch must see before it reads the expert outputs: *counter >= target (then it resets the counter).
+// The wait is bounded; when it runs out *status is set and the kernel goes on (the host reports the pass as failed).
+struct WaitPlan {
+    unsigned int *counter;
+    unsigned int target;
+    int *status;
+};
+extern WaitPlan g_next_wait;  // consumed and cleared by the next norm launch
+
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.
 void *scratch(int slot, size_t bytes);

@@ -121,6 +121,34 @@ int llamd_cuda_ep_init(int rank, int world, const void *id128) {
     return 0;
 }
 
+// One rank's handle for a buffer it allocated (64 bytes), and the mapping of a peer's handle into this process.
+// Used for the peer-written expert outputs: ranks are separate processes on one node.
+int llamd_cuda_ep_ipc_export(const void *dev, void *handle64) {
+    if (!dev || !handle64) return -1;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, const_cast<void *>(dev)) != cudaSuccess) {
+        set_error(cudaGetLastError(), "cudaIpcGetMemHandle");
+        return -1;
+    }
+    static_assert(sizeof(h) == 64, "ipc handle size");
+    memcpy(handle64, &h, 64);
+    return 0;
+}
+void *llamd_cuda_ep_ipc_open(const void *handle64) {
+    if (!handle64) return nullptr;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void *p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        set_error(cudaGetLastError(), "cudaIpcOpenMemHandle");
+        return nullptr;
+    }
+    return p;
+}
+void llamd_cuda_ep_ipc_close(void *mapped) {
+    if (mapped) cudaIpcCloseMemHandle(mapped);
+}
+
 void llamd_cuda_ep_finalize(void) {
     if (g_comm && g_nccl.CommDestroy) {
         cudaStreamSynchronize(stream());

@@ -67,6 +67,7 @@ struct MatvecParams {
     const float *xf, *xu;
     PrefetchPlan pf;  // the weights of the matvec that follows this launch (a hint for L2)
     TailPlan tail;    // gate+up launches: the slot's last CTA also produces the SiLU-gated, quantized activation
+    PeerOutPlan peer;  // expert parallelism: a slot's rows go to its home rank's buffer, followed by an arrival
 };
 
 enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2 };
@@ -293,9 +294,17 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
             if (MULTI) {
                 if (on && r == 0 && s < count) job.out[(long long)s_oidx[s] * job.rows + row0 + rl] = total;
             } else if (on && r == 0) {
-                job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
+                if (p.peer.out_tab)  // (grouped launches run one sequence per slot: s == 0)
+                    p.peer.out_tab[slot / p.peer.div][(size_t)(slot % p.peer.div) * job.rows + row0 + rl] = total;
+                else
+                    job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
             }
         }
+    }
+    if (!MULTI && p.peer.out_tab) {  // uniform over the launch; CTAs of slots this rank does not own left above
+        __threadfence_system();  // the rows are visible on the home GPU before the arrival is
+        __syncthreads();
+        if (tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
     }
     // ---- tail of a gate+up launch: silu(gate) * up and its Q8_K form, by the slot's last CTA ----
     if (!MULTI && NSEQ == 1 && p.tail.counter) {  // uniform over the launch
@@ -337,6 +346,14 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
     MatvecParams q = p;
     q.pf = g_next_prefetch;
     g_next_prefetch = PrefetchPlan{};
+    q.peer = PeerOutPlan{};
+    if (g_next_peer_out.out_tab) {
+        if (!MULTI && NSEQ == 1 && p.ids && p.njobs == 1)
+            q.peer = g_next_peer_out;
+        else
+            set_error_msg("matvec: peer outputs were planned for a launch that cannot carry them");
+        g_next_peer_out = PeerOutPlan{};
+    }
     q.tail = TailPlan{};
     if (g_next_tail.counter) {
         // only a grouped launch of two matrices whose rows are whole Q8_K blocks can take it

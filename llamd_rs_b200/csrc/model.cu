@@ -51,6 +51,9 @@ void llamd_fwd_ep_dispatch(const int32_t *ids, const float *ad, const int8_t *aq
 void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, float *down, int n_used, int n_embd, int n_expert);
 int llamd_cuda_ep_rank(void);
 int llamd_cuda_ep_world(void);
+int llamd_cuda_ep_ipc_export(const void *dev, void *handle64);
+void *llamd_cuda_ep_ipc_open(const void *handle64);
+void llamd_cuda_ep_ipc_close(void *mapped);
 void llamd_fwd_q8k_residue_major(const int8_t *aq, void *aq_rm, size_t nblocks);
 void llamd_fwd_act_f16_rm(const int8_t *aq, const float *ad, void *act16, size_t nblocks);
 void llamd_fwd_gemm_tokens_tc(const void *w0, const void *w1, const void *w2, const void *act16, float *o0, float *o1, float *o2,
@@ -131,6 +134,10 @@ struct Model {
     // expert parallelism (ep_world > 1): this rank holds experts [own_lo, own_hi)
     int ep_rank = 0, ep_world = 1, own_lo = 0, own_hi = 0;
     Buf ids_all, ad_all, aq_all, gate_all, up_all, aq2_all, ad2_all, down_all, recv_all;
+    // peer-written expert outputs (llamd_model_ep_p2p_attach): every rank's e_down and arrival counter, mapped here
+    int ep_p2p = 0;
+    Buf ep_arrive, ep_status, ep_out_tab, ep_arrive_tab;  // counter word, status word, device pointer tables [world]
+    std::vector<void *> ep_mapped;                         // what cudaIpcOpenMemHandle returned, to close
     // Opt-in phase profile (the counterpart of DeviceModel::profile, crates/llamd-runtime/src/device.rs:136-199):
     // events between the launches of an un-graphed pass; totals are never a throughput figure.
     bool profiling = false;
@@ -263,6 +270,15 @@ void queue_token(Model &m, int nseq) {
             cudaMemcpyAsync(m.trace_x.as<float>() + (size_t)il * m.max_seq * E, x, (size_t)nseq * E * sizeof(float), cudaMemcpyDeviceToDevice,
                             stream());
     };
+    // peer-written expert outputs: the norm that combines them waits for n_used x (CTAs per slot of the down projection) arrivals
+    bool ep_wait_pending = false;
+    auto plan_ep_wait = [&]() {
+        if (!ep_wait_pending) return;
+        const int rows_per_cta = 256 / (ffe / 256);
+        const unsigned target = (unsigned)nu * (unsigned)((E + rows_per_cta - 1) / rows_per_cta);
+        g_next_wait = WaitPlan{m.ep_arrive.as<unsigned int>(), target, m.ep_status.as<int>()};
+        ep_wait_pending = false;
+    };
     // what the down projection of layer il is followed by: the next layer's Q, K, V, or the head's first megabytes
     auto plan_after_down = [&](int il) {
         if (il + 1 < hp.n_layer)
@@ -278,6 +294,7 @@ void queue_token(Model &m, int nseq) {
         if (il == 0) {
             llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
         } else {
+            plan_ep_wait();
             llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
                                              m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
             trace_x(il - 1);
@@ -329,10 +346,20 @@ void queue_token(Model &m, int nseq) {
             llamd_fwd_silu_mul_quant(m.gate_all.as<float>(), m.up_all.as<float>(), nullptr, m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
                                      W * nu * ffe);
             plan_after_down(il);
-            llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
-                                              m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
-            llamd_fwd_ep_combine(m.down_all.as<float>(), m.recv_all.as<float>(), m.expert_ids.as<int32_t>(), m.e_down.as<float>(), nu, E,
-                                 hp.n_expert);
+            if (m.ep_p2p) {
+                // no return collective: an owned slot's rows go straight into its home rank's e_down (routing-order slot),
+                // each CTA bumps that rank's counter, and the home rank's next norm waits for all of them
+                g_next_peer_out = PeerOutPlan{m.ep_out_tab.as<float *>(), m.ep_arrive_tab.as<unsigned int *>(), nu};
+                llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
+                                                  m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
+                g_next_peer_out = PeerOutPlan{};
+                ep_wait_pending = true;
+            } else {
+                llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
+                                                  m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
+                llamd_fwd_ep_combine(m.down_all.as<float>(), m.recv_all.as<float>(), m.expert_ids.as<int32_t>(), m.e_down.as<float>(), nu,
+                                     E, hp.n_expert);
+            }
             if (m.trace)
                 cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
                                 cudaMemcpyDeviceToDevice, stream());
@@ -362,6 +389,7 @@ void queue_token(Model &m, int nseq) {
                             cudaMemcpyDeviceToDevice, stream());
     }
     // the last layer's combine, fused with the output norm
+    plan_ep_wait();
     llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
                                      m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
     trace_x(hp.n_layer - 1);
@@ -472,7 +500,13 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
         set_error(cudaGetLastError(), "token D2H");
         return -1;
     }
+    m.h_out[m.max_seq] = 0;
+    if (m.ep_p2p) cudaMemcpyAsync(m.h_out + m.max_seq, m.ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
     if (llamd_fwd_sync() != 0) return -1;  // THE ONE SYNCHRONISE
+    if (m.h_out[m.max_seq] != 0) {
+        m.err = "expert parallelism: a wait for the other ranks' expert rows ran out; the pass is incomplete";
+        return -1;
+    }
     for (int s = 0; s < nseq; s++) {
         if (m.h_out[s] < 0 || m.h_out[s] >= hp.n_vocab) {
             m.err = "argmax returned " + std::to_string(m.h_out[s]);
@@ -535,7 +569,9 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
         const size_t W = m->ep_world;
         ok = ok && m->ids_all.alloc(W * nu * 4) && m->ad_all.alloc(W * (E / 256) * 4) && m->aq_all.alloc(W * E) &&
              m->gate_all.alloc(W * nu * ffe * 4) && m->up_all.alloc(W * nu * ffe * 4) && m->aq2_all.alloc(W * nu * ffe) &&
-             m->ad2_all.alloc(W * nu * (ffe / 256) * 4) && m->down_all.alloc(W * nu * E * 4) && m->recv_all.alloc(W * nu * E * 4);
+             m->ad2_all.alloc(W * nu * (ffe / 256) * 4) && m->down_all.alloc(W * nu * E * 4) && m->recv_all.alloc(W * nu * E * 4) &&
+             m->ep_arrive.alloc(256) && m->ep_status.alloc(256) && m->ep_out_tab.alloc(W * sizeof(void *)) &&
+             m->ep_arrive_tab.alloc(W * sizeof(void *));
     }
     for (auto &l : m->layers) {
         ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
@@ -548,7 +584,7 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
              cudaMemcpyAsync(m->rope_tab.p, tab.data(), tab.size() * sizeof(float), cudaMemcpyHostToDevice, stream()) == cudaSuccess &&
              llamd_fwd_sync() == 0;
     }
-    ok = ok && cudaMallocHost((void **)&m->h_meta, 8 * S) == cudaSuccess && cudaMallocHost((void **)&m->h_out, 4 * S) == cudaSuccess;
+    ok = ok && cudaMallocHost((void **)&m->h_meta, 8 * S) == cudaSuccess && cudaMallocHost((void **)&m->h_out, 4 * (S + 1)) == cudaSuccess;  // + the peer-wait status word
     if (!ok) {
         llamd_model_free((llamd_model *)m);
         return nullptr;
@@ -573,8 +609,10 @@ void llamd_model_free(llamd_model *h) {
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
-                   &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all})
+                   &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
+                   &m->ep_arrive_tab})
         b->release();
+    for (void *p : m->ep_mapped) llamd_cuda_ep_ipc_close(p);
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
                    &m->pf.ids, &m->pf.w, &m->pf.logits, &m->pf.counter, &m->pf.gate, &m->pf.up, &m->pf.down, &m->pf.scores, &m->pf.meta,
                    &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work, &m->pf.aq_rm, &m->pf.aq2_rm})
@@ -959,10 +997,16 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
         set_error(cudaGetLastError(), "decode D2H");
         return -1;
     }
-    const int rc = llamd_fwd_sync();
+    m->h_out[m->max_seq] = 0;
+    if (m->ep_p2p) cudaMemcpyAsync(m->h_out + m->max_seq, m->ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
+    int rc = llamd_fwd_sync();
     if (ms_out) cudaEventElapsedTime(ms_out, e0, e1);
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
+    if (rc == 0 && m->h_out[m->max_seq] != 0) {
+        m->err = "expert parallelism: a wait for the other ranks' expert rows ran out; the tokens are not valid";
+        rc = -1;
+    }
     return rc;
 }
 
@@ -1017,6 +1061,49 @@ int llamd_model_profile_pass(llamd_model *h, int32_t token, int32_t pos, float *
         const int ph = m->prof_phase[i];
         if (ph >= 0 && ph < LLAMD_PH_COUNT) ms_out[ph] += ms;
     }
+    return 0;
+}
+
+// ---- expert parallelism with peer-written expert outputs (no return collective) ----
+// export: 128 bytes = the IPC handles of this rank's expert-output buffer and arrival counter.
+// attach: the 128-byte records of ALL ranks in rank order; maps the peers' buffers and switches the decode pass to
+// the form in which an owned expert's rows are stored straight into the home rank's buffer. Every rank must attach.
+int llamd_model_ep_p2p_export(llamd_model *h, void *out128) {
+    Model *m = (Model *)h;
+    if (!m || !out128 || m->ep_world < 2) return -1;
+    if (llamd_cuda_ep_ipc_export(m->e_down.p, out128) != 0) return -1;
+    return llamd_cuda_ep_ipc_export(m->ep_arrive.p, (char *)out128 + 64);
+}
+int llamd_model_ep_p2p_attach(llamd_model *h, const void *all, int world) {
+    Model *m = (Model *)h;
+    if (!m || !all || world != m->ep_world || world < 2) return -1;
+    std::vector<float *> outs(world);
+    std::vector<unsigned int *> arrs(world);
+    for (int r = 0; r < world; r++) {
+        if (r == m->ep_rank) {
+            outs[r] = m->e_down.as<float>();
+            arrs[r] = m->ep_arrive.as<unsigned int>();
+            continue;
+        }
+        void *a = llamd_cuda_ep_ipc_open((const char *)all + (size_t)r * 128);
+        void *b = llamd_cuda_ep_ipc_open((const char *)all + (size_t)r * 128 + 64);
+        if (a) m->ep_mapped.push_back(a);
+        if (b) m->ep_mapped.push_back(b);
+        if (!a || !b) {
+            m->err = "ep_p2p_attach: a peer's buffer could not be mapped";
+            return -1;
+        }
+        outs[r] = (float *)a;
+        arrs[r] = (unsigned int *)b;
+    }
+    if (cudaMemcpyAsync(m->ep_out_tab.p, outs.data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess ||
+        cudaMemcpyAsync(m->ep_arrive_tab.p, arrs.data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess)
+        return -1;
+    cudaMemsetAsync(m->ep_arrive.p, 0, 4, stream());
+    cudaMemsetAsync(m->ep_status.p, 0, 4, stream());
+    if (llamd_fwd_sync() != 0) return -1;
+    if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the collective
+    m->ep_p2p = 1;
     return 0;
 }
 

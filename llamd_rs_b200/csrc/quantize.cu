@@ -38,7 +38,7 @@ __device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ 
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                                                        const float *__restrict__ down, const float *__restrict__ cw, int n_used,
                                                        float *__restrict__ sum_out, const float *__restrict__ w, float *__restrict__ out,
-                                                       int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps) {
+                                                       int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps, const WaitPlan wait) {
     extern __shared__ __align__(16) float sx[];  // [n] values, then [n] squares
     float *ssq = sx + n;
     __shared__ float s_scale;
@@ -55,6 +55,23 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
         wv[u] = j < n4 ? __ldg(reinterpret_cast<const float4 *>(w) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     pdl_wait();
+    if (wait.counter) {
+        // Expert parallelism: the expert outputs read below are stored by other GPUs. Wait (bounded) for all of their
+        // arrivals, then clear the counter: nothing more arrives before this rank has passed its next dispatch.
+        if (tid == 0) {
+            bool seen = false;
+            for (int it = 0; it < (1 << 22) && !seen; it++) {
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait.counter) : "memory");
+                seen = v >= wait.target;
+                if (!seen && it > 32) __nanosleep(64);
+            }
+            if (!seen && wait.status) atomicExch(wait.status, 1);
+            *wait.counter = 0;
+            __threadfence();
+        }
+        __syncthreads();
+    }
     const float4 *x4 = reinterpret_cast<const float4 *>(x + (size_t)seq * n);
 #pragma unroll
     for (int u = 0; u < kMaxV; u++) {
@@ -77,7 +94,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
 #pragma unroll
                 for (int u = 0; u < kMaxV; u++) {
                     const int j = tid + u * 256;
-                    dv[q][u] = (j < n4 && e < n_used) ? d4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    dv[q][u] = (j < n4 && e < n_used) ? __ldcg(d4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);  // L2: may come from a peer
                 }
             }
 #pragma unroll
@@ -237,7 +254,7 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         return;
     }
     launch_kc(PDL_NORM, "rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
-             nullptr, nullptr, n, eps);
+             nullptr, nullptr, n, eps, WaitPlan{});
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
     if (n % 256 || (size_t)n * 8 > 48 * 1024) {
@@ -245,7 +262,7 @@ void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t
         return;
     }
     launch_kc(PDL_NORM, "rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
-             out, qs, d, n, eps);
+             out, qs, d, n, eps, WaitPlan{});
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
@@ -256,7 +273,7 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
         return;
     }
     launch_kc(PDL_NORM, "add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
-             w, out, qs, d, n, eps);
+             w, out, qs, d, n, eps, WaitPlan{});
 }
 // x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
 // forward.rs:586), then norm*w and its Q8_K form: the tail of one layer fused
@@ -267,8 +284,10 @@ void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const f
         set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
+    const WaitPlan wait = g_next_wait;  // set by the expert-parallel model when the rows come from peers
+    g_next_wait = WaitPlan{};
     launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
-             sum_out, w, out, qs, d, n, eps);
+             sum_out, w, out, qs, d, n, eps, wait);
 }
 void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
     if (hd % 4) {

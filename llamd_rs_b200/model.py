@@ -214,6 +214,20 @@ class CudaModel:
         if self._L.llamd_model_set_option(self._h, name.encode(), int(value)) != 0:
             raise backend.Malformed(f"set_option {name}={value}: " + self._err())
 
+    def ep_p2p_attach(self, gather) -> None:
+        """Expert parallelism without the return collective: exchange the IPC handles of every rank's expert-output
+        buffer and arrival counter and map the peers' buffers. `gather(bytes) -> list[bytes]` returns every rank's
+        record in rank order (e.g. torch.distributed.all_gather_object over gloo). Every rank must call it."""
+        buf = C.create_string_buffer(128)
+        if self._L.llamd_model_ep_p2p_export(self._h, buf) != 0:
+            raise backend.Other("ep_p2p export: " + (self._err() or backend._last_error()))
+        records = gather(bytes(buf.raw))
+        if any(len(r) != 128 for r in records):
+            raise backend.Malformed("ep_p2p: every rank's record must be 128 bytes")
+        blob = b"".join(records)
+        if self._L.llamd_model_ep_p2p_attach(self._h, C.create_string_buffer(blob, len(blob)), len(records)) != 0:
+            raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
+
     def set_prefill_attn(self, on: bool) -> None:
         """True (default): a prefill tile's attention runs on the register-tiled kernels; False: the per-token ones."""
         self._L.llamd_model_set_option(self._h, b"prefill_attn", int(on))

@@ -6,7 +6,9 @@ NCCL communicator, reloads the model with only its share of the experts and
 decodes the same sequence again together with the other ranks. Tokens and
 logits must be identical, bit for bit: the exchange moves Q8_K activations and
 f32 rows without touching them, and the home rank adds the expert outputs in
-routing order exactly as the single-GPU pass does.
+routing order exactly as the single-GPU pass does. The same is then repeated
+with the return collective replaced by stores into the home rank's buffer over
+NVLink (CUDA IPC) and arrival counters.
 """
 import json
 import os
@@ -58,10 +60,23 @@ def main():
     got_toks, got_logits = decode(m)            # captured graph with the NCCL exchange inside
     m.use_graph = False
     plain_toks, plain_logits = decode(m)        # plain queueing
-    ok = (got_toks == want_toks and plain_toks == want_toks
+
+    # the same with the return collective replaced by peer stores + arrival counters
+    def gather(b):
+        out = [None] * world
+        dist.all_gather_object(out, b)
+        return out
+
+    m.ep_p2p_attach(gather)
+    m.use_graph = True
+    p2p_toks, p2p_logits = decode(m)
+    m.use_graph = False
+    p2p_plain_toks, _ = decode(m)
+    ok = (got_toks == want_toks and plain_toks == want_toks and p2p_toks == want_toks and p2p_plain_toks == want_toks
           and np.array_equal(got_logits.view(np.uint32), want_logits.view(np.uint32))
-          and np.array_equal(plain_logits.view(np.uint32), want_logits.view(np.uint32)))
-    res = dict(rank=rank, ok=bool(ok), tokens=got_toks, want=want_toks, weight_bytes=m.weight_bytes(), single_bytes=single_bytes,
+          and np.array_equal(plain_logits.view(np.uint32), want_logits.view(np.uint32))
+          and np.array_equal(p2p_logits.view(np.uint32), want_logits.view(np.uint32)))
+    res = dict(rank=rank, ok=bool(ok), tokens=got_toks, p2p_tokens=p2p_toks, want=want_toks, weight_bytes=m.weight_bytes(), single_bytes=single_bytes,
                full_expert_bytes=full_bytes)
     m.free()
     M.ep_finalize()
