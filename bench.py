@@ -240,8 +240,8 @@ def main():
                     help="prefill workload: exact = integer tensor path (mma.sync), bit-identical to decode (default); dp4a = the same "
                          "bits, 8 tokens per weight pass; tc = tcgen05 on f16 pairs, tolerance level")
     ap.add_argument("--tile", type=int, default=0, help="prefill workload: tokens per prefill tile (0: min(prompt, 2048))")
-    ap.add_argument("--ep-p2p", action="store_true", help="with --parallelism ep: expert rows go to their home rank by peer stores "
-                    "and arrival counters instead of the all-to-all")
+    ap.add_argument("--ep-p2p", action="store_true", help="with --parallelism ep: requests and expert rows travel by peer stores "
+                    "and arrival counters instead of the two NCCL collectives per layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--prefetch", action="store_true", help="(experiment) matvec launches ask L2 for the next matvec's weights; measured slightly slower")
@@ -304,6 +304,7 @@ def main():
             return out
 
         m.ep_p2p_attach(_gather)
+        dist.barrier()
     if args.no_graph:
         m.use_graph = False
     if args.no_pdl:
@@ -437,8 +438,9 @@ def main():
         "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
         "config": {"workload": "decode_qwen3moe_q6k_b1", "layers": hp["n_layer"], "experts": "128x8", "hidden": 2048, "vocab": 151936,
                    "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
-                   "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU, NCCL all-gather dispatch + "
-                                    + ("peer stores with arrival counters" if args.ep_p2p else "all-to-all combine") + " per layer"
+                   "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU, "
+                                    + ("dispatch and combine by peer stores with arrival counters" if args.ep_p2p
+                                       else "NCCL all-gather dispatch + all-to-all combine") + " per layer"
                                    if ep else f"replicas x{world}"),
                    "token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "arith": "exact (reference order)",
                    "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch},

@@ -60,12 +60,16 @@ int llamd_cuda_ep_unique_id(void *out128);
 int llamd_cuda_ep_init(int rank, int world, const void *id128);
 void llamd_cuda_ep_finalize(void);
 int llamd_cuda_ep_rank(void);
-/* Peer-written expert outputs: the return collective of a MoE layer replaced by stores over NVLink into the home
- * rank's buffer plus an arrival counter (one process per GPU, buffers shared through CUDA IPC).
- * llamd_model_ep_p2p_export writes 128 bytes (two IPC handles); every rank collects all ranks' records in rank order
- * and calls llamd_model_ep_p2p_attach(m, all, world). The waits are bounded: if a rank's rows do not arrive, the pass
- * fails with a message in llamd_model_error instead of hanging. Same tokens as one GPU, bit for bit. */
-int llamd_model_ep_p2p_export(llamd_model *m, void *out128);
+/* Expert parallelism over peer memory: both collectives of a MoE layer replaced by stores over NVLink into the
+ * other ranks' buffers plus arrival counters (one process per GPU, buffers shared through CUDA IPC). Every rank pushes
+ * its request record (expert ids, Q8_K activation) into every rank's gathered buffers; an owned expert's rows go
+ * straight into the home rank's expert-output buffer.
+ * llamd_model_ep_p2p_export writes LLAMD_EP_P2P_RECORD bytes (six IPC handles); every rank collects all ranks'
+ * records in rank order and calls llamd_model_ep_p2p_attach(m, all, world) -- a synchronisation point: no rank may
+ * run a pass before every rank has attached. The waits are bounded: if a peer does not deliver, the pass fails with a
+ * message in llamd_model_error instead of hanging. Same tokens as one GPU, bit for bit. */
+#define LLAMD_EP_P2P_RECORD 384
+int llamd_model_ep_p2p_export(llamd_model *m, void *out_record);
 int llamd_model_ep_p2p_attach(llamd_model *m, const void *all, int world);
 int llamd_cuda_ep_ipc_export(const void *dev, void *handle64);
 void *llamd_cuda_ep_ipc_open(const void *handle64);

@@ -122,6 +122,7 @@ struct PeerOutPlan {
     float *const *out_tab;            // device array [world]: each rank's [n_used][rows] output buffer
     unsigned int *const *arrive_tab;  // device array [world]: each rank's arrival counter
     int div;                          // slots per rank: slot s belongs to rank s / div, local slot s % div
+    int all_arrive;                   // 1: CTAs of slots this rank does not own arrive too (they have read the request by then)
 };
 extern PeerOutPlan g_next_peer_out;  // consumed and cleared by the next grouped matvec launch
 // What the next norm launch must see before it reads the expert outputs: *counter >= target (then it resets the counter).
@@ -132,6 +133,16 @@ struct WaitPlan {
     int *status;
 };
 extern WaitPlan g_next_wait;  // consumed and cleared by the next norm launch
+// The request records (expert ids, Q8_K activation) of all ranks are pushed into this rank's buffers by the ranks
+// themselves; a grouped launch that reads them first waits until *counter has reached *epoch x world (counter and
+// epoch only grow; epoch is bumped by this rank's own push, which precedes the launch in the stream). Bounded.
+struct DispatchWait {
+    const unsigned int *counter;
+    const unsigned int *epoch;
+    unsigned int world;
+    int *status;
+};
+extern DispatchWait g_next_disp_wait;  // consumed and cleared by the next grouped matvec launch
 
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.

@@ -90,6 +90,29 @@ __global__ void ep_pick_kernel(const float *__restrict__ recv, const int32_t *__
     down[(size_t)s * n_embd + i] = recv[((size_t)owner * n_used + s) * n_embd + i];
 }
 
+// The dispatch without a collective: CTA `dst` of `world` copies this rank's request record (expert ids, activation
+// scales, activation quants) into slot `rank` of rank dst's gathered buffers (its own included) over NVLink, then
+// counts itself on dst's dispatch counter. CTA 0 also advances this rank's epoch, which the launches that follow
+// in the stream multiply by `world` to know how many arrivals to expect.
+__global__ void ep_push_kernel(const int32_t *__restrict__ ids, const float *__restrict__ ad, const int8_t *__restrict__ aq,
+                               int32_t *const *__restrict__ ids_tab, float *const *__restrict__ ad_tab, int8_t *const *__restrict__ aq_tab,
+                               unsigned int *const *__restrict__ disp_tab, unsigned int *__restrict__ epoch, int rank, int n_used, int blocks) {
+    pdl_trigger();
+    pdl_wait();
+    const int dst = blockIdx.x, tid = threadIdx.x;
+    const uint4 *src = reinterpret_cast<const uint4 *>(aq);
+    uint4 *q = reinterpret_cast<uint4 *>(aq_tab[dst] + (size_t)rank * blocks * 256);
+    for (int i = tid; i < blocks * 16; i += blockDim.x) q[i] = src[i];
+    if (tid < blocks) ad_tab[dst][(size_t)rank * blocks + tid] = ad[tid];
+    if (tid < n_used) ids_tab[dst][(size_t)rank * n_used + tid] = ids[tid];
+    __threadfence_system();  // the record is visible on dst before the arrival is
+    __syncthreads();
+    if (tid == 0) {
+        atomicAdd_system(disp_tab[dst], 1u);
+        if (dst == 0) *epoch = *epoch + 1;
+    }
+}
+
 }  // namespace llamd
 
 using namespace llamd;
@@ -119,6 +142,18 @@ int llamd_cuda_ep_init(int rank, int world, const void *id128) {
     g_ep_rank = rank;
     g_ep_world = world;
     return 0;
+}
+
+// Push this rank's request record to every rank (see ep_push_kernel). The tables are device arrays [world] of the
+// ranks' gathered buffers and dispatch counters.
+void llamd_fwd_ep_push(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *const *ids_tab, float *const *ad_tab,
+                       int8_t *const *aq_tab, unsigned int *const *disp_tab, unsigned int *epoch, int n_used, int blocks) {
+    if (g_ep_world < 2 || n_used > 256 || blocks > 256) {
+        set_error_msg("ep_push: needs an expert-parallel world, at most 256 experts per token and 256 blocks");
+        return;
+    }
+    launch_k("ep_push", ep_push_kernel, dim3(g_ep_world), dim3(256), 0, ids, ad, aq, ids_tab, ad_tab, aq_tab, disp_tab, epoch, g_ep_rank, n_used,
+             blocks);
 }
 
 // One rank's handle for a buffer it allocated (64 bytes), and the mapping of a peer's handle into this process.

@@ -68,6 +68,7 @@ struct MatvecParams {
     PrefetchPlan pf;  // the weights of the matvec that follows this launch (a hint for L2)
     TailPlan tail;    // gate+up launches: the slot's last CTA also produces the SiLU-gated, quantized activation
     PeerOutPlan peer;  // expert parallelism: a slot's rows go to its home rank's buffer, followed by an arrival
+    DispatchWait dwait;  // expert parallelism: the ids / activations are pushed by the peers; wait for all of them first
 };
 
 enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2 };
@@ -141,10 +142,30 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         __syncthreads();
     } else if (p.ids) {
         pdl_wait();  // the ids come from the router kernel
+        if (p.dwait.counter) {  // ... or from every rank's push: all of this layer's records must have landed
+            if (tid == 0) {
+                unsigned int ep;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ep) : "l"(p.dwait.epoch) : "memory");
+                const unsigned int target = ep * p.dwait.world;
+                bool seen = false;
+                for (int it = 0; it < (1 << 24) && !seen; it++) {  // a few seconds at the least
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.dwait.counter) : "memory");
+                    seen = (int)(v - target) >= 0;
+                    if (!seen && it > 32) __nanosleep(128);
+                }
+                if (!seen && p.dwait.status) atomicExch(p.dwait.status, 2);
+            }
+            __syncthreads();
+        }
         prefetch_issue(p.pf, blockIdx.x, gridDim.x);
-        int e = p.ids[slot];
+        int e = __ldcg(p.ids + slot);
         if (e < 0 || e >= p.n_expert) e = 0;
-        if (e < p.own_lo || e >= p.own_hi) return;  // another GPU's expert
+        if (e < p.own_lo || e >= p.own_hi) {  // another GPU's expert
+            // by now this CTA has read everything it needs of the request: the home rank may count it
+            if (p.peer.out_tab && p.peer.all_arrive && tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
+            return;
+        }
         expert_off = (long long)(e - p.own_lo) * p.expert_units;
     }
 
@@ -183,12 +204,13 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         for (int i = tid; i < n16; i += kThreads) {
             const int s = i / (nb * 16), o = i - s * nb * 16;
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
-            reinterpret_cast<uint4 *>(s_nat)[i] = __ldg(reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o);
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o;
+            reinterpret_cast<uint4 *>(s_nat)[i] = p.dwait.counter ? __ldcg(src) : __ldg(src);  // written by peers: from L2
         }
         for (int i = tid; i < NSEQ * nb; i += kThreads) {
             const int s = i / nb, o = i - s * nb;
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
-            s_ad[i] = __ldg(p.ad + a_idx * nb + o);
+            s_ad[i] = p.dwait.counter ? __ldcg(p.ad + a_idx * nb + o) : __ldg(p.ad + a_idx * nb + o);
         }
     } else {
         // ... produced here: one warp per 256-element block quantizes the f32 activation
@@ -346,6 +368,14 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
     MatvecParams q = p;
     q.pf = g_next_prefetch;
     g_next_prefetch = PrefetchPlan{};
+    q.dwait = DispatchWait{};
+    if (g_next_disp_wait.counter) {
+        if (!MULTI && NSEQ == 1 && p.ids)
+            q.dwait = g_next_disp_wait;
+        else
+            set_error_msg("matvec: a dispatch wait was planned for a launch that cannot carry it");
+        g_next_disp_wait = DispatchWait{};
+    }
     q.peer = PeerOutPlan{};
     if (g_next_peer_out.out_tab) {
         if (!MULTI && NSEQ == 1 && p.ids && p.njobs == 1)

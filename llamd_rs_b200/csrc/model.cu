@@ -54,6 +54,8 @@ int llamd_cuda_ep_world(void);
 int llamd_cuda_ep_ipc_export(const void *dev, void *handle64);
 void *llamd_cuda_ep_ipc_open(const void *handle64);
 void llamd_cuda_ep_ipc_close(void *mapped);
+void llamd_fwd_ep_push(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *const *ids_tab, float *const *ad_tab,
+                       int8_t *const *aq_tab, unsigned int *const *disp_tab, unsigned int *epoch, int n_used, int blocks);
 void llamd_fwd_q8k_residue_major(const int8_t *aq, void *aq_rm, size_t nblocks);
 void llamd_fwd_act_f16_rm(const int8_t *aq, const float *ad, void *act16, size_t nblocks);
 void llamd_fwd_gemm_tokens_tc(const void *w0, const void *w1, const void *w2, const void *act16, float *o0, float *o1, float *o2,
@@ -137,6 +139,7 @@ struct Model {
     // peer-written expert outputs (llamd_model_ep_p2p_attach): every rank's e_down and arrival counter, mapped here
     int ep_p2p = 0;
     Buf ep_arrive, ep_status, ep_out_tab, ep_arrive_tab;  // counter word, status word, device pointer tables [world]
+    Buf ep_disp, ep_epoch, ep_ids_tab, ep_ad_tab, ep_aq_tab, ep_disp_tab;  // dispatch counter, this rank's epoch, tables [world]
     std::vector<void *> ep_mapped;                         // what cudaIpcOpenMemHandle returned, to close
     // Opt-in phase profile (the counterpart of DeviceModel::profile, crates/llamd-runtime/src/device.rs:136-199):
     // events between the launches of an un-graphed pass; totals are never a throughput figure.
@@ -275,7 +278,8 @@ void queue_token(Model &m, int nseq) {
     auto plan_ep_wait = [&]() {
         if (!ep_wait_pending) return;
         const int rows_per_cta = 256 / (ffe / 256);
-        const unsigned target = (unsigned)nu * (unsigned)((E + rows_per_cta - 1) / rows_per_cta);
+        // every rank launches CTAs for every slot; owners arrive after their stores, the others after reading the request
+        const unsigned target = (unsigned)m.ep_world * (unsigned)nu * (unsigned)((E + rows_per_cta - 1) / rows_per_cta);
         g_next_wait = WaitPlan{m.ep_arrive.as<unsigned int>(), target, m.ep_status.as<int>()};
         ep_wait_pending = false;
     };
@@ -338,8 +342,17 @@ void queue_token(Model &m, int nseq) {
             // Expert parallelism: gather every rank's routed request, run the experts this
             // rank owns for all of them, return each token's rows to its home rank.
             const int W = m.ep_world;
-            llamd_fwd_ep_dispatch(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ids_all.as<int32_t>(),
-                                  m.ad_all.as<float>(), m.aq_all.as<int8_t>(), nu, eb);
+            if (m.ep_p2p) {
+                // every rank pushes its request record into every rank's gathered buffers; the gate/up launch waits for
+                // all of them (no collective)
+                llamd_fwd_ep_push(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ep_ids_tab.as<int32_t *>(),
+                                  m.ep_ad_tab.as<float *>(), m.ep_aq_tab.as<int8_t *>(), m.ep_disp_tab.as<unsigned int *>(),
+                                  m.ep_epoch.as<unsigned int>(), nu, eb);
+                g_next_disp_wait = DispatchWait{m.ep_disp.as<unsigned int>(), m.ep_epoch.as<unsigned int>(), (unsigned)W, m.ep_status.as<int>()};
+            } else {
+                llamd_fwd_ep_dispatch(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ids_all.as<int32_t>(),
+                                      m.ad_all.as<float>(), m.aq_all.as<int8_t>(), nu, eb);
+            }
             plan_experts(m, l.down_exps, m.ids_all.as<int32_t>(), W * nu);
             llamd_fwd_matvec_grouped_x2_owned(l.gate_exps.p, l.up_exps.p, m.ids_all.as<int32_t>(), m.aq_all.as<int8_t>(), m.ad_all.as<float>(),
                                               m.gate_all.as<float>(), m.up_all.as<float>(), eb, ffe, nu, W * nu, m.own_lo, m.own_hi);
@@ -349,7 +362,7 @@ void queue_token(Model &m, int nseq) {
             if (m.ep_p2p) {
                 // no return collective: an owned slot's rows go straight into its home rank's e_down (routing-order slot),
                 // each CTA bumps that rank's counter, and the home rank's next norm waits for all of them
-                g_next_peer_out = PeerOutPlan{m.ep_out_tab.as<float *>(), m.ep_arrive_tab.as<unsigned int *>(), nu};
+                g_next_peer_out = PeerOutPlan{m.ep_out_tab.as<float *>(), m.ep_arrive_tab.as<unsigned int *>(), nu, 1};
                 llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
                                                   m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
                 g_next_peer_out = PeerOutPlan{};
@@ -571,7 +584,9 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
              m->gate_all.alloc(W * nu * ffe * 4) && m->up_all.alloc(W * nu * ffe * 4) && m->aq2_all.alloc(W * nu * ffe) &&
              m->ad2_all.alloc(W * nu * (ffe / 256) * 4) && m->down_all.alloc(W * nu * E * 4) && m->recv_all.alloc(W * nu * E * 4) &&
              m->ep_arrive.alloc(256) && m->ep_status.alloc(256) && m->ep_out_tab.alloc(W * sizeof(void *)) &&
-             m->ep_arrive_tab.alloc(W * sizeof(void *));
+             m->ep_arrive_tab.alloc(W * sizeof(void *)) && m->ep_disp.alloc(256) && m->ep_epoch.alloc(256) &&
+             m->ep_ids_tab.alloc(W * sizeof(void *)) && m->ep_ad_tab.alloc(W * sizeof(void *)) && m->ep_aq_tab.alloc(W * sizeof(void *)) &&
+             m->ep_disp_tab.alloc(W * sizeof(void *));
     }
     for (auto &l : m->layers) {
         ok = ok && l.kc.alloc((size_t)max_kv * kvd * 4 * S) && l.vc.alloc((size_t)max_kv * kvd * 4 * S);
@@ -610,7 +625,7 @@ void llamd_model_free(llamd_model *h) {
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
-                   &m->ep_arrive_tab})
+                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab})
         b->release();
     for (void *p : m->ep_mapped) llamd_cuda_ep_ipc_close(p);
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
@@ -1064,45 +1079,50 @@ int llamd_model_profile_pass(llamd_model *h, int32_t token, int32_t pos, float *
     return 0;
 }
 
-// ---- expert parallelism with peer-written expert outputs (no return collective) ----
-// export: 128 bytes = the IPC handles of this rank's expert-output buffer and arrival counter.
-// attach: the 128-byte records of ALL ranks in rank order; maps the peers' buffers and switches the decode pass to
-// the form in which an owned expert's rows are stored straight into the home rank's buffer. Every rank must attach.
-int llamd_model_ep_p2p_export(llamd_model *h, void *out128) {
+// ---- expert parallelism over peer memory (no collective in the pass) ----
+// export: LLAMD_EP_P2P_RECORD bytes = the IPC handles of this rank's expert-output buffer, arrival counter, gathered
+// ids / scales / quants buffers and dispatch counter.
+// attach: the records of ALL ranks in rank order; maps the peers' buffers and switches the decode pass to the form in
+// which requests are pushed to the peers and an owned expert's rows are stored straight into the home rank's buffer.
+// Every rank must attach.
+static Buf *ep_shared_buf(Model &m, int i) {
+    Buf *b[6] = {&m.e_down, &m.ep_arrive, &m.ids_all, &m.ad_all, &m.aq_all, &m.ep_disp};
+    return b[i];
+}
+int llamd_model_ep_p2p_export(llamd_model *h, void *out) {
     Model *m = (Model *)h;
-    if (!m || !out128 || m->ep_world < 2) return -1;
-    if (llamd_cuda_ep_ipc_export(m->e_down.p, out128) != 0) return -1;
-    return llamd_cuda_ep_ipc_export(m->ep_arrive.p, (char *)out128 + 64);
+    if (!m || !out || m->ep_world < 2) return -1;
+    for (int i = 0; i < 6; i++)
+        if (llamd_cuda_ep_ipc_export(ep_shared_buf(*m, i)->p, (char *)out + 64 * i) != 0) return -1;
+    return 0;
 }
 int llamd_model_ep_p2p_attach(llamd_model *h, const void *all, int world) {
     Model *m = (Model *)h;
     if (!m || !all || world != m->ep_world || world < 2) return -1;
-    std::vector<float *> outs(world);
-    std::vector<unsigned int *> arrs(world);
+    std::vector<void *> tab[6];
+    for (int i = 0; i < 6; i++) tab[i].resize(world);
     for (int r = 0; r < world; r++) {
-        if (r == m->ep_rank) {
-            outs[r] = m->e_down.as<float>();
-            arrs[r] = m->ep_arrive.as<unsigned int>();
-            continue;
+        for (int i = 0; i < 6; i++) {
+            if (r == m->ep_rank) {
+                tab[i][r] = ep_shared_buf(*m, i)->p;
+                continue;
+            }
+            void *p = llamd_cuda_ep_ipc_open((const char *)all + (size_t)r * LLAMD_EP_P2P_RECORD + 64 * i);
+            if (!p) {
+                m->err = "ep_p2p_attach: a peer's buffer could not be mapped";
+                return -1;
+            }
+            m->ep_mapped.push_back(p);
+            tab[i][r] = p;
         }
-        void *a = llamd_cuda_ep_ipc_open((const char *)all + (size_t)r * 128);
-        void *b = llamd_cuda_ep_ipc_open((const char *)all + (size_t)r * 128 + 64);
-        if (a) m->ep_mapped.push_back(a);
-        if (b) m->ep_mapped.push_back(b);
-        if (!a || !b) {
-            m->err = "ep_p2p_attach: a peer's buffer could not be mapped";
-            return -1;
-        }
-        outs[r] = (float *)a;
-        arrs[r] = (unsigned int *)b;
     }
-    if (cudaMemcpyAsync(m->ep_out_tab.p, outs.data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess ||
-        cudaMemcpyAsync(m->ep_arrive_tab.p, arrs.data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess)
-        return -1;
-    cudaMemsetAsync(m->ep_arrive.p, 0, 4, stream());
-    cudaMemsetAsync(m->ep_status.p, 0, 4, stream());
+    Buf *dev[6] = {&m->ep_out_tab, &m->ep_arrive_tab, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab};
+    for (int i = 0; i < 6; i++)
+        if (cudaMemcpyAsync(dev[i]->p, tab[i].data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess) return -1;
+    // (the counters are zero since the model was created and only this protocol touches them: clearing them here
+    // could erase the arrival of a peer that attached first)
     if (llamd_fwd_sync() != 0) return -1;
-    if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the collective
+    if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the collectives
     m->ep_p2p = 1;
     return 0;
 }

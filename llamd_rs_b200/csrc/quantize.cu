@@ -60,11 +60,11 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
         // arrivals, then clear the counter: nothing more arrives before this rank has passed its next dispatch.
         if (tid == 0) {
             bool seen = false;
-            for (int it = 0; it < (1 << 22) && !seen; it++) {
+            for (int it = 0; it < (1 << 24) && !seen; it++) {  // a few seconds at the least
                 unsigned int v;
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait.counter) : "memory");
                 seen = v >= wait.target;
-                if (!seen && it > 32) __nanosleep(64);
+                if (!seen && it > 32) __nanosleep(128);
             }
             if (!seen && wait.status) atomicExch(wait.status, 1);
             *wait.counter = 0;

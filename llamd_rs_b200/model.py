@@ -81,6 +81,9 @@ def _bind():
     return L
 
 
+EP_P2P_RECORD = 384  # LLAMD_EP_P2P_RECORD: six 64-byte IPC handles
+
+
 def ep_init(rank: int, world: int, share) -> None:
     """Join the expert-parallel communicator. `share(bytes_or_None) -> bytes`
     hands rank 0's 128-byte id to every rank (e.g. a torch.distributed/gloo
@@ -215,15 +218,16 @@ class CudaModel:
             raise backend.Malformed(f"set_option {name}={value}: " + self._err())
 
     def ep_p2p_attach(self, gather) -> None:
-        """Expert parallelism without the return collective: exchange the IPC handles of every rank's expert-output
-        buffer and arrival counter and map the peers' buffers. `gather(bytes) -> list[bytes]` returns every rank's
-        record in rank order (e.g. torch.distributed.all_gather_object over gloo). Every rank must call it."""
-        buf = C.create_string_buffer(128)
+        """Expert parallelism over peer memory (no collective in the pass): exchange the IPC handles of every rank's
+        request and expert-output buffers and counters and map the peers' buffers. `gather(bytes) -> list[bytes]` returns every rank's
+        record in rank order (e.g. torch.distributed.all_gather_object over gloo). Every rank must call it, and the
+        ranks should meet at a barrier before the first pass: a rank waits a few seconds for its peers, not forever."""
+        buf = C.create_string_buffer(EP_P2P_RECORD)
         if self._L.llamd_model_ep_p2p_export(self._h, buf) != 0:
             raise backend.Other("ep_p2p export: " + (self._err() or backend._last_error()))
         records = gather(bytes(buf.raw))
-        if any(len(r) != 128 for r in records):
-            raise backend.Malformed("ep_p2p: every rank's record must be 128 bytes")
+        if any(len(r) != EP_P2P_RECORD for r in records):
+            raise backend.Malformed(f"ep_p2p: every rank's record must be {EP_P2P_RECORD} bytes")
         blob = b"".join(records)
         if self._L.llamd_model_ep_p2p_attach(self._h, C.create_string_buffer(blob, len(blob)), len(records)) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))

@@ -7,7 +7,7 @@ decodes the same sequence again together with the other ranks. Tokens and
 logits must be identical, bit for bit: the exchange moves Q8_K activations and
 f32 rows without touching them, and the home rank adds the expert outputs in
 routing order exactly as the single-GPU pass does. The same is then repeated
-with the return collective replaced by stores into the home rank's buffer over
+with both collectives replaced by stores into the other ranks' buffers over
 NVLink (CUDA IPC) and arrival counters.
 """
 import json
@@ -61,13 +61,14 @@ def main():
     m.use_graph = False
     plain_toks, plain_logits = decode(m)        # plain queueing
 
-    # the same with the return collective replaced by peer stores + arrival counters
+    # the same with both collectives replaced by peer stores + arrival counters
     def gather(b):
         out = [None] * world
         dist.all_gather_object(out, b)
         return out
 
     m.ep_p2p_attach(gather)
+    dist.barrier()
     m.use_graph = True
     p2p_toks, p2p_logits = decode(m)
     m.use_graph = False
