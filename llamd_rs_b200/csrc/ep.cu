@@ -14,6 +14,12 @@
 //             order, as the single-GPU pass does.
 // NCCL is loaded with dlopen when expert parallelism is first initialised, so a
 // single-GPU process never needs the library.
+//
+// Second form, after llamd_model_ep_p2p_attach: the same two exchanges as plain
+// stores into the other ranks' buffers over NVLink (mapped once through CUDA
+// IPC) with arrival counters: ep_push_kernel here for the dispatch, the
+// down-projection matvec's own epilogue for the return (matvec_q6k.cu), and
+// bounded waits in the consumers (the gate/up matvec, the combining norm).
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
