@@ -130,3 +130,92 @@ def test_expert_parallel_protocol_on_gloo(world):
     lines = [l for l in out.stdout.splitlines() if l.startswith("EP_PROTOCOL ")]
     assert out.returncode == 0 and lines, (out.stdout[-1000:], out.stderr[-2000:])
     assert json.loads(lines[0][len("EP_PROTOCOL "):]) == [True] * world
+
+
+# ---- the peer-memory exchange of expert parallelism, as a model -------------------------------
+# csrc/ep.cu + the waits in matvec_q6k.cu / quantize.cu order their accesses with two counters per rank and no
+# barrier. This is that protocol with the GPU taken out: ranks are step lists, a random scheduler picks any step whose
+# wait condition holds, and every read checks that it sees the layer it belongs to (a record or a row replaced too
+# early, or read before it arrived, shows up as a wrong tag).
+def _simulate_peer_exchange(world, layers, ctas, seed, all_arrive=True):
+    import random
+
+    rng = random.Random(seed)
+    n_used = 2
+    disp = [0] * world          # dispatch counter of each rank (only grows)
+    epoch = [0] * world         # each rank's own epoch (bumped by its push)
+    arrive = [0] * world        # arrival counter of each home rank (cleared by its norm)
+    rec = [[-1] * world for _ in range(world)]             # rec[dst][src]: layer tag of src's request record at dst
+    out = [[-1] * n_used for _ in range(world)]            # out[home][slot]: layer tag of the expert rows
+    owner = lambda home, slot, layer: (home + slot + layer) % world  # which rank owns that slot's expert
+    target_rows = (world if all_arrive else 1) * n_used * ctas
+
+    def steps(r):
+        for l in range(layers):
+            yield ("push", l)
+            # gate/up: one step per (home) after the dispatch wait; reads the home's record
+            for home in range(world):
+                yield ("gate_up", l, home)
+            # down: one step per (home, slot, cta): reads the id, owners store rows, then arrive
+            order = [(h, s, c) for h in range(world) for s in range(n_used) for c in range(ctas)]
+            rng.shuffle(order)
+            for h, s, c in order:
+                yield ("down", l, h, s, c)
+            yield ("norm", l)
+
+    its = [steps(r) for r in range(world)]
+    cur = [next(it) for it in its]
+    done = [False] * world
+    executed = 0
+    while not all(done):
+        ready = []
+        for r in range(world):
+            if done[r]:
+                continue
+            st = cur[r]
+            if st[0] == "gate_up" and disp[r] < epoch[r] * world:
+                continue  # the dispatch wait
+            if st[0] == "norm" and arrive[r] < target_rows:
+                continue  # the combine wait
+            ready.append(r)
+        assert ready, "deadlock: every rank waits"
+        r = rng.choice(ready)
+        st = cur[r]
+        if st[0] == "push":
+            for dst in range(world):
+                rec[dst][r] = st[1]
+                disp[dst] += 1
+            epoch[r] += 1
+        elif st[0] == "gate_up":
+            assert rec[r][st[2]] == st[1], f"rank {r} layer {st[1]}: record of rank {st[2]} is from layer {rec[r][st[2]]}"
+        elif st[0] == "down":
+            _, l, h, s, c = st
+            assert rec[r][h] == l, f"rank {r} layer {l}: a down CTA read a record of layer {rec[r][h]}"
+            if owner(h, s, l) == r:
+                out[h][s] = l
+                arrive[h] += 1
+            elif all_arrive:
+                arrive[h] += 1
+        else:  # norm: all rows of this layer are in; clear the counter
+            assert all(t == st[1] for t in out[r]), f"rank {r} layer {st[1]}: rows {out[r]}"
+            arrive[r] = 0
+        executed += 1
+        try:
+            cur[r] = next(its[r])
+        except StopIteration:
+            done[r] = True
+    return executed
+
+
+@pytest.mark.parametrize("world,ctas", [(2, 1), (2, 3), (4, 2), (8, 1)])
+def test_peer_exchange_protocol_orders_reads_and_writes(world, ctas):
+    for seed in range(40):
+        _simulate_peer_exchange(world, layers=5, ctas=ctas, seed=seed)
+
+
+def test_peer_exchange_needs_every_cta_to_arrive():
+    """If only the owners' CTAs counted, a rank could replace its record while a late CTA of another rank has not
+    read the old one: the model finds such a schedule."""
+    with pytest.raises(AssertionError):
+        for seed in range(400):
+            _simulate_peer_exchange(4, layers=6, ctas=2, seed=seed, all_arrive=False)
