@@ -90,7 +90,8 @@ __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s
     w[3] = u | ((s2 << 2) & 0x0C0C0C0Cu);
 }
 
-template <int NSEQ, bool MULTI, int ACT>
+// EP: the expert-parallel forms (requests pushed by peers, rows stored to peers); kept out of the other instantiations.
+template <int NSEQ, bool MULTI, int ACT, bool EP = false>
 __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         __syncthreads();
     } else if (p.ids) {
         pdl_wait();  // the ids come from the router kernel
-        if (p.dwait.counter) {  // ... or from every rank's push: all of this layer's records must have landed
+        if (EP && p.dwait.counter) {  // ... or from every rank's push: all of this layer's records must have landed
             if (tid == 0) {
                 unsigned int ep;
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ep) : "l"(p.dwait.epoch) : "memory");
@@ -159,11 +160,11 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
             __syncthreads();
         }
         prefetch_issue(p.pf, blockIdx.x, gridDim.x);
-        int e = __ldcg(p.ids + slot);
+        int e = EP ? __ldcg(p.ids + slot) : p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
         if (e < p.own_lo || e >= p.own_hi) {  // another GPU's expert
             // by now this CTA has read everything it needs of the request: the home rank may count it
-            if (p.peer.out_tab && p.peer.all_arrive && tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
+            if (EP && p.peer.out_tab && p.peer.all_arrive && tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
             return;
         }
         expert_off = (long long)(e - p.own_lo) * p.expert_units;
@@ -205,12 +206,12 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
             const int s = i / (nb * 16), o = i - s * nb * 16;
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
             const uint4 *src = reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o;
-            reinterpret_cast<uint4 *>(s_nat)[i] = p.dwait.counter ? __ldcg(src) : __ldg(src);  // written by peers: from L2
+            reinterpret_cast<uint4 *>(s_nat)[i] = (EP && p.dwait.counter) ? __ldcg(src) : __ldg(src);  // written by peers: from L2
         }
         for (int i = tid; i < NSEQ * nb; i += kThreads) {
             const int s = i / nb, o = i - s * nb;
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
-            s_ad[i] = p.dwait.counter ? __ldcg(p.ad + a_idx * nb + o) : __ldg(p.ad + a_idx * nb + o);
+            s_ad[i] = (EP && p.dwait.counter) ? __ldcg(p.ad + a_idx * nb + o) : __ldg(p.ad + a_idx * nb + o);
         }
     } else {
         // ... produced here: one warp per 256-element block quantizes the f32 activation
@@ -316,14 +317,14 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
             if (MULTI) {
                 if (on && r == 0 && s < count) job.out[(long long)s_oidx[s] * job.rows + row0 + rl] = total;
             } else if (on && r == 0) {
-                if (p.peer.out_tab)  // (grouped launches run one sequence per slot: s == 0)
+                if (EP && p.peer.out_tab)  // (grouped launches run one sequence per slot: s == 0)
                     p.peer.out_tab[slot / p.peer.div][(size_t)(slot % p.peer.div) * job.rows + row0 + rl] = total;
                 else
                     job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
             }
         }
     }
-    if (!MULTI && p.peer.out_tab) {  // uniform over the launch; CTAs of slots this rank does not own left above
+    if (EP && !MULTI && p.peer.out_tab) {  // uniform over the launch; CTAs of slots this rank does not own left above
         __threadfence_system();  // the rows are visible on the home GPU before the arrival is
         __syncthreads();
         if (tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
@@ -392,6 +393,14 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
         else
             set_error_msg("matvec: a SiLU tail was planned for a launch that cannot carry it");
         g_next_tail = TailPlan{};
+    }
+    if (NSEQ == 1 && !MULTI && ACT == ACT_Q8K && (q.peer.out_tab || q.dwait.counter)) {
+        launch_kc(PDL_GROUPED, "matvec_q6k_ep", matvec_q6k_kernel<1, false, ACT_Q8K, true>, grid, dim3(kThreads), smem, q);
+        return;
+    }
+    if (q.peer.out_tab || q.dwait.counter) {
+        set_error_msg("matvec: the expert-parallel forms exist for one sequence of Q8_K activations only");
+        return;
     }
     launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI, ACT>, grid, dim3(kThreads), smem, q);
 }
