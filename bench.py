@@ -242,6 +242,8 @@ def main():
     ap.add_argument("--tile", type=int, default=0, help="prefill workload: tokens per prefill tile (0: min(prompt, 2048))")
     ap.add_argument("--ep-p2p", action="store_true", help="with --parallelism ep: requests and expert rows travel by peer stores "
                     "and arrival counters instead of the two NCCL collectives per layer")
+    ap.add_argument("--gguf", default="", help="load the model through the GGUF reader instead of tensor by tensor: a path to an "
+                    "existing file, or a path that does not exist yet, where the same random-init model is written first")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--prefetch", action="store_true", help="(experiment) matvec launches ask L2 for the next matvec's weights; measured slightly slower")
@@ -295,7 +297,20 @@ def main():
     max_kv = args.prompt + 2 * (K + W) + 8 + (8 * (K + W) if args.batch_sweep else 0)
     t0 = time.time()
     max_seq = max([int(b) for b in args.batch_sweep.split(",")]) if args.batch_sweep else 1
-    m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
+    if args.gguf:
+        from llamd_rs_b200 import gguf as _gguf
+
+        if not os.path.exists(args.gguf):
+            if rank == 0:
+                n = _gguf.write_synthetic(args.gguf + ".part", hp, 0)
+                os.replace(args.gguf + ".part", args.gguf)
+                log(f"[rank 0] wrote {args.gguf}: {n / 2**30:.2f} GiB in {time.time() - t0:.1f}s")
+            if world > 1:
+                dist.barrier()
+        t0 = time.time()
+        m = CudaModel.open_gguf(args.gguf, max_kv=max_kv, max_seq=max_seq)
+    else:
+        m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
     if ep and args.ep_p2p:
         def _gather(b):

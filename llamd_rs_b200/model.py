@@ -165,6 +165,36 @@ class CudaModel:
                     m.set_expert(il, which, e, synth.expert_blocks(hp, seed, il, which, e))
         return m
 
+    @classmethod
+    def open_gguf(cls, path, max_kv: int, max_seq: int = 1) -> "CudaModel":
+        """``DeviceModel::load_batched(&Model::open(path)?, max_kv, max_seq)`` (crates/llamd-models/src/model.rs:108-131,
+        crates/llamd-runtime/src/device.rs:270): the file is mapped by the library and its tensors go to the device
+        from the mapping. Raises with the reference's error kinds."""
+        from . import gguf
+
+        if max_seq == 0 or max_seq > backend.MAX_SEQ:
+            raise backend.Malformed(f"device model: max_seq {max_seq} outside 1..={backend.MAX_SEQ}")
+        with gguf.Gguf.open(path) as g:
+            hp = g.hparams()
+            g.verify_present()
+            if hp["arch"] != "qwen3moe":
+                raise backend.Unsupported("device model: only MoE models are wired up; a dense FFN has no expert path")
+            if max_kv == 0:
+                raise backend.Malformed("device model: max_kv of 0")
+            if not backend.available():
+                raise backend.Unsupported("cuda: no device present (there is no CPU fallback)")
+            kind, err = C.c_int(0), C.create_string_buffer(512)
+            h = g._L.llamd_model_load_gguf(g._h, max_kv, max_seq, C.byref(kind), err, 512)
+            if not h:
+                gguf.raise_kind(kind.value, err.value.decode(errors="replace"))
+        m = cls.__new__(cls)
+        m._L = _bind()
+        m.hp = {k: hp[k] for k, _ in _Hparams._fields_}
+        m.max_kv, m.max_seq = max_kv, max_seq
+        m._h = h
+        m._use_graph = True
+        return m
+
     def set_tensor(self, layer: int, which: int, data, first_block: int = 0) -> None:
         if which in _F32:
             a = np.ascontiguousarray(data, dtype=np.float32).ravel()

@@ -25,12 +25,12 @@ def built():
 def declared_symbols(header):
     text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(llamd_(?:cuda|fwd|model)_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(llamd_(?:cuda|fwd|model|gguf)_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol(built):
     L = C.CDLL(built.SO)
-    names = declared_symbols("llamd_cuda.h") + declared_symbols("llamd_cuda_model.h")
+    names = declared_symbols("llamd_cuda.h") + declared_symbols("llamd_cuda_model.h") + declared_symbols("llamd_gguf.h")
     assert len(names) > 80
     missing = [n for n in names if not hasattr(L, n)]
     assert not missing, f"declared but not exported: {missing}"
@@ -41,14 +41,18 @@ def test_python_binding_covers_the_header(built):
     declared = set(declared_symbols("llamd_cuda.h"))
     assert declared <= bound, f"unbound: {sorted(declared - bound)}"
     built.lib()  # resolves every bound symbol or raises
+    from llamd_rs_b200 import gguf
+
+    assert set(declared_symbols("llamd_gguf.h")) <= set(gguf.SIGNATURES)
+    gguf._bind()
 
 
 def test_headers_cite_the_reference_and_compile_as_c(built, tmp_path):
-    for h in ("llamd_cuda.h", "llamd_cuda_model.h"):
+    for h in ("llamd_cuda.h", "llamd_cuda_model.h", "llamd_gguf.h"):
         text = open(os.path.join(ROOT, "include", h)).read()
         assert "crates/llamd-r" in text, "each header cites the reference interface it replaces"
     src = tmp_path / "t.c"
-    src.write_text('#include "llamd_cuda.h"\n#include "llamd_cuda_model.h"\nint main(void){return LLAMD_T_FFN_DOWN_EXPS==14?0:1;}\n')
+    src.write_text('#include "llamd_cuda.h"\n#include "llamd_cuda_model.h"\n#include "llamd_gguf.h"\nint main(void){return LLAMD_T_FFN_DOWN_EXPS==14?0:1;}\n')
     import subprocess
 
     subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(tmp_path / "t")])
