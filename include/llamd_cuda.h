@@ -64,6 +64,9 @@ unsigned long long llamd_fwd_launch_count(void);
 /* Programmatic dependent launch of the decode-path kernels: 1 (default) lets a
  * kernel's weight prefetch overlap the previous kernel's tail; 0 serialises. */
 void llamd_fwd_set_pdl(int on);
+/* Batched decode (nseq > 1) of matrices too small to fill the GPU with one CTA per 256 (row, block) units: the
+ * sequences are cut into groups of g per CTA (default 2; 0 = one CTA takes all nseq). Results do not depend on g. */
+void llamd_fwd_set_batch_group(int g);
 /* The library's stream as a cudaStream_t, for callers that time with events. */
 void *llamd_fwd_stream(void);
 
@@ -326,6 +329,22 @@ void llamd_fwd_ep_dispatch(const int32_t *ids, const float *ad, const int8_t *aq
                            int8_t *aq_all, int n_used, int blocks);
 void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, float *down, int n_used, int n_embd,
                           int n_expert);
+
+/* ---- the operations of `llamd_tensor::Backend` (crates/llamd-tensor/src/lib.rs:148-174) in their general row-wise
+ * form, with CpuBackend's arithmetic (crates/llamd-cpu/src/lib.rs:55-225): every sum one in-order f32 chain from +0.0.
+ * Device pointers; `add` is llamd_fwd_add above. ---- */
+void llamd_fwd_rms_norm_rows(const float *x, float *out, int n, int rows, float eps); /* cpu/lib.rs:55-75: no weight */
+void llamd_fwd_softmax_rows(const float *x, float *out, int n, int rows);            /* :81-101 */
+void llamd_fwd_silu(const float *x, float *out, size_t n);                            /* :103-106 */
+void llamd_fwd_mul(const float *a, const float *b, float *out, size_t n);             /* :112-114 */
+void llamd_fwd_scale(const float *x, float by, float *out, size_t n);                 /* :116-118 */
+/* w [m rows][k], x [n rows][k] -> out [n][m], out[j*m+i] (:126-149); any k. */
+void llamd_fwd_matmul_f32(const float *w, const float *x, float *out, int k, int m, int n);
+/* NeoX pairing (i, i + head_dim/2) per head (:158-209). sincos [rows][head_dim/2][2] = (sin, cos) of
+ * theta = pos*freq_scale / freq_base^(2i/head_dim), tabulated by the caller with the host libm the reference calls. */
+void llamd_fwd_rope_rows(const float *x, float *out, int row_len, int rows, int head_dim, const float *sincos);
+/* out[i] = table[ids[i]] (:211-224); the caller has refused ids outside the table. */
+void llamd_fwd_get_rows_f32(const float *table, const uint32_t *ids, float *out, int row_len, int n_ids);
 
 /* llamd_fwd_matvec_f32 for the ntok tokens of a tile: out[t][row] = fold(-0.0, +) of w[row][i]*x[t][i], i
  * ascending (crates/llamd-models/src/model.rs:253-263). w [rows][k] f32, x [ntok][k], out [ntok][rows]; k % 4 == 0. */

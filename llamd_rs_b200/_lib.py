@@ -36,6 +36,15 @@ SIGNATURES = {
     "llamd_fwd_stream": (vp, []),
     "llamd_fwd_launch_count": (C.c_ulonglong, []),
     "llamd_fwd_set_pdl": (None, [i32]),
+    "llamd_fwd_set_batch_group": (None, [i32]),
+    "llamd_fwd_rms_norm_rows": (None, [vp, vp, i32, i32, f32]),
+    "llamd_fwd_softmax_rows": (None, [vp, vp, i32, i32]),
+    "llamd_fwd_silu": (None, [vp, vp, sz]),
+    "llamd_fwd_mul": (None, [vp, vp, vp, sz]),
+    "llamd_fwd_scale": (None, [vp, f32, vp, sz]),
+    "llamd_fwd_matmul_f32": (None, [vp, vp, vp, i32, i32, i32]),
+    "llamd_fwd_rope_rows": (None, [vp, vp, i32, i32, i32, vp]),
+    "llamd_fwd_get_rows_f32": (None, [vp, vp, vp, i32, i32]),
     "llamd_fwd_repack_q6k_at": (None, [vp, vp, sz, sz]),
     "llamd_fwd_timer_start": (i32, []),
     "llamd_fwd_timer_stop": (i32, [C.POINTER(f32)]),

@@ -46,6 +46,7 @@ extern unsigned long long g_launches;
 // kernel has completed and flushed, and every kernel calls it, so completion
 // is transitive along the stream. Without the attribute both are no-ops.
 extern int g_pdl;
+extern int g_batch_group;  // matvec_q6k.cu: sequences per CTA for small ungrouped matrices at batch > 1
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

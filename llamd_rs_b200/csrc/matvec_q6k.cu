@@ -92,7 +92,7 @@ __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s
 
 // EP: the expert-parallel forms (requests pushed by peers, rows stored to peers); kept out of the other instantiations.
 template <int NSEQ, bool MULTI, int ACT, bool EP = false>
-__global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel(const MatvecParams p) {
+__global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1)) matvec_q6k_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
     // shared memory: [act: NSEQ*nb*132 words][ex: NSEQ*8*257 floats, aliased with the natural-order staging]
@@ -114,6 +114,9 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
     const int tid = threadIdx.x;
     const bool active = tid < rows_here * nb;
     const int row_l = tid / nb, b = tid - row_l * nb;
+    // ungrouped launches may be cut into groups of NSEQ sequences, one "slot" per group (small matrices at batch > 1:
+    // more CTAs for the same rows; the weights are re-read from L2)
+    const int seq0 = (!MULTI && !p.ids) ? slot * NSEQ : 0;
 
     // expert id of this slot (grouped forms); an id outside the tensor reads
     // expert 0: the host wrappers refuse such ids before any launch.
@@ -204,13 +207,13 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         const int n16 = NSEQ * nb * 16;
         for (int i = tid; i < n16; i += kThreads) {
             const int s = i / (nb * 16), o = i - s * nb * 16;
-            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
             const uint4 *src = reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o;
             reinterpret_cast<uint4 *>(s_nat)[i] = (EP && p.dwait.counter) ? __ldcg(src) : __ldg(src);  // written by peers: from L2
         }
         for (int i = tid; i < NSEQ * nb; i += kThreads) {
             const int s = i / nb, o = i - s * nb;
-            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
             s_ad[i] = (EP && p.dwait.counter) ? __ldcg(p.ad + a_idx * nb + o) : __ldg(p.ad + a_idx * nb + o);
         }
     } else {
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
         const int warp = tid >> 5, lane = tid & 31;
         for (int blk = warp; blk < NSEQ * nb; blk += kThreads / 32) {
             const int s = blk / nb, o = blk - s * nb;
-            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : s);
+            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
             const size_t base = ((size_t)a_idx * nb + o) * 256 + lane * 8;
             const float4 g0 = *reinterpret_cast<const float4 *>(p.xf + base), g1 = *reinterpret_cast<const float4 *>(p.xf + base + 4);
             float v[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
@@ -320,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
                 if (EP && p.peer.out_tab)  // (grouped launches run one sequence per slot: s == 0)
                     p.peer.out_tab[slot / p.peer.div][(size_t)(slot % p.peer.div) * job.rows + row0 + rl] = total;
                 else
-                    job.out[((long long)s + slot) * job.rows + row0 + rl] = total;
+                    job.out[((long long)s + (p.ids ? slot : seq0)) * job.rows + row0 + rl] = total;
             }
         }
     }
@@ -353,6 +356,10 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : 1) matvec_q6k_kernel
 }
 
 static size_t matvec_smem_bytes(int nseq, int nb) { return matvec_ad_offset(nseq, nb) + (size_t)nseq * nb * 4; }
+
+// sequences per CTA for small ungrouped matrices at batch > 1 (0: never split), and what "small" means
+int g_batch_group = 2;  // set through llamd_fwd_set_batch_group
+constexpr int kBatchSplitMaxCtas = 512;
 
 template <int NSEQ, bool MULTI = false, int ACT = ACT_Q8K>
 static void launch_t(const MatvecParams &p, dim3 grid) {
@@ -449,6 +456,14 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
     p.xu = xu;
     p.own_lo = own_lo;
     p.own_hi = own_hi;
+    // Small matrices at batch > 1: one CTA per 256 (row, block) units leaves most SMs with a single CTA that does nseq
+    // times the integer work. Cut the sequences into groups of g (a divisor of nseq): nseq / g times the CTAs.
+    if (!ids && nseq > 1 && g_batch_group > 0 && p.ctas_per_slot <= kBatchSplitMaxCtas) {
+        int g = g_batch_group < nseq ? g_batch_group : nseq;
+        while (nseq % g) g--;
+        p.n_slots = nseq / g;
+        nseq = g;
+    }
     const dim3 grid(p.ctas_per_slot * p.n_slots);
     if (act_mode == ACT_SILU) {
         if (nseq != 1 || !xf || !xu) {

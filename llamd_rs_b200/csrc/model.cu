@@ -744,6 +744,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         m->prefill_tile = value;
         return 0;
     }
+    if (!strcmp(name, "batch_group")) {
+        llamd_fwd_set_batch_group(value);
+        if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other grouping
+        return 0;
+    }
     if (!strcmp(name, "pdl")) {
         llamd_fwd_set_pdl(value);
         if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded in the other mode

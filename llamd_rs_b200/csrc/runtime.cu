@@ -176,6 +176,8 @@ unsigned long long llamd_fwd_launch_count(void) { return g_launches; }
 // Programmatic dependent launch on (default) or off, for A/B runs. A captured
 // graph keeps the mode it was recorded in.
 void llamd_fwd_set_pdl(int on) { g_pdl = on == 1 ? 7 : on; }
+// Batched decode: sequences per CTA for the small ungrouped matrices (0: one CTA takes all sequences).
+void llamd_fwd_set_batch_group(int g) { g_batch_group = g < 0 ? 0 : g; }
 void *llamd_fwd_stream(void) { return (void *)stream(); }
 
 // Device-time stopwatch on the library stream (CUDA events).

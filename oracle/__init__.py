@@ -194,6 +194,13 @@ def mul(a, b) -> np.ndarray:
     return out
 
 
+def scale(x, by: float) -> np.ndarray:
+    x = _f32(x)
+    out = np.zeros_like(x)
+    lib().orc_scale(_p(x), C.c_float(by), C.c_int64(x.size), _p(out))
+    return out
+
+
 def matmul(w, x) -> np.ndarray:
     """w [m rows of k], x [n rows of k] -> [n, m] (reference layout out[j*m+i])."""
     w, x = _f32(w), _f32(x)
