@@ -91,7 +91,9 @@ __device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s
 }
 
 // EP: the expert-parallel forms (requests pushed by peers, rows stored to peers); kept out of the other instantiations.
-template <int NSEQ, bool MULTI, int ACT, bool EP = false>
+// EXTRA: the optional L2 prefetch plan and the SiLU tail. Both are off by default, and their code in the plain kernel
+// cost every launch ~0.3 us and lm_head 3 % of its bandwidth, so they too are an instantiation of their own.
+template <int NSEQ, bool MULTI, int ACT, bool EP = false, bool EXTRA = false>
 __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1)) matvec_q6k_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int nb = p.nb;
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
             }
             __syncthreads();
         }
-        prefetch_issue(p.pf, blockIdx.x, gridDim.x);
+        if (EXTRA) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
         int e = EP ? __ldcg(p.ids + slot) : p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
         if (e < p.own_lo || e >= p.own_hi) {  // another GPU's expert
@@ -197,24 +199,21 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
     // Ungrouped: the weight loads above do not depend on the previous kernel and
     // are in flight while it finishes; the activations below do.
     if (!MULTI && !p.ids) {
-        if (!p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
+        if (EXTRA && !p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
         pdl_wait();
-        if (p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
+        if (EXTRA && p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
     }
     // ---- stage the activations ----------------------------------------
     // natural order bytes first ...
     if (ACT == ACT_Q8K) {
+        // (the block scales are read where they are used, straight from global memory: staging them here put a second
+        // dependent round trip in front of the barrier and cost every launch ~0.4 us)
         const int n16 = NSEQ * nb * 16;
         for (int i = tid; i < n16; i += kThreads) {
             const int s = i / (nb * 16), o = i - s * nb * 16;
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
             const uint4 *src = reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o;
             reinterpret_cast<uint4 *>(s_nat)[i] = (EP && p.dwait.counter) ? __ldcg(src) : __ldg(src);  // written by peers: from L2
-        }
-        for (int i = tid; i < NSEQ * nb; i += kThreads) {
-            const int s = i / nb, o = i - s * nb;
-            const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
-            s_ad[i] = (EP && p.dwait.counter) ? __ldcg(p.ad + a_idx * nb + o) : __ldg(p.ad + a_idx * nb + o);
         }
     } else {
         // ... produced here: one warp per 256-element block quantizes the f32 activation
@@ -289,7 +288,14 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         const float dw = f16_bits_to_f32(dbits);
 #pragma unroll
         for (int s = 0; s < NSEQ; s++) {
-            const float dsc = __fmul_rn(dw, s_ad[s * nb + b]);
+            float adv;
+            if (ACT == ACT_Q8K) {
+                const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
+                adv = (EP && p.dwait.counter) ? __ldcg(p.ad + a_idx * nb + b) : __ldg(p.ad + a_idx * nb + b);
+            } else {
+                adv = s_ad[s * nb + b];  // produced by this CTA's quantizer
+            }
+            const float dsc = __fmul_rn(dw, adv);
 #pragma unroll
             for (int r = 0; r < 8; r++)
                 s_ex[(s * 8 + r) * kExStride + tid] = __fmul_rn(dsc, (float)(aux[s][r] >> 2));
@@ -333,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         if (tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
     }
     // ---- tail of a gate+up launch: silu(gate) * up and its Q8_K form, by the slot's last CTA ----
-    if (!MULTI && NSEQ == 1 && p.tail.counter) {  // uniform over the launch
+    if (EXTRA && !MULTI && NSEQ == 1 && p.tail.counter) {  // uniform over the launch
         __shared__ bool s_last;
         __threadfence();  // this CTA's rows are visible before its arrival is
         __syncthreads();
@@ -400,6 +406,11 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
         else
             set_error_msg("matvec: a SiLU tail was planned for a launch that cannot carry it");
         g_next_tail = TailPlan{};
+    }
+    const bool extra = q.tail.counter || q.pf.ids || q.pf.bytes[0] || q.pf.bytes[1] || q.pf.bytes[2];
+    if (NSEQ == 1 && !MULTI && ACT == ACT_Q8K && extra && !(q.peer.out_tab || q.dwait.counter)) {
+        launch_kc(p.ids ? PDL_GROUPED : PDL_MATVEC, "matvec_q6k_extra", matvec_q6k_kernel<1, false, ACT_Q8K, false, true>, grid, dim3(kThreads), smem, q);
+        return;
     }
     if (NSEQ == 1 && !MULTI && ACT == ACT_Q8K && (q.peer.out_tab || q.dwait.counter)) {
         launch_kc(PDL_GROUPED, "matvec_q6k_ep", matvec_q6k_kernel<1, false, ACT_Q8K, true>, grid, dim3(kThreads), smem, q);
