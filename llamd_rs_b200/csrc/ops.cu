@@ -256,6 +256,104 @@ __global__ void __launch_bounds__(128) matvec_q8_0_kernel(const uint8_t *__restr
     for (int s = 0; s < NSEQ; s++) out[(size_t)s * rows + row] = acc[s];
 }
 
+// The same result with the row's work spread over a CTA. Above, one thread unpacks, converts, multiplies and adds
+// every element of its row alone and is bound by its own instruction latency (~20 cycles per element). Here a CTA owns
+// 32 rows: seven producer warps turn 8 blocks (256 columns) of the 32 rows into f32 weights d*q in shared memory,
+// [column][row] so that a lane per row reads without bank conflicts, while one chain warp per sequence (lane = row)
+// walks acc = acc + w*x over the previous 256 columns: only the add is on the dependent chain (~4 cycles per element).
+// Raw blocks are loaded two chunks ahead into registers, converted one chunk ahead, double-buffered in shared memory.
+constexpr int kQ80ChunkBlocks = 8;
+constexpr int kQ80Producers = 224;  // 7 warps
+template <int NSEQ>
+__global__ void __launch_bounds__(kQ80Producers + 32 * NSEQ) matvec_q8_0_rows_kernel(const uint8_t *__restrict__ tiled, const float *__restrict__ x,
+                                                                                     float *__restrict__ out, int blocks, int rows) {
+    extern __shared__ __align__(16) float smem_f[];
+    float *s_w = smem_f;                                      // [2][kQ80ChunkBlocks * 32 columns][32 rows]
+    float *sx = smem_f + 2 * kQ80ChunkBlocks * 32 * 32;       // [NSEQ][k]
+    pdl_trigger();
+    pdl_wait();
+    const int k = blocks * 32, tid = threadIdx.x;
+    const bool producer = tid < kQ80Producers;
+    const int n_chunks = (blocks + kQ80ChunkBlocks - 1) / kQ80ChunkBlocks;
+    const uint8_t *tile0 = tiled + (size_t)blockIdx.x * blocks * kQ80TileBytes;  // this CTA's 32 rows, block 0
+    constexpr int kItems = kQ80ChunkBlocks * 64;                                 // (block, half, row): 16 weights each
+    constexpr int kPer = (kItems + kQ80Producers - 1) / kQ80Producers;           // 3
+    uint4 raw[kPer];
+    uint16_t rawd[kPer];
+    auto load_chunk = [&](int ch) {
+#pragma unroll
+        for (int u = 0; u < kPer; u++) {
+            const int item = tid + u * kQ80Producers;
+            const int bl = item >> 6, h = (item >> 5) & 1, r = item & 31;
+            raw[u] = make_uint4(0, 0, 0, 0);
+            rawd[u] = 0;
+            if (item < kItems && ch * kQ80ChunkBlocks + bl < blocks) {
+                const uint8_t *t = tile0 + (size_t)(ch * kQ80ChunkBlocks + bl) * kQ80TileBytes;
+                raw[u] = __ldg(reinterpret_cast<const uint4 *>(t + 512 * h) + r);
+                rawd[u] = __ldg(reinterpret_cast<const uint16_t *>(t + 1024) + r);
+            }
+        }
+    };
+    auto store_chunk = [&](int buf) {
+        float *dst = s_w + buf * (kQ80ChunkBlocks * 32 * 32);
+#pragma unroll
+        for (int u = 0; u < kPer; u++) {
+            const int item = tid + u * kQ80Producers;
+            if (item < kItems) {
+                const int bl = item >> 6, h = (item >> 5) & 1, r = item & 31;
+                const float d = f16_bits_to_f32(rawd[u]);
+                const uint32_t ws[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    dst[(bl * 32 + h * 16 + j) * 32 + r] = __fmul_rn(d, (float)(int8_t)(ws[j >> 2] >> (8 * (j & 3))));
+            }
+        }
+    };
+    if (producer) load_chunk(0);
+    for (int i = tid; i < NSEQ * k; i += blockDim.x) sx[i] = x[i];
+    if (producer) {
+        store_chunk(0);
+        if (n_chunks > 1) load_chunk(1);
+    }
+    __syncthreads();
+    const int seq = (tid - kQ80Producers) >> 5, lane = tid & 31;  // chain warps
+    float acc = -0.0f;
+    for (int ch = 0; ch < n_chunks; ch++) {
+        if (producer) {
+            if (ch + 1 < n_chunks) store_chunk((ch + 1) & 1);
+            if (ch + 2 < n_chunks) load_chunk(ch + 2);
+        } else {
+            const float *w = s_w + (ch & 1) * (kQ80ChunkBlocks * 32 * 32) + lane;
+            const float *xs = sx + (size_t)seq * k + ch * kQ80ChunkBlocks * 32;
+            const int ncol = min(kQ80ChunkBlocks, blocks - ch * kQ80ChunkBlocks) * 32;
+            // 16 columns at a time, the next 16 loaded while these are added: the loads and the multiplies stay off
+            // the chain, which is then the 16 dependent adds (ncol is a multiple of 32)
+            float wv[16], xv[16];
+            auto fetch = [&](int c0) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) wv[j] = w[(c0 + j) * 32];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 v = *reinterpret_cast<const float4 *>(xs + c0 + 4 * j);
+                    xv[4 * j] = v.x, xv[4 * j + 1] = v.y, xv[4 * j + 2] = v.z, xv[4 * j + 3] = v.w;
+                }
+            };
+            fetch(0);
+            for (int c0 = 0; c0 < ncol; c0 += 16) {
+                float pr[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) pr[j] = __fmul_rn(wv[j], xv[j]);
+                if (c0 + 16 < ncol) fetch(c0 + 16);
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, pr[j]);
+            }
+        }
+        __syncthreads();
+    }
+    const int row = blockIdx.x * 32 + lane;
+    if (!producer && row < rows) out[(size_t)seq * rows + row] = acc;
+}
+
 // ---- QK-norm + RoPE (+ KV store) -----------------------------------------
 // crates/llamd-runtime/src/layer.rs:120-153, crates/llamd-cpu/src/lib.rs:158-209.
 // One CTA of hd/2 threads per head; thread 0 walks the sum of squares. The
@@ -876,17 +974,31 @@ void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert
              weights, probs, counter);
 }
 
+static int g_q80_rows_max_ctas = 148 * 4;
 void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq) {
-    const dim3 grid((rows + 127) / 128);
     const size_t smem = (size_t)nseq * blocks32 * 32 * sizeof(float);
-    if (nseq < 1 || nseq > LLAMD_MAX_SEQ || smem > 200 * 1024) {
-        set_error_msg("matvec_q8_0: nseq 1..8 and nseq*k*4 <= 200 KiB");
+    if (nseq < 1 || nseq > LLAMD_MAX_SEQ || smem > 200 * 1024 || rows <= 0 || blocks32 <= 0) {
+        set_error_msg("matvec_q8_0: nseq 1..8, rows and blocks positive, nseq*k*4 <= 200 KiB");
         return;
     }
     const uint8_t *t = (const uint8_t *)w;
+    // the CTA-per-32-rows form needs 64 KiB of staged weights beside the activations; the thread-per-row form takes the rest
+    const size_t smem_rows = smem + 2 * kQ80ChunkBlocks * 32 * 32 * sizeof(float);
+    // measured: it wins while its CTAs fit one wave (attn_q 40 -> 10s of us); beyond that the thread-per-row form's
+    // deeper occupancy does (lm_head)
+    const bool by_rows = smem_rows <= 220 * 1024 && (rows + 31) / 32 <= g_q80_rows_max_ctas;
+    const dim3 grid(by_rows ? (rows + 31) / 32 : (rows + 127) / 128);
 #define Q80_CASE(N)                                                                                                   \
     case N: {                                                                                                          \
-        static size_t configured = 0;                                                                                  \
+        static size_t configured = 0, configured_rows = 0;                                                             \
+        if (by_rows) {                                                                                                 \
+            if (smem_rows > configured_rows) {                                                                         \
+                cudaFuncSetAttribute(matvec_q8_0_rows_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows); \
+                configured_rows = smem_rows;                                                                           \
+            }                                                                                                          \
+            launch_k("matvec_q8_0_rows", matvec_q8_0_rows_kernel<N>, grid, dim3(kQ80Producers + 32 * N), smem_rows, t, x, out, blocks32, rows); \
+            break;                                                                                                     \
+        }                                                                                                              \
         if (smem > 48 * 1024 && smem > configured) {                                                                   \
             cudaFuncSetAttribute(matvec_q8_0_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
             configured = smem;                                                                                         \

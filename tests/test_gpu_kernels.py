@@ -199,16 +199,21 @@ def test_grouped_repeated_expert_and_bad_ids(be, orc, synth):
 
 
 # ---- Q8_0 matvec (no device kernel in the reference; CPU path model.rs:253-263) --
-@pytest.mark.parametrize("nseq", [1, 3])
-def test_q8_0_matvec_is_bit_exact(be, orc, synth, nseq):
-    rows, k = 77, 512
-    w = synth.q8_0_blocks(rows * k // 32, 51, "q80mv")
-    x = synth.normal_f32(nseq * k, 51, "q80.x")
+@pytest.mark.parametrize("rows,k,nseq", [
+    (77, 512, 1), (77, 512, 3),   # two 8-block chunks, a ragged last row tile
+    (33, 96, 2),                  # three blocks: less than one chunk
+    (256, 2080, 1),               # 65 blocks: eight chunks and one block more
+    (64, 1024, 8),                # one chain warp per sequence
+    (40, 14336, 3),               # activations too large to sit beside the staged weights: the thread-per-row form
+])
+def test_q8_0_matvec_is_bit_exact(be, orc, synth, rows, k, nseq):
+    w = synth.q8_0_blocks(rows * k // 32, 51, "q80mv", rows, k)
+    x = synth.normal_f32(nseq * k, 51, "q80.x", rows, k)
     dw = be.Q80Weights.upload(w, rows, k // 32)
     got = dw.matvec_f32(x, nseq)
     for s in range(nseq):
         want = orc.matvec_dequant(orc.Q8_0, w, x[s * k:(s + 1) * k], k, rows)
-        assert_bit_equal(got[s], want, f"q8_0 sequence {s}")
+        assert_bit_equal(got[s], want, f"q8_0 {rows}x{k} sequence {s}")
 
 
 # ---- many tokens at once: the prefill kernels --------------------------------
