@@ -114,65 +114,96 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_port_sample(hp, seed, n_layers_sample, steps, threads, tokens):
-    """Time the oracle's decode pass on a bounded sample: `n_layers_sample`
-    full layers (all their experts pre-generated so generation is not timed)
-    plus the output norm and lm_head, extrapolated to hp['n_layer'] layers.
-    -> (tokens/s estimate, seconds per sampled step list)"""
-    import oracle
-    from llamd_rs_b200 import synth
+def decode_config(args, hp, world, ep, data_plane):
+    """What names the workload: the same object in the repo arm's line and in the reference arm's."""
+    return {"workload": "decode_qwen3moe_q6k_b1", "layers": hp["n_layer"], "experts": "128x8", "hidden": 2048, "vocab": 151936,
+            "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
+            "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2",
+            "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU; {data_plane}" if ep else f"replicas x{world}"),
+            "arith": args.arith}
 
-    t0 = time.time()
-    w = dict(tok_embd=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "tok_embd"),
-             output_norm=np.ones(hp["n_embd"], np.float32),
-             output=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "output"),
-             layers=[synth.layer_weights(hp, seed, il, with_experts=True) for il in range(n_layers_sample)])
-    hp_s = dict(hp, n_layer=n_layers_sample)
-    om = oracle.Model(hp_s, w, threads=threads)
-    om.kv_new(max(64, steps + 8))
-    log(f"[cpu] sample weights ready in {time.time() - t0:.1f}s")
-    per_layer, per_head = [], []
-    for pos in range(steps):
-        tok = int(tokens[pos % len(tokens)])
-        x = oracle.dequantize(oracle.Q6K, w["tok_embd"][tok * (hp["n_embd"] // 256) * 210:], hp["n_embd"])
-        t1 = time.perf_counter()
-        for il in range(n_layers_sample):
-            x, _ = om.forward_layer(il, x, pos)
-        t2 = time.perf_counter()
-        normed = oracle.mul(oracle.rms_norm(x, hp["rms_eps"]), w["output_norm"])
-        logits = oracle.matvec_q6k(w["output"], normed, hp["n_embd"], hp["n_vocab"], threads=threads)
-        oracle.argmax(logits)
-        t3 = time.perf_counter()
-        per_layer.append((t2 - t1) / n_layers_sample)
-        per_head.append(t3 - t2)
-    tok_s = [hp["n_layer"] * a + b for a, b in zip(per_layer, per_head)]
-    return tok_s
+
+class CpuPort:
+    """The oracle's decode pass, a whole token at a time, on the host cores.
+
+    All 48 layers run. Only `n_sample` distinct layers of weights are generated (a layer with its 128 experts is
+    0.5 GB; 48 of them would not fit every host): layer il computes with the weights of layer il % n_sample, which
+    changes no operation count and no byte read. The KV cache is filled to `start_pos` positions with N(0,1) rows,
+    so attention does the work of a token that follows a `start_pos`-token prompt.
+    """
+
+    def __init__(self, hp, seed, n_sample, threads, start_pos, room):
+        import oracle
+        from llamd_rs_b200 import synth
+
+        self.oracle, self.hp, self.n_sample = oracle, hp, n_sample
+        t0 = time.time()
+        sample = [synth.layer_weights(hp, seed, il, with_experts=True) for il in range(n_sample)]
+        self.w = dict(tok_embd=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "tok_embd"),
+                      output_norm=np.ones(hp["n_embd"], np.float32),
+                      output=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "output"),
+                      layers=[sample[il % n_sample] for il in range(hp["n_layer"])])
+        self.om = oracle.Model(hp, self.w, threads=threads)
+        self.om.kv_new(start_pos + room)
+        kvd = hp["n_head_kv"] * hp["head_dim"]
+        if start_pos:
+            for il in range(hp["n_layer"]):
+                kv = synth.normal_f32(2 * start_pos * kvd, seed, "cpu.kv", il)
+                self.om.kv_fill(il, 0, kv[:start_pos * kvd], kv[start_pos * kvd:])
+        self.pos = self.start = start_pos
+        self.tok = int(synth.token_ids(1, hp["n_vocab"], seed, "cpu.first")[0])
+        log(f"[cpu] {n_sample} sampled layers + embeddings + a {start_pos}-position KV cache ready in {time.time() - t0:.1f}s")
+
+    def step(self, threads=None):
+        """One greedy token; returns its wall time in seconds."""
+        if threads is not None:
+            self.om.m.threads = threads
+        t = time.perf_counter()
+        logits = self.om.forward(self.tok, self.pos)
+        self.tok = self.oracle.argmax(logits)
+        dt = time.perf_counter() - t
+        self.pos += 1
+        return dt
+
+    def sample_text(self, what, threads):
+        return (f"{what}; every step runs all {self.hp['n_layer']} layers (weights of {self.n_sample} generated layers cycled: same work), "
+                f"output norm, lm_head and argmax on {threads} threads, at positions from {self.start} on (KV cache pre-filled with N(0,1) rows)")
 
 
 def run_reference(args, rank, world):
-    """The reference's CPU implementation of the path: the oracle port, all host threads."""
+    """The reference's CPU implementation of the path: the oracle port, all host threads. Every step is a whole token."""
     if rank != 0:
         return
     from llamd_rs_b200 import synth
 
     hp = dict(synth.QWEN3MOE_30B)
+    hp["n_layer"] = args.layers
     threads = os.cpu_count() or 1
-    tokens = synth.token_ids(512, hp["n_vocab"], 0, "prompt")
-    n_sample = 2
     total = args.warmup + args.steps
-    secs = cpu_port_sample(hp, 0, n_sample, total, threads, tokens)[args.warmup:]
-    sec_per_tok = float(np.mean(secs))
+    port = CpuPort(hp, 0, 2, threads, args.prompt, total + 2)
+    for _ in range(args.warmup):
+        port.step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        port.step()
+    sec_per_tok = (time.perf_counter() - t0) / args.steps
+    single = port.step(threads=1)  # the reference's own configuration: one thread
     v = 1.0 / sec_per_tok
-    sample = (f"{args.steps} decode steps at positions {args.warmup}..{args.warmup + args.steps - 1}; each step runs {n_sample} "
-              f"of 48 layers (every expert resident) + output norm + lm_head on {threads} threads; token time = 48 x mean layer + head")
+    ep = world > 1 and args.parallelism == "ep"
     line = {"impl": "reference", "metric": "q6k_moe_decode_tok_s", "value": v, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sec_per_tok, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
-            "config": {"workload": "decode_qwen3moe_q6k_b1", "layers": 48, "experts": "128x8", "hidden": 2048, "vocab": 151936,
-                       "batch": 1, "weights": "Q6_K random-init seed 0"},
-            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "config": decode_config(args, hp, world, ep, data_plane_text(args)),
+            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
+                             "sample": port.sample_text(f"{args.steps} decode steps after {args.warmup} warm-up steps", threads),
+                             "single_thread": {"value": 1.0 / single, "unit": "tok/s", "cores": 1, "sample": "1 step"}},
             "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def data_plane_text(args):
+    return ("NCCL all-gather dispatch + all-to-all combine per layer" if args.ep_nccl else
+            "peer stores + system-scope arrival counters over NVLink per layer, NCCL for set-up only")
 
 
 def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
@@ -233,15 +264,17 @@ def main():
     ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; the JSON line says so")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: the headline (one token per step). prefill: one pass over a --prompt token prompt per step")
-    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "ep"],
-                    help="N > 1: replicas = one full model per GPU, no exchange; ep = experts sharded 128/N per GPU, "
-                         "NCCL dispatch/combine per MoE layer (each rank still decodes its own sequence)")
+    ap.add_argument("--parallelism", default="", choices=["", "replicas", "ep"],
+                    help="N > 1: ep (default) = experts sharded 128/N per GPU, dispatch/combine per MoE layer, each rank decodes "
+                         "its own sequence; replicas = one full model per GPU, no exchange")
+    ap.add_argument("--arith", default="exact", choices=["exact"],
+                    help="exact: every f32 reduction in the reference's order (token ids bit-exact against the CPU path)")
     ap.add_argument("--gemm", default="exact", choices=["exact", "dp4a", "tc"],
                     help="prefill workload: exact = integer tensor path (mma.sync), bit-identical to decode (default); dp4a = the same "
                          "bits, 8 tokens per weight pass; tc = tcgen05 on f16 pairs, tolerance level")
     ap.add_argument("--tile", type=int, default=0, help="prefill workload: tokens per prefill tile (0: min(prompt, 2048))")
-    ap.add_argument("--ep-p2p", action="store_true", help="with --parallelism ep: requests and expert rows travel by peer stores "
-                    "and arrival counters instead of the two NCCL collectives per layer")
+    ap.add_argument("--ep-nccl", action="store_true", help="with --parallelism ep: the two exchanges per layer as NCCL collectives "
+                    "(all-gather + grouped send/recv) instead of peer stores with arrival counters")
     ap.add_argument("--gguf", default="", help="load the model through the GGUF reader instead of tensor by tensor: a path to an "
                     "existing file, or a path that does not exist yet, where the same random-init model is written first")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -255,6 +288,8 @@ def main():
                     "(for a profiler's launch list; the timed numbers are then not the headline)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if not args.parallelism:
+        args.parallelism = "ep" if env_int("WORLD_SIZE", 1) > 1 else "replicas"
 
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if args.impl == "reference":
@@ -312,7 +347,7 @@ def main():
     else:
         m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
-    if ep and args.ep_p2p:
+    if ep and not args.ep_nccl:
         def _gather(b):
             out = [None] * world
             dist.all_gather_object(out, b)
@@ -400,8 +435,10 @@ def main():
         return
 
     # ---- warm-up (both paths) ----
+    first_tok, warm_tokens = tok, []
     for _ in range(W):
         tok = m.forward(tok, pos)
+        warm_tokens.append(tok)
         pos += 1
 
     from llamd_rs_b200._lib import lib as _lib
@@ -447,24 +484,32 @@ def main():
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
 
+    # what was decoded, so that a run can be checked against the CPU path's tokens for the same inputs
+    decoded = [int(first_tok)] + [int(t) for t in warm_tokens] + [int(t) for t in e2e_tokens] + [int(t) for t in toks]
+    tokens_hash = synth.checksum(np.asarray(decoded, np.int32))
+    inputs_hash = synth.checksum(np.asarray(prompt, np.int32), synth.layer_weights(hp, 0, 0, with_experts=False)["attn_q"])
+    hashes = [tokens_hash]
+    if dist:
+        hashes = [None] * world
+        dist.all_gather_object(hashes, tokens_hash)
+    detail = {"token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "ms_per_token_per_rank": dev_ms / K,
+              "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch,
+              "inputs_hash": inputs_hash, "tokens_hash": hashes[0], "tokens_hash_per_rank": hashes,
+              "tokens_head": decoded[:8], "n_tokens_hashed": len(decoded),
+              "hash_note": "crc32 of (prompt ids, layer-0 attn_q bytes) and of the int32 token ids chosen after the prompt: "
+                           "the prefill's token, the warm-up tokens, the e2e tokens, the device-loop tokens"}
     line = {
         "metric": "q6k_moe_decode_tok_s", "value": world * K / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "i8xi8->i32, f32 tail", "data": "synthetic",
-        "config": {"workload": "decode_qwen3moe_q6k_b1", "layers": hp["n_layer"], "experts": "128x8", "hidden": 2048, "vocab": 151936,
-                   "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
-                   "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2", "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU, "
-                                    + ("dispatch and combine by peer stores with arrival counters" if args.ep_p2p
-                                       else "NCCL all-gather dispatch + all-to-all combine") + " per layer"
-                                   if ep else f"replicas x{world}"),
-                   "token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "arith": "exact (reference order)",
-                   "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch},
+        "config": decode_config(args, hp, world, ep, data_plane_text(args)),
+        "detail": detail,
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(m.launches_per_pass()) * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     # DRAM bytes per token's matvec launches: the ncu capture of the lm_head launch read+wrote 1.016x its
-                     # algorithmic bytes (profiles/matvec_q6k_lm_head_ncu_full.md); every weight byte is streamed once from
-                     # cold HBM in every launch, so the ratio carries over to the token's launches.
+                     # DRAM bytes per token's matvec launches: an ncu capture of the lm_head launch read+wrote 1.016x its
+                     # algorithmic bytes; every weight byte is streamed once from cold HBM in every launch, so the ratio
+                     # carries over to the token's launches.
                      "traffic": 1.016 * (wbytes + iobytes),
                      "kernel": "matvec_q6k_kernel<1>", "launches_per_token": mv_launches, "avg_launch_us": mv_ms / iters / mv_launches * 1e3,
                      "algorithmic_bytes_per_token": wbytes + iobytes, "peak_source": peak_src,
@@ -473,10 +518,13 @@ def main():
     }
     if rank == 0 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        n_sample, cpu_steps = 2, 3
-        secs = cpu_port_sample(dict(synth.QWEN3MOE_30B), 0, n_sample, cpu_steps, threads, synth.token_ids(512, hp["n_vocab"], 0, "prompt"))
-        line["cpu_baseline"] = {"value": 1.0 / float(np.mean(secs[1:])), "unit": "tok/s", "cores": threads, "kind": "port",
-                                "sample": f"{cpu_steps - 1} decode steps (after 1 warm) of {n_sample} of 48 layers + lm_head; token time = 48 x mean layer + head"}
+        port = CpuPort(dict(synth.QWEN3MOE_30B), 0, 2, threads, args.prompt, 8)
+        port.step()
+        secs = [port.step() for _ in range(3)]
+        single = port.step(threads=1)
+        line["cpu_baseline"] = {"value": 1.0 / float(np.mean(secs)), "unit": "tok/s", "cores": threads, "kind": "port",
+                                "sample": port.sample_text("3 decode steps after 1 warm step", threads),
+                                "single_thread": {"value": 1.0 / single, "unit": "tok/s", "cores": 1, "sample": "1 step"}}
     if rank == 0:
         print(json.dumps(line), flush=True)
     m.free()

@@ -10,8 +10,8 @@ For each of the model's matvec shapes and each batch size it reports
 and the algorithmic GB/s = (weights + activations in + results out) / time,
 against the measured HBM copy bandwidth and the nominal 8 TB/s.
 
-    python -m llamd_rs_b200.bench_matvec                 # every shape, Q6_K and Q8_0, batch 1 2 4 8
-    python -m llamd_rs_b200.bench_matvec --shapes lm_head --types q6k --batch 1 --iters 3 --no-cpu
+    python bench_matvec.py                 # every shape, Q6_K and Q8_0, batch 1 2 4 8
+    python bench_matvec.py --shapes lm_head --types q6k --batch 1 --iters 3 --no-cpu
 """
 from __future__ import annotations
 
@@ -24,8 +24,11 @@ import time
 
 import numpy as np
 
-from . import backend, synth
-from ._lib import lib
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from llamd_rs_b200 import backend, synth  # noqa: E402
+from llamd_rs_b200._lib import lib  # noqa: E402
 
 # (name, rows, k): crates/llamd-bench/src/main.rs:25-32
 SHAPES = [("attn_q", 4096, 2048), ("attn_k", 512, 2048), ("attn_out", 2048, 4096), ("expert_gate", 768, 2048),
@@ -98,7 +101,7 @@ def main(argv=None):
     backend.stream_init()
     peaks = {}
     try:
-        peaks = json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")))
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except Exception:
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))

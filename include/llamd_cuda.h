@@ -214,12 +214,23 @@ void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, 
  * score scratch is a 1 MiB array built into the library, so this call and
  * everything under it allocate nothing. q, kc, vc, out are device pointers as
  * in llamd_fwd_attention; enqueues on the library stream, does not synchronise.
- * Limit: n_head * n_kv <= 262144 (64 heads x 4096 positions); larger shapes are
- * refused with -1 and a message in llamd_cuda_last_error_string(). The first
- * call on a device looks up the array's device address (that device must be
- * current); make that first call before any stream capture begins. All calls
- * share the one array: two calls whose kernels overlap on the GPU (different
- * streams or processes' threads) race on it. Returns 0 / -1. */
+ * Limits: n_head * n_kv <= 262144 (64 heads x 4096 positions), and one head's
+ * score row must fit shared memory beside the K/V tiles: (hd + n_kv +
+ * 128 (hd + 1)) * 4 bytes <= 200 KiB, i.e. n_kv <= 34560 at head_dim 128 (the
+ * first limit is the tighter one from 8 heads up). Shapes beyond either are
+ * refused with -1 and a message in llamd_cuda_last_error_string(). The call
+ * also returns -1, launching nothing, while an earlier error of the library is
+ * still unread (llamd_fwd_last_error / llamd_fwd_sync read and clear it): a
+ * return of 0 therefore means THIS call's launches were accepted.
+ * "Allocates nothing" holds from the second call on: the first call on a
+ * device creates the library stream if llamd_fwd_stream_init has not, looks up
+ * the array's device address (that device must be current; the lookup may
+ * load the module, which is when the 1 MiB is taken) and loads the kernels.
+ * Make llamd_fwd_stream_init and one warm-up call at start-up, outside the
+ * host's no-allocation window and before any stream capture begins. The
+ * library drives one device per process (the one its stream was made on).
+ * All calls share the one array: two calls whose kernels overlap on the GPU
+ * (different streams or processes' threads) race on it. Returns 0 / -1. */
 int llamd_fwd_attention_noalloc(const float *q, const float *kc, const float *vc, float *out, int n_head,
                                 int n_head_kv, int hd, int n_kv);
 void llamd_fwd_add(const float *a, const float *b, float *out, int n);                   /* :315 */

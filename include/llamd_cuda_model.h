@@ -75,6 +75,23 @@ int llamd_cuda_ep_ipc_export(const void *dev, void *handle64);
 void *llamd_cuda_ep_ipc_open(const void *handle64);
 void llamd_cuda_ep_ipc_close(void *mapped);
 int llamd_cuda_ep_world(void);
+/* Failure detection (no counterpart in the reference). Nothing here hangs on a rank that is missing:
+ *  - llamd_cuda_ep_init waits at most the time-out below for the communicator (a rank that never joins) and then
+ *    fails with a message; a pass with NCCL collectives in it is waited for on the host with the same limit, after which
+ *    the communicator is aborted (ncclCommAbort) and the call fails;
+ *  - in the peer-memory form every device-side wait gives up after "ep_poll_limit" polls (llamd_model_set_option;
+ *    default 2^24, seconds), records which wait it was in a status word (llamd_model_ep_status: 1 expert rows,
+ *    2 requests), and the pass fails with a message. The later waits of that model then return at once. A model whose
+ *    wait ran out, or whose communicator was aborted, must be freed and recreated on every rank. */
+void llamd_cuda_ep_set_timeout_ms(int ms); /* default 60000 */
+int llamd_model_ep_status(llamd_model *m);
+/* Expert parallelism over peer memory without a communicator: sets rank and world only. The model must then be
+ * attached (llamd_model_ep_p2p_attach or _attach_ptrs) before its first pass. */
+int llamd_cuda_ep_init_local(int rank, int world);
+/* Attach with device pointers the caller already holds (ranks inside one process, or memory the caller mapped):
+ * llamd_model_ep_p2p_buffers gives this rank's six buffers; ptrs is [world][6] in that order (row `rank` ignored). */
+int llamd_model_ep_p2p_buffers(llamd_model *m, void **out6);
+int llamd_model_ep_p2p_attach_ptrs(llamd_model *m, void *const *ptrs, int world);
 
 /* DeviceModel::load_batched (device.rs:270): room for max_seq sequences of
  * max_kv positions. NULL on failure (llamd_cuda_last_error_string says why). */
@@ -91,7 +108,8 @@ int llamd_model_set_tensor(llamd_model *m, int layer, int which, size_t first_bl
 size_t llamd_model_weight_bytes(llamd_model *m); /* device.rs:473 */
 
 /* Public knobs of DeviceModel (device.rs:126-143): "use_graph" (default 1),
- * "trace" (record per-layer hidden state and expert ids; disables the graph). */
+ * "trace" (record per-layer hidden state and expert ids; disables the graph),
+ * "ep_poll_limit" (polls before a device-side wait on another rank gives up). */
 int llamd_model_set_option(llamd_model *m, const char *name, int value);
 
 /* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */

@@ -5,14 +5,6 @@
 
 #include "common.cuh"
 
-namespace llamd {
-void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
-                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode = 0,
-                   const float *xf = nullptr, const float *xu = nullptr, int own_lo = 0, int own_hi = 0x7fffffff);
-void launch_matvec_multi(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
-                         const float *ad, int n_tokens, const int32_t *work, const int32_t *n_work, int max_items, const int32_t *act_map,
-                         const int32_t *out_map, int n_expert);
-}
 using namespace llamd;
 
 // The grouped device-pointer forms do not know how many experts the tensor
@@ -21,22 +13,58 @@ using namespace llamd;
 // any non-negative id.
 static const int kAnyExpert = 0x7fffffff;
 
+namespace llamd {
+void matvec_batch(const MatvecPlans &pl, const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows, int nseq) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, aq, ad, nseq, nullptr, 1, 0, 1, 0, nullptr, nullptr, 0, 0x7fffffff, pl);
+}
+void matvec_x3_batch(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0,
+                     float *o1, float *o2, int blocks, int rows0, int rows1, int rows2, int nseq) {
+    const void *ws[3] = {w0, w1, w2};
+    float *os[3] = {o0, o1, o2};
+    const int rows[3] = {rows0, rows1, rows2};
+    launch_matvec(3, ws, os, rows, blocks, aq, ad, nseq, nullptr, 1, 0, 1, 0, nullptr, nullptr, 0, 0x7fffffff, pl);
+}
+void matvec_grouped_x2_batch(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                             float *oa, float *ob, int blocks, int rows, int n_used, int nseq) {
+    const void *ws[2] = {wa, wb};
+    float *os[2] = {oa, ob};
+    const int r2[2] = {rows, rows};
+    launch_matvec(2, ws, os, r2, blocks, aq, ad, 1, ids, n_used * nseq, kAnyExpert, n_used, 0, nullptr, nullptr, 0, 0x7fffffff, pl);
+}
+void matvec_grouped_pa_batch(const MatvecPlans &pl, const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,
+                             int blocks, int rows, int n_used, int nseq) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, aq, ad, 1, ids, n_used * nseq, kAnyExpert, 1, 0, nullptr, nullptr, 0, 0x7fffffff, pl);
+}
+void matvec_grouped_x2_owned(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                             float *oa, float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo, int own_hi) {
+    const void *ws[2] = {wa, wb};
+    float *os[2] = {oa, ob};
+    const int r2[2] = {rows, rows};
+    launch_matvec(2, ws, os, r2, blocks, aq, ad, 1, ids, n_slots, kAnyExpert, n_used, 0, nullptr, nullptr, own_lo, own_hi, pl);
+}
+void matvec_grouped_pa_owned(const MatvecPlans &pl, const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,
+                             int blocks, int rows, int n_slots, int own_lo, int own_hi) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, aq, ad, 1, ids, n_slots, kAnyExpert, 1, 0, nullptr, nullptr, own_lo, own_hi, pl);
+}
+}  // namespace llamd
+
 extern "C" {
 
 void llamd_fwd_matvec_batch(const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows, int nseq) {
-    const void *ws[1] = {w};
-    float *os[1] = {out};
-    launch_matvec(1, ws, os, &rows, blocks, aq, ad, nseq, nullptr, 1, 0, 1);
+    matvec_batch(MatvecPlans{}, w, aq, ad, out, blocks, rows, nseq);
 }
 void llamd_fwd_matvec(const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows) {
     llamd_fwd_matvec_batch(w, aq, ad, out, blocks, rows, 1);
 }
 void llamd_fwd_matvec_x3_batch(const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0, float *o1,
                                float *o2, int blocks, int rows0, int rows1, int rows2, int nseq) {
-    const void *ws[3] = {w0, w1, w2};
-    float *os[3] = {o0, o1, o2};
-    const int rows[3] = {rows0, rows1, rows2};
-    launch_matvec(3, ws, os, rows, blocks, aq, ad, nseq, nullptr, 1, 0, 1);
+    matvec_x3_batch(MatvecPlans{}, w0, w1, w2, aq, ad, o0, o1, o2, blocks, rows0, rows1, rows2, nseq);
 }
 void llamd_fwd_matvec_x3(const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0, float *o1,
                          float *o2, int blocks, int rows0, int rows1, int rows2) {
@@ -50,10 +78,7 @@ void llamd_fwd_matvec_grouped(const void *w, const int32_t *ids, const int8_t *a
 }
 void llamd_fwd_matvec_grouped_x2_batch(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad, float *oa,
                                        float *ob, int blocks, int rows, int n_used, int nseq) {
-    const void *ws[2] = {wa, wb};
-    float *os[2] = {oa, ob};
-    const int r2[2] = {rows, rows};
-    launch_matvec(2, ws, os, r2, blocks, aq, ad, 1, ids, n_used * nseq, kAnyExpert, n_used);
+    matvec_grouped_x2_batch(MatvecPlans{}, wa, wb, ids, aq, ad, oa, ob, blocks, rows, n_used, nseq);
 }
 // llamd_fwd_matvec_grouped_x2_batch followed by llamd_fwd_silu_mul_quant of its outputs, in one launch: the CTA
 // that completes a slot last writes act = silu(gate) * up as Q8_K into qs [slots][rows], d [slots][rows/256].
@@ -65,9 +90,9 @@ void llamd_fwd_matvec_grouped_x2_silu_quant(const void *wa, const void *wb, cons
         set_error_msg("matvec_grouped_x2_silu_quant: counter, qs, d must be given and rows a multiple of 256");
         return;
     }
-    g_next_tail = TailPlan{counter, qs, d};
-    llamd_fwd_matvec_grouped_x2_batch(wa, wb, ids, aq, ad, oa, ob, blocks, rows, n_used, nseq);
-    g_next_tail = TailPlan{};
+    MatvecPlans pl = {};
+    pl.tail = TailPlan{counter, qs, d};
+    matvec_grouped_x2_batch(pl, wa, wb, ids, aq, ad, oa, ob, blocks, rows, n_used, nseq);
 }
 void llamd_fwd_matvec_grouped_x2(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad, float *oa,
                                  float *ob, int blocks, int rows, int n_used) {
@@ -75,9 +100,7 @@ void llamd_fwd_matvec_grouped_x2(const void *wa, const void *wb, const int32_t *
 }
 void llamd_fwd_matvec_grouped_pa_batch(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks,
                                        int rows, int n_used, int nseq) {
-    const void *ws[1] = {w};
-    float *os[1] = {out};
-    launch_matvec(1, ws, os, &rows, blocks, aq, ad, 1, ids, n_used * nseq, kAnyExpert, 1);
+    matvec_grouped_pa_batch(MatvecPlans{}, w, ids, aq, ad, out, blocks, rows, n_used, nseq);
 }
 void llamd_fwd_matvec_grouped_pa(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks, int rows,
                                  int n_used) {
@@ -105,16 +128,11 @@ void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const f
 // x2: slot s reads activation aq[s / n_used]; pa: slot s reads aq[s].
 void llamd_fwd_matvec_grouped_x2_owned(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad, float *oa,
                                        float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo, int own_hi) {
-    const void *ws[2] = {wa, wb};
-    float *os[2] = {oa, ob};
-    const int r2[2] = {rows, rows};
-    launch_matvec(2, ws, os, r2, blocks, aq, ad, 1, ids, n_slots, kAnyExpert, n_used, 0, nullptr, nullptr, own_lo, own_hi);
+    matvec_grouped_x2_owned(MatvecPlans{}, wa, wb, ids, aq, ad, oa, ob, blocks, rows, n_used, n_slots, own_lo, own_hi);
 }
 void llamd_fwd_matvec_grouped_pa_owned(const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out, int blocks,
                                        int rows, int n_slots, int own_lo, int own_hi) {
-    const void *ws[1] = {w};
-    float *os[1] = {out};
-    launch_matvec(1, ws, os, &rows, blocks, aq, ad, 1, ids, n_slots, kAnyExpert, 1, 0, nullptr, nullptr, own_lo, own_hi);
+    matvec_grouped_pa_owned(MatvecPlans{}, w, ids, aq, ad, out, blocks, rows, n_slots, own_lo, own_hi);
 }
 
 // ---- many tokens at once (prefill) -------------------------------------------

@@ -84,7 +84,6 @@ struct PrefetchPlan {
     const int32_t *ids;           // expert ids on the device (read after the launch's dependency wait), or null
     int n_ids, own_lo, own_hi;    // experts [own_lo, own_hi) are resident, stored from local index 0
 };
-extern PrefetchPlan g_next_prefetch;  // set by the model before a matvec launch; consumed and cleared by that launch
 
 // CTA `cta` of `n_cta` asks for its share of [base, base + bytes).
 __device__ __forceinline__ void l2_prefetch_slice(const uint8_t *base, unsigned long long bytes, int cta, int n_cta) {
@@ -113,7 +112,6 @@ struct TailPlan {
     int8_t *qs;             // [n_slots][rows]
     float *d;               // [n_slots][rows / 256]
 };
-extern TailPlan g_next_tail;  // set by the model before a launch; consumed and cleared by that launch
 
 // Expert parallelism without the return collective. Each rank maps the other ranks' expert-output buffers (CUDA IPC,
 // one process per GPU); the down projection of an owned expert then stores its rows straight into the HOME rank's
@@ -125,15 +123,16 @@ struct PeerOutPlan {
     int div;                          // slots per rank: slot s belongs to rank s / div, local slot s % div
     int all_arrive;                   // 1: CTAs of slots this rank does not own arrive too (they have read the request by then)
 };
-extern PeerOutPlan g_next_peer_out;  // consumed and cleared by the next grouped matvec launch
 // What the next norm launch must see before it reads the expert outputs: *counter >= target (then it resets the counter).
 // The wait is bounded; when it runs out *status is set and the kernel goes on (the host reports the pass as failed).
+// Once *status is set, later waits of the model return at once (the pass has failed; nothing is gained by
+// running every later wait out as well) and the counters are left as they are: the model must be recreated.
 struct WaitPlan {
     unsigned int *counter;
     unsigned int target;
     int *status;
+    unsigned int limit;  // polls before giving up
 };
-extern WaitPlan g_next_wait;  // consumed and cleared by the next norm launch
 // The request records (expert ids, Q8_K activation) of all ranks are pushed into this rank's buffers by the ranks
 // themselves; a grouped launch that reads them first waits until *counter has reached *epoch x world (counter and
 // epoch only grow; epoch is bumped by this rank's own push, which precedes the launch in the stream). Bounded.
@@ -142,8 +141,57 @@ struct DispatchWait {
     const unsigned int *epoch;
     unsigned int world;
     int *status;
+    unsigned int limit;  // polls before giving up
 };
-extern DispatchWait g_next_disp_wait;  // consumed and cleared by the next grouped matvec launch
+
+// Bounded wait of ONE thread for *counter to reach `target` (wrap-safe when `monotone`, plain >= otherwise).
+// Returns false, with *status = code, when `limit` polls have passed or an earlier wait of the model already failed.
+__device__ __forceinline__ bool bounded_wait(const unsigned int *counter, unsigned int target, bool monotone, int *status, int code,
+                                             unsigned int limit) {
+    if (status) {
+        int st;
+        asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(st) : "l"(status) : "memory");
+        if (st != 0) return false;
+    }
+    for (unsigned int it = 0; it < limit; it++) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (monotone ? (int)(v - target) >= 0 : v >= target) return true;
+        if (it > 32) __nanosleep(128);
+    }
+    if (status) atomicExch(status, code);
+    return false;
+}
+
+// The optional parts of ONE Q6_K matvec launch, passed by the caller with the launch (all empty by default).
+struct MatvecPlans {
+    PrefetchPlan pf;
+    TailPlan tail;
+    PeerOutPlan peer;
+    DispatchWait dwait;
+};
+
+// Internal launch functions behind the extern "C" entry points of the same names; the model passes its plans here.
+void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
+                   const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode = 0,
+                   const float *xf = nullptr, const float *xu = nullptr, int own_lo = 0, int own_hi = 0x7fffffff,
+                   const MatvecPlans &plans = MatvecPlans{});
+void launch_matvec_multi(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
+                         const float *ad, int n_tokens, const int32_t *work, const int32_t *n_work, int max_items, const int32_t *act_map,
+                         const int32_t *out_map, int n_expert);
+void matvec_batch(const MatvecPlans &pl, const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows, int nseq);
+void matvec_x3_batch(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0,
+                     float *o1, float *o2, int blocks, int rows0, int rows1, int rows2, int nseq);
+void matvec_grouped_x2_batch(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                             float *oa, float *ob, int blocks, int rows, int n_used, int nseq);
+void matvec_grouped_pa_batch(const MatvecPlans &pl, const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,
+                             int blocks, int rows, int n_used, int nseq);
+void matvec_grouped_x2_owned(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
+                             float *oa, float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo, int own_hi);
+void matvec_grouped_pa_owned(const MatvecPlans &pl, const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,
+                             int blocks, int rows, int n_slots, int own_lo, int own_hi);
+void combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, const float *down, const float *weights, int n_used, float *sum_out,
+                                 const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq);
 
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.

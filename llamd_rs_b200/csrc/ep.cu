@@ -24,6 +24,11 @@
 #include <nccl.h>
 #include <string.h>
 
+#include <atomic>
+#include <chrono>
+#include <memory>
+#include <thread>
+
 #include "common.cuh"
 
 namespace llamd {
@@ -32,6 +37,8 @@ struct NcclApi {
     void *handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
@@ -43,6 +50,10 @@ struct NcclApi {
 static NcclApi g_nccl;
 static ncclComm_t g_comm = nullptr;
 static int g_ep_rank = 0, g_ep_world = 1;
+// How long the host waits for the other ranks (communicator set-up, and each pass that has collectives in it) before it
+// aborts the communicator and reports the failure. A rank that never joins, or leaves, then costs its peers this
+// long and an error, not a hang.
+static int g_ep_timeout_ms = 60000;
 
 static bool nccl_load() {
     if (g_nccl.handle) return true;
@@ -60,6 +71,8 @@ static bool nccl_load() {
     }
     LOAD(GetUniqueId, "ncclGetUniqueId")
     LOAD(CommInitRank, "ncclCommInitRank")
+    LOAD(CommGetAsyncError, "ncclCommGetAsyncError")
+    LOAD(CommAbort, "ncclCommAbort")
     LOAD(CommDestroy, "ncclCommDestroy")
     LOAD(AllGather, "ncclAllGather")
     LOAD(Send, "ncclSend")
@@ -78,6 +91,40 @@ static bool nccl_ok(ncclResult_t r, const char *what) {
     snprintf(msg, sizeof msg, "%s: %s", what, g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "nccl error");
     set_error_msg(msg);
     return false;
+}
+
+// Give up on the communicator: ncclCommAbort ends its kernels in flight and frees it. The model that used it is dead.
+static void comm_abort(const char *why) {
+    if (g_comm && g_nccl.CommAbort) g_nccl.CommAbort(g_comm);
+    g_comm = nullptr;
+    set_error_msg(why);
+}
+
+// The host side of a pass with collectives in it: wait for the stream, but not for ever. 0 ok, -1 failed (message set;
+// on a time-out, or an asynchronous NCCL error, the communicator has been aborted so that its kernels leave the GPU).
+int ep_bounded_sync() {
+    if (!g_comm) return llamd_fwd_sync();
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const cudaError_t q = cudaStreamQuery(stream());
+        if (q == cudaSuccess) return llamd_fwd_sync();
+        if (q != cudaErrorNotReady) {
+            set_error(q, "expert-parallel pass");
+            return -1;
+        }
+        ncclResult_t st = ncclSuccess;
+        if (g_nccl.CommGetAsyncError(g_comm, &st) == ncclSuccess && st != ncclSuccess && st != ncclInProgress) {
+            comm_abort("expert parallelism: NCCL reported an asynchronous error during the pass; communicator aborted");
+            cudaStreamSynchronize(stream());
+            return -1;
+        }
+        if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > g_ep_timeout_ms) {
+            comm_abort("expert parallelism: a pass with collectives did not complete in time (a rank left?); communicator aborted");
+            cudaStreamSynchronize(stream());  // the aborted kernels drain
+            return -1;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
 }
 
 int ep_rank() { return g_ep_rank; }
@@ -144,11 +191,51 @@ int llamd_cuda_ep_init(int rank, int world, const void *id128) {
     }
     ncclUniqueId id;
     memcpy(&id, id128, sizeof id);
-    if (!nccl_ok(g_nccl.CommInitRank(&g_comm, world, id, rank), "ncclCommInitRank")) return -1;
+    // A rank that never joins must not hang this one: the (blocking) set-up runs on a helper thread and this thread
+    // waits for it with a limit. The communicator stays a blocking one, which is what graph capture of its collectives
+    // was verified with. A set-up that timed out is left to its thread; the process should not retry but report.
+    struct Init {
+        std::atomic<int> done{0};
+        ncclComm_t comm = nullptr;
+        ncclResult_t rc = ncclSuccess;
+    };
+    auto st = std::make_shared<Init>();
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::thread([st, world, id, rank, dev]() {
+        cudaSetDevice(dev);
+        st->rc = g_nccl.CommInitRank(&st->comm, world, id, rank);
+        st->done.store(1, std::memory_order_release);
+    }).detach();
+    const auto t0 = std::chrono::steady_clock::now();
+    while (!st->done.load(std::memory_order_acquire)) {
+        if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > g_ep_timeout_ms) {
+            char msg[200];
+            snprintf(msg, sizeof msg, "expert parallelism: the communicator was not set up within %d ms (a rank never joined?)", g_ep_timeout_ms);
+            set_error_msg(msg);
+            return -1;
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
+    if (!nccl_ok(st->rc, "ncclCommInitRank")) return -1;
+    g_comm = st->comm;
     g_ep_rank = rank;
     g_ep_world = world;
     return 0;
 }
+
+// Expert parallelism over peer memory only: no communicator is made, so the two NCCL exchanges cannot be used and
+// llamd_model_ep_p2p_attach (or _attach_ptrs) must follow model creation. For ranks that share peer pointers some
+// other way than through NCCL's bootstrap (and for tests of the bounded waits).
+int llamd_cuda_ep_init_local(int rank, int world) {
+    if (world < 1 || rank < 0 || rank >= world || !stream()) return -1;
+    g_ep_rank = rank;
+    g_ep_world = world;
+    return 0;
+}
+
+// Milliseconds the host waits for other ranks before it aborts the communicator (default 60000).
+void llamd_cuda_ep_set_timeout_ms(int ms) { g_ep_timeout_ms = ms < 1 ? 1 : ms; }
 
 // Push this rank's request record to every rank (see ep_push_kernel). The tables are device arrays [world] of the
 // ranks' gathered buffers and dispatch counters.
@@ -229,6 +316,7 @@ void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, fl
         ok = ok && nccl_ok(g_nccl.Recv(recv + peer * blk, blk, ncclFloat, peer, g_comm, stream()), "ncclRecv");
     }
     nccl_ok(g_nccl.GroupEnd(), "ncclGroupEnd");
+    if (!g_comm) return;
     launch_k("ep_pick", ep_pick_kernel, dim3((n_embd + 255) / 256, n_used), dim3(256), 0, (const float *)recv, ids, down, n_used, n_embd,
              n_expert / g_ep_world);
 }

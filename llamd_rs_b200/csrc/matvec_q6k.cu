@@ -152,15 +152,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
             if (tid == 0) {
                 unsigned int ep;
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ep) : "l"(p.dwait.epoch) : "memory");
-                const unsigned int target = ep * p.dwait.world;
-                bool seen = false;
-                for (int it = 0; it < (1 << 24) && !seen; it++) {  // a few seconds at the least
-                    unsigned int v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.dwait.counter) : "memory");
-                    seen = (int)(v - target) >= 0;
-                    if (!seen && it > 32) __nanosleep(128);
-                }
-                if (!seen && p.dwait.status) atomicExch(p.dwait.status, 2);
+                bounded_wait(p.dwait.counter, ep * p.dwait.world, true, p.dwait.status, 2, p.dwait.limit);
             }
             __syncthreads();
         }
@@ -368,7 +360,7 @@ int g_batch_group = 2;  // set through llamd_fwd_set_batch_group
 constexpr int kBatchSplitMaxCtas = 512;
 
 template <int NSEQ, bool MULTI = false, int ACT = ACT_Q8K>
-static void launch_t(const MatvecParams &p, dim3 grid) {
+static void launch_t(const MatvecParams &p, dim3 grid, const MatvecPlans &plans) {
     const size_t smem = matvec_smem_bytes(NSEQ, p.nb);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -380,32 +372,23 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
         configured = smem;
     }
     MatvecParams q = p;
-    q.pf = g_next_prefetch;
-    g_next_prefetch = PrefetchPlan{};
-    q.dwait = DispatchWait{};
-    if (g_next_disp_wait.counter) {
-        if (!MULTI && NSEQ == 1 && p.ids)
-            q.dwait = g_next_disp_wait;
-        else
-            set_error_msg("matvec: a dispatch wait was planned for a launch that cannot carry it");
-        g_next_disp_wait = DispatchWait{};
+    q.pf = plans.pf;
+    q.dwait = plans.dwait;
+    q.peer = plans.peer;
+    q.tail = plans.tail;
+    // each plan fits one kind of launch only; a plan given to another kind is refused, not dropped
+    if (q.dwait.counter && !(!MULTI && NSEQ == 1 && p.ids)) {
+        set_error_msg("matvec: a dispatch wait was planned for a launch that cannot carry it");
+        return;
     }
-    q.peer = PeerOutPlan{};
-    if (g_next_peer_out.out_tab) {
-        if (!MULTI && NSEQ == 1 && p.ids && p.njobs == 1)
-            q.peer = g_next_peer_out;
-        else
-            set_error_msg("matvec: peer outputs were planned for a launch that cannot carry them");
-        g_next_peer_out = PeerOutPlan{};
+    if (q.peer.out_tab && !(!MULTI && NSEQ == 1 && p.ids && p.njobs == 1)) {
+        set_error_msg("matvec: peer outputs were planned for a launch that cannot carry them");
+        return;
     }
-    q.tail = TailPlan{};
-    if (g_next_tail.counter) {
-        // only a grouped launch of two matrices whose rows are whole Q8_K blocks can take it
-        if (!MULTI && NSEQ == 1 && p.ids && p.njobs == 2 && p.job[0].rows % 256 == 0 && p.own_lo == 0 && p.own_hi >= p.n_expert)
-            q.tail = g_next_tail;
-        else
-            set_error_msg("matvec: a SiLU tail was planned for a launch that cannot carry it");
-        g_next_tail = TailPlan{};
+    // a SiLU tail: only a grouped launch of two matrices whose rows are whole Q8_K blocks can take it
+    if (q.tail.counter && !(!MULTI && NSEQ == 1 && p.ids && p.njobs == 2 && p.job[0].rows % 256 == 0 && p.own_lo == 0 && p.own_hi >= p.n_expert)) {
+        set_error_msg("matvec: a SiLU tail was planned for a launch that cannot carry it");
+        return;
     }
     const bool extra = q.tail.counter || q.pf.ids || q.pf.bytes[0] || q.pf.bytes[1] || q.pf.bytes[2];
     if (NSEQ == 1 && !MULTI && ACT == ACT_Q8K && extra && !(q.peer.out_tab || q.dwait.counter)) {
@@ -420,6 +403,13 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
         set_error_msg("matvec: the expert-parallel forms exist for one sequence of Q8_K activations only");
         return;
     }
+    if (extra) {  // the plain instantiations do not carry the optional parts
+        q.pf = PrefetchPlan{};
+        if (q.tail.counter) {
+            set_error_msg("matvec: a SiLU tail needs one sequence of Q8_K activations");
+            return;
+        }
+    }
     launch_kc(MULTI ? PDL_OTHER : (p.ids ? PDL_GROUPED : PDL_MATVEC), "matvec_q6k", matvec_q6k_kernel<NSEQ, MULTI, ACT>, grid, dim3(kThreads), smem, q);
 }
 
@@ -429,7 +419,7 @@ static void launch_t(const MatvecParams &p, dim3 grid) {
 // slot s is index s / act_div, outputs [n_slots][rows]; nseq must be 1.
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode, const float *xf,
-                   const float *xu, int own_lo, int own_hi) {
+                   const float *xu, int own_lo, int own_hi, const MatvecPlans &plans) {
     if (blocks <= 0 || blocks > kThreads || nseq < 1 || nseq > LLAMD_MAX_SEQ || njobs < 1 || njobs > 3 || (ids && nseq != 1) ||
         (ids && (n_slots < 1 || act_div < 1))) {
         set_error_msg("matvec: blocks must be 1..256, nseq 1..8, 1..3 matrices");
@@ -481,7 +471,7 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
             set_error_msg("matvec: the silu activation mode takes gate and up, one sequence per slot");
             return;
         }
-        launch_t<1, false, ACT_SILU>(p, grid);
+        launch_t<1, false, ACT_SILU>(p, grid, plans);
         return;
     }
     if (act_mode == ACT_F32) {
@@ -490,26 +480,26 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
             return;
         }
         switch (nseq) {
-        case 1: launch_t<1, false, ACT_F32>(p, grid); break;
-        case 2: launch_t<2, false, ACT_F32>(p, grid); break;
-        case 3: launch_t<3, false, ACT_F32>(p, grid); break;
-        case 4: launch_t<4, false, ACT_F32>(p, grid); break;
-        case 5: launch_t<5, false, ACT_F32>(p, grid); break;
-        case 6: launch_t<6, false, ACT_F32>(p, grid); break;
-        case 7: launch_t<7, false, ACT_F32>(p, grid); break;
-        default: launch_t<8, false, ACT_F32>(p, grid); break;
+        case 1: launch_t<1, false, ACT_F32>(p, grid, plans); break;
+        case 2: launch_t<2, false, ACT_F32>(p, grid, plans); break;
+        case 3: launch_t<3, false, ACT_F32>(p, grid, plans); break;
+        case 4: launch_t<4, false, ACT_F32>(p, grid, plans); break;
+        case 5: launch_t<5, false, ACT_F32>(p, grid, plans); break;
+        case 6: launch_t<6, false, ACT_F32>(p, grid, plans); break;
+        case 7: launch_t<7, false, ACT_F32>(p, grid, plans); break;
+        default: launch_t<8, false, ACT_F32>(p, grid, plans); break;
         }
         return;
     }
     switch (nseq) {
-    case 1: launch_t<1>(p, grid); break;
-    case 2: launch_t<2>(p, grid); break;
-    case 3: launch_t<3>(p, grid); break;
-    case 4: launch_t<4>(p, grid); break;
-    case 5: launch_t<5>(p, grid); break;
-    case 6: launch_t<6>(p, grid); break;
-    case 7: launch_t<7>(p, grid); break;
-    default: launch_t<8>(p, grid); break;
+    case 1: launch_t<1>(p, grid, plans); break;
+    case 2: launch_t<2>(p, grid, plans); break;
+    case 3: launch_t<3>(p, grid, plans); break;
+    case 4: launch_t<4>(p, grid, plans); break;
+    case 5: launch_t<5>(p, grid, plans); break;
+    case 6: launch_t<6>(p, grid, plans); break;
+    case 7: launch_t<7>(p, grid, plans); break;
+    default: launch_t<8>(p, grid, plans); break;
     }
 }
 
@@ -563,7 +553,7 @@ void launch_matvec_multi(int njobs, const void *const *w, float *const *out, con
         set_error_msg("matvec_multi: too many items for one launch");
         return;
     }
-    launch_t<NS, true>(p, dim3(cta, items));
+    launch_t<NS, true>(p, dim3(cta, items), MatvecPlans{});
 }
 
 }  // namespace llamd

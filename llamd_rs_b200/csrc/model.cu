@@ -77,6 +77,10 @@ void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int 
 
 using namespace llamd;
 
+namespace llamd {
+int ep_bounded_sync();  // ep.cu: the stream synchronise of a pass that has NCCL collectives in it, with a host time-out
+}
+
 namespace {
 
 constexpr int kArgmaxBlocks = 512;  // crates/llamd-runtime/src/device.rs ARGMAX_BLOCKS
@@ -138,6 +142,7 @@ struct Model {
     Buf ids_all, ad_all, aq_all, gate_all, up_all, aq2_all, ad2_all, down_all, recv_all;
     // peer-written expert outputs (llamd_model_ep_p2p_attach): every rank's e_down and arrival counter, mapped here
     int ep_p2p = 0;
+    unsigned int ep_poll_limit = 1u << 24;  // polls (with back-off: seconds) before a wait on another rank gives up; option "ep_poll_limit"
     Buf ep_arrive, ep_status, ep_out_tab, ep_arrive_tab;  // counter word, status word, device pointer tables [world]
     Buf ep_disp, ep_epoch, ep_ids_tab, ep_ad_tab, ep_aq_tab, ep_disp_tab;  // dispatch counter, this rank's epoch, tables [world]
     std::vector<void *> ep_mapped;                         // what cudaIpcOpenMemHandle returned, to close
@@ -214,8 +219,9 @@ bool upload_f32(Buf &dst, const void *host, size_t n) {
 }
 
 // ---- L2 prefetch plans (common.cuh: PrefetchPlan): set just before a matvec launch, naming what follows it ----
-static void plan_static(const Model &m, const Buf *a, const Buf *b = nullptr, const Buf *c = nullptr, size_t cap = 0) {
-    if (!m.prefetch) return;
+static MatvecPlans plan_static(const Model &m, const Buf *a, const Buf *b = nullptr, const Buf *c = nullptr, size_t cap = 0) {
+    MatvecPlans pl = {};
+    if (!m.prefetch) return pl;
     PrefetchPlan pf = {};
     const Buf *r[3] = {a, b, c};
     for (int i = 0; i < 3; i++) {
@@ -225,12 +231,14 @@ static void plan_static(const Model &m, const Buf *a, const Buf *b = nullptr, co
         pf.base[i] = (const uint8_t *)r[i]->p;
         pf.bytes[i] = n;
     }
-    g_next_prefetch = pf;
+    pl.pf = pf;
+    return pl;
 }
-static void plan_experts(const Model &m, const Buf &w, const int32_t *ids, int n_ids) {
-    if (!m.prefetch || !w.p) return;
+static MatvecPlans plan_experts(const Model &m, const Buf &w, const int32_t *ids, int n_ids) {
+    MatvecPlans pl = {};
+    if (!m.prefetch || !w.p) return pl;
     const int lo = m.ep_world > 1 ? m.own_lo : 0, hi = m.ep_world > 1 ? m.own_hi : m.hp.n_expert;
-    if (hi <= lo || n_ids > 256) return;
+    if (hi <= lo || n_ids > 256) return pl;
     PrefetchPlan pf = {};
     pf.base[0] = (const uint8_t *)w.p;
     pf.bytes[0] = (w.bytes / (size_t)(hi - lo)) & ~(size_t)15;
@@ -238,7 +246,8 @@ static void plan_experts(const Model &m, const Buf &w, const int32_t *ids, int n
     pf.n_ids = n_ids;
     pf.own_lo = lo;
     pf.own_hi = hi;
-    g_next_prefetch = pf;
+    pl.pf = pf;
+    return pl;
 }
 constexpr size_t kHeadPrefetchBytes = (size_t)48 << 20;  // of the 256 MB lm_head: what comfortably stays in L2
 
@@ -275,20 +284,18 @@ void queue_token(Model &m, int nseq) {
     };
     // peer-written expert outputs: the norm that combines them waits for n_used x (CTAs per slot of the down projection) arrivals
     bool ep_wait_pending = false;
-    auto plan_ep_wait = [&]() {
-        if (!ep_wait_pending) return;
+    auto plan_ep_wait = [&]() -> WaitPlan {
+        if (!ep_wait_pending) return WaitPlan{};
         const int rows_per_cta = 256 / (ffe / 256);
         // every rank launches CTAs for every slot; owners arrive after their stores, the others after reading the request
         const unsigned target = (unsigned)m.ep_world * (unsigned)nu * (unsigned)((E + rows_per_cta - 1) / rows_per_cta);
-        g_next_wait = WaitPlan{m.ep_arrive.as<unsigned int>(), target, m.ep_status.as<int>()};
         ep_wait_pending = false;
+        return WaitPlan{m.ep_arrive.as<unsigned int>(), target, m.ep_status.as<int>(), m.ep_poll_limit};
     };
     // what the down projection of layer il is followed by: the next layer's Q, K, V, or the head's first megabytes
-    auto plan_after_down = [&](int il) {
-        if (il + 1 < hp.n_layer)
-            plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v);
-        else
-            plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
+    auto plan_after_down = [&](int il) -> MatvecPlans {
+        if (il + 1 < hp.n_layer) return plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v);
+        return plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
     };
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
@@ -298,15 +305,13 @@ void queue_token(Model &m, int nseq) {
         if (il == 0) {
             llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
         } else {
-            plan_ep_wait();
-            llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
-                                             m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+            combine_rms_norm_quant_wait(plan_ep_wait(), x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
+                                        m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
             trace_x(il - 1);
         }
         mark(LLAMD_PH_ATTN_NORM);
-        plan_static(m, &l.attn_out);
-        llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
-                                  m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        matvec_x3_batch(plan_static(m, &l.attn_out), l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
+                        m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
         mark(LLAMD_PH_QKV);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
         llamd_fwd_qk_norm_rope_store(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
@@ -328,8 +333,7 @@ void queue_token(Model &m, int nseq) {
             llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
         }
         mark(LLAMD_PH_QUANT);
-        plan_static(m, &l.ffn_gate_inp);
-        llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
         mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
         llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
@@ -342,34 +346,33 @@ void queue_token(Model &m, int nseq) {
             // Expert parallelism: gather every rank's routed request, run the experts this
             // rank owns for all of them, return each token's rows to its home rank.
             const int W = m.ep_world;
+            MatvecPlans gu = plan_experts(m, l.down_exps, m.ids_all.as<int32_t>(), W * nu);
             if (m.ep_p2p) {
                 // every rank pushes its request record into every rank's gathered buffers; the gate/up launch waits for
                 // all of them (no collective)
                 llamd_fwd_ep_push(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ep_ids_tab.as<int32_t *>(),
                                   m.ep_ad_tab.as<float *>(), m.ep_aq_tab.as<int8_t *>(), m.ep_disp_tab.as<unsigned int *>(),
                                   m.ep_epoch.as<unsigned int>(), nu, eb);
-                g_next_disp_wait = DispatchWait{m.ep_disp.as<unsigned int>(), m.ep_epoch.as<unsigned int>(), (unsigned)W, m.ep_status.as<int>()};
+                gu.dwait = DispatchWait{m.ep_disp.as<unsigned int>(), m.ep_epoch.as<unsigned int>(), (unsigned)W, m.ep_status.as<int>(), m.ep_poll_limit};
             } else {
                 llamd_fwd_ep_dispatch(m.expert_ids.as<int32_t>(), m.ad.as<float>(), m.aq.as<int8_t>(), m.ids_all.as<int32_t>(),
                                       m.ad_all.as<float>(), m.aq_all.as<int8_t>(), nu, eb);
             }
-            plan_experts(m, l.down_exps, m.ids_all.as<int32_t>(), W * nu);
-            llamd_fwd_matvec_grouped_x2_owned(l.gate_exps.p, l.up_exps.p, m.ids_all.as<int32_t>(), m.aq_all.as<int8_t>(), m.ad_all.as<float>(),
-                                              m.gate_all.as<float>(), m.up_all.as<float>(), eb, ffe, nu, W * nu, m.own_lo, m.own_hi);
+            matvec_grouped_x2_owned(gu, l.gate_exps.p, l.up_exps.p, m.ids_all.as<int32_t>(), m.aq_all.as<int8_t>(), m.ad_all.as<float>(),
+                                    m.gate_all.as<float>(), m.up_all.as<float>(), eb, ffe, nu, W * nu, m.own_lo, m.own_hi);
             llamd_fwd_silu_mul_quant(m.gate_all.as<float>(), m.up_all.as<float>(), nullptr, m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
                                      W * nu * ffe);
-            plan_after_down(il);
+            MatvecPlans dn = plan_after_down(il);
             if (m.ep_p2p) {
                 // no return collective: an owned slot's rows go straight into its home rank's e_down (routing-order slot),
                 // each CTA bumps that rank's counter, and the home rank's next norm waits for all of them
-                g_next_peer_out = PeerOutPlan{m.ep_out_tab.as<float *>(), m.ep_arrive_tab.as<unsigned int *>(), nu, 1};
-                llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
-                                                  m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
-                g_next_peer_out = PeerOutPlan{};
+                dn.peer = PeerOutPlan{m.ep_out_tab.as<float *>(), m.ep_arrive_tab.as<unsigned int *>(), nu, 1};
+                matvec_grouped_pa_owned(dn, l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
+                                        m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
                 ep_wait_pending = true;
             } else {
-                llamd_fwd_matvec_grouped_pa_owned(l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
-                                                  m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
+                matvec_grouped_pa_owned(dn, l.down_exps.p, m.ids_all.as<int32_t>(), m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
+                                        m.down_all.as<float>(), ffe / 256, E, W * nu, m.own_lo, m.own_hi);
                 llamd_fwd_ep_combine(m.down_all.as<float>(), m.recv_all.as<float>(), m.expert_ids.as<int32_t>(), m.e_down.as<float>(), nu,
                                      E, hp.n_expert);
             }
@@ -378,38 +381,36 @@ void queue_token(Model &m, int nseq) {
                                 cudaMemcpyDeviceToDevice, stream());
             continue;
         }
-        plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
+        MatvecPlans gu = plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
         // SiLU on the gate only, times up, quantized per expert; each expert's down projection reads its OWN activation
         if (fuse) {
-            llamd_fwd_matvec_grouped_x2_silu_quant(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
-                                                   m.e_gate.as<float>(), m.e_up.as<float>(), m.tail_counter.as<unsigned int>(),
-                                                   m.aq2.as<int8_t>(), m.ad2.as<float>(), eb, ffe, nu, nseq);
+            gu.tail = TailPlan{m.tail_counter.as<unsigned int>(), m.aq2.as<int8_t>(), m.ad2.as<float>()};
+            matvec_grouped_x2_batch(gu, l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
+                                    m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
             mark(LLAMD_PH_GATE_UP);
         } else {
-            llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
-                                              m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
+            matvec_grouped_x2_batch(gu, l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
+                                    m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
             mark(LLAMD_PH_GATE_UP);
             llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                      nseq * nu * ffe);
         }
         mark(LLAMD_PH_SILU);
-        plan_after_down(il);
-        llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
-                                          m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+        matvec_grouped_pa_batch(plan_after_down(il), l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                m.e_down.as<float>(), ffe / 256, E, nu, nseq);
         mark(LLAMD_PH_DOWN);
         if (m.trace)
             cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
                             cudaMemcpyDeviceToDevice, stream());
     }
     // the last layer's combine, fused with the output norm
-    plan_ep_wait();
-    llamd_fwd_combine_rms_norm_quant(x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
-                                     m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+    combine_rms_norm_quant_wait(plan_ep_wait(), x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
+                                m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
     trace_x(hp.n_layer - 1);
     mark(LLAMD_PH_ATTN_NORM);
-    plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v);  // the next token starts there
-    llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
-                           hp.n_vocab, nseq);
+    // (the prefetch plan names where the next token starts)
+    matvec_batch(plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v), m.output.p ? m.output.p : m.tok_embd.p,
+                 m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb, hp.n_vocab, nseq);
     mark(LLAMD_PH_LM_HEAD);
     llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
                      kArgmaxBlocks, nseq);
@@ -428,24 +429,26 @@ void queue_matvecs_only(Model &m, int nseq) {
     // the same prefetch plans as the full pass sets
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
-        plan_static(m, &l.attn_out);
-        llamd_fwd_matvec_x3_batch(l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
-                                  m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
-        plan_static(m, &l.ffn_gate_inp);
-        llamd_fwd_matvec_batch(l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
-        plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
-        llamd_fwd_matvec_grouped_x2_batch(l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
-                                          m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
-        if (il + 1 < hp.n_layer)
-            plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v);
-        else
-            plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
-        llamd_fwd_matvec_grouped_pa_batch(l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
-                                          m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+        matvec_x3_batch(plan_static(m, &l.attn_out), l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
+                        m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        matvec_grouped_x2_batch(plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu), l.gate_exps.p, l.up_exps.p,
+                                m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(), m.e_gate.as<float>(), m.e_up.as<float>(), eb,
+                                ffe, nu, nseq);
+        const MatvecPlans dn = il + 1 < hp.n_layer
+                                   ? plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v)
+                                   : plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
+        matvec_grouped_pa_batch(dn, l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(), m.e_down.as<float>(),
+                                ffe / 256, E, nu, nseq);
     }
-    plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v);
-    llamd_fwd_matvec_batch(m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
-                           hp.n_vocab, nseq);
+    matvec_batch(plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v), m.output.p ? m.output.p : m.tok_embd.p,
+                 m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb, hp.n_vocab, nseq);
+}
+
+// The device-side waits of the peer-memory form are bounded; what the status word they leave behind means.
+std::string ep_wait_message(int status) {
+    return std::string("expert parallelism: a wait for the other ranks' ") + (status == 2 ? "requests" : "expert rows") +
+           " ran out (status " + std::to_string(status) + "); the pass is incomplete and the model must be recreated";
 }
 
 bool check_ready(Model &m) {
@@ -515,9 +518,10 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
     }
     m.h_out[m.max_seq] = 0;
     if (m.ep_p2p) cudaMemcpyAsync(m.h_out + m.max_seq, m.ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
-    if (llamd_fwd_sync() != 0) return -1;  // THE ONE SYNCHRONISE
+    // THE ONE SYNCHRONISE (with NCCL collectives in the pass: bounded on the host, see ep_bounded_sync)
+    if ((m.ep_world > 1 && !m.ep_p2p ? ep_bounded_sync() : llamd_fwd_sync()) != 0) return -1;
     if (m.h_out[m.max_seq] != 0) {
-        m.err = "expert parallelism: a wait for the other ranks' expert rows ran out; the pass is incomplete";
+        m.err = ep_wait_message(m.h_out[m.max_seq]);
         return -1;
     }
     for (int s = 0; s < nseq; s++) {
@@ -754,6 +758,13 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded in the other mode
         return 0;
     }
+    if (!strcmp(name, "ep_poll_limit")) {
+        // polls (128 ns back-off each after the first 32) before a wait on another rank gives up: the default, 2^24, is seconds
+        if (value < 1) return -1;
+        if ((unsigned)value != m->ep_poll_limit && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other limit
+        m->ep_poll_limit = (unsigned)value;
+        return 0;
+    }
     if (!strcmp(name, "trace")) {
         if (value && !m->trace_x.p) {
             if (!m->trace_x.alloc((size_t)m->hp.n_layer * m->max_seq * m->hp.n_embd * sizeof(float)) ||
@@ -986,8 +997,8 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
     if (!check_ready(*m)) return -1;
     m->h_meta[0] = first_token;
     m->h_meta[1] = start_pos;
-    cudaMemcpyAsync(m->meta.p, m->h_meta, 8, cudaMemcpyHostToDevice, stream());
-    cudaMemsetAsync(m->tok_count.p, 0, 4, stream());
+    LLAMD_TRY(cudaMemcpyAsync(m->meta.p, m->h_meta, 8, cudaMemcpyHostToDevice, stream()), "decode meta H2D");
+    LLAMD_TRY(cudaMemsetAsync(m->tok_count.p, 0, 4, stream()), "decode counter reset");
     if (m->use_graph && (!llamd_fwd_has_graph() || g_graph_owner != m->id || m->graph_nseq != 1)) {
         llamd_fwd_graph_destroy();
         if (llamd_fwd_begin_capture() != 0) return -1;
@@ -1001,30 +1012,37 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
         g_graph_owner = m->id;
         m->graph_nseq = 1;
     }
-    cudaEvent_t e0, e1;
-    cudaEventCreate(&e0);
-    cudaEventCreate(&e1);
-    cudaEventRecord(e0, stream());
-    for (int i = 0; i < n; i++) {
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = 0;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess || cudaEventRecord(e0, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "decode events");
+        rc = -1;
+    }
+    for (int i = 0; rc == 0 && i < n; i++) {
         if (m->use_graph) {
-            if (llamd_fwd_graph_launch() != 0) return -1;
+            if (llamd_fwd_graph_launch() != 0) rc = -1;
         } else {
             queue_token(*m, 1);
         }
     }
-    cudaEventRecord(e1, stream());
-    if (cudaMemcpyAsync(out_tokens, m->tok_log.p, (size_t)n * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) {
+    if (rc == 0 && cudaEventRecord(e1, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "decode events");
+        rc = -1;
+    }
+    if (rc == 0 && cudaMemcpyAsync(out_tokens, m->tok_log.p, (size_t)n * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) {
         set_error(cudaGetLastError(), "decode D2H");
-        return -1;
+        rc = -1;
     }
     m->h_out[m->max_seq] = 0;
-    if (m->ep_p2p) cudaMemcpyAsync(m->h_out + m->max_seq, m->ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
-    int rc = llamd_fwd_sync();
-    if (ms_out) cudaEventElapsedTime(ms_out, e0, e1);
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
+    if (rc == 0 && m->ep_p2p) cudaMemcpyAsync(m->h_out + m->max_seq, m->ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
+    // whatever was queued is drained before the events go away, also after a failure
+    const int sync_rc = (m->ep_world > 1 && !m->ep_p2p) ? ep_bounded_sync() : llamd_fwd_sync();
+    if (sync_rc != 0) rc = -1;
+    if (rc == 0 && ms_out) cudaEventElapsedTime(ms_out, e0, e1);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
     if (rc == 0 && m->h_out[m->max_seq] != 0) {
-        m->err = "expert parallelism: a wait for the other ranks' expert rows ran out; the tokens are not valid";
+        m->err = ep_wait_message(m->h_out[m->max_seq]);
         rc = -1;
     }
     return rc;
@@ -1130,6 +1148,45 @@ int llamd_model_ep_p2p_attach(llamd_model *h, const void *all, int world) {
     if (g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the collectives
     m->ep_p2p = 1;
     return 0;
+}
+
+// The same switch for ranks that can hand each other device pointers directly (several models in one process, or
+// memory mapped by the caller): ptrs is [world][6] in the order of llamd_model_ep_p2p_buffers; row `rank` is ignored.
+int llamd_model_ep_p2p_buffers(llamd_model *h, void **out6) {
+    Model *m = (Model *)h;
+    if (!m || !out6 || m->ep_world < 2) return -1;
+    for (int i = 0; i < 6; i++) out6[i] = ep_shared_buf(*m, i)->p;
+    return 0;
+}
+int llamd_model_ep_p2p_attach_ptrs(llamd_model *h, void *const *ptrs, int world) {
+    Model *m = (Model *)h;
+    if (!m || !ptrs || world != m->ep_world || world < 2) return -1;
+    std::vector<void *> tab[6];
+    for (int i = 0; i < 6; i++) {
+        tab[i].resize(world);
+        for (int r = 0; r < world; r++) {
+            tab[i][r] = r == m->ep_rank ? ep_shared_buf(*m, i)->p : ptrs[(size_t)r * 6 + i];
+            if (!tab[i][r]) {
+                m->err = "ep_p2p_attach_ptrs: a null buffer";
+                return -1;
+            }
+        }
+    }
+    Buf *dev[6] = {&m->ep_out_tab, &m->ep_arrive_tab, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab};
+    for (int i = 0; i < 6; i++)
+        if (cudaMemcpyAsync(dev[i]->p, tab[i].data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess) return -1;
+    if (llamd_fwd_sync() != 0) return -1;
+    if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
+    m->ep_p2p = 1;
+    return 0;
+}
+// The status word of the bounded device-side waits: 0, or what the first wait that ran out left (1: expert rows, 2: requests).
+int llamd_model_ep_status(llamd_model *h) {
+    Model *m = (Model *)h;
+    if (!m || !m->ep_status.p) return 0;
+    int st = 0;
+    if (llamd_fwd_download(&st, m->ep_status.p, 4) != 0) return -1;
+    return st;
 }
 
 int llamd_model_logits(llamd_model *h, float *host_out, int nseq) {

@@ -1063,34 +1063,42 @@ void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, in
 }
 
 static void attention_split_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
-                                   int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride) {
+                                   int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride,
+                                   const TailPlan &tail_in) {
     const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1)) * sizeof(float);
     const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
+    // (the library runs on one device per process: llamd_cuda_set_device is refused once the stream exists, so a
+    // per-process record of the configured size is a per-device one)
     static size_t conf_a = 0, conf_b = 0;
     if (smem_a > 48 * 1024 && smem_a > conf_a) {
-        cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        const cudaError_t e = cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        if (e != cudaSuccess) {
+            set_error(e, "attention (scores) smem attribute");
+            return;
+        }
         conf_a = smem_a;
     }
     if (smem_b > 48 * 1024 && smem_b > conf_b) {
-        cudaFuncSetAttribute(attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+        const cudaError_t e = cudaFuncSetAttribute(attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+        if (e != cudaSuccess) {
+            set_error(e, "attention (output) smem attribute");
+            return;
+        }
         conf_b = smem_b;
     }
     launch_kc(PDL_ATTN, "attn_scores", attn_scores_kernel, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
              max_kv, kv_stride);
-    TailPlan tail = {};
-    if (g_next_tail.counter) {
-        if ((n_head * hd) % 256 == 0)
-            tail = g_next_tail;
-        else
-            set_error_msg("attention: a quantize tail needs n_head * head_dim to be whole Q8_K blocks");
-        g_next_tail = TailPlan{};
+    TailPlan tail = tail_in;
+    if (tail.counter && (n_head * hd) % 256 != 0) {
+        set_error_msg("attention: a quantize tail needs n_head * head_dim to be whole Q8_K blocks");
+        tail = TailPlan{};
     }
     launch_kc(PDL_ATTN, "attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
              meta, n_kv, max_kv, kv_stride, tail);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
-                             const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride) {
+                             const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride, const TailPlan &tail = TailPlan{}) {
     const size_t smem = (size_t)(hd + ((max_kv + 3) & ~3) + 2 * kAttTile * (hd + 1)) * sizeof(float);
     if (hd % 4 || hd > 256 || kAttTile * (hd / 4) > 8 * 256 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
         set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
@@ -1099,12 +1107,12 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     // With a scores buffer ([nseq][n_head][max_kv] floats) and a head_dim the
     // column split divides, the work is cut over 4x more CTAs.
     if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 8 * 256) {
-        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride);
+        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride, tail);
         return;
     }
-    if (g_next_tail.counter) {
+    if (tail.counter) {
         set_error_msg("attention: a quantize tail was planned for the single-CTA kernel, which does not carry it");
-        g_next_tail = TailPlan{};
+        return;
     }
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -1142,9 +1150,7 @@ void llamd_fwd_attention_meta_quant(const float *q, const float *kc, const float
         set_error_msg("attention_meta_quant: scores, counter, qs and d must be given");
         return;
     }
-    g_next_tail = TailPlan{counter, qs, d};
-    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv);
-    g_next_tail = TailPlan{};
+    attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv, TailPlan{counter, qs, d});
 }
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int nseq) {
@@ -1172,8 +1178,18 @@ int llamd_fwd_attention_noalloc(const float *q, const float *kc, const float *vc
         set_error_msg("attention_noalloc: null pointer or empty shape");
         return -1;
     }
+    if (error_code() != 0) {
+        // an earlier failure nobody has read yet: this call could not tell its own failure from that one
+        return -1;
+    }
     if ((long long)n_head * n_kv > kStaticScoreFloats) {
         set_error_msg("attention_noalloc: n_head * n_kv exceeds the built-in scratch of 262144 floats (64 heads x 4096 positions)");
+        return -1;
+    }
+    // the kernels keep one head's scores in shared memory beside their K/V tiles
+    if (((size_t)hd + (size_t)((n_kv + 3) & ~3) + 2 * (size_t)kAttTile * (hd + 1)) * sizeof(float) > 200 * 1024) {
+        set_error_msg("attention_noalloc: n_kv too long for the shared-memory score row: (hd + n_kv + 128 (hd + 1)) * 4 bytes "
+                      "must not exceed 200 KiB (34560 positions at head_dim 128)");
         return -1;
     }
     int dev = 0;
@@ -1193,12 +1209,11 @@ int llamd_fwd_attention_noalloc(const float *q, const float *kc, const float *vc
         g_static_scores_dev[dev] = p;
     }
     if (!stream()) return -1;
-    const int before = error_code();
     // Nothing in the scratch has to start at zero: each launch writes the
     // n_head * n_kv scores it later reads, so the previous call's contents are
     // simply overwritten.
     attention_launch(q, kc, vc, out, g_static_scores_dev[dev], n_head, n_head_kv, hd, nullptr, n_kv, n_kv, 1, n_kv);
-    return (before == 0 && error_code() != 0) ? -1 : 0;
+    return error_code() != 0 ? -1 : 0;  // the sticky error was clear on entry, so a set one is this call's
 }
 
 void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_i, int32_t *out, int nblocks, int nseq) {

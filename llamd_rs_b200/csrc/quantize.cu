@@ -59,16 +59,10 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
         // Expert parallelism: the expert outputs read below are stored by other GPUs. Wait (bounded) for all of their
         // arrivals, then clear the counter: nothing more arrives before this rank has passed its next dispatch.
         if (tid == 0) {
-            bool seen = false;
-            for (int it = 0; it < (1 << 24) && !seen; it++) {  // a few seconds at the least
-                unsigned int v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait.counter) : "memory");
-                seen = v >= wait.target;
-                if (!seen && it > 32) __nanosleep(128);
+            if (bounded_wait(wait.counter, wait.target, false, wait.status, 1, wait.limit)) {
+                *wait.counter = 0;
+                __threadfence();
             }
-            if (!seen && wait.status) atomicExch(wait.status, 1);
-            *wait.counter = 0;
-            __threadfence();
         }
         __syncthreads();
     }
@@ -238,6 +232,17 @@ __global__ void moe_combine_kernel(const float *__restrict__ down, const float *
 
 using namespace llamd;
 
+// `wait`: with expert parallelism the rows of `down` are stored by other GPUs; the launch first waits for their arrivals.
+void llamd::combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, const float *down, const float *weights, int n_used,
+                                        float *sum_out, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
+    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
+        return;
+    }
+    launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
+             sum_out, w, out, qs, d, n, eps, wait);
+}
+
 extern "C" {
 
 void llamd_fwd_quantize_bsums(const float *x, int8_t *qs, float *d, int16_t *bsums, int nblocks) {
@@ -280,14 +285,7 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
 // with the attention norm of the next (or with the output norm).
 void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const float *weights, int n_used, float *sum_out,
                                       const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
-    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
-        set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
-        return;
-    }
-    const WaitPlan wait = g_next_wait;  // set by the expert-parallel model when the rows come from peers
-    g_next_wait = WaitPlan{};
-    launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
-             sum_out, w, out, qs, d, n, eps, wait);
+    combine_rms_norm_quant_wait(WaitPlan{}, x, down, weights, n_used, sum_out, w, out, qs, d, n, eps, nseq);
 }
 void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
     if (hd % 4) {

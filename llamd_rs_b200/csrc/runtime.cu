@@ -10,11 +10,6 @@
 namespace llamd {
 
 unsigned long long g_launches = 0;
-PrefetchPlan g_next_prefetch = {};
-TailPlan g_next_tail = {};
-PeerOutPlan g_next_peer_out = {};
-WaitPlan g_next_wait = {};
-DispatchWait g_next_disp_wait = {};
 int g_pdl = 7;  // matvec, grouped matvec and router launches: measured best
 static cudaStream_t g_stream = nullptr;
 static int g_err = 0;

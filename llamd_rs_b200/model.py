@@ -77,6 +77,16 @@ def _bind():
     L.llamd_cuda_ep_finalize.argtypes = []
     L.llamd_cuda_ep_rank.restype = i32
     L.llamd_cuda_ep_world.restype = i32
+    L.llamd_cuda_ep_init_local.restype = i32
+    L.llamd_cuda_ep_init_local.argtypes = [i32, i32]
+    L.llamd_cuda_ep_set_timeout_ms.restype = None
+    L.llamd_cuda_ep_set_timeout_ms.argtypes = [i32]
+    L.llamd_model_ep_status.restype = i32
+    L.llamd_model_ep_status.argtypes = [vp]
+    L.llamd_model_ep_p2p_buffers.restype = i32
+    L.llamd_model_ep_p2p_buffers.argtypes = [vp, vp]
+    L.llamd_model_ep_p2p_attach_ptrs.restype = i32
+    L.llamd_model_ep_p2p_attach_ptrs.argtypes = [vp, vp, i32]
     L._model_bound = True
     return L
 
@@ -97,6 +107,17 @@ def ep_init(rank: int, world: int, share) -> None:
         raise backend.Malformed("ep id must be 128 bytes")
     if L.llamd_cuda_ep_init(rank, world, C.create_string_buffer(ident, 128)) != 0:
         raise backend.Other("ep init: " + backend._last_error())
+
+
+def ep_init_local(rank: int, world: int) -> None:
+    """Rank and world without a communicator: only the peer-memory form can then be used (attach before the first pass)."""
+    if _bind().llamd_cuda_ep_init_local(rank, world) != 0:
+        raise backend.Other("ep init (local): " + backend._last_error())
+
+
+def ep_set_timeout_ms(ms: int) -> None:
+    """How long the host waits for other ranks (communicator set-up, a pass with collectives) before it gives up."""
+    _bind().llamd_cuda_ep_set_timeout_ms(int(ms))
 
 
 def ep_finalize() -> None:
@@ -261,6 +282,24 @@ class CudaModel:
         blob = b"".join(records)
         if self._L.llamd_model_ep_p2p_attach(self._h, C.create_string_buffer(blob, len(blob)), len(records)) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
+
+    def ep_p2p_buffers(self):
+        """This rank's six shared buffers as device addresses (expert outputs, arrival counter, gathered ids / scales /
+        quants, dispatch counter)."""
+        out = (C.c_void_p * 6)()
+        if self._L.llamd_model_ep_p2p_buffers(self._h, out) != 0:
+            raise backend.Other("ep_p2p buffers: " + (self._err() or backend._last_error()))
+        return [int(v or 0) for v in out]
+
+    def ep_p2p_attach_ptrs(self, table) -> None:
+        """table: [world][6] device addresses in the order of ep_p2p_buffers (this rank's own row is ignored)."""
+        world = len(table)
+        flat = (C.c_void_p * (6 * world))(*[int(v) for row in table for v in row])
+        if self._L.llamd_model_ep_p2p_attach_ptrs(self._h, flat, world) != 0:
+            raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
+
+    def ep_status(self) -> int:
+        return int(self._L.llamd_model_ep_status(self._h))
 
     def set_prefill_attn(self, on: bool) -> None:
         """True (default): a prefill tile's attention runs on the register-tiled kernels; False: the per-token ones."""

@@ -384,6 +384,23 @@ def matvec_grouped_pa_silu(w: "backend.DeviceWeights", ids, gate, up, rows_per_e
     return do.download_f32(ids.size * rows_per_expert).reshape(ids.size, rows_per_expert)
 
 
+def matvec_grouped_pa(w: "backend.DeviceWeights", ids, qs, d, rows_per_expert: int):
+    """Down projection of routed experts, every slot with its own Q8_K activation (op::planar_grouped_per_act).
+    ids int32 [n_slots]; qs int8 [n_slots][k]; d f32 [n_slots][k/256] -> [n_slots][rows_per_expert]."""
+    ids = np.ascontiguousarray(ids, dtype=np.int32).ravel()
+    qs = np.ascontiguousarray(qs, dtype=np.int8).reshape(ids.size, -1)
+    d = _f32(d).reshape(ids.size, -1)
+    if qs.shape[1] != w.blocks() * QK_K or d.shape[1] != w.blocks() or w.rows() % rows_per_expert:
+        raise ShapeError("matvec_grouped_pa sizes")
+    n_expert = w.rows() // rows_per_expert
+    if ids.size == 0 or ids.min() < 0 or ids.max() >= n_expert:
+        raise Malformed(f"expert id outside 0..{n_expert}")
+    dq, dd, di, do = DevBuf.from_array(qs), DevBuf.from_array(d), DevBuf.from_array(ids), DevBuf(ids.size * rows_per_expert * 4)
+    lib().llamd_fwd_matvec_grouped_pa_batch(w.ptr, di.ptr, dq.ptr, dd.ptr, do.ptr, w.blocks(), rows_per_expert, ids.size, 1)
+    backend.sync()
+    return do.download_f32(ids.size * rows_per_expert).reshape(ids.size, rows_per_expert)
+
+
 def matvec_grouped_x2_silu_quant(wa: "backend.DeviceWeights", wb: "backend.DeviceWeights", ids, x, rows_per_expert: int, fused: bool = True):
     """gate/up of routed experts for nseq sequences, then act = silu(gate)*up as Q8_K.
     ids int32 [nseq][n_used]; x f32 [nseq][k]. fused=True: one launch (llamd_fwd_matvec_grouped_x2_silu_quant);

@@ -348,7 +348,7 @@ class Model:
             for k in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
                 setattr(m, k, ptr_array(k))
         if expert_fn is not None:
-            cache = {}
+            cache = self._expert_cache = {}
 
             def _cb(_user, layer, which, expert):
                 key = (layer, which, expert)
@@ -373,6 +373,23 @@ class Model:
         self.kv = lib().orc_kv_new(self.hp["n_layer"], self.hp["n_head_kv"] * self.hp["head_dim"], capacity)
         self.kv_capacity = capacity
         return self.kv
+
+    def expert_cache_clear(self):
+        """Forget the expert slices ``expert_fn`` has produced so far (they may be views of large arrays)."""
+        c = getattr(self, "_expert_cache", None)
+        if c is not None:
+            c.clear()
+
+    def kv_fill(self, layer: int, first_pos: int, k, v):
+        """Write rows [first_pos, first_pos + n) of one layer's cache (k, v: [n, kv_dim] f32)."""
+        kvd = self.hp["n_head_kv"] * self.hp["head_dim"]
+        k, v = _f32(k).reshape(-1, kvd), _f32(v).reshape(-1, kvd)
+        n = k.shape[0]
+        if v.shape[0] != n or first_pos < 0 or first_pos + n > self.kv_capacity:
+            raise ValueError("kv_fill outside the cache")
+        for fn, src in ((lib().orc_kv_keys, k), (lib().orc_kv_values, v)):
+            dst = np.ctypeslib.as_array(C.cast(fn(self.kv, layer), C.POINTER(C.c_float)), shape=(self.kv_capacity * kvd,))
+            dst[first_pos * kvd:(first_pos + n) * kvd] = src.ravel()
 
     def kv_free(self):
         if self.kv:

@@ -282,30 +282,101 @@ int orc_repack_q6k_planar(const uint8_t *src, int64_t src_len, int64_t rows, int
 /* ------------------------------------------------------------------------ */
 
 typedef void (*row_fn)(int64_t r0, int64_t r1, void *ctx);
-typedef struct { row_fn fn; int64_t r0, r1; void *ctx; } job_t;
-static void *job_main(void *p) {
-    job_t *j = (job_t *)p;
-    j->fn(j->r0, j->r1, j->ctx);
+
+/* A persistent pool: workers are started once and parked between calls (a short
+ * spin, then a condition variable), so that a call costs a few microseconds
+ * instead of a thread creation per worker. A decode token makes ~1500 such
+ * calls. Chunks of rows are handed out through an atomic counter; the calling
+ * thread works too. One call at a time (callers are serialised by pool.call). */
+#define ORC_MAX_THREADS 256
+static struct {
+    pthread_mutex_t call, mu;
+    pthread_cond_t cv;
+    pthread_t th[ORC_MAX_THREADS];
+    int n_workers, sleepers, atfork_set;
+    unsigned gen;                 /* bumped once per call (atomic) */
+    int use;                      /* workers with id < use take chunks */
+    int active;                   /* workers that have not yet finished the current call (atomic) */
+    row_fn fn;
+    void *ctx;
+    int64_t rows, chunk, next;    /* next: atomic */
+} pool = {PTHREAD_MUTEX_INITIALIZER, PTHREAD_MUTEX_INITIALIZER, PTHREAD_COND_INITIALIZER, {0}, 0, 0, 0, 0, 0, 0, NULL, NULL, 0, 0, 0};
+
+static void pool_take_chunks(void) {
+    for (;;) {
+        int64_t r0 = __atomic_fetch_add(&pool.next, pool.chunk, __ATOMIC_RELAXED);
+        if (r0 >= pool.rows) return;
+        int64_t r1 = r0 + pool.chunk > pool.rows ? pool.rows : r0 + pool.chunk;
+        pool.fn(r0, r1, pool.ctx);
+    }
+}
+static void *pool_worker(void *arg) {
+    int id = (int)(intptr_t)arg;
+    unsigned seen = 0;
+    for (;;) {
+        int spins = 0;
+        while (__atomic_load_n(&pool.gen, __ATOMIC_ACQUIRE) == seen) {
+            if (++spins < 4000) {
+#if defined(__x86_64__) || defined(__i386__)
+                __builtin_ia32_pause();
+#endif
+                continue;
+            }
+            pthread_mutex_lock(&pool.mu);
+            pool.sleepers++;
+            while (__atomic_load_n(&pool.gen, __ATOMIC_ACQUIRE) == seen) pthread_cond_wait(&pool.cv, &pool.mu);
+            pool.sleepers--;
+            pthread_mutex_unlock(&pool.mu);
+        }
+        seen = __atomic_load_n(&pool.gen, __ATOMIC_ACQUIRE);
+        if (id < pool.use) pool_take_chunks();
+        __atomic_fetch_sub(&pool.active, 1, __ATOMIC_RELEASE);
+    }
     return NULL;
+}
+/* a forked child has none of the parent's threads */
+static void pool_after_fork(void) {
+    pool.n_workers = 0;
+    pool.sleepers = 0;
+    pthread_mutex_init(&pool.call, NULL);
+    pthread_mutex_init(&pool.mu, NULL);
+    pthread_cond_init(&pool.cv, NULL);
 }
 static void parallel_rows(int64_t rows, int threads, row_fn fn, void *ctx) {
     if (threads <= 1 || rows < 2 * threads) {
         fn(0, rows, ctx);
         return;
     }
-    if (threads > 256) threads = 256;
-    pthread_t th[256];
-    job_t jobs[256];
-    int64_t per = (rows + threads - 1) / threads;
-    int n = 0;
-    for (int t = 0; t < threads; t++) {
-        int64_t r0 = t * per, r1 = r0 + per > rows ? rows : r0 + per;
-        if (r0 >= rows) break;
-        jobs[n] = (job_t){fn, r0, r1, ctx};
-        pthread_create(&th[n], NULL, job_main, &jobs[n]);
-        n++;
+    if (threads > ORC_MAX_THREADS) threads = ORC_MAX_THREADS;
+    pthread_mutex_lock(&pool.call);
+    if (!pool.atfork_set) {
+        pthread_atfork(NULL, NULL, pool_after_fork);
+        pool.atfork_set = 1;
     }
-    for (int t = 0; t < n; t++) pthread_join(th[t], NULL);
+    while (pool.n_workers < threads - 1) {
+        if (pthread_create(&pool.th[pool.n_workers], NULL, pool_worker, (void *)(intptr_t)pool.n_workers) != 0) break;
+        pthread_detach(pool.th[pool.n_workers]);
+        pool.n_workers++;
+    }
+    pool.fn = fn;
+    pool.ctx = ctx;
+    pool.rows = rows;
+    pool.chunk = rows / (4 * (int64_t)threads);
+    if (pool.chunk < 1) pool.chunk = 1;
+    pool.use = threads - 1;
+    __atomic_store_n(&pool.next, 0, __ATOMIC_RELAXED);
+    __atomic_store_n(&pool.active, pool.n_workers, __ATOMIC_RELAXED);
+    __atomic_fetch_add(&pool.gen, 1, __ATOMIC_RELEASE);
+    pthread_mutex_lock(&pool.mu);
+    if (pool.sleepers) pthread_cond_broadcast(&pool.cv);
+    pthread_mutex_unlock(&pool.mu);
+    pool_take_chunks();
+    while (__atomic_load_n(&pool.active, __ATOMIC_ACQUIRE) != 0) {
+#if defined(__x86_64__) || defined(__i386__)
+        __builtin_ia32_pause();
+#endif
+    }
+    pthread_mutex_unlock(&pool.call);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -541,16 +612,24 @@ int orc_route(const float *logits, int n, int n_used, int32_t *experts, float *w
 /* attend: crates/llamd-runtime/src/attention.rs:62-125                      */
 /* ------------------------------------------------------------------------ */
 
-int orc_attend(const float *q, const float *k, const float *v, int n_kv, int n_head, int n_head_kv,
-               int head_dim, float *out) {
-    if (n_head_kv == 0 || n_head % n_head_kv != 0 || head_dim == 0 || n_kv == 0) return -2;
-    int kv_dim = n_head_kv * head_dim;
+typedef struct {
+    const float *q, *k, *v;
+    int n_kv, n_head, n_head_kv, head_dim;
+    float *out;
+} attend_ctx;
+/* heads [h0, h1): each head is computed exactly as the reference's loop body does */
+static void attend_heads(int64_t h0, int64_t h1, void *p) {
+    const attend_ctx *c = (const attend_ctx *)p;
+    const float *q = c->q, *k = c->k, *v = c->v;
+    float *out = c->out;
+    int n_kv = c->n_kv, head_dim = c->head_dim;
+    int kv_dim = c->n_head_kv * head_dim;
     float scale = 1.0f / sqrtf((float)head_dim);
-    int ratio = n_head / n_head_kv;
+    int ratio = c->n_head / c->n_head_kv;
     float *logits = (float *)malloc(sizeof(float) * n_kv);
-    for (int i = 0; i < n_head * head_dim; i++) out[i] = 0.0f;
-    for (int h = 0; h < n_head; h++) {
+    for (int h = (int)h0; h < (int)h1; h++) {
         int kvh = h / ratio, qo = h * head_dim;
+        for (int d = 0; d < head_dim; d++) out[qo + d] = 0.0f;
         for (int t = 0; t < n_kv; t++) {
             size_t ko = (size_t)t * kv_dim + kvh * head_dim;
             float dot = 0.0f;
@@ -572,7 +651,20 @@ int orc_attend(const float *q, const float *k, const float *v, int n_kv, int n_h
         }
     }
     free(logits);
+}
+
+/* Heads are independent, so handing them to several threads changes no result. */
+int orc_attend_mt(const float *q, const float *k, const float *v, int n_kv, int n_head, int n_head_kv,
+                  int head_dim, float *out, int threads) {
+    if (n_head_kv == 0 || n_head % n_head_kv != 0 || head_dim == 0 || n_kv == 0) return -2;
+    attend_ctx c = {q, k, v, n_kv, n_head, n_head_kv, head_dim, out};
+    if (threads > n_head / 2) threads = n_head / 2;
+    parallel_rows(n_head, threads, attend_heads, &c);
     return 0;
+}
+int orc_attend(const float *q, const float *k, const float *v, int n_kv, int n_head, int n_head_kv,
+               int head_dim, float *out) {
+    return orc_attend_mt(q, k, v, n_kv, n_head, n_head_kv, head_dim, out, 1);
 }
 
 /* ------------------------------------------------------------------------ */
@@ -714,12 +806,12 @@ static int forward_one_layer(const orc_model *m, int il, float *x, uint32_t pos,
     memcpy(kv->k[il] + (size_t)pos * kv_dim, kr, sizeof(float) * kv_dim);
     memcpy(kv->v[il] + (size_t)pos * kv_dim, v, sizeof(float) * kv_dim);
     int n_kv = (int)pos + 1;
-    orc_attend(qr, kv->k[il], kv->v[il], n_kv, n_head, n_head_kv, hd, attn);
+    orc_attend_mt(qr, kv->k[il], kv->v[il], n_kv, n_head, n_head_kv, hd, attn, th);
     orc_matvec_q6k(m->attn_out[il], attn, qd, n_embd, kqv, th);
     orc_add(x, kqv, n_embd, ffn_inp);
     orc_rms_norm(ffn_inp, n_embd, 1, m->rms_eps, norm);
     orc_mul(norm, m->ffn_norm[il], n_embd, ffn_norm);
-    orc_matvec_dequant(ORC_F32, (const uint8_t *)m->ffn_gate_inp[il], ffn_norm, n_embd, m->n_expert, logits, 1);
+    orc_matvec_dequant(ORC_F32, (const uint8_t *)m->ffn_gate_inp[il], ffn_norm, n_embd, m->n_expert, logits, th);
     orc_softmax(logits, m->n_expert, 1, probs);
     int rc = orc_route(logits, m->n_expert, n_used, experts, wraw, &wsum, weights, NULL);
     if (rc) { free(buf); return rc; }

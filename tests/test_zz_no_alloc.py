@@ -16,7 +16,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def run_both(backend, lib, synth, n_kv, seed):
+def run_both(backend, lib, synth, n_kv, seed, check_free=False):
     n_head, n_head_kv, hd = 32, 4, 128
     q = synth.normal_f32(n_head * hd, seed, "na.q")
     k = synth.normal_f32(n_kv * n_head_kv * hd, seed, "na.k")
@@ -27,9 +27,12 @@ def run_both(backend, lib, synth, n_kv, seed):
     lib.llamd_fwd_attention(dq.ptr, dk.ptr, dv.ptr, want_buf.ptr, scores.ptr, n_head, n_head_kv, hd, n_kv)
     backend.sync()
     want = want_buf.download_f32(q.size)
+    free_before = backend.free_memory()
     rc = lib.llamd_fwd_attention_noalloc(dq.ptr, dk.ptr, dv.ptr, got_buf.ptr, n_head, n_head_kv, hd, n_kv)
     assert rc == 0, backend._last_error()
     backend.sync()
+    if check_free:
+        assert backend.free_memory() == free_before, "a warmed-up call must take no device memory"
     got = got_buf.download_f32(q.size)
     assert np.all(np.isfinite(want)) and np.any(want != 0)
     return got, want
@@ -44,8 +47,8 @@ def test_noalloc_attention_matches_the_regular_entry_point_twice():
     backend.stream_init()
     L = lib()
     # two calls in a row; the second is shorter, so stale scores of the first sit beyond (and under) it
-    for n_kv, seed in ((700, 1), (133, 2)):
-        got, want = run_both(backend, L, synth, n_kv, seed)
+    for i, (n_kv, seed) in enumerate(((700, 1), (133, 2))):
+        got, want = run_both(backend, L, synth, n_kv, seed, check_free=i > 0)  # the first call may load code and resolve the array
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"n_kv={n_kv}: differs from llamd_fwd_attention"
 
 
@@ -63,4 +66,12 @@ def test_noalloc_attention_refuses_more_than_its_scratch():
     assert rc == -1 and "262144" in backend._last_error()
     L.llamd_fwd_last_error()  # clear the sticky flag for whoever runs next
     assert L.llamd_fwd_attention_noalloc(None, tiny.ptr, tiny.ptr, tiny.ptr, 4, 4, 128, 1) == -1
+    L.llamd_fwd_last_error()
+    # 4 heads x 60000 positions fits the array but not the shared-memory score row: refused, and the message says which limit
+    rc = L.llamd_fwd_attention_noalloc(tiny.ptr, tiny.ptr, tiny.ptr, tiny.ptr, 4, 4, 128, 60000)
+    assert rc == -1 and "shared-memory" in backend._last_error()
+    L.llamd_fwd_last_error()
+    # while an earlier error is unread the call launches nothing and says so through its return value
+    assert L.llamd_fwd_attention_noalloc(None, tiny.ptr, tiny.ptr, tiny.ptr, 4, 4, 128, 1) == -1
+    assert L.llamd_fwd_attention_noalloc(tiny.ptr, tiny.ptr, tiny.ptr, tiny.ptr, 4, 4, 128, 1) == -1
     L.llamd_fwd_last_error()
