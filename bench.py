@@ -488,6 +488,14 @@ def main():
     decoded = [int(first_tok)] + [int(t) for t in warm_tokens] + [int(t) for t in e2e_tokens] + [int(t) for t in toks]
     tokens_hash = synth.checksum(np.asarray(decoded, np.int32))
     inputs_hash = synth.checksum(np.asarray(prompt, np.int32), synth.layer_weights(hp, 0, 0, with_experts=False)["attn_q"])
+    golden_check = None
+    golden_path = os.path.join(ROOT, "tests", "golden", "decode_seed0.npz")
+    if rank == 0 and args.prompt == 512 and hp["n_layer"] == 48 and os.path.exists(golden_path):
+        # the CPU oracle's greedy run of this very workload (rank 0's prompt): token ids must be the same
+        g = np.load(golden_path)
+        want = [int(t) for t in g["chosen"][args.prompt - 1:args.prompt - 1 + len(decoded)]]
+        n_cmp = min(len(want), len(decoded))
+        golden_check = {"tokens_compared": n_cmp, "equal": decoded[:n_cmp] == want[:n_cmp]}
     hashes = [tokens_hash]
     if dist:
         hashes = [None] * world
@@ -495,7 +503,7 @@ def main():
     detail = {"token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "ms_per_token_per_rank": dev_ms / K,
               "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch,
               "inputs_hash": inputs_hash, "tokens_hash": hashes[0], "tokens_hash_per_rank": hashes,
-              "tokens_head": decoded[:8], "n_tokens_hashed": len(decoded),
+              "tokens_head": decoded[:8], "n_tokens_hashed": len(decoded), "tokens_vs_cpu_golden": golden_check,
               "hash_note": "crc32 of (prompt ids, layer-0 attn_q bytes) and of the int32 token ids chosen after the prompt: "
                            "the prefill's token, the warm-up tokens, the e2e tokens, the device-loop tokens"}
     line = {
