@@ -347,6 +347,14 @@ void llamd_fwd_ep_combine(const float *send, float *recv, const int32_t *ids, fl
 void llamd_fwd_rms_norm_rows(const float *x, float *out, int n, int rows, float eps); /* cpu/lib.rs:55-75: no weight */
 void llamd_fwd_softmax_rows(const float *x, float *out, int n, int rows);            /* :81-101 */
 void llamd_fwd_silu(const float *x, float *out, size_t n);                            /* :103-106 */
+/* f32::exp as the reference's CPU path evaluates it (the host libm's expf), elementwise. The library's exponential
+ * is the correctly rounded one corrected, input by input, to the host's expf: when the stream is made, every float
+ * for which exp is not 1, 0 or infinite is evaluated on the device and compared with expf on the host, and the
+ * inputs that differ (llamd_cuda_exp_exceptions of them) are kept in a table the kernels consult. Softmax, SiLU,
+ * the router and attention are therefore bit-identical to the CPU path, not merely within an ulp of it.
+ * LLAMD_EXP_TABLE=0 in the environment switches the table off (correctly rounded exp, ~1 s less start-up). */
+void llamd_fwd_expf(const float *x, float *out, size_t n);
+long long llamd_cuda_exp_exceptions(void);
 void llamd_fwd_mul(const float *a, const float *b, float *out, size_t n);             /* :112-114 */
 void llamd_fwd_scale(const float *x, float by, float *out, size_t n);                 /* :116-118 */
 /* w [m rows][k], x [n rows][k] -> out [n][m], out[j*m+i] (:126-149); any k. */

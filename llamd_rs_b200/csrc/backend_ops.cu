@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kRowThreads) softmax_rows_kernel(const float *
     for (int i = threadIdx.x; i < n; i += kRowThreads) dst[i] = __fmul_rn(dst[i], inv);  // each thread rereads what it wrote
 }
 
-enum { EW_SILU, EW_MUL, EW_SCALE };
+enum { EW_SILU, EW_MUL, EW_SCALE, EW_EXP };
 template <int OP>
 __global__ void elementwise_kernel(const float *__restrict__ a, const float *__restrict__ b, float by, float *__restrict__ out, size_t n) {
     pdl_trigger();
@@ -97,6 +97,7 @@ __global__ void elementwise_kernel(const float *__restrict__ a, const float *__r
         if (OP == EW_SILU) out[i] = __fdiv_rn(v, __fadd_rn(1.0f, ref_expf(-v)));
         if (OP == EW_MUL) out[i] = __fmul_rn(v, b[i]);
         if (OP == EW_SCALE) out[i] = __fmul_rn(v, by);
+        if (OP == EW_EXP) out[i] = ref_expf(v);
     }
 }
 
@@ -171,6 +172,11 @@ void llamd_fwd_rms_norm_rows(const float *x, float *out, int n, int rows, float 
 void llamd_fwd_softmax_rows(const float *x, float *out, int n, int rows) {
     if (n <= 0 || rows <= 0) return;
     launch_k("softmax_rows", softmax_rows_kernel, dim3(rows), dim3(kRowThreads), 0, x, out, n);
+}
+// The exponential every kernel of the library uses (quant.cuh: ref_expf), elementwise: what the reference's
+// f32::exp, i.e. the host libm's expf, returns for the same input. For parity checks.
+void llamd_fwd_expf(const float *x, float *out, size_t n) {
+    if (n) launch_k("expf", elementwise_kernel<EW_EXP>, dim3(ew_grid(n)), dim3(256), 0, x, (const float *)nullptr, 0.0f, out, n);
 }
 void llamd_fwd_silu(const float *x, float *out, size_t n) {
     if (n) launch_k("silu", elementwise_kernel<EW_SILU>, dim3(ew_grid(n)), dim3(256), 0, x, (const float *)nullptr, 0.0f, out, n);

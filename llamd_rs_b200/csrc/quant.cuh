@@ -5,9 +5,49 @@
 
 namespace llamd {
 
-// The reference calls Rust's f32::exp, i.e. the host libm's expf. Here the
-// exponential is evaluated in double and rounded once to f32.
-__device__ __forceinline__ float ref_expf(float x) { return __double2float_rn(exp((double)x)); }
+// The reference calls Rust's f32::exp, i.e. the host libm's expf. Here the exponential is evaluated in double and
+// rounded once to f32, which is the correctly rounded result; the host's expf is not always (glibc's differs by one
+// ulp on roughly one input in 12000). Routing decisions and Q8_K roundings downstream amplify such a bit, so the
+// library makes the two agree exactly: when it starts it evaluates this very expression on the device for EVERY
+// float in the range where exp is neither 1, 0 nor infinite, compares with the host's expf, and keeps the inputs
+// that differ in a hash table (runtime.cu: build_exp_table). ref_expf looks its argument up there: one probe of a
+// sparsely filled table in L2, a hit only for the listed inputs. Each translation unit has its own copy of the two
+// pointers (constant memory), set through the binder it registers below.
+static __constant__ const uint32_t *c_exp_keys = nullptr;  // [mask + 1] input bit patterns, 0 = empty slot
+static __constant__ const uint32_t *c_exp_vals = nullptr;  // [mask + 1] the host expf's result bits
+static __constant__ uint32_t c_exp_mask = 0;
+
+__device__ __forceinline__ float ref_expf(float x) {
+    float y = __double2float_rn(exp((double)x));
+    const uint32_t *keys = c_exp_keys;
+    if (keys) {
+        const uint32_t b = __float_as_uint(x), mask = c_exp_mask;
+        uint32_t h = (b * 2654435761u) >> 8 & mask;
+        for (int probe = 0; probe < 64; probe++) {  // (a table at most a quarter full: runs are short)
+            const uint32_t k = __ldg(keys + h);
+            if (k == 0) break;
+            if (k == b) {
+                y = __uint_as_float(__ldg(c_exp_vals + h));
+                break;
+            }
+            h = (h + 1) & mask;
+        }
+    }
+    return y;
+}
+
+void register_exp_binder(void (*bind)(const uint32_t *, const uint32_t *, uint32_t));
+namespace {
+inline void bind_exp_table_here(const uint32_t *keys, const uint32_t *vals, uint32_t mask) {
+    cudaMemcpyToSymbol(c_exp_keys, &keys, sizeof keys);
+    cudaMemcpyToSymbol(c_exp_vals, &vals, sizeof vals);
+    cudaMemcpyToSymbol(c_exp_mask, &mask, sizeof mask);
+}
+struct ExpBinderRegistration {
+    ExpBinderRegistration() { register_exp_binder(bind_exp_table_here); }
+};
+static ExpBinderRegistration s_exp_binder_registration;
+}  // namespace
 
 // ---- Q8_K: crates/llamd-quant/src/dot.rs:88-128 ---------------------------
 // One warp per 256-element block; lane l owns elements 8l..8l+7.

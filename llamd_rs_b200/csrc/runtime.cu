@@ -2,8 +2,14 @@
 // captured graph: the counterpart of the host side of
 // crates/llamd-rocm/kernels/llamd_forward.hip:701-916 and
 // crates/llamd-rocm/kernels/llamd.hip:1027-1100.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
 #include <mutex>
 #include <string>
+#include <thread>
+#include <vector>
 
 #include "common.cuh"
 
@@ -19,11 +25,108 @@ static cudaGraphExec_t g_graph_exec = nullptr;
 static void *g_scratch[8] = {};
 static size_t g_scratch_bytes[8] = {};
 
+// ---- the exponential, made identical to the host libm's expf --------------------------------------------------
+// (see quant.cuh: ref_expf). Every translation unit that evaluates exp registers a binder for its constants.
+typedef void (*ExpBinder)(const uint32_t *, const uint32_t *, uint32_t);
+static std::vector<ExpBinder> &exp_binders() {
+    static std::vector<ExpBinder> v;
+    return v;
+}
+void register_exp_binder(ExpBinder bind) { exp_binders().push_back(bind); }
+
+static uint32_t *g_exp_keys_dev = nullptr, *g_exp_vals_dev = nullptr;
+static long long g_exp_exceptions = -1;  // -1: no table (switched off, or it could not be built)
+
+// out[i] = bits of (float)exp((double)x) for the float whose bits are first + i: the expression of ref_expf
+__global__ void exp_scan_kernel(uint32_t first, uint32_t n, uint32_t *__restrict__ out) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        out[i] = __float_as_uint(__double2float_rn(exp((double)__uint_as_float(first + i))));
+}
+
+// Inputs below 2^-25 in magnitude give exactly 1.0f on both sides; above 89 both overflow to +inf, below -104 both
+// give 0. Everything in between is compared, float by float. LLAMD_EXP_TABLE=0 switches the table off.
+static bool build_exp_table(cudaStream_t s) {
+    const char *sw = getenv("LLAMD_EXP_TABLE");
+    if (sw && !strcmp(sw, "0")) return true;
+    const uint32_t ranges[2][2] = {{0x33000000u, 0x42B20000u}, {0xB3000000u, 0xC2D00001u}};
+    constexpr uint32_t kChunk = 1u << 25;
+    uint32_t *d_out = nullptr;
+    if (cudaMalloc(&d_out, (size_t)kChunk * 4) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    std::vector<uint32_t> host(kChunk);
+    const unsigned hw = std::thread::hardware_concurrency();
+    const int n_threads = (int)(hw < 1 ? 1 : (hw > 64 ? 64 : hw));
+    std::vector<std::vector<uint32_t>> found(n_threads);  // (input bits, host result bits) pairs
+    bool ok = true;
+    for (int r = 0; r < 2 && ok; r++) {
+        for (uint64_t first = ranges[r][0]; first < ranges[r][1] && ok; first += kChunk) {
+            const uint32_t n = (uint32_t)((ranges[r][1] - first) < kChunk ? (ranges[r][1] - first) : kChunk);
+            exp_scan_kernel<<<148 * 8, 256, 0, s>>>((uint32_t)first, n, d_out);
+            ok = cudaMemcpyAsync(host.data(), d_out, (size_t)n * 4, cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                 cudaStreamSynchronize(s) == cudaSuccess;
+            if (!ok) break;
+            std::vector<std::thread> pool;
+            for (int t = 0; t < n_threads; t++) {
+                pool.emplace_back([&, t, first, n]() {
+                    const uint32_t lo = (uint32_t)((uint64_t)n * t / n_threads), hi = (uint32_t)((uint64_t)n * (t + 1) / n_threads);
+                    for (uint32_t i = lo; i < hi; i++) {
+                        const uint32_t bits = (uint32_t)first + i;
+                        float x, y;
+                        memcpy(&x, &bits, 4);
+                        y = expf(x);
+                        uint32_t want;
+                        memcpy(&want, &y, 4);
+                        if (want != host[i]) {
+                            found[t].push_back(bits);
+                            found[t].push_back(want);
+                        }
+                    }
+                });
+            }
+            for (auto &th : pool) th.join();
+        }
+    }
+    cudaFree(d_out);
+    if (!ok) {
+        cudaGetLastError();
+        return false;
+    }
+    size_t n_exc = 0;
+    for (auto &v : found) n_exc += v.size() / 2;
+    uint32_t slots = 1u << 16;
+    while (slots < 4 * n_exc) slots <<= 1;  // at most a quarter full
+    std::vector<uint32_t> keys(slots, 0), vals(slots, 0);
+    for (auto &v : found)
+        for (size_t i = 0; i < v.size(); i += 2) {
+            uint32_t h = (v[i] * 2654435761u) >> 8 & (slots - 1);
+            while (keys[h]) h = (h + 1) & (slots - 1);
+            keys[h] = v[i];
+            vals[h] = v[i + 1];
+        }
+    if (cudaMalloc(&g_exp_keys_dev, (size_t)slots * 4) != cudaSuccess || cudaMalloc(&g_exp_vals_dev, (size_t)slots * 4) != cudaSuccess ||
+        cudaMemcpy(g_exp_keys_dev, keys.data(), (size_t)slots * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMemcpy(g_exp_vals_dev, vals.data(), (size_t)slots * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    for (ExpBinder b : exp_binders()) b(g_exp_keys_dev, g_exp_vals_dev, slots - 1);
+    if (cudaDeviceSynchronize() != cudaSuccess || cudaGetLastError() != cudaSuccess) return false;
+    g_exp_exceptions = (long long)n_exc;
+    return true;
+}
+
 cudaStream_t stream() {
     if (!g_stream) {
         cudaError_t e = cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking);
         if (e != cudaSuccess) {
             set_error(e, "cudaStreamCreate");
+            g_stream = nullptr;
+        } else if (!build_exp_table(g_stream)) {
+            // without the table the exponential is correctly rounded, not the host libm's: refuse rather than drift
+            set_error_msg("the table that makes exp identical to the host libm's expf could not be built");
+            cudaStreamDestroy(g_stream);
             g_stream = nullptr;
         }
     }
@@ -67,6 +170,10 @@ void *scratch(int slot, size_t bytes) {
 using namespace llamd;
 
 extern "C" {
+
+// How many float inputs the device's exp needed correcting for to equal the host libm's expf (the size of the
+// exception table built when the stream was made); -1 when the table is switched off.
+long long llamd_cuda_exp_exceptions(void) { return stream() ? g_exp_exceptions : -1; }
 
 int llamd_cuda_device_count(void) {
     int n = 0;

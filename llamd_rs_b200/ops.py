@@ -166,6 +166,15 @@ def silu_mul(gate, up):
     return do.download_f32(gate.size)
 
 
+def expf(x):
+    """The library's exponential, elementwise: bit for bit the host libm's expf (llamd_fwd_expf)."""
+    x = _f32(x).ravel()
+    dx, do = DevBuf.from_array(x), DevBuf(max(x.nbytes, 4))
+    lib().llamd_fwd_expf(dx.ptr, do.ptr, x.size)
+    backend.sync()
+    return do.download_f32(x.size)
+
+
 def router(logits, n_used: int):
     """-> (ids int32 [nseq][n_used], weights, probs) (op::router)."""
     logits = _f32(logits)

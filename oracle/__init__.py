@@ -180,6 +180,14 @@ def silu(x) -> np.ndarray:
     return out
 
 
+def expf(x) -> np.ndarray:
+    """The host libm's expf, elementwise (what Rust's f32::exp lowers to)."""
+    x = _f32(x).ravel()
+    out = np.zeros_like(x)
+    lib().orc_expf(_p(x), C.c_int64(x.size), _p(out))
+    return out
+
+
 def add(a, b) -> np.ndarray:
     a, b = _f32(a), _f32(b)
     out = np.zeros_like(a)

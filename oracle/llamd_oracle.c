@@ -608,6 +608,11 @@ int orc_route(const float *logits, int n, int n_used, int32_t *experts, float *w
     return 0;
 }
 
+/* f32::exp as the reference's CPU ops call it (the host libm), elementwise: for checking the device's exponential. */
+void orc_expf(const float *x, int64_t n, float *out) {
+    for (int64_t i = 0; i < n; i++) out[i] = expf(x[i]);
+}
+
 /* ------------------------------------------------------------------------ */
 /* attend: crates/llamd-runtime/src/attention.rs:62-125                      */
 /* ------------------------------------------------------------------------ */
