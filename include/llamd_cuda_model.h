@@ -64,11 +64,11 @@ int llamd_cuda_ep_rank(void);
  * other ranks' buffers plus arrival counters (one process per GPU, buffers shared through CUDA IPC). Every rank pushes
  * its request record (expert ids, Q8_K activation) into every rank's gathered buffers; an owned expert's rows go
  * straight into the home rank's expert-output buffer.
- * llamd_model_ep_p2p_export writes LLAMD_EP_P2P_RECORD bytes (six IPC handles); every rank collects all ranks'
+ * llamd_model_ep_p2p_export writes LLAMD_EP_P2P_RECORD bytes (ten IPC handles); every rank collects all ranks'
  * records in rank order and calls llamd_model_ep_p2p_attach(m, all, world) -- a synchronisation point: no rank may
  * run a pass before every rank has attached. The waits are bounded: if a peer does not deliver, the pass fails with a
  * message in llamd_model_error instead of hanging. Same tokens as one GPU, bit for bit. */
-#define LLAMD_EP_P2P_RECORD 384
+#define LLAMD_EP_P2P_RECORD 640
 int llamd_model_ep_p2p_export(llamd_model *m, void *out_record);
 int llamd_model_ep_p2p_attach(llamd_model *m, const void *all, int world);
 int llamd_cuda_ep_ipc_export(const void *dev, void *handle64);
@@ -89,8 +89,19 @@ int llamd_model_ep_status(llamd_model *m);
  * attached (llamd_model_ep_p2p_attach or _attach_ptrs) before its first pass. */
 int llamd_cuda_ep_init_local(int rank, int world);
 /* Attach with device pointers the caller already holds (ranks inside one process, or memory the caller mapped):
- * llamd_model_ep_p2p_buffers gives this rank's six buffers; ptrs is [world][6] in that order (row `rank` ignored). */
-int llamd_model_ep_p2p_buffers(llamd_model *m, void **out6);
+ * llamd_model_ep_p2p_buffers gives this rank's LLAMD_EP_P2P_RECORD / 64 shared buffers (expert outputs, arrival
+ * counter, gathered ids / scales / quants, dispatch counter of the decode pass; expert outputs and gathered
+ * quants / scales / ids of a prefill tile); ptrs is [world][that many] in the same order (row `rank` ignored). */
+int llamd_model_ep_p2p_buffers(llamd_model *m, void **out);
+/* Expert-parallel prefill (peer-memory form): llamd_model_prefill cuts the prompt into tiles of at most this many
+ * tokens, min("prefill_tile" at the time the buffers were shared, 40960 / (world * n_expert_used), max_kv). Per MoE
+ * layer every rank stores its tile (Q8_K activations, routed ids) into every rank's gathered buffers, runs the pairs
+ * whose expert it owns over ALL ranks' tokens on the grouped integer GEMM, and the down projection stores each
+ * pair's rows into the buffer of the rank the token lives on; the ordered combine there is the single-GPU one, so
+ * tokens and logits equal one GPU's bit for bit. Every rank must call llamd_model_prefill with prompts that give
+ * the same NUMBER of tiles (their lengths may differ). With the NCCL exchanges instead of peer memory, prefill
+ * feeds the prompt through the decode pass token by token. */
+int llamd_model_ep_tile_cap(llamd_model *m);
 int llamd_model_ep_p2p_attach_ptrs(llamd_model *m, void *const *ptrs, int world);
 
 /* DeviceModel::load_batched (device.rs:270): room for max_seq sequences of

@@ -190,6 +190,20 @@ void matvec_grouped_x2_owned(const MatvecPlans &pl, const void *wa, const void *
                              float *oa, float *ob, int blocks, int rows, int n_used, int n_slots, int own_lo, int own_hi);
 void matvec_grouped_pa_owned(const MatvecPlans &pl, const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,
                              int blocks, int rows, int n_slots, int own_lo, int own_hi);
+void moe_group_owned(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount, int32_t *ptoken,
+                     int32_t *pslot, int32_t *work, int32_t *n_work, int own_lo, int own_hi);
+// The grouped expert GEMM with its output rows scattered over several GPUs: row block o goes to out_tab[o / out_div],
+// local row block o % out_div (out_tab null: everything into oa / ob).
+void expert_gemm_scatter(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
+                         const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows, int n_expert,
+                         float *const *out_tab, int out_div);
+// expert parallelism, a prefill tile (ep.cu)
+void ep_push_tile(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *const *ids_tab, float *const *ad_tab,
+                  int8_t *const *aq_tab, unsigned int *const *disp_tab, unsigned int *epoch, unsigned int *push_done, int T, int cap,
+                  int n_used, int blocks);
+void ep_wait_requests(unsigned int *counter, const unsigned int *epoch, int *status, unsigned int limit);
+void ep_wait_rows(unsigned int *counter, unsigned int target, int *status, unsigned int limit);
+void ep_signal_rows(unsigned int *const *arrive_tab);
 void combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, const float *down, const float *weights, int n_used, float *sum_out,
                                  const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq);
 

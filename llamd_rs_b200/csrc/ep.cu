@@ -166,6 +166,91 @@ __global__ void ep_push_kernel(const int32_t *__restrict__ ids, const float *__r
     }
 }
 
+// ---- a prefill tile's exchange over peer memory --------------------------------------------------------------
+// Dispatch: every rank copies the Q8_K activations, block scales and routed expert ids of its T tokens into slot
+// `rank` of EVERY rank's gathered buffers ([world][cap] token rows; ids beyond T are -1), an all-gather by peer
+// stores. blockIdx.y = destination rank, blockIdx.x strides over the rows. The last CTA to finish a destination (a
+// local arrival counter that wraps to zero) bumps that rank's dispatch counter: its own fence orders it after the
+// stores of the CTAs it saw arrive. The last CTA of destination 0 also advances this rank's epoch.
+__global__ void __launch_bounds__(256) ep_push_tile_kernel(const int32_t *__restrict__ ids, const float *__restrict__ ad,
+                                                          const int8_t *__restrict__ aq, int32_t *const *__restrict__ ids_tab,
+                                                          float *const *__restrict__ ad_tab, int8_t *const *__restrict__ aq_tab,
+                                                          unsigned int *const *__restrict__ disp_tab, unsigned int *__restrict__ epoch,
+                                                          unsigned int *__restrict__ push_done, int rank, int T, int cap, int n_used,
+                                                          int blocks) {
+    pdl_trigger();
+    pdl_wait();
+    const int dst = blockIdx.y, tid = threadIdx.x;
+    const size_t row16 = (size_t)blocks * 16;  // uint4 per token row of quants
+    const uint4 *src = reinterpret_cast<const uint4 *>(aq);
+    uint4 *q = reinterpret_cast<uint4 *>(aq_tab[dst] + (size_t)rank * cap * blocks * 256);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < (size_t)T * row16; i += (size_t)gridDim.x * blockDim.x) q[i] = src[i];
+    float *d = ad_tab[dst] + (size_t)rank * cap * blocks;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < (size_t)T * blocks; i += (size_t)gridDim.x * blockDim.x) d[i] = ad[i];
+    int32_t *e = ids_tab[dst] + (size_t)rank * cap * n_used;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < (size_t)cap * n_used; i += (size_t)gridDim.x * blockDim.x)
+        e[i] = i < (size_t)T * n_used ? ids[i] : -1;
+    __threadfence_system();  // this CTA's part of the record is visible on dst before its arrival is
+    __syncthreads();
+    if (tid == 0) {
+        const bool last = atomicInc(push_done + dst, gridDim.x - 1) == gridDim.x - 1;  // wraps to 0
+        if (last) {
+            __threadfence_system();
+            atomicAdd_system(disp_tab[dst], 1u);
+            if (dst == 0) *epoch = *epoch + 1;
+        }
+    }
+}
+
+// One thread waits (bounded) for a counter other GPUs bump: the requests of all ranks (epoch given: target =
+// *epoch x world, the counter only grows) or the arrivals of all ranks' expert rows (target given; the counter is
+// cleared once seen). The kernels that follow in the stream read what the peers stored.
+__global__ void ep_wait_kernel(unsigned int *counter, const unsigned int *epoch, unsigned int world_or_target, int *status, int code,
+                               unsigned int limit) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    if (epoch) {
+        bounded_wait(counter, *epoch * world_or_target, true, status, code, limit);
+    } else if (bounded_wait(counter, world_or_target, false, status, code, limit)) {
+        *counter = 0;
+        __threadfence();
+    }
+}
+
+// After a kernel whose stores went to other GPUs: tell every rank that this rank's rows have been written. The
+// stores belong to an earlier kernel of the stream, hence are ordered before this one; the system-scope fence
+// orders them before the arrival for the GPU that observes it.
+__global__ void ep_signal_kernel(unsigned int *const *__restrict__ arrive_tab, int world) {
+    pdl_trigger();
+    pdl_wait();
+    if ((int)threadIdx.x < world) {
+        __threadfence_system();
+        atomicAdd_system(arrive_tab[threadIdx.x], 1u);
+    }
+}
+
+void ep_push_tile(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *const *ids_tab, float *const *ad_tab,
+                  int8_t *const *aq_tab, unsigned int *const *disp_tab, unsigned int *epoch, unsigned int *push_done, int T, int cap,
+                  int n_used, int blocks) {
+    if (g_ep_world < 2 || T < 1 || T > cap) {
+        set_error_msg("ep_push_tile: needs an expert-parallel world and 1..cap tokens");
+        return;
+    }
+    const int ctas = (int)(((size_t)T * blocks * 16 + 255) / 256) < 64 ? (int)(((size_t)T * blocks * 16 + 255) / 256) : 64;
+    launch_k("ep_push_tile", ep_push_tile_kernel, dim3(ctas < 1 ? 1 : ctas, g_ep_world), dim3(256), 0, ids, ad, aq, ids_tab, ad_tab, aq_tab,
+             disp_tab, epoch, push_done, g_ep_rank, T, cap, n_used, blocks);
+}
+void ep_wait_requests(unsigned int *counter, const unsigned int *epoch, int *status, unsigned int limit) {
+    launch_k("ep_wait_requests", ep_wait_kernel, dim3(1), dim3(32), 0, counter, epoch, (unsigned)g_ep_world, status, 2, limit);
+}
+void ep_wait_rows(unsigned int *counter, unsigned int target, int *status, unsigned int limit) {
+    launch_k("ep_wait_rows", ep_wait_kernel, dim3(1), dim3(32), 0, counter, (const unsigned int *)nullptr, target, status, 1, limit);
+}
+void ep_signal_rows(unsigned int *const *arrive_tab) {
+    launch_k("ep_signal_rows", ep_signal_kernel, dim3(1), dim3(32), 0, arrive_tab, g_ep_world);
+}
+
 }  // namespace llamd
 
 using namespace llamd;

@@ -48,6 +48,9 @@ struct GemmParams {
     int n_tokens;
     long long expert_units;  // blocks between consecutive experts in w
     int prefetch_ahead;      // grouped kernel: CTA i asks L2 for the weights of CTA i + prefetch_ahead (0: off)
+    // expert parallelism: output row block o lives on GPU o / out_div, at local row block o % out_div (null: out[j])
+    float *const *out_tab;
+    int out_div;
 };
 
 // Ask L2 for the tiles that hold the 16 x nb blocks starting at block `unit0` (a hint: nothing waits on it).
@@ -275,16 +278,22 @@ __device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int 
             for (int r = 1; r < 8; r++) t = __fadd_rn(t, sums[i][r]);
             tot[i] = t;
         }
-        float *out = p.out[j];
         const bool v0 = n0 + 2 * q4 < count, v1 = n0 + 2 * q4 + 1 < count;
-        const long long o0 = p.out_map ? p.out_map[pa0] : pa0, o1 = p.out_map ? p.out_map[pa1] : pa1;
+        long long o0 = p.out_map ? p.out_map[pa0] : pa0, o1 = p.out_map ? p.out_map[pa1] : pa1;
+        float *out0 = p.out[j], *out1 = p.out[j];
+        if (p.out_tab) {  // the rows of a pair go to the GPU the pair's token lives on (plain peer stores)
+            if (v0) out0 = p.out_tab[o0 / p.out_div];
+            if (v1) out1 = p.out_tab[o1 / p.out_div];
+            o0 %= p.out_div;
+            o1 %= p.out_div;
+        }
         if (row0 + m0 < rows) {
-            if (v0) out[o0 * rows + row0 + m0] = tot[0];
-            if (v1) out[o1 * rows + row0 + m0] = tot[1];
+            if (v0) out0[o0 * rows + row0 + m0] = tot[0];
+            if (v1) out1[o1 * rows + row0 + m0] = tot[1];
         }
         if (row0 + m1 < rows) {
-            if (v0) out[o0 * rows + row0 + m1] = tot[2];
-            if (v1) out[o1 * rows + row0 + m1] = tot[3];
+            if (v0) out0[o0 * rows + row0 + m1] = tot[2];
+            if (v1) out1[o1 * rows + row0 + m1] = tot[3];
         }
     }
 }
@@ -467,7 +476,21 @@ void llamd_fwd_gemm_tokens(const void *w0, const void *w1, const void *w2, const
 void llamd_fwd_expert_gemm(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
                            const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows,
                            int n_expert) {
+    expert_gemm_scatter(wa, wb, gstart, gcount, act_map, pslot, aq_rm, ad, oa, ob, blocks, rows, n_expert, nullptr, 1);
+}
+
+}  // extern "C"
+
+void llamd::expert_gemm_scatter(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
+                                const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows,
+                                int n_expert, float *const *out_tab, int out_div) {
+    if (out_tab && (wb || out_div < 1)) {
+        set_error_msg("expert gemm: scattered outputs take one matrix and a positive row-block count per GPU");
+        return;
+    }
     GemmParams p = {};
+    p.out_tab = out_tab;
+    p.out_div = out_div;
     p.w[0] = (const uint8_t *)wa; p.w[1] = (const uint8_t *)wb;
     p.out[0] = oa; p.out[1] = ob;
     p.rows[0] = rows; p.rows[1] = rows;
@@ -479,5 +502,3 @@ void llamd_fwd_expert_gemm(const void *wa, const void *wb, const int32_t *gstart
     p.expert_units = (long long)rows * blocks;
     gemm_launch(p, n_expert);
 }
-
-}  // extern "C"

@@ -136,6 +136,11 @@ struct Model {
         Buf gstart, gcount, ptoken, pslot, work, n_work;
         Buf aq_rm, aq2_rm;  // the GEMMs' view of aq / aq2: residue-major bytes (integer path) or two f16 terms per element (tcgen05 path)
         int32_t *h_meta = nullptr;
+        // Expert parallelism over peer memory: every rank's tile (activations, scales, routed ids) gathered here by the
+        // ranks' own stores, [world][ep_cap] token rows; then this rank's share of the expert work over all of them.
+        int ep_cap = 0;  // tokens per rank the shared buffers hold; fixed once they have been exported to the peers
+        Buf aq_all, ad_all, ids_all, aq_all_rm, gate_all, up_all, aq2_all, ad2_all, aq2_all_rm, push_done;
+        Buf down_tab, aq_tab, ad_tab, ids_tab;  // device arrays [world]: every rank's down / aq_all / ad_all / ids_all
     } pf;
     // expert parallelism (ep_world > 1): this rank holds experts [own_lo, own_hi)
     int ep_rank = 0, ep_world = 1, own_lo = 0, own_hi = 0;
@@ -634,7 +639,9 @@ void llamd_model_free(llamd_model *h) {
     for (void *p : m->ep_mapped) llamd_cuda_ep_ipc_close(p);
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
                    &m->pf.ids, &m->pf.w, &m->pf.logits, &m->pf.counter, &m->pf.gate, &m->pf.up, &m->pf.down, &m->pf.scores, &m->pf.meta,
-                   &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work, &m->pf.aq_rm, &m->pf.aq2_rm})
+                   &m->pf.gstart, &m->pf.gcount, &m->pf.ptoken, &m->pf.pslot, &m->pf.work, &m->pf.n_work, &m->pf.aq_rm, &m->pf.aq2_rm,
+                   &m->pf.aq_all, &m->pf.ad_all, &m->pf.ids_all, &m->pf.aq_all_rm, &m->pf.gate_all, &m->pf.up_all, &m->pf.aq2_all,
+                   &m->pf.ad2_all, &m->pf.aq2_all_rm, &m->pf.push_done, &m->pf.down_tab, &m->pf.aq_tab, &m->pf.ad_tab, &m->pf.ids_tab})
         b->release();
     if (m->pf.h_meta) cudaFreeHost(m->pf.h_meta);
     for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
@@ -800,9 +807,15 @@ int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32
 // (moe_group), and attention needs no mask because every token of the tile has
 // stored its K and V before any query of the tile runs. Per token the
 // arithmetic is the decode pass's, so prefill == sequential decode exactly.
+constexpr int kGroupMaxPairs = 40960;  // what one scatter plan takes (ops.cu: moe_group_kernel)
+
 static bool prefill_alloc(Model &m, int tile) {
     Model::Prefill &p = m.pf;
     if (p.tile >= tile) return true;
+    if (p.ep_cap) {
+        m.err = "prefill: the tile buffers have been shared with the other ranks and cannot grow (set prefill_tile before the attach)";
+        return false;
+    }
     for (Buf *b : {&p.x, &p.xb, &p.xb2, &p.q, &p.k, &p.v, &p.attn, &p.aq, &p.ad, &p.aq2, &p.ad2, &p.ids, &p.w, &p.logits, &p.counter,
                    &p.gate, &p.up, &p.down, &p.scores, &p.meta, &p.gstart, &p.gcount, &p.ptoken, &p.pslot, &p.work, &p.n_work, &p.aq_rm,
                    &p.aq2_rm})
@@ -817,15 +830,35 @@ static bool prefill_alloc(Model &m, int tile) {
               p.aq2.alloc(T * nu * ffe) && p.ad2.alloc(T * nu * (ffe / 256) * 4) && p.ids.alloc(T * nu * 4) && p.w.alloc(T * nu * 4) &&
               p.logits.alloc(T * ne * 4) && p.counter.alloc(T * 4) && p.gate.alloc(T * nu * ffe * 4) && p.up.alloc(T * nu * ffe * 4) &&
               p.down.alloc(T * nu * E * 4) && p.scores.alloc(T * hp.n_head * (size_t)((m.max_kv + 3) & ~3) * 4) && p.meta.alloc(T * 8) &&
-              p.gstart.alloc(ne * 4) && p.gcount.alloc(ne * 4) && p.ptoken.alloc(T * nu * 4) && p.pslot.alloc(T * nu * 4) &&
+              p.gstart.alloc(ne * 4) && p.gcount.alloc(ne * 4) && p.ptoken.alloc(T * nu * 4 * (size_t)m.ep_world) &&
+              p.pslot.alloc(T * nu * 4 * (size_t)m.ep_world) &&
               p.work.alloc((T * nu / 8 + ne + 1) * 12) && p.n_work.alloc(4) && p.aq_rm.alloc(T * max_act * 4) && p.aq2_rm.alloc(T * nu * ffe * 4) &&
               cudaMallocHost((void **)&p.h_meta, T * 8) == cudaSuccess;
+    if (ok && m.ep_world > 1) {
+        for (Buf *b : {&p.aq_all, &p.ad_all, &p.ids_all, &p.aq_all_rm, &p.gate_all, &p.up_all, &p.aq2_all, &p.ad2_all, &p.aq2_all_rm, &p.push_done,
+                       &p.down_tab, &p.aq_tab, &p.ad_tab, &p.ids_tab})
+            b->release();
+        const size_t W = m.ep_world, G = W * T;  // gathered token rows
+        ok = p.aq_all.alloc(G * E) && p.ad_all.alloc(G * (E / 256) * 4) && p.ids_all.alloc(G * nu * 4) && p.aq_all_rm.alloc(G * E) &&
+             p.gate_all.alloc(G * nu * ffe * 4) && p.up_all.alloc(G * nu * ffe * 4) && p.aq2_all.alloc(G * nu * ffe) &&
+             p.ad2_all.alloc(G * nu * (ffe / 256) * 4) && p.aq2_all_rm.alloc(G * nu * ffe) && p.push_done.alloc(W * 4) &&
+             p.down_tab.alloc(W * sizeof(void *)) && p.aq_tab.alloc(W * sizeof(void *)) && p.ad_tab.alloc(W * sizeof(void *)) &&
+             p.ids_tab.alloc(W * sizeof(void *)) && p.gstart.p && llamd_fwd_sync() == 0;
+    }
     if (!ok) {
         m.err = std::string("prefill buffers: ") + llamd_cuda_last_error_string();
         return false;
     }
     p.tile = tile;
     return true;
+}
+
+// The largest tile expert-parallel prefill can take: the scatter plan covers the pairs of ALL ranks' tiles.
+static int ep_tile_cap(const Model &m) {
+    int cap = kGroupMaxPairs / (m.ep_world * m.hp.n_expert_used);
+    if (cap > m.prefill_tile) cap = m.prefill_tile;
+    if (cap > m.max_kv) cap = m.max_kv;
+    return cap < 1 ? 1 : cap;
 }
 
 static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
@@ -844,7 +877,8 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
         else
             llamd_fwd_combine_rms_norm_quant(x, p.down.as<float>(), p.w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
                                              p.aq.as<int8_t>(), p.ad.as<float>(), E, hp.rms_eps, T);
-        const bool gemm = m.prefill_gemm != 0, tc = m.prefill_gemm == 2;
+        const bool ep = m.ep_world > 1;  // sharded experts run on the integer GEMM; so then do the dense matmuls
+        const bool gemm = m.prefill_gemm != 0 || ep, tc = m.prefill_gemm == 2 && !ep;
         if (tc) {
             llamd_fwd_act_f16_rm(p.aq.as<int8_t>(), p.ad.as<float>(), p.aq_rm.p, (size_t)T * eb);
             llamd_fwd_gemm_tokens_tc(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq_rm.p, p.q.as<float>(), p.k.as<float>(), p.v.as<float>(), eb, qd,
@@ -886,6 +920,34 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
         } else {
             llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), p.xb.as<float>(), E, ne, nu, p.logits.as<float>(), p.ids.as<int32_t>(),
                                     p.w.as<float>(), nullptr, p.counter.as<unsigned int>(), T);
+        }
+        if (m.ep_world > 1) {
+            // Expert parallelism (peer-memory form). Every rank stores its tile's Q8_K activations and routed ids into every
+            // rank's gathered buffers; each rank then plans and runs the pairs whose expert it owns, over all ranks'
+            // tokens, with the integer GEMM, and the down projection stores each pair's rows straight into the buffer of
+            // the rank the token lives on, at the pair's own (token, slot) place: the combine that follows adds them in
+            // routing order exactly as one GPU does. Gathered pair id = (rank * cap + token) * n_used + slot.
+            const int W = m.ep_world, cap = p.ep_cap, G = W * cap, n_local = m.own_hi - m.own_lo;
+            ep_push_tile(p.ids.as<int32_t>(), p.ad.as<float>(), p.aq.as<int8_t>(), p.ids_tab.as<int32_t *>(), p.ad_tab.as<float *>(),
+                         p.aq_tab.as<int8_t *>(), m.ep_disp_tab.as<unsigned int *>(), m.ep_epoch.as<unsigned int>(),
+                         p.push_done.as<unsigned int>(), T, cap, nu, eb);
+            ep_wait_requests(m.ep_disp.as<unsigned int>(), m.ep_epoch.as<unsigned int>(), m.ep_status.as<int>(), m.ep_poll_limit);
+            moe_group_owned(p.ids_all.as<int32_t>(), ne, nu, G, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
+                            p.pslot.as<int32_t>(), nullptr, nullptr, m.own_lo, m.own_hi);
+            llamd_fwd_q8k_residue_major(p.aq_all.as<int8_t>(), p.aq_all_rm.p, (size_t)G * eb);
+            expert_gemm_scatter(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>() + m.own_lo, p.gcount.as<int32_t>() + m.own_lo,
+                                p.ptoken.as<int32_t>(), p.pslot.as<int32_t>(), p.aq_all_rm.p, p.ad_all.as<float>(), p.gate_all.as<float>(),
+                                p.up_all.as<float>(), eb, ffe, n_local, nullptr, 1);
+            // (every gathered pair, owned or not: the others' rows are never read)
+            llamd_fwd_silu_mul_quant(p.gate_all.as<float>(), p.up_all.as<float>(), nullptr, p.aq2_all.as<int8_t>(), p.ad2_all.as<float>(),
+                                     G * nu * ffe);
+            llamd_fwd_q8k_residue_major(p.aq2_all.as<int8_t>(), p.aq2_all_rm.p, (size_t)G * nu * (ffe / 256));
+            expert_gemm_scatter(l.down_exps.p, nullptr, p.gstart.as<int32_t>() + m.own_lo, p.gcount.as<int32_t>() + m.own_lo,
+                                p.pslot.as<int32_t>(), p.pslot.as<int32_t>(), p.aq2_all_rm.p, p.ad2_all.as<float>(), p.down.as<float>(), nullptr,
+                                ffe / 256, E, n_local, p.down_tab.as<float *>(), cap * nu);
+            ep_signal_rows(m.ep_arrive_tab.as<unsigned int *>());
+            ep_wait_rows(m.ep_arrive.as<unsigned int>(), (unsigned)W, m.ep_status.as<int>(), m.ep_poll_limit);
+            continue;
         }
         // the expert scatter plan: (token, slot) pairs sorted by expert
         llamd_fwd_moe_group_work(p.ids.as<int32_t>(), ne, nu, T, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
@@ -941,8 +1003,8 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
             return -1;
         }
     if (!check_ready(*m)) return -1;
-    if (m->ep_world > 1) {
-        // With sharded experts the prompt goes through the decode pass position by position
+    if (m->ep_world > 1 && !(m->ep_p2p && m->pf.ep_cap)) {
+        // With sharded experts and the NCCL exchanges the prompt goes through the decode pass position by position
         // (every rank makes the same number of passes, so the collectives stay in step).
         int32_t out = -1;
         for (int i = 0; i < n_tokens; i++) {
@@ -952,7 +1014,10 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
         *out_token = out;
         return 0;
     }
+    // (expert parallelism over peer memory: tiles of at most the shared capacity; every rank must bring the same number
+    // of tiles, of any length, or the others' bounded waits run out)
     int tile = m->prefill_tile < 1 ? 1 : m->prefill_tile;
+    if (m->ep_world > 1 && tile > m->pf.ep_cap) tile = m->pf.ep_cap;
     if (tile > n_tokens) tile = n_tokens;
     if (!prefill_alloc(*m, tile)) return -1;
     for (int t0 = 0; t0 < n_tokens; t0 += tile) {
@@ -969,7 +1034,13 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
         queue_prefill_tile(*m, T, base_pos + t0 + T, t0 + T >= n_tokens);
     }
     if (cudaMemcpyAsync(m->h_out, m->out_token.p, 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
+    m->h_out[m->max_seq] = 0;
+    if (m->ep_p2p) cudaMemcpyAsync(m->h_out + m->max_seq, m->ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
     if (llamd_fwd_sync() != 0) return -1;
+    if (m->h_out[m->max_seq] != 0) {
+        m->err = ep_wait_message(m->h_out[m->max_seq]);
+        return -1;
+    }
     if (m->prefill_gemm == 2 && llamd_fwd_gemm_tc_status() != 0) {
         m->err = "prefill: a wait inside the tcgen05 GEMM ran out; the pass is incomplete";
         return -1;
@@ -1108,24 +1179,40 @@ int llamd_model_profile_pass(llamd_model *h, int32_t token, int32_t pos, float *
 // attach: the records of ALL ranks in rank order; maps the peers' buffers and switches the decode pass to the form in
 // which requests are pushed to the peers and an owned expert's rows are stored straight into the home rank's buffer.
 // Every rank must attach.
+constexpr int kEpShared = LLAMD_EP_P2P_RECORD / 64;  // buffers every rank shares with the others
 static Buf *ep_shared_buf(Model &m, int i) {
-    Buf *b[6] = {&m.e_down, &m.ep_arrive, &m.ids_all, &m.ad_all, &m.aq_all, &m.ep_disp};
+    Buf *b[kEpShared] = {&m.e_down, &m.ep_arrive, &m.ids_all, &m.ad_all, &m.aq_all, &m.ep_disp,
+                         &m.pf.down, &m.pf.aq_all, &m.pf.ad_all, &m.pf.ids_all};  // the last four: a prefill tile's
     return b[i];
+}
+static Buf *ep_table_buf(Model &m, int i) {
+    Buf *b[kEpShared] = {&m.ep_out_tab, &m.ep_arrive_tab, &m.ep_ids_tab, &m.ep_ad_tab, &m.ep_aq_tab, &m.ep_disp_tab,
+                         &m.pf.down_tab, &m.pf.aq_tab, &m.pf.ad_tab, &m.pf.ids_tab};
+    return b[i];
+}
+// The tile buffers must exist before they can be shared: made here for the current prefill_tile (capped by what one
+// scatter plan over all ranks' tiles can take), and fixed from then on.
+static bool ep_prepare_shared(Model &m) {
+    if (m.pf.ep_cap) return true;
+    const int cap = ep_tile_cap(m);
+    if (!prefill_alloc(m, cap)) return false;
+    m.pf.ep_cap = m.pf.tile;
+    return true;
 }
 int llamd_model_ep_p2p_export(llamd_model *h, void *out) {
     Model *m = (Model *)h;
-    if (!m || !out || m->ep_world < 2) return -1;
-    for (int i = 0; i < 6; i++)
+    if (!m || !out || m->ep_world < 2 || !ep_prepare_shared(*m)) return -1;
+    for (int i = 0; i < kEpShared; i++)
         if (llamd_cuda_ep_ipc_export(ep_shared_buf(*m, i)->p, (char *)out + 64 * i) != 0) return -1;
     return 0;
 }
 int llamd_model_ep_p2p_attach(llamd_model *h, const void *all, int world) {
     Model *m = (Model *)h;
-    if (!m || !all || world != m->ep_world || world < 2) return -1;
-    std::vector<void *> tab[6];
-    for (int i = 0; i < 6; i++) tab[i].resize(world);
+    if (!m || !all || world != m->ep_world || world < 2 || !ep_prepare_shared(*m)) return -1;
+    std::vector<void *> tab[kEpShared];
+    for (int i = 0; i < kEpShared; i++) tab[i].resize(world);
     for (int r = 0; r < world; r++) {
-        for (int i = 0; i < 6; i++) {
+        for (int i = 0; i < kEpShared; i++) {
             if (r == m->ep_rank) {
                 tab[i][r] = ep_shared_buf(*m, i)->p;
                 continue;
@@ -1139,9 +1226,8 @@ int llamd_model_ep_p2p_attach(llamd_model *h, const void *all, int world) {
             tab[i][r] = p;
         }
     }
-    Buf *dev[6] = {&m->ep_out_tab, &m->ep_arrive_tab, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab};
-    for (int i = 0; i < 6; i++)
-        if (cudaMemcpyAsync(dev[i]->p, tab[i].data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess) return -1;
+    for (int i = 0; i < kEpShared; i++)
+        if (cudaMemcpyAsync(ep_table_buf(*m, i)->p, tab[i].data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess) return -1;
     // (the counters are zero since the model was created and only this protocol touches them: clearing them here
     // could erase the arrival of a peer that attached first)
     if (llamd_fwd_sync() != 0) return -1;
@@ -1154,32 +1240,33 @@ int llamd_model_ep_p2p_attach(llamd_model *h, const void *all, int world) {
 // memory mapped by the caller): ptrs is [world][6] in the order of llamd_model_ep_p2p_buffers; row `rank` is ignored.
 int llamd_model_ep_p2p_buffers(llamd_model *h, void **out6) {
     Model *m = (Model *)h;
-    if (!m || !out6 || m->ep_world < 2) return -1;
-    for (int i = 0; i < 6; i++) out6[i] = ep_shared_buf(*m, i)->p;
+    if (!m || !out6 || m->ep_world < 2 || !ep_prepare_shared(*m)) return -1;
+    for (int i = 0; i < kEpShared; i++) out6[i] = ep_shared_buf(*m, i)->p;
     return 0;
 }
 int llamd_model_ep_p2p_attach_ptrs(llamd_model *h, void *const *ptrs, int world) {
     Model *m = (Model *)h;
-    if (!m || !ptrs || world != m->ep_world || world < 2) return -1;
-    std::vector<void *> tab[6];
-    for (int i = 0; i < 6; i++) {
+    if (!m || !ptrs || world != m->ep_world || world < 2 || !ep_prepare_shared(*m)) return -1;
+    std::vector<void *> tab[kEpShared];
+    for (int i = 0; i < kEpShared; i++) {
         tab[i].resize(world);
         for (int r = 0; r < world; r++) {
-            tab[i][r] = r == m->ep_rank ? ep_shared_buf(*m, i)->p : ptrs[(size_t)r * 6 + i];
+            tab[i][r] = r == m->ep_rank ? ep_shared_buf(*m, i)->p : ptrs[(size_t)r * kEpShared + i];
             if (!tab[i][r]) {
                 m->err = "ep_p2p_attach_ptrs: a null buffer";
                 return -1;
             }
         }
     }
-    Buf *dev[6] = {&m->ep_out_tab, &m->ep_arrive_tab, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab};
-    for (int i = 0; i < 6; i++)
-        if (cudaMemcpyAsync(dev[i]->p, tab[i].data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess) return -1;
+    for (int i = 0; i < kEpShared; i++)
+        if (cudaMemcpyAsync(ep_table_buf(*m, i)->p, tab[i].data(), world * sizeof(void *), cudaMemcpyHostToDevice, stream()) != cudaSuccess) return -1;
     if (llamd_fwd_sync() != 0) return -1;
     if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
     m->ep_p2p = 1;
     return 0;
 }
+// Tokens per rank and tile that expert-parallel prefill takes (fixed when the buffers are shared); 0 before that.
+int llamd_model_ep_tile_cap(llamd_model *h) { return h ? ((Model *)h)->pf.ep_cap : 0; }
 // The status word of the bounded device-side waits: 0, or what the first wait that ran out left (1: expert rows, 2: requests).
 int llamd_model_ep_status(llamd_model *h) {
     Model *m = (Model *)h;

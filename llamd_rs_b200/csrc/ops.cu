@@ -822,10 +822,12 @@ __global__ void argmax_final_kernel(const float *__restrict__ pv, const int32_t 
 // Also emits the work list the expert-major matvec walks: entries of up to 8
 // pairs of one expert, (expert, first, count), and their number.
 constexpr int kGroupMaxPerLane = 40;  // pairs per lane: 32 warps x 32 lanes x 40 = 40960 pairs
+// Pairs whose expert lies outside [own_lo, own_hi) are left out of the plan (expert parallelism: they belong to
+// another GPU; an id outside the tensor is left out the same way).
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restrict__ ids, int n_expert, int npair, int n_used,
                                                          int32_t *__restrict__ gstart, int32_t *__restrict__ gcount,
                                                          int32_t *__restrict__ ptoken, int32_t *__restrict__ pslot, int32_t *__restrict__ work,
-                                                         int32_t *__restrict__ n_work) {
+                                                         int32_t *__restrict__ n_work, int own_lo, int own_hi) {
     extern __shared__ int s_hist[];  // [32 warps][n_expert]
     __shared__ int s_count[1024];
     __shared__ int s_start[1024];
@@ -844,8 +846,9 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restri
     for (int s = 0; s < kGroupMaxPerLane; s++) {
         if (s < steps) {
             const int p = warp * chunk + s * 32 + lane;
-            const bool live = p < npair;
-            const int e = live ? ids[p] : -1 - lane;  // dead lanes match nobody
+            int e = p < npair ? ids[p] : -1;
+            const bool live = e >= own_lo && e < own_hi;
+            if (!live) e = -1 - lane;  // dead lanes match nobody
             const unsigned same = __match_any_sync(0xffffffffu, e);
             const int before = __popc(same & ((1u << lane) - 1u));
             int base = 0;
@@ -853,7 +856,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restri
             __syncwarp();
             if (live && before == 0) hist[e] = base + __popc(same);
             __syncwarp();
-            my_rank[s] = ((base + before) << 10) | (e & 1023);
+            my_rank[s] = live ? (((base + before) << 10) | (e & 1023)) : -1;
         }
     }
     __syncthreads();
@@ -900,7 +903,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restri
     for (int s = 0; s < kGroupMaxPerLane; s++) {
         if (s < steps) {
             const int p = warp * chunk + s * 32 + lane;
-            if (p < npair) {
+            if (my_rank[s] >= 0) {
                 const int dst = hist[my_rank[s] & 1023] + (my_rank[s] >> 10);
                 ptoken[dst] = p / n_used;
                 pslot[dst] = p;
@@ -1224,6 +1227,13 @@ void llamd_fwd_argmax(const float *x, int n, float *scratch_v, int32_t *scratch_
 
 void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount,
                               int32_t *ptoken, int32_t *pslot, int32_t *work, int32_t *n_work) {
+    moe_group_owned(ids, n_expert, n_used, nseq, gstart, gcount, ptoken, pslot, work, n_work, 0, n_expert);
+}
+}  // extern "C"
+
+// The plan over the pairs whose expert this GPU holds, [own_lo, own_hi) (all of them without expert parallelism).
+void llamd::moe_group_owned(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount, int32_t *ptoken,
+                            int32_t *pslot, int32_t *work, int32_t *n_work, int own_lo, int own_hi) {
     const int npair = n_used * nseq;
     if (n_expert < 1 || n_expert > 1024 || npair < 0 || npair > 32 * 32 * kGroupMaxPerLane) {
         set_error_msg("moe_group: n_expert 1..1024 and at most 40960 pairs per call");
@@ -1241,8 +1251,10 @@ void llamd_fwd_moe_group_work(const int32_t *ids, int n_expert, int n_used, int 
         configured = smem;
     }
     launch_k("moe_group", moe_group_kernel, dim3(1), dim3(threads), smem, ids, n_expert, npair, n_used, gstart, gcount, ptoken, pslot, work,
-             n_work);
+             n_work, own_lo < 0 ? 0 : own_lo, own_hi > n_expert ? n_expert : own_hi);
 }
+
+extern "C" {
 void llamd_fwd_moe_group(const int32_t *ids, int n_expert, int n_used, int nseq, int32_t *gstart, int32_t *gcount, int32_t *ptoken,
                          int32_t *pslot) {
     llamd_fwd_moe_group_work(ids, n_expert, n_used, nseq, gstart, gcount, ptoken, pslot, nullptr, nullptr);

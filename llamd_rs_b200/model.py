@@ -85,13 +85,15 @@ def _bind():
     L.llamd_model_ep_status.argtypes = [vp]
     L.llamd_model_ep_p2p_buffers.restype = i32
     L.llamd_model_ep_p2p_buffers.argtypes = [vp, vp]
+    L.llamd_model_ep_tile_cap.restype = i32
+    L.llamd_model_ep_tile_cap.argtypes = [vp]
     L.llamd_model_ep_p2p_attach_ptrs.restype = i32
     L.llamd_model_ep_p2p_attach_ptrs.argtypes = [vp, vp, i32]
     L._model_bound = True
     return L
 
 
-EP_P2P_RECORD = 384  # LLAMD_EP_P2P_RECORD: six 64-byte IPC handles
+EP_P2P_RECORD = 640  # LLAMD_EP_P2P_RECORD: ten 64-byte IPC handles
 
 
 def ep_init(rank: int, world: int, share) -> None:
@@ -284,19 +286,23 @@ class CudaModel:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
 
     def ep_p2p_buffers(self):
-        """This rank's six shared buffers as device addresses (expert outputs, arrival counter, gathered ids / scales /
-        quants, dispatch counter)."""
-        out = (C.c_void_p * 6)()
+        """This rank's shared buffers as device addresses: expert outputs, arrival counter, gathered ids / scales / quants,
+        dispatch counter (decode pass); expert outputs, gathered quants / scales / ids (prefill tile)."""
+        out = (C.c_void_p * (EP_P2P_RECORD // 64))()
         if self._L.llamd_model_ep_p2p_buffers(self._h, out) != 0:
             raise backend.Other("ep_p2p buffers: " + (self._err() or backend._last_error()))
         return [int(v or 0) for v in out]
 
     def ep_p2p_attach_ptrs(self, table) -> None:
-        """table: [world][6] device addresses in the order of ep_p2p_buffers (this rank's own row is ignored)."""
+        """table: [world][EP_P2P_RECORD // 64] device addresses in the order of ep_p2p_buffers (this rank's own row is ignored)."""
         world = len(table)
-        flat = (C.c_void_p * (6 * world))(*[int(v) for row in table for v in row])
+        flat = (C.c_void_p * (EP_P2P_RECORD // 64 * world))(*[int(v) for row in table for v in row])
         if self._L.llamd_model_ep_p2p_attach_ptrs(self._h, flat, world) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
+
+    def ep_tile_cap(self) -> int:
+        """Tokens per rank and tile of expert-parallel prefill (0 until the buffers have been shared)."""
+        return int(self._L.llamd_model_ep_tile_cap(self._h))
 
     def ep_status(self) -> int:
         return int(self._L.llamd_model_ep_status(self._h))

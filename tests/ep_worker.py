@@ -8,7 +8,9 @@ logits must be identical, bit for bit: the exchange moves Q8_K activations and
 f32 rows without touching them, and the home rank adds the expert outputs in
 routing order exactly as the single-GPU pass does. The same is then repeated
 with both collectives replaced by stores into the other ranks' buffers over
-NVLink (CUDA IPC) and arrival counters.
+NVLink (CUDA IPC) and arrival counters, and in that form the tiled prefill is
+checked too: every rank's tile gathered on every rank, the owned experts run on
+the grouped GEMM over all ranks' tokens, rows stored to the token's home rank.
 """
 import json
 import os
@@ -34,6 +36,16 @@ def main():
     hp = dict(synth.QWEN3MOE_30B, n_layer=3) if full_size else synth.TINY
     n_prompt, n_gen = 5, 6
     prompt = synth.token_ids(n_prompt, hp["n_vocab"], 11, "ep", rank).tolist()
+    # prefill: ranks bring prompts of different lengths that cut into the same number of tiles
+    max_kv, pf_tile = (160, 64) if full_size else (32, 4)
+    n_pf = (100 if full_size else 7) + rank % 2
+    pf_prompt = synth.token_ids(n_pf, hp["n_vocab"], 12, "ep.prefill", rank).tolist()
+
+    def prefill_then_two(m):
+        tok = m.prefill(pf_prompt, 0)
+        logits = m.logits()[0].copy()
+        t1 = m.forward(tok, n_pf)
+        return [tok, t1, m.forward(t1, n_pf + 1)], logits
 
     def decode(m):
         toks, tok = [], None
@@ -42,11 +54,13 @@ def main():
             toks.append(tok)
         return toks, m.logits()[0].copy()
 
-    m = M.CudaModel.load_synthetic(hp, 5, max_kv=32)
+    m = M.CudaModel.load_synthetic(hp, 5, max_kv=max_kv)
     want_toks, want_logits = decode(m)
     single_bytes = m.weight_bytes()
     m.use_graph = False
     assert decode(m)[0] == want_toks
+    m.use_graph = True
+    want_pf, want_pf_logits = prefill_then_two(m)
     m.free()
 
     def share(b):
@@ -55,7 +69,7 @@ def main():
         return obj[0]
 
     M.ep_init(rank, world, share)
-    m = M.CudaModel.load_synthetic(hp, 5, max_kv=32)
+    m = M.CudaModel.load_synthetic(hp, 5, max_kv=max_kv)
     full_bytes = hp["n_layer"] * 3 * hp["n_expert"] * (hp["n_ff_expert"] * hp["n_embd"] // 256 * 210)
     got_toks, got_logits = decode(m)            # captured graph with the NCCL exchange inside
     m.use_graph = False
@@ -73,11 +87,19 @@ def main():
     p2p_toks, p2p_logits = decode(m)
     m.use_graph = False
     p2p_plain_toks, _ = decode(m)
-    ok = (got_toks == want_toks and plain_toks == want_toks and p2p_toks == want_toks and p2p_plain_toks == want_toks
+    # tiled prefill over peer memory: one tile of the whole capacity, then tiles of pf_tile tokens
+    m.use_graph = True
+    pf_results = []
+    for tile in (m.ep_tile_cap(), pf_tile):
+        m.prefill_tile = tile
+        pf_results.append(prefill_then_two(m))
+    pf_ok = all(t == want_pf and np.array_equal(lg.view(np.uint32), want_pf_logits.view(np.uint32)) for t, lg in pf_results)
+    ok = (pf_ok and got_toks == want_toks and plain_toks == want_toks and p2p_toks == want_toks and p2p_plain_toks == want_toks
           and np.array_equal(got_logits.view(np.uint32), want_logits.view(np.uint32))
           and np.array_equal(plain_logits.view(np.uint32), want_logits.view(np.uint32))
           and np.array_equal(p2p_logits.view(np.uint32), want_logits.view(np.uint32)))
-    res = dict(rank=rank, ok=bool(ok), tokens=got_toks, p2p_tokens=p2p_toks, want=want_toks, weight_bytes=m.weight_bytes(), single_bytes=single_bytes,
+    res = dict(rank=rank, ok=bool(ok), prefill_ok=bool(pf_ok), prefill_tokens=[t for t, _ in pf_results], prefill_want=want_pf,
+               tile_cap=m.ep_tile_cap(), tokens=got_toks, p2p_tokens=p2p_toks, want=want_toks, weight_bytes=m.weight_bytes(), single_bytes=single_bytes,
                full_expert_bytes=full_bytes)
     m.free()
     M.ep_finalize()

@@ -38,10 +38,15 @@ def test_a_wait_for_an_absent_rank_runs_out_and_reports(be):
     try:
         m = M.CudaModel.load_synthetic(hp, 5, max_kv=16)
         E, nu = hp["n_embd"], hp["n_expert_used"]
-        # what rank 1 would have shared: expert outputs, arrival counter, gathered ids / scales / quants, dispatch counter
-        sizes = [nu * E * 4, 256, 2 * nu * 4, 2 * (E // 256) * 4, 2 * E, 256]
+        own = m.ep_p2p_buffers()  # (this also fixes the prefill tile capacity)
+        cap = m.ep_tile_cap()
+        assert cap == 16  # min(prefill_tile, 40960 / (world * n_used), max_kv)
+        # what rank 1 would have shared: expert outputs, arrival counter, gathered ids / scales / quants, dispatch counter,
+        # then a prefill tile's expert outputs and gathered quants / scales / ids
+        sizes = [nu * E * 4, 256, 2 * nu * 4, 2 * (E // 256) * 4, 2 * E, 256,
+                 cap * nu * E * 4, 2 * cap * E, 2 * cap * (E // 256) * 4, 2 * cap * nu * 4]
         absent = [be.DevBuf.zeroed(n) for n in sizes]
-        m.ep_p2p_attach_ptrs([m.ep_p2p_buffers(), [b.ptr for b in absent]])
+        m.ep_p2p_attach_ptrs([own, [b.ptr for b in absent]])
         m.set_option("ep_poll_limit", 2000)  # a fraction of a millisecond per wait
         for use_graph in (True, False):
             m.use_graph = use_graph
@@ -51,6 +56,9 @@ def test_a_wait_for_an_absent_rank_runs_out_and_reports(be):
             assert time.time() - t0 < 5.0, "the bounded wait must give up quickly"
             assert "ran out" in str(err.value) and "recreated" in str(err.value)
             assert m.ep_status() == 2, "the first wait to run out is the one for the other rank's request"
+        with pytest.raises(be.LlamdError) as err:
+            m.prefill([3, 7, 9], 0)  # the tiled path waits for the absent rank's tile just the same
+        assert "ran out" in str(err.value)
         m.free()
     finally:
         M.ep_finalize()
@@ -72,6 +80,7 @@ try:
     print("RESULT joined")
 except backend.LlamdError as e:
     print("RESULT", round(time.time() - t0, 2), M._bind().llamd_cuda_ep_world(), str(e))
+    M._bind().llamd_fwd_last_error()  # read and clear the sticky error, as a caller that goes on would
 import numpy as np
 print("ALIVE", backend.quantize_q8k_on_device(np.arange(256, dtype=np.float32))[0].size)
 sys.stdout.flush()
