@@ -148,15 +148,15 @@ struct DispatchWait {
 // Returns false, with *status = code, when `limit` polls have passed or an earlier wait of the model already failed.
 __device__ __forceinline__ bool bounded_wait(const unsigned int *counter, unsigned int target, bool monotone, int *status, int code,
                                              unsigned int limit) {
-    if (status) {
-        int st;
-        asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(st) : "l"(status) : "memory");
-        if (st != 0) return false;
-    }
     for (unsigned int it = 0; it < limit; it++) {
         unsigned int v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
         if (monotone ? (int)(v - target) >= 0 : v >= target) return true;
+        if (it == 0 && status) {  // not there yet: has an earlier wait of this model already failed? (off the common path)
+            int st;
+            asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(st) : "l"(status) : "memory");
+            if (st != 0) return false;
+        }
         if (it > 32) __nanosleep(128);
     }
     if (status) atomicExch(status, code);
