@@ -277,6 +277,8 @@ def main():
                     "(all-gather + grouped send/recv) instead of peer stores with arrival counters")
     ap.add_argument("--gguf", default="", help="load the model through the GGUF reader instead of tensor by tensor: a path to an "
                     "existing file, or a path that does not exist yet, where the same random-init model is written first")
+    ap.add_argument("--resident", type=int, default=-1, help="1: decode through the resident kernel (one cooperative launch per token); "
+                    "0: the per-op pass; default: the library's own default")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--prefetch", action="store_true", help="(experiment) matvec launches ask L2 for the next matvec's weights; measured slightly slower")
@@ -363,6 +365,8 @@ def main():
         _l().llamd_fwd_set_pdl(0)
     if args.prefetch:
         m.set_option("prefetch", 1)
+    if args.resident >= 0 and not ep:
+        m.set_option("resident", args.resident)
 
     prompt = synth.token_ids(args.prompt, hp["n_vocab"], 0, "prompt", rank)
     if args.workload == "prefill":

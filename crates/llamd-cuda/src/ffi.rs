@@ -143,6 +143,7 @@ unsafe extern "C" {
     pub fn llamd_fwd_silu(x: *const f32, out: *mut f32, n: usize);
     pub fn llamd_fwd_expf(x: *const f32, out: *mut f32, n: usize);
     pub fn llamd_cuda_exp_exceptions() -> c_longlong;
+    pub fn llamd_cuda_exp_window_on() -> c_int;
     pub fn llamd_fwd_mul(a: *const f32, b: *const f32, out: *mut f32, n: usize);
     pub fn llamd_fwd_scale(x: *const f32, by: f32, out: *mut f32, n: usize);
     pub fn llamd_fwd_matmul_f32(w: *const f32, x: *const f32, out: *mut f32, k: c_int, m: c_int, n: c_int);

@@ -42,6 +42,7 @@ SIGNATURES = {
     "llamd_fwd_silu": (None, [vp, vp, sz]),
     "llamd_fwd_expf": (None, [vp, vp, sz]),
     "llamd_cuda_exp_exceptions": (C.c_longlong, []),
+    "llamd_cuda_exp_window_on": (i32, []),
     "llamd_fwd_mul": (None, [vp, vp, vp, sz]),
     "llamd_fwd_scale": (None, [vp, f32, vp, sz]),
     "llamd_fwd_matmul_f32": (None, [vp, vp, vp, i32, i32, i32]),

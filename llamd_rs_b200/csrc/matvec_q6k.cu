@@ -81,15 +81,6 @@ __host__ __device__ inline size_t matvec_ad_offset(int nseq, int nb) {
     return act + (((ex > nat ? ex : nat) + 15) & ~(size_t)15);
 }
 
-// Unpack the four W4 words of quad m of residue r from the three stored words.
-__device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t w[4]) {
-    w[0] = s0 & 0xFCFCFCFCu;
-    w[1] = s1 & 0xFCFCFCFCu;
-    w[2] = s2 & 0xFCFCFCFCu;
-    const uint32_t u = ((s0 << 6) & 0xC0C0C0C0u) | ((s1 << 4) & 0x30303030u);
-    w[3] = u | ((s2 << 2) & 0x0C0C0C0Cu);
-}
-
 // EP: the expert-parallel forms (requests pushed by peers, rows stored to peers); kept out of the other instantiations.
 // EXTRA: the optional L2 prefetch plan and the SiLU tail. Both are off by default, and their code in the plain kernel
 // cost every launch ~0.3 us and lm_head 3 % of its bandwidth, so they too are an instantiation of their own.

@@ -1,0 +1,615 @@
+// The resident decode pass: every layer of one token in ONE cooperative kernel.
+//
+// The per-op pass (model.cu: queue_token) spends most of a token between kernels: a dozen dependent launches per
+// layer, each paying a launch boundary and a cold start, around ~7 us of weight streaming and ~16 us of ordered f32
+// chains. Here one CTA per SM stays resident for the whole token; the layer's phases are separated by grid barriers
+// (an arrive counter in L2, ~1 us) instead of launches, small per-token vectors are recomputed by every CTA from L2
+// instead of being produced by a one-CTA kernel and re-read, the residual stream lives in shared memory, and the
+// weights of the next phase are requested before the barrier that precedes it is waited for.
+//
+// Arithmetic is the per-op pass's, operation for operation (the same device functions and the same chains in the same
+// order), so tokens, expert ids and logits are bit-identical to it and hence to the CPU path
+// (crates/llamd-runtime/src/layer.rs:85-304).
+//
+// Phases of a layer (G CTAs of kMegaThreads threads; "every CTA" = redundantly):
+//   A  every CTA: x += sum_e w_e down_e (previous layer, routing order), attention norm, Q8_K  | its rows of Q, K, V
+//   B  item (head, column quarter): QK-norm, RoPE, KV store, scores, softmax, weighted values of its columns
+//   C  every CTA: Q8_K of the attention output                                               | its rows of attn_out
+//   D  every CTA: x += attn_out, FFN norm, Q8_K (kept for E)                                  | router logit of expert r
+//   E  every CTA: route (softmax, top-n_used, weights)                                        | its rows of gate, up
+//   F  every CTA: silu(gate) * up and Q8_K for the slots its rows touch                       | its rows of down
+// then, after the last layer, the combine + output norm + Q8_K, which the lm_head matvec (a separate launch) reads.
+//
+// Every wait is bounded: a barrier that is not completed within the poll limit sets a status word and the CTA leaves
+// the kernel; the others then run out at their next barrier. The launch is cooperative, so all CTAs are resident and
+// a barrier can only fail through a bug, but nothing spins for ever.
+#include <cooperative_groups.h>
+
+#include "q6k_layout.cuh"
+#include "quant.cuh"
+#include "route.cuh"
+#include "mega.cuh"
+
+namespace llamd {
+
+constexpr int kMegaThreads = 768;
+constexpr int kMegaExStride = kMegaThreads + 1;
+constexpr int kMegaActWords = 132;   // words per activation block image (matvec_q6k.cu: kActBlockWords)
+constexpr int kMegaKTile = 192;      // positions per K tile of the score pass
+constexpr int kMegaSplit = 4;        // output-column parts per head
+
+// shared memory carve-up (floats unless noted), the same on host and device
+struct MegaSmem {
+    size_t x, xn, sq, act, nat, adv, ex, sl, tile, misc, total;
+};
+__host__ __device__ inline MegaSmem mega_smem(int E, int qd, int hd, int act_blocks, int sl_floats, int n_expert) {
+    MegaSmem s;
+    size_t o = 0;
+    auto take = [&](size_t bytes) {
+        const size_t at = o;
+        o += (bytes + 15) & ~(size_t)15;
+        return at;
+    };
+    s.x = take((size_t)E * 4);
+    s.xn = take((size_t)E * 4);
+    const size_t sqn = (size_t)(E > n_expert ? E : n_expert);
+    s.sq = take(sqn * 4);
+    s.act = take((size_t)act_blocks * kMegaActWords * 4);
+    s.nat = take((size_t)act_blocks * 256);
+    s.adv = take((size_t)act_blocks * 4);
+    s.ex = take((size_t)8 * kMegaExStride * 4);
+    s.sl = take((size_t)sl_floats * 4);
+    const size_t ktile = (size_t)kMegaKTile * (hd + 1), vtile = (size_t)kMegaThreads * (hd / kMegaSplit);
+    s.tile = take((ktile > vtile ? ktile : vtile) * 4);
+    s.misc = take((size_t)(4 * hd + 512) * 4);
+    (void)qd;
+    s.total = o;
+    return s;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// All CTAs arrive, all leave; false (for the whole CTA) when the wait ran out.
+__device__ __forceinline__ bool grid_barrier(const MegaParams &p, unsigned int &target, bool *s_flag) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        target += gridDim.x;
+        __threadfence();
+        atomicAdd(p.bar, 1u);
+        bool ok = false;
+        for (unsigned int it = 0; it < p.spin_limit; it++) {
+            if ((int)(ld_acquire_gpu(p.bar) - target) >= 0) {
+                ok = true;
+                break;
+            }
+            if (it > 64) __nanosleep(32);
+        }
+        if (!ok) atomicExch(p.status, 1);
+        *s_flag = ok;
+    }
+    __syncthreads();
+    return *s_flag;
+}
+
+// ---- one (row, block) unit of a Q6_K matvec, as matvec_q6k_kernel does it ---------------------------------------
+struct MvUnit {
+    uint32_t S[48];
+    uint4 scw;
+    uint16_t dbits;
+};
+__device__ __forceinline__ void mv_load(MvUnit &u, const uint8_t *w, size_t unit) {
+    const uint8_t *tile = w + (unit >> 5) * kTileBytes;
+    const int sl = (int)(unit & 31);
+    const uint4 *cp = reinterpret_cast<const uint4 *>(tile) + sl;
+#pragma unroll
+    for (int c = 0; c < 12; c++) {
+        const uint4 v = __ldg(cp + c * 32);
+        u.S[4 * c + 0] = v.x;
+        u.S[4 * c + 1] = v.y;
+        u.S[4 * c + 2] = v.z;
+        u.S[4 * c + 3] = v.w;
+    }
+    u.scw = __ldg(reinterpret_cast<const uint4 *>(tile + kTileScaleOff) + sl);
+    u.dbits = __ldg(reinterpret_cast<const uint16_t *>(tile + kTileDOff) + sl);
+}
+// the unit's eight (d_w * d_a) * aux products into the exchange buffer, column `col`
+__device__ __forceinline__ void mv_compute(const MvUnit &u, const uint32_t *s_act_blk, float adv, float *s_ex, int col) {
+    int sc[16];
+    {
+        const uint32_t ws[4] = {u.scw.x, u.scw.y, u.scw.z, u.scw.w};
+#pragma unroll
+        for (int i = 0; i < 16; i++) sc[i] = (int)(int8_t)(ws[i >> 2] >> (8 * (i & 3)));
+    }
+    int aux[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) aux[r] = 0;
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+#pragma unroll
+        for (int m = 0; m < 2; m++) {
+            uint32_t w4[4];
+            unpack_quad(u.S[6 * r + 3 * m], u.S[6 * r + 3 * m + 1], u.S[6 * r + 3 * m + 2], w4);
+            const uint4 *ap = reinterpret_cast<const uint4 *>(s_act_blk + r * 16 + m * 8);
+            const uint4 a01 = ap[0], a23 = ap[1];
+            int acc = aux[r];
+            acc += sc[8 * m + 0] * __dp4a((int)w4[0], (int)a01.x, 0);
+            acc += sc[8 * m + 1] * __dp4a((int)w4[0], (int)a01.y, 0);
+            acc += sc[8 * m + 2] * __dp4a((int)w4[1], (int)a01.z, 0);
+            acc += sc[8 * m + 3] * __dp4a((int)w4[1], (int)a01.w, 0);
+            acc += sc[8 * m + 4] * __dp4a((int)w4[2], (int)a23.x, 0);
+            acc += sc[8 * m + 5] * __dp4a((int)w4[2], (int)a23.y, 0);
+            acc += sc[8 * m + 6] * __dp4a((int)w4[3], (int)a23.z, 0);
+            acc += sc[8 * m + 7] * __dp4a((int)w4[3], (int)a23.w, 0);
+            aux[r] = acc;
+        }
+    }
+    const float dsc = __fmul_rn(f16_bits_to_f32(u.dbits), adv);
+#pragma unroll
+    for (int r = 0; r < 8; r++) s_ex[r * kMegaExStride + col] = __fmul_rn(dsc, (float)(aux[r] >> 2));
+}
+
+// natural-order Q8_K bytes of `nblk` blocks -> the residue-major (lo, hi) image the units read
+__device__ __forceinline__ void build_act_image(const int8_t *s_nat, uint32_t *s_act, int nblk) {
+    for (int i = threadIdx.x; i < nblk * 64; i += kMegaThreads) {
+        const int jj = i & 7, r = (i >> 3) & 7, sb = i >> 6;
+        const int8_t *src = s_nat + sb * 256;
+        const uint32_t b0 = (uint8_t)src[t32_element(r, jj, 0)], b1 = (uint8_t)src[t32_element(r, jj, 1)];
+        const uint32_t b2 = (uint8_t)src[t32_element(r, jj, 2)], b3 = (uint8_t)src[t32_element(r, jj, 3)];
+        uint32_t *dst = s_act + sb * kMegaActWords + r * 16 + jj * 2;
+        dst[0] = b0 | (b1 << 8);
+        dst[1] = (b2 << 16) | (b3 << 24);
+    }
+}
+
+// A virtual row of a phase: where its weights are, which activation it reads, where its result goes.
+struct RowRef {
+    const uint8_t *w;
+    size_t unit0;  // index of the row's first block in w
+    int act;       // activation index in the image (blocks act*nb ..)
+    float *out;
+};
+
+// The rows [row_lo, row_hi) of a phase, `nb` blocks each, in chunks of floor(T / nb) rows. ROWMAP(row) -> RowRef.
+// The first chunk's weights may have been requested earlier (pre, loaded): they stay in flight across the barrier.
+template <class RowMap>
+__device__ __forceinline__ void mv_issue(MvUnit &u, bool &have, const RowMap &map, int nb, int row_lo, int row_hi) {
+    const int tid = threadIdx.x, row_l = tid / nb, b = tid - row_l * nb;
+    const int cap = kMegaThreads / nb;
+    have = row_l < cap && row_lo + row_l < row_hi;
+    if (have) {
+        const RowRef rr = map(row_lo + row_l);
+        mv_load(u, rr.w, rr.unit0 + b);
+    }
+}
+template <class RowMap>
+__device__ __forceinline__ void mv_finish(MvUnit &u, bool have, const RowMap &map, int nb, int row_lo, int row_hi, const uint32_t *s_act,
+                                          const float *s_adv, float *s_ex) {
+    const int tid = threadIdx.x, row_l = tid / nb, b = tid - row_l * nb;
+    const int cap = kMegaThreads / nb;
+    for (int base = row_lo; base < row_hi; base += cap) {
+        const int rows_here = min(cap, row_hi - base);
+        if (base != row_lo) {  // later chunks: load now (dimensions for which one CTA's rows exceed a chunk)
+            have = row_l < rows_here;
+            if (have) {
+                const RowRef rr = map(base + row_l);
+                mv_load(u, rr.w, rr.unit0 + b);
+            }
+        }
+        if (have) {
+            const RowRef rr = map(base + row_l);
+            mv_compute(u, s_act + (size_t)(rr.act * nb + b) * kMegaActWords, s_adv[rr.act * nb + b], s_ex, tid);
+        }
+        __syncthreads();
+        const int n_out = rows_here * 8;
+        for (int o0 = 0; o0 < n_out; o0 += kMegaThreads) {
+            const int idx = o0 + tid;
+            const bool on = idx < n_out;
+            const int rl = idx >> 3, r = idx & 7;
+            float acc = 0.0f;
+            if (on) {
+                const float *ex = s_ex + r * kMegaExStride + rl * nb;
+                for (int bb = 0; bb < nb; bb++) acc = __fadd_rn(acc, ex[bb]);
+            }
+            const int lane0 = (tid & 31) & ~7;
+            float total = __shfl_sync(0xffffffffu, acc, lane0);
+#pragma unroll
+            for (int q = 1; q < 8; q++) total = __fadd_rn(total, __shfl_sync(0xffffffffu, acc, lane0 + q));
+            if (on && r == 0) *map(base + rl).out = total;
+        }
+        __syncthreads();
+    }
+}
+
+// rms norm of s_x (n floats): squares by all threads, the ordered sum by thread 0, out = (x * scale) * w into s_out,
+// then Q8_K of s_out into s_nat / s_adv (n / 256 blocks). crates/llamd-cpu/src/lib.rs:55-75, dot.rs:88-128.
+__device__ __forceinline__ void norm_quant(const float *s_x, const float *__restrict__ w, float *s_sq, float *s_out, int8_t *s_nat, float *s_adv,
+                                           int n, float eps, float *s_scalar) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < n; i += kMegaThreads) s_sq[i] = __fmul_rn(s_x[i], s_x[i]);
+    __syncthreads();
+    if (tid == 0) {
+        const float sum = chain_sum(s_sq, n, 0.0f);
+        *s_scalar = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+    }
+    __syncthreads();
+    const float scale = *s_scalar;
+    for (int i = tid; i < n; i += kMegaThreads) s_out[i] = __fmul_rn(__fmul_rn(s_x[i], scale), __ldg(w + i));
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int b = warp; b < n / 256; b += kMegaThreads / 32) {
+        const float4 a = reinterpret_cast<const float4 *>(s_out + b * 256 + lane * 8)[0], c = reinterpret_cast<const float4 *>(s_out + b * 256 + lane * 8)[1];
+        const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+        q8k_quantize_block(v, lane, s_nat + b * 256, s_adv + b, nullptr);
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int E = p.E, H = p.H, HKV = p.HKV, hd = p.hd, nu = p.nu, ffe = p.ffe, ne = p.n_expert;
+    const int qd = H * hd, kvd = HKV * hd, eb = E / 256, qb = qd / 256, fb = ffe / 256;
+    const MegaSmem L = mega_smem(E, qd, hd, p.act_blocks, p.sl_floats, ne);
+    float *s_x = reinterpret_cast<float *>(smem + L.x);
+    float *s_xn = reinterpret_cast<float *>(smem + L.xn);
+    float *s_sq = reinterpret_cast<float *>(smem + L.sq);
+    uint32_t *s_act = reinterpret_cast<uint32_t *>(smem + L.act);
+    int8_t *s_nat = reinterpret_cast<int8_t *>(smem + L.nat);
+    float *s_adv = reinterpret_cast<float *>(smem + L.adv);
+    float *s_ex = reinterpret_cast<float *>(smem + L.ex);
+    float *s_sl = reinterpret_cast<float *>(smem + L.sl);
+    float *s_tile = reinterpret_cast<float *>(smem + L.tile);
+    float *s_misc = reinterpret_cast<float *>(smem + L.misc);
+    float *s_q = s_misc, *s_k = s_misc + hd, *s_v = s_misc + 2 * hd, *s_tmp = s_misc + 3 * hd;  // [hd] each
+    float *s_red = s_misc + 4 * hd;                         // [128]: route scratch, scalars
+    int *s_redi = reinterpret_cast<int *>(s_red + 128);     // [128]
+    int32_t *s_ids = reinterpret_cast<int32_t *>(s_red + 256);  // [64]
+    float *s_w = s_red + 320;                               // [64]
+    float *s_scalar = s_red + 384;                          // a few broadcast scalars
+    __shared__ bool s_flag;
+
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x;
+    const int token = p.meta[0], pos = p.meta[1];
+    const int n_kv = pos + 1;
+    unsigned int bar_target = 0;
+    MvUnit u;
+    bool have = false;
+
+    // ---- embed: one row of token_embd, d * sc * q (crates/llamd-quant/src/lib.rs:181-226) ----
+    for (int i = tid; i < E; i += kMegaThreads) {
+        const size_t unit = (size_t)token * eb + (i >> 8);
+        const int e = i & 255;
+        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(p.tok_embd + t32_d_offset(unit)));
+        const float sc = (float)(int8_t)p.tok_embd[t32_scale_offset(unit) + (e >> 4)];
+        s_x[i] = __fmul_rn(__fmul_rn(d, sc), (float)t32_weight(p.tok_embd, unit, e));
+    }
+    __syncthreads();
+
+    for (int il = 0; il <= p.n_layer; il++) {
+        const bool tail = il == p.n_layer;  // after the last layer: combine + output norm only
+        const MegaLayer ly = p.layers[tail ? p.n_layer - 1 : il];
+        // ================= phase A: (combine) + norm + Q8_K | Q, K, V rows =================
+        const int rows_a = qd + 2 * kvd, rpc_a = (rows_a + G - 1) / G;
+        const int a_lo = min(cta * rpc_a, rows_a), a_hi = min(a_lo + rpc_a, rows_a);
+        auto map_a = [&](int row) -> RowRef {
+            if (row < qd) return RowRef{ly.attn_q, (size_t)row * eb, 0, p.q + row};
+            if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
+            return RowRef{ly.attn_v, (size_t)(row - qd - kvd) * eb, 0, p.v + (row - qd - kvd)};
+        };
+        if (!tail) mv_issue(u, have, map_a, eb, a_lo, a_hi);  // in flight while the norm's chain is walked
+        if (il > 0) {
+            // x += sum_e w_e * down_e, e in routing order, the expert sum started from 0 (layer.rs:243-258, 281-287)
+            for (int i = tid; i < E; i += kMegaThreads) {
+                float acc = 0.0f;
+                for (int e = 0; e < nu; e++) acc = __fadd_rn(acc, __fmul_rn(s_w[e], __ldcg(p.e_down + (size_t)e * E + i)));
+                s_x[i] = __fadd_rn(s_x[i], acc);
+            }
+            __syncthreads();
+            if (cta == 0 && p.trace_x)
+                for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = s_x[i];
+        }
+        norm_quant(s_x, tail ? p.output_norm : ly.attn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
+        if (tail) {
+            if (cta == 0) {
+                for (int i = tid; i < E; i += kMegaThreads) {
+                    p.x_out[i] = s_x[i];
+                    p.aq_out[i] = s_nat[i];
+                }
+                if (tid < eb) p.ad_out[tid] = s_adv[tid];
+            }
+            break;
+        }
+        build_act_image(s_nat, s_act, eb);
+        __syncthreads();
+        mv_finish(u, have, map_a, eb, a_lo, a_hi, s_act, s_adv, s_ex);
+        // attn_out's weights do not depend on anything computed here: request them before the barrier
+        const int rpc_c = (E + G - 1) / G;
+        const int c_lo = min(cta * rpc_c, E), c_hi = min(c_lo + rpc_c, E);
+        auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
+        mv_issue(u, have, map_c, qb, c_lo, c_hi);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+
+        // ================= phase B: attention, item (head, column part) =================
+        if (cta < H * kMegaSplit) {
+            const int h = cta / kMegaSplit, c = cta - h * kMegaSplit;
+            const int ratio = H / HKV, kvh = h / ratio, half = hd / 2, cols = hd / kMegaSplit;
+            // the current token's q head, k head, v head
+            for (int i = tid; i < hd; i += kMegaThreads) {
+                s_q[i] = __ldcg(p.q + (size_t)h * hd + i);
+                s_k[i] = __ldcg(p.k + (size_t)kvh * hd + i);
+                s_v[i] = __ldcg(p.v + (size_t)kvh * hd + i);
+            }
+            __syncthreads();
+            // per-head norm (layer.rs:62-79): the sum of squares walked in order, by one thread per vector
+            if (tid == 0 || tid == 32) {
+                const float *sx = tid == 0 ? s_q : s_k;
+                const float *w = tid == 0 ? ly.q_norm : ly.k_norm;
+                float scale = 1.0f;
+                if (w) {
+                    float sum = 0.0f;
+                    for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
+                    scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), p.eps)));
+                }
+                s_scalar[tid == 0 ? 1 : 2] = scale;
+            }
+            __syncthreads();
+            if (tid < 2 * half) {  // NeoX RoPE on (i, i + half) pairs, angles from the host-built table
+                const bool is_k = tid >= half;
+                const int i = is_k ? tid - half : tid;
+                float *sx = is_k ? s_k : s_q;
+                const float *w = is_k ? ly.k_norm : ly.q_norm;
+                const float scale = s_scalar[is_k ? 2 : 1];
+                float a = sx[i], b = sx[i + half];
+                if (w) {
+                    a = __fmul_rn(__fmul_rn(a, scale), __ldg(w + i));
+                    b = __fmul_rn(__fmul_rn(b, scale), __ldg(w + i + half));
+                }
+                const float2 sc = *reinterpret_cast<const float2 *>(p.rope_tab + ((size_t)pos * half + i) * 2);
+                const float o0 = __fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x));
+                const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
+                float *dst = is_k ? s_tmp : s_tile;  // (roped q parks at the start of the tile buffer for a moment)
+                dst[i] = o0;
+                dst[i + half] = o1;
+            }
+            __syncthreads();
+            for (int i = tid; i < hd; i += kMegaThreads) {
+                s_q[i] = s_tile[i];
+                s_k[i] = s_tmp[i];
+            }
+            __syncthreads();
+            if (c == 0 && h % ratio == 0) {  // one item per kv head stores this position's K and V
+                for (int i = tid; i < hd; i += kMegaThreads) {
+                    ly.kc[(size_t)pos * kvd + (size_t)kvh * hd + i] = s_k[i];
+                    ly.vc[(size_t)pos * kvd + (size_t)kvh * hd + i] = s_v[i];
+                }
+            }
+            // scores: logit[t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106)
+            const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+            const float *kb = ly.kc + (size_t)kvh * hd;
+            const int stride = hd + 1, hd4 = hd / 4;
+            float lmax = -INFINITY;
+            for (int t0 = 0; t0 < n_kv; t0 += kMegaKTile) {
+                const int cnt = min(kMegaKTile, n_kv - t0);
+                __syncthreads();
+                for (int idx = tid; idx < cnt * hd4; idx += kMegaThreads) {
+                    const int r = idx / hd4, cc = idx - r * hd4;
+                    const int t = t0 + r;
+                    // the row of this very position is not in the cache yet for the other items: take it from s_k
+                    const float4 v = t == pos ? *reinterpret_cast<const float4 *>(s_k + 4 * cc)
+                                              : __ldg(reinterpret_cast<const float4 *>(kb + (size_t)t * kvd) + cc);
+                    float *d = s_tile + r * stride + 4 * cc;
+                    d[0] = v.x;
+                    d[1] = v.y;
+                    d[2] = v.z;
+                    d[3] = v.w;
+                }
+                __syncthreads();
+                if (tid < cnt) {
+                    const float *kr = s_tile + tid * stride;
+                    float dot = 0.0f;
+                    for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(s_q[d], kr[d]));
+                    const float l = __fmul_rn(dot, scale);
+                    s_sl[t0 + tid] = l;
+                    lmax = fmaxf(lmax, l);
+                }
+            }
+            // max (order-free), e[t] = exp(l - max), the sum walked in order (attention.rs:107-115)
+            for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
+            if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
+            __syncthreads();
+            lmax = s_red[0];
+            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, s_red[w]);
+            __syncthreads();
+            for (int t = tid; t < n_kv; t += kMegaThreads) s_sl[t] = ref_expf(__fsub_rn(s_sl[t], lmax));
+            __syncthreads();
+            if (tid == 0) s_scalar[3] = __fdiv_rn(1.0f, chain_sum(s_sl, n_kv, 0.0f));
+            // weighted values of this item's columns: out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
+            const float *vb = ly.vc + (size_t)kvh * hd + (size_t)c * cols;
+            const int cols4 = cols / 4;
+            float acc = 0.0f;
+            for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
+                const int cnt = min(kMegaThreads, n_kv - t0);
+                __syncthreads();  // (also publishes s_scalar[3]; the K tile is dead)
+                for (int idx = tid; idx < cnt * cols4; idx += kMegaThreads) {
+                    const int r = idx / cols4, cc = idx - r * cols4;
+                    const int t = t0 + r;
+                    const float4 v = t == pos ? *reinterpret_cast<const float4 *>(s_v + c * cols + 4 * cc)
+                                              : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
+                    reinterpret_cast<float4 *>(s_tile)[idx] = v;
+                }
+                __syncthreads();
+                if (tid < cols) {
+                    const float inv = s_scalar[3];
+                    for (int r = 0; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s_sl[t0 + r], inv), s_tile[r * cols + tid]));
+                }
+            }
+            if (tid < cols) p.attn[(size_t)h * hd + (size_t)c * cols + tid] = acc;
+        }
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+
+        // ================= phase C: Q8_K of the attention output | attn_out rows =================
+        {
+            const int warp = tid >> 5, lane = tid & 31;
+            for (int b = warp; b < qb; b += kMegaThreads / 32) {
+                const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8)), c4 = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8) + 1);
+                const float v[8] = {a.x, a.y, a.z, a.w, c4.x, c4.y, c4.z, c4.w};
+                q8k_quantize_block(v, lane, s_nat + b * 256, s_adv + b, nullptr);
+            }
+            __syncthreads();
+            build_act_image(s_nat, s_act, qb);
+            __syncthreads();
+            mv_finish(u, have, map_c, qb, c_lo, c_hi, s_act, s_adv, s_ex);
+        }
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+
+        // ================= phase D: x += attn_out, FFN norm, Q8_K | router logits =================
+        for (int i = tid; i < E; i += kMegaThreads) s_x[i] = __fadd_rn(s_x[i], __ldcg(p.xb2 + i));
+        __syncthreads();
+        norm_quant(s_x, ly.ffn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
+        build_act_image(s_nat, s_act, eb);  // kept for phase E
+        for (int r = cta; r < ne; r += G) {
+            // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
+            const float *wr = ly.router + (size_t)r * E;
+            __syncthreads();
+            for (int i = tid; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
+            __syncthreads();
+            if (tid == 0) p.logits[r] = chain_sum(s_sq, E, -0.0f);
+        }
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+
+        // ================= phase E: route | gate and up rows of the routed experts =================
+        for (int i = tid; i < ne; i += kMegaThreads) s_sq[i] = __ldcg(p.logits + i);
+        __syncthreads();
+        route_block(s_sq, s_red, s_redi, ne, nu, s_ids, s_w, nullptr);
+        __syncthreads();
+        if (cta == 0 && tid < nu) {
+            p.expert_ids[tid] = s_ids[tid];
+            p.expert_w[tid] = s_w[tid];
+            if (p.trace_ids) p.trace_ids[(size_t)il * nu + tid] = s_ids[tid];
+        }
+        const int rows_e = nu * 2 * ffe, rpc_e = (rows_e + G - 1) / G;
+        const int e_lo = min(cta * rpc_e, rows_e), e_hi = min(e_lo + rpc_e, rows_e);
+        auto map_e = [&](int row) -> RowRef {
+            const int slot = row / (2 * ffe), rem = row - slot * 2 * ffe, mat = rem / ffe, r = rem - mat * ffe;
+            int ex = s_ids[slot];
+            if (ex < 0 || ex >= ne) ex = 0;
+            return RowRef{mat ? ly.up : ly.gate, ((size_t)ex * ffe + r) * eb, 0, (mat ? p.e_up : p.e_gate) + (size_t)slot * ffe + r};
+        };
+        mv_issue(u, have, map_e, eb, e_lo, e_hi);
+        mv_finish(u, have, map_e, eb, e_lo, e_hi, s_act, s_adv, s_ex);  // the activation image is phase D's
+        // the down projection's weights are known now (the ids are): request them before the barrier
+        const int rows_f = nu * E, rpc_f = (rows_f + G - 1) / G;
+        const int f_lo = min(cta * rpc_f, rows_f), f_hi = min(f_lo + rpc_f, rows_f);
+        const int slot_lo = f_lo / E, slot_hi = f_hi > f_lo ? (f_hi - 1) / E : slot_lo;
+        auto map_f = [&](int row) -> RowRef {
+            const int slot = row / E, r = row - slot * E;
+            int ex = s_ids[slot];
+            if (ex < 0 || ex >= ne) ex = 0;
+            return RowRef{ly.down, ((size_t)ex * E + r) * fb, slot - slot_lo, p.e_down + (size_t)slot * E + r};
+        };
+        mv_issue(u, have, map_f, fb, f_lo, f_hi);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+
+        // ================= phase F: silu(gate) * up, Q8_K, for the slots of this CTA's rows | down rows =================
+        if (f_hi > f_lo) {
+            const int warp = tid >> 5, lane = tid & 31, nslot = slot_hi - slot_lo + 1;
+            for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
+                const int s = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
+                const size_t base = (size_t)s * ffe + (size_t)b * 256 + lane * 8;
+                const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base) + 1);
+                const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base) + 1);
+                const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
+                                    silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
+                q8k_quantize_block(v, lane, s_nat + blk * 256, s_adv + blk, nullptr);
+            }
+            __syncthreads();
+            build_act_image(s_nat, s_act, nslot * fb);
+            __syncthreads();
+        }
+        mv_finish(u, have, map_f, fb, f_lo, f_hi, s_act, s_adv, s_ex);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+    }
+}
+
+}  // namespace llamd
+
+using namespace llamd;
+
+namespace llamd {
+
+// Shared memory the kernel needs for these dimensions, or 0 when they do not fit it.
+size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats) {
+    const int E = hp.n_embd, qd = hp.n_head * hp.head_dim, ffe = hp.n_ff_expert;
+    int ab = E / 256;
+    if (qd / 256 > ab) ab = qd / 256;
+    if (2 * (ffe / 256) > ab) ab = 2 * (ffe / 256);
+    const int sl = (max_kv + 3) & ~3;
+    if (act_blocks) *act_blocks = ab;
+    if (sl_floats) *sl_floats = sl;
+    return mega_smem(E, qd, hp.head_dim, ab, sl, hp.n_expert).total;
+}
+
+// Can this model run in the resident kernel on the current device? (dimension and shared-memory limits)
+bool mega_supported(const llamd_hparams &hp, int max_kv) {
+    const int E = hp.n_embd, qd = hp.n_head * hp.head_dim, ffe = hp.n_ff_expert, hd = hp.head_dim;
+    if (E % 256 || qd % 256 || ffe % 256 || hd % (4 * kMegaSplit) || hd > kMegaThreads / 2 || hp.n_head % hp.n_head_kv) return false;
+    if (E / 256 > kMegaThreads || qd / 256 > kMegaThreads || hp.n_expert_used > 64 || hp.n_expert > 1024) return false;
+    int dev = 0, sms = 0, optin = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    if (hp.n_head * kMegaSplit > sms || hp.n_expert_used > sms) return false;  // one attention item per CTA; a CTA's down rows span <= 2 slots
+    return mega_smem_bytes(hp, max_kv, nullptr, nullptr) <= (size_t)optin;
+}
+
+// Queue the resident pass for one token (meta = [token, pos] on the device). `bar` and `status` are one word each;
+// the barrier word is cleared here, in stream order, before the launch.
+void launch_decode_mega(MegaParams p, const llamd_hparams &hp) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t smem = mega_smem_bytes(hp, p.max_kv, &p.act_blocks, &p.sl_floats);
+    static size_t configured = 0;
+    if (smem > configured) {
+        const cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error(e, "resident decode kernel: shared memory attribute");
+            return;
+        }
+        configured = smem;
+    }
+    static int resident = -1;
+    if (resident < 0) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_mega_kernel, kMegaThreads, smem) != cudaSuccess) per_sm = 0;
+        resident = per_sm;
+    }
+    if (resident < 1) {
+        set_error_msg("resident decode kernel: a CTA does not fit an SM with these dimensions");
+        return;
+    }
+    if (cudaMemsetAsync(p.bar, 0, sizeof(unsigned int), stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "resident decode kernel: barrier reset");
+        return;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms);
+    cfg.blockDim = dim3(kMegaThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // every CTA resident at once: the grid barriers rely on it
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    g_launches++;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mega_kernel, p);
+    if (e != cudaSuccess) set_error(e, "resident decode kernel");
+}
+
+}  // namespace llamd

@@ -1,0 +1,38 @@
+// Interface of the resident decode kernel (mega.cu) for the model that launches it (model.cu).
+#pragma once
+#include "common.cuh"
+#include "../../include/llamd_cuda_model.h"
+
+namespace llamd {
+
+struct MegaLayer {
+    const uint8_t *attn_q, *attn_k, *attn_v, *attn_out, *gate, *up, *down;  // tiled Q6_K
+    const float *attn_norm, *q_norm, *k_norm, *ffn_norm, *router;           // f32 (q_norm / k_norm may be null)
+    float *kc, *vc;                                                          // [max_kv][kv_dim]
+};
+
+struct MegaParams {
+    int n_layer, E, H, HKV, hd, n_expert, nu, ffe, max_kv;
+    float eps;
+    const MegaLayer *layers;
+    const uint8_t *tok_embd;
+    const float *output_norm, *rope_tab;
+    const int32_t *meta;
+    float *q, *k, *v, *attn, *xb2, *logits, *e_gate, *e_up, *e_down, *x_out, *expert_w;
+    int32_t *expert_ids;
+    int8_t *aq_out;
+    float *ad_out;
+    float *trace_x;      // [n_layer][E] or null
+    int32_t *trace_ids;  // [n_layer][nu] or null
+    unsigned int *bar;
+    int *status;
+    unsigned int spin_limit;
+    int act_blocks;      // blocks the activation image must hold
+    int sl_floats;       // padded max_kv
+};
+
+size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats);
+bool mega_supported(const llamd_hparams &hp, int max_kv);
+void launch_decode_mega(MegaParams p, const llamd_hparams &hp);
+
+}  // namespace llamd

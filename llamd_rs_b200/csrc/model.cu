@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "mega.cuh"
 #include "../../include/llamd_cuda_model.h"
 
 extern "C" {
@@ -156,6 +157,10 @@ struct Model {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_phase;
+    // The resident decode kernel (mega.cu): one cooperative launch per token instead of a dozen launches per layer.
+    int resident = 0;        // option "resident": 1 = use it for single-sequence passes when the dimensions allow
+    Buf mega_layers, mega_bar, mega_status;
+    bool mega_ready = false;
     int fuse_tails = 0;      // 1: the attention output's and the gate/up outputs' follow-up ops run in the producer's last CTA
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
@@ -256,6 +261,57 @@ static MatvecPlans plan_experts(const Model &m, const Buf &w, const int32_t *ids
 }
 constexpr size_t kHeadPrefetchBytes = (size_t)48 << 20;  // of the 256 MB lm_head: what comfortably stays in L2
 
+// The resident kernel reads the layers' pointers from a device table, made once all tensors are there.
+bool mega_prepare(Model &m) {
+    if (m.mega_ready) return true;
+    if (!mega_supported(m.hp, m.max_kv)) return false;
+    std::vector<MegaLayer> tab(m.layers.size());
+    for (size_t i = 0; i < m.layers.size(); i++) {
+        Layer &l = m.layers[i];
+        tab[i] = MegaLayer{l.attn_q.as<uint8_t>(), l.attn_k.as<uint8_t>(), l.attn_v.as<uint8_t>(), l.attn_out.as<uint8_t>(),
+                           l.gate_exps.as<uint8_t>(), l.up_exps.as<uint8_t>(), l.down_exps.as<uint8_t>(), l.attn_norm.as<float>(),
+                           l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr,
+                           l.ffn_norm.as<float>(), l.ffn_gate_inp.as<float>(), l.kc.as<float>(), l.vc.as<float>()};
+    }
+    if (!m.mega_layers.alloc(tab.size() * sizeof(MegaLayer)) || !m.mega_bar.alloc(256) || !m.mega_status.alloc(256)) return false;
+    if (cudaMemcpyAsync(m.mega_layers.p, tab.data(), tab.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, stream()) != cudaSuccess ||
+        llamd_fwd_sync() != 0)
+        return false;
+    m.mega_ready = true;
+    return true;
+}
+
+// One token through the resident kernel, then the head as in the per-op pass.
+void queue_token_resident(Model &m) {
+    const llamd_hparams &hp = m.hp;
+    const int eb = hp.n_embd / 256;
+    MegaParams p = {};
+    p.n_layer = hp.n_layer; p.E = hp.n_embd; p.H = hp.n_head; p.HKV = hp.n_head_kv; p.hd = hp.head_dim;
+    p.n_expert = hp.n_expert; p.nu = hp.n_expert_used; p.ffe = hp.n_ff_expert; p.max_kv = m.max_kv;
+    p.eps = hp.rms_eps;
+    p.layers = m.mega_layers.as<MegaLayer>();
+    p.tok_embd = m.tok_embd.as<uint8_t>();
+    p.output_norm = m.output_norm.as<float>();
+    p.rope_tab = m.rope_tab.as<float>();
+    p.meta = m.meta.as<int32_t>();
+    p.q = m.q.as<float>(); p.k = m.k.as<float>(); p.v = m.v.as<float>(); p.attn = m.attn.as<float>(); p.xb2 = m.xb2.as<float>();
+    p.logits = m.router_logits.as<float>(); p.e_gate = m.e_gate.as<float>(); p.e_up = m.e_up.as<float>(); p.e_down = m.e_down.as<float>();
+    p.x_out = m.x.as<float>(); p.expert_w = m.expert_w.as<float>(); p.expert_ids = m.expert_ids.as<int32_t>();
+    p.aq_out = m.aq.as<int8_t>(); p.ad_out = m.ad.as<float>();
+    p.trace_x = m.trace ? m.trace_x.as<float>() : nullptr;
+    p.trace_ids = m.trace ? m.trace_ids.as<int32_t>() : nullptr;
+    p.bar = m.mega_bar.as<unsigned int>();
+    p.status = m.mega_status.as<int>();
+    p.spin_limit = 1u << 22;
+    launch_decode_mega(p, hp);
+    matvec_batch(MatvecPlans{}, m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
+                 hp.n_vocab, 1);
+    llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
+                     kArgmaxBlocks, 1);
+    launch_k("advance_meta", advance_meta_kernel, dim3(1), dim3(32), 0, m.meta.as<int32_t>(), (const int32_t *)m.out_token.as<int32_t>(),
+             m.tok_log.as<int32_t>(), m.tok_count.as<int32_t>(), 1, m.max_kv * m.max_seq);
+}
+
 // Queue one pass for `nseq` sequences. Does not synchronise.
 // The order is crates/llamd-runtime/src/device.rs:486-655 (itself the CPU
 // order of crates/llamd-runtime/src/layer.rs:85-203, 230-304).
@@ -267,6 +323,10 @@ void queue_token(Model &m, int nseq) {
     const int32_t *meta = m.meta.as<int32_t>();
     float *x = m.x.as<float>();
 
+    if (m.resident && nseq == 1 && m.max_seq == 1 && m.ep_world == 1 && !m.profiling && mega_prepare(m)) {
+        queue_token_resident(m);
+        return;
+    }
     size_t n_marks = 0;
     auto mark = [&](int phase) {
         if (!m.profiling) return;
@@ -491,6 +551,7 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
         m.h_meta[2 * s + 1] = positions[s];
     }
     if (!check_ready(m)) return -1;
+    if (m.resident) mega_prepare(m);  // (uploads a pointer table: not inside a capture)
     // the only per-token host->device traffic: 8 bytes per sequence
     if (cudaMemcpyAsync(m.meta.p, m.h_meta, (size_t)nseq * 8, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
         set_error(cudaGetLastError(), "meta H2D");
@@ -523,10 +584,12 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
     }
     m.h_out[m.max_seq] = 0;
     if (m.ep_p2p) cudaMemcpyAsync(m.h_out + m.max_seq, m.ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
+    if (m.mega_ready && m.resident) cudaMemcpyAsync(m.h_out + m.max_seq, m.mega_status.p, 4, cudaMemcpyDeviceToHost, stream());
     // THE ONE SYNCHRONISE (with NCCL collectives in the pass: bounded on the host, see ep_bounded_sync)
     if ((m.ep_world > 1 && !m.ep_p2p ? ep_bounded_sync() : llamd_fwd_sync()) != 0) return -1;
     if (m.h_out[m.max_seq] != 0) {
-        m.err = ep_wait_message(m.h_out[m.max_seq]);
+        m.err = m.ep_p2p ? ep_wait_message(m.h_out[m.max_seq])
+                         : std::string("resident decode kernel: a grid barrier was not completed within its limit; the pass is incomplete");
         return -1;
     }
     for (int s = 0; s < nseq; s++) {
@@ -634,7 +697,7 @@ void llamd_model_free(llamd_model *h) {
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
-                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab})
+                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab, &m->mega_layers, &m->mega_bar, &m->mega_status})
         b->release();
     for (void *p : m->ep_mapped) llamd_cuda_ep_ipc_close(p);
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
@@ -730,6 +793,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!m || !name) return -1;
     if (!strcmp(name, "use_graph")) {
         m->use_graph = value;
+        return 0;
+    }
+    if (!strcmp(name, "resident")) {
+        if (m->resident != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other pass
+        m->resident = value;
         return 0;
     }
     if (!strcmp(name, "fuse_tails")) {
@@ -1066,6 +1134,7 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
         return -1;
     }
     if (!check_ready(*m)) return -1;
+    if (m->resident) mega_prepare(*m);
     m->h_meta[0] = first_token;
     m->h_meta[1] = start_pos;
     LLAMD_TRY(cudaMemcpyAsync(m->meta.p, m->h_meta, 8, cudaMemcpyHostToDevice, stream()), "decode meta H2D");
@@ -1106,6 +1175,7 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
     }
     m->h_out[m->max_seq] = 0;
     if (rc == 0 && m->ep_p2p) cudaMemcpyAsync(m->h_out + m->max_seq, m->ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
+    if (rc == 0 && m->mega_ready && m->resident) cudaMemcpyAsync(m->h_out + m->max_seq, m->mega_status.p, 4, cudaMemcpyDeviceToHost, stream());
     // whatever was queued is drained before the events go away, also after a failure
     const int sync_rc = (m->ep_world > 1 && !m->ep_p2p) ? ep_bounded_sync() : llamd_fwd_sync();
     if (sync_rc != 0) rc = -1;
@@ -1113,7 +1183,8 @@ int llamd_model_decode(llamd_model *h, int32_t first_token, int32_t start_pos, i
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     if (rc == 0 && m->h_out[m->max_seq] != 0) {
-        m->err = ep_wait_message(m->h_out[m->max_seq]);
+        m->err = m->ep_p2p ? ep_wait_message(m->h_out[m->max_seq])
+                           : std::string("resident decode kernel: a grid barrier was not completed within its limit; the tokens are not valid");
         rc = -1;
     }
     return rc;

@@ -69,6 +69,15 @@ __device__ __forceinline__ int t32_weight(const uint8_t *tiled, size_t unit, int
     return (int)(c6 ^ 0x20u) - 32;
 }
 
+// Unpack the four W4 words of quad m of residue r from the three stored words.
+__device__ __forceinline__ void unpack_quad(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t w[4]) {
+    w[0] = s0 & 0xFCFCFCFCu;
+    w[1] = s1 & 0xFCFCFCFCu;
+    w[2] = s2 & 0xFCFCFCFCu;
+    const uint32_t u = ((s0 << 6) & 0xC0C0C0C0u) | ((s1 << 4) & 0x30303030u);
+    w[3] = u | ((s2 << 2) & 0x0C0C0C0Cu);
+}
+
 // Q8_0 device layout: tiles of 32 rows x 1 block (1088 B): two 16-byte halves
 // of each row's 32 quants, lane-interleaved, then the 32 f16 scales.
 constexpr int kQ80TileBytes = 32 * 34;

@@ -16,11 +16,25 @@ namespace llamd {
 static __constant__ const uint32_t *c_exp_keys = nullptr;  // [mask + 1] input bit patterns, 0 = empty slot
 static __constant__ const uint32_t *c_exp_vals = nullptr;  // [mask + 1] the host expf's result bits
 static __constant__ uint32_t c_exp_mask = 0;
+static __constant__ uint32_t c_exp_window = 0;  // see exp_needs_lookup; 0 = look every input up
+
+// The host's expf can differ from the correctly rounded value only where exp(x) lies very close to the midpoint of
+// two neighbouring floats (its error before the final rounding is a few thousandths of an ulp). The 29 bits of the
+// double result below float precision say how close: the table is consulted only within `window` (in units of
+// 2^-29 ulp) of the midpoint, about one input in sixty. That every listed input passes this test is verified when
+// the table is built, on the device, input by input; if one did not, the window is switched off. Results that are
+// subnormal as floats round at another bit position and are always looked up.
+__device__ __forceinline__ bool exp_needs_lookup(float x, double yd, uint32_t window) {
+    if (window == 0 || x < -87.0f) return true;
+    const uint32_t frac = (uint32_t)__double_as_longlong(yd) & 0x1FFFFFFFu;
+    return frac - (0x10000000u - window) < 2u * window;  // |frac - 2^28| < window
+}
 
 __device__ __forceinline__ float ref_expf(float x) {
-    float y = __double2float_rn(exp((double)x));
+    const double yd = exp((double)x);
+    float y = __double2float_rn(yd);
     const uint32_t *keys = c_exp_keys;
-    if (keys) {
+    if (keys && exp_needs_lookup(x, yd, c_exp_window)) {
         const uint32_t b = __float_as_uint(x), mask = c_exp_mask;
         uint32_t h = (b * 2654435761u) >> 8 & mask;
         for (int probe = 0; probe < 64; probe++) {  // (a table at most a quarter full: runs are short)
@@ -36,12 +50,13 @@ __device__ __forceinline__ float ref_expf(float x) {
     return y;
 }
 
-void register_exp_binder(void (*bind)(const uint32_t *, const uint32_t *, uint32_t));
+void register_exp_binder(void (*bind)(const uint32_t *, const uint32_t *, uint32_t, uint32_t));
 namespace {
-inline void bind_exp_table_here(const uint32_t *keys, const uint32_t *vals, uint32_t mask) {
+inline void bind_exp_table_here(const uint32_t *keys, const uint32_t *vals, uint32_t mask, uint32_t window) {
     cudaMemcpyToSymbol(c_exp_keys, &keys, sizeof keys);
     cudaMemcpyToSymbol(c_exp_vals, &vals, sizeof vals);
     cudaMemcpyToSymbol(c_exp_mask, &mask, sizeof mask);
+    cudaMemcpyToSymbol(c_exp_window, &window, sizeof window);
 }
 struct ExpBinderRegistration {
     ExpBinderRegistration() { register_exp_binder(bind_exp_table_here); }

@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "quant.cuh"
 
 namespace llamd {
 
@@ -27,7 +28,7 @@ static size_t g_scratch_bytes[8] = {};
 
 // ---- the exponential, made identical to the host libm's expf --------------------------------------------------
 // (see quant.cuh: ref_expf). Every translation unit that evaluates exp registers a binder for its constants.
-typedef void (*ExpBinder)(const uint32_t *, const uint32_t *, uint32_t);
+typedef void (*ExpBinder)(const uint32_t *, const uint32_t *, uint32_t, uint32_t);
 static std::vector<ExpBinder> &exp_binders() {
     static std::vector<ExpBinder> v;
     return v;
@@ -36,12 +37,22 @@ void register_exp_binder(ExpBinder bind) { exp_binders().push_back(bind); }
 
 static uint32_t *g_exp_keys_dev = nullptr, *g_exp_vals_dev = nullptr;
 static long long g_exp_exceptions = -1;  // -1: no table (switched off, or it could not be built)
+static uint32_t g_exp_window = 0;        // the look-up window in use (0: every input is looked up)
 
 // out[i] = bits of (float)exp((double)x) for the float whose bits are first + i: the expression of ref_expf
 __global__ void exp_scan_kernel(uint32_t first, uint32_t n, uint32_t *__restrict__ out) {
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         out[i] = __float_as_uint(__double2float_rn(exp((double)__uint_as_float(first + i))));
 }
+
+// flags[i] = would ref_expf consult the table for input bits in[i], with this window?
+__global__ void exp_window_kernel(const uint32_t *__restrict__ in, uint32_t n, uint32_t window, uint32_t *__restrict__ flags) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float x = __uint_as_float(in[i]);
+        flags[i] = exp_needs_lookup(x, exp((double)x), window) ? 1u : 0u;
+    }
+}
+constexpr uint32_t kExpWindow = 1u << 22;  // 2^-7 ulp either side of a midpoint
 
 // Inputs below 2^-25 in magnitude give exactly 1.0f on both sides; above 89 both overflow to +inf, below -104 both
 // give 0. Everything in between is compared, float by float. LLAMD_EXP_TABLE=0 switches the table off.
@@ -111,7 +122,32 @@ static bool build_exp_table(cudaStream_t s) {
         cudaGetLastError();
         return false;
     }
-    for (ExpBinder b : exp_binders()) b(g_exp_keys_dev, g_exp_vals_dev, slots - 1);
+    // The window that spares most inputs the look-up is an observation about the host's expf, not a guarantee: check it
+    // against every listed input, on the device, and do without it if a single one falls outside.
+    uint32_t window = kExpWindow;
+    if (n_exc) {
+        std::vector<uint32_t> in;
+        in.reserve(n_exc);
+        for (auto &v : found)
+            for (size_t i = 0; i < v.size(); i += 2) in.push_back(v[i]);
+        uint32_t *d_in = nullptr, *d_fl = nullptr;
+        std::vector<uint32_t> fl(n_exc, 0);
+        const bool ran = cudaMalloc(&d_in, n_exc * 4) == cudaSuccess && cudaMalloc(&d_fl, n_exc * 4) == cudaSuccess &&
+                         cudaMemcpy(d_in, in.data(), n_exc * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+        if (ran) {
+            exp_window_kernel<<<148 * 4, 256, 0, s>>>(d_in, (uint32_t)n_exc, window, d_fl);
+            if (cudaMemcpyAsync(fl.data(), d_fl, n_exc * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) window = 0;
+        } else {
+            window = 0;
+        }
+        for (uint32_t f : fl)
+            if (!f) window = 0;
+        if (d_in) cudaFree(d_in);
+        if (d_fl) cudaFree(d_fl);
+        cudaGetLastError();
+    }
+    g_exp_window = window;
+    for (ExpBinder b : exp_binders()) b(g_exp_keys_dev, g_exp_vals_dev, slots - 1, window);
     if (cudaDeviceSynchronize() != cudaSuccess || cudaGetLastError() != cudaSuccess) return false;
     g_exp_exceptions = (long long)n_exc;
     return true;
@@ -174,6 +210,9 @@ extern "C" {
 // How many float inputs the device's exp needed correcting for to equal the host libm's expf (the size of the
 // exception table built when the stream was made); -1 when the table is switched off.
 long long llamd_cuda_exp_exceptions(void) { return stream() ? g_exp_exceptions : -1; }
+// 1 when the table is consulted only for results within 2^-7 ulp of a rounding midpoint (every listed input was
+// verified to lie there), 0 when every input is looked up.
+int llamd_cuda_exp_window_on(void) { return stream() && g_exp_window != 0 ? 1 : 0; }
 
 int llamd_cuda_device_count(void) {
     int n = 0;

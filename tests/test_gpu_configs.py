@@ -222,5 +222,9 @@ def test_config3_decode_run_matches_the_cpu_path(be, golden):
         n_dec = n_pos - n_prompt
         toks, _ = m.decode(int(golden["chosen"][n_prompt - 1]), n_prompt, n_dec)
         assert toks.tolist() == golden["chosen"][n_prompt:n_pos].tolist(), "greedy tokens of the resident loop"
+        # the same loop through the resident decode kernel (one cooperative launch per token)
+        m.set_option("resident", 1)
+        toks, _ = m.decode(int(golden["chosen"][n_prompt - 1]), n_prompt, n_dec)
+        assert toks.tolist() == golden["chosen"][n_prompt:n_pos].tolist(), "greedy tokens of the resident decode kernel"
     finally:
         m.free()
