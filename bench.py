@@ -284,6 +284,7 @@ def main():
     ap.add_argument("--prefetch", action="store_true", help="(experiment) matvec launches ask L2 for the next matvec's weights; measured slightly slower")
     ap.add_argument("--batch-sweep", default="", help="(secondary) comma list of batch sizes: time forward_batch over that many "
                     "independent sequences (crates/llamd-runtime/src/device.rs:741-962) and print tok/s per batch size to stderr")
+    ap.add_argument("--resident-phases", action="store_true", help="(diagnostic) per-phase time inside the resident decode kernel, then exit")
     ap.add_argument("--phases", action="store_true", help="(diagnostic) print the per-phase time of an un-graphed pass and exit")
     ap.add_argument("--pdl-sweep", default="", help="(experiment) comma list of PDL class masks to time, e.g. 0,1,5,15")
     ap.add_argument("--no-graph", action="store_true", help="queue every launch instead of replaying the captured graph "
@@ -413,6 +414,23 @@ def main():
             backend.sync()
             dt = time.perf_counter() - t1
             log(f"[batch-sweep] batch {B}: {B * K / dt:.1f} tok/s aggregate, {dt / K * 1e3:.3f} ms/pass, position ~{p0}")
+        return
+    if args.resident_phases:
+        m.set_option("resident", 1)
+        for _ in range(4):
+            tok = m.forward(tok, pos)
+            pos += 1
+        m.set_option("resident_profile", 1)
+        n = 16
+        for _ in range(n):
+            tok = m.forward(tok, pos)
+            pos += 1
+        backend.sync()
+        prof = m.resident_profile()
+        tot = sum(prof.values())
+        for k, v in prof.items():
+            log(f"[resident] {k:28s} {v / n / 1e3:9.1f} us/token {v / n / hp['n_layer'] / 1e3:7.2f} us/layer {100 * v / max(tot, 1):5.1f} %")
+        log(f"[resident] total {tot / n / 1e6:.3f} ms/token inside the kernel (CTA 0's clock)")
         return
     if args.phases:
         m.forward(tok, pos)

@@ -177,6 +177,7 @@ unsafe extern "C" {
     pub fn llamd_model_set_tensor(m: *mut llamd_model, layer: c_int, which: c_int, first_block: usize, host: *const c_void, count: usize) -> c_int;
     pub fn llamd_model_weight_bytes(m: *mut llamd_model) -> usize;
     pub fn llamd_model_set_option(m: *mut llamd_model, name: *const c_char, value: c_int) -> c_int;
+    pub fn llamd_model_resident_profile(m: *mut llamd_model, out32: *mut c_ulonglong) -> c_int;
     pub fn llamd_model_forward(m: *mut llamd_model, token: i32, pos: i32, out_token: *mut i32) -> c_int;
     pub fn llamd_model_forward_batch(m: *mut llamd_model, tokens: *const i32, positions: *const i32, nseq: c_int, out_tokens: *mut i32) -> c_int;
     pub fn llamd_model_prefill(m: *mut llamd_model, tokens: *const i32, n_tokens: c_int, base_pos: c_int, out_token: *mut i32) -> c_int;

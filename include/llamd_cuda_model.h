@@ -123,6 +123,14 @@ size_t llamd_model_weight_bytes(llamd_model *m); /* device.rs:473 */
  * "ep_poll_limit" (polls before a device-side wait on another rank gives up). */
 int llamd_model_set_option(llamd_model *m, const char *name, int value);
 
+/* The resident decode kernel (no counterpart in the reference): option "resident" = 1 runs a single-sequence pass as
+ * ONE cooperative launch per token (every layer inside it, grid barriers between a layer's phases) instead of a dozen
+ * launches per layer; the same arithmetic in the same order, so the same bits. Falls back to the per-op pass when the
+ * dimensions do not fit (shared memory, heads x 4 > SMs) or with max_seq > 1 / expert parallelism. Option
+ * "resident_profile" = 1 makes its CTA 0 accumulate nanoseconds per phase, read by llamd_model_resident_profile
+ * (32 values, 19 used, in the kernel's phase order). */
+int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
+
 /* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */
 int llamd_model_forward(llamd_model *m, int32_t token, int32_t pos, int32_t *out_token);
 /* DeviceModel::forward_batch (device.rs:741-962): nseq independent sequences. */

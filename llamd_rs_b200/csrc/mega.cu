@@ -35,7 +35,7 @@ namespace llamd {
 constexpr int kMegaThreads = 768;
 constexpr int kMegaExStride = kMegaThreads + 1;
 constexpr int kMegaActWords = 132;   // words per activation block image (matvec_q6k.cu: kActBlockWords)
-constexpr int kMegaKTile = 192;      // positions per K tile of the score pass
+constexpr int kMegaKTile = 192;      // positions per K tile of the score pass (rows of head_dim + 4 words)
 constexpr int kMegaSplit = 4;        // output-column parts per head
 
 // shared memory carve-up (floats unless noted), the same on host and device
@@ -59,7 +59,7 @@ __host__ __device__ inline MegaSmem mega_smem(int E, int qd, int hd, int act_blo
     s.adv = take((size_t)act_blocks * 4);
     s.ex = take((size_t)8 * kMegaExStride * 4);
     s.sl = take((size_t)sl_floats * 4);
-    const size_t ktile = (size_t)kMegaKTile * (hd + 1), vtile = (size_t)kMegaThreads * (hd / kMegaSplit);
+    const size_t ktile = (size_t)kMegaKTile * (hd + 4), vtile = (size_t)kMegaThreads * (hd / kMegaSplit);
     s.tile = take((ktile > vtile ? ktile : vtile) * 4);
     s.misc = take((size_t)(4 * hd + 512) * 4);
     (void)qd;
@@ -224,11 +224,20 @@ __device__ __forceinline__ void mv_finish(MvUnit &u, bool have, const RowMap &ma
     }
 }
 
+constexpr int kMegaElems = 4;  // elements of an n_embd-long vector per thread per sweep (n_embd <= 3072 in one sweep)
+
 // rms norm of s_x (n floats): squares by all threads, the ordered sum by thread 0, out = (x * scale) * w into s_out,
 // then Q8_K of s_out into s_nat / s_adv (n / 256 blocks). crates/llamd-cpu/src/lib.rs:55-75, dot.rs:88-128.
+// The weight vector is read before the chain is walked, so that its latency is hidden behind it.
 __device__ __forceinline__ void norm_quant(const float *s_x, const float *__restrict__ w, float *s_sq, float *s_out, int8_t *s_nat, float *s_adv,
                                            int n, float eps, float *s_scalar) {
     const int tid = threadIdx.x;
+    float wv[kMegaElems];
+#pragma unroll
+    for (int u = 0; u < kMegaElems; u++) {
+        const int i = tid + u * kMegaThreads;
+        wv[u] = i < n ? __ldg(w + i) : 0.0f;
+    }
     for (int i = tid; i < n; i += kMegaThreads) s_sq[i] = __fmul_rn(s_x[i], s_x[i]);
     __syncthreads();
     if (tid == 0) {
@@ -237,7 +246,12 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
     }
     __syncthreads();
     const float scale = *s_scalar;
-    for (int i = tid; i < n; i += kMegaThreads) s_out[i] = __fmul_rn(__fmul_rn(s_x[i], scale), __ldg(w + i));
+#pragma unroll
+    for (int u = 0; u < kMegaElems; u++) {
+        const int i = tid + u * kMegaThreads;
+        if (i < n) s_out[i] = __fmul_rn(__fmul_rn(s_x[i], scale), wv[u]);
+    }
+    for (int i = tid + kMegaElems * kMegaThreads; i < n; i += kMegaThreads) s_out[i] = __fmul_rn(__fmul_rn(s_x[i], scale), __ldg(w + i));
     __syncthreads();
     const int warp = tid >> 5, lane = tid & 31;
     for (int b = warp; b < n / 256; b += kMegaThreads / 32) {
@@ -246,6 +260,62 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
         q8k_quantize_block(v, lane, s_nat + b * 256, s_adv + b, nullptr);
     }
     __syncthreads();
+}
+
+// route (crates/llamd-models/src/moe.rs:73-113) by ONE warp: the same operations as route_block -- max, exp(l - max),
+// the sum walked in index order from -0.0, p / sum, n_used rounds of (probability descending, index ascending), the
+// chosen weights summed in choice order from -0.0, the 2^-14 floor, the division -- with the arg-max rounds done by
+// shuffles instead of block-wide barriers. s_p: logits in, probabilities out (taken ones marked -1). Call with warp 0.
+__device__ __forceinline__ void route_warp(float *s_p, int n_expert, int n_used, int32_t *ids, float *weights) {
+    const int lane = threadIdx.x & 31;
+    float m = -INFINITY;
+    for (int i = lane; i < n_expert; i += 32) m = fmaxf(m, s_p[i]);
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    for (int i = lane; i < n_expert; i += 32) s_p[i] = ref_expf(__fsub_rn(s_p[i], m));
+    __syncwarp();
+    float total = 0.0f;
+    if (lane == 0) total = chain_sum(s_p, n_expert, -0.0f);
+    total = __shfl_sync(0xffffffffu, total, 0);
+    for (int i = lane; i < n_expert; i += 32) s_p[i] = __fdiv_rn(s_p[i], total);
+    __syncwarp();
+    for (int k = 0; k < n_used; k++) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < n_expert; i += 32) {
+            const float v = s_p[i];
+            if (v > bv || (v == bv && i < bi)) {
+                bv = v;
+                bi = i;
+            }
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            ids[k] = bi;
+            weights[k] = bv;
+            s_p[bi] = -1.0f;  // taken: cannot win again
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float sum = -0.0f;
+        for (int k = 0; k < n_used; k++) sum = __fadd_rn(sum, weights[k]);
+        sum = fmaxf(sum, WEIGHT_SUM_FLOOR);
+        for (int k = 0; k < n_used; k++) weights[k] = __fdiv_rn(weights[k], sum);
+    }
+    __syncwarp();
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
 }
 
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaParams p) {
@@ -264,11 +334,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     float *s_tile = reinterpret_cast<float *>(smem + L.tile);
     float *s_misc = reinterpret_cast<float *>(smem + L.misc);
     float *s_q = s_misc, *s_k = s_misc + hd, *s_v = s_misc + 2 * hd, *s_tmp = s_misc + 3 * hd;  // [hd] each
-    float *s_red = s_misc + 4 * hd;                         // [128]: route scratch, scalars
-    int *s_redi = reinterpret_cast<int *>(s_red + 128);     // [128]
+    float *s_red = s_misc + 4 * hd;                             // [128] reduction scratch
     int32_t *s_ids = reinterpret_cast<int32_t *>(s_red + 256);  // [64]
-    float *s_w = s_red + 320;                               // [64]
-    float *s_scalar = s_red + 384;                          // a few broadcast scalars
+    float *s_w = s_red + 320;                                   // [64]
+    float *s_scalar = s_red + 384;                              // a few broadcast scalars
     __shared__ bool s_flag;
 
     const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x;
@@ -277,6 +346,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     unsigned int bar_target = 0;
     MvUnit u;
     bool have = false;
+    // optional phase clock: CTA 0 adds the time since the previous stamp to slot k
+    unsigned long long t_prev = 0;
+    const bool prof = p.prof && cta == 0 && tid == 0;
+    if (prof) t_prev = global_ns();
+#define MEGA_STAMP(k)                              \
+    do {                                           \
+        if (prof) {                                \
+            const unsigned long long t_ = global_ns(); \
+            p.prof[k] += t_ - t_prev;              \
+            t_prev = t_;                           \
+        }                                          \
+    } while (0)
 
     // ---- embed: one row of token_embd, d * sc * q (crates/llamd-quant/src/lib.rs:181-226) ----
     for (int i = tid; i < E; i += kMegaThreads) {
@@ -299,18 +380,41 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
             return RowRef{ly.attn_v, (size_t)(row - qd - kvd) * eb, 0, p.v + (row - qd - kvd)};
         };
-        if (!tail) mv_issue(u, have, map_a, eb, a_lo, a_hi);  // in flight while the norm's chain is walked
         if (il > 0) {
-            // x += sum_e w_e * down_e, e in routing order, the expert sum started from 0 (layer.rs:243-258, 281-287)
-            for (int i = tid; i < E; i += kMegaThreads) {
-                float acc = 0.0f;
-                for (int e = 0; e < nu; e++) acc = __fadd_rn(acc, __fmul_rn(s_w[e], __ldcg(p.e_down + (size_t)e * E + i)));
-                s_x[i] = __fadd_rn(s_x[i], acc);
+            // x += sum_e w_e * down_e, e in routing order, the expert sum started from 0 (layer.rs:243-258, 281-287).
+            // All of a sweep's loads are issued before the first is used.
+            for (int base = 0; base < E; base += kMegaElems * kMegaThreads) {
+                float acc[kMegaElems];
+#pragma unroll
+                for (int q = 0; q < kMegaElems; q++) acc[q] = 0.0f;
+                for (int e0 = 0; e0 < nu; e0 += 8) {
+                    float dv[8][kMegaElems];
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+#pragma unroll
+                        for (int q = 0; q < kMegaElems; q++) {
+                            const int i = base + tid + q * kMegaThreads;
+                            dv[e][q] = (e0 + e < nu && i < E) ? __ldcg(p.e_down + (size_t)(e0 + e) * E + i) : 0.0f;
+                        }
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                        if (e0 + e < nu) {
+                            const float we = s_w[e0 + e];
+#pragma unroll
+                            for (int q = 0; q < kMegaElems; q++) acc[q] = __fadd_rn(acc[q], __fmul_rn(we, dv[e][q]));
+                        }
+                }
+#pragma unroll
+                for (int q = 0; q < kMegaElems; q++) {
+                    const int i = base + tid + q * kMegaThreads;
+                    if (i < E) s_x[i] = __fadd_rn(s_x[i], acc[q]);
+                }
             }
             __syncthreads();
             if (cta == 0 && p.trace_x)
                 for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = s_x[i];
         }
+        if (!tail) mv_issue(u, have, map_a, eb, a_lo, a_hi);  // in flight while the norm's chain is walked
         norm_quant(s_x, tail ? p.output_norm : ly.attn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
         if (tail) {
             if (cta == 0) {
@@ -324,13 +428,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         }
         build_act_image(s_nat, s_act, eb);
         __syncthreads();
+        MEGA_STAMP(0);
         mv_finish(u, have, map_a, eb, a_lo, a_hi, s_act, s_adv, s_ex);
-        // attn_out's weights do not depend on anything computed here: request them before the barrier
-        const int rpc_c = (E + G - 1) / G;
-        const int c_lo = min(cta * rpc_c, E), c_hi = min(c_lo + rpc_c, E);
-        auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
-        mv_issue(u, have, map_c, qb, c_lo, c_hi);
+        MEGA_STAMP(1);
         if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(2);
 
         // ================= phase B: attention, item (head, column part) =================
         if (cta < H * kMegaSplit) {
@@ -350,6 +452,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                 float scale = 1.0f;
                 if (w) {
                     float sum = 0.0f;
+#pragma unroll 8
                     for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
                     scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), p.eps)));
                 }
@@ -386,36 +489,70 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                     ly.vc[(size_t)pos * kvd + (size_t)kvh * hd + i] = s_v[i];
                 }
             }
-            // scores: logit[t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106)
+            MEGA_STAMP(3);
+            // scores: logit[t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106). Tiles of kMegaKTile
+            // positions go through shared memory (rows padded to hd + 4 words: 16-byte aligned and conflict-free for the
+            // 16-byte reads below); a thread's loads of a tile are all issued before the first is stored.
             const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
             const float *kb = ly.kc + (size_t)kvh * hd;
-            const int stride = hd + 1, hd4 = hd / 4;
+            const int stride = hd + 4, hd4 = hd / 4;
+            constexpr int kLd = 8;  // 16-byte loads in flight per thread (kMegaKTile * 32 / kMegaThreads at head_dim 128)
             float lmax = -INFINITY;
             for (int t0 = 0; t0 < n_kv; t0 += kMegaKTile) {
                 const int cnt = min(kMegaKTile, n_kv - t0);
                 __syncthreads();
-                for (int idx = tid; idx < cnt * hd4; idx += kMegaThreads) {
-                    const int r = idx / hd4, cc = idx - r * hd4;
-                    const int t = t0 + r;
-                    // the row of this very position is not in the cache yet for the other items: take it from s_k
-                    const float4 v = t == pos ? *reinterpret_cast<const float4 *>(s_k + 4 * cc)
-                                              : __ldg(reinterpret_cast<const float4 *>(kb + (size_t)t * kvd) + cc);
-                    float *d = s_tile + r * stride + 4 * cc;
-                    d[0] = v.x;
-                    d[1] = v.y;
-                    d[2] = v.z;
-                    d[3] = v.w;
+                for (int i0 = 0; i0 < cnt * hd4; i0 += kLd * kMegaThreads) {
+                    float4 reg[kLd];
+#pragma unroll
+                    for (int j = 0; j < kLd; j++) {
+                        const int idx = i0 + tid + j * kMegaThreads;
+                        const int r = idx / hd4, cc = idx - r * hd4;
+                        const int t = t0 + r;
+                        // the row of this very position is not in the cache yet for the other items: take it from s_k
+                        reg[j] = idx >= cnt * hd4 ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                 : t == pos       ? *reinterpret_cast<const float4 *>(s_k + 4 * cc)
+                                                  : __ldg(reinterpret_cast<const float4 *>(kb + (size_t)t * kvd) + cc);
+                    }
+#pragma unroll
+                    for (int j = 0; j < kLd; j++) {
+                        const int idx = i0 + tid + j * kMegaThreads;
+                        if (idx < cnt * hd4) {
+                            const int r = idx / hd4, cc = idx - r * hd4;
+                            *reinterpret_cast<float4 *>(s_tile + r * stride + 4 * cc) = reg[j];
+                        }
+                    }
                 }
                 __syncthreads();
                 if (tid < cnt) {
-                    const float *kr = s_tile + tid * stride;
+                    const float4 *kr = reinterpret_cast<const float4 *>(s_tile + tid * stride);
+                    const float4 *q4 = reinterpret_cast<const float4 *>(s_q);
                     float dot = 0.0f;
-                    for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(s_q[d], kr[d]));
+                    // four 16-byte reads ahead of the adds: the chain is then the dependent adds alone
+                    float pa[16];
+#pragma unroll
+                    for (int j = 0; j < 4 && j < hd4; j++) {
+                        const float4 kv = kr[j], qv = q4[j];
+                        pa[4 * j] = __fmul_rn(qv.x, kv.x), pa[4 * j + 1] = __fmul_rn(qv.y, kv.y), pa[4 * j + 2] = __fmul_rn(qv.z, kv.z), pa[4 * j + 3] = __fmul_rn(qv.w, kv.w);
+                    }
+                    for (int d4 = 0; d4 < hd4; d4 += 4) {
+                        float pb[16];
+                        const int n4 = d4 + 4 < hd4 ? d4 + 4 : d4;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const float4 kv = kr[n4 + j], qv = q4[n4 + j];
+                            pb[4 * j] = __fmul_rn(qv.x, kv.x), pb[4 * j + 1] = __fmul_rn(qv.y, kv.y), pb[4 * j + 2] = __fmul_rn(qv.z, kv.z), pb[4 * j + 3] = __fmul_rn(qv.w, kv.w);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; j++) dot = __fadd_rn(dot, pa[j]);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) pa[j] = pb[j];
+                    }
                     const float l = __fmul_rn(dot, scale);
                     s_sl[t0 + tid] = l;
                     lmax = fmaxf(lmax, l);
                 }
             }
+            MEGA_STAMP(4);
             // max (order-free), e[t] = exp(l - max), the sum walked in order (attention.rs:107-115)
             for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
             if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
@@ -425,32 +562,64 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             __syncthreads();
             for (int t = tid; t < n_kv; t += kMegaThreads) s_sl[t] = ref_expf(__fsub_rn(s_sl[t], lmax));
             __syncthreads();
-            if (tid == 0) s_scalar[3] = __fdiv_rn(1.0f, chain_sum(s_sl, n_kv, 0.0f));
-            // weighted values of this item's columns: out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
+            // the V rows of this item's columns start their trip while the sum is walked
             const float *vb = ly.vc + (size_t)kvh * hd + (size_t)c * cols;
             const int cols4 = cols / 4;
             float acc = 0.0f;
             for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
                 const int cnt = min(kMegaThreads, n_kv - t0);
-                __syncthreads();  // (also publishes s_scalar[3]; the K tile is dead)
-                for (int idx = tid; idx < cnt * cols4; idx += kMegaThreads) {
+                float4 reg[kLd];
+#pragma unroll
+                for (int j = 0; j < kLd; j++) {
+                    const int idx = tid + j * kMegaThreads;
                     const int r = idx / cols4, cc = idx - r * cols4;
                     const int t = t0 + r;
-                    const float4 v = t == pos ? *reinterpret_cast<const float4 *>(s_v + c * cols + 4 * cc)
-                                              : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
-                    reinterpret_cast<float4 *>(s_tile)[idx] = v;
+                    reg[j] = idx >= cnt * cols4 ? make_float4(0.f, 0.f, 0.f, 0.f)
+                             : t == pos         ? *reinterpret_cast<const float4 *>(s_v + c * cols + 4 * cc)
+                                                : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
+                }
+                if (t0 == 0 && tid == 0) s_scalar[3] = __fdiv_rn(1.0f, chain_sum(s_sl, n_kv, 0.0f));
+                __syncthreads();  // (the K tile, or the previous V tile, is dead; the scalar is published)
+#pragma unroll
+                for (int j = 0; j < kLd; j++) {
+                    const int idx = tid + j * kMegaThreads;
+                    if (idx < cnt * cols4) reinterpret_cast<float4 *>(s_tile)[idx] = reg[j];
                 }
                 __syncthreads();
+                if (t0 == 0) MEGA_STAMP(5);
+                // weighted values of this item's columns: out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
                 if (tid < cols) {
                     const float inv = s_scalar[3];
-                    for (int r = 0; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s_sl[t0 + r], inv), s_tile[r * cols + tid]));
+                    int r = 0;
+                    if (cnt >= 16) {
+                        float pa[16], pb[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) pa[j] = __fmul_rn(__fmul_rn(s_sl[t0 + j], inv), s_tile[j * cols + tid]);
+                        for (; r + 16 <= cnt; r += 16) {
+                            const int rn = (r + 32 <= cnt) ? r + 16 : r;
+#pragma unroll
+                            for (int j = 0; j < 16; j++) pb[j] = __fmul_rn(__fmul_rn(s_sl[t0 + rn + j], inv), s_tile[(rn + j) * cols + tid]);
+#pragma unroll
+                            for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, pa[j]);
+#pragma unroll
+                            for (int j = 0; j < 16; j++) pa[j] = pb[j];
+                        }
+                    }
+                    for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s_sl[t0 + r], inv), s_tile[r * cols + tid]));
                 }
+                __syncthreads();
             }
             if (tid < cols) p.attn[(size_t)h * hd + (size_t)c * cols + tid] = acc;
+            MEGA_STAMP(6);
         }
         if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(7);
 
         // ================= phase C: Q8_K of the attention output | attn_out rows =================
+        const int rpc_c = (E + G - 1) / G;
+        const int c_lo = min(cta * rpc_c, E), c_hi = min(c_lo + rpc_c, E);
+        auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
+        mv_issue(u, have, map_c, qb, c_lo, c_hi);
         {
             const int warp = tid >> 5, lane = tid & 31;
             for (int b = warp; b < qb; b += kMegaThreads / 32) {
@@ -463,27 +632,61 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             __syncthreads();
             mv_finish(u, have, map_c, qb, c_lo, c_hi, s_act, s_adv, s_ex);
         }
+        // the router row this CTA will dot, read before the barrier and the norm: its latency hides behind them
+        float wr_pre[kMegaElems];
+#pragma unroll
+        for (int q = 0; q < kMegaElems; q++) {
+            const int i = tid + q * kMegaThreads;
+            wr_pre[q] = (cta < ne && i < E) ? __ldg(ly.router + (size_t)cta * E + i) : 0.0f;
+        }
+        MEGA_STAMP(8);
         if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(9);
 
         // ================= phase D: x += attn_out, FFN norm, Q8_K | router logits =================
-        for (int i = tid; i < E; i += kMegaThreads) s_x[i] = __fadd_rn(s_x[i], __ldcg(p.xb2 + i));
+        {
+            float rv[kMegaElems];
+#pragma unroll
+            for (int q = 0; q < kMegaElems; q++) {
+                const int i = tid + q * kMegaThreads;
+                rv[q] = i < E ? __ldcg(p.xb2 + i) : 0.0f;
+            }
+#pragma unroll
+            for (int q = 0; q < kMegaElems; q++) {
+                const int i = tid + q * kMegaThreads;
+                if (i < E) s_x[i] = __fadd_rn(s_x[i], rv[q]);
+            }
+            for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_x[i] = __fadd_rn(s_x[i], __ldcg(p.xb2 + i));
+        }
         __syncthreads();
         norm_quant(s_x, ly.ffn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
         build_act_image(s_nat, s_act, eb);  // kept for phase E
+        MEGA_STAMP(10);
         for (int r = cta; r < ne; r += G) {
             // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
             const float *wr = ly.router + (size_t)r * E;
             __syncthreads();
-            for (int i = tid; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
+            if (r == cta) {
+#pragma unroll
+                for (int q = 0; q < kMegaElems; q++) {
+                    const int i = tid + q * kMegaThreads;
+                    if (i < E) s_sq[i] = __fmul_rn(wr_pre[q], s_xn[i]);
+                }
+                for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
+            } else {
+                for (int i = tid; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
+            }
             __syncthreads();
             if (tid == 0) p.logits[r] = chain_sum(s_sq, E, -0.0f);
         }
+        MEGA_STAMP(11);
         if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(12);
 
         // ================= phase E: route | gate and up rows of the routed experts =================
         for (int i = tid; i < ne; i += kMegaThreads) s_sq[i] = __ldcg(p.logits + i);
         __syncthreads();
-        route_block(s_sq, s_red, s_redi, ne, nu, s_ids, s_w, nullptr);
+        if (tid < 32) route_warp(s_sq, ne, nu, s_ids, s_w);
         __syncthreads();
         if (cta == 0 && tid < nu) {
             p.expert_ids[tid] = s_ids[tid];
@@ -499,6 +702,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             return RowRef{mat ? ly.up : ly.gate, ((size_t)ex * ffe + r) * eb, 0, (mat ? p.e_up : p.e_gate) + (size_t)slot * ffe + r};
         };
         mv_issue(u, have, map_e, eb, e_lo, e_hi);
+        MEGA_STAMP(13);
         mv_finish(u, have, map_e, eb, e_lo, e_hi, s_act, s_adv, s_ex);  // the activation image is phase D's
         // the down projection's weights are known now (the ids are): request them before the barrier
         const int rows_f = nu * E, rpc_f = (rows_f + G - 1) / G;
@@ -511,7 +715,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             return RowRef{ly.down, ((size_t)ex * E + r) * fb, slot - slot_lo, p.e_down + (size_t)slot * E + r};
         };
         mv_issue(u, have, map_f, fb, f_lo, f_hi);
+        MEGA_STAMP(14);
         if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(15);
 
         // ================= phase F: silu(gate) * up, Q8_K, for the slots of this CTA's rows | down rows =================
         if (f_hi > f_lo) {
@@ -529,9 +735,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             build_act_image(s_nat, s_act, nslot * fb);
             __syncthreads();
         }
+        MEGA_STAMP(16);
         mv_finish(u, have, map_f, fb, f_lo, f_hi, s_act, s_adv, s_ex);
+        MEGA_STAMP(17);
         if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(18);
     }
+#undef MEGA_STAMP
 }
 
 }  // namespace llamd

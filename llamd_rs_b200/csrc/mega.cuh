@@ -25,6 +25,7 @@ struct MegaParams {
     float *trace_x;      // [n_layer][E] or null
     int32_t *trace_ids;  // [n_layer][nu] or null
     unsigned int *bar;
+    unsigned long long *prof;  // [32] nanoseconds per phase, accumulated by CTA 0 (null: off)
     int *status;
     unsigned int spin_limit;
     int act_blocks;      // blocks the activation image must hold

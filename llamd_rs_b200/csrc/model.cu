@@ -159,7 +159,8 @@ struct Model {
     std::vector<int> prof_phase;
     // The resident decode kernel (mega.cu): one cooperative launch per token instead of a dozen launches per layer.
     int resident = 0;        // option "resident": 1 = use it for single-sequence passes when the dimensions allow
-    Buf mega_layers, mega_bar, mega_status;
+    Buf mega_layers, mega_bar, mega_status, mega_prof;
+    int resident_profile = 0;  // option "resident_profile": CTA 0 of the resident kernel accumulates nanoseconds per phase
     bool mega_ready = false;
     int fuse_tails = 0;      // 1: the attention output's and the gate/up outputs' follow-up ops run in the producer's last CTA
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
@@ -273,7 +274,8 @@ bool mega_prepare(Model &m) {
                            l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr,
                            l.ffn_norm.as<float>(), l.ffn_gate_inp.as<float>(), l.kc.as<float>(), l.vc.as<float>()};
     }
-    if (!m.mega_layers.alloc(tab.size() * sizeof(MegaLayer)) || !m.mega_bar.alloc(256) || !m.mega_status.alloc(256)) return false;
+    if (!m.mega_layers.alloc(tab.size() * sizeof(MegaLayer)) || !m.mega_bar.alloc(256) || !m.mega_status.alloc(256) || !m.mega_prof.alloc(32 * 8))
+        return false;
     if (cudaMemcpyAsync(m.mega_layers.p, tab.data(), tab.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, stream()) != cudaSuccess ||
         llamd_fwd_sync() != 0)
         return false;
@@ -303,6 +305,7 @@ void queue_token_resident(Model &m) {
     p.bar = m.mega_bar.as<unsigned int>();
     p.status = m.mega_status.as<int>();
     p.spin_limit = 1u << 22;
+    p.prof = m.resident_profile ? m.mega_prof.as<unsigned long long>() : nullptr;
     launch_decode_mega(p, hp);
     matvec_batch(MatvecPlans{}, m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
                  hp.n_vocab, 1);
@@ -697,7 +700,7 @@ void llamd_model_free(llamd_model *h) {
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
-                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab, &m->mega_layers, &m->mega_bar, &m->mega_status})
+                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab, &m->mega_layers, &m->mega_bar, &m->mega_status, &m->mega_prof})
         b->release();
     for (void *p : m->ep_mapped) llamd_cuda_ep_ipc_close(p);
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
@@ -798,6 +801,12 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "resident")) {
         if (m->resident != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other pass
         m->resident = value;
+        return 0;
+    }
+    if (!strcmp(name, "resident_profile")) {
+        if (m->resident_profile != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
+        m->resident_profile = value;
+        if (m->mega_prof.p) cudaMemsetAsync(m->mega_prof.p, 0, 32 * 8, stream());
         return 0;
     }
     if (!strcmp(name, "fuse_tails")) {
@@ -1335,6 +1344,14 @@ int llamd_model_ep_p2p_attach_ptrs(llamd_model *h, void *const *ptrs, int world)
     if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
     m->ep_p2p = 1;
     return 0;
+}
+// Nanoseconds per phase of the resident decode kernel, accumulated by its CTA 0 since "resident_profile" was set:
+// 19 slots in the kernel's order (A prologue, A rows, barrier, B prepare, B scores, B softmax, B values, barrier, C,
+// barrier, D norm, D router, barrier, E route, E rows, barrier, F activation, F rows, barrier); out32 gets 32 values.
+int llamd_model_resident_profile(llamd_model *h, unsigned long long *out32) {
+    Model *m = (Model *)h;
+    if (!m || !out32 || !m->mega_prof.p) return -1;
+    return llamd_fwd_download(out32, m->mega_prof.p, 32 * 8);
 }
 // Tokens per rank and tile that expert-parallel prefill takes (fixed when the buffers are shared); 0 before that.
 int llamd_model_ep_tile_cap(llamd_model *h) { return h ? ((Model *)h)->pf.ep_cap : 0; }

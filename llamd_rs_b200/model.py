@@ -85,6 +85,8 @@ def _bind():
     L.llamd_model_ep_status.argtypes = [vp]
     L.llamd_model_ep_p2p_buffers.restype = i32
     L.llamd_model_ep_p2p_buffers.argtypes = [vp, vp]
+    L.llamd_model_resident_profile.restype = i32
+    L.llamd_model_resident_profile.argtypes = [vp, vp]
     L.llamd_model_ep_tile_cap.restype = i32
     L.llamd_model_ep_tile_cap.argtypes = [vp]
     L.llamd_model_ep_p2p_attach_ptrs.restype = i32
@@ -299,6 +301,17 @@ class CudaModel:
         flat = (C.c_void_p * (EP_P2P_RECORD // 64 * world))(*[int(v) for row in table for v in row])
         if self._L.llamd_model_ep_p2p_attach_ptrs(self._h, flat, world) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
+
+    RESIDENT_PHASES = ("A combine+norm+quant", "A qkv rows", "barrier", "B qk-norm rope", "B scores", "B softmax", "B values", "barrier",
+                       "C quant + attn_out rows", "barrier", "D add+norm+quant", "D router", "barrier", "E route", "E gate/up rows",
+                       "barrier", "F silu+quant", "F down rows", "barrier")
+
+    def resident_profile(self) -> dict:
+        """Nanoseconds per phase accumulated by the resident kernel's CTA 0 since set_option("resident_profile", 1)."""
+        out = (C.c_ulonglong * 32)()
+        if self._L.llamd_model_resident_profile(self._h, out) != 0:
+            raise backend.Other("resident profile: " + (self._err() or backend._last_error()))
+        return {f"{i:02d} {name}": int(out[i]) for i, name in enumerate(self.RESIDENT_PHASES)}
 
     def ep_tile_cap(self) -> int:
         """Tokens per rank and tile of expert-parallel prefill (0 until the buffers have been shared)."""

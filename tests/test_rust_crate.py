@@ -31,7 +31,7 @@ C_TO_RUST = {
     "const llamd_gguf *": "*const llamd_gguf", "const llamd_hparams *": "*const llamd_hparams", "llamd_hparams *": "*mut llamd_hparams",
     "void **": "*mut *mut c_void", "void *const *": "*const *mut c_void", "const void **": "*mut *const c_void",
     "const char **": "*mut *const c_char", "int32_t": "i32", "uint8_t *": "*mut u8", "const uint8_t *": "*const u8",
-    "int64_t *": "*mut i64", "double *": "*mut f64",
+    "int64_t *": "*mut i64", "double *": "*mut f64", "unsigned long long *": "*mut c_ulonglong", "long long *": "*mut c_longlong",
 }
 
 
