@@ -181,6 +181,7 @@ unsafe extern "C" {
     pub fn llamd_model_forward(m: *mut llamd_model, token: i32, pos: i32, out_token: *mut i32) -> c_int;
     pub fn llamd_model_forward_batch(m: *mut llamd_model, tokens: *const i32, positions: *const i32, nseq: c_int, out_tokens: *mut i32) -> c_int;
     pub fn llamd_model_prefill(m: *mut llamd_model, tokens: *const i32, n_tokens: c_int, base_pos: c_int, out_token: *mut i32) -> c_int;
+    pub fn llamd_model_verify(m: *mut llamd_model, tokens: *const i32, n_tokens: c_int, base_pos: c_int, out_tokens: *mut i32) -> c_int;
     pub fn llamd_model_decode(m: *mut llamd_model, first_token: i32, start_pos: i32, n: c_int, out_tokens: *mut i32, ms_out: *mut f32) -> c_int;
     pub fn llamd_model_bench_matvecs(m: *mut llamd_model, iters: c_int, nseq: c_int, ms_out: *mut f32, launches_out: *mut c_int) -> c_int;
     pub fn llamd_model_launches_per_pass(m: *mut llamd_model) -> c_ulonglong;

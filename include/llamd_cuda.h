@@ -34,7 +34,8 @@ extern "C" {
 #define LLAMD_QK_K 256
 #define LLAMD_Q6K_BLOCK_BYTES 210
 #define LLAMD_Q8_0_BLOCK_BYTES 34
-#define LLAMD_MAX_SEQ 8 /* crates/llamd-rocm/kernels/llamd_batch.hip:41 MAX_SEQ */
+#define LLAMD_MAX_SEQ 8 /* crates/llamd-rocm/kernels/llamd_batch.hip:41 MAX_SEQ: sequences per launch of the nseq kernels */
+#define LLAMD_MAX_BATCH 256 /* sequences a model can hold; beyond LLAMD_MAX_SEQ a pass runs on the prefill GEMM kernels */
 
 /* ---- device discovery: crates/llamd-rocm/src/lib.rs:74-85 ------------- */
 int llamd_cuda_device_count(void);

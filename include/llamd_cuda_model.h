@@ -133,13 +133,21 @@ int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
 
 /* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */
 int llamd_model_forward(llamd_model *m, int32_t token, int32_t pos, int32_t *out_token);
-/* DeviceModel::forward_batch (device.rs:741-962): nseq independent sequences. */
+/* DeviceModel::forward_batch (device.rs:741-962): nseq independent sequences. Up to LLAMD_MAX_SEQ (8) they share
+ * each weight read inside the nseq kernels; from 9 to max_seq (at most LLAMD_MAX_BATCH) the pass runs as a prefill
+ * tile whose tokens belong to different sequences, on the integer GEMM. Either way sequence s gets exactly the
+ * single-sequence pass's bits. */
 int llamd_model_forward_batch(llamd_model *m, const int32_t *tokens, const int32_t *positions, int nseq,
                               int32_t *out_tokens);
 /* VulkanModel::prefill (crates/llamd-runtime/src/vulkan_model.rs:877-907):
  * consume n_tokens prompt ids at positions base_pos.., return the greedy token
  * after the last one. */
 int llamd_model_prefill(llamd_model *m, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_token);
+/* Verification for speculative decoding (the reference plans it "verified only": docs/porting-matrix.md row 20). Consumes
+ * n_tokens at base_pos.. like llamd_model_prefill, but out_tokens[i] = the greedy token after tokens[0..=i], for every
+ * i. A drafter keeps the longest prefix with tokens[i + 1] == out_tokens[i]; output with drafting equals output
+ * without it, because the tiled pass equals token-by-token decode bit for bit. */
+int llamd_model_verify(llamd_model *m, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_tokens);
 /* Resident greedy decode: n passes back to back, each pass's token fed to the
  * next on the device, one synchronise at the end; the same tokens as n calls
  * of llamd_model_forward. ms_out (may be NULL) gets the device time of the n

@@ -20,6 +20,7 @@ QK_K = 256
 Q6K_BLOCK_BYTES = 210
 Q8_0_BLOCK_BYTES = 34
 MAX_SEQ = 8
+MAX_BATCH = 256  # LLAMD_MAX_BATCH: sequences a model can hold (beyond MAX_SEQ a pass runs on the prefill GEMM kernels)
 
 
 class LlamdError(RuntimeError):

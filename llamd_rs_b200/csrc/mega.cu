@@ -35,14 +35,13 @@ namespace llamd {
 constexpr int kMegaThreads = 768;
 constexpr int kMegaExStride = kMegaThreads + 1;
 constexpr int kMegaActWords = 132;   // words per activation block image (matvec_q6k.cu: kActBlockWords)
-constexpr int kMegaKTile = 192;      // positions per K tile of the score pass (rows of head_dim + 4 words)
 constexpr int kMegaSplit = 4;        // output-column parts per head
 
 // shared memory carve-up (floats unless noted), the same on host and device
 struct MegaSmem {
     size_t x, xn, sq, act, nat, adv, ex, sl, tile, misc, total;
 };
-__host__ __device__ inline MegaSmem mega_smem(int E, int qd, int hd, int act_blocks, int sl_floats, int n_expert) {
+__host__ __device__ inline MegaSmem mega_smem(int E, int qd, int hd, int act_blocks, int sl_floats, int n_expert, int ktile_rows, int ratio) {
     MegaSmem s;
     size_t o = 0;
     auto take = [&](size_t bytes) {
@@ -59,7 +58,9 @@ __host__ __device__ inline MegaSmem mega_smem(int E, int qd, int hd, int act_blo
     s.adv = take((size_t)act_blocks * 4);
     s.ex = take((size_t)8 * kMegaExStride * 4);
     s.sl = take((size_t)sl_floats * 4);
-    const size_t ktile = (size_t)kMegaKTile * (hd + 4), vtile = (size_t)kMegaThreads * (hd / kMegaSplit);
+    // B1: the K rows of this CTA's position chunk (rows of hd + 4 words) after the group's q heads, raw and roped;
+    // B2: a V tile of kMegaThreads positions x hd / kMegaSplit columns
+    const size_t ktile = (size_t)ktile_rows * (hd + 4) + 2 * (size_t)ratio * hd, vtile = (size_t)kMegaThreads * (hd / kMegaSplit);
     s.tile = take((ktile > vtile ? ktile : vtile) * 4);
     s.misc = take((size_t)(4 * hd + 512) * 4);
     (void)qd;
@@ -224,6 +225,26 @@ __device__ __forceinline__ void mv_finish(MvUnit &u, bool have, const RowMap &ma
     }
 }
 
+// Hints to L2 (nothing waits on them): a byte range, cut into pieces that the CTA's threads each ask for; the tiles that
+// hold blocks [unit_lo, unit_hi) of a tiled Q6_K matrix; a phase's rows [lo, hi) as far as they fall into the matrix
+// that holds virtual rows [first, first + rows).
+__device__ __forceinline__ void l2_prefetch_bytes(const uint8_t *base, size_t bytes) {
+    constexpr size_t kPiece = 8192;
+    for (size_t off = (size_t)threadIdx.x * kPiece; off < bytes; off += (size_t)kMegaThreads * kPiece) {
+        const size_t n = (bytes - off < kPiece ? bytes - off : kPiece) & ~(size_t)15;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"((uint32_t)n) : "memory");
+    }
+}
+__device__ __forceinline__ void l2_prefetch_units(const uint8_t *w, size_t unit_lo, size_t unit_hi) {
+    if (unit_hi <= unit_lo) return;
+    const size_t t0 = unit_lo >> 5, t1 = (unit_hi - 1) >> 5;
+    l2_prefetch_bytes(w + t0 * kTileBytes, (t1 - t0 + 1) * kTileBytes);
+}
+__device__ __forceinline__ void l2_prefetch_rows(const uint8_t *w, int lo, int hi, int first, int rows, int nb) {
+    const int a = max(lo, first), b = min(hi, first + rows);
+    if (b > a) l2_prefetch_units(w, (size_t)(a - first) * nb, (size_t)(b - first) * nb);
+}
+
 constexpr int kMegaElems = 4;  // elements of an n_embd-long vector per thread per sweep (n_embd <= 3072 in one sweep)
 
 // rms norm of s_x (n floats): squares by all threads, the ordered sum by thread 0, out = (x * scale) * w into s_out,
@@ -322,7 +343,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     extern __shared__ __align__(16) uint8_t smem[];
     const int E = p.E, H = p.H, HKV = p.HKV, hd = p.hd, nu = p.nu, ffe = p.ffe, ne = p.n_expert;
     const int qd = H * hd, kvd = HKV * hd, eb = E / 256, qb = qd / 256, fb = ffe / 256;
-    const MegaSmem L = mega_smem(E, qd, hd, p.act_blocks, p.sl_floats, ne);
+    const MegaSmem L = mega_smem(E, qd, hd, p.act_blocks, p.sl_floats, ne, p.ktile_rows, H / HKV);
     float *s_x = reinterpret_cast<float *>(smem + L.x);
     float *s_xn = reinterpret_cast<float *>(smem + L.xn);
     float *s_sq = reinterpret_cast<float *>(smem + L.sq);
@@ -333,7 +354,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     float *s_sl = reinterpret_cast<float *>(smem + L.sl);
     float *s_tile = reinterpret_cast<float *>(smem + L.tile);
     float *s_misc = reinterpret_cast<float *>(smem + L.misc);
-    float *s_q = s_misc, *s_k = s_misc + hd, *s_v = s_misc + 2 * hd, *s_tmp = s_misc + 3 * hd;  // [hd] each
+    float *s_k = s_misc + hd, *s_v = s_misc + 2 * hd, *s_tmp = s_misc + 3 * hd;  // [hd] each
     float *s_red = s_misc + 4 * hd;                             // [128] reduction scratch
     int32_t *s_ids = reinterpret_cast<int32_t *>(s_red + 256);  // [64]
     float *s_w = s_red + 320;                                   // [64]
@@ -369,17 +390,53 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     }
     __syncthreads();
 
+    // Row ranges of the phases (the same every layer)
+    const int rows_a = qd + 2 * kvd, rpc_a = (rows_a + G - 1) / G;
+    const int a_lo = min(cta * rpc_a, rows_a), a_hi = min(a_lo + rpc_a, rows_a);
+    const int rpc_c = (E + G - 1) / G;
+    const int c_lo = min(cta * rpc_c, E), c_hi = min(c_lo + rpc_c, E);
+    const int rows_e = nu * 2 * ffe, rpc_e = (rows_e + G - 1) / G;
+    const int e_lo = min(cta * rpc_e, rows_e), e_hi = min(e_lo + rpc_e, rows_e);
+    const int rows_f = nu * E, rpc_f = (rows_f + G - 1) / G;
+    const int f_lo = min(cta * rpc_f, rows_f), f_hi = min(f_lo + rpc_f, rows_f);
+    const int slot_lo = f_lo / E, slot_hi = f_hi > f_lo ? (f_hi - 1) / E : slot_lo;
+    // attention, first half: CTA -> (kv head, chunk of positions); second half: CTA -> (head, column part)
+    const int ratio = H / HKV, half = hd / 2, cols = hd / kMegaSplit;
+    const int ncp = G / HKV;  // position chunks per kv head
+    const int b1_kvh = cta / ncp, b1_chunk = cta - b1_kvh * ncp;
+    const int ppc = (n_kv + ncp - 1) / ncp;
+    const int t_lo = min(b1_chunk * ppc, n_kv), t_hi = b1_kvh < HKV ? min(t_lo + ppc, n_kv) : t_lo;
+    const bool b1_has_pos = b1_kvh < HKV && pos >= t_lo && pos < t_hi;
+
+    // What this CTA will read of a layer's attention-side weights, asked of L2 ahead of time (hints: nothing waits).
+    auto prefetch_attn_side = [&](const MegaLayer &w) {
+        l2_prefetch_rows(w.attn_q, a_lo, a_hi, 0, qd, eb);
+        l2_prefetch_rows(w.attn_k, a_lo, a_hi, qd, kvd, eb);
+        l2_prefetch_rows(w.attn_v, a_lo, a_hi, qd + kvd, kvd, eb);
+        l2_prefetch_rows(w.attn_out, c_lo, c_hi, 0, E, qb);
+        for (int r = cta; r < ne; r += G) l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(w.router + (size_t)r * E), (size_t)E * 4);
+    };
+    prefetch_attn_side(p.layers[0]);
+
     for (int il = 0; il <= p.n_layer; il++) {
         const bool tail = il == p.n_layer;  // after the last layer: combine + output norm only
         const MegaLayer ly = p.layers[tail ? p.n_layer - 1 : il];
         // ================= phase A: (combine) + norm + Q8_K | Q, K, V rows =================
-        const int rows_a = qd + 2 * kvd, rpc_a = (rows_a + G - 1) / G;
-        const int a_lo = min(cta * rpc_a, rows_a), a_hi = min(a_lo + rpc_a, rows_a);
         auto map_a = [&](int row) -> RowRef {
             if (row < qd) return RowRef{ly.attn_q, (size_t)row * eb, 0, p.q + row};
             if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
             return RowRef{ly.attn_v, (size_t)(row - qd - kvd) * eb, 0, p.v + (row - qd - kvd)};
         };
+        if (!tail && n_kv > 1) {
+            // this layer's cached K and V rows (evicted since the last token): every CTA asks for a slice of each
+            const size_t kv_bytes = (size_t)(n_kv - 1) * kvd * 4;
+            const size_t per = ((kv_bytes + G - 1) / G + 15) & ~(size_t)15, off = per * cta;
+            if (off < kv_bytes) {
+                const size_t n = kv_bytes - off < per ? kv_bytes - off : per;
+                l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(ly.kc) + off, n);
+                l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(ly.vc) + off, n);
+            }
+        }
         if (il > 0) {
             // x += sum_e w_e * down_e, e in routing order, the expert sum started from 0 (layer.rs:243-258, 281-287).
             // All of a sweep's loads are issued before the first is used.
@@ -414,7 +471,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             if (cta == 0 && p.trace_x)
                 for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = s_x[i];
         }
-        if (!tail) mv_issue(u, have, map_a, eb, a_lo, a_hi);  // in flight while the norm's chain is walked
         norm_quant(s_x, tail ? p.output_norm : ly.attn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
         if (tail) {
             if (cta == 0) {
@@ -426,29 +482,54 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             }
             break;
         }
+        MEGA_STAMP(0);
+        mv_issue(u, have, map_a, eb, a_lo, a_hi);  // (from L2: asked for a phase ago)
         build_act_image(s_nat, s_act, eb);
         __syncthreads();
-        MEGA_STAMP(0);
         mv_finish(u, have, map_a, eb, a_lo, a_hi, s_act, s_adv, s_ex);
         MEGA_STAMP(1);
         if (!grid_barrier(p, bar_target, &s_flag)) return;
         MEGA_STAMP(2);
 
-        // ================= phase B: attention, item (head, column part) =================
-        if (cta < H * kMegaSplit) {
-            const int h = cta / kMegaSplit, c = cta - h * kMegaSplit;
-            const int ratio = H / HKV, kvh = h / ratio, half = hd / 2, cols = hd / kMegaSplit;
-            // the current token's q head, k head, v head
-            for (int i = tid; i < hd; i += kMegaThreads) {
-                s_q[i] = __ldcg(p.q + (size_t)h * hd + i);
-                s_k[i] = __ldcg(p.k + (size_t)kvh * hd + i);
-                s_v[i] = __ldcg(p.v + (size_t)kvh * hd + i);
+        // ================= phase B1: QK-norm, RoPE, KV store, scores of (kv head, chunk of positions) =================
+        if (b1_kvh < HKV && t_hi > t_lo) {
+            float *s_qraw = s_tile, *s_qr = s_tile + ratio * hd, *s_kt = s_tile + 2 * ratio * hd;  // [ratio][hd] x2, [ppc][hd + 4]
+            const int stride = hd + 4, hd4 = hd / 4, cnt = t_hi - t_lo;
+            const float *kb = ly.kc + (size_t)b1_kvh * hd;
+            // the chunk's cached K rows start their trip first (the row of this very position is made below)
+            constexpr int kLd = 4;
+            for (int i0 = 0; i0 < cnt * hd4; i0 += kLd * kMegaThreads) {
+                float4 reg[kLd];
+#pragma unroll
+                for (int j = 0; j < kLd; j++) {
+                    const int idx = i0 + tid + j * kMegaThreads;
+                    const int r = idx / hd4, cc = idx - r * hd4;
+                    reg[j] = (idx < cnt * hd4 && t_lo + r != pos) ? __ldg(reinterpret_cast<const float4 *>(kb + (size_t)(t_lo + r) * kvd) + cc)
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                // the group's q heads and this token's k, v head, raw
+                if (i0 == 0) {
+                    for (int i = tid; i < ratio * hd; i += kMegaThreads) s_qraw[i] = __ldcg(p.q + (size_t)b1_kvh * ratio * hd + i);
+                    for (int i = tid; i < hd; i += kMegaThreads) {
+                        s_k[i] = __ldcg(p.k + (size_t)b1_kvh * hd + i);
+                        s_v[i] = __ldcg(p.v + (size_t)b1_kvh * hd + i);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < kLd; j++) {
+                    const int idx = i0 + tid + j * kMegaThreads;
+                    if (idx < cnt * hd4) {
+                        const int r = idx / hd4, cc = idx - r * hd4;
+                        *reinterpret_cast<float4 *>(s_kt + r * stride + 4 * cc) = reg[j];
+                    }
+                }
             }
             __syncthreads();
-            // per-head norm (layer.rs:62-79): the sum of squares walked in order, by one thread per vector
-            if (tid == 0 || tid == 32) {
-                const float *sx = tid == 0 ? s_q : s_k;
-                const float *w = tid == 0 ? ly.q_norm : ly.k_norm;
+            // per-head norm (layer.rs:62-79): each sum of squares walked in order by its own thread
+            if ((tid & 31) == 0 && (tid >> 5) <= ratio) {
+                const int j = tid >> 5;  // 0..ratio-1: q heads, ratio: the k head
+                const float *sx = j < ratio ? s_qraw + j * hd : s_k;
+                const float *w = j < ratio ? ly.q_norm : ly.k_norm;
                 float scale = 1.0f;
                 if (w) {
                     float sum = 0.0f;
@@ -456,15 +537,16 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                     for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
                     scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), p.eps)));
                 }
-                s_scalar[tid == 0 ? 1 : 2] = scale;
+                s_scalar[8 + j] = scale;
             }
             __syncthreads();
-            if (tid < 2 * half) {  // NeoX RoPE on (i, i + half) pairs, angles from the host-built table
-                const bool is_k = tid >= half;
-                const int i = is_k ? tid - half : tid;
-                float *sx = is_k ? s_k : s_q;
+            // NeoX RoPE on (i, i + half) pairs, angles from the host-built table
+            for (int idx = tid; idx < (ratio + 1) * half; idx += kMegaThreads) {
+                const int j = idx / half, i = idx - j * half;
+                const bool is_k = j == ratio;
+                const float *sx = is_k ? s_k : s_qraw + j * hd;
                 const float *w = is_k ? ly.k_norm : ly.q_norm;
-                const float scale = s_scalar[is_k ? 2 : 1];
+                const float scale = s_scalar[8 + j];
                 float a = sx[i], b = sx[i + half];
                 if (w) {
                     a = __fmul_rn(__fmul_rn(a, scale), __ldg(w + i));
@@ -473,121 +555,104 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                 const float2 sc = *reinterpret_cast<const float2 *>(p.rope_tab + ((size_t)pos * half + i) * 2);
                 const float o0 = __fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x));
                 const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
-                float *dst = is_k ? s_tmp : s_tile;  // (roped q parks at the start of the tile buffer for a moment)
+                float *dst = is_k ? s_tmp : s_qr + j * hd;
                 dst[i] = o0;
                 dst[i + half] = o1;
             }
             __syncthreads();
-            for (int i = tid; i < hd; i += kMegaThreads) {
-                s_q[i] = s_tile[i];
-                s_k[i] = s_tmp[i];
-            }
-            __syncthreads();
-            if (c == 0 && h % ratio == 0) {  // one item per kv head stores this position's K and V
+            if (b1_has_pos) {  // this position's K (roped) and V go into the cache and into the chunk
                 for (int i = tid; i < hd; i += kMegaThreads) {
-                    ly.kc[(size_t)pos * kvd + (size_t)kvh * hd + i] = s_k[i];
-                    ly.vc[(size_t)pos * kvd + (size_t)kvh * hd + i] = s_v[i];
+                    ly.kc[(size_t)pos * kvd + (size_t)b1_kvh * hd + i] = s_tmp[i];
+                    ly.vc[(size_t)pos * kvd + (size_t)b1_kvh * hd + i] = s_v[i];
+                    s_kt[(pos - t_lo) * stride + i] = s_tmp[i];
                 }
+                __syncthreads();
             }
             MEGA_STAMP(3);
-            // scores: logit[t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106). Tiles of kMegaKTile
-            // positions go through shared memory (rows padded to hd + 4 words: 16-byte aligned and conflict-free for the
-            // 16-byte reads below); a thread's loads of a tile are all issued before the first is stored.
+            // logit[h][t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106): one thread per (head, position)
             const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-            const float *kb = ly.kc + (size_t)kvh * hd;
-            const int stride = hd + 4, hd4 = hd / 4;
-            constexpr int kLd = 8;  // 16-byte loads in flight per thread (kMegaKTile * 32 / kMegaThreads at head_dim 128)
-            float lmax = -INFINITY;
-            for (int t0 = 0; t0 < n_kv; t0 += kMegaKTile) {
-                const int cnt = min(kMegaKTile, n_kv - t0);
-                __syncthreads();
-                for (int i0 = 0; i0 < cnt * hd4; i0 += kLd * kMegaThreads) {
-                    float4 reg[kLd];
+            for (int idx = tid; idx < ratio * cnt; idx += kMegaThreads) {
+                const int j = idx / cnt, r = idx - j * cnt;
+                const float4 *kr = reinterpret_cast<const float4 *>(s_kt + r * stride);
+                const float4 *q4 = reinterpret_cast<const float4 *>(s_qr + j * hd);
+                float dot = 0.0f;
+                float pa[16];  // four 16-byte reads ahead of the adds: the chain is then the dependent adds alone
 #pragma unroll
-                    for (int j = 0; j < kLd; j++) {
-                        const int idx = i0 + tid + j * kMegaThreads;
-                        const int r = idx / hd4, cc = idx - r * hd4;
-                        const int t = t0 + r;
-                        // the row of this very position is not in the cache yet for the other items: take it from s_k
-                        reg[j] = idx >= cnt * hd4 ? make_float4(0.f, 0.f, 0.f, 0.f)
-                                 : t == pos       ? *reinterpret_cast<const float4 *>(s_k + 4 * cc)
-                                                  : __ldg(reinterpret_cast<const float4 *>(kb + (size_t)t * kvd) + cc);
-                    }
-#pragma unroll
-                    for (int j = 0; j < kLd; j++) {
-                        const int idx = i0 + tid + j * kMegaThreads;
-                        if (idx < cnt * hd4) {
-                            const int r = idx / hd4, cc = idx - r * hd4;
-                            *reinterpret_cast<float4 *>(s_tile + r * stride + 4 * cc) = reg[j];
-                        }
-                    }
+                for (int jj = 0; jj < 4; jj++) {
+                    const float4 kv = kr[jj], qv = q4[jj];
+                    pa[4 * jj] = __fmul_rn(qv.x, kv.x), pa[4 * jj + 1] = __fmul_rn(qv.y, kv.y), pa[4 * jj + 2] = __fmul_rn(qv.z, kv.z), pa[4 * jj + 3] = __fmul_rn(qv.w, kv.w);
                 }
-                __syncthreads();
-                if (tid < cnt) {
-                    const float4 *kr = reinterpret_cast<const float4 *>(s_tile + tid * stride);
-                    const float4 *q4 = reinterpret_cast<const float4 *>(s_q);
-                    float dot = 0.0f;
-                    // four 16-byte reads ahead of the adds: the chain is then the dependent adds alone
-                    float pa[16];
+                for (int d4 = 0; d4 < hd4; d4 += 4) {
+                    float pb[16];
+                    const int n4 = d4 + 4 < hd4 ? d4 + 4 : d4;
 #pragma unroll
-                    for (int j = 0; j < 4 && j < hd4; j++) {
-                        const float4 kv = kr[j], qv = q4[j];
-                        pa[4 * j] = __fmul_rn(qv.x, kv.x), pa[4 * j + 1] = __fmul_rn(qv.y, kv.y), pa[4 * j + 2] = __fmul_rn(qv.z, kv.z), pa[4 * j + 3] = __fmul_rn(qv.w, kv.w);
+                    for (int jj = 0; jj < 4; jj++) {
+                        const float4 kv = kr[n4 + jj], qv = q4[n4 + jj];
+                        pb[4 * jj] = __fmul_rn(qv.x, kv.x), pb[4 * jj + 1] = __fmul_rn(qv.y, kv.y), pb[4 * jj + 2] = __fmul_rn(qv.z, kv.z), pb[4 * jj + 3] = __fmul_rn(qv.w, kv.w);
                     }
-                    for (int d4 = 0; d4 < hd4; d4 += 4) {
-                        float pb[16];
-                        const int n4 = d4 + 4 < hd4 ? d4 + 4 : d4;
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const float4 kv = kr[n4 + j], qv = q4[n4 + j];
-                            pb[4 * j] = __fmul_rn(qv.x, kv.x), pb[4 * j + 1] = __fmul_rn(qv.y, kv.y), pb[4 * j + 2] = __fmul_rn(qv.z, kv.z), pb[4 * j + 3] = __fmul_rn(qv.w, kv.w);
-                        }
+                    for (int jj = 0; jj < 16; jj++) dot = __fadd_rn(dot, pa[jj]);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) dot = __fadd_rn(dot, pa[j]);
-#pragma unroll
-                        for (int j = 0; j < 16; j++) pa[j] = pb[j];
-                    }
-                    const float l = __fmul_rn(dot, scale);
-                    s_sl[t0 + tid] = l;
-                    lmax = fmaxf(lmax, l);
+                    for (int jj = 0; jj < 16; jj++) pa[jj] = pb[jj];
                 }
+                p.scores[(size_t)(b1_kvh * ratio + j) * p.max_kv + t_lo + r] = __fmul_rn(dot, scale);
             }
             MEGA_STAMP(4);
-            // max (order-free), e[t] = exp(l - max), the sum walked in order (attention.rs:107-115)
-            for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
-            if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
-            __syncthreads();
-            lmax = s_red[0];
-            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, s_red[w]);
-            __syncthreads();
-            for (int t = tid; t < n_kv; t += kMegaThreads) s_sl[t] = ref_expf(__fsub_rn(s_sl[t], lmax));
-            __syncthreads();
-            // the V rows of this item's columns start their trip while the sum is walked
+        }
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(5);
+
+        // ================= phase B2: softmax and weighted values of (head, column part) =================
+        if (cta < H * kMegaSplit) {
+            const int h = cta / kMegaSplit, c = cta - h * kMegaSplit, kvh = h / ratio;
+            constexpr int kLd = 8;
+            // the V rows of this item's columns start their trip first
             const float *vb = ly.vc + (size_t)kvh * hd + (size_t)c * cols;
             const int cols4 = cols / 4;
-            float acc = 0.0f;
-            for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
-                const int cnt = min(kMegaThreads, n_kv - t0);
-                float4 reg[kLd];
+            float4 reg[kLd];
+            auto fetch_v = [&](int t0, int cnt) {
 #pragma unroll
                 for (int j = 0; j < kLd; j++) {
                     const int idx = tid + j * kMegaThreads;
                     const int r = idx / cols4, cc = idx - r * cols4;
                     const int t = t0 + r;
+                    // (this position's row was stored by another CTA before the barrier: read it from L2)
                     reg[j] = idx >= cnt * cols4 ? make_float4(0.f, 0.f, 0.f, 0.f)
-                             : t == pos         ? *reinterpret_cast<const float4 *>(s_v + c * cols + 4 * cc)
+                             : t == pos         ? __ldcg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc)
                                                 : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
                 }
-                if (t0 == 0 && tid == 0) s_scalar[3] = __fdiv_rn(1.0f, chain_sum(s_sl, n_kv, 0.0f));
-                __syncthreads();  // (the K tile, or the previous V tile, is dead; the scalar is published)
+            };
+            fetch_v(0, min(kMegaThreads, n_kv));
+            // max (order-free), e[t] = exp(l - max), the sum walked in order (attention.rs:107-115)
+            float lmax = -INFINITY;
+            for (int t = tid; t < n_kv; t += kMegaThreads) {
+                const float l = __ldcg(p.scores + (size_t)h * p.max_kv + t);
+                s_sl[t] = l;
+                lmax = fmaxf(lmax, l);
+            }
+            for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
+            if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
+            __syncthreads();
+            lmax = s_red[0];
+            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, s_red[w]);
+            for (int t = tid; t < n_kv; t += kMegaThreads) s_sl[t] = ref_expf(__fsub_rn(s_sl[t], lmax));
+            __syncthreads();
+            float acc = 0.0f;
+            for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
+                const int cnt = min(kMegaThreads, n_kv - t0);
+                if (t0 > 0) {
+                    __syncthreads();  // the previous V tile is dead
+                    fetch_v(t0, cnt);
+                }
 #pragma unroll
                 for (int j = 0; j < kLd; j++) {
                     const int idx = tid + j * kMegaThreads;
                     if (idx < cnt * cols4) reinterpret_cast<float4 *>(s_tile)[idx] = reg[j];
                 }
+                if (t0 == 0 && tid == 0) s_scalar[3] = __fdiv_rn(1.0f, chain_sum(s_sl, n_kv, 0.0f));
                 __syncthreads();
-                if (t0 == 0) MEGA_STAMP(5);
-                // weighted values of this item's columns: out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
+                if (t0 == 0) MEGA_STAMP(6);
+                // out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
                 if (tid < cols) {
                     const float inv = s_scalar[3];
                     int r = 0;
@@ -607,17 +672,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                     }
                     for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s_sl[t0 + r], inv), s_tile[r * cols + tid]));
                 }
-                __syncthreads();
             }
             if (tid < cols) p.attn[(size_t)h * hd + (size_t)c * cols + tid] = acc;
-            MEGA_STAMP(6);
+            MEGA_STAMP(7);
         }
         if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(7);
+        MEGA_STAMP(8);
 
         // ================= phase C: Q8_K of the attention output | attn_out rows =================
-        const int rpc_c = (E + G - 1) / G;
-        const int c_lo = min(cta * rpc_c, E), c_hi = min(c_lo + rpc_c, E);
         auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
         mv_issue(u, have, map_c, qb, c_lo, c_hi);
         {
@@ -632,24 +694,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             __syncthreads();
             mv_finish(u, have, map_c, qb, c_lo, c_hi, s_act, s_adv, s_ex);
         }
-        // the router row this CTA will dot, read before the barrier and the norm: its latency hides behind them
-        float wr_pre[kMegaElems];
-#pragma unroll
-        for (int q = 0; q < kMegaElems; q++) {
-            const int i = tid + q * kMegaThreads;
-            wr_pre[q] = (cta < ne && i < E) ? __ldg(ly.router + (size_t)cta * E + i) : 0.0f;
-        }
-        MEGA_STAMP(8);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
         MEGA_STAMP(9);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(10);
 
         // ================= phase D: x += attn_out, FFN norm, Q8_K | router logits =================
         {
-            float rv[kMegaElems];
+            // the router row this CTA dots (asked of L2 a layer ago) and attn_out's result, read before the norm's chain
+            float wr_pre[kMegaElems], rv[kMegaElems];
 #pragma unroll
             for (int q = 0; q < kMegaElems; q++) {
                 const int i = tid + q * kMegaThreads;
                 rv[q] = i < E ? __ldcg(p.xb2 + i) : 0.0f;
+                wr_pre[q] = (cta < ne && i < E) ? __ldg(ly.router + (size_t)cta * E + i) : 0.0f;
             }
 #pragma unroll
             for (int q = 0; q < kMegaElems; q++) {
@@ -657,31 +714,31 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                 if (i < E) s_x[i] = __fadd_rn(s_x[i], rv[q]);
             }
             for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_x[i] = __fadd_rn(s_x[i], __ldcg(p.xb2 + i));
-        }
-        __syncthreads();
-        norm_quant(s_x, ly.ffn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
-        build_act_image(s_nat, s_act, eb);  // kept for phase E
-        MEGA_STAMP(10);
-        for (int r = cta; r < ne; r += G) {
-            // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
-            const float *wr = ly.router + (size_t)r * E;
             __syncthreads();
-            if (r == cta) {
+            norm_quant(s_x, ly.ffn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
+            build_act_image(s_nat, s_act, eb);  // kept for phase E
+            MEGA_STAMP(11);
+            for (int r = cta; r < ne; r += G) {
+                // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
+                const float *wr = ly.router + (size_t)r * E;
+                __syncthreads();
+                if (r == cta) {
 #pragma unroll
-                for (int q = 0; q < kMegaElems; q++) {
-                    const int i = tid + q * kMegaThreads;
-                    if (i < E) s_sq[i] = __fmul_rn(wr_pre[q], s_xn[i]);
+                    for (int q = 0; q < kMegaElems; q++) {
+                        const int i = tid + q * kMegaThreads;
+                        if (i < E) s_sq[i] = __fmul_rn(wr_pre[q], s_xn[i]);
+                    }
+                    for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
+                } else {
+                    for (int i = tid; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
                 }
-                for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
-            } else {
-                for (int i = tid; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
+                __syncthreads();
+                if (tid == 0) p.logits[r] = chain_sum(s_sq, E, -0.0f);
             }
-            __syncthreads();
-            if (tid == 0) p.logits[r] = chain_sum(s_sq, E, -0.0f);
         }
-        MEGA_STAMP(11);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
         MEGA_STAMP(12);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(13);
 
         // ================= phase E: route | gate and up rows of the routed experts =================
         for (int i = tid; i < ne; i += kMegaThreads) s_sq[i] = __ldcg(p.logits + i);
@@ -693,38 +750,40 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             p.expert_w[tid] = s_w[tid];
             if (p.trace_ids) p.trace_ids[(size_t)il * nu + tid] = s_ids[tid];
         }
-        const int rows_e = nu * 2 * ffe, rpc_e = (rows_e + G - 1) / G;
-        const int e_lo = min(cta * rpc_e, rows_e), e_hi = min(e_lo + rpc_e, rows_e);
+        auto expert_of = [&](int slot) {
+            const int ex = s_ids[slot];
+            return (ex < 0 || ex >= ne) ? 0 : ex;
+        };
         auto map_e = [&](int row) -> RowRef {
             const int slot = row / (2 * ffe), rem = row - slot * 2 * ffe, mat = rem / ffe, r = rem - mat * ffe;
-            int ex = s_ids[slot];
-            if (ex < 0 || ex >= ne) ex = 0;
-            return RowRef{mat ? ly.up : ly.gate, ((size_t)ex * ffe + r) * eb, 0, (mat ? p.e_up : p.e_gate) + (size_t)slot * ffe + r};
+            return RowRef{mat ? ly.up : ly.gate, ((size_t)expert_of(slot) * ffe + r) * eb, 0, (mat ? p.e_up : p.e_gate) + (size_t)slot * ffe + r};
         };
-        mv_issue(u, have, map_e, eb, e_lo, e_hi);
-        MEGA_STAMP(13);
-        mv_finish(u, have, map_e, eb, e_lo, e_hi, s_act, s_adv, s_ex);  // the activation image is phase D's
-        // the down projection's weights are known now (the ids are): request them before the barrier
-        const int rows_f = nu * E, rpc_f = (rows_f + G - 1) / G;
-        const int f_lo = min(cta * rpc_f, rows_f), f_hi = min(f_lo + rpc_f, rows_f);
-        const int slot_lo = f_lo / E, slot_hi = f_hi > f_lo ? (f_hi - 1) / E : slot_lo;
         auto map_f = [&](int row) -> RowRef {
             const int slot = row / E, r = row - slot * E;
-            int ex = s_ids[slot];
-            if (ex < 0 || ex >= ne) ex = 0;
-            return RowRef{ly.down, ((size_t)ex * E + r) * fb, slot - slot_lo, p.e_down + (size_t)slot * E + r};
+            return RowRef{ly.down, ((size_t)expert_of(slot) * E + r) * fb, slot - slot_lo, p.e_down + (size_t)slot * E + r};
         };
-        mv_issue(u, have, map_f, fb, f_lo, f_hi);
+        mv_issue(u, have, map_e, eb, e_lo, e_hi);
+        // the down projection's rows are known too (the ids are): ask L2 for them now, they are needed a phase later;
+        // then the next layer's attention side
+        for (int seg = f_lo; seg < f_hi;) {
+            const int slot = seg / E, seg_hi = min(f_hi, (slot + 1) * E);
+            l2_prefetch_units(ly.down, ((size_t)expert_of(slot) * E + (seg - slot * E)) * fb, ((size_t)expert_of(slot) * E + (seg_hi - slot * E)) * fb);
+            seg = seg_hi;
+        }
         MEGA_STAMP(14);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        mv_finish(u, have, map_e, eb, e_lo, e_hi, s_act, s_adv, s_ex);  // the activation image is phase D's
+        if (il + 1 < p.n_layer) prefetch_attn_side(p.layers[il + 1]);
         MEGA_STAMP(15);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(16);
 
         // ================= phase F: silu(gate) * up, Q8_K, for the slots of this CTA's rows | down rows =================
+        mv_issue(u, have, map_f, fb, f_lo, f_hi);
         if (f_hi > f_lo) {
             const int warp = tid >> 5, lane = tid & 31, nslot = slot_hi - slot_lo + 1;
             for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
-                const int s = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
-                const size_t base = (size_t)s * ffe + (size_t)b * 256 + lane * 8;
+                const int sl_ = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
+                const size_t base = (size_t)sl_ * ffe + (size_t)b * 256 + lane * 8;
                 const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base) + 1);
                 const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base) + 1);
                 const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
@@ -735,11 +794,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
             build_act_image(s_nat, s_act, nslot * fb);
             __syncthreads();
         }
-        MEGA_STAMP(16);
-        mv_finish(u, have, map_f, fb, f_lo, f_hi, s_act, s_adv, s_ex);
         MEGA_STAMP(17);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        mv_finish(u, have, map_f, fb, f_lo, f_hi, s_act, s_adv, s_ex);
         MEGA_STAMP(18);
+        if (!grid_barrier(p, bar_target, &s_flag)) return;
+        MEGA_STAMP(19);
     }
 #undef MEGA_STAMP
 }
@@ -751,7 +810,7 @@ using namespace llamd;
 namespace llamd {
 
 // Shared memory the kernel needs for these dimensions, or 0 when they do not fit it.
-size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats) {
+size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats, int *ktile_rows_out) {
     const int E = hp.n_embd, qd = hp.n_head * hp.head_dim, ffe = hp.n_ff_expert;
     int ab = E / 256;
     if (qd / 256 > ab) ab = qd / 256;
@@ -759,7 +818,13 @@ size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int
     const int sl = (max_kv + 3) & ~3;
     if (act_blocks) *act_blocks = ab;
     if (sl_floats) *sl_floats = sl;
-    return mega_smem(E, qd, hp.head_dim, ab, sl, hp.n_expert).total;
+    int dev = 0, sms = 1;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int ncp = sms / hp.n_head_kv > 0 ? sms / hp.n_head_kv : 1;
+    const int ktile_rows = (max_kv + ncp - 1) / ncp;
+    if (ktile_rows_out) *ktile_rows_out = ktile_rows;
+    return mega_smem(E, qd, hp.head_dim, ab, sl, hp.n_expert, ktile_rows, hp.n_head / hp.n_head_kv).total;
 }
 
 // Can this model run in the resident kernel on the current device? (dimension and shared-memory limits)
@@ -774,7 +839,8 @@ bool mega_supported(const llamd_hparams &hp, int max_kv) {
         return false;
     }
     if (hp.n_head * kMegaSplit > sms || hp.n_expert_used > sms) return false;  // one attention item per CTA; a CTA's down rows span <= 2 slots
-    return mega_smem_bytes(hp, max_kv, nullptr, nullptr) <= (size_t)optin;
+    if (hp.n_head_kv > sms) return false;  // one score chunk per CTA and kv head
+    return mega_smem_bytes(hp, max_kv, nullptr, nullptr, nullptr) <= (size_t)optin;
 }
 
 // Queue the resident pass for one token (meta = [token, pos] on the device). `bar` and `status` are one word each;
@@ -783,7 +849,7 @@ void launch_decode_mega(MegaParams p, const llamd_hparams &hp) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const size_t smem = mega_smem_bytes(hp, p.max_kv, &p.act_blocks, &p.sl_floats);
+    const size_t smem = mega_smem_bytes(hp, p.max_kv, &p.act_blocks, &p.sl_floats, &p.ktile_rows);
     static size_t configured = 0;
     if (smem > configured) {
         const cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

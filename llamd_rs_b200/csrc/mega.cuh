@@ -18,6 +18,7 @@ struct MegaParams {
     const uint8_t *tok_embd;
     const float *output_norm, *rope_tab;
     const int32_t *meta;
+    float *scores;  // [n_head][max_kv] scaled attention logits of this token
     float *q, *k, *v, *attn, *xb2, *logits, *e_gate, *e_up, *e_down, *x_out, *expert_w;
     int32_t *expert_ids;
     int8_t *aq_out;
@@ -30,9 +31,10 @@ struct MegaParams {
     unsigned int spin_limit;
     int act_blocks;      // blocks the activation image must hold
     int sl_floats;       // padded max_kv
+    int ktile_rows;      // cached positions one CTA scores: ceil(max_kv / (SMs / n_head_kv))
 };
 
-size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats);
+size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats, int *ktile_rows_out);
 bool mega_supported(const llamd_hparams &hp, int max_kv);
 void launch_decode_mega(MegaParams p, const llamd_hparams &hp);
 

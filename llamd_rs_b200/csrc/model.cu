@@ -135,6 +135,8 @@ struct Model {
         int tile = 0;
         Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, ids, w, logits, counter, gate, up, down, scores, meta;
         Buf gstart, gcount, ptoken, pslot, work, n_work;
+        Buf logits_all, amax_v, amax_i, out_tokens;  // every token's logits and greedy pick (verification, wide batches)
+        int32_t *h_out_tokens = nullptr;             // pinned [tile]
         Buf aq_rm, aq2_rm;  // the GEMMs' view of aq / aq2: residue-major bytes (integer path) or two f16 terms per element (tcgen05 path)
         int32_t *h_meta = nullptr;
         // Expert parallelism over peer memory: every rank's tile (activations, scales, routed ids) gathered here by the
@@ -297,6 +299,7 @@ void queue_token_resident(Model &m) {
     p.rope_tab = m.rope_tab.as<float>();
     p.meta = m.meta.as<int32_t>();
     p.q = m.q.as<float>(); p.k = m.k.as<float>(); p.v = m.v.as<float>(); p.attn = m.attn.as<float>(); p.xb2 = m.xb2.as<float>();
+    p.scores = m.scores.as<float>();
     p.logits = m.router_logits.as<float>(); p.e_gate = m.e_gate.as<float>(); p.e_up = m.e_up.as<float>(); p.e_down = m.e_down.as<float>();
     p.x_out = m.x.as<float>(); p.expert_w = m.expert_w.as<float>(); p.expert_ids = m.expert_ids.as<int32_t>();
     p.aq_out = m.aq.as<int8_t>(); p.ad_out = m.ad.as<float>();
@@ -610,8 +613,8 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
 extern "C" {
 
 llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq) {
-    if (!hp || max_kv <= 0 || max_seq < 1 || max_seq > LLAMD_MAX_SEQ) {
-        set_error_msg("model: max_kv of 0 or max_seq outside 1..8");
+    if (!hp || max_kv <= 0 || max_seq < 1 || max_seq > LLAMD_MAX_BATCH) {
+        set_error_msg("model: max_kv of 0 or max_seq outside 1..256");
         return nullptr;
     }
     if (hp->n_layer <= 0 || hp->n_embd % 256 || (hp->n_head * hp->head_dim) % 256 || hp->n_ff_expert % 256 || hp->head_dim % 4 ||
@@ -710,6 +713,8 @@ void llamd_model_free(llamd_model *h) {
                    &m->pf.ad2_all, &m->pf.aq2_all_rm, &m->pf.push_done, &m->pf.down_tab, &m->pf.aq_tab, &m->pf.ad_tab, &m->pf.ids_tab})
         b->release();
     if (m->pf.h_meta) cudaFreeHost(m->pf.h_meta);
+    for (Buf *b : {&m->pf.logits_all, &m->pf.amax_v, &m->pf.amax_i, &m->pf.out_tokens}) b->release();
+    if (m->pf.h_out_tokens) cudaFreeHost(m->pf.h_out_tokens);
     for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out) cudaFreeHost(m->h_out);
@@ -862,6 +867,8 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     return -1;
 }
 
+static int run_wide_batch(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int32_t *out_tokens);
+
 int llamd_model_forward(llamd_model *h, int32_t token, int32_t pos, int32_t *out_token) {
     Model *m = (Model *)h;
     if (!m || !out_token) return -1;
@@ -873,6 +880,7 @@ int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32
     Model *m = (Model *)h;
     if (!m || !tokens || !positions || !out_tokens) return -1;
     m->err.clear();
+    if (nseq > LLAMD_MAX_SEQ && nseq <= m->max_seq) return run_wide_batch(*m, tokens, positions, nseq, out_tokens);
     return run(*m, tokens, positions, nseq, out_tokens);
 }
 
@@ -899,6 +907,9 @@ static bool prefill_alloc(Model &m, int tile) {
         b->release();
     if (p.h_meta) cudaFreeHost(p.h_meta);
     p.h_meta = nullptr;
+    for (Buf *b : {&p.logits_all, &p.amax_v, &p.amax_i, &p.out_tokens}) b->release();
+    if (p.h_out_tokens) cudaFreeHost(p.h_out_tokens);
+    p.h_out_tokens = nullptr;
     const llamd_hparams &hp = m.hp;
     const size_t T = tile, E = hp.n_embd, qd = (size_t)hp.n_head * hp.head_dim, kvd = (size_t)hp.n_head_kv * hp.head_dim;
     const size_t nu = hp.n_expert_used, ffe = hp.n_ff_expert, ne = hp.n_expert, max_act = E > qd ? E : qd;
@@ -930,6 +941,21 @@ static bool prefill_alloc(Model &m, int tile) {
     return true;
 }
 
+static bool prefill_alloc_all_logits(Model &m, bool own_logits) {
+    Model::Prefill &p = m.pf;
+    const size_t T = p.tile;
+    if (p.out_tokens.p && p.out_tokens.bytes >= T * 4 && (!own_logits || (p.logits_all.p && p.logits_all.bytes >= T * (size_t)m.hp.n_vocab * 4))) return true;
+    for (Buf *b : {&p.amax_v, &p.amax_i, &p.out_tokens}) b->release();
+    if (own_logits) p.logits_all.release();
+    if (p.h_out_tokens) cudaFreeHost(p.h_out_tokens);
+    p.h_out_tokens = nullptr;
+    const bool ok = p.amax_v.alloc(T * kArgmaxBlocks * 4) && p.amax_i.alloc(T * kArgmaxBlocks * 4) && p.out_tokens.alloc(T * 4) &&
+                    (!own_logits || p.logits_all.alloc(T * (size_t)m.hp.n_vocab * 4)) &&
+                    cudaMallocHost((void **)&p.h_out_tokens, T * 4) == cudaSuccess;
+    if (!ok) m.err = std::string("verification buffers: ") + llamd_cuda_last_error_string();
+    return ok;
+}
+
 // The largest tile expert-parallel prefill can take: the scatter plan covers the pairs of ALL ranks' tiles.
 static int ep_tile_cap(const Model &m) {
     int cap = kGroupMaxPairs / (m.ep_world * m.hp.n_expert_used);
@@ -938,7 +964,11 @@ static int ep_tile_cap(const Model &m) {
     return cap < 1 ? 1 : cap;
 }
 
-static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
+// multi_seq: the T tokens belong to T different sequences, token i with its own cache (sequence i) and position:
+// K/V go to the per-sequence caches and attention runs the per-sequence decode kernels. all_logits: the head runs for
+// every token of the tile (logits into `logits_out`, greedy picks into pf.out_tokens), not only for the last one.
+static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool multi_seq = false, bool all_logits = false,
+                               float *logits_out = nullptr) {
     const llamd_hparams &hp = m.hp;
     Model::Prefill &p = m.pf;
     const int E = hp.n_embd, H = hp.n_head, HKV = hp.n_head_kv, hd = hp.head_dim;
@@ -968,10 +998,18 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
             llamd_fwd_matvec_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq.as<int8_t>(), p.ad.as<float>(), p.q.as<float>(),
                                     p.k.as<float>(), p.v.as<float>(), eb, qd, kvd, kvd, T);
         }
+        if (multi_seq) {
+            llamd_fwd_qk_norm_rope_store(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
+                                         l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
+                                         l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
+            llamd_fwd_attention_meta(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV,
+                                     hd, meta, m.max_kv, T);
+        } else
         llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
                                           l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
                                           l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
-        if (m.prefill_attn)
+        if (multi_seq) {
+        } else if (m.prefill_attn)
             llamd_fwd_attention_prefill(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H,
                                         HKV, hd, meta, (m.max_kv + 3) & ~3, T, n_kv_max);  // score rows padded to 16 bytes
         else
@@ -1055,6 +1093,16 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last) {
                                    ne);
         }
     }
+    if (all_logits) {
+        // the head for every token of the tile: combine + output norm + Q8_K per row, lm_head as a GEMM, greedy pick per row
+        llamd_fwd_combine_rms_norm_quant(x, p.down.as<float>(), p.w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
+                                         p.aq.as<int8_t>(), p.ad.as<float>(), E, hp.rms_eps, T);
+        llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * eb);
+        llamd_fwd_gemm_tokens(m.output.p ? m.output.p : m.tok_embd.p, nullptr, nullptr, p.aq_rm.p, p.ad.as<float>(), logits_out, nullptr,
+                              nullptr, eb, hp.n_vocab, 0, 0, T);
+        llamd_fwd_argmax(logits_out, hp.n_vocab, p.amax_v.as<float>(), p.amax_i.as<int32_t>(), p.out_tokens.as<int32_t>(), kArgmaxBlocks, T);
+        return;
+    }
     if (!last) return;
     // logits for the tile's last token only (vulkan_model.rs:793-818)
     const size_t r = (size_t)(T - 1);
@@ -1127,6 +1175,103 @@ int llamd_model_prefill(llamd_model *h, const int32_t *tokens, int n_tokens, int
         return -1;
     }
     *out_token = m->h_out[0];
+    return 0;
+}
+
+// Verification of drafted tokens (speculative decoding, "verified only": the target model always decides). The n
+// tokens are consumed at positions base_pos.. exactly as llamd_model_prefill consumes them -- the same tiles, the same
+// arithmetic as token-by-token decode -- but the head runs for EVERY token: out_tokens[i] is the greedy token after
+// tokens[0..=i]. A caller that drafted tokens[1..] keeps the longest prefix with tokens[i + 1] == out_tokens[i] and
+// continues from there: K/V rows written beyond the accepted position are simply overwritten later. Because the
+// tiled pass equals sequential decode bit for bit, output with drafting equals output without it.
+int llamd_model_verify(llamd_model *h, const int32_t *tokens, int n_tokens, int base_pos, int32_t *out_tokens) {
+    Model *m = (Model *)h;
+    if (!m || !tokens || n_tokens <= 0 || !out_tokens) return -1;
+    m->err.clear();
+    if (m->ep_world > 1) {
+        m->err = "verify: not available with sharded experts";
+        return -1;
+    }
+    if (base_pos < 0 || base_pos + n_tokens > m->max_kv) {
+        m->err = "verify: positions beyond the " + std::to_string(m->max_kv) + " allocated";
+        return -1;
+    }
+    for (int i = 0; i < n_tokens; i++)
+        if (tokens[i] < 0 || tokens[i] >= m->hp.n_vocab) {
+            m->err = "verify: token id outside the vocabulary";
+            return -1;
+        }
+    if (!check_ready(*m)) return -1;
+    int tile = m->prefill_tile < 1 ? 1 : m->prefill_tile;
+    if (tile > 64) tile = 64;  // every token's logits are kept: 0.6 MB each
+    if (tile > n_tokens) tile = n_tokens;
+    if (!prefill_alloc(*m, tile) || !prefill_alloc_all_logits(*m, true)) return -1;
+    for (int t0 = 0; t0 < n_tokens; t0 += tile) {
+        const int T = n_tokens - t0 < tile ? n_tokens - t0 : tile;
+        if (llamd_fwd_sync() != 0) return -1;  // the pinned staging is reused per tile
+        for (int i = 0; i < T; i++) {
+            m->pf.h_meta[2 * i] = tokens[t0 + i];
+            m->pf.h_meta[2 * i + 1] = base_pos + t0 + i;
+        }
+        if (cudaMemcpyAsync(m->pf.meta.p, m->pf.h_meta, (size_t)T * 8, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
+            set_error(cudaGetLastError(), "verify meta H2D");
+            return -1;
+        }
+        queue_prefill_tile(*m, T, base_pos + t0 + T, true, false, true, m->pf.logits_all.as<float>());
+        if (cudaMemcpyAsync(m->pf.h_out_tokens, m->pf.out_tokens.p, (size_t)T * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
+        if (llamd_fwd_sync() != 0) return -1;
+        for (int i = 0; i < T; i++) {
+            if (m->pf.h_out_tokens[i] < 0 || m->pf.h_out_tokens[i] >= m->hp.n_vocab) {
+                m->err = "argmax returned " + std::to_string(m->pf.h_out_tokens[i]);
+                return -1;
+            }
+            out_tokens[t0 + i] = m->pf.h_out_tokens[i];
+        }
+    }
+    return 0;
+}
+
+// forward_batch beyond LLAMD_MAX_SEQ sequences: the pass of a prefill tile whose tokens belong to nseq different
+// sequences (own cache, own position), so that the matmuls run on the integer GEMM with every weight read once for all
+// sequences. Per sequence the arithmetic is the single-sequence pass's.
+static int run_wide_batch(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int32_t *out_tokens) {
+    if (m.ep_world > 1) {
+        m.err = "forward_batch: wide batches are not available with sharded experts";
+        return -1;
+    }
+    for (int s = 0; s < nseq; s++) {
+        if (positions[s] < 0 || positions[s] >= m.max_kv || tokens[s] < 0 || tokens[s] >= m.hp.n_vocab) {
+            m.err = "forward_batch: a position beyond the allocated cache or a token outside the vocabulary";
+            return -1;
+        }
+    }
+    if (!check_ready(m)) return -1;
+    if (m.hp.n_expert_used * nseq > kGroupMaxPairs) {
+        m.err = "forward_batch: too many (sequence, expert) pairs for one scatter plan";
+        return -1;
+    }
+    if (!prefill_alloc(m, nseq) || !prefill_alloc_all_logits(m, false)) return -1;
+    if (llamd_fwd_sync() != 0) return -1;
+    int n_kv_max = 0;
+    for (int s = 0; s < nseq; s++) {
+        m.pf.h_meta[2 * s] = tokens[s];
+        m.pf.h_meta[2 * s + 1] = positions[s];
+        if (positions[s] + 1 > n_kv_max) n_kv_max = positions[s] + 1;
+    }
+    if (cudaMemcpyAsync(m.pf.meta.p, m.pf.h_meta, (size_t)nseq * 8, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
+        set_error(cudaGetLastError(), "batch meta H2D");
+        return -1;
+    }
+    queue_prefill_tile(m, nseq, n_kv_max, true, true, true, m.logits.as<float>());
+    if (cudaMemcpyAsync(m.pf.h_out_tokens, m.pf.out_tokens.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
+    if (llamd_fwd_sync() != 0) return -1;
+    for (int s = 0; s < nseq; s++) {
+        if (m.pf.h_out_tokens[s] < 0 || m.pf.h_out_tokens[s] >= m.hp.n_vocab) {
+            m.err = "argmax returned " + std::to_string(m.pf.h_out_tokens[s]);
+            return -1;
+        }
+        out_tokens[s] = m.pf.h_out_tokens[s];
+    }
     return 0;
 }
 
@@ -1346,8 +1491,8 @@ int llamd_model_ep_p2p_attach_ptrs(llamd_model *h, void *const *ptrs, int world)
     return 0;
 }
 // Nanoseconds per phase of the resident decode kernel, accumulated by its CTA 0 since "resident_profile" was set:
-// 19 slots in the kernel's order (A prologue, A rows, barrier, B prepare, B scores, B softmax, B values, barrier, C,
-// barrier, D norm, D router, barrier, E route, E rows, barrier, F activation, F rows, barrier); out32 gets 32 values.
+// 20 slots in the kernel's order (A prologue, A rows, barrier, B1 prepare, B1 scores, barrier, B2 softmax, B2 values,
+// barrier, C, barrier, D norm, D router, barrier, E route, E rows, barrier, F activation, F rows, barrier); out32 gets 32 values.
 int llamd_model_resident_profile(llamd_model *h, unsigned long long *out32) {
     Model *m = (Model *)h;
     if (!m || !out32 || !m->mega_prof.p) return -1;

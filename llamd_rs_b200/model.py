@@ -85,6 +85,8 @@ def _bind():
     L.llamd_model_ep_status.argtypes = [vp]
     L.llamd_model_ep_p2p_buffers.restype = i32
     L.llamd_model_ep_p2p_buffers.argtypes = [vp, vp]
+    L.llamd_model_verify.restype = i32
+    L.llamd_model_verify.argtypes = [vp, vp, i32, i32, vp]
     L.llamd_model_resident_profile.restype = i32
     L.llamd_model_resident_profile.argtypes = [vp, vp]
     L.llamd_model_ep_tile_cap.restype = i32
@@ -132,8 +134,8 @@ class CudaModel:
     def __init__(self, hp: dict, max_kv: int, max_seq: int = 1):
         if max_kv == 0:
             raise backend.Malformed("device model: max_kv of 0")
-        if max_seq == 0 or max_seq > backend.MAX_SEQ:
-            raise backend.Malformed(f"device model: max_seq {max_seq} outside 1..={backend.MAX_SEQ}")
+        if max_seq == 0 or max_seq > backend.MAX_BATCH:
+            raise backend.Malformed(f"device model: max_seq {max_seq} outside 1..={backend.MAX_BATCH}")
         if not backend.available():
             raise backend.Unsupported("cuda: no device present (there is no CPU fallback)")
         self._L = _bind()
@@ -302,9 +304,9 @@ class CudaModel:
         if self._L.llamd_model_ep_p2p_attach_ptrs(self._h, flat, world) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
 
-    RESIDENT_PHASES = ("A combine+norm+quant", "A qkv rows", "barrier", "B qk-norm rope", "B scores", "B softmax", "B values", "barrier",
-                       "C quant + attn_out rows", "barrier", "D add+norm+quant", "D router", "barrier", "E route", "E gate/up rows",
-                       "barrier", "F silu+quant", "F down rows", "barrier")
+    RESIDENT_PHASES = ("A combine+norm+quant", "A qkv rows", "barrier", "B1 qk-norm rope kv-store", "B1 scores", "barrier",
+                       "B2 softmax", "B2 values", "barrier", "C quant + attn_out rows", "barrier", "D add+norm+quant", "D router",
+                       "barrier", "E route + issue", "E gate/up rows", "barrier", "F silu+quant", "F down rows", "barrier")
 
     def resident_profile(self) -> dict:
         """Nanoseconds per phase accumulated by the resident kernel's CTA 0 since set_option("resident_profile", 1)."""
@@ -358,6 +360,34 @@ class CudaModel:
         if self._L.llamd_model_prefill(self._h, t.ctypes.data_as(C.c_void_p), t.size, int(base_pos), C.byref(out)) != 0:
             raise backend.Other("prefill: " + self._err())
         return int(out.value)
+
+    def verify(self, tokens, base_pos: int = 0) -> np.ndarray:
+        """out[i] = the greedy token after tokens[0..=i] (llamd_model_verify): every drafted token checked by the model."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        if t.size == 0 or base_pos + t.size > self.max_kv:
+            raise backend.Malformed("verify: empty, or positions beyond the allocated cache")
+        out = np.zeros(t.size, dtype=np.int32)
+        if self._L.llamd_model_verify(self._h, t.ctypes.data_as(C.c_void_p), t.size, int(base_pos), out.ctypes.data_as(C.c_void_p)) != 0:
+            raise backend.Other("verify: " + self._err())
+        return out
+
+    def speculative_decode(self, first_token: int, start_pos: int, n: int, draft, max_draft: int = 8):
+        """n greedy tokens after `first_token` at `start_pos`, with `draft(context_tokens, k) -> k guessed tokens` proposing
+        and the model verifying every guess. Returns (tokens, passes): the tokens equal plain greedy decode's whatever
+        the drafter says; only the number of passes changes."""
+        out, cur, pos, passes = [], int(first_token), int(start_pos), 0
+        while len(out) < n:
+            k = min(max_draft, n - len(out) - 1, self.max_kv - pos - 1)
+            guess = [int(g) for g in draft(out, k)] if k > 0 else []
+            got = self.verify([cur] + guess, pos)
+            passes += 1
+            accepted = 0
+            while accepted < len(guess) and guess[accepted] == int(got[accepted]):
+                accepted += 1
+            new = [int(t) for t in got[:accepted + 1]]  # the accepted guesses are the model's own picks; plus one more
+            out.extend(new)
+            cur, pos = new[-1], pos + accepted + 1
+        return out[:n], passes
 
     def decode(self, first_token: int, start_pos: int, n: int):
         """Resident greedy decode of n tokens -> (tokens int32[n], device milliseconds)."""
