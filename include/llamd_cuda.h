@@ -356,7 +356,7 @@ void llamd_fwd_silu(const float *x, float *out, size_t n);                      
  * LLAMD_EXP_TABLE=0 in the environment switches the table off (correctly rounded exp, ~1 s less start-up). */
 void llamd_fwd_expf(const float *x, float *out, size_t n);
 long long llamd_cuda_exp_exceptions(void);
-int llamd_cuda_exp_window_on(void); /* 1: only results within 2^-7 ulp of a rounding midpoint are looked up (verified at start-up) */
+int llamd_cuda_exp_window_on(void); /* > 0: only results this close (in 2^-29 ulp) to a rounding midpoint are looked up; measured at start-up */
 void llamd_fwd_mul(const float *a, const float *b, float *out, size_t n);             /* :112-114 */
 void llamd_fwd_scale(const float *x, float by, float *out, size_t n);                 /* :116-118 */
 /* w [m rows][k], x [n rows][k] -> out [n][m], out[j*m+i] (:126-149); any k. */

@@ -175,33 +175,18 @@ struct RowRef {
 };
 
 // The rows [row_lo, row_hi) of a phase, `nb` blocks each, in chunks of floor(T / nb) rows. ROWMAP(row) -> RowRef.
-// The first chunk's weights may have been requested earlier (pre, loaded): they stay in flight across the barrier.
+// The weights come from L2 (the phase before asked for them); nothing is held in registers outside a chunk's
+// load -> dot -> exchange sequence, which at 80 registers per thread is what keeps the 53 loaded words out of local memory.
 template <class RowMap>
-__device__ __forceinline__ void mv_issue(MvUnit &u, bool &have, const RowMap &map, int nb, int row_lo, int row_hi) {
-    const int tid = threadIdx.x, row_l = tid / nb, b = tid - row_l * nb;
-    const int cap = kMegaThreads / nb;
-    have = row_l < cap && row_lo + row_l < row_hi;
-    if (have) {
-        const RowRef rr = map(row_lo + row_l);
-        mv_load(u, rr.w, rr.unit0 + b);
-    }
-}
-template <class RowMap>
-__device__ __forceinline__ void mv_finish(MvUnit &u, bool have, const RowMap &map, int nb, int row_lo, int row_hi, const uint32_t *s_act,
-                                          const float *s_adv, float *s_ex) {
+__device__ __forceinline__ void mv_rows(const RowMap &map, int nb, int row_lo, int row_hi, const uint32_t *s_act, const float *s_adv, float *s_ex) {
     const int tid = threadIdx.x, row_l = tid / nb, b = tid - row_l * nb;
     const int cap = kMegaThreads / nb;
     for (int base = row_lo; base < row_hi; base += cap) {
         const int rows_here = min(cap, row_hi - base);
-        if (base != row_lo) {  // later chunks: load now (dimensions for which one CTA's rows exceed a chunk)
-            have = row_l < rows_here;
-            if (have) {
-                const RowRef rr = map(base + row_l);
-                mv_load(u, rr.w, rr.unit0 + b);
-            }
-        }
-        if (have) {
+        if (row_l < rows_here) {
             const RowRef rr = map(base + row_l);
+            MvUnit u;
+            mv_load(u, rr.w, rr.unit0 + b);
             mv_compute(u, s_act + (size_t)(rr.act * nb + b) * kMegaActWords, s_adv[rr.act * nb + b], s_ex, tid);
         }
         __syncthreads();
@@ -339,467 +324,497 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-__global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaParams p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    const int E = p.E, H = p.H, HKV = p.HKV, hd = p.hd, nu = p.nu, ffe = p.ffe, ne = p.n_expert;
-    const int qd = H * hd, kvd = HKV * hd, eb = E / 256, qb = qd / 256, fb = ffe / 256;
-    const MegaSmem L = mega_smem(E, qd, hd, p.act_blocks, p.sl_floats, ne, p.ktile_rows, H / HKV);
-    float *s_x = reinterpret_cast<float *>(smem + L.x);
-    float *s_xn = reinterpret_cast<float *>(smem + L.xn);
-    float *s_sq = reinterpret_cast<float *>(smem + L.sq);
-    uint32_t *s_act = reinterpret_cast<uint32_t *>(smem + L.act);
-    int8_t *s_nat = reinterpret_cast<int8_t *>(smem + L.nat);
-    float *s_adv = reinterpret_cast<float *>(smem + L.adv);
-    float *s_ex = reinterpret_cast<float *>(smem + L.ex);
-    float *s_sl = reinterpret_cast<float *>(smem + L.sl);
-    float *s_tile = reinterpret_cast<float *>(smem + L.tile);
-    float *s_misc = reinterpret_cast<float *>(smem + L.misc);
-    float *s_k = s_misc + hd, *s_v = s_misc + 2 * hd, *s_tmp = s_misc + 3 * hd;  // [hd] each
-    float *s_red = s_misc + 4 * hd;                             // [128] reduction scratch
-    int32_t *s_ids = reinterpret_cast<int32_t *>(s_red + 256);  // [64]
-    float *s_w = s_red + 320;                                   // [64]
-    float *s_scalar = s_red + 384;                              // a few broadcast scalars
-    __shared__ bool s_flag;
+// What a CTA knows for the whole token: its shared-memory regions, the model's dimensions, its share of every phase.
+// One copy per CTA in shared memory; the phase functions below are separate functions (not inlined) so that each gets
+// a register allocation of its own -- inside one 2000-line kernel body at 80 registers per thread the ordered-sum loops
+// and the attention loops were spilling.
+struct MegaCtx {
+    float *s_x, *s_xn, *s_sq, *s_adv, *s_ex, *s_sl, *s_tile, *s_k, *s_v, *s_tmp, *s_red, *s_w, *s_scalar;
+    uint32_t *s_act;
+    int8_t *s_nat;
+    int32_t *s_ids;
+    int E, H, HKV, hd, nu, ffe, ne, qd, kvd, eb, qb, fb;
+    int cta, G, pos, n_kv;
+    int a_lo, a_hi, c_lo, c_hi, e_lo, e_hi, f_lo, f_hi, slot_lo, slot_hi;
+    int ratio, half, cols, b1_kvh, t_lo, t_hi, b1_has_pos;
+};
 
-    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x;
-    const int token = p.meta[0], pos = p.meta[1];
-    const int n_kv = pos + 1;
-    unsigned int bar_target = 0;
-    MvUnit u;
-    bool have = false;
-    // optional phase clock: CTA 0 adds the time since the previous stamp to slot k
-    unsigned long long t_prev = 0;
-    const bool prof = p.prof && cta == 0 && tid == 0;
-    if (prof) t_prev = global_ns();
-#define MEGA_STAMP(k)                              \
-    do {                                           \
-        if (prof) {                                \
-            const unsigned long long t_ = global_ns(); \
-            p.prof[k] += t_ - t_prev;              \
-            t_prev = t_;                           \
-        }                                          \
-    } while (0)
+__device__ __noinline__ void mega_prefetch_attn_side(const MegaCtx &c, const MegaLayer &w) {
+    l2_prefetch_rows(w.attn_q, c.a_lo, c.a_hi, 0, c.qd, c.eb);
+    l2_prefetch_rows(w.attn_k, c.a_lo, c.a_hi, c.qd, c.kvd, c.eb);
+    l2_prefetch_rows(w.attn_v, c.a_lo, c.a_hi, c.qd + c.kvd, c.kvd, c.eb);
+    l2_prefetch_rows(w.attn_out, c.c_lo, c.c_hi, 0, c.E, c.qb);
+    for (int r = c.cta; r < c.ne; r += c.G) l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(w.router + (size_t)r * c.E), (size_t)c.E * 4);
+}
 
-    // ---- embed: one row of token_embd, d * sc * q (crates/llamd-quant/src/lib.rs:181-226) ----
-    for (int i = tid; i < E; i += kMegaThreads) {
-        const size_t unit = (size_t)token * eb + (i >> 8);
-        const int e = i & 255;
-        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(p.tok_embd + t32_d_offset(unit)));
-        const float sc = (float)(int8_t)p.tok_embd[t32_scale_offset(unit) + (e >> 4)];
-        s_x[i] = __fmul_rn(__fmul_rn(d, sc), (float)t32_weight(p.tok_embd, unit, e));
+// ---- phase A: (combine) + norm + Q8_K | Q, K, V rows. Returns after the tail's output when `tail`. ----
+__device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly, int il, bool tail) {
+    const int tid = threadIdx.x, E = c.E, nu = c.nu, eb = c.eb, qd = c.qd, kvd = c.kvd;
+    if (!tail && c.n_kv > 1) {
+        // this layer's cached K and V rows (evicted since the last token): every CTA asks L2 for a slice of each
+        const size_t kv_bytes = (size_t)(c.n_kv - 1) * kvd * 4;
+        const size_t per = ((kv_bytes + c.G - 1) / c.G + 15) & ~(size_t)15, off = per * c.cta;
+        if (off < kv_bytes) {
+            const size_t n = kv_bytes - off < per ? kv_bytes - off : per;
+            l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(ly.kc) + off, n);
+            l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(ly.vc) + off, n);
+        }
+    }
+    if (il > 0) {
+        // x += sum_e w_e * down_e, e in routing order, the expert sum started from 0 (layer.rs:243-258, 281-287).
+        // All of a sweep's loads are issued before the first is used.
+        for (int base = 0; base < E; base += kMegaElems * kMegaThreads) {
+            float acc[kMegaElems];
+#pragma unroll
+            for (int q = 0; q < kMegaElems; q++) acc[q] = 0.0f;
+            for (int e0 = 0; e0 < nu; e0 += 8) {
+                float dv[8][kMegaElems];
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+#pragma unroll
+                    for (int q = 0; q < kMegaElems; q++) {
+                        const int i = base + tid + q * kMegaThreads;
+                        dv[e][q] = (e0 + e < nu && i < E) ? __ldcg(p.e_down + (size_t)(e0 + e) * E + i) : 0.0f;
+                    }
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    if (e0 + e < nu) {
+                        const float we = c.s_w[e0 + e];
+#pragma unroll
+                        for (int q = 0; q < kMegaElems; q++) acc[q] = __fadd_rn(acc[q], __fmul_rn(we, dv[e][q]));
+                    }
+            }
+#pragma unroll
+            for (int q = 0; q < kMegaElems; q++) {
+                const int i = base + tid + q * kMegaThreads;
+                if (i < E) c.s_x[i] = __fadd_rn(c.s_x[i], acc[q]);
+            }
+        }
+        __syncthreads();
+        if (c.cta == 0 && p.trace_x)
+            for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = c.s_x[i];
+    }
+    norm_quant(c.s_x, tail ? p.output_norm : ly.attn_norm, c.s_sq, c.s_xn, c.s_nat, c.s_adv, E, p.eps, c.s_scalar);
+    if (tail) {
+        if (c.cta == 0) {
+            for (int i = tid; i < E; i += kMegaThreads) {
+                p.x_out[i] = c.s_x[i];
+                p.aq_out[i] = c.s_nat[i];
+            }
+            if (tid < eb) p.ad_out[tid] = c.s_adv[tid];
+        }
+        return;
+    }
+    auto map_a = [&](int row) -> RowRef {
+        if (row < qd) return RowRef{ly.attn_q, (size_t)row * eb, 0, p.q + row};
+        if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
+        return RowRef{ly.attn_v, (size_t)(row - qd - kvd) * eb, 0, p.v + (row - qd - kvd)};
+    };
+    build_act_image(c.s_nat, c.s_act, eb);
+    __syncthreads();
+    mv_rows(map_a, eb, c.a_lo, c.a_hi, c.s_act, c.s_adv, c.s_ex);
+}
+
+// ---- phase B1: QK-norm, RoPE, KV store, scores of (kv head, chunk of positions) ----
+__device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    if (!(c.b1_kvh < c.HKV && c.t_hi > c.t_lo)) return;
+    const int tid = threadIdx.x, hd = c.hd, ratio = c.ratio, half = c.half, kvd = c.kvd, pos = c.pos, t_lo = c.t_lo;
+    float *s_qraw = c.s_tile, *s_qr = c.s_tile + ratio * hd, *s_kt = c.s_tile + 2 * ratio * hd;  // [ratio][hd] x2, [chunk][hd + 4]
+    const int stride = hd + 4, hd4 = hd / 4, cnt = c.t_hi - t_lo;
+    const float *kb = ly.kc + (size_t)c.b1_kvh * hd;
+    // the chunk's cached K rows start their trip first (the row of this very position is made below)
+    constexpr int kLd = 4;
+    for (int i0 = 0; i0 < cnt * hd4; i0 += kLd * kMegaThreads) {
+        float4 reg[kLd];
+#pragma unroll
+        for (int j = 0; j < kLd; j++) {
+            const int idx = i0 + tid + j * kMegaThreads;
+            const int r = idx / hd4, cc = idx - r * hd4;
+            reg[j] = (idx < cnt * hd4 && t_lo + r != pos) ? __ldg(reinterpret_cast<const float4 *>(kb + (size_t)(t_lo + r) * kvd) + cc)
+                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (i0 == 0) {  // the group's q heads and this token's k, v head, raw
+            for (int i = tid; i < ratio * hd; i += kMegaThreads) s_qraw[i] = __ldcg(p.q + (size_t)c.b1_kvh * ratio * hd + i);
+            for (int i = tid; i < hd; i += kMegaThreads) {
+                c.s_k[i] = __ldcg(p.k + (size_t)c.b1_kvh * hd + i);
+                c.s_v[i] = __ldcg(p.v + (size_t)c.b1_kvh * hd + i);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kLd; j++) {
+            const int idx = i0 + tid + j * kMegaThreads;
+            if (idx < cnt * hd4) {
+                const int r = idx / hd4, cc = idx - r * hd4;
+                *reinterpret_cast<float4 *>(s_kt + r * stride + 4 * cc) = reg[j];
+            }
+        }
     }
     __syncthreads();
-
-    // Row ranges of the phases (the same every layer)
-    const int rows_a = qd + 2 * kvd, rpc_a = (rows_a + G - 1) / G;
-    const int a_lo = min(cta * rpc_a, rows_a), a_hi = min(a_lo + rpc_a, rows_a);
-    const int rpc_c = (E + G - 1) / G;
-    const int c_lo = min(cta * rpc_c, E), c_hi = min(c_lo + rpc_c, E);
-    const int rows_e = nu * 2 * ffe, rpc_e = (rows_e + G - 1) / G;
-    const int e_lo = min(cta * rpc_e, rows_e), e_hi = min(e_lo + rpc_e, rows_e);
-    const int rows_f = nu * E, rpc_f = (rows_f + G - 1) / G;
-    const int f_lo = min(cta * rpc_f, rows_f), f_hi = min(f_lo + rpc_f, rows_f);
-    const int slot_lo = f_lo / E, slot_hi = f_hi > f_lo ? (f_hi - 1) / E : slot_lo;
-    // attention, first half: CTA -> (kv head, chunk of positions); second half: CTA -> (head, column part)
-    const int ratio = H / HKV, half = hd / 2, cols = hd / kMegaSplit;
-    const int ncp = G / HKV;  // position chunks per kv head
-    const int b1_kvh = cta / ncp, b1_chunk = cta - b1_kvh * ncp;
-    const int ppc = (n_kv + ncp - 1) / ncp;
-    const int t_lo = min(b1_chunk * ppc, n_kv), t_hi = b1_kvh < HKV ? min(t_lo + ppc, n_kv) : t_lo;
-    const bool b1_has_pos = b1_kvh < HKV && pos >= t_lo && pos < t_hi;
-
-    // What this CTA will read of a layer's attention-side weights, asked of L2 ahead of time (hints: nothing waits).
-    auto prefetch_attn_side = [&](const MegaLayer &w) {
-        l2_prefetch_rows(w.attn_q, a_lo, a_hi, 0, qd, eb);
-        l2_prefetch_rows(w.attn_k, a_lo, a_hi, qd, kvd, eb);
-        l2_prefetch_rows(w.attn_v, a_lo, a_hi, qd + kvd, kvd, eb);
-        l2_prefetch_rows(w.attn_out, c_lo, c_hi, 0, E, qb);
-        for (int r = cta; r < ne; r += G) l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(w.router + (size_t)r * E), (size_t)E * 4);
-    };
-    prefetch_attn_side(p.layers[0]);
-
-    for (int il = 0; il <= p.n_layer; il++) {
-        const bool tail = il == p.n_layer;  // after the last layer: combine + output norm only
-        const MegaLayer ly = p.layers[tail ? p.n_layer - 1 : il];
-        // ================= phase A: (combine) + norm + Q8_K | Q, K, V rows =================
-        auto map_a = [&](int row) -> RowRef {
-            if (row < qd) return RowRef{ly.attn_q, (size_t)row * eb, 0, p.q + row};
-            if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
-            return RowRef{ly.attn_v, (size_t)(row - qd - kvd) * eb, 0, p.v + (row - qd - kvd)};
-        };
-        if (!tail && n_kv > 1) {
-            // this layer's cached K and V rows (evicted since the last token): every CTA asks for a slice of each
-            const size_t kv_bytes = (size_t)(n_kv - 1) * kvd * 4;
-            const size_t per = ((kv_bytes + G - 1) / G + 15) & ~(size_t)15, off = per * cta;
-            if (off < kv_bytes) {
-                const size_t n = kv_bytes - off < per ? kv_bytes - off : per;
-                l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(ly.kc) + off, n);
-                l2_prefetch_bytes(reinterpret_cast<const uint8_t *>(ly.vc) + off, n);
-            }
-        }
-        if (il > 0) {
-            // x += sum_e w_e * down_e, e in routing order, the expert sum started from 0 (layer.rs:243-258, 281-287).
-            // All of a sweep's loads are issued before the first is used.
-            for (int base = 0; base < E; base += kMegaElems * kMegaThreads) {
-                float acc[kMegaElems];
-#pragma unroll
-                for (int q = 0; q < kMegaElems; q++) acc[q] = 0.0f;
-                for (int e0 = 0; e0 < nu; e0 += 8) {
-                    float dv[8][kMegaElems];
-#pragma unroll
-                    for (int e = 0; e < 8; e++)
-#pragma unroll
-                        for (int q = 0; q < kMegaElems; q++) {
-                            const int i = base + tid + q * kMegaThreads;
-                            dv[e][q] = (e0 + e < nu && i < E) ? __ldcg(p.e_down + (size_t)(e0 + e) * E + i) : 0.0f;
-                        }
-#pragma unroll
-                    for (int e = 0; e < 8; e++)
-                        if (e0 + e < nu) {
-                            const float we = s_w[e0 + e];
-#pragma unroll
-                            for (int q = 0; q < kMegaElems; q++) acc[q] = __fadd_rn(acc[q], __fmul_rn(we, dv[e][q]));
-                        }
-                }
-#pragma unroll
-                for (int q = 0; q < kMegaElems; q++) {
-                    const int i = base + tid + q * kMegaThreads;
-                    if (i < E) s_x[i] = __fadd_rn(s_x[i], acc[q]);
-                }
-            }
-            __syncthreads();
-            if (cta == 0 && p.trace_x)
-                for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = s_x[i];
-        }
-        norm_quant(s_x, tail ? p.output_norm : ly.attn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
-        if (tail) {
-            if (cta == 0) {
-                for (int i = tid; i < E; i += kMegaThreads) {
-                    p.x_out[i] = s_x[i];
-                    p.aq_out[i] = s_nat[i];
-                }
-                if (tid < eb) p.ad_out[tid] = s_adv[tid];
-            }
-            break;
-        }
-        MEGA_STAMP(0);
-        mv_issue(u, have, map_a, eb, a_lo, a_hi);  // (from L2: asked for a phase ago)
-        build_act_image(s_nat, s_act, eb);
-        __syncthreads();
-        mv_finish(u, have, map_a, eb, a_lo, a_hi, s_act, s_adv, s_ex);
-        MEGA_STAMP(1);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(2);
-
-        // ================= phase B1: QK-norm, RoPE, KV store, scores of (kv head, chunk of positions) =================
-        if (b1_kvh < HKV && t_hi > t_lo) {
-            float *s_qraw = s_tile, *s_qr = s_tile + ratio * hd, *s_kt = s_tile + 2 * ratio * hd;  // [ratio][hd] x2, [ppc][hd + 4]
-            const int stride = hd + 4, hd4 = hd / 4, cnt = t_hi - t_lo;
-            const float *kb = ly.kc + (size_t)b1_kvh * hd;
-            // the chunk's cached K rows start their trip first (the row of this very position is made below)
-            constexpr int kLd = 4;
-            for (int i0 = 0; i0 < cnt * hd4; i0 += kLd * kMegaThreads) {
-                float4 reg[kLd];
-#pragma unroll
-                for (int j = 0; j < kLd; j++) {
-                    const int idx = i0 + tid + j * kMegaThreads;
-                    const int r = idx / hd4, cc = idx - r * hd4;
-                    reg[j] = (idx < cnt * hd4 && t_lo + r != pos) ? __ldg(reinterpret_cast<const float4 *>(kb + (size_t)(t_lo + r) * kvd) + cc)
-                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                // the group's q heads and this token's k, v head, raw
-                if (i0 == 0) {
-                    for (int i = tid; i < ratio * hd; i += kMegaThreads) s_qraw[i] = __ldcg(p.q + (size_t)b1_kvh * ratio * hd + i);
-                    for (int i = tid; i < hd; i += kMegaThreads) {
-                        s_k[i] = __ldcg(p.k + (size_t)b1_kvh * hd + i);
-                        s_v[i] = __ldcg(p.v + (size_t)b1_kvh * hd + i);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kLd; j++) {
-                    const int idx = i0 + tid + j * kMegaThreads;
-                    if (idx < cnt * hd4) {
-                        const int r = idx / hd4, cc = idx - r * hd4;
-                        *reinterpret_cast<float4 *>(s_kt + r * stride + 4 * cc) = reg[j];
-                    }
-                }
-            }
-            __syncthreads();
-            // per-head norm (layer.rs:62-79): each sum of squares walked in order by its own thread
-            if ((tid & 31) == 0 && (tid >> 5) <= ratio) {
-                const int j = tid >> 5;  // 0..ratio-1: q heads, ratio: the k head
-                const float *sx = j < ratio ? s_qraw + j * hd : s_k;
-                const float *w = j < ratio ? ly.q_norm : ly.k_norm;
-                float scale = 1.0f;
-                if (w) {
-                    float sum = 0.0f;
+    // per-head norm (layer.rs:62-79): each sum of squares walked in order by its own thread
+    if ((tid & 31) == 0 && (tid >> 5) <= ratio) {
+        const int j = tid >> 5;  // 0..ratio-1: q heads, ratio: the k head
+        const float *sx = j < ratio ? s_qraw + j * hd : c.s_k;
+        const float *w = j < ratio ? ly.q_norm : ly.k_norm;
+        float scale = 1.0f;
+        if (w) {
+            float sum = 0.0f;
 #pragma unroll 8
-                    for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
-                    scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), p.eps)));
-                }
-                s_scalar[8 + j] = scale;
-            }
-            __syncthreads();
-            // NeoX RoPE on (i, i + half) pairs, angles from the host-built table
-            for (int idx = tid; idx < (ratio + 1) * half; idx += kMegaThreads) {
-                const int j = idx / half, i = idx - j * half;
-                const bool is_k = j == ratio;
-                const float *sx = is_k ? s_k : s_qraw + j * hd;
-                const float *w = is_k ? ly.k_norm : ly.q_norm;
-                const float scale = s_scalar[8 + j];
-                float a = sx[i], b = sx[i + half];
-                if (w) {
-                    a = __fmul_rn(__fmul_rn(a, scale), __ldg(w + i));
-                    b = __fmul_rn(__fmul_rn(b, scale), __ldg(w + i + half));
-                }
-                const float2 sc = *reinterpret_cast<const float2 *>(p.rope_tab + ((size_t)pos * half + i) * 2);
-                const float o0 = __fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x));
-                const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
-                float *dst = is_k ? s_tmp : s_qr + j * hd;
-                dst[i] = o0;
-                dst[i + half] = o1;
-            }
-            __syncthreads();
-            if (b1_has_pos) {  // this position's K (roped) and V go into the cache and into the chunk
-                for (int i = tid; i < hd; i += kMegaThreads) {
-                    ly.kc[(size_t)pos * kvd + (size_t)b1_kvh * hd + i] = s_tmp[i];
-                    ly.vc[(size_t)pos * kvd + (size_t)b1_kvh * hd + i] = s_v[i];
-                    s_kt[(pos - t_lo) * stride + i] = s_tmp[i];
-                }
-                __syncthreads();
-            }
-            MEGA_STAMP(3);
-            // logit[h][t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106): one thread per (head, position)
-            const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
-            for (int idx = tid; idx < ratio * cnt; idx += kMegaThreads) {
-                const int j = idx / cnt, r = idx - j * cnt;
-                const float4 *kr = reinterpret_cast<const float4 *>(s_kt + r * stride);
-                const float4 *q4 = reinterpret_cast<const float4 *>(s_qr + j * hd);
-                float dot = 0.0f;
-                float pa[16];  // four 16-byte reads ahead of the adds: the chain is then the dependent adds alone
-#pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
-                    const float4 kv = kr[jj], qv = q4[jj];
-                    pa[4 * jj] = __fmul_rn(qv.x, kv.x), pa[4 * jj + 1] = __fmul_rn(qv.y, kv.y), pa[4 * jj + 2] = __fmul_rn(qv.z, kv.z), pa[4 * jj + 3] = __fmul_rn(qv.w, kv.w);
-                }
-                for (int d4 = 0; d4 < hd4; d4 += 4) {
-                    float pb[16];
-                    const int n4 = d4 + 4 < hd4 ? d4 + 4 : d4;
-#pragma unroll
-                    for (int jj = 0; jj < 4; jj++) {
-                        const float4 kv = kr[n4 + jj], qv = q4[n4 + jj];
-                        pb[4 * jj] = __fmul_rn(qv.x, kv.x), pb[4 * jj + 1] = __fmul_rn(qv.y, kv.y), pb[4 * jj + 2] = __fmul_rn(qv.z, kv.z), pb[4 * jj + 3] = __fmul_rn(qv.w, kv.w);
-                    }
-#pragma unroll
-                    for (int jj = 0; jj < 16; jj++) dot = __fadd_rn(dot, pa[jj]);
-#pragma unroll
-                    for (int jj = 0; jj < 16; jj++) pa[jj] = pb[jj];
-                }
-                p.scores[(size_t)(b1_kvh * ratio + j) * p.max_kv + t_lo + r] = __fmul_rn(dot, scale);
-            }
-            MEGA_STAMP(4);
+            for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
+            scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), p.eps)));
         }
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(5);
-
-        // ================= phase B2: softmax and weighted values of (head, column part) =================
-        if (cta < H * kMegaSplit) {
-            const int h = cta / kMegaSplit, c = cta - h * kMegaSplit, kvh = h / ratio;
-            constexpr int kLd = 8;
-            // the V rows of this item's columns start their trip first
-            const float *vb = ly.vc + (size_t)kvh * hd + (size_t)c * cols;
-            const int cols4 = cols / 4;
-            float4 reg[kLd];
-            auto fetch_v = [&](int t0, int cnt) {
+        c.s_scalar[8 + j] = scale;
+    }
+    __syncthreads();
+    // NeoX RoPE on (i, i + half) pairs, angles from the host-built table
+    for (int idx = tid; idx < (ratio + 1) * half; idx += kMegaThreads) {
+        const int j = idx / half, i = idx - j * half;
+        const bool is_k = j == ratio;
+        const float *sx = is_k ? c.s_k : s_qraw + j * hd;
+        const float *w = is_k ? ly.k_norm : ly.q_norm;
+        const float scale = c.s_scalar[8 + j];
+        float a = sx[i], b = sx[i + half];
+        if (w) {
+            a = __fmul_rn(__fmul_rn(a, scale), __ldg(w + i));
+            b = __fmul_rn(__fmul_rn(b, scale), __ldg(w + i + half));
+        }
+        const float2 sc = *reinterpret_cast<const float2 *>(p.rope_tab + ((size_t)pos * half + i) * 2);
+        const float o0 = __fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x));
+        const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
+        float *dst = is_k ? c.s_tmp : s_qr + j * hd;
+        dst[i] = o0;
+        dst[i + half] = o1;
+    }
+    __syncthreads();
+    if (c.b1_has_pos) {  // this position's K (roped) and V go into the cache and into the chunk
+        for (int i = tid; i < hd; i += kMegaThreads) {
+            ly.kc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = c.s_tmp[i];
+            ly.vc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = c.s_v[i];
+            s_kt[(pos - t_lo) * stride + i] = c.s_tmp[i];
+        }
+        __syncthreads();
+    }
+    // logit[h][t] = (sum_d q[d] * k[t][d], d ascending) * scale (attention.rs:99-106): one thread per (head, position)
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    for (int idx = tid; idx < ratio * cnt; idx += kMegaThreads) {
+        const int j = idx / cnt, r = idx - j * cnt;
+        const float4 *kr = reinterpret_cast<const float4 *>(s_kt + r * stride);
+        const float4 *q4 = reinterpret_cast<const float4 *>(s_qr + j * hd);
+        float dot = 0.0f;
+        float pa[16];  // four 16-byte reads ahead of the adds: the chain is then the dependent adds alone
 #pragma unroll
-                for (int j = 0; j < kLd; j++) {
-                    const int idx = tid + j * kMegaThreads;
-                    const int r = idx / cols4, cc = idx - r * cols4;
-                    const int t = t0 + r;
-                    // (this position's row was stored by another CTA before the barrier: read it from L2)
-                    reg[j] = idx >= cnt * cols4 ? make_float4(0.f, 0.f, 0.f, 0.f)
-                             : t == pos         ? __ldcg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc)
-                                                : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
-                }
-            };
-            fetch_v(0, min(kMegaThreads, n_kv));
+        for (int jj = 0; jj < 4; jj++) {
+            const float4 kv = kr[jj], qv = q4[jj];
+            pa[4 * jj] = __fmul_rn(qv.x, kv.x), pa[4 * jj + 1] = __fmul_rn(qv.y, kv.y), pa[4 * jj + 2] = __fmul_rn(qv.z, kv.z), pa[4 * jj + 3] = __fmul_rn(qv.w, kv.w);
+        }
+        for (int d4 = 0; d4 < hd4; d4 += 4) {
+            float pb[16];
+            const int n4 = d4 + 4 < hd4 ? d4 + 4 : d4;
+#pragma unroll
+            for (int jj = 0; jj < 4; jj++) {
+                const float4 kv = kr[n4 + jj], qv = q4[n4 + jj];
+                pb[4 * jj] = __fmul_rn(qv.x, kv.x), pb[4 * jj + 1] = __fmul_rn(qv.y, kv.y), pb[4 * jj + 2] = __fmul_rn(qv.z, kv.z), pb[4 * jj + 3] = __fmul_rn(qv.w, kv.w);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 16; jj++) dot = __fadd_rn(dot, pa[jj]);
+#pragma unroll
+            for (int jj = 0; jj < 16; jj++) pa[jj] = pb[jj];
+        }
+        p.scores[(size_t)(c.b1_kvh * ratio + j) * p.max_kv + t_lo + r] = __fmul_rn(dot, scale);
+    }
+}
+
+// ---- phase B2: softmax and weighted values of (head, column part) ----
+__device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    if (c.cta >= c.H * kMegaSplit) return;
+    const int tid = threadIdx.x, hd = c.hd, cols = c.cols, kvd = c.kvd, n_kv = c.n_kv, pos = c.pos;
+    const int h = c.cta / kMegaSplit, cpart = c.cta - h * kMegaSplit, kvh = h / c.ratio;
+    constexpr int kLd = 8;
+    const float *vb = ly.vc + (size_t)kvh * hd + (size_t)cpart * cols;
+    const int cols4 = cols / 4;
+    float acc = 0.0f;
+    for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
+        const int cnt = min(kMegaThreads, n_kv - t0);
+        // the V rows of this item's columns start their trip first
+        float4 reg[kLd];
+#pragma unroll
+        for (int j = 0; j < kLd; j++) {
+            const int idx = tid + j * kMegaThreads;
+            const int r = idx / cols4, cc = idx - r * cols4;
+            const int t = t0 + r;
+            // (this position's row was stored by another CTA before the barrier: read it from L2)
+            reg[j] = idx >= cnt * cols4 ? make_float4(0.f, 0.f, 0.f, 0.f)
+                     : t == pos         ? __ldcg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc)
+                                        : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
+        }
+        if (t0 == 0) {
             // max (order-free), e[t] = exp(l - max), the sum walked in order (attention.rs:107-115)
             float lmax = -INFINITY;
             for (int t = tid; t < n_kv; t += kMegaThreads) {
                 const float l = __ldcg(p.scores + (size_t)h * p.max_kv + t);
-                s_sl[t] = l;
+                c.s_sl[t] = l;
                 lmax = fmaxf(lmax, l);
             }
             for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
-            if ((tid & 31) == 0) s_red[tid >> 5] = lmax;
+            if ((tid & 31) == 0) c.s_red[tid >> 5] = lmax;
             __syncthreads();
-            lmax = s_red[0];
-            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, s_red[w]);
-            for (int t = tid; t < n_kv; t += kMegaThreads) s_sl[t] = ref_expf(__fsub_rn(s_sl[t], lmax));
-            __syncthreads();
-            float acc = 0.0f;
-            for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
-                const int cnt = min(kMegaThreads, n_kv - t0);
-                if (t0 > 0) {
-                    __syncthreads();  // the previous V tile is dead
-                    fetch_v(t0, cnt);
-                }
-#pragma unroll
-                for (int j = 0; j < kLd; j++) {
-                    const int idx = tid + j * kMegaThreads;
-                    if (idx < cnt * cols4) reinterpret_cast<float4 *>(s_tile)[idx] = reg[j];
-                }
-                if (t0 == 0 && tid == 0) s_scalar[3] = __fdiv_rn(1.0f, chain_sum(s_sl, n_kv, 0.0f));
-                __syncthreads();
-                if (t0 == 0) MEGA_STAMP(6);
-                // out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
-                if (tid < cols) {
-                    const float inv = s_scalar[3];
-                    int r = 0;
-                    if (cnt >= 16) {
-                        float pa[16], pb[16];
-#pragma unroll
-                        for (int j = 0; j < 16; j++) pa[j] = __fmul_rn(__fmul_rn(s_sl[t0 + j], inv), s_tile[j * cols + tid]);
-                        for (; r + 16 <= cnt; r += 16) {
-                            const int rn = (r + 32 <= cnt) ? r + 16 : r;
-#pragma unroll
-                            for (int j = 0; j < 16; j++) pb[j] = __fmul_rn(__fmul_rn(s_sl[t0 + rn + j], inv), s_tile[(rn + j) * cols + tid]);
-#pragma unroll
-                            for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, pa[j]);
-#pragma unroll
-                            for (int j = 0; j < 16; j++) pa[j] = pb[j];
-                        }
-                    }
-                    for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(s_sl[t0 + r], inv), s_tile[r * cols + tid]));
-                }
-            }
-            if (tid < cols) p.attn[(size_t)h * hd + (size_t)c * cols + tid] = acc;
-            MEGA_STAMP(7);
+            lmax = c.s_red[0];
+            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, c.s_red[w]);
+            for (int t = tid; t < n_kv; t += kMegaThreads) c.s_sl[t] = ref_expf(__fsub_rn(c.s_sl[t], lmax));
         }
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(8);
-
-        // ================= phase C: Q8_K of the attention output | attn_out rows =================
-        auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
-        mv_issue(u, have, map_c, qb, c_lo, c_hi);
-        {
-            const int warp = tid >> 5, lane = tid & 31;
-            for (int b = warp; b < qb; b += kMegaThreads / 32) {
-                const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8)), c4 = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8) + 1);
-                const float v[8] = {a.x, a.y, a.z, a.w, c4.x, c4.y, c4.z, c4.w};
-                q8k_quantize_block(v, lane, s_nat + b * 256, s_adv + b, nullptr);
-            }
-            __syncthreads();
-            build_act_image(s_nat, s_act, qb);
-            __syncthreads();
-            mv_finish(u, have, map_c, qb, c_lo, c_hi, s_act, s_adv, s_ex);
+        __syncthreads();  // (the exponentials are in place; a previous V tile is dead)
+#pragma unroll
+        for (int j = 0; j < kLd; j++) {
+            const int idx = tid + j * kMegaThreads;
+            if (idx < cnt * cols4) reinterpret_cast<float4 *>(c.s_tile)[idx] = reg[j];
         }
-        MEGA_STAMP(9);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(10);
-
-        // ================= phase D: x += attn_out, FFN norm, Q8_K | router logits =================
-        {
-            // the router row this CTA dots (asked of L2 a layer ago) and attn_out's result, read before the norm's chain
-            float wr_pre[kMegaElems], rv[kMegaElems];
-#pragma unroll
-            for (int q = 0; q < kMegaElems; q++) {
-                const int i = tid + q * kMegaThreads;
-                rv[q] = i < E ? __ldcg(p.xb2 + i) : 0.0f;
-                wr_pre[q] = (cta < ne && i < E) ? __ldg(ly.router + (size_t)cta * E + i) : 0.0f;
-            }
-#pragma unroll
-            for (int q = 0; q < kMegaElems; q++) {
-                const int i = tid + q * kMegaThreads;
-                if (i < E) s_x[i] = __fadd_rn(s_x[i], rv[q]);
-            }
-            for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_x[i] = __fadd_rn(s_x[i], __ldcg(p.xb2 + i));
-            __syncthreads();
-            norm_quant(s_x, ly.ffn_norm, s_sq, s_xn, s_nat, s_adv, E, p.eps, s_scalar);
-            build_act_image(s_nat, s_act, eb);  // kept for phase E
-            MEGA_STAMP(11);
-            for (int r = cta; r < ne; r += G) {
-                // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
-                const float *wr = ly.router + (size_t)r * E;
-                __syncthreads();
-                if (r == cta) {
-#pragma unroll
-                    for (int q = 0; q < kMegaElems; q++) {
-                        const int i = tid + q * kMegaThreads;
-                        if (i < E) s_sq[i] = __fmul_rn(wr_pre[q], s_xn[i]);
-                    }
-                    for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
-                } else {
-                    for (int i = tid; i < E; i += kMegaThreads) s_sq[i] = __fmul_rn(__ldg(wr + i), s_xn[i]);
-                }
-                __syncthreads();
-                if (tid == 0) p.logits[r] = chain_sum(s_sq, E, -0.0f);
-            }
-        }
-        MEGA_STAMP(12);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(13);
-
-        // ================= phase E: route | gate and up rows of the routed experts =================
-        for (int i = tid; i < ne; i += kMegaThreads) s_sq[i] = __ldcg(p.logits + i);
+        if (t0 == 0 && tid == 0) c.s_scalar[3] = __fdiv_rn(1.0f, chain_sum(c.s_sl, n_kv, 0.0f));
         __syncthreads();
-        if (tid < 32) route_warp(s_sq, ne, nu, s_ids, s_w);
-        __syncthreads();
-        if (cta == 0 && tid < nu) {
-            p.expert_ids[tid] = s_ids[tid];
-            p.expert_w[tid] = s_w[tid];
-            if (p.trace_ids) p.trace_ids[(size_t)il * nu + tid] = s_ids[tid];
-        }
-        auto expert_of = [&](int slot) {
-            const int ex = s_ids[slot];
-            return (ex < 0 || ex >= ne) ? 0 : ex;
-        };
-        auto map_e = [&](int row) -> RowRef {
-            const int slot = row / (2 * ffe), rem = row - slot * 2 * ffe, mat = rem / ffe, r = rem - mat * ffe;
-            return RowRef{mat ? ly.up : ly.gate, ((size_t)expert_of(slot) * ffe + r) * eb, 0, (mat ? p.e_up : p.e_gate) + (size_t)slot * ffe + r};
-        };
-        auto map_f = [&](int row) -> RowRef {
-            const int slot = row / E, r = row - slot * E;
-            return RowRef{ly.down, ((size_t)expert_of(slot) * E + r) * fb, slot - slot_lo, p.e_down + (size_t)slot * E + r};
-        };
-        mv_issue(u, have, map_e, eb, e_lo, e_hi);
-        // the down projection's rows are known too (the ids are): ask L2 for them now, they are needed a phase later;
-        // then the next layer's attention side
-        for (int seg = f_lo; seg < f_hi;) {
-            const int slot = seg / E, seg_hi = min(f_hi, (slot + 1) * E);
-            l2_prefetch_units(ly.down, ((size_t)expert_of(slot) * E + (seg - slot * E)) * fb, ((size_t)expert_of(slot) * E + (seg_hi - slot * E)) * fb);
-            seg = seg_hi;
-        }
-        MEGA_STAMP(14);
-        mv_finish(u, have, map_e, eb, e_lo, e_hi, s_act, s_adv, s_ex);  // the activation image is phase D's
-        if (il + 1 < p.n_layer) prefetch_attn_side(p.layers[il + 1]);
-        MEGA_STAMP(15);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(16);
-
-        // ================= phase F: silu(gate) * up, Q8_K, for the slots of this CTA's rows | down rows =================
-        mv_issue(u, have, map_f, fb, f_lo, f_hi);
-        if (f_hi > f_lo) {
-            const int warp = tid >> 5, lane = tid & 31, nslot = slot_hi - slot_lo + 1;
-            for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
-                const int sl_ = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
-                const size_t base = (size_t)sl_ * ffe + (size_t)b * 256 + lane * 8;
-                const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base) + 1);
-                const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base) + 1);
-                const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
-                                    silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
-                q8k_quantize_block(v, lane, s_nat + blk * 256, s_adv + blk, nullptr);
+        // out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
+        if (tid < cols) {
+            const float inv = c.s_scalar[3];
+            const float *sl = c.s_sl + t0, *tile = c.s_tile + tid;
+            int r = 0;
+            if (cnt >= 16) {
+                float pa[16], pb[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) pa[j] = __fmul_rn(__fmul_rn(sl[j], inv), tile[j * cols]);
+                for (; r + 16 <= cnt; r += 16) {
+                    const int rn = (r + 32 <= cnt) ? r + 16 : r;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) pb[j] = __fmul_rn(__fmul_rn(sl[rn + j], inv), tile[(rn + j) * cols]);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc = __fadd_rn(acc, pa[j]);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) pa[j] = pb[j];
+                }
             }
-            __syncthreads();
-            build_act_image(s_nat, s_act, nslot * fb);
-            __syncthreads();
+            for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[r], inv), tile[r * cols]));
         }
-        MEGA_STAMP(17);
-        mv_finish(u, have, map_f, fb, f_lo, f_hi, s_act, s_adv, s_ex);
-        MEGA_STAMP(18);
-        if (!grid_barrier(p, bar_target, &s_flag)) return;
-        MEGA_STAMP(19);
+        __syncthreads();
     }
+    if (tid < cols) p.attn[(size_t)h * hd + (size_t)cpart * cols + tid] = acc;
+}
+
+// ---- phase C: Q8_K of the attention output | attn_out rows ----
+__device__ __noinline__ void mega_phase_c(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const int tid = threadIdx.x, qb = c.qb;
+    auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int b = warp; b < qb; b += kMegaThreads / 32) {
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8)), c4 = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8) + 1);
+        const float v[8] = {a.x, a.y, a.z, a.w, c4.x, c4.y, c4.z, c4.w};
+        q8k_quantize_block(v, lane, c.s_nat + b * 256, c.s_adv + b, nullptr);
+    }
+    __syncthreads();
+    build_act_image(c.s_nat, c.s_act, qb);
+    __syncthreads();
+    mv_rows(map_c, qb, c.c_lo, c.c_hi, c.s_act, c.s_adv, c.s_ex);
+}
+
+// ---- phase D: x += attn_out, FFN norm, Q8_K (kept for E) | router logits ----
+__device__ __noinline__ void mega_phase_d(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const int tid = threadIdx.x, E = c.E;
+    // the router row this CTA dots (asked of L2 a layer ago) and attn_out's result, read before the norm's chain
+    float wr_pre[kMegaElems], rv[kMegaElems];
+#pragma unroll
+    for (int q = 0; q < kMegaElems; q++) {
+        const int i = tid + q * kMegaThreads;
+        rv[q] = i < E ? __ldcg(p.xb2 + i) : 0.0f;
+        wr_pre[q] = (c.cta < c.ne && i < E) ? __ldg(ly.router + (size_t)c.cta * E + i) : 0.0f;
+    }
+#pragma unroll
+    for (int q = 0; q < kMegaElems; q++) {
+        const int i = tid + q * kMegaThreads;
+        if (i < E) c.s_x[i] = __fadd_rn(c.s_x[i], rv[q]);
+    }
+    for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) c.s_x[i] = __fadd_rn(c.s_x[i], __ldcg(p.xb2 + i));
+    __syncthreads();
+    norm_quant(c.s_x, ly.ffn_norm, c.s_sq, c.s_xn, c.s_nat, c.s_adv, E, p.eps, c.s_scalar);
+    build_act_image(c.s_nat, c.s_act, c.eb);  // kept for phase E
+    for (int r = c.cta; r < c.ne; r += c.G) {
+        // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
+        const float *wr = ly.router + (size_t)r * E;
+        __syncthreads();
+        if (r == c.cta) {
+#pragma unroll
+            for (int q = 0; q < kMegaElems; q++) {
+                const int i = tid + q * kMegaThreads;
+                if (i < E) c.s_sq[i] = __fmul_rn(wr_pre[q], c.s_xn[i]);
+            }
+            for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) c.s_sq[i] = __fmul_rn(__ldg(wr + i), c.s_xn[i]);
+        } else {
+            for (int i = tid; i < E; i += kMegaThreads) c.s_sq[i] = __fmul_rn(__ldg(wr + i), c.s_xn[i]);
+        }
+        __syncthreads();
+        if (tid == 0) p.logits[r] = chain_sum(c.s_sq, E, -0.0f);
+    }
+}
+
+__device__ __forceinline__ int mega_expert_of(const MegaCtx &c, int slot) {
+    const int ex = c.s_ids[slot];
+    return (ex < 0 || ex >= c.ne) ? 0 : ex;
+}
+
+// ---- phase E: route | gate and up rows of the routed experts ----
+__device__ __noinline__ void mega_phase_e(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly, int il) {
+    const int tid = threadIdx.x, ne = c.ne, nu = c.nu, ffe = c.ffe, eb = c.eb, E = c.E, fb = c.fb;
+    for (int i = tid; i < ne; i += kMegaThreads) c.s_sq[i] = __ldcg(p.logits + i);
+    __syncthreads();
+    if (tid < 32) route_warp(c.s_sq, ne, nu, c.s_ids, c.s_w);
+    __syncthreads();
+    if (c.cta == 0 && tid < nu) {
+        p.expert_ids[tid] = c.s_ids[tid];
+        p.expert_w[tid] = c.s_w[tid];
+        if (p.trace_ids) p.trace_ids[(size_t)il * nu + tid] = c.s_ids[tid];
+    }
+    auto map_e = [&](int row) -> RowRef {
+        const int slot = row / (2 * ffe), rem = row - slot * 2 * ffe, mat = rem / ffe, r = rem - mat * ffe;
+        return RowRef{mat ? ly.up : ly.gate, ((size_t)mega_expert_of(c, slot) * ffe + r) * eb, 0, (mat ? p.e_up : p.e_gate) + (size_t)slot * ffe + r};
+    };
+    // the down projection's rows are known too (the ids are): ask L2 for them now, they are needed a phase later
+    for (int seg = c.f_lo; seg < c.f_hi;) {
+        const int slot = seg / E, seg_hi = min(c.f_hi, (slot + 1) * E);
+        const size_t row0 = (size_t)mega_expert_of(c, slot) * E;
+        l2_prefetch_units(ly.down, (row0 + (seg - slot * E)) * fb, (row0 + (seg_hi - slot * E)) * fb);
+        seg = seg_hi;
+    }
+    mv_rows(map_e, eb, c.e_lo, c.e_hi, c.s_act, c.s_adv, c.s_ex);  // the activation image is phase D's
+}
+
+// ---- phase F: silu(gate) * up, Q8_K, for the slots of this CTA's rows | down rows ----
+__device__ __noinline__ void mega_phase_f(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const int tid = threadIdx.x, ffe = c.ffe, fb = c.fb, E = c.E, slot_lo = c.slot_lo;
+    auto map_f = [&](int row) -> RowRef {
+        const int slot = row / E, r = row - slot * E;
+        return RowRef{ly.down, ((size_t)mega_expert_of(c, slot) * E + r) * fb, slot - slot_lo, p.e_down + (size_t)slot * E + r};
+    };
+    if (c.f_hi > c.f_lo) {
+        const int warp = tid >> 5, lane = tid & 31, nslot = c.slot_hi - slot_lo + 1;
+        for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
+            const int sl_ = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
+            const size_t base = (size_t)sl_ * ffe + (size_t)b * 256 + lane * 8;
+            const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base) + 1);
+            const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base) + 1);
+            const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
+                                silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
+            q8k_quantize_block(v, lane, c.s_nat + blk * 256, c.s_adv + blk, nullptr);
+        }
+        __syncthreads();
+        build_act_image(c.s_nat, c.s_act, nslot * fb);
+        __syncthreads();
+    }
+    mv_rows(map_f, fb, c.f_lo, c.f_hi, c.s_act, c.s_adv, c.s_ex);
+}
+
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ MegaCtx ctx;
+    __shared__ bool s_flag;
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x;
+    if (tid == 0) {
+        MegaCtx c;
+        c.E = p.E, c.H = p.H, c.HKV = p.HKV, c.hd = p.hd, c.nu = p.nu, c.ffe = p.ffe, c.ne = p.n_expert;
+        c.qd = c.H * c.hd, c.kvd = c.HKV * c.hd, c.eb = c.E / 256, c.qb = c.qd / 256, c.fb = c.ffe / 256;
+        c.ratio = c.H / c.HKV, c.half = c.hd / 2, c.cols = c.hd / kMegaSplit;
+        const MegaSmem L = mega_smem(c.E, c.qd, c.hd, p.act_blocks, p.sl_floats, c.ne, p.ktile_rows, c.ratio);
+        c.s_x = reinterpret_cast<float *>(smem + L.x);
+        c.s_xn = reinterpret_cast<float *>(smem + L.xn);
+        c.s_sq = reinterpret_cast<float *>(smem + L.sq);
+        c.s_act = reinterpret_cast<uint32_t *>(smem + L.act);
+        c.s_nat = reinterpret_cast<int8_t *>(smem + L.nat);
+        c.s_adv = reinterpret_cast<float *>(smem + L.adv);
+        c.s_ex = reinterpret_cast<float *>(smem + L.ex);
+        c.s_sl = reinterpret_cast<float *>(smem + L.sl);
+        c.s_tile = reinterpret_cast<float *>(smem + L.tile);
+        float *s_misc = reinterpret_cast<float *>(smem + L.misc);
+        c.s_k = s_misc + c.hd, c.s_v = s_misc + 2 * c.hd, c.s_tmp = s_misc + 3 * c.hd;  // [hd] each
+        c.s_red = s_misc + 4 * c.hd;                                    // [128] reduction scratch
+        c.s_ids = reinterpret_cast<int32_t *>(c.s_red + 256);           // [64]
+        c.s_w = c.s_red + 320;                                          // [64]
+        c.s_scalar = c.s_red + 384;                                     // a few broadcast scalars
+        c.cta = cta, c.G = G, c.pos = p.meta[1], c.n_kv = c.pos + 1;
+        // row ranges of the phases (the same every layer)
+        const int rows_a = c.qd + 2 * c.kvd, rpc_a = (rows_a + G - 1) / G;
+        c.a_lo = min(cta * rpc_a, rows_a), c.a_hi = min(c.a_lo + rpc_a, rows_a);
+        const int rpc_c = (c.E + G - 1) / G;
+        c.c_lo = min(cta * rpc_c, c.E), c.c_hi = min(c.c_lo + rpc_c, c.E);
+        const int rows_e = c.nu * 2 * c.ffe, rpc_e = (rows_e + G - 1) / G;
+        c.e_lo = min(cta * rpc_e, rows_e), c.e_hi = min(c.e_lo + rpc_e, rows_e);
+        const int rows_f = c.nu * c.E, rpc_f = (rows_f + G - 1) / G;
+        c.f_lo = min(cta * rpc_f, rows_f), c.f_hi = min(c.f_lo + rpc_f, rows_f);
+        c.slot_lo = c.f_lo / c.E, c.slot_hi = c.f_hi > c.f_lo ? (c.f_hi - 1) / c.E : c.slot_lo;
+        // attention, first half: CTA -> (kv head, chunk of positions); second half: CTA -> (head, column part)
+        const int ncp = G / c.HKV;  // position chunks per kv head
+        c.b1_kvh = cta / ncp;
+        const int chunk = cta - c.b1_kvh * ncp, ppc = (c.n_kv + ncp - 1) / ncp;
+        c.t_lo = min(chunk * ppc, c.n_kv);
+        c.t_hi = c.b1_kvh < c.HKV ? min(c.t_lo + ppc, c.n_kv) : c.t_lo;
+        c.b1_has_pos = c.b1_kvh < c.HKV && c.pos >= c.t_lo && c.pos < c.t_hi;
+        ctx = c;
+    }
+    __syncthreads();
+    const int token = p.meta[0];
+    unsigned int bar_target = 0;
+    // optional phase clock: CTA 0 adds the time since the previous stamp to slot k
+    unsigned long long t_prev = 0;
+    const bool prof = p.prof && cta == 0 && tid == 0;
+    if (prof) t_prev = global_ns();
+#define MEGA_STAMP(k)                                  \
+    do {                                               \
+        if (prof) {                                    \
+            const unsigned long long t_ = global_ns(); \
+            p.prof[k] += t_ - t_prev;                  \
+            t_prev = t_;                               \
+        }                                              \
+    } while (0)
+#define MEGA_BARRIER(k)                                       \
+    do {                                                      \
+        if (!grid_barrier(p, bar_target, &s_flag)) return;    \
+        MEGA_STAMP(k);                                        \
+    } while (0)
+
+    // ---- embed: one row of token_embd, d * sc * q (crates/llamd-quant/src/lib.rs:181-226) ----
+    {
+        const int E = p.E, eb = E / 256;
+        for (int i = tid; i < E; i += kMegaThreads) {
+            const size_t unit = (size_t)token * eb + (i >> 8);
+            const int e = i & 255;
+            const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(p.tok_embd + t32_d_offset(unit)));
+            const float sc = (float)(int8_t)p.tok_embd[t32_scale_offset(unit) + (e >> 4)];
+            ctx.s_x[i] = __fmul_rn(__fmul_rn(d, sc), (float)t32_weight(p.tok_embd, unit, e));
+        }
+    }
+    mega_prefetch_attn_side(ctx, p.layers[0]);
+    __syncthreads();
+
+    for (int il = 0; il <= p.n_layer; il++) {
+        const bool tail = il == p.n_layer;  // after the last layer: combine + output norm only
+        const MegaLayer &ly = p.layers[tail ? p.n_layer - 1 : il];
+        mega_phase_a(p, ctx, ly, il, tail);
+        if (tail) break;
+        MEGA_STAMP(0);
+        MEGA_BARRIER(1);
+        mega_phase_b1(p, ctx, ly);
+        MEGA_STAMP(2);
+        MEGA_BARRIER(3);
+        mega_phase_b2(p, ctx, ly);
+        MEGA_STAMP(4);
+        MEGA_BARRIER(5);
+        mega_phase_c(p, ctx, ly);
+        MEGA_STAMP(6);
+        MEGA_BARRIER(7);
+        mega_phase_d(p, ctx, ly);
+        MEGA_STAMP(8);
+        MEGA_BARRIER(9);
+        mega_phase_e(p, ctx, ly, il);
+        if (il + 1 < p.n_layer) mega_prefetch_attn_side(ctx, p.layers[il + 1]);  // streams behind the expert weights
+        MEGA_STAMP(10);
+        MEGA_BARRIER(11);
+        mega_phase_f(p, ctx, ly);
+        MEGA_STAMP(12);
+        MEGA_BARRIER(13);
+    }
+#undef MEGA_BARRIER
 #undef MEGA_STAMP
 }
 

@@ -1491,8 +1491,7 @@ int llamd_model_ep_p2p_attach_ptrs(llamd_model *h, void *const *ptrs, int world)
     return 0;
 }
 // Nanoseconds per phase of the resident decode kernel, accumulated by its CTA 0 since "resident_profile" was set:
-// 20 slots in the kernel's order (A prologue, A rows, barrier, B1 prepare, B1 scores, barrier, B2 softmax, B2 values,
-// barrier, C, barrier, D norm, D router, barrier, E route, E rows, barrier, F activation, F rows, barrier); out32 gets 32 values.
+// 14 slots in the kernel's order (phases A, B1, B2, C, D, E, F, each followed by its barrier); out32 gets 32 values.
 int llamd_model_resident_profile(llamd_model *h, unsigned long long *out32) {
     Model *m = (Model *)h;
     if (!m || !out32 || !m->mega_prof.p) return -1;

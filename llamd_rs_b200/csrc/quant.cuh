@@ -21,9 +21,9 @@ static __constant__ uint32_t c_exp_window = 0;  // see exp_needs_lookup; 0 = loo
 // The host's expf can differ from the correctly rounded value only where exp(x) lies very close to the midpoint of
 // two neighbouring floats (its error before the final rounding is a few thousandths of an ulp). The 29 bits of the
 // double result below float precision say how close: the table is consulted only within `window` (in units of
-// 2^-29 ulp) of the midpoint, about one input in sixty. That every listed input passes this test is verified when
-// the table is built, on the device, input by input; if one did not, the window is switched off. Results that are
-// subnormal as floats round at another bit position and are always looked up.
+// 2^-29 ulp) of the midpoint. The window is measured when the table is built: the largest distance over every listed
+// input, on the device, plus one; an input outside it is therefore not in the table. Results that are subnormal as
+// floats round at another bit position and are always looked up.
 __device__ __forceinline__ bool exp_needs_lookup(float x, double yd, uint32_t window) {
     if (window == 0 || x < -87.0f) return true;
     const uint32_t frac = (uint32_t)__double_as_longlong(yd) & 0x1FFFFFFFu;

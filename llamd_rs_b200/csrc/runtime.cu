@@ -45,14 +45,15 @@ __global__ void exp_scan_kernel(uint32_t first, uint32_t n, uint32_t *__restrict
         out[i] = __float_as_uint(__double2float_rn(exp((double)__uint_as_float(first + i))));
 }
 
-// flags[i] = would ref_expf consult the table for input bits in[i], with this window?
-__global__ void exp_window_kernel(const uint32_t *__restrict__ in, uint32_t n, uint32_t window, uint32_t *__restrict__ flags) {
+// dist[i] = how far (in units of 2^-29 ulp) the double result for input bits in[i] lies from the midpoint of two
+// floats; 0 for inputs whose float result is subnormal (those are always looked up)
+__global__ void exp_window_kernel(const uint32_t *__restrict__ in, uint32_t n, uint32_t *__restrict__ dist) {
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const float x = __uint_as_float(in[i]);
-        flags[i] = exp_needs_lookup(x, exp((double)x), window) ? 1u : 0u;
+        const uint32_t frac = (uint32_t)__double_as_longlong(exp((double)x)) & 0x1FFFFFFFu;
+        dist[i] = x < -87.0f ? 0u : (frac >= 0x10000000u ? frac - 0x10000000u : 0x10000000u - frac);
     }
 }
-constexpr uint32_t kExpWindow = 1u << 22;  // 2^-7 ulp either side of a midpoint
 
 // Inputs below 2^-25 in magnitude give exactly 1.0f on both sides; above 89 both overflow to +inf, below -104 both
 // give 0. Everything in between is compared, float by float. LLAMD_EXP_TABLE=0 switches the table off.
@@ -122,28 +123,29 @@ static bool build_exp_table(cudaStream_t s) {
         cudaGetLastError();
         return false;
     }
-    // The window that spares most inputs the look-up is an observation about the host's expf, not a guarantee: check it
-    // against every listed input, on the device, and do without it if a single one falls outside.
-    uint32_t window = kExpWindow;
+    // Which inputs need the table at all? The host's expf can only differ from the correctly rounded value where the
+    // exact result lies close to the midpoint of two floats. How close is measured here, on the device, over every
+    // listed input: the window is the largest distance found plus one, so an input outside it is, by this exhaustive
+    // construction, not in the table. (Should the window come out wider than a quarter ulp, it is not worth having.)
+    uint32_t window = 0;
     if (n_exc) {
         std::vector<uint32_t> in;
         in.reserve(n_exc);
         for (auto &v : found)
             for (size_t i = 0; i < v.size(); i += 2) in.push_back(v[i]);
-        uint32_t *d_in = nullptr, *d_fl = nullptr;
-        std::vector<uint32_t> fl(n_exc, 0);
-        const bool ran = cudaMalloc(&d_in, n_exc * 4) == cudaSuccess && cudaMalloc(&d_fl, n_exc * 4) == cudaSuccess &&
-                         cudaMemcpy(d_in, in.data(), n_exc * 4, cudaMemcpyHostToDevice) == cudaSuccess;
-        if (ran) {
-            exp_window_kernel<<<148 * 4, 256, 0, s>>>(d_in, (uint32_t)n_exc, window, d_fl);
-            if (cudaMemcpyAsync(fl.data(), d_fl, n_exc * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) window = 0;
-        } else {
-            window = 0;
+        uint32_t *d_in = nullptr, *d_ds = nullptr;
+        std::vector<uint32_t> ds(n_exc, 0xFFFFFFFFu);
+        if (cudaMalloc(&d_in, n_exc * 4) == cudaSuccess && cudaMalloc(&d_ds, n_exc * 4) == cudaSuccess &&
+            cudaMemcpy(d_in, in.data(), n_exc * 4, cudaMemcpyHostToDevice) == cudaSuccess) {
+            exp_window_kernel<<<148 * 4, 256, 0, s>>>(d_in, (uint32_t)n_exc, d_ds);
+            if (cudaMemcpyAsync(ds.data(), d_ds, n_exc * 4, cudaMemcpyDeviceToHost, s) == cudaSuccess && cudaStreamSynchronize(s) == cudaSuccess) {
+                uint32_t worst = 0;
+                for (uint32_t d : ds) worst = d > worst ? d : worst;
+                if (worst < (1u << 27)) window = worst + 1;
+            }
         }
-        for (uint32_t f : fl)
-            if (!f) window = 0;
         if (d_in) cudaFree(d_in);
-        if (d_fl) cudaFree(d_fl);
+        if (d_ds) cudaFree(d_ds);
         cudaGetLastError();
     }
     g_exp_window = window;
@@ -210,9 +212,9 @@ extern "C" {
 // How many float inputs the device's exp needed correcting for to equal the host libm's expf (the size of the
 // exception table built when the stream was made); -1 when the table is switched off.
 long long llamd_cuda_exp_exceptions(void) { return stream() ? g_exp_exceptions : -1; }
-// 1 when the table is consulted only for results within 2^-7 ulp of a rounding midpoint (every listed input was
-// verified to lie there), 0 when every input is looked up.
-int llamd_cuda_exp_window_on(void) { return stream() && g_exp_window != 0 ? 1 : 0; }
+// The look-up window in units of 2^-29 ulp: the table is consulted only for results at most this close to the midpoint
+// of two floats (the largest distance measured over the listed inputs, plus one); 0 when every input is looked up.
+int llamd_cuda_exp_window_on(void) { return stream() ? (int)g_exp_window : 0; }
 
 int llamd_cuda_device_count(void) {
     int n = 0;

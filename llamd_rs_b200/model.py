@@ -304,9 +304,9 @@ class CudaModel:
         if self._L.llamd_model_ep_p2p_attach_ptrs(self._h, flat, world) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
 
-    RESIDENT_PHASES = ("A combine+norm+quant", "A qkv rows", "barrier", "B1 qk-norm rope kv-store", "B1 scores", "barrier",
-                       "B2 softmax", "B2 values", "barrier", "C quant + attn_out rows", "barrier", "D add+norm+quant", "D router",
-                       "barrier", "E route + issue", "E gate/up rows", "barrier", "F silu+quant", "F down rows", "barrier")
+    RESIDENT_PHASES = ("A combine+norm+quant, qkv rows", "barrier", "B1 qk-norm rope kv-store scores", "barrier", "B2 softmax values",
+                       "barrier", "C quant + attn_out rows", "barrier", "D add+norm+quant, router", "barrier", "E route, gate/up rows",
+                       "barrier", "F silu+quant, down rows", "barrier")
 
     def resident_profile(self) -> dict:
         """Nanoseconds per phase accumulated by the resident kernel's CTA 0 since set_option("resident_profile", 1)."""

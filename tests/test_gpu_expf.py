@@ -33,8 +33,9 @@ def test_exception_table_exists(be):
     # glibc's expf differs from the correctly rounded value on a few inputs in 100000; none at all would mean the
     # comparison did not run, millions would mean the two functions are not the same function
     assert 100 < n < 5_000_000, n
-    # the cheap test that spares most inputs the look-up was verified against every listed input at start-up
-    assert lib().llamd_cuda_exp_window_on() == 1
+    # the cheap test that spares most inputs the look-up: a window around rounding midpoints, measured over every listed
+    # input at start-up; well under a hundredth of an ulp for glibc's expf
+    assert 0 < lib().llamd_cuda_exp_window_on() < (1 << 22)
 
 
 @pytest.mark.parametrize("first", [0x33000000, 0x3F000000, 0x3F800000, 0x40A00000, 0x42AF0000, 0xB3000000, 0xBE000000, 0xC0000000, 0xC1F00000, 0xC2C00000])
