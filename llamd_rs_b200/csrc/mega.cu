@@ -324,6 +324,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
+// Phase clock, usable inside the phase functions: thread 0 of CTA 0 adds the time since the previous stamp to slot k.
+__device__ unsigned long long g_mega_t_prev;
+__device__ __forceinline__ void mega_stamp(const MegaParams &p, int k) {
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
+        const unsigned long long t = global_ns();
+        p.prof[k] += t - g_mega_t_prev;
+        g_mega_t_prev = t;
+    }
+}
+
 // What a CTA knows for the whole token: its shared-memory regions, the model's dimensions, its share of every phase.
 // One copy per CTA in shared memory; the phase functions below are separate functions (not inlined) so that each gets
 // a register allocation of its own -- inside one 2000-line kernel body at 80 registers per thread the ordered-sum loops
@@ -394,6 +404,7 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
         if (c.cta == 0 && p.trace_x)
             for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = c.s_x[i];
     }
+    mega_stamp(p, 14);
     norm_quant(c.s_x, tail ? p.output_norm : ly.attn_norm, c.s_sq, c.s_xn, c.s_nat, c.s_adv, E, p.eps, c.s_scalar);
     if (tail) {
         if (c.cta == 0) {
@@ -405,6 +416,7 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
         }
         return;
     }
+    mega_stamp(p, 15);
     auto map_a = [&](int row) -> RowRef {
         if (row < qd) return RowRef{ly.attn_q, (size_t)row * eb, 0, p.q + row};
         if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
@@ -631,6 +643,7 @@ __device__ __noinline__ void mega_phase_d(const MegaParams &p, const MegaCtx &c,
     __syncthreads();
     norm_quant(c.s_x, ly.ffn_norm, c.s_sq, c.s_xn, c.s_nat, c.s_adv, E, p.eps, c.s_scalar);
     build_act_image(c.s_nat, c.s_act, c.eb);  // kept for phase E
+    mega_stamp(p, 17);
     for (int r = c.cta; r < c.ne; r += c.G) {
         // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
         const float *wr = ly.router + (size_t)r * E;
@@ -660,8 +673,10 @@ __device__ __noinline__ void mega_phase_e(const MegaParams &p, const MegaCtx &c,
     const int tid = threadIdx.x, ne = c.ne, nu = c.nu, ffe = c.ffe, eb = c.eb, E = c.E, fb = c.fb;
     for (int i = tid; i < ne; i += kMegaThreads) c.s_sq[i] = __ldcg(p.logits + i);
     __syncthreads();
+    mega_stamp(p, 18);
     if (tid < 32) route_warp(c.s_sq, ne, nu, c.s_ids, c.s_w);
     __syncthreads();
+    mega_stamp(p, 19);
     if (c.cta == 0 && tid < nu) {
         p.expert_ids[tid] = c.s_ids[tid];
         p.expert_w[tid] = c.s_w[tid];
@@ -678,6 +693,7 @@ __device__ __noinline__ void mega_phase_e(const MegaParams &p, const MegaCtx &c,
         l2_prefetch_units(ly.down, (row0 + (seg - slot * E)) * fb, (row0 + (seg_hi - slot * E)) * fb);
         seg = seg_hi;
     }
+    mega_stamp(p, 20);
     mv_rows(map_e, eb, c.e_lo, c.e_hi, c.s_act, c.s_adv, c.s_ex);  // the activation image is phase D's
 }
 
@@ -703,6 +719,7 @@ __device__ __noinline__ void mega_phase_f(const MegaParams &p, const MegaCtx &c,
         build_act_image(c.s_nat, c.s_act, nslot * fb);
         __syncthreads();
     }
+    mega_stamp(p, 21);
     mv_rows(map_f, fb, c.f_lo, c.f_hi, c.s_act, c.s_adv, c.s_ex);
 }
 
@@ -755,18 +772,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     __syncthreads();
     const int token = p.meta[0];
     unsigned int bar_target = 0;
-    // optional phase clock: CTA 0 adds the time since the previous stamp to slot k
-    unsigned long long t_prev = 0;
-    const bool prof = p.prof && cta == 0 && tid == 0;
-    if (prof) t_prev = global_ns();
-#define MEGA_STAMP(k)                                  \
-    do {                                               \
-        if (prof) {                                    \
-            const unsigned long long t_ = global_ns(); \
-            p.prof[k] += t_ - t_prev;                  \
-            t_prev = t_;                               \
-        }                                              \
-    } while (0)
+    if (p.prof && cta == 0 && tid == 0) g_mega_t_prev = global_ns();
+#define MEGA_STAMP(k) mega_stamp(p, k)
 #define MEGA_BARRIER(k)                                       \
     do {                                                      \
         if (!grid_barrier(p, bar_target, &s_flag)) return;    \

@@ -304,9 +304,10 @@ class CudaModel:
         if self._L.llamd_model_ep_p2p_attach_ptrs(self._h, flat, world) != 0:
             raise backend.Other("ep_p2p attach: " + (self._err() or backend._last_error()))
 
-    RESIDENT_PHASES = ("A combine+norm+quant, qkv rows", "barrier", "B1 qk-norm rope kv-store scores", "barrier", "B2 softmax values",
-                       "barrier", "C quant + attn_out rows", "barrier", "D add+norm+quant, router", "barrier", "E route, gate/up rows",
-                       "barrier", "F silu+quant, down rows", "barrier")
+    RESIDENT_PHASES = ("A image + qkv rows", "barrier", "B1 qk-norm rope kv-store scores", "barrier", "B2 softmax values",
+                       "barrier", "C quant + attn_out rows", "barrier", "D router", "barrier", "E gate/up rows",
+                       "barrier", "F down rows", "barrier", "A combine", "A norm + quant", "-", "D add + norm + quant + image",
+                       "E logits load", "E route", "E prefetch of down rows", "F silu + quant + image")
 
     def resident_profile(self) -> dict:
         """Nanoseconds per phase accumulated by the resident kernel's CTA 0 since set_option("resident_profile", 1)."""
