@@ -206,6 +206,18 @@ def data_plane_text(args):
             "peer stores + system-scope arrival counters over NVLink per layer, NCCL for set-up only")
 
 
+def measured_peaks():
+    """(HBM GB/s, where it came from, the file's content): the pool's measured copy bandwidth when the file is there, else the
+    stated fallback."""
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        peaks = {}
+    if "hbm_gbs" in peaks:
+        return float(peaks["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)", peaks
+    return 6650.0, "fallback 6650", peaks
+
+
 def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
     """Prompt throughput: K passes of the tiled prefill over the same prompt from position 0 (pp<prompt>)."""
     import ctypes as C
@@ -238,7 +250,11 @@ def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms.value, wall = float(t[0]), float(t[1])
     n = len(prompt)
-    wbytes = 48 * (15482880 + 128 * 3 * 1290240)  # a 512-token tile touches every expert of every layer
+    wbytes = hp["n_layer"] * (15482880 + 128 * 3 * 1290240)  # a 512-token tile touches every expert of every layer
+    peak, peak_src, peaks = measured_peaks()
+    # the matmuls of one pass as multiply-adds: per token and layer QKV + attn_out + 8 experts x (gate, up, down)
+    macs = n * hp["n_layer"] * (2048 * 5120 + 4096 * 2048 + 8 * 3 * 768 * 2048)
+    tops = 2.0 * macs / (ms.value / K * 1e-3) / 1e12
     line = {"metric": "q6k_moe_prefill_tok_s", "value": world * n * K / (ms.value * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms.value / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 pairs -> f32 (tcgen05, tolerance level)" if args.gemm == "tc" else "i8xi8->i32, f32 tail", "data": "synthetic",
@@ -246,9 +262,12 @@ def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
                        "l2": "a tile streams every expert of every layer (23.8 GB): inputs larger than L2"},
             "e2e": {"value": world * n * K / wall, "unit": "tok/s", "h2d_bytes_per_step": 8 * n, "d2h_bytes_per_step": 4},
             "gpu_launches": int(L.llamd_fwd_launch_count() - launches0), "last_token": int(tok),
-            "roofline": {"bound": "hbm", "achieved": wbytes / (ms.value / K * 1e-3) / 1e9, "peak": 6541.5, "unit": "GB/s",
-                         "frac": wbytes / (ms.value / K * 1e-3) / 1e9 / 6541.5, "traffic": None,
-                         "note": "weight bytes of one pass / pass time; the pass is bound by the integer pipe, not HBM"}}
+            "roofline": {"bound": "hbm", "achieved": wbytes / (ms.value / K * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": wbytes / (ms.value / K * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                         "matmul_tops": tops, "matmul_frac_of_bf16_peak": tops / float(peaks.get("bf16_tflops_sustained", 1400.0)),
+                         "note": "weight bytes of one pass / pass time against the copy peak; matmul_tops = 2 x multiply-adds of the "
+                                 "pass's matmuls / pass time, against the measured sustained bf16 GEMM rate for scale (the exact path "
+                                 "runs integer MMAs and is bound by folding Q6_K blocks into operands on the CUDA cores)"}}
     if rank == 0:
         print(json.dumps(line), flush=True)
     m.free()
@@ -427,6 +446,9 @@ def main():
             pos += 1
         backend.sync()
         prof = m.resident_profile()
+        raw = m.resident_profile_raw()
+        if raw[31]:
+            log(f"[resident] SM clock inside the kernel: {raw[30]} cycles / {raw[31]} ns = {raw[30] / raw[31] * 1e3:.0f} MHz")
         tot = sum(prof.values())
         for k, v in prof.items():
             log(f"[resident] {k:28s} {v / n / 1e3:9.1f} us/token {v / n / hp['n_layer'] / 1e3:7.2f} us/layer {100 * v / max(tot, 1):5.1f} %")
@@ -498,13 +520,7 @@ def main():
     else:
         mv_ms, mv_launches = m.bench_matvecs(iters)
     achieved = (wbytes + iobytes) / (mv_ms / iters * 1e-3) / 1e9
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
-    peak = float(peaks.get("hbm_gbs", 6650.0))
-    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650"
+    peak, peak_src, _ = measured_peaks()
 
     # what was decoded, so that a run can be checked against the CPU path's tokens for the same inputs
     decoded = [int(first_tok)] + [int(t) for t in warm_tokens] + [int(t) for t in e2e_tokens] + [int(t) for t in toks]

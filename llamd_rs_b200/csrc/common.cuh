@@ -222,28 +222,46 @@ __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
     return __half2float(__ushort_as_half(h));
 }
 
-// Left-to-right f32 sum of n values in shared memory, starting from `acc`:
-// acc = (...((acc + s[0]) + s[1]) + ...). The adds form one dependent chain, so
-// the loop is software-pipelined (the next 16 values are fetched while the
-// current 16 are added) to run at the latency of a dependent add.
-// s must be 16-byte aligned.
-__device__ __forceinline__ float chain_sum(const float *__restrict__ s, int n, float acc) {
-    const float4 *p = reinterpret_cast<const float4 *>(s);
+// Left-to-right f32 sum of n values in SHARED memory, starting from `acc`:
+// acc = (...((acc + s[0]) + s[1]) + ...). The adds form one dependent chain, so the loop is software-pipelined to run
+// at the latency of a dependent add (~4.3 cycles, measured): two register sets of 16 values alternate, and a set is
+// re-loaded right after it has been added, so that its load latency hides behind the other set's 16 adds. The loads are
+// written as ld.shared: through a pointer whose address space the compiler cannot see they become generic loads, whose
+// longer latency no longer hides (6.3 cycles per add, measured inside the resident decode kernel). A function of its
+// own, so that every caller gets this schedule. s must be 16-byte aligned.
+__device__ __forceinline__ float4 chain_lds(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+#define LLAMD_CHAIN_ADD16(q0, q1, q2, q3)                                                                              \
+    acc = __fadd_rn(acc, q0.x); acc = __fadd_rn(acc, q0.y); acc = __fadd_rn(acc, q0.z); acc = __fadd_rn(acc, q0.w);     \
+    acc = __fadd_rn(acc, q1.x); acc = __fadd_rn(acc, q1.y); acc = __fadd_rn(acc, q1.z); acc = __fadd_rn(acc, q1.w);     \
+    acc = __fadd_rn(acc, q2.x); acc = __fadd_rn(acc, q2.y); acc = __fadd_rn(acc, q2.z); acc = __fadd_rn(acc, q2.w);     \
+    acc = __fadd_rn(acc, q3.x); acc = __fadd_rn(acc, q3.y); acc = __fadd_rn(acc, q3.z); acc = __fadd_rn(acc, q3.w)
+static __device__ __noinline__ float chain_sum(const float *s, int n, float acc) {
+    const uint32_t p = (uint32_t)__cvta_generic_to_shared(s);
     const int nblk = n / 16;
-    if (nblk > 0) {
-        float4 a = p[0], b = p[1], c = p[2], d = p[3];
-        for (int i = 0; i < nblk; i++) {
-            const int j = (i + 1 < nblk) ? (i + 1) : i;
-            const float4 na = p[4 * j], nb = p[4 * j + 1], nc = p[4 * j + 2], nd = p[4 * j + 3];
-            acc = __fadd_rn(acc, a.x); acc = __fadd_rn(acc, a.y); acc = __fadd_rn(acc, a.z); acc = __fadd_rn(acc, a.w);
-            acc = __fadd_rn(acc, b.x); acc = __fadd_rn(acc, b.y); acc = __fadd_rn(acc, b.z); acc = __fadd_rn(acc, b.w);
-            acc = __fadd_rn(acc, c.x); acc = __fadd_rn(acc, c.y); acc = __fadd_rn(acc, c.z); acc = __fadd_rn(acc, c.w);
-            acc = __fadd_rn(acc, d.x); acc = __fadd_rn(acc, d.y); acc = __fadd_rn(acc, d.z); acc = __fadd_rn(acc, d.w);
-            a = na; b = nb; c = nc; d = nd;
+    int i = 0;
+    if (nblk >= 2) {
+        float4 a0 = chain_lds(p), a1 = chain_lds(p + 16), a2 = chain_lds(p + 32), a3 = chain_lds(p + 48);
+        float4 b0 = chain_lds(p + 64), b1 = chain_lds(p + 80), b2 = chain_lds(p + 96), b3 = chain_lds(p + 112);
+        for (; i + 2 <= nblk; i += 2) {
+            LLAMD_CHAIN_ADD16(a0, a1, a2, a3);
+            const uint32_t ja = p + 64u * (uint32_t)min(i + 2, nblk - 1);  // (past the end: a harmless re-load of the last block)
+            a0 = chain_lds(ja), a1 = chain_lds(ja + 16), a2 = chain_lds(ja + 32), a3 = chain_lds(ja + 48);
+            LLAMD_CHAIN_ADD16(b0, b1, b2, b3);
+            const uint32_t jb = p + 64u * (uint32_t)min(i + 3, nblk - 1);
+            b0 = chain_lds(jb), b1 = chain_lds(jb + 16), b2 = chain_lds(jb + 32), b3 = chain_lds(jb + 48);
+        }
+        if (i < nblk) {  // an odd count: the last block is the one set `a` was re-loaded with
+            LLAMD_CHAIN_ADD16(a0, a1, a2, a3);
+            i++;
         }
     }
-    for (int i = nblk * 16; i < n; i++) acc = __fadd_rn(acc, s[i]);
+    for (int k = i * 16; k < n; k++) acc = __fadd_rn(acc, s[k]);
     return acc;
 }
+#undef LLAMD_CHAIN_ADD16
 
 }  // namespace llamd

@@ -214,11 +214,10 @@ __device__ __forceinline__ void mv_rows(const RowMap &map, int nb, int row_lo, i
 // hold blocks [unit_lo, unit_hi) of a tiled Q6_K matrix; a phase's rows [lo, hi) as far as they fall into the matrix
 // that holds virtual rows [first, first + rows).
 __device__ __forceinline__ void l2_prefetch_bytes(const uint8_t *base, size_t bytes) {
-    constexpr size_t kPiece = 8192;
-    for (size_t off = (size_t)threadIdx.x * kPiece; off < bytes; off += (size_t)kMegaThreads * kPiece) {
-        const size_t n = (bytes - off < kPiece ? bytes - off : kPiece) & ~(size_t)15;
-        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"((uint32_t)n) : "memory");
-    }
+    // one 128-byte line per instruction, the CTA's threads striding over the range: a hint that costs the issuing thread
+    // nothing (the bulk form, cp.async.bulk.prefetch.L2, held its issuing thread for ~1 us per instruction)
+    for (size_t off = (size_t)threadIdx.x * 128; off < bytes; off += (size_t)kMegaThreads * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
 }
 __device__ __forceinline__ void l2_prefetch_units(const uint8_t *w, size_t unit_lo, size_t unit_hi) {
     if (unit_hi <= unit_lo) return;
@@ -235,8 +234,9 @@ constexpr int kMegaElems = 4;  // elements of an n_embd-long vector per thread p
 // rms norm of s_x (n floats): squares by all threads, the ordered sum by thread 0, out = (x * scale) * w into s_out,
 // then Q8_K of s_out into s_nat / s_adv (n / 256 blocks). crates/llamd-cpu/src/lib.rs:55-75, dot.rs:88-128.
 // The weight vector is read before the chain is walked, so that its latency is hidden behind it.
+template <class Stamp>
 __device__ __forceinline__ void norm_quant(const float *s_x, const float *__restrict__ w, float *s_sq, float *s_out, int8_t *s_nat, float *s_adv,
-                                           int n, float eps, float *s_scalar) {
+                                           int n, float eps, float *s_scalar, const Stamp &stamp) {
     const int tid = threadIdx.x;
     float wv[kMegaElems];
 #pragma unroll
@@ -246,11 +246,13 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
     }
     for (int i = tid; i < n; i += kMegaThreads) s_sq[i] = __fmul_rn(s_x[i], s_x[i]);
     __syncthreads();
+    stamp(0);
     if (tid == 0) {
         const float sum = chain_sum(s_sq, n, 0.0f);
         *s_scalar = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
     }
     __syncthreads();
+    stamp(1);
     const float scale = *s_scalar;
 #pragma unroll
     for (int u = 0; u < kMegaElems; u++) {
@@ -259,6 +261,7 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
     }
     for (int i = tid + kMegaElems * kMegaThreads; i < n; i += kMegaThreads) s_out[i] = __fmul_rn(__fmul_rn(s_x[i], scale), __ldg(w + i));
     __syncthreads();
+    stamp(2);
     const int warp = tid >> 5, lane = tid & 31;
     for (int b = warp; b < n / 256; b += kMegaThreads / 32) {
         const float4 a = reinterpret_cast<const float4 *>(s_out + b * 256 + lane * 8)[0], c = reinterpret_cast<const float4 *>(s_out + b * 256 + lane * 8)[1];
@@ -268,54 +271,65 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
     __syncthreads();
 }
 
-// route (crates/llamd-models/src/moe.rs:73-113) by ONE warp: the same operations as route_block -- max, exp(l - max),
-// the sum walked in index order from -0.0, p / sum, n_used rounds of (probability descending, index ascending), the
-// chosen weights summed in choice order from -0.0, the 2^-14 floor, the division -- with the arg-max rounds done by
-// shuffles instead of block-wide barriers. s_p: logits in, probabilities out (taken ones marked -1). Call with warp 0.
-__device__ __forceinline__ void route_warp(float *s_p, int n_expert, int n_used, int32_t *ids, float *weights) {
-    const int lane = threadIdx.x & 31;
+// route (crates/llamd-models/src/moe.rs:73-113), called by the whole CTA: the same operations as route_block -- max,
+// exp(l - max), the sum walked in index order from -0.0, p / sum, n_used rounds of (probability descending, index
+// ascending), the chosen weights summed in choice order from -0.0, the 2^-14 floor, the division. The exponentials are
+// spread over the CTA's threads; the selection runs in warp 0 with the probabilities in registers (8 per lane: n_expert
+// <= 256) and shuffles, no shared memory and no barrier inside a round. s_p: logits in (overwritten). s_red: 40 floats.
+constexpr int kRoutePerLane = 8;
+__device__ __forceinline__ void route_cta(float *s_p, int n_expert, int n_used, int32_t *ids, float *weights, float *s_red) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float m = -INFINITY;
-    for (int i = lane; i < n_expert; i += 32) m = fmaxf(m, s_p[i]);
+    for (int i = tid; i < n_expert; i += kMegaThreads) m = fmaxf(m, s_p[i]);
     for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-    for (int i = lane; i < n_expert; i += 32) s_p[i] = ref_expf(__fsub_rn(s_p[i], m));
-    __syncwarp();
-    float total = 0.0f;
-    if (lane == 0) total = chain_sum(s_p, n_expert, -0.0f);
-    total = __shfl_sync(0xffffffffu, total, 0);
-    for (int i = lane; i < n_expert; i += 32) s_p[i] = __fdiv_rn(s_p[i], total);
-    __syncwarp();
-    for (int k = 0; k < n_used; k++) {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int i = lane; i < n_expert; i += 32) {
-            const float v = s_p[i];
-            if (v > bv || (v == bv && i < bi)) {
-                bv = v;
-                bi = i;
-            }
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    m = s_red[0];
+    for (int w = 1; w < kMegaThreads / 32; w++) m = fmaxf(m, s_red[w]);
+    for (int i = tid; i < n_expert; i += kMegaThreads) s_p[i] = ref_expf(__fsub_rn(s_p[i], m));
+    __syncthreads();
+    if (tid == 0) s_red[32] = chain_sum(s_p, n_expert, -0.0f);
+    __syncthreads();
+    if (warp == 0) {
+        const float total = s_red[32];
+        float v[kRoutePerLane];
+#pragma unroll
+        for (int j = 0; j < kRoutePerLane; j++) {
+            const int i = lane + 32 * j;
+            v[j] = i < n_expert ? __fdiv_rn(s_p[i], total) : -2.0f;  // (probabilities are >= 0; taken ones become -1)
         }
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (ov > bv || (ov == bv && oi < bi)) {
-                bv = ov;
-                bi = oi;
+        float wsum = -0.0f;
+        for (int k = 0; k < n_used; k++) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < kRoutePerLane; j++)
+                if (v[j] > bv) {  // (a lane's indices ascend with j: a strict test keeps the lowest)
+                    bv = v[j];
+                    bi = lane + 32 * j;
+                }
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+                if (ov > bv || (ov == bv && oi < bi)) {
+                    bv = ov;
+                    bi = oi;
+                }
             }
-        }
-        if (lane == 0) {
-            ids[k] = bi;
-            weights[k] = bv;
-            s_p[bi] = -1.0f;  // taken: cannot win again
+#pragma unroll
+            for (int j = 0; j < kRoutePerLane; j++)
+                if (bi == lane + 32 * j) v[j] = -1.0f;  // taken: cannot win again
+            wsum = __fadd_rn(wsum, bv);                 // (every lane walks the same sum, in choice order)
+            if (lane == 0) {
+                ids[k] = bi;
+                weights[k] = bv;  // raw; divided below, once the sum is known
+            }
         }
         __syncwarp();
+        wsum = fmaxf(wsum, WEIGHT_SUM_FLOOR);
+        for (int k = lane; k < n_used; k += 32) weights[k] = __fdiv_rn(weights[k], wsum);
     }
-    if (lane == 0) {
-        float sum = -0.0f;
-        for (int k = 0; k < n_used; k++) sum = __fadd_rn(sum, weights[k]);
-        sum = fmaxf(sum, WEIGHT_SUM_FLOOR);
-        for (int k = 0; k < n_used; k++) weights[k] = __fdiv_rn(weights[k], sum);
-    }
-    __syncwarp();
+    __syncthreads();
 }
 
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -325,12 +339,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Phase clock, usable inside the phase functions: thread 0 of CTA 0 adds the time since the previous stamp to slot k.
-__device__ unsigned long long g_mega_t_prev;
+// The sums and the previous stamp live in shared memory (a stamp costs a few dozen cycles; kept in global memory each one
+// put a ~1 us read-modify-write into the interval after it) and go to p.prof when the kernel ends.
+__shared__ unsigned long long s_mega_prof[33];  // [32]: the previous stamp
 __device__ __forceinline__ void mega_stamp(const MegaParams &p, int k) {
     if (p.prof && blockIdx.x == 0 && threadIdx.x == 0) {
         const unsigned long long t = global_ns();
-        p.prof[k] += t - g_mega_t_prev;
-        g_mega_t_prev = t;
+        s_mega_prof[k] += t - s_mega_prof[32];
+        s_mega_prof[32] = t;
     }
 }
 
@@ -339,14 +355,40 @@ __device__ __forceinline__ void mega_stamp(const MegaParams &p, int k) {
 // a register allocation of its own -- inside one 2000-line kernel body at 80 registers per thread the ordered-sum loops
 // and the attention loops were spilling.
 struct MegaCtx {
-    float *s_x, *s_xn, *s_sq, *s_adv, *s_ex, *s_sl, *s_tile, *s_k, *s_v, *s_tmp, *s_red, *s_w, *s_scalar;
-    uint32_t *s_act;
-    int8_t *s_nat;
-    int32_t *s_ids;
+    uint32_t o_x, o_xn, o_sq, o_act, o_nat, o_adv, o_ex, o_sl, o_tile, o_misc;  // byte offsets into the dynamic shared memory
     int E, H, HKV, hd, nu, ffe, ne, qd, kvd, eb, qb, fb;
     int cta, G, pos, n_kv;
     int a_lo, a_hi, c_lo, c_hi, e_lo, e_hi, f_lo, f_hi, slot_lo, slot_hi;
     int ratio, half, cols, b1_kvh, t_lo, t_hi, b1_has_pos;
+};
+
+// The CTA's shared-memory regions as typed pointers. Built from the `extern __shared__` base inside every phase function
+// (not stored in MegaCtx): a pointer read back from memory is a generic pointer to the compiler, every access through it
+// a generic load or store, and the ordered sums then walk at the generic path's latency (measured: 6.3 cycles per add
+// instead of 4.3).
+struct MegaPtrs {
+    float *s_x, *s_xn, *s_sq, *s_adv, *s_ex, *s_sl, *s_tile, *s_k, *s_v, *s_tmp, *s_red, *s_w, *s_scalar;
+    uint32_t *s_act;
+    int8_t *s_nat;
+    int32_t *s_ids;
+    __device__ __forceinline__ explicit MegaPtrs(const MegaCtx &c) {
+        extern __shared__ __align__(16) uint8_t smem[];
+        s_x = reinterpret_cast<float *>(smem + c.o_x);
+        s_xn = reinterpret_cast<float *>(smem + c.o_xn);
+        s_sq = reinterpret_cast<float *>(smem + c.o_sq);
+        s_act = reinterpret_cast<uint32_t *>(smem + c.o_act);
+        s_nat = reinterpret_cast<int8_t *>(smem + c.o_nat);
+        s_adv = reinterpret_cast<float *>(smem + c.o_adv);
+        s_ex = reinterpret_cast<float *>(smem + c.o_ex);
+        s_sl = reinterpret_cast<float *>(smem + c.o_sl);
+        s_tile = reinterpret_cast<float *>(smem + c.o_tile);
+        float *s_misc = reinterpret_cast<float *>(smem + c.o_misc);
+        s_k = s_misc + c.hd, s_v = s_misc + 2 * c.hd, s_tmp = s_misc + 3 * c.hd;  // [hd] each
+        s_red = s_misc + 4 * c.hd;                                          // [128] reduction scratch
+        s_ids = reinterpret_cast<int32_t *>(s_red + 256);                   // [64]
+        s_w = s_red + 320;                                                  // [64]
+        s_scalar = s_red + 384;                                             // a few broadcast scalars
+    }
 };
 
 __device__ __noinline__ void mega_prefetch_attn_side(const MegaCtx &c, const MegaLayer &w) {
@@ -359,6 +401,7 @@ __device__ __noinline__ void mega_prefetch_attn_side(const MegaCtx &c, const Meg
 
 // ---- phase A: (combine) + norm + Q8_K | Q, K, V rows. Returns after the tail's output when `tail`. ----
 __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly, int il, bool tail) {
+    const MegaPtrs S(c);
     const int tid = threadIdx.x, E = c.E, nu = c.nu, eb = c.eb, qd = c.qd, kvd = c.kvd;
     if (!tail && c.n_kv > 1) {
         // this layer's cached K and V rows (evicted since the last token): every CTA asks L2 for a slice of each
@@ -389,7 +432,7 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
 #pragma unroll
                 for (int e = 0; e < 8; e++)
                     if (e0 + e < nu) {
-                        const float we = c.s_w[e0 + e];
+                        const float we = S.s_w[e0 + e];
 #pragma unroll
                         for (int q = 0; q < kMegaElems; q++) acc[q] = __fadd_rn(acc[q], __fmul_rn(we, dv[e][q]));
                     }
@@ -397,22 +440,22 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
 #pragma unroll
             for (int q = 0; q < kMegaElems; q++) {
                 const int i = base + tid + q * kMegaThreads;
-                if (i < E) c.s_x[i] = __fadd_rn(c.s_x[i], acc[q]);
+                if (i < E) S.s_x[i] = __fadd_rn(S.s_x[i], acc[q]);
             }
         }
         __syncthreads();
         if (c.cta == 0 && p.trace_x)
-            for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = c.s_x[i];
+            for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = S.s_x[i];
     }
     mega_stamp(p, 14);
-    norm_quant(c.s_x, tail ? p.output_norm : ly.attn_norm, c.s_sq, c.s_xn, c.s_nat, c.s_adv, E, p.eps, c.s_scalar);
+    norm_quant(S.s_x, tail ? p.output_norm : ly.attn_norm, S.s_sq, S.s_xn, S.s_nat, S.s_adv, E, p.eps, S.s_scalar, [&](int k) { mega_stamp(p, 22 + k); });
     if (tail) {
         if (c.cta == 0) {
             for (int i = tid; i < E; i += kMegaThreads) {
-                p.x_out[i] = c.s_x[i];
-                p.aq_out[i] = c.s_nat[i];
+                p.x_out[i] = S.s_x[i];
+                p.aq_out[i] = S.s_nat[i];
             }
-            if (tid < eb) p.ad_out[tid] = c.s_adv[tid];
+            if (tid < eb) p.ad_out[tid] = S.s_adv[tid];
         }
         return;
     }
@@ -422,16 +465,17 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
         if (row < qd + kvd) return RowRef{ly.attn_k, (size_t)(row - qd) * eb, 0, p.k + (row - qd)};
         return RowRef{ly.attn_v, (size_t)(row - qd - kvd) * eb, 0, p.v + (row - qd - kvd)};
     };
-    build_act_image(c.s_nat, c.s_act, eb);
+    build_act_image(S.s_nat, S.s_act, eb);
     __syncthreads();
-    mv_rows(map_a, eb, c.a_lo, c.a_hi, c.s_act, c.s_adv, c.s_ex);
+    mv_rows(map_a, eb, c.a_lo, c.a_hi, S.s_act, S.s_adv, S.s_ex);
 }
 
 // ---- phase B1: QK-norm, RoPE, KV store, scores of (kv head, chunk of positions) ----
 __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const MegaPtrs S(c);
     if (!(c.b1_kvh < c.HKV && c.t_hi > c.t_lo)) return;
     const int tid = threadIdx.x, hd = c.hd, ratio = c.ratio, half = c.half, kvd = c.kvd, pos = c.pos, t_lo = c.t_lo;
-    float *s_qraw = c.s_tile, *s_qr = c.s_tile + ratio * hd, *s_kt = c.s_tile + 2 * ratio * hd;  // [ratio][hd] x2, [chunk][hd + 4]
+    float *s_qraw = S.s_tile, *s_qr = S.s_tile + ratio * hd, *s_kt = S.s_tile + 2 * ratio * hd;  // [ratio][hd] x2, [chunk][hd + 4]
     const int stride = hd + 4, hd4 = hd / 4, cnt = c.t_hi - t_lo;
     const float *kb = ly.kc + (size_t)c.b1_kvh * hd;
     // the chunk's cached K rows start their trip first (the row of this very position is made below)
@@ -448,8 +492,8 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
         if (i0 == 0) {  // the group's q heads and this token's k, v head, raw
             for (int i = tid; i < ratio * hd; i += kMegaThreads) s_qraw[i] = __ldcg(p.q + (size_t)c.b1_kvh * ratio * hd + i);
             for (int i = tid; i < hd; i += kMegaThreads) {
-                c.s_k[i] = __ldcg(p.k + (size_t)c.b1_kvh * hd + i);
-                c.s_v[i] = __ldcg(p.v + (size_t)c.b1_kvh * hd + i);
+                S.s_k[i] = __ldcg(p.k + (size_t)c.b1_kvh * hd + i);
+                S.s_v[i] = __ldcg(p.v + (size_t)c.b1_kvh * hd + i);
             }
         }
 #pragma unroll
@@ -465,7 +509,7 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
     // per-head norm (layer.rs:62-79): each sum of squares walked in order by its own thread
     if ((tid & 31) == 0 && (tid >> 5) <= ratio) {
         const int j = tid >> 5;  // 0..ratio-1: q heads, ratio: the k head
-        const float *sx = j < ratio ? s_qraw + j * hd : c.s_k;
+        const float *sx = j < ratio ? s_qraw + j * hd : S.s_k;
         const float *w = j < ratio ? ly.q_norm : ly.k_norm;
         float scale = 1.0f;
         if (w) {
@@ -474,16 +518,16 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
             for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
             scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), p.eps)));
         }
-        c.s_scalar[8 + j] = scale;
+        S.s_scalar[8 + j] = scale;
     }
     __syncthreads();
     // NeoX RoPE on (i, i + half) pairs, angles from the host-built table
     for (int idx = tid; idx < (ratio + 1) * half; idx += kMegaThreads) {
         const int j = idx / half, i = idx - j * half;
         const bool is_k = j == ratio;
-        const float *sx = is_k ? c.s_k : s_qraw + j * hd;
+        const float *sx = is_k ? S.s_k : s_qraw + j * hd;
         const float *w = is_k ? ly.k_norm : ly.q_norm;
-        const float scale = c.s_scalar[8 + j];
+        const float scale = S.s_scalar[8 + j];
         float a = sx[i], b = sx[i + half];
         if (w) {
             a = __fmul_rn(__fmul_rn(a, scale), __ldg(w + i));
@@ -492,16 +536,16 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
         const float2 sc = *reinterpret_cast<const float2 *>(p.rope_tab + ((size_t)pos * half + i) * 2);
         const float o0 = __fsub_rn(__fmul_rn(a, sc.y), __fmul_rn(b, sc.x));
         const float o1 = __fadd_rn(__fmul_rn(a, sc.x), __fmul_rn(b, sc.y));
-        float *dst = is_k ? c.s_tmp : s_qr + j * hd;
+        float *dst = is_k ? S.s_tmp : s_qr + j * hd;
         dst[i] = o0;
         dst[i + half] = o1;
     }
     __syncthreads();
     if (c.b1_has_pos) {  // this position's K (roped) and V go into the cache and into the chunk
         for (int i = tid; i < hd; i += kMegaThreads) {
-            ly.kc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = c.s_tmp[i];
-            ly.vc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = c.s_v[i];
-            s_kt[(pos - t_lo) * stride + i] = c.s_tmp[i];
+            ly.kc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = S.s_tmp[i];
+            ly.vc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = S.s_v[i];
+            s_kt[(pos - t_lo) * stride + i] = S.s_tmp[i];
         }
         __syncthreads();
     }
@@ -537,6 +581,7 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
 
 // ---- phase B2: softmax and weighted values of (head, column part) ----
 __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const MegaPtrs S(c);
     if (c.cta >= c.H * kMegaSplit) return;
     const int tid = threadIdx.x, hd = c.hd, cols = c.cols, kvd = c.kvd, n_kv = c.n_kv, pos = c.pos;
     const int h = c.cta / kMegaSplit, cpart = c.cta - h * kMegaSplit, kvh = h / c.ratio;
@@ -563,28 +608,28 @@ __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c
             float lmax = -INFINITY;
             for (int t = tid; t < n_kv; t += kMegaThreads) {
                 const float l = __ldcg(p.scores + (size_t)h * p.max_kv + t);
-                c.s_sl[t] = l;
+                S.s_sl[t] = l;
                 lmax = fmaxf(lmax, l);
             }
             for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
-            if ((tid & 31) == 0) c.s_red[tid >> 5] = lmax;
+            if ((tid & 31) == 0) S.s_red[tid >> 5] = lmax;
             __syncthreads();
-            lmax = c.s_red[0];
-            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, c.s_red[w]);
-            for (int t = tid; t < n_kv; t += kMegaThreads) c.s_sl[t] = ref_expf(__fsub_rn(c.s_sl[t], lmax));
+            lmax = S.s_red[0];
+            for (int w = 1; w < kMegaThreads / 32; w++) lmax = fmaxf(lmax, S.s_red[w]);
+            for (int t = tid; t < n_kv; t += kMegaThreads) S.s_sl[t] = ref_expf(__fsub_rn(S.s_sl[t], lmax));
         }
         __syncthreads();  // (the exponentials are in place; a previous V tile is dead)
 #pragma unroll
         for (int j = 0; j < kLd; j++) {
             const int idx = tid + j * kMegaThreads;
-            if (idx < cnt * cols4) reinterpret_cast<float4 *>(c.s_tile)[idx] = reg[j];
+            if (idx < cnt * cols4) reinterpret_cast<float4 *>(S.s_tile)[idx] = reg[j];
         }
-        if (t0 == 0 && tid == 0) c.s_scalar[3] = __fdiv_rn(1.0f, chain_sum(c.s_sl, n_kv, 0.0f));
+        if (t0 == 0 && tid == 0) S.s_scalar[3] = __fdiv_rn(1.0f, chain_sum(S.s_sl, n_kv, 0.0f));
         __syncthreads();
         // out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
         if (tid < cols) {
-            const float inv = c.s_scalar[3];
-            const float *sl = c.s_sl + t0, *tile = c.s_tile + tid;
+            const float inv = S.s_scalar[3];
+            const float *sl = S.s_sl + t0, *tile = S.s_tile + tid;
             int r = 0;
             if (cnt >= 16) {
                 float pa[16], pb[16];
@@ -609,22 +654,24 @@ __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c
 
 // ---- phase C: Q8_K of the attention output | attn_out rows ----
 __device__ __noinline__ void mega_phase_c(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const MegaPtrs S(c);
     const int tid = threadIdx.x, qb = c.qb;
     auto map_c = [&](int row) -> RowRef { return RowRef{ly.attn_out, (size_t)row * qb, 0, p.xb2 + row}; };
     const int warp = tid >> 5, lane = tid & 31;
     for (int b = warp; b < qb; b += kMegaThreads / 32) {
         const float4 a = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8)), c4 = __ldcg(reinterpret_cast<const float4 *>(p.attn + b * 256 + lane * 8) + 1);
         const float v[8] = {a.x, a.y, a.z, a.w, c4.x, c4.y, c4.z, c4.w};
-        q8k_quantize_block(v, lane, c.s_nat + b * 256, c.s_adv + b, nullptr);
+        q8k_quantize_block(v, lane, S.s_nat + b * 256, S.s_adv + b, nullptr);
     }
     __syncthreads();
-    build_act_image(c.s_nat, c.s_act, qb);
+    build_act_image(S.s_nat, S.s_act, qb);
     __syncthreads();
-    mv_rows(map_c, qb, c.c_lo, c.c_hi, c.s_act, c.s_adv, c.s_ex);
+    mv_rows(map_c, qb, c.c_lo, c.c_hi, S.s_act, S.s_adv, S.s_ex);
 }
 
 // ---- phase D: x += attn_out, FFN norm, Q8_K (kept for E) | router logits ----
 __device__ __noinline__ void mega_phase_d(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const MegaPtrs S(c);
     const int tid = threadIdx.x, E = c.E;
     // the router row this CTA dots (asked of L2 a layer ago) and attn_out's result, read before the norm's chain
     float wr_pre[kMegaElems], rv[kMegaElems];
@@ -637,12 +684,12 @@ __device__ __noinline__ void mega_phase_d(const MegaParams &p, const MegaCtx &c,
 #pragma unroll
     for (int q = 0; q < kMegaElems; q++) {
         const int i = tid + q * kMegaThreads;
-        if (i < E) c.s_x[i] = __fadd_rn(c.s_x[i], rv[q]);
+        if (i < E) S.s_x[i] = __fadd_rn(S.s_x[i], rv[q]);
     }
-    for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) c.s_x[i] = __fadd_rn(c.s_x[i], __ldcg(p.xb2 + i));
+    for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) S.s_x[i] = __fadd_rn(S.s_x[i], __ldcg(p.xb2 + i));
     __syncthreads();
-    norm_quant(c.s_x, ly.ffn_norm, c.s_sq, c.s_xn, c.s_nat, c.s_adv, E, p.eps, c.s_scalar);
-    build_act_image(c.s_nat, c.s_act, c.eb);  // kept for phase E
+    norm_quant(S.s_x, ly.ffn_norm, S.s_sq, S.s_xn, S.s_nat, S.s_adv, E, p.eps, S.s_scalar, [](int) {});
+    build_act_image(S.s_nat, S.s_act, c.eb);  // kept for phase E
     mega_stamp(p, 17);
     for (int r = c.cta; r < c.ne; r += c.G) {
         // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
@@ -652,35 +699,36 @@ __device__ __noinline__ void mega_phase_d(const MegaParams &p, const MegaCtx &c,
 #pragma unroll
             for (int q = 0; q < kMegaElems; q++) {
                 const int i = tid + q * kMegaThreads;
-                if (i < E) c.s_sq[i] = __fmul_rn(wr_pre[q], c.s_xn[i]);
+                if (i < E) S.s_sq[i] = __fmul_rn(wr_pre[q], S.s_xn[i]);
             }
-            for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) c.s_sq[i] = __fmul_rn(__ldg(wr + i), c.s_xn[i]);
+            for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) S.s_sq[i] = __fmul_rn(__ldg(wr + i), S.s_xn[i]);
         } else {
-            for (int i = tid; i < E; i += kMegaThreads) c.s_sq[i] = __fmul_rn(__ldg(wr + i), c.s_xn[i]);
+            for (int i = tid; i < E; i += kMegaThreads) S.s_sq[i] = __fmul_rn(__ldg(wr + i), S.s_xn[i]);
         }
         __syncthreads();
-        if (tid == 0) p.logits[r] = chain_sum(c.s_sq, E, -0.0f);
+        if (tid == 0) p.logits[r] = chain_sum(S.s_sq, E, -0.0f);
     }
 }
 
 __device__ __forceinline__ int mega_expert_of(const MegaCtx &c, int slot) {
-    const int ex = c.s_ids[slot];
+    const MegaPtrs S(c);
+    const int ex = S.s_ids[slot];
     return (ex < 0 || ex >= c.ne) ? 0 : ex;
 }
 
 // ---- phase E: route | gate and up rows of the routed experts ----
 __device__ __noinline__ void mega_phase_e(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly, int il) {
+    const MegaPtrs S(c);
     const int tid = threadIdx.x, ne = c.ne, nu = c.nu, ffe = c.ffe, eb = c.eb, E = c.E, fb = c.fb;
-    for (int i = tid; i < ne; i += kMegaThreads) c.s_sq[i] = __ldcg(p.logits + i);
+    for (int i = tid; i < ne; i += kMegaThreads) S.s_sq[i] = __ldcg(p.logits + i);
     __syncthreads();
     mega_stamp(p, 18);
-    if (tid < 32) route_warp(c.s_sq, ne, nu, c.s_ids, c.s_w);
-    __syncthreads();
+    route_cta(S.s_sq, ne, nu, S.s_ids, S.s_w, S.s_red);
     mega_stamp(p, 19);
     if (c.cta == 0 && tid < nu) {
-        p.expert_ids[tid] = c.s_ids[tid];
-        p.expert_w[tid] = c.s_w[tid];
-        if (p.trace_ids) p.trace_ids[(size_t)il * nu + tid] = c.s_ids[tid];
+        p.expert_ids[tid] = S.s_ids[tid];
+        p.expert_w[tid] = S.s_w[tid];
+        if (p.trace_ids) p.trace_ids[(size_t)il * nu + tid] = S.s_ids[tid];
     }
     auto map_e = [&](int row) -> RowRef {
         const int slot = row / (2 * ffe), rem = row - slot * 2 * ffe, mat = rem / ffe, r = rem - mat * ffe;
@@ -694,11 +742,12 @@ __device__ __noinline__ void mega_phase_e(const MegaParams &p, const MegaCtx &c,
         seg = seg_hi;
     }
     mega_stamp(p, 20);
-    mv_rows(map_e, eb, c.e_lo, c.e_hi, c.s_act, c.s_adv, c.s_ex);  // the activation image is phase D's
+    mv_rows(map_e, eb, c.e_lo, c.e_hi, S.s_act, S.s_adv, S.s_ex);  // the activation image is phase D's
 }
 
 // ---- phase F: silu(gate) * up, Q8_K, for the slots of this CTA's rows | down rows ----
 __device__ __noinline__ void mega_phase_f(const MegaParams &p, const MegaCtx &c, const MegaLayer &ly) {
+    const MegaPtrs S(c);
     const int tid = threadIdx.x, ffe = c.ffe, fb = c.fb, E = c.E, slot_lo = c.slot_lo;
     auto map_f = [&](int row) -> RowRef {
         const int slot = row / E, r = row - slot * E;
@@ -706,24 +755,36 @@ __device__ __noinline__ void mega_phase_f(const MegaParams &p, const MegaCtx &c,
     };
     if (c.f_hi > c.f_lo) {
         const int warp = tid >> 5, lane = tid & 31, nslot = c.slot_hi - slot_lo + 1;
-        for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
-            const int sl_ = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
-            const size_t base = (size_t)sl_ * ffe + (size_t)b * 256 + lane * 8;
-            const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base) + 1);
-            const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base) + 1);
-            const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
-                                silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
-            q8k_quantize_block(v, lane, c.s_nat + blk * 256, c.s_adv + blk, nullptr);
-        }
+        if (nslot * ffe <= E) {
+            // silu(gate) * up of the slots' elements, one or two per thread (a warp per block would leave most of the CTA idle
+            // behind eight dependent exponentials per lane), then a warp per block quantizes from shared memory
+            const size_t base = (size_t)slot_lo * ffe;
+            for (int i = tid; i < nslot * ffe; i += kMegaThreads) S.s_xn[i] = silu_mul(__ldcg(p.e_gate + base + i), __ldcg(p.e_up + base + i));
+            __syncthreads();
+            for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
+                const float4 a = reinterpret_cast<const float4 *>(S.s_xn + blk * 256 + lane * 8)[0], b4 = reinterpret_cast<const float4 *>(S.s_xn + blk * 256 + lane * 8)[1];
+                const float v[8] = {a.x, a.y, a.z, a.w, b4.x, b4.y, b4.z, b4.w};
+                q8k_quantize_block(v, lane, S.s_nat + blk * 256, S.s_adv + blk, nullptr);
+            }
+        } else
+            for (int blk = warp; blk < nslot * fb; blk += kMegaThreads / 32) {
+                const int sl_ = slot_lo + blk / fb, b = blk - (blk / fb) * fb;
+                const size_t base = (size_t)sl_ * ffe + (size_t)b * 256 + lane * 8;
+                const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base)), g1 = __ldcg(reinterpret_cast<const float4 *>(p.e_gate + base) + 1);
+                const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base)), u1 = __ldcg(reinterpret_cast<const float4 *>(p.e_up + base) + 1);
+                const float v[8] = {silu_mul(g0.x, u0.x), silu_mul(g0.y, u0.y), silu_mul(g0.z, u0.z), silu_mul(g0.w, u0.w),
+                                    silu_mul(g1.x, u1.x), silu_mul(g1.y, u1.y), silu_mul(g1.z, u1.z), silu_mul(g1.w, u1.w)};
+                q8k_quantize_block(v, lane, S.s_nat + blk * 256, S.s_adv + blk, nullptr);
+            }
         __syncthreads();
-        build_act_image(c.s_nat, c.s_act, nslot * fb);
+        build_act_image(S.s_nat, S.s_act, nslot * fb);
         __syncthreads();
     }
     mega_stamp(p, 21);
-    mv_rows(map_f, fb, c.f_lo, c.f_hi, c.s_act, c.s_adv, c.s_ex);
+    mv_rows(map_f, fb, c.f_lo, c.f_hi, S.s_act, S.s_adv, S.s_ex);
 }
 
-__global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaParams p) {
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const __grid_constant__ MegaParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ MegaCtx ctx;
     __shared__ bool s_flag;
@@ -734,21 +795,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         c.qd = c.H * c.hd, c.kvd = c.HKV * c.hd, c.eb = c.E / 256, c.qb = c.qd / 256, c.fb = c.ffe / 256;
         c.ratio = c.H / c.HKV, c.half = c.hd / 2, c.cols = c.hd / kMegaSplit;
         const MegaSmem L = mega_smem(c.E, c.qd, c.hd, p.act_blocks, p.sl_floats, c.ne, p.ktile_rows, c.ratio);
-        c.s_x = reinterpret_cast<float *>(smem + L.x);
-        c.s_xn = reinterpret_cast<float *>(smem + L.xn);
-        c.s_sq = reinterpret_cast<float *>(smem + L.sq);
-        c.s_act = reinterpret_cast<uint32_t *>(smem + L.act);
-        c.s_nat = reinterpret_cast<int8_t *>(smem + L.nat);
-        c.s_adv = reinterpret_cast<float *>(smem + L.adv);
-        c.s_ex = reinterpret_cast<float *>(smem + L.ex);
-        c.s_sl = reinterpret_cast<float *>(smem + L.sl);
-        c.s_tile = reinterpret_cast<float *>(smem + L.tile);
-        float *s_misc = reinterpret_cast<float *>(smem + L.misc);
-        c.s_k = s_misc + c.hd, c.s_v = s_misc + 2 * c.hd, c.s_tmp = s_misc + 3 * c.hd;  // [hd] each
-        c.s_red = s_misc + 4 * c.hd;                                    // [128] reduction scratch
-        c.s_ids = reinterpret_cast<int32_t *>(c.s_red + 256);           // [64]
-        c.s_w = c.s_red + 320;                                          // [64]
-        c.s_scalar = c.s_red + 384;                                     // a few broadcast scalars
+        c.o_x = (uint32_t)L.x, c.o_xn = (uint32_t)L.xn, c.o_sq = (uint32_t)L.sq, c.o_act = (uint32_t)L.act, c.o_nat = (uint32_t)L.nat;
+        c.o_adv = (uint32_t)L.adv, c.o_ex = (uint32_t)L.ex, c.o_sl = (uint32_t)L.sl, c.o_tile = (uint32_t)L.tile, c.o_misc = (uint32_t)L.misc;
         c.cta = cta, c.G = G, c.pos = p.meta[1], c.n_kv = c.pos + 1;
         // row ranges of the phases (the same every layer)
         const int rows_a = c.qd + 2 * c.kvd, rpc_a = (rows_a + G - 1) / G;
@@ -772,7 +820,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     __syncthreads();
     const int token = p.meta[0];
     unsigned int bar_target = 0;
-    if (p.prof && cta == 0 && tid == 0) g_mega_t_prev = global_ns();
+    long long prof_c0 = 0;
+    unsigned long long prof_t0 = 0;
+    if (p.prof && cta == 0 && tid == 0) {
+        for (int k = 0; k < 32; k++) s_mega_prof[k] = 0;
+        prof_c0 = clock64();
+        prof_t0 = s_mega_prof[32] = global_ns();
+    }
 #define MEGA_STAMP(k) mega_stamp(p, k)
 #define MEGA_BARRIER(k)                                       \
     do {                                                      \
@@ -783,12 +837,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     // ---- embed: one row of token_embd, d * sc * q (crates/llamd-quant/src/lib.rs:181-226) ----
     {
         const int E = p.E, eb = E / 256;
+        float *sx0 = reinterpret_cast<float *>(smem + ctx.o_x);
         for (int i = tid; i < E; i += kMegaThreads) {
             const size_t unit = (size_t)token * eb + (i >> 8);
             const int e = i & 255;
             const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(p.tok_embd + t32_d_offset(unit)));
             const float sc = (float)(int8_t)p.tok_embd[t32_scale_offset(unit) + (e >> 4)];
-            ctx.s_x[i] = __fmul_rn(__fmul_rn(d, sc), (float)t32_weight(p.tok_embd, unit, e));
+            sx0[i] = __fmul_rn(__fmul_rn(d, sc), (float)t32_weight(p.tok_embd, unit, e));
         }
     }
     mega_prefetch_attn_side(ctx, p.layers[0]);
@@ -820,6 +875,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         mega_phase_f(p, ctx, ly);
         MEGA_STAMP(12);
         MEGA_BARRIER(13);
+    }
+    if (p.prof && cta == 0 && tid == 0) {
+        s_mega_prof[30] = (unsigned long long)(clock64() - prof_c0);  // SM cycles and nanoseconds of the whole token: their
+        s_mega_prof[31] = global_ns() - prof_t0;                      // ratio is the clock the SM really ran at
+        for (int k = 0; k < 32; k++) p.prof[k] += s_mega_prof[k];
     }
 #undef MEGA_BARRIER
 #undef MEGA_STAMP
@@ -853,7 +913,7 @@ size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int
 bool mega_supported(const llamd_hparams &hp, int max_kv) {
     const int E = hp.n_embd, qd = hp.n_head * hp.head_dim, ffe = hp.n_ff_expert, hd = hp.head_dim;
     if (E % 256 || qd % 256 || ffe % 256 || hd % (4 * kMegaSplit) || hd > kMegaThreads / 2 || hp.n_head % hp.n_head_kv) return false;
-    if (E / 256 > kMegaThreads || qd / 256 > kMegaThreads || hp.n_expert_used > 64 || hp.n_expert > 1024) return false;
+    if (E / 256 > kMegaThreads || qd / 256 > kMegaThreads || hp.n_expert_used > 64 || hp.n_expert > 32 * kRoutePerLane) return false;
     int dev = 0, sms = 0, optin = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {

@@ -307,14 +307,21 @@ class CudaModel:
     RESIDENT_PHASES = ("A image + qkv rows", "barrier", "B1 qk-norm rope kv-store scores", "barrier", "B2 softmax values",
                        "barrier", "C quant + attn_out rows", "barrier", "D router", "barrier", "E gate/up rows",
                        "barrier", "F down rows", "barrier", "A combine", "A norm + quant", "-", "D add + norm + quant + image",
-                       "E logits load", "E route", "E prefetch of down rows", "F silu + quant + image")
+                       "E logits load", "E route", "E prefetch of down rows", "F silu + quant + image",
+                       "A norm: squares", "A norm: chain", "A norm: scale")
 
-    def resident_profile(self) -> dict:
-        """Nanoseconds per phase accumulated by the resident kernel's CTA 0 since set_option("resident_profile", 1)."""
+    def resident_profile_raw(self) -> list:
+        """The 32 counters of the resident kernel's CTA 0 since set_option("resident_profile", 1): nanoseconds per phase in
+        RESIDENT_PHASES' order; [30] SM cycles and [31] nanoseconds of the whole kernel, summed over the tokens."""
         out = (C.c_ulonglong * 32)()
         if self._L.llamd_model_resident_profile(self._h, out) != 0:
             raise backend.Other("resident profile: " + (self._err() or backend._last_error()))
-        return {f"{i:02d} {name}": int(out[i]) for i, name in enumerate(self.RESIDENT_PHASES)}
+        return [int(v) for v in out]
+
+    def resident_profile(self) -> dict:
+        """Nanoseconds per phase accumulated by the resident kernel's CTA 0 since set_option("resident_profile", 1)."""
+        out = self.resident_profile_raw()
+        return {f"{i:02d} {name}": out[i] for i, name in enumerate(self.RESIDENT_PHASES)}
 
     def ep_tile_cap(self) -> int:
         """Tokens per rank and tile of expert-parallel prefill (0 until the buffers have been shared)."""

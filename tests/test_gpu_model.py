@@ -46,7 +46,7 @@ def test_bad_arguments_are_refused(tiny):
     with pytest.raises(backend.Malformed):
         CudaModel(hp, 0)
     with pytest.raises(backend.Malformed):
-        CudaModel(hp, 16, 9)
+        CudaModel(hp, 16, backend.MAX_BATCH + 1)
     with pytest.raises(backend.Malformed):
         gm.forward(1, 64)
     with pytest.raises(backend.Other):
