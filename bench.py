@@ -286,8 +286,10 @@ def main():
     ap.add_argument("--parallelism", default="", choices=["", "replicas", "ep"],
                     help="N > 1: ep (default) = experts sharded 128/N per GPU, dispatch/combine per MoE layer, each rank decodes "
                          "its own sequence; replicas = one full model per GPU, no exchange")
-    ap.add_argument("--arith", default="exact", choices=["exact"],
-                    help="exact: every f32 reduction in the reference's order (token ids bit-exact against the CPU path)")
+    ap.add_argument("--arith", default="exact", choices=["exact", "fast"],
+                    help="exact: every f32 reduction in the reference's order (token ids bit-exact against the CPU path; what `value` "
+                         "is unless asked otherwise). fast: the long sums of a decode token as reduction trees, through the resident "
+                         "kernel (tolerance-level floats). An exact run on one GPU also times the fast mode and reports it in detail.fast_arith")
     ap.add_argument("--gemm", default="exact", choices=["exact", "dp4a", "tc"],
                     help="prefill workload: exact = integer tensor path (mma.sync), bit-identical to decode (default); dp4a = the same "
                          "bits, 8 tokens per weight pass; tc = tcgen05 on f16 pairs, tolerance level")
@@ -387,6 +389,10 @@ def main():
         m.set_option("prefetch", 1)
     if args.resident >= 0 and not ep:
         m.set_option("resident", args.resident)
+    if args.arith == "fast":
+        if ep:
+            raise SystemExit("--arith fast is a single-GPU decode mode (replicas); not available with expert parallelism")
+        m.set_option("arith", 1)
 
     prompt = synth.token_ids(args.prompt, hp["n_vocab"], 0, "prompt", rank)
     if args.workload == "prefill":
@@ -504,11 +510,31 @@ def main():
 
     # ---- value: resident loop, device-timed ----
     barrier()
+    tok0, pos0 = tok, pos
     toks, ms = m.decode(tok, pos, K)
     barrier()
     dev_ms = max_over_ranks(ms)
     pos += K
     clocks = sampler.stop()
+
+    # ---- the other arithmetic mode over the same K positions (one GPU, exact runs only): how fast, and whether it chose the same tokens
+    fast_arith = None
+    if args.arith == "exact" and not ep and world == 1 and args.workload == "decode":
+        try:
+            m.set_option("arith", 1)
+            m.decode(tok0, pos0, min(K, 8))
+            ftoks, fms = m.decode(tok0, pos0, K)
+            same = [int(a) == int(b) for a, b in zip(ftoks, toks)]
+            fast_arith = {"value": K / (fms * 1e-3), "unit": "tok/s", "ms_per_step": fms / K, "tokens_equal_exact": all(same),
+                          "first_difference_at_step": None if all(same) else same.index(False), "steps": K,
+                          "note": "the same K positions decoded again through the resident kernel with reduction trees for the two "
+                                  "norms' sums, the router's dots and attention's sums (model option arith = 1); everything else as in "
+                                  "the exact mode"}
+            m.set_option("arith", 0)
+            m.set_option("resident", max(args.resident, 0))
+            m.decode(tok0, pos0, K)  # leave the cache as the exact run left it
+        except Exception as e:  # a shape the resident kernel does not support
+            fast_arith = {"unavailable": str(e)}
 
     # ---- roofline of the dominant kernel ----
     iters = max(4, min(K, 16))
@@ -541,7 +567,7 @@ def main():
     detail = {"token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "ms_per_token_per_rank": dev_ms / K,
               "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch,
               "inputs_hash": inputs_hash, "tokens_hash": hashes[0], "tokens_hash_per_rank": hashes,
-              "tokens_head": decoded[:8], "n_tokens_hashed": len(decoded), "tokens_vs_cpu_golden": golden_check,
+              "tokens_head": decoded[:8], "n_tokens_hashed": len(decoded), "tokens_vs_cpu_golden": golden_check, "fast_arith": fast_arith,
               "hash_note": "crc32 of (prompt ids, layer-0 attn_q bytes) and of the int32 token ids chosen after the prompt: "
                            "the prefill's token, the warm-up tokens, the e2e tokens, the device-loop tokens"}
     line = {

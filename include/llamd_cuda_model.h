@@ -128,7 +128,15 @@ int llamd_model_set_option(llamd_model *m, const char *name, int value);
  * launches per layer; the same arithmetic in the same order, so the same bits. Falls back to the per-op pass when the
  * dimensions do not fit (shared memory, heads x 4 > SMs) or with max_seq > 1 / expert parallelism. Option
  * "resident_profile" = 1 makes its CTA 0 accumulate nanoseconds per phase, read by llamd_model_resident_profile
- * (32 values, 19 used, in the kernel's phase order). */
+ * (32 values in the kernel's phase order; [30] SM cycles and [31] nanoseconds of the whole kernel).
+ *
+ * Option "arith" = 1, or a mask of 2 (norms) | 4 (router) | 8 (attention) (no counterpart in the reference's CPU path; its device backends reduce in parallel too): the
+ * resident kernel sums the 2048-term sums of the two norms and of the router's dots, the softmax sum and the weighted
+ * values of attention as reduction trees instead of walking them in the reference's order. Integers, indices, `exp`
+ * and every other float operation are unchanged, so results agree with arith = 0 to the last bits of those sums, NOT
+ * bit for bit, and a near-tie in a router can then choose another expert. Implies "resident" = 1; refused (-1, message)
+ * for max_seq > 1, expert parallelism or a shape the resident kernel does not support. Prefill and batches always use
+ * the exact arithmetic. */
 int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
 
 /* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */

@@ -231,12 +231,26 @@ __device__ __forceinline__ void l2_prefetch_rows(const uint8_t *w, int lo, int h
 
 constexpr int kMegaElems = 4;  // elements of an n_embd-long vector per thread per sweep (n_embd <= 3072 in one sweep)
 
+// Sum of one value per thread over the CTA, the same on every thread and from run to run: xor-shuffle tree inside a warp,
+// then the warps' sums added in warp order. Used by the `fast` arithmetic only. s_red: kMegaThreads / 32 floats.
+__device__ __forceinline__ float block_sum(float v, float *s_red) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = s_red[0];
+#pragma unroll
+    for (int w = 1; w < kMegaThreads / 32; w++) t = __fadd_rn(t, s_red[w]);
+    __syncthreads();
+    return t;
+}
+
 // rms norm of s_x (n floats): squares by all threads, the ordered sum by thread 0, out = (x * scale) * w into s_out,
 // then Q8_K of s_out into s_nat / s_adv (n / 256 blocks). crates/llamd-cpu/src/lib.rs:55-75, dot.rs:88-128.
 // The weight vector is read before the chain is walked, so that its latency is hidden behind it.
 template <class Stamp>
 __device__ __forceinline__ void norm_quant(const float *s_x, const float *__restrict__ w, float *s_sq, float *s_out, int8_t *s_nat, float *s_adv,
-                                           int n, float eps, float *s_scalar, const Stamp &stamp) {
+                                           int n, float eps, float *s_scalar, const Stamp &stamp, bool fast, float *s_red) {
     const int tid = threadIdx.x;
     float wv[kMegaElems];
 #pragma unroll
@@ -244,16 +258,25 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
         const int i = tid + u * kMegaThreads;
         wv[u] = i < n ? __ldg(w + i) : 0.0f;
     }
-    for (int i = tid; i < n; i += kMegaThreads) s_sq[i] = __fmul_rn(s_x[i], s_x[i]);
-    __syncthreads();
-    stamp(0);
-    if (tid == 0) {
-        const float sum = chain_sum(s_sq, n, 0.0f);
-        *s_scalar = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+    float scale;
+    if (fast) {
+        float part = 0.0f;
+        for (int i = tid; i < n; i += kMegaThreads) part = __fadd_rn(part, __fmul_rn(s_x[i], s_x[i]));
+        const float sum = block_sum(part, s_red);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+        stamp(1);
+    } else {
+        for (int i = tid; i < n; i += kMegaThreads) s_sq[i] = __fmul_rn(s_x[i], s_x[i]);
+        __syncthreads();
+        stamp(0);
+        if (tid == 0) {
+            const float sum = chain_sum(s_sq, n, 0.0f);
+            *s_scalar = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+        }
+        __syncthreads();
+        stamp(1);
+        scale = *s_scalar;
     }
-    __syncthreads();
-    stamp(1);
-    const float scale = *s_scalar;
 #pragma unroll
     for (int u = 0; u < kMegaElems; u++) {
         const int i = tid + u * kMegaThreads;
@@ -272,63 +295,46 @@ __device__ __forceinline__ void norm_quant(const float *s_x, const float *__rest
 }
 
 // route (crates/llamd-models/src/moe.rs:73-113), called by the whole CTA: the same operations as route_block -- max,
-// exp(l - max), the sum walked in index order from -0.0, p / sum, n_used rounds of (probability descending, index
-// ascending), the chosen weights summed in choice order from -0.0, the 2^-14 floor, the division. The exponentials are
-// spread over the CTA's threads; the selection runs in warp 0 with the probabilities in registers (8 per lane: n_expert
-// <= 256) and shuffles, no shared memory and no barrier inside a round. s_p: logits in (overwritten). s_red: 40 floats.
-constexpr int kRoutePerLane = 8;
+// exp(l - max), the sum walked in index order from -0.0, p / sum, the n_used best by (probability descending, index
+// ascending), the chosen weights summed in choice order from -0.0, the 2^-14 floor, the division. The stable sort is
+// done by rank: thread i counts the experts that come before expert i in that order, and the experts of rank < n_used
+// write themselves into place (one pass over shared memory instead of n_used arg-max rounds). n_expert <= kMegaThreads.
+// s_p: logits in (overwritten with the probabilities). s_red: 40 floats.
 __device__ __forceinline__ void route_cta(float *s_p, int n_expert, int n_used, int32_t *ids, float *weights, float *s_red) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float m = -INFINITY;
-    for (int i = tid; i < n_expert; i += kMegaThreads) m = fmaxf(m, s_p[i]);
+    float m = tid < n_expert ? s_p[tid] : -INFINITY;
     for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
     if (lane == 0) s_red[warp] = m;
     __syncthreads();
     m = s_red[0];
     for (int w = 1; w < kMegaThreads / 32; w++) m = fmaxf(m, s_red[w]);
-    for (int i = tid; i < n_expert; i += kMegaThreads) s_p[i] = ref_expf(__fsub_rn(s_p[i], m));
+    if (tid < n_expert) s_p[tid] = ref_expf(__fsub_rn(s_p[tid], m));
     __syncthreads();
     if (tid == 0) s_red[32] = chain_sum(s_p, n_expert, -0.0f);
     __syncthreads();
-    if (warp == 0) {
-        const float total = s_red[32];
-        float v[kRoutePerLane];
-#pragma unroll
-        for (int j = 0; j < kRoutePerLane; j++) {
-            const int i = lane + 32 * j;
-            v[j] = i < n_expert ? __fdiv_rn(s_p[i], total) : -2.0f;  // (probabilities are >= 0; taken ones become -1)
+    const float mine = tid < n_expert ? __fdiv_rn(s_p[tid], s_red[32]) : 0.0f;
+    __syncthreads();
+    if (tid < n_expert) s_p[tid] = mine;
+    __syncthreads();
+    if (tid < n_expert) {
+        int rank = 0;
+        for (int j = 0; j < n_expert; j++) {
+            const float o = s_p[j];
+            rank += (o > mine || (o == mine && j < tid)) ? 1 : 0;
         }
-        float wsum = -0.0f;
-        for (int k = 0; k < n_used; k++) {
-            float bv = -INFINITY;
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < kRoutePerLane; j++)
-                if (v[j] > bv) {  // (a lane's indices ascend with j: a strict test keeps the lowest)
-                    bv = v[j];
-                    bi = lane + 32 * j;
-                }
-            for (int off = 16; off > 0; off >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-                if (ov > bv || (ov == bv && oi < bi)) {
-                    bv = ov;
-                    bi = oi;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < kRoutePerLane; j++)
-                if (bi == lane + 32 * j) v[j] = -1.0f;  // taken: cannot win again
-            wsum = __fadd_rn(wsum, bv);                 // (every lane walks the same sum, in choice order)
-            if (lane == 0) {
-                ids[k] = bi;
-                weights[k] = bv;  // raw; divided below, once the sum is known
-            }
+        if (rank < n_used) {
+            ids[rank] = tid;
+            weights[rank] = mine;
         }
-        __syncwarp();
-        wsum = fmaxf(wsum, WEIGHT_SUM_FLOOR);
-        for (int k = lane; k < n_used; k += 32) weights[k] = __fdiv_rn(weights[k], wsum);
     }
+    __syncthreads();
+    if (tid == 0) {
+        float sum = -0.0f;
+        for (int k = 0; k < n_used; k++) sum = __fadd_rn(sum, weights[k]);
+        s_red[33] = fmaxf(sum, WEIGHT_SUM_FLOOR);
+    }
+    __syncthreads();
+    if (tid < n_used) weights[tid] = __fdiv_rn(weights[tid], s_red[33]);
     __syncthreads();
 }
 
@@ -448,7 +454,7 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
             for (int i = tid; i < E; i += kMegaThreads) p.trace_x[(size_t)(il - 1) * E + i] = S.s_x[i];
     }
     mega_stamp(p, 14);
-    norm_quant(S.s_x, tail ? p.output_norm : ly.attn_norm, S.s_sq, S.s_xn, S.s_nat, S.s_adv, E, p.eps, S.s_scalar, [&](int k) { mega_stamp(p, 22 + k); });
+    norm_quant(S.s_x, tail ? p.output_norm : ly.attn_norm, S.s_sq, S.s_xn, S.s_nat, S.s_adv, E, p.eps, S.s_scalar, [&](int k) { mega_stamp(p, 22 + k); }, (p.fast & 1) != 0, S.s_red);
     if (tail) {
         if (c.cta == 0) {
             for (int i = tid; i < E; i += kMegaThreads) {
@@ -624,6 +630,25 @@ __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c
             const int idx = tid + j * kMegaThreads;
             if (idx < cnt * cols4) reinterpret_cast<float4 *>(S.s_tile)[idx] = reg[j];
         }
+        if (p.fast & 4) {
+            // the softmax sum by the CTA's reduction tree; the weighted values by kMegaThreads / cols groups of positions
+            // per column, whose partial sums are added in group order after the last tile
+            __syncthreads();
+            if (t0 == 0) {
+                float part = 0.0f;
+                for (int t = tid; t < n_kv; t += kMegaThreads) part = __fadd_rn(part, S.s_sl[t]);
+                const float total = block_sum(part, S.s_red);
+                if (tid == 0) S.s_scalar[3] = __fdiv_rn(1.0f, total);
+                __syncthreads();
+            }
+            const float inv = S.s_scalar[3];
+            const int g = tid / cols, d = tid - g * cols, ng = min(kMegaThreads, c.E) / cols;  // (the partial sums go to s_sq: n_embd floats)
+            const float *sl = S.s_sl + t0;
+            if (g < ng)
+                for (int r = g; r < cnt; r += ng) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[r], inv), S.s_tile[r * cols + d]));
+            __syncthreads();
+            continue;
+        }
         if (t0 == 0 && tid == 0) S.s_scalar[3] = __fdiv_rn(1.0f, chain_sum(S.s_sl, n_kv, 0.0f));
         __syncthreads();
         // out[d] = sum_t (e[t] * inv) * v[t][d], t ascending (:116-121)
@@ -648,6 +673,15 @@ __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c
             for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[r], inv), tile[r * cols]));
         }
         __syncthreads();
+    }
+    if (p.fast & 4) {
+        const int ng = min(kMegaThreads, c.E) / cols;
+        if (tid < ng * cols) S.s_sq[tid] = acc;  // [group][column]
+        __syncthreads();
+        if (tid < cols) {
+            acc = S.s_sq[tid];
+            for (int g = 1; g < ng; g++) acc = __fadd_rn(acc, S.s_sq[g * cols + tid]);
+        }
     }
     if (tid < cols) p.attn[(size_t)h * hd + (size_t)cpart * cols + tid] = acc;
 }
@@ -688,9 +722,29 @@ __device__ __noinline__ void mega_phase_d(const MegaParams &p, const MegaCtx &c,
     }
     for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) S.s_x[i] = __fadd_rn(S.s_x[i], __ldcg(p.xb2 + i));
     __syncthreads();
-    norm_quant(S.s_x, ly.ffn_norm, S.s_sq, S.s_xn, S.s_nat, S.s_adv, E, p.eps, S.s_scalar, [](int) {});
+    norm_quant(S.s_x, ly.ffn_norm, S.s_sq, S.s_xn, S.s_nat, S.s_adv, E, p.eps, S.s_scalar, [](int) {}, (p.fast & 1) != 0, S.s_red);
     build_act_image(S.s_nat, S.s_act, c.eb);  // kept for phase E
     mega_stamp(p, 17);
+    if (p.fast & 2) {
+        // the same products, summed by the CTA's reduction tree
+        for (int r = c.cta; r < c.ne; r += c.G) {
+            const float *wr = ly.router + (size_t)r * E;
+            float part = 0.0f;
+            if (r == c.cta) {
+#pragma unroll
+                for (int q = 0; q < kMegaElems; q++) {
+                    const int i = tid + q * kMegaThreads;
+                    if (i < E) part = __fadd_rn(part, __fmul_rn(wr_pre[q], S.s_xn[i]));
+                }
+                for (int i = tid + kMegaElems * kMegaThreads; i < E; i += kMegaThreads) part = __fadd_rn(part, __fmul_rn(__ldg(wr + i), S.s_xn[i]));
+            } else {
+                for (int i = tid; i < E; i += kMegaThreads) part = __fadd_rn(part, __fmul_rn(__ldg(wr + i), S.s_xn[i]));
+            }
+            const float y = block_sum(part, S.s_red);
+            if (tid == 0) p.logits[r] = y;
+        }
+        return;
+    }
     for (int r = c.cta; r < c.ne; r += c.G) {
         // y = fold(-0.0, +) of w[r][t] * x[t], t ascending (crates/llamd-models/src/model.rs:253-263)
         const float *wr = ly.router + (size_t)r * E;
@@ -913,7 +967,7 @@ size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int
 bool mega_supported(const llamd_hparams &hp, int max_kv) {
     const int E = hp.n_embd, qd = hp.n_head * hp.head_dim, ffe = hp.n_ff_expert, hd = hp.head_dim;
     if (E % 256 || qd % 256 || ffe % 256 || hd % (4 * kMegaSplit) || hd > kMegaThreads / 2 || hp.n_head % hp.n_head_kv) return false;
-    if (E / 256 > kMegaThreads || qd / 256 > kMegaThreads || hp.n_expert_used > 64 || hp.n_expert > 32 * kRoutePerLane) return false;
+    if (E / 256 > kMegaThreads || qd / 256 > kMegaThreads || hp.n_expert_used > 64 || hp.n_expert > kMegaThreads || hp.n_expert_used > hp.n_expert) return false;
     int dev = 0, sms = 0, optin = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {

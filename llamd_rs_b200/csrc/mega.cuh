@@ -32,6 +32,7 @@ struct MegaParams {
     int act_blocks;      // blocks the activation image must hold
     int sl_floats;       // padded max_kv
     int ktile_rows;      // cached positions one CTA scores: ceil(max_kv / (SMs / n_head_kv))
+    int fast;            // bit mask: tree reductions in place of the long ordered f32 sums of 1 the norms, 2 the router's dots, 4 attention
 };
 
 size_t mega_smem_bytes(const llamd_hparams &hp, int max_kv, int *act_blocks, int *sl_floats, int *ktile_rows_out);

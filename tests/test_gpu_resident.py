@@ -79,3 +79,75 @@ def test_resident_pass_equals_the_per_op_pass(be, which):
         assert m.launches_per_pass() < 12, "one resident launch, the head and the bookkeeping"
     finally:
         m.free()
+
+
+LAYER = 1e-4   # crates/llamd-core/src/tolerance.rs:100
+LOGITS = 2e-3  # tolerance.rs:109
+
+
+def dev_rms(a, b):
+    """Largest |a - b| relative to the rms of the exact vector. The reference's tolerances are stated for activations of
+    order 1; the random-init models here carry hidden states of rms 50..500, so the deviation is scaled by the vector's own
+    size instead of llamd_core::tolerance::max_deviation's floor of 1."""
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.max(np.abs(a - b)) / max(float(np.sqrt(np.mean(b * b))), 1e-30))
+
+
+@pytest.mark.parametrize("which", ["tiny", "wider", "full3"])
+def test_fast_arithmetic_is_the_same_function_up_to_rounding(be, which):
+    """Option arith = 1: reduction trees for the norms' sums, the router's dots and attention's sums, nothing else changed.
+    Checked where rounding noise is all that can differ: at position 0 (softmax over one key is exactly 1) the hidden
+    state after every layer stays within LAYER, the K/V rows within LAYER and the logits within LOGITS of the exact
+    mode's, relative to each vector's rms, and the routed experts are the same. Later positions are only required to run
+    and to be reproducible: a random-init network is chaotic (one flipped Q8_K rounding after a one-ulp change of a norm's
+    scale moves a V row by 0.6 %, saturated softmaxes amplify that), so the modes' continuations drift apart there, which
+    is why the exact mode is the default."""
+    from llamd_rs_b200 import backend, synth
+    from llamd_rs_b200.model import CudaModel
+
+    hp = synth.TINY if which == "tiny" else (dict(synth.QWEN3MOE_30B, n_layer=3) if which == "full3" else DIMS[which])
+    tokens = synth.token_ids(6, hp["n_vocab"], 33, "fast", which).tolist()
+    m = CudaModel.load_synthetic(hp, 7, max_kv=64)
+    try:
+        m.set_option("resident", 1)
+        _, exact_tr, _ = run_traced(m, tokens[:1], 0)
+        exact_logits = m.logits()[0].copy()
+        exact_kv = [m.read_kv(il, 1) for il in range(hp["n_layer"])]
+        for mask in (2, 4, 8, 1):  # norms, router, attention, all
+            m.set_option("arith", mask)
+            _, fast_tr, _ = run_traced(m, tokens[:1], 0)
+            fast_logits = m.logits()[0].copy()
+            (ex, ei), (fx, fi) = exact_tr[0], fast_tr[0]
+            assert np.array_equal(ei, fi), f"{which} mask {mask}: expert ids at position 0"
+            for il in range(hp["n_layer"]):
+                assert dev_rms(fx[il, 0], ex[il, 0]) <= LAYER, f"{which} mask {mask}: layer {il} hidden state"
+                k, v = m.read_kv(il, 1)
+                assert dev_rms(k, exact_kv[il][0]) <= LAYER and dev_rms(v, exact_kv[il][1]) <= LAYER, f"{which} mask {mask}: layer {il} K/V"
+            assert dev_rms(fast_logits, exact_logits) <= LOGITS
+        assert not np.array_equal(bits(fast_tr[0][0]), bits(exact_tr[0][0])), "the two modes should not be the same code path"
+        with pytest.raises(backend.Malformed):
+            m.set_option("resident", 0)  # the fast arithmetic lives in the resident kernel
+        with pytest.raises(backend.Malformed):
+            m.set_option("arith", 3)
+        # reproducible: the trees have a fixed shape
+        toks_a, tr_a, log_a = run_traced(m, tokens, 4)
+        toks_b, tr_b, log_b = run_traced(m, tokens, 4)
+        assert toks_a == toks_b and np.array_equal(bits(log_a), bits(log_b))
+        assert all(0 <= t < hp["n_vocab"] for t in toks_a)
+        m.set_option("arith", 0)
+        _, again_tr, _ = run_traced(m, tokens[:1], 0)
+        assert np.array_equal(bits(again_tr[0][0]), bits(exact_tr[0][0])), "switching back restores the exact arithmetic"
+    finally:
+        m.free()
+
+
+def test_fast_arithmetic_is_refused_where_it_does_not_exist(be):
+    from llamd_rs_b200 import backend, synth
+    from llamd_rs_b200.model import CudaModel
+
+    m = CudaModel.load_synthetic(synth.TINY, 7, max_kv=32, max_seq=2)
+    try:
+        with pytest.raises(backend.Malformed):
+            m.set_option("arith", 1)
+    finally:
+        m.free()
