@@ -588,7 +588,7 @@ def main():
                      "frac_of_nominal_8tbs": achieved / 8000.0},
         "clocks": clocks,
     }
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:  # (the CPU port is timed beside the single-GPU run only)
         threads = os.cpu_count() or 1
         port = CpuPort(dict(synth.QWEN3MOE_30B), 0, 2, threads, args.prompt, 8)
         port.step()

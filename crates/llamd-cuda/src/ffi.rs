@@ -95,6 +95,7 @@ unsafe extern "C" {
     pub fn llamd_fwd_matvec_f32_batch(w: *const f32, x: *const f32, out: *mut f32, k: c_int, rows: c_int, nseq: c_int);
     pub fn llamd_fwd_transpose_f32(w: *const f32, wt: *mut f32, rows: c_int, k: c_int);
     pub fn llamd_fwd_matvec_q8_0(w: *const c_void, x: *const f32, out: *mut f32, blocks32: c_int, rows: c_int, nseq: c_int);
+    pub fn llamd_fwd_matvec_q8_0_status() -> c_int;
     pub fn llamd_fwd_embed(table: *const c_void, token: c_int, out: *mut f32, blocks: c_int);
     pub fn llamd_fwd_embed_meta(table: *const c_void, meta: *const i32, out: *mut f32, blocks: c_int, nseq: c_int);
     pub fn llamd_fwd_rms_norm_mul(x: *const f32, w: *const f32, out: *mut f32, n: c_int, eps: f32, nseq: c_int);

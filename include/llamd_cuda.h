@@ -172,6 +172,10 @@ void llamd_fwd_matvec_f32(const float *w, const float *x, float *out, int k, int
 void llamd_fwd_matvec_f32_batch(const float *w, const float *x, float *out, int k, int rows, int nseq);
 void llamd_fwd_transpose_f32(const float *w, float *wt, int rows, int k);
 void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq);
+/* Small and medium matrices run with their weights brought into shared memory by bulk copies whose waits are
+ * bounded: 0 while every copy has arrived within its limit, else 1 + the first CTA whose wait ran out (its 32 rows
+ * were not written). Synchronises the stream. No counterpart in the reference. */
+int llamd_fwd_matvec_q8_0_status(void);
 
 void llamd_fwd_embed(const void *table, int token, float *out, int blocks);              /* :279 */
 void llamd_fwd_embed_meta(const void *table, const int32_t *meta, float *out, int blocks, int nseq); /* :594 */

@@ -135,6 +135,7 @@ SIGNATURES = {
     "llamd_fwd_gemm_tokens_tc": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
     "llamd_fwd_expert_gemm_tc": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]),
     "llamd_fwd_gemm_tc_status": (i32, []),
+    "llamd_fwd_matvec_q8_0_status": (i32, []),
     "llamd_fwd_matmul_f32_tokens": (None, [vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_attention_prefill": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32, i32]),
     "llamd_fwd_moe_group": (None, [vp, i32, i32, i32, vp, vp, vp, vp]),

@@ -299,7 +299,12 @@ int llamd_cuda_matvec_q8_0_f32(const void *d_w, const float *x, float *out, int 
     LLAMD_TRY(cudaMemcpyAsync(d_x, x, nseq * k * sizeof(float), cudaMemcpyHostToDevice, stream()), "x H2D");
     llamd_fwd_matvec_q8_0(d_w, d_x, d_out, blocks32, rows, nseq);
     LLAMD_TRY(cudaMemcpyAsync(out, d_out, (size_t)nseq * rows * sizeof(float), cudaMemcpyDeviceToHost, stream()), "out D2H");
-    return llamd_fwd_sync();
+    if (llamd_fwd_sync() != 0) return -1;
+    if (llamd_fwd_matvec_q8_0_status() != 0) {
+        set_error_msg("matvec_q8_0: a bulk copy of the weights did not arrive within its limit; rows are missing");
+        return -1;
+    }
+    return 0;
 }
 
 }  // extern "C"

@@ -274,6 +274,156 @@ __global__ void __launch_bounds__(kQ80Producers + 32 * NSEQ) matvec_q8_0_rows_ke
     if (!producer && row < rows) out[(size_t)seq * rows + row] = acc;
 }
 
+// The same arithmetic again, fed by bulk copies. The form above keeps ONE chunk of raw blocks in flight per CTA (8.7 KB
+// per SM against an HBM round trip of ~2 us: 0.5 TB/s over the whole GPU, which is what it measured). Here one thread
+// asks for the CTA's WHOLE slice of the matrix -- 32 rows x all blocks, one contiguous run of the tiled layout -- as one
+// bulk copy per 256-column chunk (cp.async.bulk, each completing on its own mbarrier) before anything else happens, so
+// the memory latency is paid once and the producers then convert from shared memory. With one sequence the producers
+// store the products (d*q)*x, so the chain warp's loop is a shared load and the dependent add alone.
+// Every mbarrier wait is bounded; a wait that runs out sets *status and the CTA leaves its outputs unwritten.
+__device__ __forceinline__ uint32_t q80_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool q80_mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t a = q80_smem_u32(bar);
+    for (int it = 0; it < (1 << 14); it++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(a), "r"(parity), "r"(20000u)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+constexpr int kQ80MaxChunks = 32;  // k <= 8192
+template <int NSEQ>
+__global__ void __launch_bounds__(kQ80Producers + 32 * NSEQ) matvec_q8_0_bulk_kernel(const uint8_t *__restrict__ tiled, const float *__restrict__ x,
+                                                                                     float *__restrict__ out, int blocks, int rows, int *status) {
+    extern __shared__ __align__(16) float smem_f[];
+    __shared__ __align__(8) uint64_t s_bar[kQ80MaxChunks];
+    __shared__ int s_fail;
+    constexpr bool kProd = NSEQ == 1;                         // the ring holds products w*x instead of weights
+    // ring: [2][64 column quads][32 rows][4]: a lane (= row) reads four consecutive columns with one 16-byte load, and the
+    // 32 lanes' loads are one conflict-free 512-byte run (a scalar load per column cost the chain warp 16 issue slots per
+    // 16 adds and ran at ~7 cycles per add instead of ~4.4)
+    float *s_w = smem_f;
+    float *sx = smem_f + 2 * kQ80ChunkBlocks * 32 * 32;       // [NSEQ][k]
+    const int k = blocks * 32, tid = threadIdx.x;
+    uint8_t *s_raw = reinterpret_cast<uint8_t *>(sx + (size_t)NSEQ * k);  // [blocks][1088]: the tiles as they lie in memory
+    const bool producer = tid < kQ80Producers;
+    const int n_chunks = (blocks + kQ80ChunkBlocks - 1) / kQ80ChunkBlocks;
+    const uint8_t *tile0 = tiled + (size_t)blockIdx.x * blocks * kQ80TileBytes;  // this CTA's 32 rows, block 0
+    if (tid == 0) {
+        s_fail = 0;
+        for (int ch = 0; ch < n_chunks; ch++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(q80_smem_u32(&s_bar[ch])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the weights do not depend on the previous kernel: their copies start before the dependency wait
+        for (int ch = 0; ch < n_chunks; ch++) {
+            const int nb = min(kQ80ChunkBlocks, blocks - ch * kQ80ChunkBlocks);
+            const uint32_t bytes = (uint32_t)nb * kQ80TileBytes;  // (1088 = 68 x 16)
+            const uint32_t bar = q80_smem_u32(&s_bar[ch]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             q80_smem_u32(s_raw + (size_t)ch * kQ80ChunkBlocks * kQ80TileBytes)),
+                         "l"(tile0 + (size_t)ch * kQ80ChunkBlocks * kQ80TileBytes), "r"(bytes), "r"(bar)
+                         : "memory");
+        }
+    }
+    pdl_trigger();
+    pdl_wait();
+    for (int i = tid; i < NSEQ * k; i += blockDim.x) sx[i] = x[i];
+    __syncthreads();  // (the barriers are initialised, the activations staged)
+    constexpr int kItems = kQ80ChunkBlocks * 64;                        // (block, half, row): 16 weights each
+    constexpr int kPer = (kItems + kQ80Producers - 1) / kQ80Producers;  // 3
+    auto convert_chunk = [&](int ch) -> bool {
+        if (!q80_mbar_wait(&s_bar[ch], 0)) return false;
+        float4 *dst = reinterpret_cast<float4 *>(s_w + (ch & 1) * (kQ80ChunkBlocks * 32 * 32));
+#pragma unroll
+        for (int u = 0; u < kPer; u++) {
+            const int item = tid + u * kQ80Producers;
+            const int bl = item >> 6, h = (item >> 5) & 1, r = item & 31;
+            if (item < kItems && ch * kQ80ChunkBlocks + bl < blocks) {
+                const uint8_t *t = s_raw + (size_t)(ch * kQ80ChunkBlocks + bl) * kQ80TileBytes;
+                const uint4 raw = *(reinterpret_cast<const uint4 *>(t + 512 * h) + r);
+                const float d = f16_bits_to_f32(*(reinterpret_cast<const uint16_t *>(t + 1024) + r));
+                const uint32_t ws[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+                const float4 *xs = reinterpret_cast<const float4 *>(sx + (ch * kQ80ChunkBlocks + bl) * 32 + h * 16);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    // q as f32 without the converter unit: the byte q + 128 dropped into the mantissa of 2^23 is 2^23 + 128 + q
+                    float q[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) q[j] = __fsub_rn(__uint_as_float(__byte_perm(ws[g], 0x4B000000u, 0x7650 + j)), 8388736.0f);
+                    float4 o = make_float4(__fmul_rn(d, q[0]), __fmul_rn(d, q[1]), __fmul_rn(d, q[2]), __fmul_rn(d, q[3]));
+                    if (kProd) {
+                        const float4 xv = xs[g];
+                        o = make_float4(__fmul_rn(o.x, xv.x), __fmul_rn(o.y, xv.y), __fmul_rn(o.z, xv.z), __fmul_rn(o.w, xv.w));
+                    }
+                    dst[(bl * 8 + h * 4 + g) * 32 + r] = o;
+                }
+            }
+        }
+        return true;
+    };
+    if (producer && !convert_chunk(0)) s_fail = 1;
+    __syncthreads();
+    const int seq = (tid - kQ80Producers) >> 5, lane = tid & 31;  // chain warps
+    float acc = -0.0f;
+#define Q80_ADD4(v) acc = __fadd_rn(acc, v.x), acc = __fadd_rn(acc, v.y), acc = __fadd_rn(acc, v.z), acc = __fadd_rn(acc, v.w)
+    for (int ch = 0; ch < n_chunks; ch++) {
+        if (producer) {
+            if (ch + 1 < n_chunks && !s_fail && !convert_chunk(ch + 1)) s_fail = 1;
+        } else {
+            const float4 *w = reinterpret_cast<const float4 *>(s_w + (ch & 1) * (kQ80ChunkBlocks * 32 * 32)) + lane;
+            const int nq = min(kQ80ChunkBlocks, blocks - ch * kQ80ChunkBlocks) * 8;  // column quads: a multiple of 8
+            if (kProd) {
+                // two register sets of 16 products alternate; a set is re-loaded right after it has been added
+                float4 a0 = w[0], a1 = w[32], a2 = w[64], a3 = w[96], b0 = w[128], b1 = w[160], b2 = w[192], b3 = w[224];
+                for (int q0 = 0; q0 < nq; q0 += 8) {
+                    Q80_ADD4(a0), Q80_ADD4(a1), Q80_ADD4(a2), Q80_ADD4(a3);
+                    const int qa = min(q0 + 8, nq - 8) * 32;
+                    a0 = w[qa], a1 = w[qa + 32], a2 = w[qa + 64], a3 = w[qa + 96];
+                    Q80_ADD4(b0), Q80_ADD4(b1), Q80_ADD4(b2), Q80_ADD4(b3);
+                    const int qb = min(q0 + 12, nq - 4) * 32;
+                    b0 = w[qb], b1 = w[qb + 32], b2 = w[qb + 64], b3 = w[qb + 96];
+                }
+            } else {
+                const float4 *xs = reinterpret_cast<const float4 *>(sx + (size_t)seq * k + ch * kQ80ChunkBlocks * 32);
+                float4 wv[4], xv[4];
+                auto fetch = [&](int q0) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) wv[j] = w[(q0 + j) * 32], xv[j] = xs[q0 + j];
+                };
+                fetch(0);
+                for (int q0 = 0; q0 < nq; q0 += 4) {
+                    float4 pr[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        pr[j] = make_float4(__fmul_rn(wv[j].x, xv[j].x), __fmul_rn(wv[j].y, xv[j].y), __fmul_rn(wv[j].z, xv[j].z), __fmul_rn(wv[j].w, xv[j].w));
+                    if (q0 + 4 < nq) fetch(q0 + 4);
+                    Q80_ADD4(pr[0]), Q80_ADD4(pr[1]), Q80_ADD4(pr[2]), Q80_ADD4(pr[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#undef Q80_ADD4
+    if (s_fail) {
+        // a copy did not arrive within the limit: wait (bounded again) for the ones still in flight before this CTA's shared
+        // memory is given up, record it, write nothing
+        if (tid == 0) {
+            for (int ch = 0; ch < n_chunks; ch++) q80_mbar_wait(&s_bar[ch], 0);
+            atomicExch(status, 1 + (int)blockIdx.x);
+        }
+        return;
+    }
+    const int row = blockIdx.x * 32 + lane;
+    if (!producer && row < rows) out[(size_t)seq * rows + row] = acc;
+}
+
 // ---- QK-norm + RoPE (+ KV store) -----------------------------------------
 // crates/llamd-runtime/src/layer.rs:120-153, crates/llamd-cpu/src/lib.rs:158-209.
 // One CTA of hd/2 threads per head; thread 0 walks the sum of squares. The
@@ -898,6 +1048,25 @@ void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert
 }
 
 static int g_q80_rows_max_ctas = 148 * 4;
+static int *g_q80_status = nullptr;
+static int *q80_status_word() {
+    if (!g_q80_status) {
+        if (cudaMalloc(&g_q80_status, sizeof(int)) != cudaSuccess || cudaMemsetAsync(g_q80_status, 0, sizeof(int), stream()) != cudaSuccess) {
+            cudaGetLastError();
+            g_q80_status = nullptr;
+        }
+    }
+    return g_q80_status;
+}
+// 0 while every bulk copy of the Q8_0 matvec has arrived within its limit; otherwise 1 + the CTA whose wait ran out (its
+// 32 rows were not written). Synchronises the stream.
+int llamd_fwd_matvec_q8_0_status(void) {
+    if (!g_q80_status) return 0;
+    int h = 0;
+    if (cudaMemcpyAsync(&h, g_q80_status, sizeof(int), cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(stream()) != cudaSuccess) return -1;
+    return h;
+}
 void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks32, int rows, int nseq) {
     const size_t smem = (size_t)nseq * blocks32 * 32 * sizeof(float);
     if (nseq < 1 || nseq > LLAMD_MAX_SEQ || smem > 200 * 1024 || rows <= 0 || blocks32 <= 0) {
@@ -910,10 +1079,26 @@ void llamd_fwd_matvec_q8_0(const void *w, const float *x, float *out, int blocks
     // measured: it wins while its CTAs fit one wave (attn_q 40 -> 10s of us); beyond that the thread-per-row form's
     // deeper occupancy does (lm_head)
     const bool by_rows = smem_rows <= 220 * 1024 && (rows + 31) / 32 <= g_q80_rows_max_ctas;
+    // ... and with the CTA's whole slice of the matrix brought in by bulk copies, where that fits beside the rest
+    const size_t smem_bulk = smem_rows + (size_t)blocks32 * kQ80TileBytes;
+    const bool by_bulk = by_rows && smem_bulk <= 226 * 1024 && (blocks32 + kQ80ChunkBlocks - 1) / kQ80ChunkBlocks <= kQ80MaxChunks &&
+                         ((uintptr_t)w & 15) == 0 && q80_status_word() != nullptr;
     const dim3 grid(by_rows ? (rows + 31) / 32 : (rows + 127) / 128);
 #define Q80_CASE(N)                                                                                                   \
     case N: {                                                                                                          \
         static size_t configured = 0, configured_rows = 0;                                                             \
+        if (by_bulk) {                                                                                                 \
+            static size_t configured_bulk = 0;                                                                         \
+            if (smem_bulk > configured_bulk) {                                                                         \
+                if (cudaFuncSetAttribute(matvec_q8_0_bulk_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bulk) != cudaSuccess) { \
+                    set_error_msg("matvec_q8_0: shared memory attribute");                                             \
+                    return;                                                                                            \
+                }                                                                                                      \
+                configured_bulk = smem_bulk;                                                                           \
+            }                                                                                                          \
+            launch_kc(PDL_OTHER, "matvec_q8_0_bulk", matvec_q8_0_bulk_kernel<N>, grid, dim3(kQ80Producers + 32 * N), smem_bulk, t, x, out, blocks32, rows, q80_status_word()); \
+            break;                                                                                                     \
+        }                                                                                                              \
         if (by_rows) {                                                                                                 \
             if (smem_rows > configured_rows) {                                                                         \
                 cudaFuncSetAttribute(matvec_q8_0_rows_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows); \
