@@ -372,6 +372,9 @@ def main():
         m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
     if ep and not args.ep_nccl:
+        if args.batch_sweep:
+            m.prefill_tile = max(max_seq, 8)  # the tile exchange's capacity is fixed at the attach: size it for the batches
+
         def _gather(b):
             out = [None] * world
             dist.all_gather_object(out, b)
@@ -432,13 +435,16 @@ def main():
                 toks = m.forward_batch(toks, [p0] * B)
                 p0 += 1
             backend.sync()
+            barrier()
             t1 = time.perf_counter()
             for _ in range(K):
                 toks = m.forward_batch(toks, [p0] * B)
                 p0 += 1
             backend.sync()
-            dt = time.perf_counter() - t1
-            log(f"[batch-sweep] batch {B}: {B * K / dt:.1f} tok/s aggregate, {dt / K * 1e3:.3f} ms/pass, position ~{p0}")
+            barrier()
+            dt = max_over_ranks(time.perf_counter() - t1)
+            log(f"[batch-sweep] batch {B} per GPU x {world} GPU(s){' expert-parallel' if ep else ''}: {world * B * K / dt:.1f} tok/s aggregate, "
+                f"{dt / K * 1e3:.3f} ms/pass, position ~{p0}")
         return
     if args.resident_phases:
         m.set_option("resident", 1)

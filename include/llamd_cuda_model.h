@@ -53,9 +53,13 @@ enum {
  * llamd_cuda_ep_init(rank, world, id) after llamd_cuda_set_device and BEFORE
  * llamd_model_create. A model created afterwards keeps only experts
  * [rank*n_expert/world, (rank+1)*n_expert/world) of what set_tensor is given,
- * decodes its own sequence (max_seq 1), and per MoE layer all-gathers the routed
+ * decodes its own sequence(s), and per MoE layer all-gathers the routed
  * requests (ids + Q8_K activation) and returns expert outputs to their home rank
- * over NCCL. Every rank must make the same sequence of forward calls. */
+ * over NCCL. Every rank must make the same sequence of forward calls.
+ * With max_seq > 1 (peer-memory form only, below): llamd_model_forward_batch of 2..max_seq sequences runs as one tile
+ * of the peer-memory exchange -- one rendezvous each way per layer for ALL of a rank's sequences, the expert matmuls
+ * as grouped GEMMs over every rank's sequences -- and gives each sequence the single-sequence pass's bits. A batch may
+ * not exceed llamd_model_ep_tile_cap; the ranks' batch sizes need not agree, their sequence of calls must. */
 int llamd_cuda_ep_unique_id(void *out128);
 int llamd_cuda_ep_init(int rank, int world, const void *id128);
 void llamd_cuda_ep_finalize(void);
@@ -143,8 +147,8 @@ int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
 int llamd_model_forward(llamd_model *m, int32_t token, int32_t pos, int32_t *out_token);
 /* DeviceModel::forward_batch (device.rs:741-962): nseq independent sequences. Up to LLAMD_MAX_SEQ (8) they share
  * each weight read inside the nseq kernels; from 9 to max_seq (at most LLAMD_MAX_BATCH) the pass runs as a prefill
- * tile whose tokens belong to different sequences, on the integer GEMM. Either way sequence s gets exactly the
- * single-sequence pass's bits. */
+ * tile whose tokens belong to different sequences, on the integer GEMM (with sharded experts: from 2 on, through the
+ * tile exchange over peer memory). Either way sequence s gets exactly the single-sequence pass's bits. */
 int llamd_model_forward_batch(llamd_model *m, const int32_t *tokens, const int32_t *positions, int nseq,
                               int32_t *out_tokens);
 /* VulkanModel::prefill (crates/llamd-runtime/src/vulkan_model.rs:877-907):

@@ -634,8 +634,8 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     m->layers.resize(hp->n_layer);
     m->ep_rank = llamd_cuda_ep_rank();
     m->ep_world = llamd_cuda_ep_world();
-    if (m->ep_world > 1 && (hp->n_expert % m->ep_world != 0 || max_seq != 1)) {
-        set_error_msg("model: expert parallelism needs n_expert divisible by the world size and max_seq 1");
+    if (m->ep_world > 1 && hp->n_expert % m->ep_world != 0) {
+        set_error_msg("model: expert parallelism needs n_expert divisible by the world size");
         delete m;
         return nullptr;
     }
@@ -905,6 +905,8 @@ int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32
     if (!m || !tokens || !positions || !out_tokens) return -1;
     m->err.clear();
     if (nseq > LLAMD_MAX_SEQ && nseq <= m->max_seq) return run_wide_batch(*m, tokens, positions, nseq, out_tokens);
+    // sharded experts: the per-op pass exchanges one sequence per rank; several go through the tile exchange
+    if (m->ep_world > 1 && nseq > 1 && nseq <= m->max_seq) return run_wide_batch(*m, tokens, positions, nseq, out_tokens);
     return run(*m, tokens, positions, nseq, out_tokens);
 }
 
@@ -1259,8 +1261,10 @@ int llamd_model_verify(llamd_model *h, const int32_t *tokens, int n_tokens, int 
 // sequences (own cache, own position), so that the matmuls run on the integer GEMM with every weight read once for all
 // sequences. Per sequence the arithmetic is the single-sequence pass's.
 static int run_wide_batch(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int32_t *out_tokens) {
-    if (m.ep_world > 1) {
-        m.err = "forward_batch: wide batches are not available with sharded experts";
+    if (m.ep_world > 1 && (!m.ep_p2p || nseq > m.pf.ep_cap)) {
+        // sharded experts: the batch runs as one tile of the peer-memory exchange (one rendezvous each way per layer for
+        // all of a rank's sequences); every rank must make the same sequence of calls, with any batch size of its own
+        m.err = "forward_batch: with sharded experts a batch needs the peer-memory attach, and at most as many sequences as its tile capacity";
         return -1;
     }
     for (int s = 0; s < nseq; s++) {
@@ -1288,7 +1292,13 @@ static int run_wide_batch(Model &m, const int32_t *tokens, const int32_t *positi
     }
     queue_prefill_tile(m, nseq, n_kv_max, true, true, true, m.logits.as<float>());
     if (cudaMemcpyAsync(m.pf.h_out_tokens, m.pf.out_tokens.p, (size_t)nseq * 4, cudaMemcpyDeviceToHost, stream()) != cudaSuccess) return -1;
+    m.h_out[m.max_seq] = 0;
+    if (m.ep_p2p) cudaMemcpyAsync(m.h_out + m.max_seq, m.ep_status.p, 4, cudaMemcpyDeviceToHost, stream());
     if (llamd_fwd_sync() != 0) return -1;
+    if (m.h_out[m.max_seq] != 0) {
+        m.err = ep_wait_message(m.h_out[m.max_seq]);
+        return -1;
+    }
     for (int s = 0; s < nseq; s++) {
         if (m.pf.h_out_tokens[s] < 0 || m.pf.h_out_tokens[s] >= m.hp.n_vocab) {
             m.err = "argmax returned " + std::to_string(m.pf.h_out_tokens[s]);

@@ -11,6 +11,9 @@ with both collectives replaced by stores into the other ranks' buffers over
 NVLink (CUDA IPC) and arrival counters, and in that form the tiled prefill is
 checked too: every rank's tile gathered on every rank, the owned experts run on
 the grouped GEMM over all ranks' tokens, rows stored to the token's home rank.
+Batches of sequences (forward_batch, 3 and 12 per rank, each rank its own) go
+through the same tile exchange: one rendezvous each way per layer for all of a
+rank's sequences.
 """
 import json
 import os
@@ -54,7 +57,21 @@ def main():
             toks.append(tok)
         return toks, m.logits()[0].copy()
 
-    m = M.CudaModel.load_synthetic(hp, 5, max_kv=max_kv)
+    n_batch = 12
+    batch_tokens = synth.token_ids(n_batch * 4, hp["n_vocab"], 13, "ep.batch", rank).reshape(4, n_batch)
+
+    def batches(m):
+        """Four steps of 12 sequences, then the first 3 sequences one step further: tokens and logits of every step."""
+        out = []
+        for pos in range(4):
+            toks = m.forward_batch(batch_tokens[pos].tolist(), [pos] * n_batch)
+            out.append((toks.tolist(), m.logits(n_batch).copy()))
+        toks = m.forward_batch(batch_tokens[0][:3].tolist(), [4] * 3)
+        out.append((toks.tolist(), m.logits(3).copy()))
+        return out
+
+    m = M.CudaModel.load_synthetic(hp, 5, max_kv=max_kv, max_seq=n_batch)
+    want_batches = batches(m)
     want_toks, want_logits = decode(m)
     single_bytes = m.weight_bytes()
     m.use_graph = False
@@ -69,7 +86,7 @@ def main():
         return obj[0]
 
     M.ep_init(rank, world, share)
-    m = M.CudaModel.load_synthetic(hp, 5, max_kv=max_kv)
+    m = M.CudaModel.load_synthetic(hp, 5, max_kv=max_kv, max_seq=n_batch)
     full_bytes = hp["n_layer"] * 3 * hp["n_expert"] * (hp["n_ff_expert"] * hp["n_embd"] // 256 * 210)
     got_toks, got_logits = decode(m)            # captured graph with the NCCL exchange inside
     m.use_graph = False
@@ -94,11 +111,14 @@ def main():
         m.prefill_tile = tile
         pf_results.append(prefill_then_two(m))
     pf_ok = all(t == want_pf and np.array_equal(lg.view(np.uint32), want_pf_logits.view(np.uint32)) for t, lg in pf_results)
+    got_batches = batches(m)
+    batch_ok = all(gt == wt and np.array_equal(gl.view(np.uint32), wl.view(np.uint32)) for (gt, gl), (wt, wl) in zip(got_batches, want_batches))
+    pf_ok = pf_ok and batch_ok
     ok = (pf_ok and got_toks == want_toks and plain_toks == want_toks and p2p_toks == want_toks and p2p_plain_toks == want_toks
           and np.array_equal(got_logits.view(np.uint32), want_logits.view(np.uint32))
           and np.array_equal(plain_logits.view(np.uint32), want_logits.view(np.uint32))
           and np.array_equal(p2p_logits.view(np.uint32), want_logits.view(np.uint32)))
-    res = dict(rank=rank, ok=bool(ok), prefill_ok=bool(pf_ok), prefill_tokens=[t for t, _ in pf_results], prefill_want=want_pf,
+    res = dict(rank=rank, ok=bool(ok), prefill_ok=bool(pf_ok), batch_ok=bool(batch_ok), prefill_tokens=[t for t, _ in pf_results], prefill_want=want_pf,
                tile_cap=m.ep_tile_cap(), tokens=got_toks, p2p_tokens=p2p_toks, want=want_toks, weight_bytes=m.weight_bytes(), single_bytes=single_bytes,
                full_expert_bytes=full_bytes)
     m.free()
