@@ -443,8 +443,9 @@ def main():
             backend.sync()
             barrier()
             dt = max_over_ranks(time.perf_counter() - t1)
-            log(f"[batch-sweep] batch {B} per GPU x {world} GPU(s){' expert-parallel' if ep else ''}: {world * B * K / dt:.1f} tok/s aggregate, "
-                f"{dt / K * 1e3:.3f} ms/pass, position ~{p0}")
+            if rank == 0:
+                log(f"[batch-sweep] batch {B} per GPU x {world} GPU(s){' expert-parallel' if ep else ''}: {world * B * K / dt:.1f} tok/s aggregate, "
+                    f"{dt / K * 1e3:.3f} ms/pass, position ~{p0}")
         return
     if args.resident_phases:
         m.set_option("resident", 1)
