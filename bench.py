@@ -229,6 +229,8 @@ def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
     # the library default (512) is the reference's; larger tiles fold each expert's weights for more tokens at once
     m.prefill_tile = args.tile if args.tile > 0 else min(len(prompt), 2048)
     m.set_prefill_gemm({"exact": 1, "dp4a": 0, "tc": 2}[args.gemm])
+    if args.prefold:
+        m.set_option("prefill_prefold", 1)
     for _ in range(W):
         m.prefill(prompt, 0)
     backend.sync()
@@ -258,7 +260,7 @@ def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
     line = {"metric": "q6k_moe_prefill_tok_s", "value": world * n * K / (ms.value * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms.value / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 pairs -> f32 (tcgen05, tolerance level)" if args.gemm == "tc" else "i8xi8->i32, f32 tail", "data": "synthetic",
-            "config": {"workload": f"prefill_qwen3moe_q6k_pp{n}", "layers": hp["n_layer"], "tile": m.prefill_tile, "gemm": args.gemm,
+            "config": {"workload": f"prefill_qwen3moe_q6k_pp{n}", "layers": hp["n_layer"], "tile": m.prefill_tile, "gemm": args.gemm, "prefold": bool(args.prefold),
                        "l2": "a tile streams every expert of every layer (23.8 GB): inputs larger than L2"},
             "e2e": {"value": world * n * K / wall, "unit": "tok/s", "h2d_bytes_per_step": 8 * n, "d2h_bytes_per_step": 4},
             "gpu_launches": int(L.llamd_fwd_launch_count() - launches0), "last_token": int(tok),
@@ -293,6 +295,8 @@ def main():
     ap.add_argument("--gemm", default="exact", choices=["exact", "dp4a", "tc"],
                     help="prefill workload: exact = integer tensor path (mma.sync), bit-identical to decode (default); dp4a = the same "
                          "bits, 8 tokens per weight pass; tc = tcgen05 on f16 pairs, tolerance level")
+    ap.add_argument("--prefold", action="store_true", help="prefill workload: keep the expert matrices a second time, folded for the integer "
+                    "GEMM (model option prefill_prefold; +58 GB on the 48-layer model; same bits)")
     ap.add_argument("--tile", type=int, default=0, help="prefill workload: tokens per prefill tile (0: min(prompt, 2048))")
     ap.add_argument("--ep-nccl", action="store_true", help="with --parallelism ep: the two exchanges per layer as NCCL collectives "
                     "(all-gather + grouped send/recv) instead of peer stores with arrival counters")

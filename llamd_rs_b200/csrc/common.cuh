@@ -196,7 +196,12 @@ void moe_group_owned(const int32_t *ids, int n_expert, int n_used, int nseq, int
 // local row block o % out_div (out_tab null: everything into oa / ob).
 void expert_gemm_scatter(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
                          const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows, int n_expert,
-                         float *const *out_tab, int out_div);
+                         float *const *out_tab, int out_div, const void *fa = nullptr, const void *fb = nullptr);
+// Pre-folded expert matrices (prefill): every (expert, 16-row tile) folded once into the integer MMA's operand order and
+// kept (2 bytes per weight); fa / fb above name such copies of wa / wb.
+size_t expert_fold_tile_bytes(int blocks);
+size_t expert_fold_bytes(int blocks, int rows, int n_expert);
+void expert_prefold(const void *w, void *dst, int blocks, int rows, int n_expert);
 // expert parallelism, a prefill tile (ep.cu)
 void ep_push_tile(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *const *ids_tab, float *const *ad_tab,
                   int8_t *const *aq_tab, unsigned int *const *disp_tab, unsigned int *epoch, unsigned int *push_done, int T, int cap,

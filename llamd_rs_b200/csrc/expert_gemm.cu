@@ -51,6 +51,10 @@ struct GemmParams {
     // expert parallelism: output row block o lives on GPU o / out_div, at local row block o % out_div (null: out[j])
     float *const *out_tab;
     int out_div;
+    // pre-folded copies of the matrices (grouped kernel; null: fold from w): [expert][row tile] images of fold_tile_bytes,
+    // each exactly what fold_row_tile leaves in shared memory (A fragments, then the 16 x nb block scales)
+    const uint8_t *folded[3];
+    long long fold_tile_bytes;
 };
 
 // Ask L2 for the tiles that hold the 16 x nb blocks starting at block `unit0` (a hint: nothing waits on it).
@@ -195,6 +199,7 @@ __device__ __forceinline__ void fold_row_tile(const uint8_t *__restrict__ w, siz
 // Warp `warp` of `nwarps` takes tiles tile_lo + warp, + nwarps, ... below tile_hi. Per block b the warp copies its
 // 8 tokens' 256 activation bytes into its own buffer with coalesced 16-byte loads; the next block's bytes wait in
 // registers meanwhile.
+template <int DEPTH>
 __device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int row0, int rows, int first, int count, int tile_lo, int tile_hi,
                                                 const uint4 *s_frag, const float *s_d, uint32_t *s_b, int warp, int nwarps, int lane) {
     const int nb = p.nb;
@@ -222,52 +227,65 @@ __device__ __forceinline__ void mma_token_tiles(const GemmParams &p, int j, int 
         for (int i = 0; i < 4; i++)
 #pragma unroll
             for (int r = 0; r < 8; r++) sums[i][r] = 0.0f;
-        uint4 st[4];
+        // The tokens' activation bytes of the next DEPTH blocks wait in registers. (DEPTH 3-4 was measured: no faster than
+        // 1 -- the warps wait on the tile's own copy, on shared-memory and MMA latency and on fixed-latency dependencies
+        // in equal parts, at 12 warps per SM -- so the kernels use 1 and keep their registers.)
+        uint4 st[DEPTH][4];
+        float an[DEPTH][2];
 #pragma unroll
-        for (int i = 0; i < 4; i++) st[i] = __ldg(src[i]);
-        float a0n = __ldg(p.ad + ia0 * nb), a1n = __ldg(p.ad + ia1 * nb);
-        for (int b = 0; b < nb; b++) {
+        for (int s = 0; s < DEPTH; s++) {
+            if (s < nb) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(s_b + dsto[i]) = st[i];
-            __syncwarp();
-            if (b + 1 < nb) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) st[i] = __ldg(src[i] + (size_t)(b + 1) * 16);
+                for (int i = 0; i < 4; i++) st[s][i] = __ldg(src[i] + (size_t)s * 16);
+                an[s][0] = __ldg(p.ad + ia0 * nb + s);
+                an[s][1] = __ldg(p.ad + ia1 * nb + s);
             }
-            const float a0 = a0n, a1 = a1n;
-            if (b + 1 < nb) {
-                a0n = __ldg(p.ad + ia0 * nb + b + 1);
-                a1n = __ldg(p.ad + ia1 * nb + b + 1);
-            }
-            const float d0 = s_d[m0 * nb + b], d1 = s_d[m1 * nb + b];
-            const float dsc[4] = {__fmul_rn(d0, a0), __fmul_rn(d0, a1), __fmul_rn(d1, a0), __fmul_rn(d1, a1)};
-            const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + (lane ^ (lane >> 3) ^ (b & 7));
-            const uint32_t *bt = s_b + g4 * kTokStride + q4;
+        }
+        for (int b0 = 0; b0 < nb; b0 += DEPTH) {
 #pragma unroll
-            for (int r = 0; r < 8; r++) {
-                const uint4 ah = fr[(r * 2 + 0) * 32], al = fr[(r * 2 + 1) * 32];
-                const uint32_t b0 = bt[r * 8], b1 = bt[r * 8 + 4];
-                int ch[4], cl[4];
-                mma_s8(ch, ah, b0, b1);
-                mma_s8(cl, al, b0, b1);
+            for (int s = 0; s < DEPTH; s++) {
+                const int b = b0 + s;
+                if (b >= nb) break;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    // aux = 64*hi + lo as a float, exactly (|aux| < 2^24). Two routes share the work between pipes:
-                    // the int->float converter (a quarter-rate unit), and an arithmetic route for the fourth output:
-                    // |hi|, |lo| < 2^22, so adding them to 1.5*2^23 as integers and subtracting the constant as floats
-                    // converts each exactly, and 64*fh + fl is exact because the sum is representable.
-                    float aux;
-                    if (i < 3) {
-                        aux = (float)(ch[i] * 64 + cl[i]);
-                    } else {
-                        const float fh = __fsub_rn(__int_as_float(0x4B400000 + ch[i]), 12582912.0f);
-                        const float fl = __fsub_rn(__int_as_float(0x4B400000 + cl[i]), 12582912.0f);
-                        aux = __fmaf_rn(fh, 64.0f, fl);
-                    }
-                    sums[i][r] = __fadd_rn(sums[i][r], __fmul_rn(dsc[i], aux));
+                for (int i = 0; i < 4; i++) *reinterpret_cast<uint4 *>(s_b + dsto[i]) = st[s][i];
+                __syncwarp();
+                const float a0 = an[s][0], a1 = an[s][1];
+                if (b + DEPTH < nb) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) st[s][i] = __ldg(src[i] + (size_t)(b + DEPTH) * 16);
+                    an[s][0] = __ldg(p.ad + ia0 * nb + b + DEPTH);
+                    an[s][1] = __ldg(p.ad + ia1 * nb + b + DEPTH);
                 }
+                const float d0 = s_d[m0 * nb + b], d1 = s_d[m1 * nb + b];
+                const float dsc[4] = {__fmul_rn(d0, a0), __fmul_rn(d0, a1), __fmul_rn(d1, a0), __fmul_rn(d1, a1)};
+                const uint4 *fr = s_frag + (size_t)b * 8 * 2 * 32 + (lane ^ (lane >> 3) ^ (b & 7));
+                const uint32_t *bt = s_b + g4 * kTokStride + q4;
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    const uint4 ah = fr[(r * 2 + 0) * 32], al = fr[(r * 2 + 1) * 32];
+                    const uint32_t b0w = bt[r * 8], b1w = bt[r * 8 + 4];
+                    int ch[4], cl[4];
+                    mma_s8(ch, ah, b0w, b1w);
+                    mma_s8(cl, al, b0w, b1w);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        // aux = 64*hi + lo as a float, exactly (|aux| < 2^24). Two routes share the work between pipes:
+                        // the int->float converter (a quarter-rate unit), and an arithmetic route for the fourth output:
+                        // |hi|, |lo| < 2^22, so adding them to 1.5*2^23 as integers and subtracting the constant as floats
+                        // converts each exactly, and 64*fh + fl is exact because the sum is representable.
+                        float aux;
+                        if (i < 3) {
+                            aux = (float)(ch[i] * 64 + cl[i]);
+                        } else {
+                            const float fh = __fsub_rn(__int_as_float(0x4B400000 + ch[i]), 12582912.0f);
+                            const float fl = __fsub_rn(__int_as_float(0x4B400000 + cl[i]), 12582912.0f);
+                            aux = __fmaf_rn(fh, 64.0f, fl);
+                        }
+                        sums[i][r] = __fadd_rn(sums[i][r], __fmul_rn(dsc[i], aux));
+                    }
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
         // y = ((((((s0+s1)+s2)+s3)+s4)+s5)+s6)+s7, then scatter
         float tot[4];
@@ -328,6 +346,11 @@ __global__ void __launch_bounds__(128, HOIST ? 3 : 5) q6k_gemm_grouped_kernel(co
             const int px = (int)(lin % gridDim.x), pe = (int)(lin / gridDim.x);
             const int pj = job_of_tile(p, px);
             const int prow0 = (px - p.tile_begin[pj]) * kGemmRows;
+            if (p.folded[pj]) {
+                const int tiles_j = (p.rows[pj] + kGemmRows - 1) / kGemmRows;
+                const uint8_t *src = p.folded[pj] + ((size_t)pe * tiles_j + (size_t)(px - p.tile_begin[pj])) * (size_t)p.fold_tile_bytes;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)p.fold_tile_bytes) : "memory");
+            } else
             prefetch_row_tile(p.w[pj], (size_t)pe * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)prow0 * nb, p.rows[pj] - prow0, nb);
         }
     }
@@ -340,10 +363,39 @@ __global__ void __launch_bounds__(128, HOIST ? 3 : 5) q6k_gemm_grouped_kernel(co
     const int count = p.gstart ? p.gcount[e] : p.n_tokens;
     if (count <= 0) return;
     const size_t unit0 = (size_t)e * (size_t)(p.gstart ? p.expert_units : 0) + (size_t)row0 * nb;
-    fold_row_tile<128, HOIST>(p.w[j], unit0, rows - row0, nb, s_frag, s_d, tid);
+    if (p.folded[j]) {
+        // the tile was folded when the model was loaded: its image comes straight into place, 16 bytes per request, and
+        // the CTA's time goes to the MMAs instead of to turning Q6_K blocks into operands again
+        const int tiles_j = (rows + kGemmRows - 1) / kGemmRows;
+        const uint8_t *src = p.folded[j] + ((size_t)e * tiles_j + (size_t)(row0 / kGemmRows)) * (size_t)p.fold_tile_bytes;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+        const int n16 = (int)(p.fold_tile_bytes >> 4);
+        for (int i = tid; i < n16; i += 128)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * (uint32_t)i), "l"(src + 16 * (size_t)i) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+        fold_row_tile<128, HOIST>(p.w[j], unit0, rows - row0, nb, s_frag, s_d, tid);
+    }
     __syncthreads();
     uint32_t *s_b = reinterpret_cast<uint32_t *>(s_d + kGemmRows * nb) + (size_t)warp * 8 * kTokStride;
-    mma_token_tiles(p, j, row0, rows, first, count, 0, (count + 7) >> 3, s_frag, s_d, s_b, warp, 4, lane);
+    mma_token_tiles<1>(p, j, row0, rows, first, count, 0, (count + 7) >> 3, s_frag, s_d, s_b, warp, 4, lane);
+}
+
+// Folds every (expert, row tile) of one matrix once and keeps the image: grid (row tiles, experts).
+__global__ void __launch_bounds__(128) q6k_prefold_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ dst, int rows, int nb,
+                                                          long long expert_units, long long tile_bytes) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint4 *s_frag = reinterpret_cast<uint4 *>(smem);
+    float *s_d = reinterpret_cast<float *>(smem + (size_t)nb * 8 * 2 * 32 * 16);
+    const int tid = threadIdx.x, row0 = blockIdx.x * kGemmRows, e = blockIdx.y;
+    for (int i = tid; i < kGemmRows * nb; i += 128) s_d[i] = 0.0f;  // (rows past the matrix: fold_store leaves their scales alone)
+    __syncthreads();
+    fold_row_tile<128, false>(w, (size_t)e * (size_t)expert_units + (size_t)row0 * nb, rows - row0, nb, s_frag, s_d, tid);
+    __syncthreads();
+    uint4 *out = reinterpret_cast<uint4 *>(dst + ((size_t)e * gridDim.x + blockIdx.x) * (size_t)tile_bytes);
+    const int n16 = (int)(tile_bytes >> 4);
+    for (int i = tid; i < n16; i += 128) out[i] = reinterpret_cast<const uint4 *>(smem)[i];
 }
 
 // One group of n_tokens tokens; gridDim.x resident CTAs share the (row tile, chunk of kChunkTiles token tiles) items,
@@ -377,7 +429,7 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_dense_kernel(const GemmParams
             fold_row_tile<256, false>(p.w[j], (size_t)row0 * nb, p.rows[j] - row0, nb, s_frag, s_d, tid);
             __syncthreads();
         }
-        mma_token_tiles(p, j, row0, p.rows[j], 0, p.n_tokens, ch * kChunkTiles, min(n_tiles, (ch + 1) * kChunkTiles), s_frag, s_d, s_b, warp, 8,
+        mma_token_tiles<1>(p, j, row0, p.rows[j], 0, p.n_tokens, ch * kChunkTiles, min(n_tiles, (ch + 1) * kChunkTiles), s_frag, s_d, s_b, warp, 8,
                         lane);
     }
 }
@@ -476,14 +528,36 @@ void llamd_fwd_gemm_tokens(const void *w0, const void *w1, const void *w2, const
 void llamd_fwd_expert_gemm(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
                            const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows,
                            int n_expert) {
-    expert_gemm_scatter(wa, wb, gstart, gcount, act_map, pslot, aq_rm, ad, oa, ob, blocks, rows, n_expert, nullptr, 1);
+    expert_gemm_scatter(wa, wb, gstart, gcount, act_map, pslot, aq_rm, ad, oa, ob, blocks, rows, n_expert, nullptr, 1, nullptr, nullptr);
 }
 
 }  // extern "C"
 
+size_t llamd::expert_fold_tile_bytes(int blocks) { return (size_t)blocks * 8 * 2 * 32 * 16 + (size_t)kGemmRows * blocks * 4; }
+size_t llamd::expert_fold_bytes(int blocks, int rows, int n_expert) {
+    return expert_fold_tile_bytes(blocks) * (size_t)((rows + kGemmRows - 1) / kGemmRows) * (size_t)n_expert;
+}
+void llamd::expert_prefold(const void *w, void *dst, int blocks, int rows, int n_expert) {
+    const size_t tile_bytes = expert_fold_tile_bytes(blocks);
+    static size_t configured = 0;
+    if (tile_bytes > 48 * 1024 && tile_bytes > configured) {
+        if (cudaFuncSetAttribute(q6k_prefold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_bytes) != cudaSuccess) {
+            set_error_msg("expert prefold: shared memory attribute");
+            return;
+        }
+        configured = tile_bytes;
+    }
+    if (n_expert > 65535 || n_expert < 1 || rows < 1) {
+        set_error_msg("expert prefold: 1..65535 experts, rows positive");
+        return;
+    }
+    launch_k("q6k_prefold", q6k_prefold_kernel, dim3((rows + kGemmRows - 1) / kGemmRows, n_expert), dim3(128), tile_bytes, (const uint8_t *)w,
+             (uint8_t *)dst, rows, blocks, (long long)rows * blocks, (long long)tile_bytes);
+}
+
 void llamd::expert_gemm_scatter(const void *wa, const void *wb, const int32_t *gstart, const int32_t *gcount, const int32_t *act_map,
                                 const int32_t *pslot, const void *aq_rm, const float *ad, float *oa, float *ob, int blocks, int rows,
-                                int n_expert, float *const *out_tab, int out_div) {
+                                int n_expert, float *const *out_tab, int out_div, const void *fa, const void *fb) {
     if (out_tab && (wb || out_div < 1)) {
         set_error_msg("expert gemm: scattered outputs take one matrix and a positive row-block count per GPU");
         return;
@@ -492,6 +566,8 @@ void llamd::expert_gemm_scatter(const void *wa, const void *wb, const int32_t *g
     p.out_tab = out_tab;
     p.out_div = out_div;
     p.w[0] = (const uint8_t *)wa; p.w[1] = (const uint8_t *)wb;
+    p.folded[0] = (const uint8_t *)fa; p.folded[1] = wb ? (const uint8_t *)fb : nullptr;
+    p.fold_tile_bytes = (long long)expert_fold_tile_bytes(blocks);
     p.out[0] = oa; p.out[1] = ob;
     p.rows[0] = rows; p.rows[1] = rows;
     p.njobs = wb ? 2 : 1;

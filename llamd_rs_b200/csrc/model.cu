@@ -112,6 +112,7 @@ struct Buf {
 struct Layer {
     Buf attn_norm, attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_out, ffn_norm, ffn_gate_inp;
     Buf gate_exps, up_exps, down_exps;
+    Buf gate_fold, up_fold, down_fold;  // option "prefill_prefold": the expert matrices folded once for the prefill GEMM
     bool has_q_norm = false, has_k_norm = false;
     Buf kc, vc;
 };
@@ -169,6 +170,8 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int prefold = 0;         // option "prefill_prefold"; prefold_ready once the folded copies exist
+    bool prefold_ready = false;
     int prefill_gemm = 1;    // 1: integer tensor path (mma.sync), exact; 0: dp4a, 8 tokens per weight pass, exact;
                              // 2: tcgen05 on f16 pairs, tolerance level (gemm_tc.cu)
     int prefill_tile = 512;  // VulkanModel::prefill_tile default max_seq.min(512), vulkan_model.rs:343
@@ -698,7 +701,7 @@ void llamd_model_free(llamd_model *h) {
     }
     for (auto &l : m->layers)
         for (Buf *b : {&l.attn_norm, &l.attn_q, &l.attn_k, &l.attn_v, &l.attn_q_norm, &l.attn_k_norm, &l.attn_out, &l.ffn_norm,
-                       &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.kc, &l.vc})
+                       &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.gate_fold, &l.up_fold, &l.down_fold, &l.kc, &l.vc})
             b->release();
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
@@ -852,6 +855,19 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         m->prefill_attn = value;
         return 0;
     }
+    if (!strcmp(name, "prefill_prefold")) {
+        // 1: keep every expert matrix a second time, folded into the integer MMA's operand order (2 bytes per weight:
+        // +58 GB for the 48-layer model), so that a prefill tile's grouped GEMMs copy operands instead of folding them.
+        // Built at the next prefill; 0 releases the copies. Same bits either way.
+        if (!value && m->prefold_ready) {
+            cudaStreamSynchronize(stream());
+            for (auto &l : m->layers)
+                for (Buf *b : {&l.gate_fold, &l.up_fold, &l.down_fold}) b->release();
+            m->prefold_ready = false;
+        }
+        m->prefold = value != 0;
+        return 0;
+    }
     if (!strcmp(name, "prefill_gemm")) {
         m->prefill_gemm = value;
         return 0;
@@ -920,7 +936,36 @@ int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32
 // arithmetic is the decode pass's, so prefill == sequential decode exactly.
 constexpr int kGroupMaxPairs = 40960;  // what one scatter plan takes (ops.cu: moe_group_kernel)
 
+// The folded copies of the expert matrices (option "prefill_prefold"), made once all tensors are there.
+static bool ensure_prefold(Model &m) {
+    if (!m.prefold || m.prefold_ready) return true;
+    const llamd_hparams &hp = m.hp;
+    const int eb = hp.n_embd / 256, fb = hp.n_ff_expert / 256, n_local = m.own_hi - m.own_lo;
+    const size_t gu = expert_fold_bytes(eb, hp.n_ff_expert, n_local), dn = expert_fold_bytes(fb, hp.n_embd, n_local);
+    const size_t need = (size_t)hp.n_layer * (2 * gu + dn);
+    if (need + ((size_t)2 << 30) > llamd_cuda_free_mem()) {
+        m.err = "prefill_prefold: the folded expert matrices need " + std::to_string(need >> 20) + " MiB of device memory";
+        return false;
+    }
+    for (auto &l : m.layers) {
+        if (!l.gate_fold.alloc(gu) || !l.up_fold.alloc(gu) || !l.down_fold.alloc(dn)) {
+            m.err = std::string("prefill_prefold: ") + llamd_cuda_last_error_string();
+            return false;
+        }
+        expert_prefold(l.gate_exps.p, l.gate_fold.p, eb, hp.n_ff_expert, n_local);
+        expert_prefold(l.up_exps.p, l.up_fold.p, eb, hp.n_ff_expert, n_local);
+        expert_prefold(l.down_exps.p, l.down_fold.p, fb, hp.n_embd, n_local);
+    }
+    if (llamd_fwd_sync() != 0) {
+        m.err = std::string("prefill_prefold: ") + llamd_cuda_last_error_string();
+        return false;
+    }
+    m.prefold_ready = true;
+    return true;
+}
+
 static bool prefill_alloc(Model &m, int tile) {
+    if (!ensure_prefold(m)) return false;
     Model::Prefill &p = m.pf;
     if (p.tile >= tile) return true;
     if (p.ep_cap) {
@@ -1076,9 +1121,10 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
             moe_group_owned(p.ids_all.as<int32_t>(), ne, nu, G, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
                             p.pslot.as<int32_t>(), nullptr, nullptr, m.own_lo, m.own_hi);
             llamd_fwd_q8k_residue_major(p.aq_all.as<int8_t>(), p.aq_all_rm.p, (size_t)G * eb);
+            const bool pre = m.prefold_ready;
             expert_gemm_scatter(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>() + m.own_lo, p.gcount.as<int32_t>() + m.own_lo,
                                 p.ptoken.as<int32_t>(), p.pslot.as<int32_t>(), p.aq_all_rm.p, p.ad_all.as<float>(), p.gate_all.as<float>(),
-                                p.up_all.as<float>(), eb, ffe, n_local, nullptr, 1);
+                                p.up_all.as<float>(), eb, ffe, n_local, nullptr, 1, pre ? l.gate_fold.p : nullptr, pre ? l.up_fold.p : nullptr);
             // (every gathered pair, owned or not: the others' rows are never read)
             llamd_fwd_silu_mul_quant(p.gate_all.as<float>(), p.up_all.as<float>(), nullptr, p.aq2_all.as<int8_t>(), p.ad2_all.as<float>(),
                                      G * nu * ffe);
@@ -1103,12 +1149,15 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
                                      p.pslot.as<int32_t>(), p.aq2_rm.p, p.down.as<float>(), nullptr, ffe / 256, E, ne, T);
         } else if (gemm) {
             llamd_fwd_q8k_residue_major(p.aq.as<int8_t>(), p.aq_rm.p, (size_t)T * eb);
-            llamd_fwd_expert_gemm(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
-                                  p.pslot.as<int32_t>(), p.aq_rm.p, p.ad.as<float>(), p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne);
+            const bool pre = m.prefold_ready;
+            expert_gemm_scatter(l.gate_exps.p, l.up_exps.p, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.ptoken.as<int32_t>(),
+                                p.pslot.as<int32_t>(), p.aq_rm.p, p.ad.as<float>(), p.gate.as<float>(), p.up.as<float>(), eb, ffe, ne, nullptr, 1,
+                                pre ? l.gate_fold.p : nullptr, pre ? l.up_fold.p : nullptr);
             llamd_fwd_silu_mul_quant(p.gate.as<float>(), p.up.as<float>(), nullptr, p.aq2.as<int8_t>(), p.ad2.as<float>(), T * nu * ffe);
             llamd_fwd_q8k_residue_major(p.aq2.as<int8_t>(), p.aq2_rm.p, (size_t)T * nu * (ffe / 256));
-            llamd_fwd_expert_gemm(l.down_exps.p, nullptr, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.pslot.as<int32_t>(),
-                                  p.pslot.as<int32_t>(), p.aq2_rm.p, p.ad2.as<float>(), p.down.as<float>(), nullptr, ffe / 256, E, ne);
+            expert_gemm_scatter(l.down_exps.p, nullptr, p.gstart.as<int32_t>(), p.gcount.as<int32_t>(), p.pslot.as<int32_t>(),
+                                p.pslot.as<int32_t>(), p.aq2_rm.p, p.ad2.as<float>(), p.down.as<float>(), nullptr, ffe / 256, E, ne, nullptr, 1,
+                                pre ? l.down_fold.p : nullptr, nullptr);
         } else {
             llamd_fwd_expert_major(l.gate_exps.p, l.up_exps.p, p.work.as<int32_t>(), p.n_work.as<int32_t>(), max_items,
                                    p.ptoken.as<int32_t>(), p.pslot.as<int32_t>(), p.aq.as<int8_t>(), p.ad.as<float>(), p.gate.as<float>(),

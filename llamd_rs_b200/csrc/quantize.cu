@@ -210,6 +210,28 @@ __global__ void __launch_bounds__(256) silu_mul_quant_kernel(const float *__rest
     q8k_quantize_block(v, lane, qs + (size_t)warp * 256, d + warp, nullptr);
 }
 
+// The same for a handful of blocks (a decode token: 8 experts x 3 blocks): a CTA per block, one element per thread, so
+// that the eight dependent exp evaluations a lane would walk one after the other run side by side; warp 0 quantizes
+// from shared memory. Same operations per element, same bits.
+__global__ void __launch_bounds__(256) silu_mul_quant_small_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                                   float *__restrict__ out, int8_t *__restrict__ qs, float *__restrict__ d,
+                                                                   int nblocks) {
+    __shared__ __align__(16) float s_v[256];
+    pdl_trigger();
+    pdl_wait();
+    const int blk = blockIdx.x, tid = threadIdx.x;
+    const size_t i = (size_t)blk * 256 + tid;
+    const float v = silu_mul(gate[i], up[i]);
+    if (out) out[i] = v;
+    s_v[tid] = v;
+    __syncthreads();
+    if (tid < 32) {
+        const float4 a = reinterpret_cast<const float4 *>(s_v + tid * 8)[0], b = reinterpret_cast<const float4 *>(s_v + tid * 8)[1];
+        const float w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        q8k_quantize_block(w, tid, qs + (size_t)blk * 256, d + blk, nullptr);
+    }
+}
+
 // out[i] = residual[i] + sum_e w[e]*down[e][i], e in routing order
 // (crates/llamd-runtime/src/layer.rs:243-258 then :281-287): the expert sum
 // starts from 0 and the residual is added last.
@@ -309,6 +331,10 @@ void llamd_fwd_silu_mul_quant(const float *gate, const float *up, float *out, in
         return;
     }
     const int nblocks = n / 256;
+    if (nblocks <= 592) {  // (four CTAs per SM: beyond that the warp-per-block form's throughput wins)
+        launch_kc(PDL_SMALL, "silu_mul_quant_small", silu_mul_quant_small_kernel, dim3(nblocks), dim3(256), 0, gate, up, out, qs, d, nblocks);
+        return;
+    }
     launch_kc(PDL_SMALL, "silu_mul_quant", silu_mul_quant_kernel, dim3((nblocks + 7) / 8), dim3(256), 0, gate, up, out, qs, d, nblocks);
 }
 void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd) {

@@ -105,4 +105,11 @@ def test_full_model_prefill_equals_sequential_decode(full):
         gm.prefill_tile = tile
         assert gm.prefill(prompt, 0) == tok
         assert np.array_equal(gm.logits()[0].view(np.uint32), logits.view(np.uint32)), f"tile {tile}"
+    # with the expert matrices folded once and kept (nb = 8 and nb = 3 images at the benchmark's widths)
+    gm.set_option("prefill_prefold", 1)
+    for tile in (16, 512):
+        gm.prefill_tile = tile
+        assert gm.prefill(prompt, 0) == tok
+        assert np.array_equal(gm.logits()[0].view(np.uint32), logits.view(np.uint32)), f"prefold, tile {tile}"
+    gm.set_option("prefill_prefold", 0)
     gm.prefill_tile = 512

@@ -177,6 +177,17 @@ def test_prefill_equals_sequential_decode(tiny):
             assert np.array_equal(gm.logits()[0].view(np.uint32), seq_logits[length].view(np.uint32)), f"tile {tile} length {length}: logits"
     gm.set_prefill_gemm(True)
     gm.set_prefill_attn(True)
+    # the expert matrices folded once and kept (option prefill_prefold): the grouped GEMM copies operands instead of
+    # folding them, the same bits
+    gm.set_option("prefill_prefold", 1)
+    for tile, length in [(4, 5), (8, 17), (16, 37), (512, 37)]:
+        gm.prefill_tile = tile
+        got = gm.prefill(prompt[:length], 0)
+        assert got == seq_tok[length], f"prefold: tile {tile} length {length}"
+        assert np.array_equal(gm.logits()[0].view(np.uint32), seq_logits[length].view(np.uint32)), f"prefold: tile {tile} length {length}: logits"
+    gm.set_option("prefill_prefold", 0)
+    gm.prefill_tile = 512
+    assert gm.prefill(prompt, 0) == seq_tok[len(prompt)]
     for il in range(hp["n_layer"]):
         k, v = gm.read_kv(il, len(prompt))
         assert np.array_equal(k.view(np.uint32), kv_ref[il][0].view(np.uint32)) and np.array_equal(v.view(np.uint32), kv_ref[il][1].view(np.uint32))
