@@ -117,7 +117,7 @@ class ClockSampler:
 def decode_config(args, hp, world, ep, data_plane):
     """What names the workload: the same object in the repo arm's line and in the reference arm's."""
     return {"workload": "decode_qwen3moe_q6k_b1", "layers": hp["n_layer"], "experts": "128x8", "hidden": 2048, "vocab": 151936,
-            "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": "f32",
+            "batch": 1, "prompt": args.prompt, "weights": "Q6_K random-init seed 0", "kv": args.kv,
             "l2": "each token reads ~2.5 GB of a 24 GB model: inputs larger than L2",
             "parallelism": (f"ep{world}: experts sharded {128 // world} per GPU; {data_plane}" if ep else f"replicas x{world}"),
             "arith": args.arith}
@@ -132,7 +132,7 @@ class CpuPort:
     so attention does the work of a token that follows a `start_pos`-token prompt.
     """
 
-    def __init__(self, hp, seed, n_sample, threads, start_pos, room):
+    def __init__(self, hp, seed, n_sample, threads, start_pos, room, kv_f16=False):
         import oracle
         from llamd_rs_b200 import synth
 
@@ -144,11 +144,13 @@ class CpuPort:
                       output=synth.q6k_blocks(hp["n_vocab"] * hp["n_embd"] // 256, seed, "output"),
                       layers=[sample[il % n_sample] for il in range(hp["n_layer"])])
         self.om = oracle.Model(hp, self.w, threads=threads)
-        self.om.kv_new(start_pos + room)
+        self.om.kv_new(start_pos + room, f16=kv_f16)
         kvd = hp["n_head_kv"] * hp["head_dim"]
         if start_pos:
             for il in range(hp["n_layer"]):
                 kv = synth.normal_f32(2 * start_pos * kvd, seed, "cpu.kv", il)
+                if kv_f16:
+                    kv = kv.astype(np.float16).astype(np.float32)
                 self.om.kv_fill(il, 0, kv[:start_pos * kvd], kv[start_pos * kvd:])
         self.pos = self.start = start_pos
         self.tok = int(synth.token_ids(1, hp["n_vocab"], seed, "cpu.first")[0])
@@ -180,7 +182,7 @@ def run_reference(args, rank, world):
     hp["n_layer"] = args.layers
     threads = os.cpu_count() or 1
     total = args.warmup + args.steps
-    port = CpuPort(hp, 0, 2, threads, args.prompt, total + 2)
+    port = CpuPort(hp, 0, 2, threads, args.prompt, total + 2, kv_f16=args.kv == "f16")
     for _ in range(args.warmup):
         port.step()
     t0 = time.perf_counter()
@@ -292,6 +294,9 @@ def main():
                     help="exact: every f32 reduction in the reference's order (token ids bit-exact against the CPU path; what `value` "
                          "is unless asked otherwise). fast: the long sums of a decode token as reduction trees, through the resident "
                          "kernel (tolerance-level floats). An exact run on one GPU also times the fast mode and reports it in detail.fast_arith")
+    ap.add_argument("--kv", default="f32", choices=["f32", "f16"],
+                    help="K/V cache element type. f32: the reference's (every backend of it), and what the committed CPU run of the "
+                         "benchmark used. f16: binary16, rounded once at the store (model option kv_f16; the oracle has the same mode)")
     ap.add_argument("--gemm", default="exact", choices=["exact", "dp4a", "tc"],
                     help="prefill workload: exact = integer tensor path (mma.sync), bit-identical to decode (default); dp4a = the same "
                          "bits, 8 tokens per weight pass; tc = tcgen05 on f16 pairs, tolerance level")
@@ -375,6 +380,8 @@ def main():
     else:
         m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
+    if args.kv == "f16":
+        m.set_option("kv_f16", 1)  # (before the attach: the caches are re-allocated)
     if ep and not args.ep_nccl:
         if args.batch_sweep:
             m.prefill_tile = max(max_seq, 8)  # the tile exchange's capacity is fixed at the attach: size it for the batches
@@ -565,7 +572,7 @@ def main():
     inputs_hash = synth.checksum(np.asarray(prompt, np.int32), synth.layer_weights(hp, 0, 0, with_experts=False)["attn_q"])
     golden_check = None
     golden_path = os.path.join(ROOT, "tests", "golden", "decode_seed0.npz")
-    if rank == 0 and args.prompt == 512 and hp["n_layer"] == 48 and os.path.exists(golden_path):
+    if rank == 0 and args.prompt == 512 and hp["n_layer"] == 48 and args.kv == "f32" and args.arith == "exact" and os.path.exists(golden_path):
         # the CPU oracle's greedy run of this very workload (rank 0's prompt): token ids must be the same
         g = np.load(golden_path)
         want = [int(t) for t in g["chosen"][args.prompt - 1:args.prompt - 1 + len(decoded)]]
@@ -601,7 +608,7 @@ def main():
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:  # (the CPU port is timed beside the single-GPU run only)
         threads = os.cpu_count() or 1
-        port = CpuPort(dict(synth.QWEN3MOE_30B), 0, 2, threads, args.prompt, 8)
+        port = CpuPort(dict(synth.QWEN3MOE_30B), 0, 2, threads, args.prompt, 8, kv_f16=args.kv == "f16")
         port.step()
         secs = [port.step() for _ in range(3)]
         single = port.step(threads=1)

@@ -299,6 +299,21 @@ void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, cons
                                        const float *rope_tab, float eps, int ntok);
 void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
                               int n_head_kv, int hd, const int32_t *meta, int max_kv, int ntok);
+/* ---- a binary16 K/V cache (no counterpart in the reference, whose caches are f32, crates/llamd-runtime/src/kv.rs:27-170;
+ * the benchmark configuration names an f16 cache). kc / vc hold IEEE binary16 elements, same shapes as above. A value is
+ * rounded to nearest-even ONCE, by the store; every load widens it exactly, and all arithmetic stays f32 in the
+ * reference's order, so results are those of the f32 path over a cache of f16-representable values.
+ * llamd_fwd_kv16_expand widens rows [0, n_pos) of both caches into f32 buffers: what the tiled prefill attention
+ * (llamd_fwd_attention_prefill / _tile) reads in place of an f32 cache. */
+void llamd_fwd_qk_norm_rope_store_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc,
+                                       void *vc, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                                       const float *rope_tab, float eps, int nseq, int max_kv);
+void llamd_fwd_qk_norm_rope_store_tile_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc,
+                                            void *vc, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                                            const float *rope_tab, float eps, int ntok);
+void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head,
+                                   int n_head_kv, int hd, const int32_t *meta, int max_kv, int nseq);
+void llamd_fwd_kv16_expand(const void *kc16, const void *vc16, float *kc32, float *vc32, int n_pos, int kv_dim);
 /* ---- two decode launches fewer per layer: the producer's last CTA does the small follow-up op itself ----
  * llamd_fwd_matvec_grouped_x2_silu_quant = llamd_fwd_matvec_grouped_x2 (crates/llamd-rocm/src/forward.rs: planar_grouped_x2)
  * followed by llamd_fwd_silu_mul_quant of oa, ob: qs [slots][rows], d [slots][rows/256]; rows % 256 == 0.

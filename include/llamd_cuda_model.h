@@ -134,6 +134,13 @@ int llamd_model_set_option(llamd_model *m, const char *name, int value);
  * "resident_profile" = 1 makes its CTA 0 accumulate nanoseconds per phase, read by llamd_model_resident_profile
  * (32 values in the kernel's phase order; [30] SM cycles and [31] nanoseconds of the whole kernel).
  *
+ * Option "kv_f16" = 1 (the benchmark configuration's "KV cache is f16"; the reference's caches are f32): the K/V caches
+ * hold binary16 values, rounded to nearest-even once at the store and widened exactly at every load; nothing else changes,
+ * so a pass is bit-identical to the f32 arithmetic over a cache of f16-representable values (which is what the oracle's
+ * f16-store mode computes). The caches are re-allocated and EMPTY after the option changes: set it before the first pass
+ * (and before a peer-memory attach). Every path honours it: per-op decode, batches, the tiled prefill (through an f32 view
+ * of the rows it attends), the resident kernel, llamd_model_read_kv (returns the widened values).
+ *
  * Option "arith" = 1, or a mask of 2 (norms) | 4 (router) | 8 (attention) (no counterpart in the reference's CPU path; its device backends reduce in parallel too): the
  * resident kernel sums the 2048-term sums of the two norms and of the router's dots, the softmax sum and the weighted
  * values of attention as reduction trees instead of walking them in the reference's order. Integers, indices, `exp`

@@ -28,6 +28,8 @@
 #include "q6k_layout.cuh"
 #include "quant.cuh"
 #include "route.cuh"
+#include <cuda_fp16.h>
+
 #include "mega.cuh"
 
 namespace llamd {
@@ -71,6 +73,28 @@ __host__ __device__ inline MegaSmem mega_smem(int E, int qd, int hd, int act_blo
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int *p) {
     unsigned int v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Four consecutive cache elements as f32: the cache holds f32, or binary16 values that widen exactly.
+__device__ __forceinline__ float4 kv_ld4(const float *base, size_t elem, bool kv16, bool through_l2) {
+    if (kv16) {
+        const uint2 *p = reinterpret_cast<const uint2 *>(reinterpret_cast<const __half *>(base) + elem);
+        const uint2 u = through_l2 ? __ldcg(p) : __ldg(p);
+        const __half2 a = *reinterpret_cast<const __half2 *>(&u.x), b = *reinterpret_cast<const __half2 *>(&u.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    const float4 *p = reinterpret_cast<const float4 *>(base + elem);
+    return through_l2 ? __ldcg(p) : __ldg(p);
+}
+// Store one element; returns the value as the cache now holds it.
+__device__ __forceinline__ float kv_st(float *base, size_t elem, float v, bool kv16) {
+    if (kv16) {
+        const __half h = __float2half_rn(v);
+        reinterpret_cast<__half *>(base)[elem] = h;
+        return __half2float(h);
+    }
+    base[elem] = v;
     return v;
 }
 
@@ -411,7 +435,7 @@ __device__ __noinline__ void mega_phase_a(const MegaParams &p, const MegaCtx &c,
     const int tid = threadIdx.x, E = c.E, nu = c.nu, eb = c.eb, qd = c.qd, kvd = c.kvd;
     if (!tail && c.n_kv > 1) {
         // this layer's cached K and V rows (evicted since the last token): every CTA asks L2 for a slice of each
-        const size_t kv_bytes = (size_t)(c.n_kv - 1) * kvd * 4;
+        const size_t kv_bytes = (size_t)(c.n_kv - 1) * kvd * (p.kv16 ? 2 : 4);
         const size_t per = ((kv_bytes + c.G - 1) / c.G + 15) & ~(size_t)15, off = per * c.cta;
         if (off < kv_bytes) {
             const size_t n = kv_bytes - off < per ? kv_bytes - off : per;
@@ -483,7 +507,8 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
     const int tid = threadIdx.x, hd = c.hd, ratio = c.ratio, half = c.half, kvd = c.kvd, pos = c.pos, t_lo = c.t_lo;
     float *s_qraw = S.s_tile, *s_qr = S.s_tile + ratio * hd, *s_kt = S.s_tile + 2 * ratio * hd;  // [ratio][hd] x2, [chunk][hd + 4]
     const int stride = hd + 4, hd4 = hd / 4, cnt = c.t_hi - t_lo;
-    const float *kb = ly.kc + (size_t)c.b1_kvh * hd;
+    const bool kv16 = p.kv16 != 0;
+    const size_t kb = (size_t)c.b1_kvh * hd;  // element offset of this kv head inside a cache row
     // the chunk's cached K rows start their trip first (the row of this very position is made below)
     constexpr int kLd = 4;
     for (int i0 = 0; i0 < cnt * hd4; i0 += kLd * kMegaThreads) {
@@ -492,7 +517,7 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
         for (int j = 0; j < kLd; j++) {
             const int idx = i0 + tid + j * kMegaThreads;
             const int r = idx / hd4, cc = idx - r * hd4;
-            reg[j] = (idx < cnt * hd4 && t_lo + r != pos) ? __ldg(reinterpret_cast<const float4 *>(kb + (size_t)(t_lo + r) * kvd) + cc)
+            reg[j] = (idx < cnt * hd4 && t_lo + r != pos) ? kv_ld4(ly.kc, kb + (size_t)(t_lo + r) * kvd + 4 * cc, kv16, false)
                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         if (i0 == 0) {  // the group's q heads and this token's k, v head, raw
@@ -549,9 +574,9 @@ __device__ __noinline__ void mega_phase_b1(const MegaParams &p, const MegaCtx &c
     __syncthreads();
     if (c.b1_has_pos) {  // this position's K (roped) and V go into the cache and into the chunk
         for (int i = tid; i < hd; i += kMegaThreads) {
-            ly.kc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = S.s_tmp[i];
-            ly.vc[(size_t)pos * kvd + (size_t)c.b1_kvh * hd + i] = S.s_v[i];
-            s_kt[(pos - t_lo) * stride + i] = S.s_tmp[i];
+            const float kept = kv_st(ly.kc, (size_t)pos * kvd + kb + i, S.s_tmp[i], kv16);
+            kv_st(ly.vc, (size_t)pos * kvd + kb + i, S.s_v[i], kv16);
+            s_kt[(pos - t_lo) * stride + i] = kept;  // (what a later token will read from the cache)
         }
         __syncthreads();
     }
@@ -592,7 +617,8 @@ __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c
     const int tid = threadIdx.x, hd = c.hd, cols = c.cols, kvd = c.kvd, n_kv = c.n_kv, pos = c.pos;
     const int h = c.cta / kMegaSplit, cpart = c.cta - h * kMegaSplit, kvh = h / c.ratio;
     constexpr int kLd = 8;
-    const float *vb = ly.vc + (size_t)kvh * hd + (size_t)cpart * cols;
+    const bool kv16 = p.kv16 != 0;
+    const size_t vb = (size_t)kvh * hd + (size_t)cpart * cols;  // element offset of this item's columns inside a cache row
     const int cols4 = cols / 4;
     float acc = 0.0f;
     for (int t0 = 0; t0 < n_kv; t0 += kMegaThreads) {
@@ -606,8 +632,7 @@ __device__ __noinline__ void mega_phase_b2(const MegaParams &p, const MegaCtx &c
             const int t = t0 + r;
             // (this position's row was stored by another CTA before the barrier: read it from L2)
             reg[j] = idx >= cnt * cols4 ? make_float4(0.f, 0.f, 0.f, 0.f)
-                     : t == pos         ? __ldcg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc)
-                                        : __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kvd) + cc);
+                                        : kv_ld4(ly.vc, vb + (size_t)t * kvd + 4 * cc, kv16, t == pos);
         }
         if (t0 == 0) {
             // max (order-free), e[t] = exp(l - max), the sum walked in order (attention.rs:107-115)

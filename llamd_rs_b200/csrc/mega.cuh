@@ -8,7 +8,7 @@ namespace llamd {
 struct MegaLayer {
     const uint8_t *attn_q, *attn_k, *attn_v, *attn_out, *gate, *up, *down;  // tiled Q6_K
     const float *attn_norm, *q_norm, *k_norm, *ffn_norm, *router;           // f32 (q_norm / k_norm may be null)
-    float *kc, *vc;                                                          // [max_kv][kv_dim]
+    float *kc, *vc;                                                          // [max_kv][kv_dim] f32, or binary16 when MegaParams::kv16
 };
 
 struct MegaParams {
@@ -32,6 +32,7 @@ struct MegaParams {
     int act_blocks;      // blocks the activation image must hold
     int sl_floats;       // padded max_kv
     int ktile_rows;      // cached positions one CTA scores: ceil(max_kv / (SMs / n_head_kv))
+    int kv16;            // 1: the caches hold binary16 values (rounded at the store, widened exactly at the load)
     int fast;            // bit mask: tree reductions in place of the long ordered f32 sums of 1 the norms, 2 the router's dots, 4 attention
 };
 

@@ -35,6 +35,13 @@ void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, 
 void llamd_fwd_attention_prefill(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                                  int hd, const int32_t *meta, int max_kv, int ntok, int n_kv_max);
 void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int k, int rows, int ntok);
+void llamd_fwd_qk_norm_rope_store_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc, int n_head,
+                                       int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv);
+void llamd_fwd_qk_norm_rope_store_tile_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc,
+                                            int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok);
+void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head, int n_head_kv,
+                                   int hd, const int32_t *meta, int max_kv, int nseq);
+void llamd_fwd_kv16_expand(const void *kc16, const void *vc16, float *kc32, float *vc32, int n_pos, int kv_dim);
 void llamd_fwd_matvec_grouped_x2_silu_quant(const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
                                             float *oa, float *ob, unsigned int *counter, int8_t *qs, float *d, int blocks, int rows,
                                             int n_used, int nseq);
@@ -170,6 +177,8 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int kv16 = 0;            // option "kv_f16": the caches hold binary16 values (rounded at the store)
+    Buf kc32, vc32;          // a prefill tile's view of one layer's binary16 cache, widened to f32 ([max_kv][kv_dim] each)
     int prefold = 0;         // option "prefill_prefold"; prefold_ready once the folded copies exist
     bool prefold_ready = false;
     int prefill_gemm = 1;    // 1: integer tensor path (mma.sync), exact; 0: dp4a, 8 tokens per weight pass, exact;
@@ -280,6 +289,7 @@ bool mega_prepare(Model &m) {
                            l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr,
                            l.ffn_norm.as<float>(), l.ffn_gate_inp.as<float>(), l.kc.as<float>(), l.vc.as<float>()};
     }
+    for (Buf *b : {&m.mega_layers, &m.mega_bar, &m.mega_status, &m.mega_prof}) b->release();  // (made again after the caches moved)
     if (!m.mega_layers.alloc(tab.size() * sizeof(MegaLayer)) || !m.mega_bar.alloc(256) || !m.mega_status.alloc(256) || !m.mega_prof.alloc(32 * 8))
         return false;
     if (cudaMemcpyAsync(m.mega_layers.p, tab.data(), tab.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, stream()) != cudaSuccess ||
@@ -314,6 +324,7 @@ void queue_token_resident(Model &m) {
     p.spin_limit = 1u << 22;
     p.prof = m.resident_profile ? m.mega_prof.as<unsigned long long>() : nullptr;
     p.fast = m.arith_fast;
+    p.kv16 = m.kv16;
     launch_decode_mega(p, hp);
     matvec_batch(MatvecPlans{}, m.output.p ? m.output.p : m.tok_embd.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb,
                  hp.n_vocab, 1);
@@ -390,11 +401,16 @@ void queue_token(Model &m, int nseq) {
                         m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
         mark(LLAMD_PH_QKV);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
+        if (m.kv16)
+            llamd_fwd_qk_norm_rope_store_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
+                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
+                                              m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
+        else
         llamd_fwd_qk_norm_rope_store(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
                                      l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
                                      l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
         mark(LLAMD_PH_ROPE);
-        const bool fuse = m.fuse_tails && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
+        const bool fuse = m.fuse_tails && !m.kv16 && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
         if (fuse) {
             // the CTA that finishes a sequence's attention last also writes its Q8_K form
             llamd_fwd_attention_meta_quant(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
@@ -402,6 +418,10 @@ void queue_token(Model &m, int nseq) {
                                            m.ad.as<float>());
             mark(LLAMD_PH_ATTENTION);
         } else {
+            if (m.kv16)
+                llamd_fwd_attention_meta_kv16(m.q.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
+                                              m.max_kv, nseq);
+            else
             llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV,
                                      hd, meta, m.max_kv, nseq);
             mark(LLAMD_PH_ATTENTION);
@@ -708,7 +728,8 @@ void llamd_model_free(llamd_model *h) {
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
-                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab, &m->mega_layers, &m->mega_bar, &m->mega_status, &m->mega_prof})
+                   &m->ep_arrive_tab, &m->ep_disp, &m->ep_epoch, &m->ep_ids_tab, &m->ep_ad_tab, &m->ep_aq_tab, &m->ep_disp_tab, &m->mega_layers, &m->mega_bar, &m->mega_status, &m->mega_prof,
+                   &m->kc32, &m->vc32})
         b->release();
     for (void *p : m->ep_mapped) llamd_cuda_ep_ipc_close(p);
     for (Buf *b : {&m->pf.x, &m->pf.xb, &m->pf.xb2, &m->pf.q, &m->pf.k, &m->pf.v, &m->pf.attn, &m->pf.aq, &m->pf.ad, &m->pf.aq2, &m->pf.ad2,
@@ -853,6 +874,35 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     }
     if (!strcmp(name, "prefill_attn")) {
         m->prefill_attn = value;
+        return 0;
+    }
+    if (!strcmp(name, "kv_f16")) {
+        // 1: the K/V caches hold binary16 values (the benchmark configuration's "KV cache is f16"; the reference's caches are
+        // f32): a value is rounded to nearest-even once, at the store, and widened exactly at every load, nothing else
+        // changes. The caches are re-allocated and EMPTY afterwards: set it before the first pass.
+        if ((value != 0) == (m->kv16 != 0)) return 0;
+        if (m->ep_world > 1 && m->ep_p2p) {
+            m->err = "option kv_f16: set it before the peer-memory attach";
+            return -1;
+        }
+        cudaStreamSynchronize(stream());
+        if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
+        const size_t kvd = (size_t)m->hp.n_head_kv * m->hp.head_dim, elem = value ? 2 : 4;
+        bool ok = true;
+        for (auto &l : m->layers) {
+            l.kc.release();
+            l.vc.release();
+            ok = ok && l.kc.alloc((size_t)m->max_kv * kvd * elem * m->max_seq) && l.vc.alloc((size_t)m->max_kv * kvd * elem * m->max_seq);
+        }
+        m->kc32.release();
+        m->vc32.release();
+        if (value) ok = ok && m->kc32.alloc((size_t)m->max_kv * kvd * 4) && m->vc32.alloc((size_t)m->max_kv * kvd * 4);
+        if (!ok) {
+            m->err = std::string("option kv_f16: ") + llamd_cuda_last_error_string();
+            return -1;
+        }
+        m->kv16 = value != 0;
+        m->mega_ready = false;  // (the resident kernel's layer table names the caches)
         return 0;
     }
     if (!strcmp(name, "prefill_prefold")) {
@@ -1069,22 +1119,37 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
             llamd_fwd_matvec_tokens(l.attn_q.p, l.attn_k.p, l.attn_v.p, p.aq.as<int8_t>(), p.ad.as<float>(), p.q.as<float>(),
                                     p.k.as<float>(), p.v.as<float>(), eb, qd, kvd, kvd, T);
         }
-        if (multi_seq) {
+        const float *kc_view = l.kc.as<float>(), *vc_view = l.vc.as<float>();  // what the tile's attention reads
+        if (multi_seq && m.kv16) {
+            llamd_fwd_qk_norm_rope_store_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
+                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
+                                              m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
+            llamd_fwd_attention_meta_kv16(p.q.as<float>(), l.kc.p, l.vc.p, p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta, m.max_kv, T);
+        } else if (multi_seq) {
             llamd_fwd_qk_norm_rope_store(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
                                          l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
                                          l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
             llamd_fwd_attention_meta(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV,
                                      hd, meta, m.max_kv, T);
+        } else if (m.kv16) {
+            // one sequence's tile over a binary16 cache: store rounded, then widen the rows the tile attends (exactly) into an
+            // f32 view that the tiled kernels read as they read an f32 cache
+            llamd_fwd_qk_norm_rope_store_tile_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
+                                                   l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd,
+                                                   meta, m.rope_tab.as<float>(), hp.rms_eps, T);
+            llamd_fwd_kv16_expand(l.kc.p, l.vc.p, m.kc32.as<float>(), m.vc32.as<float>(), n_kv_max, kvd);
+            kc_view = m.kc32.as<float>();
+            vc_view = m.vc32.as<float>();
         } else
         llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
                                           l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
                                           l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
         if (multi_seq) {
         } else if (m.prefill_attn)
-            llamd_fwd_attention_prefill(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H,
+            llamd_fwd_attention_prefill(p.q.as<float>(), kc_view, vc_view, p.attn.as<float>(), p.scores.as<float>(), H,
                                         HKV, hd, meta, (m.max_kv + 3) & ~3, T, n_kv_max);  // score rows padded to 16 bytes
         else
-            llamd_fwd_attention_tile(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV,
+            llamd_fwd_attention_tile(p.q.as<float>(), kc_view, vc_view, p.attn.as<float>(), p.scores.as<float>(), H, HKV,
                                      hd, meta, m.max_kv, T);
         llamd_fwd_quantize(p.attn.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(), T * (qd / 256));
         if (tc) {
@@ -1614,6 +1679,14 @@ int llamd_model_read_kv(llamd_model *h, int layer, int seq, int n_pos, float *k_
     if (!m || layer < 0 || layer >= m->hp.n_layer || seq < 0 || seq >= m->max_seq || n_pos < 0 || n_pos > m->max_kv) return -1;
     const size_t kvd = (size_t)m->hp.n_head_kv * m->hp.head_dim;
     const size_t off = (size_t)seq * m->max_kv * kvd;
+    if (m->kv16) {
+        // (one sequence's rows widened on the device into the f32 view, then read: the values are the cache's, exactly)
+        const uint8_t *k16 = (const uint8_t *)m->layers[layer].kc.p + off * 2, *v16 = (const uint8_t *)m->layers[layer].vc.p + off * 2;
+        llamd_fwd_kv16_expand(k16, v16, m->kc32.as<float>(), m->vc32.as<float>(), n_pos, (int)kvd);
+        if (k_out && llamd_fwd_download(k_out, m->kc32.p, n_pos * kvd * sizeof(float)) != 0) return -1;
+        if (v_out && llamd_fwd_download(v_out, m->vc32.p, n_pos * kvd * sizeof(float)) != 0) return -1;
+        return 0;
+    }
     if (k_out && llamd_fwd_download(k_out, m->layers[layer].kc.as<float>() + off, n_pos * kvd * sizeof(float)) != 0) return -1;
     if (v_out && llamd_fwd_download(v_out, m->layers[layer].vc.as<float>() + off, n_pos * kvd * sizeof(float)) != 0) return -1;
     return 0;

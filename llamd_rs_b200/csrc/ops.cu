@@ -4,6 +4,7 @@
 // Reductions whose order is observable in the reference (sequential f32 sums)
 // are walked in that order by one thread; everything that is order-free (max,
 // integer counts) is done in parallel.
+#include <cuda_fp16.h>
 #include <math.h>
 
 #include <vector>
@@ -425,12 +426,34 @@ __global__ void __launch_bounds__(kQ80Producers + 32 * NSEQ) matvec_q8_0_bulk_ke
 }
 
 // ---- QK-norm + RoPE (+ KV store) -----------------------------------------
+// The KV cache's element type. The reference's caches are f32 (crates/llamd-runtime/src/kv.rs:27-170) and that is the
+// default; with binary16 elements (model option "kv_f16": the benchmark configuration names an f16 cache) a K or V value
+// is rounded to nearest-even once, when it is stored, and widened exactly when it is read: every other operation is
+// unchanged, so the results are those of the f32 arithmetic over a cache of f16-representable values.
+template <class T>
+struct KvIo;
+template <>
+struct KvIo<float> {
+    static __device__ __forceinline__ float4 ld4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+    static __device__ __forceinline__ void st(float *p, float v) { *p = v; }
+};
+template <>
+struct KvIo<__half> {
+    static __device__ __forceinline__ float4 ld4(const __half *p) {
+        const uint2 u = __ldg(reinterpret_cast<const uint2 *>(p));
+        const __half2 a = *reinterpret_cast<const __half2 *>(&u.x), b = *reinterpret_cast<const __half2 *>(&u.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void st(__half *p, float v) { *p = __float2half_rn(v); }
+};
+
 // crates/llamd-runtime/src/layer.rs:120-153, crates/llamd-cpu/src/lib.rs:158-209.
 // One CTA of hd/2 threads per head; thread 0 walks the sum of squares. The
 // sin/cos come from a table the host built with its own libm, which is what
 // the reference's CPU path calls (powf, sin, cos).
+template <class KVT>
 __global__ void norm_rope_kernel(float *__restrict__ xq, const float *__restrict__ wq, float *__restrict__ xk, const float *__restrict__ wk,
-                                 const float *__restrict__ v_src, float *__restrict__ kc, float *__restrict__ vc, int n_head_q,
+                                 const float *__restrict__ v_src, KVT *__restrict__ kc, KVT *__restrict__ vc, int n_head_q,
                                  int n_head_k, int hd, const int32_t *__restrict__ meta, int pos_imm, const float *__restrict__ rope_tab,
                                  float eps, int kv_stride) {
     extern __shared__ float sx[];
@@ -474,13 +497,13 @@ __global__ void norm_rope_kernel(float *__restrict__ xq, const float *__restrict
         const int kv_dim = n_head * hd;
         // kv_stride: positions between two sequences' caches; 0 when every row of
         // the launch is a position of ONE sequence (a prefill tile)
-        float *kdst = kc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)head * hd;
-        float *vdst = vc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)head * hd;
+        KVT *kdst = kc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)head * hd;
+        KVT *vdst = vc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)head * hd;
         const float *vs = v_src + ((size_t)seq * n_head + head) * hd;
-        kdst[i] = o0;
-        kdst[i + half] = o1;
-        vdst[i] = vs[i];
-        vdst[i + half] = vs[i + half];
+        KvIo<KVT>::st(kdst + i, o0);
+        KvIo<KVT>::st(kdst + i + half, o1);
+        KvIo<KVT>::st(vdst + i, vs[i]);
+        KvIo<KVT>::st(vdst + i + half, vs[i + half]);
     }
 }
 
@@ -651,7 +674,8 @@ __global__ void __launch_bounds__(256) attention_kernel(const float *__restrict_
 constexpr int kSplit = 4;    // output-column split of attn_out_kernel
 constexpr int kSplitT = 8;   // position-tile split of attn_scores_kernel
 
-__global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restrict__ q, const float *__restrict__ kc, float *__restrict__ scores,
+template <class KVT>
+__global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restrict__ q, const KVT *__restrict__ kc, float *__restrict__ scores,
                                                           int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta,
                                                           int n_kv_imm, int max_kv, int kv_stride) {
     extern __shared__ __align__(16) float sm[];
@@ -663,7 +687,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
     const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
     const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
-    const float *kb = kc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
+    const KVT *kb = kc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
     const float *qh = q + ((size_t)seq * n_head + h) * hd;
     float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
     for (int i = tid; i < hd; i += blockDim.x) sq[i] = qh[i];
@@ -678,8 +702,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
             const int idx = tid + j * 256;
             const int r = idx / hd4, cc = idx - r * hd4;
             const int t = ti * kAttTile + r;
-            reg[j] = (idx < per_tile4 && t < n_kv) ? __ldg(reinterpret_cast<const float4 *>(kb + (size_t)t * kv_dim) + cc)
-                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            reg[j] = (idx < per_tile4 && t < n_kv) ? KvIo<KVT>::ld4(kb + (size_t)t * kv_dim + 4 * cc) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
     auto stash = [&](float *dst) {
@@ -729,7 +752,8 @@ constexpr int kPvTile = 256;  // positions per V tile
 
 // With a TailPlan the CTA that finishes a sequence last also writes the Q8_K form of that sequence's whole
 // attention output (what llamd_fwd_quantize would do one launch later).
-__global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const float *__restrict__ vc, float *__restrict__ out,
+template <class KVT>
+__global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const KVT *__restrict__ vc, float *__restrict__ out,
                                                        int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int n_kv_imm,
                                                        int max_kv, int kv_stride, const TailPlan tail) {
     extern __shared__ __align__(16) float sm[];
@@ -743,7 +767,7 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     float *sl = sm;                                  // [n_kv]
     float *tile = sm + ((n_kv_cap + 3) & ~3);        // [2][kPvTile][cols]
     const int kv_dim = n_head_kv * hd, kvh = h / (n_head / n_head_kv);
-    const float *vb = vc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd + (size_t)c * cols;
+    const KVT *vb = vc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd + (size_t)c * cols;
     const float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
     const int per_tile4 = kPvTile * cols4;
     const int n_tiles = (n_kv + kPvTile - 1) / kPvTile;
@@ -755,8 +779,7 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
             const int idx = tid + j * 256;
             const int r = idx / cols4, cc = idx - r * cols4;
             const int t = ti * kPvTile + r;
-            reg[j] = (idx < per_tile4 && t < n_kv) ? __ldg(reinterpret_cast<const float4 *>(vb + (size_t)t * kv_dim) + cc)
-                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            reg[j] = (idx < per_tile4 && t < n_kv) ? KvIo<KVT>::ld4(vb + (size_t)t * kv_dim + 4 * cc) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
     auto stash = [&](float *dst) {
@@ -1138,11 +1161,11 @@ int llamd_cuda_rope_table(float *host_out, int max_pos, int hd, float freq_base)
 }
 
 void llamd_fwd_rope(float *x, int pos, int n_head, int hd, const float *rope_tab) {
-    launch_k("rope", norm_rope_kernel, dim3(n_head, 1), dim3(hd / 2), hd * sizeof(float), x, nullptr, nullptr, nullptr, nullptr, nullptr,
+    launch_k("rope", norm_rope_kernel<float>, dim3(n_head, 1), dim3(hd / 2), hd * sizeof(float), x, nullptr, nullptr, nullptr, nullptr, nullptr,
              nullptr, n_head, 0, hd, nullptr, pos, rope_tab, 0.0f, 0);
 }
 void llamd_fwd_norm_rope(float *x, const float *w, int n_head, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq) {
-    launch_k("norm_rope", norm_rope_kernel, dim3(n_head, nseq), dim3(hd / 2), hd * sizeof(float), x, w, nullptr, nullptr, nullptr, nullptr,
+    launch_k("norm_rope", norm_rope_kernel<float>, dim3(n_head, nseq), dim3(hd / 2), hd * sizeof(float), x, w, nullptr, nullptr, nullptr, nullptr,
              nullptr, n_head, 0, hd, meta, 0, rope_tab, eps, 0);
 }
 void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float *kc, float *vc, int n_head_kv, int hd, int kv_dim,
@@ -1151,62 +1174,98 @@ void llamd_fwd_k_norm_rope_store(float *k, const float *w, const float *v, float
         set_error_msg("k_norm_rope_store: kv_dim != n_head_kv*hd");
         return;
     }
-    launch_k("k_norm_rope_store", norm_rope_kernel, dim3(n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), nullptr, nullptr, k, w, v, kc,
+    launch_k("k_norm_rope_store", norm_rope_kernel<float>, dim3(n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), nullptr, nullptr, k, w, v, kc,
              vc, 0, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
 }
 // Query heads and key heads in one launch: QK-norm, RoPE, and the KV store.
 void llamd_fwd_qk_norm_rope_store(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc, int n_head,
                                   int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv) {
-    launch_kc(PDL_SMALL, "qk_norm_rope_store", norm_rope_kernel, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc, vc,
+    launch_kc(PDL_SMALL, "qk_norm_rope_store", norm_rope_kernel<float>, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc, vc,
              n_head, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
 }
 // The same for the ntok tokens of a prefill tile: all rows go into ONE cache.
 void llamd_fwd_qk_norm_rope_store_tile(float *q, const float *wq, float *k, const float *wk, const float *v, float *kc, float *vc,
                                        int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok) {
-    launch_k("qk_norm_rope_store_tile", norm_rope_kernel, dim3(n_head + n_head_kv, ntok), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc,
+    launch_k("qk_norm_rope_store_tile", norm_rope_kernel<float>, dim3(n_head + n_head_kv, ntok), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v, kc,
              vc, n_head, n_head_kv, hd, meta, 0, rope_tab, eps, 0);
 }
 void llamd_fwd_kv_store(float *kc, float *vc, const float *k, const float *v, int pos, int kv_dim) {
     launch_k("kv_store", kv_store_kernel, dim3((kv_dim + 255) / 256), dim3(256), 0, kc, vc, k, v, pos, kv_dim);
 }
+// The same three with a binary16 cache (kc, vc: [..][n_head_kv*hd] halves): values rounded to nearest-even at the store.
+void llamd_fwd_qk_norm_rope_store_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc, int n_head,
+                                       int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv) {
+    launch_kc(PDL_SMALL, "qk_norm_rope_store_kv16", norm_rope_kernel<__half>, dim3(n_head + n_head_kv, nseq), dim3(hd / 2), hd * sizeof(float), q, wq, k,
+              wk, v, (__half *)kc, (__half *)vc, n_head, n_head_kv, hd, meta, 0, rope_tab, eps, max_kv);
+}
+void llamd_fwd_qk_norm_rope_store_tile_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc,
+                                            int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int ntok) {
+    launch_k("qk_norm_rope_store_tile_kv16", norm_rope_kernel<__half>, dim3(n_head + n_head_kv, ntok), dim3(hd / 2), hd * sizeof(float), q, wq, k, wk, v,
+             (__half *)kc, (__half *)vc, n_head, n_head_kv, hd, meta, 0, rope_tab, eps, 0);
+}
+// rows [0, n_pos) of a binary16 cache widened (exactly) to f32: what the tiled prefill attention reads
+__global__ void kv_expand_kernel(const __half *__restrict__ src, float *__restrict__ dst, size_t n4) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
+        reinterpret_cast<float4 *>(dst)[i] = KvIo<__half>::ld4(src + 4 * i);
+}
+void llamd_fwd_kv16_expand(const void *kc16, const void *vc16, float *kc32, float *vc32, int n_pos, int kv_dim) {
+    const size_t n4 = (size_t)n_pos * kv_dim / 4;
+    if (!n4 || kv_dim % 4) return;
+    const unsigned grid = (unsigned)((n4 + 255) / 256 < 1184 ? (n4 + 255) / 256 : 1184);
+    launch_k("kv16_expand", kv_expand_kernel, dim3(grid), dim3(256), 0, (const __half *)kc16, kc32, n4);
+    launch_k("kv16_expand", kv_expand_kernel, dim3(grid), dim3(256), 0, (const __half *)vc16, vc32, n4);
+}
 
-static void attention_split_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head,
+static void attention_split_launch(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head,
                                    int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride,
-                                   const TailPlan &tail_in) {
+                                   const TailPlan &tail_in, bool kv16 = false) {
     const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1)) * sizeof(float);
     const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
     // (the library runs on one device per process: llamd_cuda_set_device is refused once the stream exists, so a
     // per-process record of the configured size is a per-device one)
-    static size_t conf_a = 0, conf_b = 0;
-    if (smem_a > 48 * 1024 && smem_a > conf_a) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+    static size_t conf_a[2] = {0, 0}, conf_b[2] = {0, 0};
+    if (smem_a > 48 * 1024 && smem_a > conf_a[kv16]) {
+        const cudaError_t e = kv16 ? cudaFuncSetAttribute(attn_scores_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a)
+                                   : cudaFuncSetAttribute(attn_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
         if (e != cudaSuccess) {
             set_error(e, "attention (scores) smem attribute");
             return;
         }
-        conf_a = smem_a;
+        conf_a[kv16] = smem_a;
     }
-    if (smem_b > 48 * 1024 && smem_b > conf_b) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+    if (smem_b > 48 * 1024 && smem_b > conf_b[kv16]) {
+        const cudaError_t e = kv16 ? cudaFuncSetAttribute(attn_out_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b)
+                                   : cudaFuncSetAttribute(attn_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
         if (e != cudaSuccess) {
             set_error(e, "attention (output) smem attribute");
             return;
         }
-        conf_b = smem_b;
+        conf_b[kv16] = smem_b;
     }
-    launch_kc(PDL_ATTN, "attn_scores", attn_scores_kernel, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, kc, scores, n_head, n_head_kv, hd, meta, n_kv,
+    if (kv16)
+        launch_kc(PDL_ATTN, "attn_scores", attn_scores_kernel<__half>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, (const __half *)kc, scores, n_head,
+                  n_head_kv, hd, meta, n_kv, max_kv, kv_stride);
+    else
+    launch_kc(PDL_ATTN, "attn_scores", attn_scores_kernel<float>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, (const float *)kc, scores, n_head, n_head_kv, hd, meta, n_kv,
              max_kv, kv_stride);
     TailPlan tail = tail_in;
     if (tail.counter && (n_head * hd) % 256 != 0) {
         set_error_msg("attention: a quantize tail needs n_head * head_dim to be whole Q8_K blocks");
         tail = TailPlan{};
     }
-    launch_kc(PDL_ATTN, "attn_out", attn_out_kernel, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, vc, out, n_head, n_head_kv, hd,
+    if (kv16)
+        launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc, out,
+                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail);
+    else
+    launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc, out, n_head, n_head_kv, hd,
              meta, n_kv, max_kv, kv_stride, tail);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
-                             const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride, const TailPlan &tail = TailPlan{}) {
+                             const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride, const TailPlan &tail = TailPlan{},
+                             bool kv16 = false) {
     const size_t smem = (size_t)(hd + ((max_kv + 3) & ~3) + 2 * kAttTile * (hd + 1)) * sizeof(float);
     if (hd % 4 || hd > 256 || kAttTile * (hd / 4) > 8 * 256 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
         set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
@@ -1215,7 +1274,11 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     // With a scores buffer ([nseq][n_head][max_kv] floats) and a head_dim the
     // column split divides, the work is cut over 4x more CTAs.
     if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 8 * 256) {
-        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride, tail);
+        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride, tail, kv16);
+        return;
+    }
+    if (kv16) {
+        set_error_msg("attention: a binary16 cache needs the scores buffer and a head_dim the column split divides");
         return;
     }
     if (tail.counter) {
@@ -1259,6 +1322,10 @@ void llamd_fwd_attention_meta_quant(const float *q, const float *kc, const float
         return;
     }
     attention_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv, TailPlan{counter, qs, d});
+}
+void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head, int n_head_kv,
+                                   int hd, const int32_t *meta, int max_kv, int nseq) {
+    attention_launch(q, (const float *)kc, (const float *)vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv, TailPlan{}, true);
 }
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int nseq) {

@@ -51,6 +51,9 @@ def lib() -> C.CDLL:
         L.orc_kv_new.restype = C.c_void_p
         L.orc_kv_new.argtypes = [C.c_int, C.c_int, C.c_int]
         L.orc_kv_free.argtypes = [C.c_void_p]
+        L.orc_kv_set_f16.argtypes = [C.c_void_p, C.c_int]
+        L.orc_round_to_f16.restype = C.c_float
+        L.orc_round_to_f16.argtypes = [C.c_float]
         L.orc_kv_keys.restype = C.c_void_p
         L.orc_kv_keys.argtypes = [C.c_void_p, C.c_int]
         L.orc_kv_values.restype = C.c_void_p
@@ -376,10 +379,13 @@ class Model:
         self.m = m
         self.kv = None
 
-    def kv_new(self, capacity: int):
+    def kv_new(self, capacity: int, f16: bool = False):
+        """A fresh cache. f16: every appended K/V value is rounded to binary16 (nearest-even) first."""
         self.kv_free()
         self.kv = lib().orc_kv_new(self.hp["n_layer"], self.hp["n_head_kv"] * self.hp["head_dim"], capacity)
         self.kv_capacity = capacity
+        if f16:
+            lib().orc_kv_set_f16(self.kv, 1)
         return self.kv
 
     def expert_cache_clear(self):

@@ -706,12 +706,42 @@ typedef struct {
     int32_t threads;
 } orc_model;
 
-/* KvCache: crates/llamd-runtime/src/kv.rs:27-170, f32, [pos][kv_dim] per layer. */
+/* KvCache: crates/llamd-runtime/src/kv.rs:27-170, f32, [pos][kv_dim] per layer.
+ * f16_store (no counterpart in the reference, whose caches are f32; the benchmark configuration names an f16 cache): a
+ * value is rounded to IEEE binary16, nearest-even, when it is appended, and kept as the f32 that binary16 value widens
+ * to. Everything downstream is the same arithmetic. */
 typedef struct {
     int32_t n_layer, kv_dim, capacity;
     float **k;
     float **v;
+    int32_t f16_store;
 } orc_kv;
+
+/* f32 -> binary16 (round to nearest, ties to even; overflow to infinity; subnormals kept) -> f32. */
+static float round_to_f16(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    const uint32_t sign = u & 0x80000000u;
+    uint32_t a = u & 0x7FFFFFFFu;
+    if (a >= 0x7F800000u) return x; /* inf, NaN */
+    if (a >= 0x477FF000u) {         /* rounds to 65536 or more: infinity */
+        a = 0x7F800000u;
+    } else if (a >= 0x38800000u) {  /* normal in binary16: keep 10 mantissa bits */
+        const uint32_t lsb = (a >> 13) & 1u;
+        a = (a + 0x0FFFu + lsb) & ~0x1FFFu;
+    } else {                        /* subnormal in binary16 (or zero): multiples of 2^-24 */
+        float f;
+        memcpy(&f, &a, 4);
+        f = nearbyintf(f * 16777216.0f) / 16777216.0f; /* exact: nearbyintf rounds ties to even under the default mode */
+        memcpy(&a, &f, 4);
+    }
+    a |= sign;
+    float r;
+    memcpy(&r, &a, 4);
+    return r;
+}
+void orc_kv_set_f16(orc_kv *kv, int on) { if (kv) kv->f16_store = on != 0; }
+float orc_round_to_f16(float x) { return round_to_f16(x); }
 
 orc_kv *orc_kv_new(int n_layer, int kv_dim, int capacity) {
     if (n_layer <= 0 || kv_dim <= 0 || capacity <= 0) return NULL;
@@ -810,6 +840,13 @@ static int forward_one_layer(const orc_model *m, int il, float *x, uint32_t pos,
     orc_rope(kn, kv_dim, 1, &pos, hd, m->rope_freq_base, 1.0f, kr);
     memcpy(kv->k[il] + (size_t)pos * kv_dim, kr, sizeof(float) * kv_dim);
     memcpy(kv->v[il] + (size_t)pos * kv_dim, v, sizeof(float) * kv_dim);
+    if (kv->f16_store) {
+        float *kd = kv->k[il] + (size_t)pos * kv_dim, *vd = kv->v[il] + (size_t)pos * kv_dim;
+        for (int i = 0; i < kv_dim; i++) {
+            kd[i] = round_to_f16(kd[i]);
+            vd[i] = round_to_f16(vd[i]);
+        }
+    }
     int n_kv = (int)pos + 1;
     orc_attend_mt(qr, kv->k[il], kv->v[il], n_kv, n_head, n_head_kv, hd, attn, th);
     orc_matvec_q6k(m->attn_out[il], attn, qd, n_embd, kqv, th);

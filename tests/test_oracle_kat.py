@@ -356,3 +356,19 @@ def test_matvec_dequant_q8_0_is_sequential_f32(orc):
         for t in range(k):
             acc = np.float32(acc + np.float32(wf[r, t] * x[t]))
         assert close(got[r], acc, 0.0)
+
+
+def test_round_to_f16_is_ieee_nearest_even():
+    """The oracle's f16-store mode of the KV cache rounds as numpy's float16 conversion does (IEEE binary16, ties to
+    even, overflow to infinity, subnormals kept), including the midpoints."""
+    import oracle
+
+    L = oracle.lib()
+    rng = np.random.default_rng(5)
+    xs = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-8, 1e-6, 1e-4, 1e-2, 1.0, 100.0, 3e4)]
+                        + [np.array([0.0, -0.0, 65504.0, 65519.99, 65520.0, 65536.0, -65520.0, 6.1e-5, 6.103515625e-5, 5.96e-8, 2.98e-8,
+                                     2.9802322e-8, 8.9e-8, 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -11, np.inf, -np.inf], np.float32)])
+    with np.errstate(over="ignore"):
+        want = xs.astype(np.float16).astype(np.float32)
+    got = np.array([L.orc_round_to_f16(float(v)) for v in xs], np.float32)
+    assert np.array_equal(want.view(np.uint32), got.view(np.uint32))
