@@ -267,7 +267,12 @@ def run_prefill(args, m, hp, prompt, rank, world, backend, dist):
             "e2e": {"value": world * n * K / wall, "unit": "tok/s", "h2d_bytes_per_step": 8 * n, "d2h_bytes_per_step": 4},
             "gpu_launches": int(L.llamd_fwd_launch_count() - launches0), "last_token": int(tok),
             "roofline": {"bound": "hbm", "achieved": wbytes / (ms.value / K * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                         "frac": wbytes / (ms.value / K * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": wbytes / (ms.value / K * 1e-3) / 1e9 / peak,
+                         # one ncu capture of the grouped GEMM read 1.006x its algorithmic bytes (pre-folded: 816.7 MB for the 811 MB of
+                         # gate+up images); the matmuls' weights are the pass's traffic to within that
+                         "traffic": 1.006 * hp["n_layer"] * (15482880 + 128 * 3 * 1290240 * (2.016 / 0.8203 if args.prefold else 1.0))
+                         if world == 1 else None,
+                         "peak_source": peak_src,
                          "matmul_tops": tops, "matmul_frac_of_bf16_peak": tops / float(peaks.get("bf16_tflops_sustained", 1400.0)),
                          "note": "weight bytes of one pass / pass time against the copy peak; matmul_tops = 2 x multiply-adds of the "
                                  "pass's matmuls / pass time, against the measured sustained bf16 GEMM rate for scale (the exact path "
