@@ -117,6 +117,7 @@ unsafe extern "C" {
     pub fn llamd_fwd_silu_mul_quant(gate: *const f32, up: *const f32, out: *mut f32, qs: *mut i8, d: *mut f32, n: c_int);
     pub fn llamd_fwd_router(logits: *const f32, n_expert: c_int, n_used: c_int, ids: *mut i32, weights: *mut f32, probs: *mut f32, nseq: c_int);
     pub fn llamd_fwd_router_matvec(w: *const f32, x: *const f32, k: c_int, n_expert: c_int, n_used: c_int, logits: *mut f32, ids: *mut i32, weights: *mut f32, probs: *mut f32, counter: *mut c_uint, nseq: c_int);
+    pub fn llamd_fwd_norm_router(w: *const f32, x: *const f32, residual: *const f32, x_out: *mut f32, w_norm: *const f32, xn_out: *mut f32, qs: *mut i8, d: *mut f32, k: c_int, eps: f32, n_expert: c_int, n_used: c_int, logits: *mut f32, ids: *mut i32, weights: *mut f32, probs: *mut f32, counter: *mut c_uint, nseq: c_int);
     pub fn llamd_fwd_moe_combine(down: *const f32, weights: *const f32, out: *mut f32, n_used: c_int, n_embd: c_int);
     pub fn llamd_fwd_moe_combine_add(down: *const f32, weights: *const f32, residual: *const f32, out: *mut f32, n_used: c_int, n_embd: c_int, nseq: c_int);
     pub fn llamd_fwd_argmax(x: *const f32, n: c_int, scratch_v: *mut f32, scratch_i: *mut i32, out: *mut i32, nblocks: c_int, nseq: c_int);

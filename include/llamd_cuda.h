@@ -249,6 +249,14 @@ void llamd_fwd_router(const float *logits, int n_expert, int n_used, int32_t *id
  * probs may be NULL; counter is nseq zeroed words, left zeroed. */
 void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert, int n_used, float *logits,
                              int32_t *ids, float *weights, float *probs, unsigned int *counter, int nseq);
+/* The FFN norm fused in front of it (no counterpart in the reference, which launches them apart:
+ * crates/llamd-rocm/src/forward.rs op::rms_norm_quant then op::router): x_out = x + residual; xn = rms_norm(x_out) *
+ * w_norm; qs / d = Q8_K of xn (for the experts); logits / ids / weights = the router over xn. x_out must be a buffer
+ * other than x and residual (every CTA of the launch reads them); xn_out and probs may be NULL. Same bits as
+ * llamd_fwd_add_rms_norm_quant followed by llamd_fwd_router_matvec. */
+void llamd_fwd_norm_router(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm,
+                           float *xn_out, int8_t *qs, float *d, int k, float eps, int n_expert, int n_used, float *logits,
+                           int32_t *ids, float *weights, float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_moe_combine(const float *down, const float *weights, float *out, int n_used, int n_embd); /* :325 */
 void llamd_fwd_moe_combine_add(const float *down, const float *weights, const float *residual,
                                float *out, int n_used, int n_embd, int nseq);           /* :586 */

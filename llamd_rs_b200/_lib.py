@@ -114,6 +114,7 @@ SIGNATURES = {
     "llamd_fwd_silu_mul_quant": (None, [vp, vp, vp, vp, vp, i32]),
     "llamd_fwd_router": (None, [vp, i32, i32, vp, vp, vp, i32]),
     "llamd_fwd_router_matvec": (None, [vp, vp, i32, i32, i32, vp, vp, vp, vp, vp, i32]),
+    "llamd_fwd_norm_router": (None, [vp, vp, vp, vp, vp, vp, vp, vp, i32, f32, i32, i32, vp, vp, vp, vp, vp, i32]),
     "llamd_fwd_moe_combine": (None, [vp, vp, vp, i32, i32]),
     "llamd_fwd_moe_combine_add": (None, [vp, vp, vp, vp, i32, i32, i32]),
     "llamd_fwd_argmax": (None, [vp, i32, vp, vp, vp, i32, i32]),

@@ -35,6 +35,9 @@ void llamd_fwd_attention_tile(const float *q, const float *kc, const float *vc, 
 void llamd_fwd_attention_prefill(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                                  int hd, const int32_t *meta, int max_kv, int ntok, int n_kv_max);
 void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int k, int rows, int ntok);
+void llamd_fwd_norm_router(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm, float *xn_out,
+                           int8_t *qs, float *d, int k, float eps, int n_expert, int n_used, float *logits, int32_t *ids, float *weights,
+                           float *probs, unsigned int *counter, int nseq);
 void llamd_fwd_qk_norm_rope_store_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc, int n_head,
                                        int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv);
 void llamd_fwd_qk_norm_rope_store_tile_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc,
@@ -177,6 +180,7 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int fuse_norm_router = 1;  // option "fuse_norm_router": the FFN norm and the router as one launch (decode pass)
     int kv16 = 0;            // option "kv_f16": the caches hold binary16 values (rounded at the store)
     Buf kc32, vc32;          // a prefill tile's view of one layer's binary16 cache, widened to f32 ([max_kv][kv_dim] each)
     int prefold = 0;         // option "prefill_prefold"; prefold_ready once the folded copies exist
@@ -384,6 +388,10 @@ void queue_token(Model &m, int nseq) {
         if (il + 1 < hp.n_layer) return plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v);
         return plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
     };
+    // where the residual stream lives: m.x, or m.xb after a fused norm + router launch (which may not write in place: its
+    // other CTAs still read the old stream); the combine that opens the next layer moves it back to m.x
+    const float *x_res = x;
+    const bool fuse_nr = m.fuse_norm_router && (size_t)6 * E * sizeof(float) <= 200 * 1024 && E % 256 == 0 && hp.n_expert <= 4 * E;
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
         // Attention norm, f32 and Q8_K in one pass (Q, K and V read the same
@@ -392,8 +400,9 @@ void queue_token(Model &m, int nseq) {
         if (il == 0) {
             llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
         } else {
-            combine_rms_norm_quant_wait(plan_ep_wait(), x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
+            combine_rms_norm_quant_wait(plan_ep_wait(), x_res, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
                                         m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+            x_res = x;
             trace_x(il - 1);
         }
         mark(LLAMD_PH_ATTN_NORM);
@@ -432,11 +441,19 @@ void queue_token(Model &m, int nseq) {
         matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
         mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
+        if (fuse_nr) {
+            llamd_fwd_norm_router(l.ffn_gate_inp.as<float>(), x, m.xb2.as<float>(), m.xb.as<float>(), l.ffn_norm.as<float>(), nullptr,
+                                  m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, hp.n_expert, nu, m.router_logits.as<float>(),
+                                  m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
+            x_res = m.xb.as<float>();
+            mark(LLAMD_PH_FFN_NORM);
+        } else {
         llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
                                      m.ad.as<float>(), E, hp.rms_eps, nseq);
         mark(LLAMD_PH_FFN_NORM);
         llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
                                 m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
+        }
         mark(LLAMD_PH_ROUTER);
         if (m.ep_world > 1) {
             // Expert parallelism: gather every rank's routed request, run the experts this
@@ -500,7 +517,7 @@ void queue_token(Model &m, int nseq) {
                             cudaMemcpyDeviceToDevice, stream());
     }
     // the last layer's combine, fused with the output norm
-    combine_rms_norm_quant_wait(plan_ep_wait(), x, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
+    combine_rms_norm_quant_wait(plan_ep_wait(), x_res, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
                                 m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
     trace_x(hp.n_layer - 1);
     mark(LLAMD_PH_ATTN_NORM);
@@ -874,6 +891,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     }
     if (!strcmp(name, "prefill_attn")) {
         m->prefill_attn = value;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_norm_router")) {
+        if (m->fuse_norm_router != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_norm_router = value;
         return 0;
     }
     if (!strcmp(name, "kv_f16")) {

@@ -136,6 +136,99 @@ __global__ void __launch_bounds__(128) router_rows_kernel(const float *__restric
                 probs ? probs + (size_t)seq * n_expert : nullptr);
 }
 
+// The FFN norm and the router in ONE launch (decode): x_out = x + residual; xn = rms_norm(x_out) * w_norm; the Q8_K form
+// of xn for the experts; the 128 router logits over xn; the routing decision. Every CTA repeats the cheap norm (one
+// 2048-add chain, which sits in front of the router's chains whichever kernel walks it) and then does its four router
+// rows as router_rows_kernel does; CTA 0 also writes x_out, the Q8_K bytes and scales (and xn, if asked). One launch
+// boundary fewer per layer than norm -> router, the same operations in the same order, hence the same bits.
+// x_out must not alias x or residual: the other CTAs still read them.
+__global__ void __launch_bounds__(128) norm_router_kernel(const float *__restrict__ w, const float *__restrict__ x, const float *__restrict__ residual,
+                                                          float *__restrict__ x_out, const float *__restrict__ w_norm, float *__restrict__ xn_out,
+                                                          int8_t *__restrict__ qs, float *__restrict__ d, int k, float eps, int n_expert, int n_used,
+                                                          float *__restrict__ logits, int32_t *__restrict__ ids, float *__restrict__ weights,
+                                                          float *__restrict__ probs, unsigned int *__restrict__ done_counter) {
+    extern __shared__ __align__(16) float sm[];  // [4][k] router rows / products, [k] x then xn, [k] squares
+    __shared__ float s_red[40 + kMaxUsed];
+    __shared__ int s_redi[40 + kMaxUsed];
+    __shared__ float s_scale;
+    __shared__ bool s_last;
+    pdl_trigger();
+    const int seq = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row = blockIdx.x * 4 + warp, k4 = k / 4;
+    float *prod = sm + (size_t)warp * k, *sx = sm + (size_t)4 * k, *ssq = sx + k;
+    // the router rows and the norm weights do not depend on the previous kernel: they travel before the wait
+    if (row < n_expert) {
+        const float4 *wr = reinterpret_cast<const float4 *>(w + (size_t)row * k);
+        for (int i0 = 0; i0 < k4; i0 += 512) {
+            float4 r[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int idx = i0 + j * 32 + lane;
+                r[j] = idx < k4 ? __ldg(wr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int idx = i0 + j * 32 + lane;
+                if (idx < k4) reinterpret_cast<float4 *>(prod)[idx] = r[j];
+            }
+        }
+    }
+    pdl_wait();
+    // x + residual, its squares (crates/llamd-cpu/src/lib.rs:55-75 after the add of layer.rs:281-287)
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + (size_t)seq * k), *r4 = reinterpret_cast<const float4 *>(residual + (size_t)seq * k);
+    for (int j = tid; j < k4; j += 128) {
+        const float4 a = x4[j], b = r4[j];
+        const float4 v = make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
+        reinterpret_cast<float4 *>(sx)[j] = v;
+        reinterpret_cast<float4 *>(ssq)[j] = make_float4(__fmul_rn(v.x, v.x), __fmul_rn(v.y, v.y), __fmul_rn(v.z, v.z), __fmul_rn(v.w, v.w));
+        if (blockIdx.x == 0) reinterpret_cast<float4 *>(x_out + (size_t)seq * k)[j] = v;
+    }
+    __syncthreads();
+    if (tid == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(chain_sum(ssq, k, 0.0f), (float)k), eps)));
+    __syncthreads();
+    const float scale = s_scale;
+    for (int j = tid; j < k4; j += 128) {
+        const float4 v = reinterpret_cast<const float4 *>(sx)[j], wn = __ldg(reinterpret_cast<const float4 *>(w_norm) + j);
+        const float4 o = make_float4(__fmul_rn(__fmul_rn(v.x, scale), wn.x), __fmul_rn(__fmul_rn(v.y, scale), wn.y),
+                                     __fmul_rn(__fmul_rn(v.z, scale), wn.z), __fmul_rn(__fmul_rn(v.w, scale), wn.w));
+        reinterpret_cast<float4 *>(sx)[j] = o;
+        if (blockIdx.x == 0 && xn_out) reinterpret_cast<float4 *>(xn_out + (size_t)seq * k)[j] = o;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0) {  // the Q8_K form for the experts (dot.rs:88-128): a warp per 256-element block
+        for (int b = warp; b < k / 256; b += 4) {
+            const float4 a = reinterpret_cast<const float4 *>(sx + b * 256 + lane * 8)[0], c = reinterpret_cast<const float4 *>(sx + b * 256 + lane * 8)[1];
+            const float v[8] = {a.x, a.y, a.z, a.w, c.x, c.y, c.z, c.w};
+            q8k_quantize_block(v, lane, qs + (size_t)seq * k + (size_t)b * 256, d + (size_t)seq * (k / 256) + b, nullptr);
+        }
+    }
+    // the router rows: y = fold(-0.0, +) of w[r][t] * xn[t], t ascending (crates/llamd-models/src/model.rs:253-263)
+    if (row < n_expert) {
+        for (int j = lane; j < k4; j += 32) {
+            const float4 a = reinterpret_cast<const float4 *>(prod)[j], b = reinterpret_cast<const float4 *>(sx)[j];
+            reinterpret_cast<float4 *>(prod)[j] = make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
+        }
+        __syncwarp();
+        if (lane == 0) {
+            logits[(size_t)seq * n_expert + row] = chain_sum(prod, k, -0.0f);
+            __threadfence();
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int prev = atomicInc(done_counter + seq, gridDim.x - 1);  // wraps to 0 after the last CTA
+        s_last = prev == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float *s_p = sm;
+    for (int i = tid; i < n_expert; i += blockDim.x) s_p[i] = __ldcg(logits + (size_t)seq * n_expert + i);
+    __syncthreads();
+    route_block(s_p, s_red, s_redi, n_expert, n_used, ids + (size_t)seq * n_used, weights + (size_t)seq * n_used,
+                probs ? probs + (size_t)seq * n_expert : nullptr);
+}
+
 // ---- Q8_0 matvec: dequantize (d*q) then the sequential f32 dot -------------
 // (crates/llamd-quant/src/lib.rs:154-162 + crates/llamd-models/src/model.rs:253-263)
 template <int NSEQ>
@@ -1068,6 +1161,29 @@ void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert
     }
     launch_kc(PDL_ROUTER, "router_matvec", router_rows_kernel, dim3((n_expert + 3) / 4, nseq), dim3(128), smem, w, x, k, n_expert, n_used, logits, ids,
              weights, probs, counter);
+}
+
+// The FFN norm fused in front (see norm_router_kernel). x_out: the new residual stream, a buffer other than x / residual.
+void llamd_fwd_norm_router(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm, float *xn_out,
+                           int8_t *qs, float *d, int k, float eps, int n_expert, int n_used, float *logits, int32_t *ids, float *weights,
+                           float *probs, unsigned int *counter, int nseq) {
+    const size_t smem = (size_t)6 * k * sizeof(float);
+    if (k % 256 || n_expert < 1 || n_used < 1 || n_used > kMaxUsed || n_used > n_expert || (size_t)4 * k < (size_t)n_expert || smem > 200 * 1024 ||
+        x_out == x || x_out == residual) {
+        set_error_msg("norm_router: k a multiple of 256 that fits shared memory, 1 <= n_used <= n_expert <= 4k, x_out a buffer of its own");
+        return;
+    }
+    static size_t configured = 0;
+    if (smem > 44 * 1024 && smem > configured) {
+        const cudaError_t e = cudaFuncSetAttribute(norm_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error(e, "norm_router smem attribute");
+            return;
+        }
+        configured = smem;
+    }
+    launch_kc(PDL_ROUTER, "norm_router", norm_router_kernel, dim3((n_expert + 3) / 4, nseq), dim3(128), smem, w, x, residual, x_out, w_norm, xn_out, qs, d,
+              k, eps, n_expert, n_used, logits, ids, weights, probs, counter);
 }
 
 static int g_q80_rows_max_ctas = 148 * 4;

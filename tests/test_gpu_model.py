@@ -155,6 +155,33 @@ def test_fused_tails_change_nothing(tiny):
         assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
 
 
+def test_fused_norm_and_router_change_nothing(tiny):
+    """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router, the default) and as two:
+    same tokens, same hidden states after every layer, same routed experts, same logits, bit for bit; one and four
+    sequences."""
+    hp, w, gm, om = tiny
+    runs = {}
+    for fuse in (1, 0, 1):
+        gm.set_option("fuse_norm_router", fuse)
+        gm.set_trace(True)
+        toks, tok, traces = [], 3, []
+        for pos in range(6):
+            tok = gm.forward(tok, pos)
+            toks.append(tok)
+            x, ids = gm.read_trace()
+            traces.append((x.copy(), ids.copy()))
+        gm.set_trace(False)
+        batch = [gm.forward_batch([5 + pos, 9, 100 + pos, 7], [pos] * 4).tolist() for pos in range(3)]
+        runs.setdefault(fuse, []).append((toks, traces, gm.logits(4).copy(), batch))
+    gm.set_option("fuse_norm_router", 1)
+    ref = runs[0][0]
+    for toks, traces, logits, batch in runs[1]:
+        assert toks == ref[0] and batch == ref[3]
+        assert np.array_equal(logits.view(np.uint32), ref[2].view(np.uint32))
+        for (x, ids), (rx, rids) in zip(traces, ref[1]):
+            assert np.array_equal(x.view(np.uint32), rx.view(np.uint32)) and np.array_equal(ids, rids)
+
+
 def test_prefill_equals_sequential_decode(tiny):
     """crates/llamd-testing/tests/vulkan_prefill.rs:48-136: prefill gives the token (and here the logits and the
     K/V cache, bit for bit) of sequential decode, for (tile, length) pairs that straddle tile and chunk boundaries."""
