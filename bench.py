@@ -315,6 +315,8 @@ def main():
     ap.add_argument("--resident", type=int, default=-1, help="1: decode through the resident kernel (one cooperative launch per token); "
                     "0: the per-op pass; default: the library's own default")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-rank-arrive", action="store_true", help="(A/B) expert parallelism: one arrival per rank and launch on the return "
+                    "path instead of one per CTA of the down projection (measured 0.8 %% slower at 4 GPUs)")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
     ap.add_argument("--prefetch", action="store_true", help="(experiment) matvec launches ask L2 for the next matvec's weights; measured slightly slower")
     ap.add_argument("--batch-sweep", default="", help="(secondary) comma list of batch sizes: time forward_batch over that many "
@@ -385,6 +387,8 @@ def main():
     else:
         m = CudaModel.load_synthetic(hp, 0, max_kv=max_kv, max_seq=max_seq)
     log(f"[rank {rank}] model resident: {m.weight_bytes() / 2**30:.2f} GiB in {time.time() - t0:.1f}s on {info.name}")
+    if args.ep_rank_arrive:
+        m.set_option("ep_rank_arrive", 1)
     if args.kv == "f16":
         m.set_option("kv_f16", 1)  # (before the attach: the caches are re-allocated)
     if ep and not args.ep_nccl:

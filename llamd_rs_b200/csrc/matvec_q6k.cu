@@ -81,6 +81,19 @@ __host__ __device__ inline size_t matvec_ad_offset(int nseq, int nb) {
     return act + (((ex > nat ? ex : nat) + 15) & ~(size_t)15);
 }
 
+// One CTA of a launch with peer outputs is done (its stores, if any, fenced at system scope by the caller): count it,
+// and let the CTA that completes the count tell every rank that this rank's rows are in place.
+__device__ __forceinline__ void peer_arrive(const PeerOutPlan &peer, unsigned int total_ctas, int home) {
+    if (!peer.local_done) {  // the per-CTA form: every CTA arrives on its slot's home rank
+        atomicAdd_system(peer.arrive_tab[home], 1u);
+        return;
+    }
+    if (atomicInc(peer.local_done, total_ctas - 1) == total_ctas - 1) {  // wraps to 0 for the next launch
+        __threadfence_system();  // (orders the counted CTAs' fenced stores before the arrivals below)
+        for (int h = 0; h < peer.world; h++) atomicAdd_system(peer.arrive_tab[h], 1u);
+    }
+}
+
 // EP: the expert-parallel forms (requests pushed by peers, rows stored to peers); kept out of the other instantiations.
 // EXTRA: the optional L2 prefetch plan and the SiLU tail. Both are off by default, and their code in the plain kernel
 // cost every launch ~0.3 us and lm_head 3 % of its bandwidth, so they too are an instantiation of their own.
@@ -152,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         if (e < 0 || e >= p.n_expert) e = 0;
         if (e < p.own_lo || e >= p.own_hi) {  // another GPU's expert
             // by now this CTA has read everything it needs of the request: the home rank may count it
-            if (EP && p.peer.out_tab && p.peer.all_arrive && tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
+            if (EP && p.peer.out_tab && tid == 0) peer_arrive(p.peer, gridDim.x, slot / p.peer.div);
             return;
         }
         expert_off = (long long)(e - p.own_lo) * p.expert_units;
@@ -317,9 +330,9 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         }
     }
     if (EP && !MULTI && p.peer.out_tab) {  // uniform over the launch; CTAs of slots this rank does not own left above
-        __threadfence_system();  // the rows are visible on the home GPU before the arrival is
+        __threadfence_system();  // the rows are visible on the home GPU before the rank's arrival is
         __syncthreads();
-        if (tid == 0) atomicAdd_system(p.peer.arrive_tab[slot / p.peer.div], 1u);
+        if (tid == 0) peer_arrive(p.peer, gridDim.x, slot / p.peer.div);
     }
     // ---- tail of a gate+up launch: silu(gate) * up and its Q8_K form, by the slot's last CTA ----
     if (EXTRA && !MULTI && NSEQ == 1 && p.tail.counter) {  // uniform over the launch

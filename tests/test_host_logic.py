@@ -137,7 +137,7 @@ def test_expert_parallel_protocol_on_gloo(world):
 # barrier. This is that protocol with the GPU taken out: ranks are step lists, a random scheduler picks any step whose
 # wait condition holds, and every read checks that it sees the layer it belongs to (a record or a row replaced too
 # early, or read before it arrived, shows up as a wrong tag).
-def _simulate_peer_exchange(world, layers, ctas, seed, all_arrive=True):
+def _simulate_peer_exchange(world, layers, ctas, seed, mode="per_rank"):
     import random
 
     rng = random.Random(seed)
@@ -148,7 +148,11 @@ def _simulate_peer_exchange(world, layers, ctas, seed, all_arrive=True):
     rec = [[-1] * world for _ in range(world)]             # rec[dst][src]: layer tag of src's request record at dst
     out = [[-1] * n_used for _ in range(world)]            # out[home][slot]: layer tag of the expert rows
     owner = lambda home, slot, layer: (home + slot + layer) % world  # which rank owns that slot's expert
-    target_rows = (world if all_arrive else 1) * n_used * ctas
+    # per_cta (the kernels' default): every CTA arrives on its slot's home; per_rank (option ep_rank_arrive): a rank counts its
+    # own down CTAs and arrives once on every home when the last is done; owners_only: only the CTAs that store rows do (the
+    # broken variant)
+    target_rows = {"per_rank": world, "per_cta": world * n_used * ctas, "owners_only": n_used * ctas}[mode]
+    local_done = [0] * world
 
     def steps(r):
         for l in range(layers):
@@ -193,8 +197,13 @@ def _simulate_peer_exchange(world, layers, ctas, seed, all_arrive=True):
             assert rec[r][h] == l, f"rank {r} layer {l}: a down CTA read a record of layer {rec[r][h]}"
             if owner(h, s, l) == r:
                 out[h][s] = l
-                arrive[h] += 1
-            elif all_arrive:
+            if mode == "per_rank":
+                local_done[r] += 1
+                if local_done[r] == world * n_used * ctas:  # the CTA that completes the count signals every home
+                    local_done[r] = 0
+                    for hh in range(world):
+                        arrive[hh] += 1
+            elif owner(h, s, l) == r or mode == "per_cta":
                 arrive[h] += 1
         else:  # norm: all rows of this layer are in; clear the counter
             assert all(t == st[1] for t in out[r]), f"rank {r} layer {st[1]}: rows {out[r]}"
@@ -211,6 +220,7 @@ def _simulate_peer_exchange(world, layers, ctas, seed, all_arrive=True):
 def test_peer_exchange_protocol_orders_reads_and_writes(world, ctas):
     for seed in range(40):
         _simulate_peer_exchange(world, layers=5, ctas=ctas, seed=seed)
+        _simulate_peer_exchange(world, layers=5, ctas=ctas, seed=seed, mode="per_cta")
 
 
 def test_peer_exchange_needs_every_cta_to_arrive():
@@ -218,4 +228,4 @@ def test_peer_exchange_needs_every_cta_to_arrive():
     read the old one: the model finds such a schedule."""
     with pytest.raises(AssertionError):
         for seed in range(400):
-            _simulate_peer_exchange(4, layers=6, ctas=2, seed=seed, all_arrive=False)
+            _simulate_peer_exchange(4, layers=6, ctas=2, seed=seed, mode="owners_only")
