@@ -134,6 +134,8 @@ unsafe extern "C" {
     pub fn llamd_fwd_qk_norm_rope_store_tile_kv16(q: *mut f32, wq: *const f32, k: *mut f32, wk: *const f32, v: *const f32, kc: *mut c_void, vc: *mut c_void, n_head: c_int, n_head_kv: c_int, hd: c_int, meta: *const i32, rope_tab: *const f32, eps: f32, ntok: c_int);
     pub fn llamd_fwd_attention_meta_kv16(q: *const f32, kc: *const c_void, vc: *const c_void, out: *mut f32, scores: *mut f32, n_head: c_int, n_head_kv: c_int, hd: c_int, meta: *const i32, max_kv: c_int, nseq: c_int);
     pub fn llamd_fwd_kv16_expand(kc16: *const c_void, vc16: *const c_void, kc32: *mut f32, vc32: *mut f32, n_pos: c_int, kv_dim: c_int);
+    pub fn llamd_fwd_attention_rope_meta(q: *const f32, wq: *const f32, k: *const f32, wk: *const f32, v: *const f32, kc: *mut f32, vc: *mut f32, out: *mut f32, scores: *mut f32, n_head: c_int, n_head_kv: c_int, hd: c_int, meta: *const i32, rope_tab: *const f32, eps: f32, max_kv: c_int, nseq: c_int);
+    pub fn llamd_fwd_attention_rope_meta_kv16(q: *const f32, wq: *const f32, k: *const f32, wk: *const f32, v: *const f32, kc: *mut c_void, vc: *mut c_void, out: *mut f32, scores: *mut f32, n_head: c_int, n_head_kv: c_int, hd: c_int, meta: *const i32, rope_tab: *const f32, eps: f32, max_kv: c_int, nseq: c_int);
     pub fn llamd_fwd_matvec_grouped_x2_silu_quant(wa: *const c_void, wb: *const c_void, ids: *const i32, aq: *const i8, ad: *const f32, oa: *mut f32, ob: *mut f32, counter: *mut c_uint, qs: *mut i8, d: *mut f32, blocks: c_int, rows: c_int, n_used: c_int, nseq: c_int);
     pub fn llamd_fwd_attention_meta_quant(q: *const f32, kc: *const f32, vc: *const f32, out: *mut f32, scores: *mut f32, n_head: c_int, n_head_kv: c_int, hd: c_int, meta: *const i32, max_kv: c_int, nseq: c_int, counter: *mut c_uint, qs: *mut i8, d: *mut f32);
     pub fn llamd_fwd_act_f16_rm(aq: *const i8, ad: *const f32, act16: *mut c_void, nblocks: usize);

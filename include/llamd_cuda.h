@@ -322,6 +322,17 @@ void llamd_fwd_qk_norm_rope_store_tile_kv16(float *q, const float *wq, float *k,
 void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head,
                                    int n_head_kv, int hd, const int32_t *meta, int max_kv, int nseq);
 void llamd_fwd_kv16_expand(const void *kc16, const void *vc16, float *kc32, float *vc32, int n_pos, int kv_dim);
+/* ---- one decode launch fewer per layer: QK-norm, RoPE and the K/V store inside the attention-scores launch ----
+ * (no counterpart in the reference, which launches op::norm_rope, op::k_norm_rope_store and op::attention_meta apart,
+ * crates/llamd-rocm/src/forward.rs). q, k, v are the projections as the matvec left them (not modified); the K and V rows
+ * of each sequence's position meta[2s+1] are stored; out gets the attention output. Same bits as
+ * llamd_fwd_qk_norm_rope_store followed by llamd_fwd_attention_meta (_kv16: over binary16 caches). */
+void llamd_fwd_attention_rope_meta(const float *q, const float *wq, const float *k, const float *wk, const float *v, float *kc,
+                                   float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
+                                   const int32_t *meta, const float *rope_tab, float eps, int max_kv, int nseq);
+void llamd_fwd_attention_rope_meta_kv16(const float *q, const float *wq, const float *k, const float *wk, const float *v,
+                                        void *kc, void *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
+                                        const int32_t *meta, const float *rope_tab, float eps, int max_kv, int nseq);
 /* ---- two decode launches fewer per layer: the producer's last CTA does the small follow-up op itself ----
  * llamd_fwd_matvec_grouped_x2_silu_quant = llamd_fwd_matvec_grouped_x2 (crates/llamd-rocm/src/forward.rs: planar_grouped_x2)
  * followed by llamd_fwd_silu_mul_quant of oa, ob: qs [slots][rows], d [slots][rows/256]; rows % 256 == 0.

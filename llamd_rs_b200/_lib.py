@@ -101,6 +101,8 @@ SIGNATURES = {
     "llamd_fwd_qk_norm_rope_store_tile_kv16": (None, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32]),
     "llamd_fwd_attention_meta_kv16": (None, [vp, vp, vp, vp, vp, i32, i32, i32, vp, i32, i32]),
     "llamd_fwd_kv16_expand": (None, [vp, vp, vp, vp, i32, i32]),
+    "llamd_fwd_attention_rope_meta": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32]),
+    "llamd_fwd_attention_rope_meta_kv16": (None, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, i32, i32]),
     "llamd_cuda_rope_table": (i32, [vp, i32, i32, f32]),
     "llamd_fwd_rope": (None, [vp, i32, i32, i32, vp]),
     "llamd_fwd_norm_rope": (None, [vp, vp, i32, i32, vp, vp, f32, i32]),

@@ -38,6 +38,12 @@ void llamd_fwd_matmul_f32_tokens(const float *w, const float *x, float *out, int
 void llamd_fwd_norm_router(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm, float *xn_out,
                            int8_t *qs, float *d, int k, float eps, int n_expert, int n_used, float *logits, int32_t *ids, float *weights,
                            float *probs, unsigned int *counter, int nseq);
+void llamd_fwd_attention_rope_meta(const float *q, const float *wq, const float *k, const float *wk, const float *v, float *kc, float *vc,
+                                   float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab,
+                                   float eps, int max_kv, int nseq);
+void llamd_fwd_attention_rope_meta_kv16(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc,
+                                        float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                                        const float *rope_tab, float eps, int max_kv, int nseq);
 void llamd_fwd_qk_norm_rope_store_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc, int n_head,
                                        int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int nseq, int max_kv);
 void llamd_fwd_qk_norm_rope_store_tile_kv16(float *q, const float *wq, float *k, const float *wk, const float *v, void *kc, void *vc,
@@ -183,6 +189,7 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int fuse_rope_attn = 1;  // option "fuse_rope_attn": QK-norm, RoPE and the KV store inside the attention-scores launch (decode pass)
     int fuse_norm_router = 1;  // option "fuse_norm_router": the FFN norm and the router as one launch (decode pass)
     int kv16 = 0;            // option "kv_f16": the caches hold binary16 values (rounded at the store)
     Buf kc32, vc32;          // a prefill tile's view of one layer's binary16 cache, widened to f32 ([max_kv][kv_dim] each)
@@ -415,6 +422,24 @@ void queue_token(Model &m, int nseq) {
                         m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
         mark(LLAMD_PH_QKV);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
+        const bool fuse = m.fuse_tails && !m.kv16 && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
+        const bool fuse_ra = m.fuse_rope_attn && !fuse && hd % 16 == 0 && hd <= 256;
+        if (fuse_ra) {
+            // ... inside the attention-scores launch: one launch fewer, the same bits
+            if (m.kv16)
+                llamd_fwd_attention_rope_meta_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
+                                                   l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p,
+                                                   m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(),
+                                                   hp.rms_eps, m.max_kv, nseq);
+            else
+                llamd_fwd_attention_rope_meta(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
+                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
+                                              l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
+                                              m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, nseq);
+            mark(LLAMD_PH_ROPE);
+            mark(LLAMD_PH_ATTENTION);
+            llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+        } else {
         if (m.kv16)
             llamd_fwd_qk_norm_rope_store_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
                                               l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
@@ -424,7 +449,6 @@ void queue_token(Model &m, int nseq) {
                                      l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
                                      l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
         mark(LLAMD_PH_ROPE);
-        const bool fuse = m.fuse_tails && !m.kv16 && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
         if (fuse) {
             // the CTA that finishes a sequence's attention last also writes its Q8_K form
             llamd_fwd_attention_meta_quant(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
@@ -441,6 +465,7 @@ void queue_token(Model &m, int nseq) {
             mark(LLAMD_PH_ATTENTION);
             // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
             llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+        }
         }
         mark(LLAMD_PH_QUANT);
         matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
@@ -901,6 +926,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "ep_rank_arrive")) {
         if (m->ep_rank_arrive != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->ep_rank_arrive = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_rope_attn")) {
+        if (m->fuse_rope_attn != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_rope_attn = value;
         return 0;
     }
     if (!strcmp(name, "fuse_norm_router")) {

@@ -841,6 +841,149 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const float *__restric
     }
 }
 
+// attn_scores_kernel with the launch in front of it folded in (decode): QK-norm, RoPE and the K/V store of the token's
+// own position (norm_rope_kernel). Every CTA of head h norms and ropes h's query itself (a 128-add chain, repeated by the
+// kSplitT CTAs of the head); the CTA whose tiles contain the token's position does the same for the kv head's new key
+// and scores it from shared memory instead of from the cache; of the query heads that share a kv head the first one's
+// such CTA stores the K and V rows for later tokens (and for attn_out_kernel, which follows in the stream). The same
+// operations on the same values as the two launches: with a binary16 cache the new key is scored as the cache will
+// hold it, rounded.
+template <class KVT>
+__global__ void __launch_bounds__(256) attn_rope_scores_kernel(const float *__restrict__ q_raw, const float *__restrict__ wq,
+                                                               const float *__restrict__ k_raw, const float *__restrict__ wk,
+                                                               const float *__restrict__ v_raw, KVT *__restrict__ kc, KVT *__restrict__ vc,
+                                                               float *__restrict__ scores, int n_head, int n_head_kv, int hd,
+                                                               const int32_t *__restrict__ meta, int max_kv, int kv_stride,
+                                                               const float *__restrict__ rope_tab, float eps) {
+    extern __shared__ __align__(16) float sm[];
+    const int stride = hd + 1, half = hd / 2;
+    float *sq = sm;                 // [hd] the roped query
+    float *tile = sm + hd;          // [2][kAttTile][stride]
+    float *s_raw = tile + 2 * kAttTile * stride;  // [2][hd] raw q, raw k
+    float *sk = s_raw + 2 * hd;     // [hd] the roped new key, as the cache holds it
+    __shared__ float s_scale[2];
+    pdl_trigger();
+    pdl_wait();
+    const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+    const int pos = meta[2 * seq + 1], n_kv = pos + 1;
+    const int ratio = n_head / n_head_kv, kv_dim = n_head_kv * hd, kvh = h / ratio;
+    const int ti_pos = pos / kAttTile;
+    const bool need_k = (ti_pos % kSplitT) == c;        // this CTA scores the new key
+    const bool storer = need_k && (h % ratio) == 0;     // ... and writes the K and V rows of the position
+    KVT *krow = kc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)kvh * hd;
+    KVT *vrow = vc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)kvh * hd;
+    const KVT *kb = kc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
+    float *sc = scores + ((size_t)seq * n_head + h) * max_kv;
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    const int hd4 = hd / 4, per_tile4 = kAttTile * hd4;
+    const int n_tiles = (n_kv + kAttTile - 1) / kAttTile;
+    constexpr int kMaxLd = 8;
+    float4 reg[kMaxLd];
+    auto fetch = [&](int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / hd4, cc = idx - r * hd4;
+            const int t = ti * kAttTile + r;
+            // (the token's own row is not in the cache yet: it comes from shared memory below)
+            reg[j] = (idx < per_tile4 && t < pos) ? KvIo<KVT>::ld4(kb + (size_t)t * kv_dim + 4 * cc) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](float *dst, int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / hd4, cc = idx - r * hd4;
+            if (idx < per_tile4 && ti * kAttTile + r != pos) {  // (the token's own row is written below, by other threads)
+                float *p = dst + r * stride + 4 * cc;
+                p[0] = reg[j].x; p[1] = reg[j].y; p[2] = reg[j].z; p[3] = reg[j].w;
+            }
+        }
+    };
+    if (c < n_tiles) fetch(c);  // the cached rows travel while the query is prepared
+    // ---- QK-norm (crates/llamd-runtime/src/layer.rs:62-79) and RoPE (crates/llamd-cpu/src/lib.rs:158-209) ----
+    const float *qh = q_raw + ((size_t)seq * n_head + h) * hd, *kh = k_raw + ((size_t)seq * n_head_kv + kvh) * hd;
+    for (int i = tid; i < hd; i += blockDim.x) {
+        s_raw[i] = qh[i];
+        if (need_k) s_raw[hd + i] = kh[i];
+    }
+    __syncthreads();
+    if ((tid == 0 && wq) || (tid == 32 && wk && need_k)) {  // each sum of squares walked in order, the two side by side
+        const float *sx = s_raw + (tid ? hd : 0);
+        float sum = 0.0f;
+#pragma unroll 8
+        for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
+        s_scale[tid ? 1 : 0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), eps)));
+    }
+    __syncthreads();
+    for (int idx = tid; idx < (need_k ? 2 : 1) * half; idx += blockDim.x) {
+        const bool is_k = idx >= half;
+        const int i = is_k ? idx - half : idx;
+        const float *sx = s_raw + (is_k ? hd : 0);
+        const float *w = is_k ? wk : wq;
+        float a = sx[i], b = sx[i + half];
+        if (w) {
+            const float nsc = s_scale[is_k ? 1 : 0];
+            a = __fmul_rn(__fmul_rn(a, nsc), w[i]);
+            b = __fmul_rn(__fmul_rn(b, nsc), w[i + half]);
+        }
+        const float2 cs = *reinterpret_cast<const float2 *>(rope_tab + ((size_t)pos * half + i) * 2);
+        const float o0 = __fsub_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+        const float o1 = __fadd_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+        if (!is_k) {
+            sq[i] = o0;
+            sq[i + half] = o1;
+        } else {
+            // as the cache holds it (a binary16 cache rounds here, once); the storer writes the rows
+            KVT t0, t1;
+            KvIo<KVT>::st(&t0, o0);
+            KvIo<KVT>::st(&t1, o1);
+            sk[i] = (float)t0;
+            sk[i + half] = (float)t1;
+            if (storer) {
+                krow[i] = t0;
+                krow[i + half] = t1;
+                const float *vs = v_raw + ((size_t)seq * n_head_kv + kvh) * hd;
+                KvIo<KVT>::st(vrow + i, vs[i]);
+                KvIo<KVT>::st(vrow + i + half, vs[i + half]);
+            }
+        }
+    }
+    __syncthreads();
+    // ---- scores, as attn_scores_kernel ----
+    int buf = 0;
+    for (int ti = c; ti < n_tiles; ti += kSplitT, buf ^= 1) {
+        float *cur = tile + buf * kAttTile * stride;
+        stash(cur, ti);
+        if (ti == ti_pos)
+            for (int i = tid; i < hd; i += blockDim.x) cur[(pos - ti * kAttTile) * stride + i] = sk[i];
+        __syncthreads();
+        if (ti + kSplitT < n_tiles) fetch(ti + kSplitT);
+        const int t = ti * kAttTile + tid;
+        if (tid < kAttTile && t < n_kv) {
+            const float *kr = cur + tid * stride;
+            float dot = 0.0f;
+            if ((hd & 15) == 0) {
+                float pa[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(sq[i], kr[i]);
+                for (int d0 = 0; d0 < hd; d0 += 16) {
+                    const int dn = (d0 + 16 < hd) ? d0 + 16 : d0;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(sq[dn + i], kr[dn + i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) dot = __fadd_rn(dot, pa[i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pa[i] = pb[i];
+                }
+            } else {
+                for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(sq[d], kr[d]));
+            }
+            sc[t] = __fmul_rn(dot, scale);
+        }
+    }
+}
+
 constexpr int kPvTile = 256;  // positions per V tile
 
 // With a TailPlan the CTA that finishes a sequence last also writes the Q8_K form of that sequence's whole
@@ -1442,6 +1585,61 @@ void llamd_fwd_attention_meta_quant(const float *q, const float *kc, const float
 void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head, int n_head_kv,
                                    int hd, const int32_t *meta, int max_kv, int nseq) {
     attention_launch(q, (const float *)kc, (const float *)vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv, TailPlan{}, true);
+}
+// QK-norm + RoPE + KV store + attention of one decode token per sequence in TWO launches (scores with the preparation
+// folded in, then softmax and weighted values) instead of three; q, k, v are the projections as the matvec left them
+// (they are not modified). kv16: the caches hold binary16. Same bits as llamd_fwd_qk_norm_rope_store followed by
+// llamd_fwd_attention_meta.
+static void attention_rope_launch(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc,
+                                  float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab,
+                                  float eps, int max_kv, int nseq, bool kv16) {
+    const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1) + 3 * hd) * sizeof(float);
+    const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
+    if (!scores || !meta || hd % (4 * kSplit) || hd > 256 || hd / 2 > 256 || kAttTile * (hd / 4) > 8 * 256 || kPvTile * (hd / kSplit) / 4 > 8 * 256 ||
+        n_head_kv <= 0 || n_head % n_head_kv || smem_a > 200 * 1024 || smem_b > 200 * 1024) {
+        set_error_msg("attention (with the rope folded in): needs the scores buffer, positions on the device, and a head_dim the kernels divide");
+        return;
+    }
+    static size_t conf_a[2] = {0, 0}, conf_b[2] = {0, 0};
+    if (smem_a > 48 * 1024 && smem_a > conf_a[kv16]) {
+        const cudaError_t e = kv16 ? cudaFuncSetAttribute(attn_rope_scores_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a)
+                                   : cudaFuncSetAttribute(attn_rope_scores_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        if (e != cudaSuccess) {
+            set_error(e, "attention (rope + scores) smem attribute");
+            return;
+        }
+        conf_a[kv16] = smem_a;
+    }
+    if (smem_b > 48 * 1024 && smem_b > conf_b[kv16]) {
+        const cudaError_t e = kv16 ? cudaFuncSetAttribute(attn_out_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b)
+                                   : cudaFuncSetAttribute(attn_out_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+        if (e != cudaSuccess) {
+            set_error(e, "attention (output) smem attribute");
+            return;
+        }
+        conf_b[kv16] = smem_b;
+    }
+    if (kv16) {
+        launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<__half>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
+                  (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps);
+        launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc,
+                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{});
+    } else {
+        launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<float>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
+                  (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps);
+        launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc,
+                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{});
+    }
+}
+void llamd_fwd_attention_rope_meta(const float *q, const float *wq, const float *k, const float *wk, const float *v, float *kc, float *vc,
+                                   float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab,
+                                   float eps, int max_kv, int nseq) {
+    attention_rope_launch(q, wq, k, wk, v, kc, vc, out, scores, n_head, n_head_kv, hd, meta, rope_tab, eps, max_kv, nseq, false);
+}
+void llamd_fwd_attention_rope_meta_kv16(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc,
+                                        float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta,
+                                        const float *rope_tab, float eps, int max_kv, int nseq) {
+    attention_rope_launch(q, wq, k, wk, v, kc, vc, out, scores, n_head, n_head_kv, hd, meta, rope_tab, eps, max_kv, nseq, true);
 }
 void llamd_fwd_attention_meta(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv,
                               int hd, const int32_t *meta, int max_kv, int nseq) {

@@ -155,14 +155,17 @@ def test_fused_tails_change_nothing(tiny):
         assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
 
 
-def test_fused_norm_and_router_change_nothing(tiny):
-    """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router, the default) and as two:
-    same tokens, same hidden states after every layer, same routed experts, same logits, bit for bit; one and four
-    sequences."""
+@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn"])
+def test_fused_launches_change_nothing(tiny, option):
+    """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router), and with QK-norm, RoPE and
+    the KV store inside the attention-scores launch (option fuse_rope_attn) -- both the default -- against the separate
+    launches: same tokens, same hidden states after every layer, same routed experts, same logits and cache rows, bit for
+    bit; one and four sequences. (Positions beyond a 64-position tile, where the token's own row moves from tile to tile, are
+    covered by the 768-position run against the CPU fixture, which uses the defaults.)"""
     hp, w, gm, om = tiny
     runs = {}
     for fuse in (1, 0, 1):
-        gm.set_option("fuse_norm_router", fuse)
+        gm.set_option(option, fuse)
         gm.set_trace(True)
         toks, tok, traces = [], 3, []
         for pos in range(6):
@@ -172,12 +175,15 @@ def test_fused_norm_and_router_change_nothing(tiny):
             traces.append((x.copy(), ids.copy()))
         gm.set_trace(False)
         batch = [gm.forward_batch([5 + pos, 9, 100 + pos, 7], [pos] * 4).tolist() for pos in range(3)]
-        runs.setdefault(fuse, []).append((toks, traces, gm.logits(4).copy(), batch))
-    gm.set_option("fuse_norm_router", 1)
+        kv = [gm.read_kv(il, 3) for il in range(hp["n_layer"])]
+        runs.setdefault(fuse, []).append((toks, traces, gm.logits(4).copy(), batch, kv))
+    gm.set_option(option, 1)
     ref = runs[0][0]
-    for toks, traces, logits, batch in runs[1]:
+    for toks, traces, logits, batch, kv in runs[1]:
         assert toks == ref[0] and batch == ref[3]
         assert np.array_equal(logits.view(np.uint32), ref[2].view(np.uint32))
+        for (k, v), (rk, rv) in zip(kv, ref[4]):
+            assert np.array_equal(k.view(np.uint32), rk.view(np.uint32)) and np.array_equal(v.view(np.uint32), rv.view(np.uint32))
         for (x, ids), (rx, rids) in zip(traces, ref[1]):
             assert np.array_equal(x.view(np.uint32), rx.view(np.uint32)) and np.array_equal(ids, rids)
 
