@@ -26,6 +26,14 @@ void matvec_x3_batch(const MatvecPlans &pl, const void *w0, const void *w1, cons
     const int rows[3] = {rows0, rows1, rows2};
     launch_matvec(3, ws, os, rows, blocks, aq, ad, nseq, nullptr, 1, 0, 1, 0, nullptr, nullptr, 0, 0x7fffffff, pl);
 }
+// Q, K, V of one sequence with the attention norm (and the MoE combine before it) folded in: pl.norm says from what.
+void matvec_x3_norm(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, float *o0, float *o1, float *o2, int blocks,
+                    int rows0, int rows1, int rows2) {
+    const void *ws[3] = {w0, w1, w2};
+    float *os[3] = {o0, o1, o2};
+    const int rows[3] = {rows0, rows1, rows2};
+    launch_matvec(3, ws, os, rows, blocks, nullptr, nullptr, 1, nullptr, 1, 0, 1, /*ACT_NORM*/ 3, nullptr, nullptr, 0, 0x7fffffff, pl);
+}
 void matvec_grouped_x2_batch(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
                              float *oa, float *ob, int blocks, int rows, int n_used, int nseq) {
     const void *ws[2] = {wa, wb};

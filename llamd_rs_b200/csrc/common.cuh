@@ -172,12 +172,27 @@ __device__ __forceinline__ bool bounded_wait(const unsigned int *counter, unsign
     return false;
 }
 
+// The norm in front of a matvec, folded into it (one sequence, ungrouped): every CTA computes
+//   x' = x (+ sum_e cw[e] * down[e], e ascending: the MoE combine that closes the previous layer),
+//   xn = rms_norm(x') * w, and the Q8_K form of xn, which is the activation it multiplies;
+// CTA 0 also writes x' to x_out (null: x is not changed, as for the first layer). The operations and their order are
+// rms_norm_kernel's. x_out must not alias x or down: the other CTAs still read them.
+struct NormPlan {
+    const float *x;      // [k] null: no folded norm
+    const float *down;   // [n_used][k] or null
+    const float *cw;     // [n_used]
+    int n_used;
+    float *x_out;        // [k] or null
+    const float *w;      // [k] norm weights
+    float eps;
+};
 // The optional parts of ONE Q6_K matvec launch, passed by the caller with the launch (all empty by default).
 struct MatvecPlans {
     PrefetchPlan pf;
     TailPlan tail;
     PeerOutPlan peer;
     DispatchWait dwait;
+    NormPlan norm;
 };
 
 // Internal launch functions behind the extern "C" entry points of the same names; the model passes its plans here.
@@ -191,6 +206,8 @@ void launch_matvec_multi(int njobs, const void *const *w, float *const *out, con
 void matvec_batch(const MatvecPlans &pl, const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows, int nseq);
 void matvec_x3_batch(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0,
                      float *o1, float *o2, int blocks, int rows0, int rows1, int rows2, int nseq);
+void matvec_x3_norm(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, float *o0, float *o1, float *o2, int blocks,
+                    int rows0, int rows1, int rows2);
 void matvec_grouped_x2_batch(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,
                              float *oa, float *ob, int blocks, int rows, int n_used, int nseq);
 void matvec_grouped_pa_batch(const MatvecPlans &pl, const void *w, const int32_t *ids, const int8_t *aq, const float *ad, float *out,

@@ -69,9 +69,12 @@ struct MatvecParams {
     TailPlan tail;    // gate+up launches: the slot's last CTA also produces the SiLU-gated, quantized activation
     PeerOutPlan peer;  // expert parallelism: a slot's rows go to its home rank's buffer, followed by an arrival
     DispatchWait dwait;  // expert parallelism: the ids / activations are pushed by the peers; wait for all of them first
+    NormPlan norm;       // ACT_NORM: the activation is made here from the residual stream (combine + rms norm + Q8_K)
 };
 
-enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2 };
+//   ACT_NORM the activation is rms_norm(x + combine) * w, quantized, made by every CTA (NormPlan): the norm launch in front
+//            of the matvec folded into it.
+enum { ACT_Q8K = 0, ACT_F32 = 1, ACT_SILU = 2, ACT_NORM = 3 };
 
 // shared memory: [act image][exchange floats, aliased with the natural-order staging][activation block scales]
 __host__ __device__ inline size_t matvec_ad_offset(int nseq, int nb) {
@@ -210,6 +213,67 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
             const long long a_idx = MULTI ? s_aidx[s] : (p.ids ? slot / p.act_div : seq0 + s);
             const uint4 *src = reinterpret_cast<const uint4 *>(p.aq + a_idx * nb * 256) + o;
             reinterpret_cast<uint4 *>(s_nat)[i] = (EP && p.dwait.counter) ? __ldcg(src) : __ldg(src);  // written by peers: from L2
+        }
+    } else if (ACT == ACT_NORM) {
+        // ... made here from the residual stream: combine, norm (its sum of squares walked in order by one thread), weight,
+        // Q8_K (crates/llamd-runtime/src/layer.rs:243-258 and 281-287, crates/llamd-cpu/src/lib.rs:55-75, dot.rs:88-128)
+        const NormPlan &np = p.norm;
+        const int k = nb * 256, k4 = k / 4;
+        float *s_x = reinterpret_cast<float *>(smem + ((matvec_ad_offset(NSEQ, nb) + (size_t)NSEQ * nb * 4 + 15) & ~(size_t)15));
+        float *s_sq = s_x + k;
+        __shared__ float s_nscale;
+        for (int j0 = 0; j0 < k4; j0 += 2 * kThreads) {
+            const int ja = j0 + tid, jb = j0 + kThreads + tid;
+            float4 xa = ja < k4 ? reinterpret_cast<const float4 *>(np.x)[ja] : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 xb = jb < k4 ? reinterpret_cast<const float4 *>(np.x)[jb] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (np.down) {
+                float4 aa = make_float4(0.f, 0.f, 0.f, 0.f), ab = aa;
+                for (int e0 = 0; e0 < np.n_used; e0 += 4) {
+                    float4 da[4], db[4];
+                    float we[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int e = e0 + q;
+                        we[q] = e < np.n_used ? np.cw[e] : 0.0f;
+                        const float4 *d4 = reinterpret_cast<const float4 *>(np.down + (size_t)(e < np.n_used ? e : 0) * k);
+                        da[q] = (ja < k4 && e < np.n_used) ? __ldcg(d4 + ja) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        db[q] = (jb < k4 && e < np.n_used) ? __ldcg(d4 + jb) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        if (e0 + q < np.n_used) {
+                            aa.x = __fadd_rn(aa.x, __fmul_rn(we[q], da[q].x)); aa.y = __fadd_rn(aa.y, __fmul_rn(we[q], da[q].y));
+                            aa.z = __fadd_rn(aa.z, __fmul_rn(we[q], da[q].z)); aa.w = __fadd_rn(aa.w, __fmul_rn(we[q], da[q].w));
+                            ab.x = __fadd_rn(ab.x, __fmul_rn(we[q], db[q].x)); ab.y = __fadd_rn(ab.y, __fmul_rn(we[q], db[q].y));
+                            ab.z = __fadd_rn(ab.z, __fmul_rn(we[q], db[q].z)); ab.w = __fadd_rn(ab.w, __fmul_rn(we[q], db[q].w));
+                        }
+                }
+                xa = make_float4(__fadd_rn(xa.x, aa.x), __fadd_rn(xa.y, aa.y), __fadd_rn(xa.z, aa.z), __fadd_rn(xa.w, aa.w));
+                xb = make_float4(__fadd_rn(xb.x, ab.x), __fadd_rn(xb.y, ab.y), __fadd_rn(xb.z, ab.z), __fadd_rn(xb.w, ab.w));
+            }
+            if (ja < k4) {
+                reinterpret_cast<float4 *>(s_x)[ja] = xa;
+                reinterpret_cast<float4 *>(s_sq)[ja] = make_float4(__fmul_rn(xa.x, xa.x), __fmul_rn(xa.y, xa.y), __fmul_rn(xa.z, xa.z), __fmul_rn(xa.w, xa.w));
+                if (blockIdx.x == 0 && np.x_out) reinterpret_cast<float4 *>(np.x_out)[ja] = xa;
+            }
+            if (jb < k4) {
+                reinterpret_cast<float4 *>(s_x)[jb] = xb;
+                reinterpret_cast<float4 *>(s_sq)[jb] = make_float4(__fmul_rn(xb.x, xb.x), __fmul_rn(xb.y, xb.y), __fmul_rn(xb.z, xb.z), __fmul_rn(xb.w, xb.w));
+                if (blockIdx.x == 0 && np.x_out) reinterpret_cast<float4 *>(np.x_out)[jb] = xb;
+            }
+        }
+        __syncthreads();
+        if (tid == 0) s_nscale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(chain_sum(s_sq, k, 0.0f), (float)k), np.eps)));
+        __syncthreads();
+        const float nscale = s_nscale;
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int blk = warp; blk < nb; blk += kThreads / 32) {
+            const float4 a = reinterpret_cast<const float4 *>(s_x + blk * 256 + lane * 8)[0], c4 = reinterpret_cast<const float4 *>(s_x + blk * 256 + lane * 8)[1];
+            const float4 wa = __ldg(reinterpret_cast<const float4 *>(np.w + blk * 256 + lane * 8)), wb = __ldg(reinterpret_cast<const float4 *>(np.w + blk * 256 + lane * 8) + 1);
+            const float v[8] = {__fmul_rn(__fmul_rn(a.x, nscale), wa.x), __fmul_rn(__fmul_rn(a.y, nscale), wa.y), __fmul_rn(__fmul_rn(a.z, nscale), wa.z),
+                                __fmul_rn(__fmul_rn(a.w, nscale), wa.w), __fmul_rn(__fmul_rn(c4.x, nscale), wb.x), __fmul_rn(__fmul_rn(c4.y, nscale), wb.y),
+                                __fmul_rn(__fmul_rn(c4.z, nscale), wb.z), __fmul_rn(__fmul_rn(c4.w, nscale), wb.w)};
+            q8k_quantize_block(v, lane, s_nat + blk * 256, s_ad + blk, nullptr);
         }
     } else {
         // ... produced here: one warp per 256-element block quantizes the f32 activation
@@ -357,7 +421,10 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
     }
 }
 
-static size_t matvec_smem_bytes(int nseq, int nb) { return matvec_ad_offset(nseq, nb) + (size_t)nseq * nb * 4; }
+static size_t matvec_smem_bytes(int nseq, int nb, int act = ACT_Q8K) {
+    const size_t base = matvec_ad_offset(nseq, nb) + (size_t)nseq * nb * 4;
+    return act == ACT_NORM ? ((base + 15) & ~(size_t)15) + (size_t)2 * nb * 256 * 4 : base;  // + the residual stream and its squares
+}
 
 // sequences per CTA for small ungrouped matrices at batch > 1 (0: never split), and what "small" means
 int g_batch_group = 2;  // set through llamd_fwd_set_batch_group
@@ -365,7 +432,7 @@ constexpr int kBatchSplitMaxCtas = 512;
 
 template <int NSEQ, bool MULTI = false, int ACT = ACT_Q8K>
 static void launch_t(const MatvecParams &p, dim3 grid, const MatvecPlans &plans) {
-    const size_t smem = matvec_smem_bytes(NSEQ, p.nb);
+    const size_t smem = matvec_smem_bytes(NSEQ, p.nb, ACT);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(matvec_q6k_kernel<NSEQ, MULTI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -377,6 +444,7 @@ static void launch_t(const MatvecParams &p, dim3 grid, const MatvecPlans &plans)
     }
     MatvecParams q = p;
     q.pf = plans.pf;
+    q.norm = plans.norm;
     q.dwait = plans.dwait;
     q.peer = plans.peer;
     q.tail = plans.tail;
@@ -470,6 +538,15 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
         nseq = g;
     }
     const dim3 grid(p.ctas_per_slot * p.n_slots);
+    if (act_mode == ACT_NORM) {
+        if (nseq != 1 || ids || !plans.norm.x || !plans.norm.w || plans.norm.x_out == plans.norm.x || (plans.norm.down && (plans.norm.n_used < 1 || !plans.norm.cw)) ||
+            matvec_smem_bytes(1, blocks, ACT_NORM) > 200 * 1024) {
+            set_error_msg("matvec: a folded norm takes one sequence, ungrouped, with x, w and an x_out other than x");
+            return;
+        }
+        launch_t<1, false, ACT_NORM>(p, grid, plans);
+        return;
+    }
     if (act_mode == ACT_SILU) {
         if (nseq != 1 || !xf || !xu) {
             set_error_msg("matvec: the silu activation mode takes gate and up, one sequence per slot");

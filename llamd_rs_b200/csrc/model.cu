@@ -189,6 +189,8 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int fuse_norm_qkv = 0;   // option "fuse_norm_qkv": the attention norm (and the combine before it) inside the QKV matvec (one sequence);
+                             // the same bits, measured 0.8 % slower (288.1 against 290.5 tok/s: 160 CTAs each repeat the combine), so off
     int fuse_rope_attn = 1;  // option "fuse_rope_attn": QK-norm, RoPE and the KV store inside the attention-scores launch (decode pass)
     int fuse_norm_router = 1;  // option "fuse_norm_router": the FFN norm and the router as one launch (decode pass)
     int kv16 = 0;            // option "kv_f16": the caches hold binary16 values (rounded at the store)
@@ -409,6 +411,21 @@ void queue_token(Model &m, int nseq) {
         // Attention norm, f32 and Q8_K in one pass (Q, K and V read the same
         // activation). From the second layer on the same launch first finishes
         // the previous layer: x += sum_e w_e * down_e.
+        // (with one sequence on one GPU both fold into the QKV matvec, whose every CTA then makes its own activation: one
+        // launch fewer; it may not update the stream in place, so it needs the stream in m.xb, where a fused norm + router
+        // launch leaves it)
+        const bool fuse_nq = m.fuse_norm_qkv && nseq == 1 && m.ep_world == 1 && (il == 0 || x_res != x);
+        if (fuse_nq) {
+            MatvecPlans pl = plan_static(m, &l.attn_out);
+            pl.norm = NormPlan{x_res, il ? m.e_down.as<float>() : nullptr, m.expert_w.as<float>(), nu, il ? x : nullptr, l.attn_norm.as<float>(),
+                               hp.rms_eps};
+            matvec_x3_norm(pl, l.attn_q.p, l.attn_k.p, l.attn_v.p, m.q.as<float>(), m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd);
+            if (il) {
+                x_res = x;
+                trace_x(il - 1);
+            }
+            mark(LLAMD_PH_ATTN_NORM);
+        } else {
         if (il == 0) {
             llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
         } else {
@@ -420,6 +437,7 @@ void queue_token(Model &m, int nseq) {
         mark(LLAMD_PH_ATTN_NORM);
         matvec_x3_batch(plan_static(m, &l.attn_out), l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
                         m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+        }
         mark(LLAMD_PH_QKV);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
         const bool fuse = m.fuse_tails && !m.kv16 && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
@@ -926,6 +944,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "ep_rank_arrive")) {
         if (m->ep_rank_arrive != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->ep_rank_arrive = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_norm_qkv")) {
+        if (m->fuse_norm_qkv != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_norm_qkv = value;
         return 0;
     }
     if (!strcmp(name, "fuse_rope_attn")) {

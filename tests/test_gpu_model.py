@@ -155,15 +155,16 @@ def test_fused_tails_change_nothing(tiny):
         assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
 
 
-@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn"])
+@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv"])
 def test_fused_launches_change_nothing(tiny, option):
-    """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router), and with QK-norm, RoPE and
-    the KV store inside the attention-scores launch (option fuse_rope_attn) -- both the default -- against the separate
-    launches: same tokens, same hidden states after every layer, same routed experts, same logits and cache rows, bit for
+    """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router), with QK-norm, RoPE and
+    the KV store inside the attention-scores launch (option fuse_rope_attn), and with the attention norm and the MoE combine
+    inside the QKV matvec (option fuse_norm_qkv; off by default) -- against the separate launches: same tokens, same hidden states after every layer, same routed experts, same logits and cache rows, bit for
     bit; one and four sequences. (Positions beyond a 64-position tile, where the token's own row moves from tile to tile, are
     covered by the 768-position run against the CPU fixture, which uses the defaults.)"""
     hp, w, gm, om = tiny
     runs = {}
+    default = 0 if option == "fuse_norm_qkv" else 1  # (measured slower, so off unless asked for)
     for fuse in (1, 0, 1):
         gm.set_option(option, fuse)
         gm.set_trace(True)
@@ -177,7 +178,7 @@ def test_fused_launches_change_nothing(tiny, option):
         batch = [gm.forward_batch([5 + pos, 9, 100 + pos, 7], [pos] * 4).tolist() for pos in range(3)]
         kv = [gm.read_kv(il, 3) for il in range(hp["n_layer"])]
         runs.setdefault(fuse, []).append((toks, traces, gm.logits(4).copy(), batch, kv))
-    gm.set_option(option, 1)
+    gm.set_option(option, default)
     ref = runs[0][0]
     for toks, traces, logits, batch, kv in runs[1]:
         assert toks == ref[0] and batch == ref[3]
