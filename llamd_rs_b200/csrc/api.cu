@@ -26,6 +26,12 @@ void matvec_x3_batch(const MatvecPlans &pl, const void *w0, const void *w1, cons
     const int rows[3] = {rows0, rows1, rows2};
     launch_matvec(3, ws, os, rows, blocks, aq, ad, nseq, nullptr, 1, 0, 1, 0, nullptr, nullptr, 0, 0x7fffffff, pl);
 }
+void matvec_grouped_pa_silu(const MatvecPlans &pl, const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
+                            int rows, int n_used, int nseq) {
+    const void *ws[1] = {w};
+    float *os[1] = {out};
+    launch_matvec(1, ws, os, &rows, blocks, nullptr, nullptr, 1, ids, n_used * nseq, kAnyExpert, 1, 2, gate, up, 0, 0x7fffffff, pl);
+}
 // Q, K, V of one sequence with the attention norm (and the MoE combine before it) folded in: pl.norm says from what.
 void matvec_x3_norm(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, float *o0, float *o1, float *o2, int blocks,
                     int rows0, int rows1, int rows2) {
@@ -126,9 +132,7 @@ void llamd_fwd_matvec_f32act(const void *w, const float *x, float *out, int bloc
 // (fuses device.rs:615-618 into :622): gate/up are [nseq*n_used][blocks*256].
 void llamd_fwd_matvec_grouped_pa_silu(const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
                                       int rows, int n_used, int nseq) {
-    const void *ws[1] = {w};
-    float *os[1] = {out};
-    launch_matvec(1, ws, os, &rows, blocks, nullptr, nullptr, 1, ids, n_used * nseq, kAnyExpert, 1, 2, gate, up);
+    matvec_grouped_pa_silu(MatvecPlans{}, w, ids, gate, up, out, blocks, rows, n_used, nseq);
 }
 
 // Expert-parallel forms: `ids` are GLOBAL expert ids for n_slots slots; this GPU holds experts

@@ -206,6 +206,8 @@ void launch_matvec_multi(int njobs, const void *const *w, float *const *out, con
 void matvec_batch(const MatvecPlans &pl, const void *w, const int8_t *aq, const float *ad, float *out, int blocks, int rows, int nseq);
 void matvec_x3_batch(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, const int8_t *aq, const float *ad, float *o0,
                      float *o1, float *o2, int blocks, int rows0, int rows1, int rows2, int nseq);
+void matvec_grouped_pa_silu(const MatvecPlans &pl, const void *w, const int32_t *ids, const float *gate, const float *up, float *out, int blocks,
+                            int rows, int n_used, int nseq);
 void matvec_x3_norm(const MatvecPlans &pl, const void *w0, const void *w1, const void *w2, float *o0, float *o1, float *o2, int blocks,
                     int rows0, int rows1, int rows2);
 void matvec_grouped_x2_batch(const MatvecPlans &pl, const void *wa, const void *wb, const int32_t *ids, const int8_t *aq, const float *ad,

@@ -275,6 +275,20 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
                                 __fmul_rn(__fmul_rn(c4.z, nscale), wb.z), __fmul_rn(__fmul_rn(c4.w, nscale), wb.w)};
             q8k_quantize_block(v, lane, s_nat + blk * 256, s_ad + blk, nullptr);
         }
+    } else if (ACT == ACT_SILU) {
+        // ... produced here: silu(gate) * up with one or a few elements per thread (a lane walking eight dependent exp
+        // evaluations one after the other was most of this prologue), then one warp per 256-element block quantizes
+        float *s_f = reinterpret_cast<float *>(smem + ((matvec_ad_offset(NSEQ, nb) + (size_t)NSEQ * nb * 4 + 15) & ~(size_t)15));
+        const long long a_idx = p.ids ? slot / p.act_div : seq0;
+        const size_t base = (size_t)a_idx * nb * 256;
+        for (int i = tid; i < nb * 256; i += kThreads) s_f[i] = silu_mul(p.xf[base + i], p.xu[base + i]);
+        __syncthreads();
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int blk = warp; blk < nb; blk += kThreads / 32) {
+            const float4 a = reinterpret_cast<const float4 *>(s_f + blk * 256 + lane * 8)[0], c4 = reinterpret_cast<const float4 *>(s_f + blk * 256 + lane * 8)[1];
+            const float v[8] = {a.x, a.y, a.z, a.w, c4.x, c4.y, c4.z, c4.w};
+            q8k_quantize_block(v, lane, s_nat + blk * 256, s_ad + blk, nullptr);
+        }
     } else {
         // ... produced here: one warp per 256-element block quantizes the f32 activation
         const int warp = tid >> 5, lane = tid & 31;
@@ -423,6 +437,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
 
 static size_t matvec_smem_bytes(int nseq, int nb, int act = ACT_Q8K) {
     const size_t base = matvec_ad_offset(nseq, nb) + (size_t)nseq * nb * 4;
+    if (act == ACT_SILU) return ((base + 15) & ~(size_t)15) + (size_t)nb * 256 * 4;  // + the activation as f32
     return act == ACT_NORM ? ((base + 15) & ~(size_t)15) + (size_t)2 * nb * 256 * 4 : base;  // + the residual stream and its squares
 }
 

@@ -189,6 +189,8 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int fuse_silu_down = 0;  // option "fuse_silu_down": silu(gate) * up and its Q8_K form inside the down projection's launch (decode pass);
+                             // the same bits and the same speed (290.3 against 290.5 tok/s: 200 CTAs each redo their slot's 768 exps), so off
     int fuse_norm_qkv = 0;   // option "fuse_norm_qkv": the attention norm (and the combine before it) inside the QKV matvec (one sequence);
                              // the same bits, measured 0.8 % slower (288.1 against 290.5 tok/s: 160 CTAs each repeat the combine), so off
     int fuse_rope_attn = 1;  // option "fuse_rope_attn": QK-norm, RoPE and the KV store inside the attention-scores launch (decode pass)
@@ -553,10 +555,15 @@ void queue_token(Model &m, int nseq) {
             matvec_grouped_x2_batch(gu, l.gate_exps.p, l.up_exps.p, m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(),
                                     m.e_gate.as<float>(), m.e_up.as<float>(), eb, ffe, nu, nseq);
             mark(LLAMD_PH_GATE_UP);
-            llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
-                                     nseq * nu * ffe);
+            if (!m.fuse_silu_down)
+                llamd_fwd_silu_mul_quant(m.e_gate.as<float>(), m.e_up.as<float>(), nullptr, m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                         nseq * nu * ffe);
         }
         mark(LLAMD_PH_SILU);
+        if (!fuse && m.fuse_silu_down)  // every CTA of a slot makes the slot's activation itself: one launch fewer, the same bits
+            matvec_grouped_pa_silu(plan_after_down(il), l.down_exps.p, m.expert_ids.as<int32_t>(), m.e_gate.as<float>(), m.e_up.as<float>(),
+                                   m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+        else
         matvec_grouped_pa_batch(plan_after_down(il), l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
                                 m.e_down.as<float>(), ffe / 256, E, nu, nseq);
         mark(LLAMD_PH_DOWN);
@@ -944,6 +951,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "ep_rank_arrive")) {
         if (m->ep_rank_arrive != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->ep_rank_arrive = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_silu_down")) {
+        if (m->fuse_silu_down != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_silu_down = value;
         return 0;
     }
     if (!strcmp(name, "fuse_norm_qkv")) {

@@ -155,7 +155,7 @@ def test_fused_tails_change_nothing(tiny):
         assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
 
 
-@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv"])
+@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv", "fuse_silu_down"])
 def test_fused_launches_change_nothing(tiny, option):
     """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router), with QK-norm, RoPE and
     the KV store inside the attention-scores launch (option fuse_rope_attn), and with the attention norm and the MoE combine
@@ -164,7 +164,7 @@ def test_fused_launches_change_nothing(tiny, option):
     covered by the 768-position run against the CPU fixture, which uses the defaults.)"""
     hp, w, gm, om = tiny
     runs = {}
-    default = 0 if option == "fuse_norm_qkv" else 1  # (measured slower, so off unless asked for)
+    default = 0 if option in ("fuse_norm_qkv", "fuse_silu_down") else 1  # (measured no faster, so off unless asked for)
     for fuse in (1, 0, 1):
         gm.set_option(option, fuse)
         gm.set_trace(True)
