@@ -297,8 +297,8 @@ def main():
                          "its own sequence; replicas = one full model per GPU, no exchange")
     ap.add_argument("--arith", default="exact", choices=["exact", "fast"],
                     help="exact: every f32 reduction in the reference's order (token ids bit-exact against the CPU path; what `value` "
-                         "is unless asked otherwise). fast: the long sums of a decode token as reduction trees, through the resident "
-                         "kernel (tolerance-level floats). An exact run on one GPU also times the fast mode and reports it in detail.fast_arith")
+                         "is unless asked otherwise). fast: the long sums of a decode token as reduction trees, same launches "
+                         "(tolerance-level floats; with --resident 1 through the resident kernel). An exact run on one GPU also times the fast mode and reports it in detail.fast_arith")
     ap.add_argument("--kv", default="f32", choices=["f32", "f16"],
                     help="K/V cache element type. f32: the reference's (every backend of it), and what the committed CPU run of the "
                          "benchmark used. f16: binary16, rounded once at the store (model option kv_f16; the oracle has the same mode)")
@@ -554,13 +554,12 @@ def main():
             same = [int(a) == int(b) for a, b in zip(ftoks, toks)]
             fast_arith = {"value": K / (fms * 1e-3), "unit": "tok/s", "ms_per_step": fms / K, "tokens_equal_exact": all(same),
                           "first_difference_at_step": None if all(same) else same.index(False), "steps": K,
-                          "note": "the same K positions decoded again through the resident kernel with reduction trees for the two "
-                                  "norms' sums, the router's dots and attention's sums (model option arith = 1); everything else as in "
+                          "note": "the same K positions decoded again, same launches, with reduction trees for the two norms' "
+                                  "sums, the router's dots and attention's sums (model option arith = 1); everything else as in "
                                   "the exact mode"}
             m.set_option("arith", 0)
-            m.set_option("resident", max(args.resident, 0))
             m.decode(tok0, pos0, K)  # leave the cache as the exact run left it
-        except Exception as e:  # a shape the resident kernel does not support
+        except Exception as e:
             fast_arith = {"unavailable": str(e)}
 
     # ---- roofline of the dominant kernel ----

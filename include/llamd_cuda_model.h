@@ -141,13 +141,14 @@ int llamd_model_set_option(llamd_model *m, const char *name, int value);
  * (and before a peer-memory attach). Every path honours it: per-op decode, batches, the tiled prefill (through an f32 view
  * of the rows it attends), the resident kernel, llamd_model_read_kv (returns the widened values).
  *
- * Option "arith" = 1, or a mask of 2 (norms) | 4 (router) | 8 (attention) (no counterpart in the reference's CPU path; its device backends reduce in parallel too): the
- * resident kernel sums the 2048-term sums of the two norms and of the router's dots, the softmax sum and the weighted
- * values of attention as reduction trees instead of walking them in the reference's order. Integers, indices, `exp`
- * and every other float operation are unchanged, so results agree with arith = 0 to the last bits of those sums, NOT
- * bit for bit, and a near-tie in a router can then choose another expert. Implies "resident" = 1; refused (-1, message)
- * for max_seq > 1, expert parallelism or a shape the resident kernel does not support. Prefill and batches always use
- * the exact arithmetic. */
+ * Option "arith" = 1, or a mask of 2 (norms) | 4 (router) | 8 (attention) (no counterpart in the reference's CPU path; its
+ * device backends reduce in parallel too): a decode pass sums the 2048-term sums of the two norms and of the router's
+ * dots, the softmax sum and the weighted values of attention as reduction trees instead of walking them in the reference's
+ * order. Integers, indices, `exp` and every other float operation are unchanged, so results agree with arith = 0 to the
+ * last bits of those sums, NOT bit for bit, and a near-tie in a router can then choose another expert. Deterministic (fixed
+ * tree shapes). Honoured by the graph of separate launches (1..8 sequences; needs "fuse_norm_router", the default) and by
+ * the resident kernel; refused (-1, message) with expert parallelism. Prefill tiles and wide batches always use the exact
+ * arithmetic. */
 int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
 
 /* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */

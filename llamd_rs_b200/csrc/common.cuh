@@ -46,6 +46,10 @@ extern unsigned long long g_launches;
 // kernel has completed and flushed, and every kernel calls it, so completion
 // is transitive along the stream. Without the attribute both are no-ops.
 extern int g_pdl;
+// The `fast` arithmetic of a decode pass (model option arith): bit 1 the norms' sums of squares, bit 2 the router's dots, bit 4
+// attention's softmax sum and weighted values as reduction trees instead of the reference's ordered sums. 0 (exact) except
+// while a model with the option queues its decode pass; the launchers pass it to the kernels as an argument.
+extern int g_fast_sums;
 extern int g_batch_group;  // matvec_q6k.cu: sequences per CTA for small ungrouped matrices at batch > 1
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -253,6 +257,21 @@ constexpr int kTileDOff = 6656;        // 32 x 2 B
 // IEEE binary16 -> binary32, exact (crates/llamd-quant/src/lib.rs:104-108).
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
     return __half2float(__ushort_as_half(h));
+}
+
+// One value per thread summed over the CTA, the same on every thread and from run to run: xor-shuffle tree inside a warp,
+// then the warps' sums added in warp order. The `fast` arithmetic's replacement for an ordered sum. s_scratch: 32 floats;
+// all threads of the CTA must call it.
+__device__ __forceinline__ float block_tree_sum(float v, float *s_scratch) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+    const int nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();  // (the scratch may still be read from an earlier call)
+    if ((threadIdx.x & 31) == 0) s_scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = s_scratch[0];
+    for (int w = 1; w < nwarps; w++) t = __fadd_rn(t, s_scratch[w]);
+    return t;
 }
 
 // Left-to-right f32 sum of n values in SHARED memory, starting from `acc`:

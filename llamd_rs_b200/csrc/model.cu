@@ -182,7 +182,7 @@ struct Model {
     // The resident decode kernel (mega.cu): one cooperative launch per token instead of a dozen launches per layer.
     int resident = 0;        // option "resident": 1 = use it for single-sequence passes when the dimensions allow
     Buf mega_layers, mega_bar, mega_status, mega_prof;
-    int arith_fast = 0;      // option "arith": non-zero = tree reductions for the long ordered sums of a decode token (resident kernel only)
+    int arith_fast = 0;      // option "arith": non-zero = tree reductions for the long ordered sums of a decode token
     int resident_profile = 0;  // option "resident_profile": CTA 0 of the resident kernel accumulates nanoseconds per phase
     bool mega_ready = false;
     int fuse_tails = 0;      // 1: the attention output's and the gate/up outputs' follow-up ops run in the producer's last CTA
@@ -367,6 +367,12 @@ void queue_token(Model &m, int nseq) {
         queue_token_resident(m);
         return;
     }
+    // the `fast` arithmetic (option arith): the decode pass's norm, router and attention launches take the mask as an argument
+    // while this pass is queued (the fused norm + router launch carries the router's tree, so the mask needs it on)
+    struct FastSums {
+        explicit FastSums(int v) { g_fast_sums = v; }
+        ~FastSums() { g_fast_sums = 0; }
+    } fast_sums(m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0);
     size_t n_marks = 0;
     auto mark = [&](int phase) {
         if (!m.profiling) return;
@@ -902,10 +908,6 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         return 0;
     }
     if (!strcmp(name, "resident")) {
-        if (!value && m->arith_fast) {
-            m->err = "option resident: the fast arithmetic exists in the resident kernel only; set arith to 0 first";
-            return -1;
-        }
         if (m->resident != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other pass
         m->resident = value;
         return 0;
@@ -913,9 +915,10 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "arith")) {
         // 0: every f32 sum in the reference's order (bit-exact against the CPU path). 1: the 2048-term sums of the two norms
         // and the router, the softmax sum and the weighted-value sum of attention as reduction trees; integers, indices and
-        // every other float operation unchanged. Single-sequence decode through the resident kernel only.
-        if (value && (m->max_seq != 1 || m->ep_world != 1 || !mega_supported(m->hp, m->max_kv))) {
-            m->err = "option arith: the fast arithmetic needs a single-sequence, single-GPU model whose shape the resident kernel supports";
+        // every other float operation unchanged. Decode passes on one GPU: the graph of separate launches (any number of
+        // sequences up to 8) and the resident kernel; prefill tiles and wide batches keep the exact arithmetic.
+        if (value && m->ep_world != 1) {
+            m->err = "option arith: the fast arithmetic is a single-GPU decode mode";
             return -1;
         }
         if (value < 0 || value > 14 || (value > 1 && (value & 1))) {
@@ -925,7 +928,6 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         value = value == 1 ? 7 : value >> 1;  // (the kernel's mask: 1 norms, 2 router, 4 attention)
         if (m->arith_fast != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->arith_fast = value;
-        if (value) m->resident = 1;
         return 0;
     }
     if (!strcmp(name, "resident_profile")) {
@@ -1622,10 +1624,6 @@ int llamd_model_profile_pass(llamd_model *h, int32_t token, int32_t pos, float *
     Model *m = (Model *)h;
     if (!m || !ms_out || m->ep_world > 1) return -1;
     m->err.clear();
-    if (m->arith_fast) {
-        m->err = "profile_pass times the per-op pass, which has no fast arithmetic; set arith to 0 first";
-        return -1;
-    }
     const int saved_graph = m->use_graph;
     m->use_graph = 0;
     m->profiling = true;

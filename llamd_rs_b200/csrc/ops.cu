@@ -146,8 +146,9 @@ __global__ void __launch_bounds__(128) norm_router_kernel(const float *__restric
                                                           float *__restrict__ x_out, const float *__restrict__ w_norm, float *__restrict__ xn_out,
                                                           int8_t *__restrict__ qs, float *__restrict__ d, int k, float eps, int n_expert, int n_used,
                                                           float *__restrict__ logits, int32_t *__restrict__ ids, float *__restrict__ weights,
-                                                          float *__restrict__ probs, unsigned int *__restrict__ done_counter) {
+                                                          float *__restrict__ probs, unsigned int *__restrict__ done_counter, int fast) {
     extern __shared__ __align__(16) float sm[];  // [4][k] router rows / products, [k] x then xn, [k] squares
+    __shared__ float s_tree[32];
     __shared__ float s_red[40 + kMaxUsed];
     __shared__ int s_redi[40 + kMaxUsed];
     __shared__ float s_scale;
@@ -184,9 +185,16 @@ __global__ void __launch_bounds__(128) norm_router_kernel(const float *__restric
         if (blockIdx.x == 0) reinterpret_cast<float4 *>(x_out + (size_t)seq * k)[j] = v;
     }
     __syncthreads();
-    if (tid == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(chain_sum(ssq, k, 0.0f), (float)k), eps)));
-    __syncthreads();
-    const float scale = s_scale;
+    float scale;
+    if (fast & 1) {  // the `fast` arithmetic: the sum of squares as a reduction tree
+        float part = 0.0f;
+        for (int i = tid; i < k; i += 128) part = __fadd_rn(part, ssq[i]);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(block_tree_sum(part, s_tree), (float)k), eps)));
+    } else {
+        if (tid == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(chain_sum(ssq, k, 0.0f), (float)k), eps)));
+        __syncthreads();
+        scale = s_scale;
+    }
     for (int j = tid; j < k4; j += 128) {
         const float4 v = reinterpret_cast<const float4 *>(sx)[j], wn = __ldg(reinterpret_cast<const float4 *>(w_norm) + j);
         const float4 o = make_float4(__fmul_rn(__fmul_rn(v.x, scale), wn.x), __fmul_rn(__fmul_rn(v.y, scale), wn.y),
@@ -203,7 +211,22 @@ __global__ void __launch_bounds__(128) norm_router_kernel(const float *__restric
         }
     }
     // the router rows: y = fold(-0.0, +) of w[r][t] * xn[t], t ascending (crates/llamd-models/src/model.rs:253-263)
-    if (row < n_expert) {
+    if (row < n_expert && (fast & 2)) {  // the `fast` arithmetic: the same products, summed by a tree over the warp
+        float part = 0.0f;
+        for (int j = lane; j < k4; j += 32) {
+            const float4 a = reinterpret_cast<const float4 *>(prod)[j], b = reinterpret_cast<const float4 *>(sx)[j];
+            part = __fadd_rn(part, __fmul_rn(a.x, b.x));
+            part = __fadd_rn(part, __fmul_rn(a.y, b.y));
+            part = __fadd_rn(part, __fmul_rn(a.z, b.z));
+            part = __fadd_rn(part, __fmul_rn(a.w, b.w));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+        if (lane == 0) {
+            logits[(size_t)seq * n_expert + row] = part;
+            __threadfence();
+        }
+    } else if (row < n_expert) {
         for (int j = lane; j < k4; j += 32) {
             const float4 a = reinterpret_cast<const float4 *>(prod)[j], b = reinterpret_cast<const float4 *>(sx)[j];
             reinterpret_cast<float4 *>(prod)[j] = make_float4(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y), __fmul_rn(a.z, b.z), __fmul_rn(a.w, b.w));
@@ -991,9 +1014,11 @@ constexpr int kPvTile = 256;  // positions per V tile
 template <class KVT>
 __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__ scores, const KVT *__restrict__ vc, float *__restrict__ out,
                                                        int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int n_kv_imm,
-                                                       int max_kv, int kv_stride, const TailPlan tail) {
+                                                       int max_kv, int kv_stride, const TailPlan tail, int fast) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float s_red[16];
+    __shared__ float s_tree[32];
+    __shared__ float s_part[256];
     pdl_trigger();
     pdl_wait();
     const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
@@ -1039,16 +1064,28 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     for (int w = 1; w < 8; w++) lmax = fmaxf(lmax, s_red[w]);
     for (int t = tid; t < n_kv; t += blockDim.x) sl[t] = ref_expf(__fsub_rn(sl[t], lmax));
     __syncthreads();
-    if (tid == 0) s_red[8] = __fdiv_rn(1.0f, chain_sum(sl, n_kv, 0.0f));
-    __syncthreads();
-    const float inv = s_red[8];
+    float inv;
+    if (fast & 4) {  // the `fast` arithmetic: the softmax sum as a reduction tree
+        float part = 0.0f;
+        for (int t = tid; t < n_kv; t += blockDim.x) part = __fadd_rn(part, sl[t]);
+        inv = __fdiv_rn(1.0f, block_tree_sum(part, s_tree));
+    } else {
+        if (tid == 0) s_red[8] = __fdiv_rn(1.0f, chain_sum(sl, n_kv, 0.0f));
+        __syncthreads();
+        inv = s_red[8];
+    }
     float acc = 0.0f;
     for (int ti = 0; ti < n_tiles; ti++) {
         float *cur = tile + (ti & 1) * kPvTile * cols;
         stash(cur);
         __syncthreads();
         if (ti + 1 < n_tiles) fetch(ti + 1);
-        if (tid < cols) {
+        if (fast & 4) {
+            // ... and the weighted values by 256 / cols groups of positions per column, joined in group order below
+            const int t0 = ti * kPvTile, cnt = min(kPvTile, n_kv - t0);
+            const int g = tid / cols, dcol = tid - g * cols, ng = 256 / cols;
+            for (int r = g; r < cnt; r += ng) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t0 + r], inv), cur[r * cols + dcol]));
+        } else if (tid < cols) {
             const int t0 = ti * kPvTile, cnt = min(kPvTile, n_kv - t0);
             int r = 0;
             if (cnt >= 16) {
@@ -1066,6 +1103,14 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
                 }
             }
             for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(sl[t0 + r], inv), cur[r * cols + tid]));
+        }
+    }
+    if (fast & 4) {
+        s_part[tid] = acc;  // [group][column]
+        __syncthreads();
+        if (tid < cols) {
+            acc = s_part[tid];
+            for (int g = 1; g < 256 / cols; g++) acc = __fadd_rn(acc, s_part[g * cols + tid]);
         }
     }
     if (tid < cols) out[((size_t)seq * n_head + h) * hd + (size_t)c * cols + tid] = acc;
@@ -1326,7 +1371,7 @@ void llamd_fwd_norm_router(const float *w, const float *x, const float *residual
         configured = smem;
     }
     launch_kc(PDL_ROUTER, "norm_router", norm_router_kernel, dim3((n_expert + 3) / 4, nseq), dim3(128), smem, w, x, residual, x_out, w_norm, xn_out, qs, d,
-              k, eps, n_expert, n_used, logits, ids, weights, probs, counter);
+              k, eps, n_expert, n_used, logits, ids, weights, probs, counter, g_fast_sums);
 }
 
 static int g_q80_rows_max_ctas = 148 * 4;
@@ -1516,10 +1561,10 @@ static void attention_split_launch(const float *q, const void *kc, const void *v
     }
     if (kv16)
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc, out,
-                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail);
+                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail, g_fast_sums);
     else
     launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc, out, n_head, n_head_kv, hd,
-             meta, n_kv, max_kv, kv_stride, tail);
+             meta, n_kv, max_kv, kv_stride, tail, g_fast_sums);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
@@ -1623,12 +1668,12 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<__half>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
                   (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps);
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc,
-                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{});
+                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_fast_sums);
     } else {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<float>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
                   (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps);
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc,
-                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{});
+                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_fast_sums);
     }
 }
 void llamd_fwd_attention_rope_meta(const float *q, const float *wq, const float *k, const float *wk, const float *v, float *kc, float *vc,

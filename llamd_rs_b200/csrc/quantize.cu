@@ -38,10 +38,11 @@ __device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ 
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                                                        const float *__restrict__ down, const float *__restrict__ cw, int n_used,
                                                        float *__restrict__ sum_out, const float *__restrict__ w, float *__restrict__ out,
-                                                       int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps, const WaitPlan wait) {
+                                                       int8_t *__restrict__ qs, float *__restrict__ d, int n, float eps, const WaitPlan wait, int fast) {
     extern __shared__ __align__(16) float sx[];  // [n] values, then [n] squares
     float *ssq = sx + n;
     __shared__ float s_scale;
+    __shared__ float s_tree[32];
     pdl_trigger();
     const int seq = blockIdx.x, tid = threadIdx.x;
     // Thread t owns the float4 groups t, t+256, ...: every global load of the
@@ -136,9 +137,17 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
         }
     }
     __syncthreads();
-    if (tid == 0) s_scale = rms_scale_sequential(ssq, n, eps);
-    __syncthreads();
-    const float scale = s_scale;
+    float scale;
+    if (fast & 1) {  // the sum of squares as a reduction tree (the `fast` arithmetic)
+        float part = 0.0f;
+        for (int i = tid; i < n; i += 256) part = __fadd_rn(part, ssq[i]);
+        const float sum = block_tree_sum(part, s_tree);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+    } else {
+        if (tid == 0) s_scale = rms_scale_sequential(ssq, n, eps);
+        __syncthreads();
+        scale = s_scale;
+    }
 #pragma unroll
     for (int u = 0; u < kMaxV; u++) {
         const int j = tid + u * 256;
@@ -262,7 +271,7 @@ void llamd::combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, co
         return;
     }
     launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
-             sum_out, w, out, qs, d, n, eps, wait);
+             sum_out, w, out, qs, d, n, eps, wait, g_fast_sums);
 }
 
 extern "C" {
@@ -281,7 +290,7 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         return;
     }
     launch_kc(PDL_NORM, "rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
-             nullptr, nullptr, n, eps, WaitPlan{});
+             nullptr, nullptr, n, eps, WaitPlan{}, g_fast_sums);
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
     if (n % 256 || (size_t)n * 8 > 48 * 1024) {
@@ -289,7 +298,7 @@ void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t
         return;
     }
     launch_kc(PDL_NORM, "rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
-             out, qs, d, n, eps, WaitPlan{});
+             out, qs, d, n, eps, WaitPlan{}, g_fast_sums);
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
@@ -300,7 +309,7 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
         return;
     }
     launch_kc(PDL_NORM, "add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
-             w, out, qs, d, n, eps, WaitPlan{});
+             w, out, qs, d, n, eps, WaitPlan{}, g_fast_sums);
 }
 // x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
 // forward.rs:586), then norm*w and its Q8_K form: the tail of one layer fused

@@ -93,10 +93,11 @@ def dev_rms(a, b):
     return float(np.max(np.abs(a - b)) / max(float(np.sqrt(np.mean(b * b))), 1e-30))
 
 
+@pytest.mark.parametrize("resident", [1, 0])
 @pytest.mark.parametrize("which", ["tiny", "wider", "full3"])
-def test_fast_arithmetic_is_the_same_function_up_to_rounding(be, which):
-    """Option arith = 1: reduction trees for the norms' sums, the router's dots and attention's sums, nothing else changed.
-    Checked where rounding noise is all that can differ: at position 0 (softmax over one key is exactly 1) the hidden
+def test_fast_arithmetic_is_the_same_function_up_to_rounding(be, which, resident):
+    """Option arith = 1: reduction trees for the norms' sums, the router's dots and attention's sums, nothing else changed; in
+    the resident kernel and in the graph of separate launches alike. Checked where rounding noise is all that can differ: at position 0 (softmax over one key is exactly 1) the hidden
     state after every layer stays within LAYER, the K/V rows within LAYER and the logits within LOGITS of the exact
     mode's, relative to each vector's rms, and the routed experts are the same. Later positions are only required to run
     and to be reproducible: a random-init network is chaotic (one flipped Q8_K rounding after a one-ulp change of a norm's
@@ -109,7 +110,7 @@ def test_fast_arithmetic_is_the_same_function_up_to_rounding(be, which):
     tokens = synth.token_ids(6, hp["n_vocab"], 33, "fast", which).tolist()
     m = CudaModel.load_synthetic(hp, 7, max_kv=64)
     try:
-        m.set_option("resident", 1)
+        m.set_option("resident", resident)
         _, exact_tr, _ = run_traced(m, tokens[:1], 0)
         exact_logits = m.logits()[0].copy()
         exact_kv = [m.read_kv(il, 1) for il in range(hp["n_layer"])]
@@ -126,8 +127,6 @@ def test_fast_arithmetic_is_the_same_function_up_to_rounding(be, which):
             assert dev_rms(fast_logits, exact_logits) <= LOGITS
         assert not np.array_equal(bits(fast_tr[0][0]), bits(exact_tr[0][0])), "the two modes should not be the same code path"
         with pytest.raises(backend.Malformed):
-            m.set_option("resident", 0)  # the fast arithmetic lives in the resident kernel
-        with pytest.raises(backend.Malformed):
             m.set_option("arith", 3)
         # reproducible: the trees have a fixed shape
         toks_a, tr_a, log_a = run_traced(m, tokens, 4)
@@ -141,13 +140,26 @@ def test_fast_arithmetic_is_the_same_function_up_to_rounding(be, which):
         m.free()
 
 
-def test_fast_arithmetic_is_refused_where_it_does_not_exist(be):
-    from llamd_rs_b200 import backend, synth
+def test_fast_arithmetic_in_a_batch_of_sequences(be):
+    """The graph of separate launches carries the tree sums for batches too: four sequences in one pass give what four
+    single passes give in the same mode, bit for bit (the trees do not depend on the batch)."""
+    from llamd_rs_b200 import synth
     from llamd_rs_b200.model import CudaModel
 
-    m = CudaModel.load_synthetic(synth.TINY, 7, max_kv=32, max_seq=2)
+    hp = synth.TINY
+    m = CudaModel.load_synthetic(hp, 7, max_kv=32, max_seq=4)
     try:
-        with pytest.raises(backend.Malformed):
-            m.set_option("arith", 1)
+        m.set_option("arith", 1)
+        toks = synth.token_ids(12, hp["n_vocab"], 4, "fast.batch").reshape(3, 4)
+        single = []
+        for s_ in range(4):
+            for pos in range(3):
+                t = m.forward(int(toks[pos, s_]), pos)
+            single.append((t, m.logits()[0].copy()))
+        for pos in range(3):
+            out = m.forward_batch(toks[pos].tolist(), [pos] * 4)
+        lb = m.logits(4)
+        for s_ in range(4):
+            assert int(out[s_]) == single[s_][0] and np.array_equal(bits(lb[s_]), bits(single[s_][1])), f"sequence {s_}"
     finally:
         m.free()
