@@ -315,6 +315,8 @@ def main():
     ap.add_argument("--resident", type=int, default=-1, help="1: decode through the resident kernel (one cooperative launch per token); "
                     "0: the per-op pass; default: the library's own default")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--set", default="", help="(A/B) comma list of model options name=value set before the run, e.g. early_loads=0; "
+                                              "the JSON line's detail.options repeats it")
     ap.add_argument("--ep-rank-arrive", action="store_true", help="(A/B) expert parallelism: one arrival per rank and launch on the return "
                     "path instead of one per CTA of the down projection (measured 0.8 %% slower at 4 GPUs)")
     ap.add_argument("--no-pdl", action="store_true", help="serialise kernels instead of programmatic dependent launch (A/B)")
@@ -410,6 +412,9 @@ def main():
         _l().llamd_fwd_set_pdl(0)
     if args.prefetch:
         m.set_option("prefetch", 1)
+    for kv in [t for t in args.set.split(",") if t]:
+        name, _, val = kv.partition("=")
+        m.set_option(name.strip(), int(val))
     if args.resident >= 0 and not ep:
         m.set_option("resident", args.resident)
     if args.arith == "fast":
@@ -591,7 +596,7 @@ def main():
         hashes = [None] * world
         dist.all_gather_object(hashes, tokens_hash)
     detail = {"token_gbs": (wbytes + iobytes) / (dev_ms / K * 1e-3) / 1e9, "ms_per_token_per_rank": dev_ms / K,
-              "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch,
+              "graph": not args.no_graph, "pdl": not args.no_pdl, "l2_prefetch": args.prefetch, "options": args.set,
               "inputs_hash": inputs_hash, "tokens_hash": hashes[0], "tokens_hash_per_rank": hashes,
               "tokens_head": decoded[:8], "n_tokens_hashed": len(decoded), "tokens_vs_cpu_golden": golden_check, "fast_arith": fast_arith,
               "hash_note": "crc32 of (prompt ids, layer-0 attn_q bytes) and of the int32 token ids chosen after the prompt: "

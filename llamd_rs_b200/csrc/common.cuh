@@ -46,10 +46,13 @@ extern unsigned long long g_launches;
 // kernel has completed and flushed, and every kernel calls it, so completion
 // is transitive along the stream. Without the attribute both are no-ops.
 extern int g_pdl;
-// The `fast` arithmetic of a decode pass (model option arith): bit 1 the norms' sums of squares, bit 2 the router's dots, bit 4
-// attention's softmax sum and weighted values as reduction trees instead of the reference's ordered sums. 0 (exact) except
-// while a model with the option queues its decode pass; the launchers pass it to the kernels as an argument.
-extern int g_fast_sums;
+// What a model's decode pass asks of the kernels it launches; 0 except while such a pass is being queued, and the launchers
+// pass it to the kernels as an argument. Bits 1 | 2 | 4: the `fast` arithmetic (model option arith) -- the norms' sums of
+// squares, the router's dots, attention's softmax sum and weighted values as reduction trees instead of the reference's
+// ordered sums. kPassEarlyLoads: the attention kernels read the positions and the cached rows of earlier positions before
+// their dependency wait; true only inside a pass whose first launch waits for everything in front of it.
+constexpr int kPassEarlyLoads = 8;
+extern int g_pass_flags;
 extern int g_batch_group;  // matvec_q6k.cu: sequences per CTA for small ungrouped matrices at batch > 1
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -197,6 +200,12 @@ struct MatvecPlans {
     PeerOutPlan peer;
     DispatchWait dwait;
     NormPlan norm;
+    // A grouped launch may read its expert ids before its dependency wait when they were complete before the launch in
+    // front of it could begin. That holds for the down projection of a decode pass: the launch in front of it is the
+    // gate+up launch or the SiLU launch behind that one, and a gate+up launch lets nothing start before it has itself
+    // waited for the router. The weights then travel while the launch in front still runs. Never set for a launch whose
+    // ids are written by the launch directly in front of it.
+    int ids_early;
 };
 
 // Internal launch functions behind the extern "C" entry points of the same names; the model passes its plans here.

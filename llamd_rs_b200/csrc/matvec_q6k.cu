@@ -70,6 +70,9 @@ struct MatvecParams {
     PeerOutPlan peer;  // expert parallelism: a slot's rows go to its home rank's buffer, followed by an arrival
     DispatchWait dwait;  // expert parallelism: the ids / activations are pushed by the peers; wait for all of them first
     NormPlan norm;       // ACT_NORM: the activation is made here from the residual stream (combine + rms norm + Q8_K)
+    // Grouped launches: the ids were complete before the launch in front of this one began (see MatvecPlans::ids_early),
+    // so they are read, and the weight loads issued, before the dependency wait.
+    int ids_early;
 };
 
 //   ACT_NORM the activation is rms_norm(x + combine) * w, quantized, made by every CTA (NormPlan): the norm launch in front
@@ -110,7 +113,11 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
     int8_t *s_nat = reinterpret_cast<int8_t *>(s_ex);
     float *s_ad = reinterpret_cast<float *>(smem + matvec_ad_offset(NSEQ, nb));  // [NSEQ*nb] activation block scales
 
-    pdl_trigger();
+    // A grouped launch lets its successor start only once it has passed its own wait: whatever starts after it may then
+    // take the router's ids as complete (the down projection reads them before ITS wait). The other forms let go at once.
+    const bool early = !MULTI && p.ids && p.ids_early;
+    const bool late_trigger = !MULTI && p.ids && !early;
+    if (!late_trigger) pdl_trigger();
     // ---- which job / slot / rows -------------------------------------
     const int slot = blockIdx.x / p.ctas_per_slot;
     const int cta = blockIdx.x - slot * p.ctas_per_slot;
@@ -154,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         }
         __syncthreads();
     } else if (p.ids) {
-        pdl_wait();  // the ids come from the router kernel
+        if (!early) pdl_wait();  // the ids come from the router kernel
         if (EP && p.dwait.counter) {  // ... or from every rank's push: all of this layer's records must have landed
             if (tid == 0) {
                 unsigned int ep;
@@ -163,12 +170,17 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
             }
             __syncthreads();
         }
+        if (!early) pdl_trigger();  // (behind the wait for the records too: what starts after this launch may read them)
         if (EXTRA) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
-        int e = EP ? __ldcg(p.ids + slot) : p.ids[slot];
+        int e = (EP || early) ? __ldcg(p.ids + slot) : p.ids[slot];
         if (e < 0 || e >= p.n_expert) e = 0;
         if (e < p.own_lo || e >= p.own_hi) {  // another GPU's expert
-            // by now this CTA has read everything it needs of the request: the home rank may count it
-            if (EP && p.peer.out_tab && tid == 0) peer_arrive(p.peer, gridDim.x, slot / p.peer.div);
+            // by now this CTA has read everything it needs of the request: the home rank may count it -- but only once
+            // the launches in front, which read the same request, are complete (the home rank overwrites it afterwards)
+            if (EP && p.peer.out_tab) {
+                if (early) pdl_wait();
+                if (tid == 0) peer_arrive(p.peer, gridDim.x, slot / p.peer.div);
+            }
             return;
         }
         expert_off = (long long)(e - p.own_lo) * p.expert_units;
@@ -201,6 +213,8 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         if (EXTRA && !p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
         pdl_wait();
         if (EXTRA && p.pf.ids) prefetch_issue(p.pf, blockIdx.x, gridDim.x);
+    } else if (early) {
+        pdl_wait();  // the activations come from the launch in front
     }
     // ---- stage the activations ----------------------------------------
     // natural order bytes first ...
@@ -463,6 +477,7 @@ static void launch_t(const MatvecParams &p, dim3 grid, const MatvecPlans &plans)
     q.dwait = plans.dwait;
     q.peer = plans.peer;
     q.tail = plans.tail;
+    q.ids_early = (plans.ids_early && !MULTI && p.ids && !q.dwait.counter) ? 1 : 0;
     // each plan fits one kind of launch only; a plan given to another kind is refused, not dropped
     if (q.dwait.counter && !(!MULTI && NSEQ == 1 && p.ids)) {
         set_error_msg("matvec: a dispatch wait was planned for a launch that cannot carry it");

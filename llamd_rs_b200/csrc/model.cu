@@ -189,6 +189,8 @@ struct Model {
                              // (measured slower: fence + arrival + reload cost more than a graph's kernel boundary)
     int prefetch = 0;        // 1: every matvec launch asks L2 for the weights of the matvec after it (measured: no gain)
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
+    int early_loads = 1;     // option "early_loads": the down projection reads its expert ids, and attention its positions and the cached rows
+                             // of earlier positions, before the dependency wait (what they read was complete before the launch in front began)
     int fuse_silu_down = 0;  // option "fuse_silu_down": silu(gate) * up and its Q8_K form inside the down projection's launch (decode pass);
                              // the same bits and the same speed (290.3 against 290.5 tok/s: 200 CTAs each redo their slot's 768 exps), so off
     int fuse_norm_qkv = 0;   // option "fuse_norm_qkv": the attention norm (and the combine before it) inside the QKV matvec (one sequence);
@@ -369,10 +371,10 @@ void queue_token(Model &m, int nseq) {
     }
     // the `fast` arithmetic (option arith): the decode pass's norm, router and attention launches take the mask as an argument
     // while this pass is queued (the fused norm + router launch carries the router's tree, so the mask needs it on)
-    struct FastSums {
-        explicit FastSums(int v) { g_fast_sums = v; }
-        ~FastSums() { g_fast_sums = 0; }
-    } fast_sums(m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0);
+    struct PassFlags {
+        explicit PassFlags(int v) { g_pass_flags = v; }
+        ~PassFlags() { g_pass_flags = 0; }
+    } pass_flags((m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0) | (m.early_loads ? kPassEarlyLoads : 0));
     size_t n_marks = 0;
     auto mark = [&](int phase) {
         if (!m.profiling) return;
@@ -532,6 +534,7 @@ void queue_token(Model &m, int nseq) {
             llamd_fwd_silu_mul_quant(m.gate_all.as<float>(), m.up_all.as<float>(), nullptr, m.aq2_all.as<int8_t>(), m.ad2_all.as<float>(),
                                      W * nu * ffe);
             MatvecPlans dn = plan_after_down(il);
+            dn.ids_early = m.early_loads;  // (the gathered ids were complete before the gate+up launch let anything start behind it)
             if (m.ep_p2p) {
                 // no return collective: an owned slot's rows go straight into its home rank's e_down (routing-order slot),
                 // each CTA bumps that rank's counter, and the home rank's next norm waits for all of them
@@ -566,12 +569,16 @@ void queue_token(Model &m, int nseq) {
                                          nseq * nu * ffe);
         }
         mark(LLAMD_PH_SILU);
+        // (the ids were complete before the gate+up launch let anything start behind it: the down projection's weights
+        // travel while the SiLU launch runs)
+        MatvecPlans dn_plan = plan_after_down(il);
+        dn_plan.ids_early = m.early_loads;
         if (!fuse && m.fuse_silu_down)  // every CTA of a slot makes the slot's activation itself: one launch fewer, the same bits
-            matvec_grouped_pa_silu(plan_after_down(il), l.down_exps.p, m.expert_ids.as<int32_t>(), m.e_gate.as<float>(), m.e_up.as<float>(),
+            matvec_grouped_pa_silu(dn_plan, l.down_exps.p, m.expert_ids.as<int32_t>(), m.e_gate.as<float>(), m.e_up.as<float>(),
                                    m.e_down.as<float>(), ffe / 256, E, nu, nseq);
         else
-        matvec_grouped_pa_batch(plan_after_down(il), l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
-                                m.e_down.as<float>(), ffe / 256, E, nu, nseq);
+            matvec_grouped_pa_batch(dn_plan, l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(),
+                                    m.e_down.as<float>(), ffe / 256, E, nu, nseq);
         mark(LLAMD_PH_DOWN);
         if (m.trace)
             cudaMemcpyAsync(m.trace_ids.as<int32_t>() + (size_t)il * m.max_seq * nu, m.expert_ids.p, (size_t)nseq * nu * sizeof(int32_t),
@@ -609,9 +616,10 @@ void queue_matvecs_only(Model &m, int nseq) {
         matvec_grouped_x2_batch(plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu), l.gate_exps.p, l.up_exps.p,
                                 m.expert_ids.as<int32_t>(), m.aq.as<int8_t>(), m.ad.as<float>(), m.e_gate.as<float>(), m.e_up.as<float>(), eb,
                                 ffe, nu, nseq);
-        const MatvecPlans dn = il + 1 < hp.n_layer
-                                   ? plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v)
-                                   : plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
+        MatvecPlans dn = il + 1 < hp.n_layer
+                             ? plan_static(m, &m.layers[il + 1].attn_q, &m.layers[il + 1].attn_k, &m.layers[il + 1].attn_v)
+                             : plan_static(m, m.output.p ? &m.output : &m.tok_embd, nullptr, nullptr, kHeadPrefetchBytes);
+        dn.ids_early = m.early_loads;
         matvec_grouped_pa_batch(dn, l.down_exps.p, m.expert_ids.as<int32_t>(), m.aq2.as<int8_t>(), m.ad2.as<float>(), m.e_down.as<float>(),
                                 ffe / 256, E, nu, nseq);
     }
@@ -953,6 +961,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "ep_rank_arrive")) {
         if (m->ep_rank_arrive != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->ep_rank_arrive = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "early_loads")) {
+        if (m->early_loads != (value != 0) && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->early_loads = value != 0;
         return 0;
     }
     if (!strcmp(name, "fuse_silu_down")) {

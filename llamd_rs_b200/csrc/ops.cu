@@ -174,6 +174,13 @@ __global__ void __launch_bounds__(128) norm_router_kernel(const float *__restric
             }
         }
     }
+    constexpr int kWn = 4;  // (k <= 2048: one register set; a longer row reads the rest where it is used)
+    float4 wn_r[kWn];
+#pragma unroll
+    for (int u = 0; u < kWn; u++) {
+        const int j = tid + u * 128;
+        wn_r[u] = j < k4 ? __ldg(reinterpret_cast<const float4 *>(w_norm) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_wait();
     // x + residual, its squares (crates/llamd-cpu/src/lib.rs:55-75 after the add of layer.rs:281-287)
     const float4 *x4 = reinterpret_cast<const float4 *>(x + (size_t)seq * k), *r4 = reinterpret_cast<const float4 *>(residual + (size_t)seq * k);
@@ -195,13 +202,17 @@ __global__ void __launch_bounds__(128) norm_router_kernel(const float *__restric
         __syncthreads();
         scale = s_scale;
     }
-    for (int j = tid; j < k4; j += 128) {
-        const float4 v = reinterpret_cast<const float4 *>(sx)[j], wn = __ldg(reinterpret_cast<const float4 *>(w_norm) + j);
+    auto weigh = [&](int j, const float4 wn) {
+        const float4 v = reinterpret_cast<const float4 *>(sx)[j];
         const float4 o = make_float4(__fmul_rn(__fmul_rn(v.x, scale), wn.x), __fmul_rn(__fmul_rn(v.y, scale), wn.y),
                                      __fmul_rn(__fmul_rn(v.z, scale), wn.z), __fmul_rn(__fmul_rn(v.w, scale), wn.w));
         reinterpret_cast<float4 *>(sx)[j] = o;
         if (blockIdx.x == 0 && xn_out) reinterpret_cast<float4 *>(xn_out + (size_t)seq * k)[j] = o;
-    }
+    };
+#pragma unroll
+    for (int u = 0; u < kWn; u++)
+        if (tid + u * 128 < k4) weigh(tid + u * 128, wn_r[u]);
+    for (int j = tid + kWn * 128; j < k4; j += 128) weigh(j, __ldg(reinterpret_cast<const float4 *>(w_norm) + j));
     __syncthreads();
     if (blockIdx.x == 0) {  // the Q8_K form for the experts (dot.rs:88-128): a warp per 256-element block
         for (int b = warp; b < k / 256; b += 4) {
@@ -877,7 +888,7 @@ __global__ void __launch_bounds__(256) attn_rope_scores_kernel(const float *__re
                                                                const float *__restrict__ v_raw, KVT *__restrict__ kc, KVT *__restrict__ vc,
                                                                float *__restrict__ scores, int n_head, int n_head_kv, int hd,
                                                                const int32_t *__restrict__ meta, int max_kv, int kv_stride,
-                                                               const float *__restrict__ rope_tab, float eps) {
+                                                               const float *__restrict__ rope_tab, float eps, int flags) {
     extern __shared__ __align__(16) float sm[];
     const int stride = hd + 1, half = hd / 2;
     float *sq = sm;                 // [hd] the roped query
@@ -886,7 +897,11 @@ __global__ void __launch_bounds__(256) attn_rope_scores_kernel(const float *__re
     float *sk = s_raw + 2 * hd;     // [hd] the roped new key, as the cache holds it
     __shared__ float s_scale[2];
     pdl_trigger();
-    pdl_wait();
+    // kPassEarlyLoads: the positions and the cached rows of earlier positions were complete before this pass began (its
+    // first launch waits for everything in front of it), so they are read before the wait, while the projections that
+    // produce q, k and v are still running.
+    const bool early = (flags & kPassEarlyLoads) != 0;
+    if (!early) pdl_wait();
     const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
     const int pos = meta[2 * seq + 1], n_kv = pos + 1;
     const int ratio = n_head / n_head_kv, kv_dim = n_head_kv * hd, kvh = h / ratio;
@@ -924,6 +939,33 @@ __global__ void __launch_bounds__(256) attn_rope_scores_kernel(const float *__re
         }
     };
     if (c < n_tiles) fetch(c);  // the cached rows travel while the query is prepared
+    // the norm weights and the rotation of this position do not depend on the launch in front either
+    float w_lo = 1.0f, w_hi = 1.0f;
+    float2 cs_r = make_float2(0.f, 1.f);
+    {
+        const int idx = tid;
+        const bool is_k = idx >= half;
+        const int i = is_k ? idx - half : idx;
+        const float *w = is_k ? wk : wq;
+        if (idx < 2 * half && idx < (int)blockDim.x) {
+            if (w) {
+                w_lo = __ldg(w + i);
+                w_hi = __ldg(w + i + half);
+            }
+            cs_r = __ldg(reinterpret_cast<const float2 *>(rope_tab + ((size_t)pos * half + i) * 2));
+        }
+    }
+    if (early) {
+        // the CTA's later tiles: asked into L2 now, read from there in the loop below
+        const int lpr = hd * (int)sizeof(KVT) / 128;  // 128-byte lines per cached row of this head
+        if (lpr > 0)
+            for (int ti = c + kSplitT; ti < n_tiles; ti += kSplitT)
+                for (int i = tid; i < kAttTile * lpr; i += blockDim.x) {
+                    const int r = i / lpr, l = i - r * lpr, t = ti * kAttTile + r;
+                    if (t < pos) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(kb + (size_t)t * kv_dim) + l * 128));
+                }
+        pdl_wait();
+    }
     // ---- QK-norm (crates/llamd-runtime/src/layer.rs:62-79) and RoPE (crates/llamd-cpu/src/lib.rs:158-209) ----
     const float *qh = q_raw + ((size_t)seq * n_head + h) * hd, *kh = k_raw + ((size_t)seq * n_head_kv + kvh) * hd;
     for (int i = tid; i < hd; i += blockDim.x) {
@@ -944,13 +986,14 @@ __global__ void __launch_bounds__(256) attn_rope_scores_kernel(const float *__re
         const int i = is_k ? idx - half : idx;
         const float *sx = s_raw + (is_k ? hd : 0);
         const float *w = is_k ? wk : wq;
+        const bool first = idx == tid;  // (the first round's weights and rotation are in registers)
         float a = sx[i], b = sx[i + half];
         if (w) {
             const float nsc = s_scale[is_k ? 1 : 0];
-            a = __fmul_rn(__fmul_rn(a, nsc), w[i]);
-            b = __fmul_rn(__fmul_rn(b, nsc), w[i + half]);
+            a = __fmul_rn(__fmul_rn(a, nsc), first ? w_lo : w[i]);
+            b = __fmul_rn(__fmul_rn(b, nsc), first ? w_hi : w[i + half]);
         }
-        const float2 cs = *reinterpret_cast<const float2 *>(rope_tab + ((size_t)pos * half + i) * 2);
+        const float2 cs = first ? cs_r : *reinterpret_cast<const float2 *>(rope_tab + ((size_t)pos * half + i) * 2);
         const float o0 = __fsub_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
         const float o1 = __fadd_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
         if (!is_k) {
@@ -1020,7 +1063,8 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     __shared__ float s_tree[32];
     __shared__ float s_part[256];
     pdl_trigger();
-    pdl_wait();
+    const bool early = (fast & kPassEarlyLoads) != 0 && meta;  // (see attn_rope_scores_kernel)
+    if (!early) pdl_wait();
     const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
     const int n_kv = meta ? meta[2 * seq + 1] + 1 : n_kv_imm;
     const int n_kv_cap = meta ? max_kv : n_kv_imm;
@@ -1050,6 +1094,13 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
             if (idx < per_tile4) reinterpret_cast<float4 *>(dst)[idx] = reg[j];
         }
     };
+    if (early) {
+        // this CTA's slice of every cached value row, asked into L2 while the scores are still being made (the row of the
+        // token's own position is written by the launch in front: a hint for it is harmless, its load comes after the wait)
+        for (int t = tid; t < n_kv; t += blockDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(vb + (size_t)t * kv_dim)));
+        pdl_wait();
+    }
     fetch(0);  // V tile 0 travels while the softmax runs
     float lmax = -INFINITY;
     for (int t = tid; t < n_kv; t += blockDim.x) {
@@ -1371,7 +1422,7 @@ void llamd_fwd_norm_router(const float *w, const float *x, const float *residual
         configured = smem;
     }
     launch_kc(PDL_ROUTER, "norm_router", norm_router_kernel, dim3((n_expert + 3) / 4, nseq), dim3(128), smem, w, x, residual, x_out, w_norm, xn_out, qs, d,
-              k, eps, n_expert, n_used, logits, ids, weights, probs, counter, g_fast_sums);
+              k, eps, n_expert, n_used, logits, ids, weights, probs, counter, g_pass_flags);
 }
 
 static int g_q80_rows_max_ctas = 148 * 4;
@@ -1561,10 +1612,10 @@ static void attention_split_launch(const float *q, const void *kc, const void *v
     }
     if (kv16)
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc, out,
-                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail, g_fast_sums);
+                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail, g_pass_flags);
     else
     launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc, out, n_head, n_head_kv, hd,
-             meta, n_kv, max_kv, kv_stride, tail, g_fast_sums);
+             meta, n_kv, max_kv, kv_stride, tail, g_pass_flags);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
@@ -1666,14 +1717,14 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
     }
     if (kv16) {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<__half>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
-                  (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps);
+                  (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc,
-                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_fast_sums);
+                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
     } else {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<float>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
-                  (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps);
+                  (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc,
-                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_fast_sums);
+                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
     }
 }
 void llamd_fwd_attention_rope_meta(const float *q, const float *wq, const float *k, const float *wk, const float *v, float *kc, float *vc,

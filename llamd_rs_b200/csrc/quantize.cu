@@ -271,7 +271,7 @@ void llamd::combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, co
         return;
     }
     launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
-             sum_out, w, out, qs, d, n, eps, wait, g_fast_sums);
+             sum_out, w, out, qs, d, n, eps, wait, g_pass_flags);
 }
 
 extern "C" {
@@ -290,7 +290,7 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         return;
     }
     launch_kc(PDL_NORM, "rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
-             nullptr, nullptr, n, eps, WaitPlan{}, g_fast_sums);
+             nullptr, nullptr, n, eps, WaitPlan{}, g_pass_flags);
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
     if (n % 256 || (size_t)n * 8 > 48 * 1024) {
@@ -298,7 +298,7 @@ void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t
         return;
     }
     launch_kc(PDL_NORM, "rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
-             out, qs, d, n, eps, WaitPlan{}, g_fast_sums);
+             out, qs, d, n, eps, WaitPlan{}, g_pass_flags);
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
@@ -309,7 +309,7 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
         return;
     }
     launch_kc(PDL_NORM, "add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
-             w, out, qs, d, n, eps, WaitPlan{}, g_fast_sums);
+             w, out, qs, d, n, eps, WaitPlan{}, g_pass_flags);
 }
 // x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
 // forward.rs:586), then norm*w and its Q8_K form: the tail of one layer fused

@@ -200,7 +200,9 @@ void llamd_fwd_embed(const void *table, int token, float *out, int blocks) {
              blocks);
 }
 void llamd_fwd_embed_meta(const void *table, const int32_t *meta, float *out, int blocks, int nseq) {
-    launch_k("embed_meta", embed_meta_kernel, dim3((blocks * LLAMD_QK_K + 255) / 256, nseq), dim3(256), 0, (const uint8_t *)table, meta, 0,
+    // (the first launch of a pass: no programmatic overlap with whatever is in front of it, so that everything the pass
+    // launches afterwards starts after the previous pass has completed)
+    launch_kc(0, "embed_meta", embed_meta_kernel, dim3((blocks * LLAMD_QK_K + 255) / 256, nseq), dim3(256), 0, (const uint8_t *)table, meta, 0,
              out, blocks);
 }
 
