@@ -208,6 +208,10 @@ struct MatvecPlans {
     int ids_early;
 };
 
+// The decode pass's attention (QK-norm, RoPE and the K/V store inside the scores launch) leaving its result quantized as well.
+void attention_rope_quant(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc, float *out,
+                          float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int max_kv,
+                          int nseq, bool kv16, int8_t *qs, float *d);
 // Internal launch functions behind the extern "C" entry points of the same names; the model passes its plans here.
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode = 0,

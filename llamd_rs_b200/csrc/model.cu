@@ -191,6 +191,10 @@ struct Model {
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int early_loads = 1;     // option "early_loads": the down projection reads its expert ids, and attention its positions and the cached rows
                              // of earlier positions, before the dependency wait (what they read was complete before the launch in front began)
+    int fuse_attn_quant = 0; // option "fuse_attn_quant": the attention-output launch leaves its result quantized (clusters of the CTAs of a
+                             // 256-element block exchange their maxima through distributed shared memory); needs fuse_rope_attn. The same
+                             // bits, one launch fewer, and measured 7 % SLOWER (270.4 against 291.2 tok/s): a launch of 16 clusters of
+                             // eight co-scheduled CTAs starts later behind a running kernel than 128 free CTAs do, so off
     int fuse_silu_down = 0;  // option "fuse_silu_down": silu(gate) * up and its Q8_K form inside the down projection's launch (decode pass);
                              // the same bits and the same speed (290.3 against 290.5 tok/s: 200 CTAs each redo their slot's 768 exps), so off
     int fuse_norm_qkv = 0;   // option "fuse_norm_qkv": the attention norm (and the combine before it) inside the QKV matvec (one sequence);
@@ -454,6 +458,15 @@ void queue_token(Model &m, int nseq) {
         const bool fuse_ra = m.fuse_rope_attn && !fuse && hd % 16 == 0 && hd <= 256;
         if (fuse_ra) {
             // ... inside the attention-scores launch: one launch fewer, the same bits
+            if (m.fuse_attn_quant) {
+                // ... and the Q8_K form of the result made by the output launch itself (a cluster per 256-element block)
+                attention_rope_quant(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
+                                     l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(),
+                                     m.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, nseq, m.kv16,
+                                     m.aq.as<int8_t>(), m.ad.as<float>());
+                mark(LLAMD_PH_ROPE);
+                mark(LLAMD_PH_ATTENTION);
+            } else {
             if (m.kv16)
                 llamd_fwd_attention_rope_meta_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
                                                    l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p,
@@ -467,6 +480,7 @@ void queue_token(Model &m, int nseq) {
             mark(LLAMD_PH_ROPE);
             mark(LLAMD_PH_ATTENTION);
             llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+            }
         } else {
         if (m.kv16)
             llamd_fwd_qk_norm_rope_store_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
@@ -961,6 +975,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "ep_rank_arrive")) {
         if (m->ep_rank_arrive != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->ep_rank_arrive = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_attn_quant")) {
+        if (m->fuse_attn_quant != (value != 0) && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_attn_quant = value != 0;
         return 0;
     }
     if (!strcmp(name, "early_loads")) {

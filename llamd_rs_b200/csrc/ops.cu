@@ -4,6 +4,7 @@
 // Reductions whose order is observable in the reference (sequential f32 sums)
 // are walked in that order by one thread; everything that is order-free (max,
 // integer counts) is done in parallel.
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -1063,6 +1064,10 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     __shared__ float s_tree[32];
     __shared__ float s_part[256];
     pdl_trigger();
+    const bool clusters = !tail.counter && tail.qs;  // launched as clusters that quantize the result (below); uniform
+    // (a CTA's shared memory may be written by its cluster only once it runs: every CTA says so here, and waits for the
+    // others' word just before it writes theirs)
+    if (clusters) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     const bool early = (fast & kPassEarlyLoads) != 0 && meta;  // (see attn_rope_scores_kernel)
     if (!early) pdl_wait();
     const int h = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
@@ -1165,6 +1170,62 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
         }
     }
     if (tid < cols) out[((size_t)seq * n_head + h) * hd + (size_t)c * cols + tid] = acc;
+    if (clusters) {
+        // Launched as clusters of the 256 / hd heads x kSplit column slices that make up one 256-element block of the
+        // attention output (hd == 128, 32 columns per CTA: the block's eight 32-element runs, one per CTA): the Q8_K form
+        // of the block (dot.rs:88-128) is made here, what llamd_fwd_quantize would do one launch later. Each CTA finds
+        // the first largest magnitude of its run and leaves it, with its signed value, in every CTA's table at the run's
+        // place; behind the cluster barrier each CTA walks the eight in element order and quantizes its own run.
+        __shared__ float s_ca[8], s_cm[8];
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        const int e0 = (h * hd + c * cols) & 255;  // this run's place in its block
+        const int run = e0 / cols;                 // 0..7
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster has started
+        if (tid < 32) {
+            float amax = fabsf(acc), mx = acc;
+            int idx = e0 + tid;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
+                const float om = __shfl_xor_sync(0xffffffffu, mx, off);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+                if (oa > amax || (oa == amax && oi < idx)) {
+                    amax = oa;
+                    mx = om;
+                    idx = oi;
+                }
+            }
+            if (tid < 8) {  // lane r writes CTA r's table
+                *cluster.map_shared_rank(&s_ca[run], tid) = amax;
+                *cluster.map_shared_rank(&s_cm[run], tid) = mx;
+            }
+        }
+        cluster.sync();
+        if (tid < 32) {
+            float amax = 0.0f, mx = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+                if (s_ca[r] > amax) {  // (runs in element order: an equal magnitude later in the block does not replace)
+                    amax = s_ca[r];
+                    mx = s_cm[r];
+                }
+            int q = 0;
+            float dd = 0.0f;
+            if (amax != 0.0f) {
+                const float iscale = __fdiv_rn(-127.0f, mx);
+                q = min(127, __float2int_rn(__fmul_rn(iscale, acc)));
+                dd = __fdiv_rn(1.0f, iscale);
+            }
+            // four lanes' bytes into one word
+            uint32_t w = (uint32_t)q & 0xFFu;
+            w |= __shfl_down_sync(0xffffffffu, w, 1) << 8;
+            w |= __shfl_down_sync(0xffffffffu, w, 2) << 16;
+            const size_t blk = ((size_t)seq * n_head * hd + (size_t)h * hd + (size_t)c * cols) >> 8;
+            if ((tid & 3) == 0) *reinterpret_cast<uint32_t *>(tail.qs + blk * 256 + e0 + tid) = w;
+            if (run == 0 && tid == 0) tail.d[blk] = dd;
+        }
+    }
     if (tail.counter) {  // uniform over the launch
         __shared__ bool s_last;
         const unsigned per_seq = gridDim.x * gridDim.y;
@@ -1183,6 +1244,34 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
             }
         }
     }
+}
+
+// The attention-output launch with a cluster per 256-element block of its result (attn_out_kernel's quantizing tail).
+template <class KVT>
+static void attn_out_cluster_launch(size_t smem, const float *scores, const KVT *vc, float *out, int n_head, int n_head_kv, int hd,
+                                    const int32_t *meta, int max_kv, int nseq, int8_t *qs, float *d) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_head, kSplit, nseq);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 256 / hd;
+    attr[0].val.clusterDim.y = kSplit;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (g_pdl & PDL_ATTN) ? 2 : 1;
+    g_launches++;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_out_kernel<KVT>, scores, vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv,
+                                             TailPlan{nullptr, qs, d}, g_pass_flags);
+    if (e != cudaSuccess) set_error(e, "attn_out (clusters)");
+}
+// whether the attention output can leave its launch quantized: one cluster = one block
+static bool attn_out_cluster_ok(int n_head, int hd) {
+    return hd == 128 && hd / kSplit == 32 && (256 / hd) * kSplit <= 8 && n_head % (256 / hd) == 0;
 }
 
 // ---- argmax, lowest index on a tie (llamd_forward.hip:353-389) -------------
@@ -1688,7 +1777,7 @@ void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *v
 // llamd_fwd_attention_meta.
 static void attention_rope_launch(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc,
                                   float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab,
-                                  float eps, int max_kv, int nseq, bool kv16) {
+                                  float eps, int max_kv, int nseq, bool kv16, int8_t *qs = nullptr, float *qd = nullptr) {
     const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1) + 3 * hd) * sizeof(float);
     const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
     if (!scores || !meta || hd % (4 * kSplit) || hd > 256 || hd / 2 > 256 || kAttTile * (hd / 4) > 8 * 256 || kPvTile * (hd / kSplit) / 4 > 8 * 256 ||
@@ -1715,18 +1804,37 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
         }
         conf_b[kv16] = smem_b;
     }
+    const bool clusters = qs && qd && attn_out_cluster_ok(n_head, hd);
     if (kv16) {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<__half>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
                   (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
-        launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc,
-                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
+        if (clusters)
+            attn_out_cluster_launch<__half>(smem_b, scores, (const __half *)vc, out, n_head, n_head_kv, hd, meta, max_kv, nseq, qs, qd);
+        else
+            launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores,
+                      (const __half *)vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
     } else {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<float>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
                   (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
-        launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc,
-                  out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
+        if (clusters)
+            attn_out_cluster_launch<float>(smem_b, scores, (const float *)vc, out, n_head, n_head_kv, hd, meta, max_kv, nseq, qs, qd);
+        else
+            launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores,
+                      (const float *)vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
     }
+    if (qs && qd && !clusters) llamd_fwd_quantize(out, qs, qd, nseq * (n_head * hd / 256));
 }
+} // extern "C"
+namespace llamd {
+// The decode pass's attention with the Q8_K form of its result: three launches' work in two where the head size lets a
+// cluster cover a block (the quantize launch otherwise). Same bits as llamd_fwd_attention_rope_meta + llamd_fwd_quantize.
+void attention_rope_quant(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc, float *out,
+                          float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int max_kv,
+                          int nseq, bool kv16, int8_t *qs, float *d) {
+    attention_rope_launch(q, wq, k, wk, v, kc, vc, out, scores, n_head, n_head_kv, hd, meta, rope_tab, eps, max_kv, nseq, kv16, qs, d);
+}
+}  // namespace llamd
+extern "C" {
 void llamd_fwd_attention_rope_meta(const float *q, const float *wq, const float *k, const float *wk, const float *v, float *kc, float *vc,
                                    float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab,
                                    float eps, int max_kv, int nseq) {

@@ -155,7 +155,7 @@ def test_fused_tails_change_nothing(tiny):
         assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
 
 
-@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv", "fuse_silu_down", "early_loads"])
+@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv", "fuse_silu_down", "early_loads", "fuse_attn_quant"])
 def test_fused_launches_change_nothing(tiny, option):
     """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router), with QK-norm, RoPE and
     the KV store inside the attention-scores launch (option fuse_rope_attn), and with the attention norm and the MoE combine
@@ -165,7 +165,7 @@ def test_fused_launches_change_nothing(tiny, option):
     covered by the 768-position run against the CPU fixture, which uses the defaults.)"""
     hp, w, gm, om = tiny
     runs = {}
-    default = 0 if option in ("fuse_norm_qkv", "fuse_silu_down") else 1  # (measured no faster, so off unless asked for)
+    default = 0 if option in ("fuse_norm_qkv", "fuse_silu_down", "fuse_attn_quant") else 1  # (measured no faster, so off unless asked for)
     for fuse in (1, 0, 1):
         gm.set_option(option, fuse)
         gm.set_trace(True)
@@ -188,6 +188,57 @@ def test_fused_launches_change_nothing(tiny, option):
             assert np.array_equal(k.view(np.uint32), rk.view(np.uint32)) and np.array_equal(v.view(np.uint32), rv.view(np.uint32))
         for (x, ids), (rx, rids) in zip(traces, ref[1]):
             assert np.array_equal(x.view(np.uint32), rx.view(np.uint32)) and np.array_equal(ids, rids)
+
+
+@pytest.mark.parametrize("kv_f16", [0, 1])
+def test_attention_output_leaves_its_launch_quantized(kv_f16):
+    """Heads of 128: the eight CTAs that make a 256-element block of the attention output form a cluster, exchange their
+    largest magnitudes through distributed shared memory and write the block's Q8_K form themselves (option fuse_attn_quant;
+    off by default, measured slower) -- against the separate quantize launch: the same tokens, hidden states, experts, logits and cache rows, bit
+    for bit; one and four sequences; against the oracle for the first tokens. Also with the loads before the wait off."""
+    import oracle
+    from llamd_rs_b200 import synth
+    from llamd_rs_b200.model import CudaModel
+
+    hp = dict(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, head_dim=128, n_expert=8, n_expert_used=2, n_ff_expert=256, n_vocab=512,
+              rope_freq_base=1e7, rms_eps=1e-6)
+    w = synth.make_model(hp, seed=11)
+    gm = CudaModel.load_batched(hp, w, max_kv=96, max_seq=4)
+    try:
+        if kv_f16:
+            gm.set_option("kv_f16", 1)
+        runs = []
+        for fuse, early in ((1, 1), (0, 1), (1, 0), (1, 1)):
+            gm.set_option("fuse_attn_quant", fuse)
+            gm.set_option("early_loads", early)
+            gm.set_trace(True)
+            toks, tok, traces = [], 3, []
+            for pos in range(70):  # (past one 64-position tile of the scores launch)
+                tok = gm.forward(tok, pos)
+                toks.append(tok)
+                if pos < 6 or pos > 62:
+                    x, ids = gm.read_trace()
+                    traces.append((x.copy(), ids.copy()))
+            gm.set_trace(False)
+            batch = [gm.forward_batch([5 + pos, 9, 100 + pos, 7], [pos] * 4).tolist() for pos in range(3)]
+            runs.append((toks, traces, gm.logits(4).copy(), batch, [gm.read_kv(il, 3) for il in range(hp["n_layer"])]))
+        ref = runs[1]
+        for toks, traces, logits, batch, kv in (runs[0], runs[2], runs[3]):
+            assert toks == ref[0] and batch == ref[3]
+            assert np.array_equal(logits.view(np.uint32), ref[2].view(np.uint32))
+            for (k, v), (rk, rv) in zip(kv, ref[4]):
+                assert np.array_equal(k.view(np.uint32), rk.view(np.uint32)) and np.array_equal(v.view(np.uint32), rv.view(np.uint32))
+            for (x, ids), (rx, rids) in zip(traces, ref[1]):
+                assert np.array_equal(x.view(np.uint32), rx.view(np.uint32)) and np.array_equal(ids, rids)
+        if not kv_f16:
+            om = oracle.Model(hp, w, threads=4)
+            om.kv_new(96)
+            tok = 3
+            for pos in range(8):
+                tok = oracle.argmax(om.forward(tok, pos))
+                assert tok == ref[0][pos], f"position {pos}"
+    finally:
+        gm.free()
 
 
 def test_prefill_equals_sequential_decode(tiny):
