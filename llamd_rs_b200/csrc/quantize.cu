@@ -35,6 +35,7 @@ __device__ __forceinline__ float rms_scale_sequential(const float *__restrict__ 
 //   - `down`/`cw`: x := x + sum_e cw[e]*down[e] with e in routing order and the
 //     expert sum started from 0 (moe_ffn, layer.rs:243-258, then :281-287),
 // and the updated x is written to sum_out.
+template <int kMaxV>  // float4 groups per thread: rows of up to 1024 * kMaxV elements
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, const float *__restrict__ residual,
                                                        const float *__restrict__ down, const float *__restrict__ cw, int n_used,
                                                        float *__restrict__ sum_out, const float *__restrict__ w, float *__restrict__ out,
@@ -47,7 +48,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__
     const int seq = blockIdx.x, tid = threadIdx.x;
     // Thread t owns the float4 groups t, t+256, ...: every global load of the
     // kernel is issued before anything waits on one.
-    constexpr int kMaxV = 6;  // n <= 6144
+    // (kMaxV = 2 for rows of up to 2048: a third of the registers of the widest form, so three CTAs share an SM where a
+    // tile of 512 rows had one, each waiting on its own chain)
     const int n4 = n / 4;
     float4 wv[kMaxV], xv[kMaxV];
 #pragma unroll
@@ -263,6 +265,14 @@ __global__ void moe_combine_kernel(const float *__restrict__ down, const float *
 
 using namespace llamd;
 
+template <typename... Args>
+static void launch_rms_norm(const char *what, int nseq, int n, Args... args) {
+    if (n <= 2048)
+        launch_kc(PDL_NORM, what, rms_norm_kernel<2>, dim3(nseq), dim3(256), 2 * n * sizeof(float), args...);
+    else
+        launch_kc(PDL_NORM, what, rms_norm_kernel<6>, dim3(nseq), dim3(256), 2 * n * sizeof(float), args...);
+}
+
 // `wait`: with expert parallelism the rows of `down` are stored by other GPUs; the launch first waits for their arrivals.
 void llamd::combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, const float *down, const float *weights, int n_used,
                                         float *sum_out, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
@@ -270,8 +280,8 @@ void llamd::combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, co
         set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    launch_kc(PDL_NORM, "combine_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, down, weights, n_used,
-             sum_out, w, out, qs, d, n, eps, wait, g_pass_flags);
+    launch_rms_norm("combine_rms_norm_quant", nseq, n, x, (const float *)nullptr, down, weights, n_used, sum_out, w, out, qs, d, n, eps, wait,
+                    g_pass_flags);
 }
 
 extern "C" {
@@ -289,16 +299,16 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         set_error_msg("rms_norm: n must be a multiple of 4 and at most 6144");
         return;
     }
-    launch_kc(PDL_NORM, "rms_norm_mul", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w, out,
-             nullptr, nullptr, n, eps, WaitPlan{}, g_pass_flags);
+    launch_rms_norm("rms_norm_mul", nseq, n, x, (const float *)nullptr, (const float *)nullptr, (const float *)nullptr, 0, (float *)nullptr, w, out,
+                    (int8_t *)nullptr, (float *)nullptr, n, eps, WaitPlan{}, g_pass_flags);
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
     if (n % 256 || (size_t)n * 8 > 48 * 1024) {
         set_error_msg("rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    launch_kc(PDL_NORM, "rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, nullptr, nullptr, nullptr, 0, nullptr, w,
-             out, qs, d, n, eps, WaitPlan{}, g_pass_flags);
+    launch_rms_norm("rms_norm_quant", nseq, n, x, (const float *)nullptr, (const float *)nullptr, (const float *)nullptr, 0, (float *)nullptr, w, out,
+                    qs, d, n, eps, WaitPlan{}, g_pass_flags);
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
@@ -308,8 +318,8 @@ void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *
         set_error_msg("add_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
-    launch_kc(PDL_NORM, "add_rms_norm_quant", rms_norm_kernel, dim3(nseq), dim3(256), 2 * n * sizeof(float), x, residual, nullptr, nullptr, 0, sum_out,
-             w, out, qs, d, n, eps, WaitPlan{}, g_pass_flags);
+    launch_rms_norm("add_rms_norm_quant", nseq, n, x, residual, (const float *)nullptr, (const float *)nullptr, 0, sum_out, w, out, qs, d, n, eps,
+                    WaitPlan{}, g_pass_flags);
 }
 // x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
 // forward.rs:586), then norm*w and its Q8_K form: the tail of one layer fused
