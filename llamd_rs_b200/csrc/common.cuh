@@ -52,6 +52,8 @@ extern int g_pdl;
 // ordered sums. kPassEarlyLoads: the attention kernels read the positions and the cached rows of earlier positions before
 // their dependency wait; true only inside a pass whose first launch waits for everything in front of it.
 constexpr int kPassEarlyLoads = 8;
+// kPassAttnGqa: a batch of sequences runs attention as one CTA per kv head for all the query heads that share it.
+constexpr int kPassAttnGqa = 16;
 extern int g_pass_flags;
 extern int g_batch_group;  // matvec_q6k.cu: sequences per CTA for small ungrouped matrices at batch > 1
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

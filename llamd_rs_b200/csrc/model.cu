@@ -191,6 +191,7 @@ struct Model {
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int early_loads = 1;     // option "early_loads": the down projection reads its expert ids, and attention its positions and the cached rows
                              // of earlier positions, before the dependency wait (what they read was complete before the launch in front began)
+    int attn_gqa = 1;        // option "attn_gqa": batches of sequences run attention with one CTA per kv head for all its query heads (the same bits)
     int fuse_attn_quant = 0; // option "fuse_attn_quant": the attention-output launch leaves its result quantized (clusters of the CTAs of a
                              // 256-element block exchange their maxima through distributed shared memory); needs fuse_rope_attn. The same
                              // bits, one launch fewer, and measured 7 % SLOWER (270.4 against 291.2 tok/s): a launch of 16 clusters of
@@ -378,7 +379,8 @@ void queue_token(Model &m, int nseq) {
     struct PassFlags {
         explicit PassFlags(int v) { g_pass_flags = v; }
         ~PassFlags() { g_pass_flags = 0; }
-    } pass_flags((m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0) | (m.early_loads ? kPassEarlyLoads : 0));
+    } pass_flags((m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0) | (m.early_loads ? kPassEarlyLoads : 0) |
+                 (m.attn_gqa ? kPassAttnGqa : 0));
     size_t n_marks = 0;
     auto mark = [&](int phase) {
         if (!m.profiling) return;
@@ -975,6 +977,11 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
     if (!strcmp(name, "ep_rank_arrive")) {
         if (m->ep_rank_arrive != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();
         m->ep_rank_arrive = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "attn_gqa")) {
+        if (m->attn_gqa != (value != 0) && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->attn_gqa = value != 0;
         return 0;
     }
     if (!strcmp(name, "fuse_attn_quant")) {

@@ -1246,6 +1246,250 @@ __global__ void __launch_bounds__(256) attn_out_kernel(const float *__restrict__
     }
 }
 
+// ---- the same two launches for a batch of sequences -----------------------------------------------------------------
+// With several sequences per pass the grids above are many small CTAs in which a quarter (scores) or an eighth (values) of
+// the threads walk chains while the rest wait, several waves of them. Here a CTA serves ALL the query heads that share
+// a kv head: the cached tile is read once for them instead of once each, every thread has a chain to walk, and the grid is
+// one wave. The same operations on the same values in the same order per (head, position) and per (head, column), hence
+// the same bits as the per-head kernels.
+constexpr int kGqaMax = 8;  // query heads per kv head these kernels hold
+
+template <class KVT>
+__global__ void __launch_bounds__(256) attn_rope_scores_gqa_kernel(const float *__restrict__ q_raw, const float *__restrict__ wq,
+                                                                   const float *__restrict__ k_raw, const float *__restrict__ wk,
+                                                                   const float *__restrict__ v_raw, KVT *__restrict__ kc, KVT *__restrict__ vc,
+                                                                   float *__restrict__ scores, int n_head, int n_head_kv, int hd,
+                                                                   const int32_t *__restrict__ meta, int max_kv, int kv_stride,
+                                                                   const float *__restrict__ rope_tab, float eps, int flags) {
+    extern __shared__ __align__(16) float sm[];
+    const int stride = hd + 1, half = hd / 2, ratio = n_head / n_head_kv;
+    float *sq = sm;                               // [ratio][hd] the roped queries
+    float *tile = sq + ratio * hd;                // [2][kAttTile][stride]
+    float *s_raw = tile + 2 * kAttTile * stride;  // [ratio + 1][hd] raw queries, raw key
+    float *sk = s_raw + (ratio + 1) * hd;         // [hd] the roped new key, as the cache holds it
+    __shared__ float s_scale[kGqaMax + 1];
+    pdl_trigger();
+    const bool early = (flags & kPassEarlyLoads) != 0;  // (see attn_rope_scores_kernel)
+    if (!early) pdl_wait();
+    const int kvh = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+    const int pos = meta[2 * seq + 1], n_kv = pos + 1;
+    const int kv_dim = n_head_kv * hd, h0 = kvh * ratio;
+    const int ti_pos = pos / kAttTile;
+    const bool need_k = (ti_pos % kSplitT) == c;  // this CTA scores the new key, and stores the K and V rows of the position
+    KVT *krow = kc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)kvh * hd;
+    KVT *vrow = vc + ((size_t)seq * kv_stride + pos) * kv_dim + (size_t)kvh * hd;
+    const KVT *kb = kc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd;
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn((float)hd));
+    const int hd4 = hd / 4, per_tile4 = kAttTile * hd4;
+    const int n_tiles = (n_kv + kAttTile - 1) / kAttTile;
+    constexpr int kMaxLd = 8;
+    float4 reg[kMaxLd];
+    auto fetch = [&](int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / hd4, cc = idx - r * hd4;
+            const int t = ti * kAttTile + r;
+            reg[j] = (idx < per_tile4 && t < pos) ? KvIo<KVT>::ld4(kb + (size_t)t * kv_dim + 4 * cc) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](float *dst, int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / hd4, cc = idx - r * hd4;
+            if (idx < per_tile4 && ti * kAttTile + r != pos) {  // (the token's own row is written below, by other threads)
+                float *p = dst + r * stride + 4 * cc;
+                p[0] = reg[j].x; p[1] = reg[j].y; p[2] = reg[j].z; p[3] = reg[j].w;
+            }
+        }
+    };
+    if (c < n_tiles) fetch(c);
+    if (early) {
+        const int lpr = hd * (int)sizeof(KVT) / 128;
+        if (lpr > 0)
+            for (int ti = c + kSplitT; ti < n_tiles; ti += kSplitT)
+                for (int i = tid; i < kAttTile * lpr; i += blockDim.x) {
+                    const int r = i / lpr, l = i - r * lpr, t = ti * kAttTile + r;
+                    if (t < pos) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(kb + (size_t)t * kv_dim) + l * 128));
+                }
+        pdl_wait();
+    }
+    // ---- QK-norm (crates/llamd-runtime/src/layer.rs:62-79) and RoPE (crates/llamd-cpu/src/lib.rs:158-209) of the kv head's
+    // query heads (adjacent in q_raw) and, where needed, of the new key
+    const int n_vec = ratio + (need_k ? 1 : 0);
+    for (int i = tid; i < ratio * hd; i += blockDim.x) s_raw[i] = q_raw[((size_t)seq * n_head + h0) * hd + i];
+    if (need_k)
+        for (int i = tid; i < hd; i += blockDim.x) s_raw[ratio * hd + i] = k_raw[((size_t)seq * n_head_kv + kvh) * hd + i];
+    __syncthreads();
+    {
+        // vector v's sum of squares is walked in order by lane v / 8 of warp v % 8: the chains run side by side
+        const int warp = tid >> 5, lane = tid & 31, v = lane * 8 + warp;
+        if (lane < 2 && v < n_vec && (v < ratio ? wq != nullptr : wk != nullptr)) {
+            const float *sx = s_raw + v * hd;
+            float sum = 0.0f;
+#pragma unroll 8
+            for (int t = 0; t < hd; t++) sum = __fadd_rn(sum, __fmul_rn(sx[t], sx[t]));
+            s_scale[v] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)hd), eps)));
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < n_vec * half; idx += blockDim.x) {
+        const int v = idx / half, i = idx - v * half;
+        const bool is_k = v == ratio;
+        const float *sx = s_raw + v * hd;
+        const float *w = is_k ? wk : wq;
+        float a = sx[i], b = sx[i + half];
+        if (w) {
+            const float nsc = s_scale[v];
+            a = __fmul_rn(__fmul_rn(a, nsc), w[i]);
+            b = __fmul_rn(__fmul_rn(b, nsc), w[i + half]);
+        }
+        const float2 cs = *reinterpret_cast<const float2 *>(rope_tab + ((size_t)pos * half + i) * 2);
+        const float o0 = __fsub_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x));
+        const float o1 = __fadd_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+        if (!is_k) {
+            sq[v * hd + i] = o0;
+            sq[v * hd + i + half] = o1;
+        } else {
+            KVT t0, t1;  // as the cache holds it (a binary16 cache rounds here, once)
+            KvIo<KVT>::st(&t0, o0);
+            KvIo<KVT>::st(&t1, o1);
+            sk[i] = (float)t0;
+            sk[i + half] = (float)t1;
+            krow[i] = t0;
+            krow[i + half] = t1;
+            const float *vs = v_raw + ((size_t)seq * n_head_kv + kvh) * hd;
+            KvIo<KVT>::st(vrow + i, vs[i]);
+            KvIo<KVT>::st(vrow + i + half, vs[i + half]);
+        }
+    }
+    __syncthreads();
+    // ---- scores: (query head, position) pairs of the tile over the threads ----
+    int buf = 0;
+    for (int ti = c; ti < n_tiles; ti += kSplitT, buf ^= 1) {
+        float *cur = tile + buf * kAttTile * stride;
+        stash(cur, ti);
+        if (ti == ti_pos)
+            for (int i = tid; i < hd; i += blockDim.x) cur[(pos - ti * kAttTile) * stride + i] = sk[i];
+        __syncthreads();
+        if (ti + kSplitT < n_tiles) fetch(ti + kSplitT);
+        for (int idx = tid; idx < ratio * kAttTile; idx += blockDim.x) {
+            const int j = idx / kAttTile, r = idx - j * kAttTile;
+            const int t = ti * kAttTile + r;
+            if (t >= n_kv) continue;
+            const float *kr = cur + r * stride, *q = sq + j * hd;
+            float dot = 0.0f;
+            if ((hd & 15) == 0) {
+                float pa[16], pb[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(q[i], kr[i]);
+                for (int d0 = 0; d0 < hd; d0 += 16) {
+                    const int dn = (d0 + 16 < hd) ? d0 + 16 : d0;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(q[dn + i], kr[dn + i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) dot = __fadd_rn(dot, pa[i]);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) pa[i] = pb[i];
+                }
+            } else {
+                for (int d = 0; d < hd; d++) dot = __fadd_rn(dot, __fmul_rn(q[d], kr[d]));
+            }
+            scores[((size_t)seq * n_head + h0 + j) * max_kv + t] = __fmul_rn(dot, scale);
+        }
+    }
+}
+
+// Softmax and weighted values for the query heads of one kv head: warp j is head j (ratio * hd / kSplit == 256 threads).
+template <class KVT>
+__global__ void __launch_bounds__(256) attn_out_gqa_kernel(const float *__restrict__ scores, const KVT *__restrict__ vc, float *__restrict__ out,
+                                                           int n_head, int n_head_kv, int hd, const int32_t *__restrict__ meta, int max_kv,
+                                                           int kv_stride, int flags) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float s_inv[kGqaMax];
+    pdl_trigger();
+    const bool early = (flags & kPassEarlyLoads) != 0;
+    if (!early) pdl_wait();
+    const int kvh = blockIdx.x, c = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+    const int ratio = n_head / n_head_kv, h0 = kvh * ratio;
+    const int n_kv = meta[2 * seq + 1] + 1, cap = (max_kv + 3) & ~3;
+    const int cols = hd / kSplit, cols4 = cols / 4;
+    float *sl = sm;                 // [ratio][cap]
+    float *tile = sm + ratio * cap;  // [2][kPvTile][cols]
+    const int kv_dim = n_head_kv * hd;
+    const KVT *vb = vc + (size_t)seq * kv_stride * kv_dim + (size_t)kvh * hd + (size_t)c * cols;
+    const int per_tile4 = kPvTile * cols4;
+    const int n_tiles = (n_kv + kPvTile - 1) / kPvTile;
+    constexpr int kMaxLd = 8;
+    float4 reg[kMaxLd];
+    auto fetch = [&](int ti) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            const int r = idx / cols4, cc = idx - r * cols4;
+            const int t = ti * kPvTile + r;
+            reg[j] = (idx < per_tile4 && t < n_kv) ? KvIo<KVT>::ld4(vb + (size_t)t * kv_dim + 4 * cc) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stash = [&](float *dst) {
+#pragma unroll
+        for (int j = 0; j < kMaxLd; j++) {
+            const int idx = tid + j * 256;
+            if (idx < per_tile4) reinterpret_cast<float4 *>(dst)[idx] = reg[j];
+        }
+    };
+    if (early) {
+        for (int t = tid; t < n_kv; t += blockDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(vb + (size_t)t * kv_dim)));
+        pdl_wait();
+    }
+    fetch(0);
+    const int j = tid >> 5, lane = tid & 31;  // (ratio == 8 warps: warp j is query head h0 + j)
+    {
+        const float *sc = scores + ((size_t)seq * n_head + h0 + j) * max_kv;
+        float *slj = sl + (size_t)j * cap;
+        float lmax = -INFINITY;
+        for (int t = lane; t < n_kv; t += 32) {
+            const float l = sc[t];
+            slj[t] = l;
+            lmax = fmaxf(lmax, l);
+        }
+        for (int off = 16; off > 0; off >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, off));
+        for (int t = lane; t < n_kv; t += 32) slj[t] = ref_expf(__fsub_rn(slj[t], lmax));
+        __syncwarp();
+        if (lane == 0) s_inv[j] = __fdiv_rn(1.0f, chain_sum(slj, n_kv, 0.0f));
+    }
+    __syncthreads();
+    const float inv = s_inv[j];
+    const float *slj = sl + (size_t)j * cap;
+    float acc = 0.0f;
+    for (int ti = 0; ti < n_tiles; ti++) {
+        float *cur = tile + (ti & 1) * kPvTile * cols;
+        stash(cur);
+        __syncthreads();
+        if (ti + 1 < n_tiles) fetch(ti + 1);
+        const int t0 = ti * kPvTile, cnt = min(kPvTile, n_kv - t0);
+        int r = 0;
+        if (cnt >= 16) {
+            float pa[16], pb[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) pa[i] = __fmul_rn(__fmul_rn(slj[t0 + i], inv), cur[i * cols + lane]);
+            for (; r + 16 <= cnt; r += 16) {
+                const int rn = (r + 32 <= cnt) ? r + 16 : r;
+#pragma unroll
+                for (int i = 0; i < 16; i++) pb[i] = __fmul_rn(__fmul_rn(slj[t0 + rn + i], inv), cur[(rn + i) * cols + lane]);
+#pragma unroll
+                for (int i = 0; i < 16; i++) acc = __fadd_rn(acc, pa[i]);
+#pragma unroll
+                for (int i = 0; i < 16; i++) pa[i] = pb[i];
+            }
+        }
+        for (; r < cnt; r++) acc = __fadd_rn(acc, __fmul_rn(__fmul_rn(slj[t0 + r], inv), cur[r * cols + lane]));
+    }
+    out[((size_t)seq * n_head + h0 + j) * hd + (size_t)c * cols + lane] = acc;
+}
+
 // The attention-output launch with a cluster per 256-element block of its result (attn_out_kernel's quantizing tail).
 template <class KVT>
 static void attn_out_cluster_launch(size_t smem, const float *scores, const KVT *vc, float *out, int n_head, int n_head_kv, int hd,
@@ -1803,6 +2047,47 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
             return;
         }
         conf_b[kv16] = smem_b;
+    }
+    // A batch of sequences: one CTA per (kv head, ...) for all the query heads that share it (the decode pass asks for it)
+    const int ratio = n_head / n_head_kv, cap = (max_kv + 3) & ~3;
+    const size_t smem_ga = (size_t)(ratio * hd + 2 * kAttTile * (hd + 1) + (ratio + 1) * hd + hd) * sizeof(float);
+    const size_t smem_gb = (size_t)((size_t)ratio * cap + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
+    // (measured, 48 layers at position ~520: 8 sequences 814.7 -> 1044.8 tok/s, 4 sequences 641.8 -> 717.2, 2 sequences 456.2 -> 439.7,
+    // so from four sequences on)
+    if ((g_pass_flags & kPassAttnGqa) && !(g_pass_flags & 4) && nseq >= 4 && ratio == kGqaMax && hd / kSplit == 32 && smem_ga <= 200 * 1024 &&
+        smem_gb <= 200 * 1024) {
+        static size_t conf_ga[2] = {0, 0}, conf_gb[2] = {0, 0};
+        if (smem_ga > conf_ga[kv16]) {
+            const cudaError_t e = kv16 ? cudaFuncSetAttribute(attn_rope_scores_gqa_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ga)
+                                       : cudaFuncSetAttribute(attn_rope_scores_gqa_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ga);
+            if (e != cudaSuccess) {
+                set_error(e, "attention (rope + scores, per kv head) smem attribute");
+                return;
+            }
+            conf_ga[kv16] = smem_ga;
+        }
+        if (smem_gb > conf_gb[kv16]) {
+            const cudaError_t e = kv16 ? cudaFuncSetAttribute(attn_out_gqa_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gb)
+                                       : cudaFuncSetAttribute(attn_out_gqa_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gb);
+            if (e != cudaSuccess) {
+                set_error(e, "attention (output, per kv head) smem attribute");
+                return;
+            }
+            conf_gb[kv16] = smem_gb;
+        }
+        if (kv16) {
+            launch_kc(PDL_ATTN, "attn_rope_scores_gqa", attn_rope_scores_gqa_kernel<__half>, dim3(n_head_kv, kSplitT, nseq), dim3(256), smem_ga, q, wq, k,
+                      wk, v, (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
+            launch_kc(PDL_ATTN, "attn_out_gqa", attn_out_gqa_kernel<__half>, dim3(n_head_kv, kSplit, nseq), dim3(256), smem_gb, (const float *)scores,
+                      (const __half *)vc, out, n_head, n_head_kv, hd, meta, max_kv, max_kv, g_pass_flags);
+        } else {
+            launch_kc(PDL_ATTN, "attn_rope_scores_gqa", attn_rope_scores_gqa_kernel<float>, dim3(n_head_kv, kSplitT, nseq), dim3(256), smem_ga, q, wq, k,
+                      wk, v, (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
+            launch_kc(PDL_ATTN, "attn_out_gqa", attn_out_gqa_kernel<float>, dim3(n_head_kv, kSplit, nseq), dim3(256), smem_gb, (const float *)scores,
+                      (const float *)vc, out, n_head, n_head_kv, hd, meta, max_kv, max_kv, g_pass_flags);
+        }
+        if (qs && qd) llamd_fwd_quantize(out, qs, qd, nseq * (n_head * hd / 256));
+        return;
     }
     const bool clusters = qs && qd && attn_out_cluster_ok(n_head, hd);
     if (kv16) {

@@ -241,6 +241,51 @@ def test_attention_output_leaves_its_launch_quantized(kv_f16):
         gm.free()
 
 
+@pytest.mark.parametrize("kv_f16", [0, 1])
+def test_batch_attention_per_kv_head(kv_f16):
+    """Eight query heads of 128 per kv head: a batch of sequences runs attention as one CTA per kv head for all of them
+    (option attn_gqa, the default, from four sequences on). Sequences at different positions, across the 64-position score tiles and the
+    256-position value tiles: each sequence's tokens, logits and cache rows equal a single-sequence run's, bit for bit, and
+    the per-head kernels' on the same batch."""
+    from llamd_rs_b200 import synth
+    from llamd_rs_b200.model import CudaModel
+
+    hp = dict(n_layer=2, n_embd=256, n_head=8, n_head_kv=1, head_dim=128, n_expert=8, n_expert_used=2, n_ff_expert=256, n_vocab=512,
+              rope_freq_base=1e7, rms_eps=1e-6)
+    w = synth.make_model(hp, seed=13)
+    gm = CudaModel.load_batched(hp, w, max_kv=320, max_seq=4)
+    try:
+        if kv_f16:
+            gm.set_option("kv_f16", 1)
+        lens = [300, 70, 5, 130]  # the sequences end at different positions
+        prompts = [synth.token_ids(n, hp["n_vocab"], 40 + i, "gqa").tolist() for i, n in enumerate(lens)]
+        single = []
+        for s_, pr in enumerate(prompts):
+            for pos, t in enumerate(pr):
+                tok = gm.forward(t, pos)
+            single.append((tok, gm.logits()[0].copy(), [gm.read_kv(il, len(pr)) for il in range(hp["n_layer"])]))
+        runs = {}
+        for gqa in (1, 0):
+            gm.set_option("attn_gqa", gqa)
+            # the four sequences advance together while they last; a finished one repeats its last token at its last position
+            for step in range(max(lens)):
+                toks = [pr[min(step, len(pr) - 1)] for pr in prompts]
+                poss = [min(step, len(pr) - 1) for pr in prompts]
+                out = gm.forward_batch(toks, poss)
+            runs[gqa] = (out.tolist(), gm.logits(4).copy())
+        gm.set_option("attn_gqa", 1)
+        assert runs[1][0] == runs[0][0] and np.array_equal(runs[1][1].view(np.uint32), runs[0][1].view(np.uint32))
+        for s_ in range(4):  # (a finished sequence repeated its last position: the same row, the same logits)
+            assert runs[1][0][s_] == single[s_][0], f"sequence {s_}"
+            assert np.array_equal(runs[1][1][s_].view(np.uint32), single[s_][1].view(np.uint32)), f"sequence {s_}: logits"
+            for il in range(hp["n_layer"]):
+                k, v = gm.read_kv(il, lens[s_], s_)
+                rk, rv = single[s_][2][il]
+                assert np.array_equal(k.view(np.uint32), rk.view(np.uint32)) and np.array_equal(v.view(np.uint32), rv.view(np.uint32))
+    finally:
+        gm.free()
+
+
 def test_prefill_equals_sequential_decode(tiny):
     """crates/llamd-testing/tests/vulkan_prefill.rs:48-136: prefill gives the token (and here the logits and the
     K/V cache, bit for bit) of sequential decode, for (tile, length) pairs that straddle tile and chunk boundaries."""
