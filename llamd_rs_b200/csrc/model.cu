@@ -1258,7 +1258,25 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
                                     p.k.as<float>(), p.v.as<float>(), eb, qd, kvd, kvd, T);
         }
         const float *kc_view = l.kc.as<float>(), *vc_view = l.vc.as<float>();  // what the tile's attention reads
-        if (multi_seq && m.kv16) {
+        if (multi_seq && m.fuse_rope_attn && hd % 16 == 0 && hd <= 256) {
+            // every token is another sequence at its own position, as in a decode pass: the decode pass's attention launches
+            // (QK-norm, RoPE and the K/V store inside the scores launch; one CTA per kv head for all its query heads where
+            // the shape allows; the rows of earlier positions read before the dependency wait -- earlier passes wrote them)
+            struct PassFlags {
+                explicit PassFlags(int v) { g_pass_flags = v; }
+                ~PassFlags() { g_pass_flags = 0; }
+            } pass_flags((m.early_loads ? kPassEarlyLoads : 0) | (m.attn_gqa ? kPassAttnGqa : 0));
+            if (m.kv16)
+                llamd_fwd_attention_rope_meta_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
+                                                   l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p,
+                                                   p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(),
+                                                   hp.rms_eps, m.max_kv, T);
+            else
+                llamd_fwd_attention_rope_meta(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
+                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
+                                              l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta,
+                                              m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, T);
+        } else if (multi_seq && m.kv16) {
             llamd_fwd_qk_norm_rope_store_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
                                               l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
                                               m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
