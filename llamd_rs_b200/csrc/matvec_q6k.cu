@@ -522,14 +522,26 @@ static void launch_t(const MatvecParams &p, dim3 grid, const MatvecPlans &plans)
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode, const float *xf,
                    const float *xu, int own_lo, int own_hi, const MatvecPlans &plans) {
-    if (blocks <= 0 || blocks > kThreads || nseq < 1 || nseq > LLAMD_MAX_SEQ || njobs < 1 || njobs > 3 || (ids && nseq != 1) ||
-        (ids && (n_slots < 1 || act_div < 1))) {
-        set_error_msg("matvec: blocks must be 1..256, nseq 1..8, 1..3 matrices");
+    if (blocks <= 0 || blocks > kThreads || nseq < 1 || nseq > LLAMD_MAX_BATCH || njobs < 1 || njobs > 3 || (ids && nseq != 1) ||
+        (ids && (n_slots < 1 || act_div < 1)) || (nseq > LLAMD_MAX_SEQ && act_mode != ACT_Q8K)) {
+        set_error_msg("matvec: blocks must be 1..256, nseq 1..8 (ungrouped Q8_K activations: up to 256), 1..3 matrices");
         return;
     }
-    if (matvec_smem_bytes(nseq, blocks) > 200 * 1024) {
-        set_error_msg("matvec: blocks x nseq does not fit shared memory");
-        return;
+    if (nseq > LLAMD_MAX_SEQ) {
+        // more sequences than one launch holds: the launch's group size where it splits small matrices over the sequences
+        // anyway (below), else one launch per LLAMD_MAX_SEQ sequences (activations and outputs are [nseq][...])
+        int ctas = 0;
+        for (int i = 0; i < njobs; i++) ctas += rows[i] > 0 ? (rows[i] + kThreads / blocks - 1) / (kThreads / blocks) : 0;
+        if (!(g_batch_group > 0 && ctas <= kBatchSplitMaxCtas)) {
+            for (int s0 = 0; s0 < nseq; s0 += LLAMD_MAX_SEQ) {
+                const int cnt = nseq - s0 < LLAMD_MAX_SEQ ? nseq - s0 : LLAMD_MAX_SEQ;
+                float *o[3] = {nullptr, nullptr, nullptr};
+                for (int i = 0; i < njobs; i++) o[i] = out[i] + (size_t)s0 * rows[i];
+                launch_matvec(njobs, w, o, rows, blocks, aq + (size_t)s0 * blocks * 256, ad + (size_t)s0 * blocks, cnt, ids, n_slots, n_expert,
+                              act_div, act_mode, xf, xu, own_lo, own_hi, plans);
+            }
+            return;
+        }
     }
     MatvecParams p = {};
     p.njobs = njobs;
@@ -566,6 +578,10 @@ void launch_matvec(int njobs, const void *const *w, float *const *out, const int
         while (nseq % g) g--;
         p.n_slots = nseq / g;
         nseq = g;
+    }
+    if (nseq > LLAMD_MAX_SEQ || matvec_smem_bytes(nseq, blocks) > 200 * 1024) {
+        set_error_msg("matvec: blocks x nseq does not fit a launch");
+        return;
     }
     const dim3 grid(p.ctas_per_slot * p.n_slots);
     if (act_mode == ACT_NORM) {

@@ -191,6 +191,10 @@ struct Model {
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int early_loads = 1;     // option "early_loads": the down projection reads its expert ids, and attention its positions and the cached rows
                              // of earlier positions, before the dependency wait (what they read was complete before the launch in front began)
+    int matvec_batch_max = 40;  // option "matvec_batch_max": batches up to this many sequences run the decode pass of matvec launches (beyond
+                                // LLAMD_MAX_SEQ its large matrices take one launch per LLAMD_MAX_SEQ sequences), larger ones the tile pass.
+                                // Measured at position ~500, tok/s aggregate, matvec / tile: 9 sequences 1109 / 529, 16: 1299 / 776,
+                                // 24: 1374 / 1015, 32: 1424 / 1247, 48: 1479 / 1652, 64: 1529 / 2048
     int attn_gqa = 1;        // option "attn_gqa": batches of sequences run attention with one CTA per kv head for all its query heads (the same bits)
     int fuse_attn_quant = 0; // option "fuse_attn_quant": the attention-output launch leaves its result quantized (clusters of the CTAs of a
                              // 256-element block exchange their maxima through distributed shared memory); needs fuse_rope_attn. The same
@@ -979,6 +983,14 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         m->ep_rank_arrive = value != 0;
         return 0;
     }
+    if (!strcmp(name, "matvec_batch_max")) {
+        if (value < LLAMD_MAX_SEQ || value > LLAMD_MAX_BATCH) {
+            m->err = "option matvec_batch_max: 8..256";
+            return -1;
+        }
+        m->matvec_batch_max = value;
+        return 0;
+    }
     if (!strcmp(name, "attn_gqa")) {
         if (m->attn_gqa != (value != 0) && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
         m->attn_gqa = value != 0;
@@ -1108,7 +1120,7 @@ int llamd_model_forward_batch(llamd_model *h, const int32_t *tokens, const int32
     Model *m = (Model *)h;
     if (!m || !tokens || !positions || !out_tokens) return -1;
     m->err.clear();
-    if (nseq > LLAMD_MAX_SEQ && nseq <= m->max_seq) return run_wide_batch(*m, tokens, positions, nseq, out_tokens);
+    if (nseq > m->matvec_batch_max && nseq > LLAMD_MAX_SEQ && nseq <= m->max_seq) return run_wide_batch(*m, tokens, positions, nseq, out_tokens);
     // sharded experts: the per-op pass exchanges one sequence per rank; several go through the tile exchange
     if (m->ep_world > 1 && nseq > 1 && nseq <= m->max_seq) return run_wide_batch(*m, tokens, positions, nseq, out_tokens);
     return run(*m, tokens, positions, nseq, out_tokens);

@@ -1,7 +1,9 @@
-"""Wide batches and draft verification, both on the tiled (GEMM) pass, against single-sequence decode.
+"""Wide batches and draft verification against single-sequence decode.
 
-  - forward_batch with more than 8 sequences (the nseq kernels' limit) runs as a tile whose tokens belong to different
-    sequences; every sequence must get exactly the tokens and logits of its own single-sequence run
+  - forward_batch with more than 8 sequences (the nseq kernels' limit per launch) runs either as the decode pass of matvec
+    launches, whose large matrices then take one launch per 8 sequences (up to option matvec_batch_max sequences, 40 by
+    default), or as a tile whose tokens belong to different sequences (beyond); either way every sequence must get
+    exactly the tokens and logits of its own single-sequence run
     (crates/llamd-testing/tests/batch_decode.rs:102-125, beyond its 8);
   - verify() returns the greedy token after every prefix of what it is given, so speculative decoding with ANY drafter
     reproduces plain greedy decode token for token (the reference's rule for it: "acceptance may change speed; it may
@@ -27,8 +29,9 @@ def bits(a):
     return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
 
 
+@pytest.mark.parametrize("path", ["matvec", "tile"])
 @pytest.mark.parametrize("nseq", [9, 20, 33])
-def test_wide_batch_equals_single_sequences(be, nseq):
+def test_wide_batch_equals_single_sequences(be, nseq, path):
     from llamd_rs_b200 import synth
     from llamd_rs_b200.model import CudaModel
 
@@ -47,6 +50,7 @@ def test_wide_batch_equals_single_sequences(be, nseq):
     single.free()
     m = CudaModel.load_synthetic(hp, 9, max_kv=16, max_seq=nseq)
     try:
+        m.set_option("matvec_batch_max", 256 if path == "matvec" else 8)
         toks = np.array(first, dtype=np.int32)
         got = []
         for pos in range(steps):
