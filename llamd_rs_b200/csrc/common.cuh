@@ -208,7 +208,13 @@ struct MatvecPlans {
     // waited for the router. The weights then travel while the launch in front still runs. Never set for a launch whose
     // ids are written by the launch directly in front of it.
     int ids_early;
+    // A grouped launch over many slots (a batch of sequences): a permutation of the slots, sorted by expert id, in which
+    // the CTAs take them. Slots that name the same expert then run side by side and the second finds the expert's bytes in
+    // L2 instead of reading them from HBM again. Produced by slot_order_launch; must be complete when the ids are.
+    const int32_t *slot_order;
 };
+// order[] = the slots 0..n_slots-1 sorted by (ids[slot], slot). One small launch.
+void slot_order_launch(const int32_t *ids, int n_slots, int32_t *order);
 
 // The decode pass's attention (QK-norm, RoPE and the K/V store inside the scores launch) leaving its result quantized as well.
 void attention_rope_quant(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc, float *out,

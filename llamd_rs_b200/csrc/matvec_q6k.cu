@@ -73,6 +73,8 @@ struct MatvecParams {
     // Grouped launches: the ids were complete before the launch in front of this one began (see MatvecPlans::ids_early),
     // so they are read, and the weight loads issued, before the dependency wait.
     int ids_early;
+    // Grouped launches: the order in which the CTAs take the slots (MatvecPlans::slot_order), or null for 0, 1, 2, ...
+    const int32_t *slot_order;
 };
 
 //   ACT_NORM the activation is rms_norm(x + combine) * w, quantized, made by every CTA (NormPlan): the norm launch in front
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
     const bool late_trigger = !MULTI && p.ids && !early;
     if (!late_trigger) pdl_trigger();
     // ---- which job / slot / rows -------------------------------------
-    const int slot = blockIdx.x / p.ctas_per_slot;
+    int slot = blockIdx.x / p.ctas_per_slot;
     const int cta = blockIdx.x - slot * p.ctas_per_slot;
     int j = 0;
     if (p.njobs > 1 && cta >= p.job[1].cta_begin) j = 1;
@@ -162,6 +164,7 @@ __global__ void __launch_bounds__(kThreads, NSEQ == 1 ? 3 : (NSEQ == 2 ? 2 : 1))
         __syncthreads();
     } else if (p.ids) {
         if (!early) pdl_wait();  // the ids come from the router kernel
+        if (!EP && p.slot_order) slot = __ldcg(p.slot_order + slot);  // (slots of one expert side by side: its second reader finds it in L2)
         if (EP && p.dwait.counter) {  // ... or from every rank's push: all of this layer's records must have landed
             if (tid == 0) {
                 unsigned int ep;
@@ -478,6 +481,7 @@ static void launch_t(const MatvecParams &p, dim3 grid, const MatvecPlans &plans)
     q.peer = plans.peer;
     q.tail = plans.tail;
     q.ids_early = (plans.ids_early && !MULTI && p.ids && !q.dwait.counter) ? 1 : 0;
+    q.slot_order = (!MULTI && p.ids && !q.dwait.counter && !q.peer.out_tab) ? plans.slot_order : nullptr;
     // each plan fits one kind of launch only; a plan given to another kind is refused, not dropped
     if (q.dwait.counter && !(!MULTI && NSEQ == 1 && p.ids)) {
         set_error_msg("matvec: a dispatch wait was planned for a launch that cannot carry it");

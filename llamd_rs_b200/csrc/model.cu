@@ -140,6 +140,7 @@ struct Model {
     Buf tok_embd, output_norm, output, rope_tab;
     // scratch (crates/llamd-runtime/src/device.rs:407-434)
     Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, router_logits, router_probs, expert_ids, expert_w;
+    Buf slot_order;          // [max_seq * n_expert_used] a batch's (sequence, slot) pairs sorted by expert (decode pass, 8 sequences and more)
     Buf e_gate, e_up, e_down, logits, amax_v, amax_i, out_token, meta;
     Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
     Buf scores;              // [max_seq][n_head][max_kv] scaled attention logits
@@ -195,6 +196,7 @@ struct Model {
                                 // LLAMD_MAX_SEQ its large matrices take one launch per LLAMD_MAX_SEQ sequences), larger ones the tile pass.
                                 // Measured at position ~500, tok/s aggregate, matvec / tile: 9 sequences 1109 / 529, 16: 1299 / 776,
                                 // 24: 1374 / 1015, 32: 1424 / 1247, 48: 1479 / 1652, 64: 1529 / 2048
+    int sort_slots = 8;      // option "sort_slots" = n: from n sequences per pass the expert launches take their slots in expert order (0: never)
     int attn_gqa = 1;        // option "attn_gqa": batches of sequences run attention with one CTA per kv head for all its query heads (the same bits)
     int fuse_attn_quant = 0; // option "fuse_attn_quant": the attention-output launch leaves its result quantized (clusters of the CTAs of a
                              // 256-element block exchange their maxima through distributed shared memory); needs fuse_rope_attn. The same
@@ -574,6 +576,14 @@ void queue_token(Model &m, int nseq) {
             continue;
         }
         MatvecPlans gu = plan_experts(m, l.down_exps, m.expert_ids.as<int32_t>(), nseq * nu);
+        // a batch's slots in expert order, so that the sequences that chose the same expert read it side by side (one small
+        // launch; measured worth it from 8 sequences on)
+        const int32_t *order = nullptr;
+        if (m.sort_slots && nseq >= m.sort_slots) {
+            slot_order_launch(m.expert_ids.as<int32_t>(), nseq * nu, m.slot_order.as<int32_t>());
+            order = m.slot_order.as<int32_t>();
+        }
+        gu.slot_order = order;
         // SiLU on the gate only, times up, quantized per expert; each expert's down projection reads its OWN activation
         if (fuse) {
             gu.tail = TailPlan{m.tail_counter.as<unsigned int>(), m.aq2.as<int8_t>(), m.ad2.as<float>()};
@@ -593,6 +603,7 @@ void queue_token(Model &m, int nseq) {
         // travel while the SiLU launch runs)
         MatvecPlans dn_plan = plan_after_down(il);
         dn_plan.ids_early = m.early_loads;
+        dn_plan.slot_order = order;
         if (!fuse && m.fuse_silu_down)  // every CTA of a slot makes the slot's activation itself: one launch fewer, the same bits
             matvec_grouped_pa_silu(dn_plan, l.down_exps.p, m.expert_ids.as<int32_t>(), m.e_gate.as<float>(), m.e_up.as<float>(),
                                    m.e_down.as<float>(), ffe / 256, E, nu, nseq);
@@ -781,7 +792,7 @@ llamd_model *llamd_model_create(const llamd_hparams *hp, int max_kv, int max_seq
     ok = ok && m->aq2.alloc(nu * ffe * S);
     f(m->ad2, nu * ffe / 256);
     f(m->router_logits, hp->n_expert); f(m->router_probs, hp->n_expert);
-    ok = ok && m->expert_ids.alloc(nu * 4 * S);
+    ok = ok && m->expert_ids.alloc(nu * 4 * S) && m->slot_order.alloc(nu * 4 * S);
     f(m->expert_w, nu); f(m->e_gate, nu * ffe); f(m->e_up, nu * ffe); f(m->e_down, nu * E);
     f(m->logits, hp->n_vocab); f(m->amax_v, kArgmaxBlocks);
     ok = ok && m->amax_i.alloc(kArgmaxBlocks * 4 * S) && m->out_token.alloc(4 * S) && m->meta.alloc(8 * S);
@@ -830,7 +841,7 @@ void llamd_model_free(llamd_model *h) {
                        &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.gate_fold, &l.up_fold, &l.down_fold, &l.kc, &l.vc})
             b->release();
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
-                   &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->expert_w, &m->e_gate,
+                   &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->slot_order, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
@@ -989,6 +1000,15 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
             return -1;
         }
         m->matvec_batch_max = value;
+        return 0;
+    }
+    if (!strcmp(name, "sort_slots")) {
+        if (value < 0 || value > LLAMD_MAX_BATCH) {
+            m->err = "option sort_slots: 0 (never) or the number of sequences from which on, up to 256";
+            return -1;
+        }
+        if (m->sort_slots != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->sort_slots = value;
         return 0;
     }
     if (!strcmp(name, "attn_gqa")) {

@@ -1518,6 +1518,25 @@ static bool attn_out_cluster_ok(int n_head, int hd) {
     return hd == 128 && hd / kSplit == 32 && (256 / hd) * kSplit <= 8 && n_head % (256 / hd) == 0;
 }
 
+// order[] = the slots sorted by (expert id, slot): every slot counts the slots that come before it (a few hundred slots:
+// one CTA, no scratch memory).
+__global__ void __launch_bounds__(256) slot_order_kernel(const int32_t *__restrict__ ids, int n_slots, int32_t *__restrict__ order) {
+    extern __shared__ int32_t s_ids[];
+    pdl_trigger();
+    pdl_wait();
+    for (int i = threadIdx.x; i < n_slots; i += blockDim.x) s_ids[i] = ids[i];
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_slots; i += blockDim.x) {
+        const int mine = s_ids[i];
+        int rank = 0;
+        for (int j = 0; j < n_slots; j++) {
+            const int o = s_ids[j];
+            rank += (o < mine || (o == mine && j < i)) ? 1 : 0;
+        }
+        order[rank] = i;
+    }
+}
+
 // ---- argmax, lowest index on a tie (llamd_forward.hip:353-389) -------------
 __device__ __forceinline__ void argmax_combine(float &v, int &i, float ov, int oi) {
     if (ov > v || (ov == v && oi < i)) {
@@ -2236,3 +2255,11 @@ void llamd_fwd_moe_group(const int32_t *ids, int n_expert, int n_used, int nseq,
 }
 
 }  // extern "C"
+
+void llamd::slot_order_launch(const int32_t *ids, int n_slots, int32_t *order) {
+    if (n_slots < 1 || n_slots > 8192) {
+        set_error_msg("slot_order: 1..8192 slots");
+        return;
+    }
+    launch_kc(PDL_SMALL, "slot_order", slot_order_kernel, dim3(1), dim3(256), (size_t)n_slots * sizeof(int32_t), ids, n_slots, order);
+}
