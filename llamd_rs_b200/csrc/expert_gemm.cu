@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(256, 2) q6k_gemm_dense_kernel(const GemmParams
 using namespace llamd;
 
 static void gemm_launch(GemmParams &p, int n_groups) {
-    const int threads = n_groups > 1 || p.gstart ? 128 : 256;
+    const int threads = n_groups > 1 || p.gstart || p.folded[0] ? 128 : 256;  // (a folded matrix: the kernel that copies tiles)
     const size_t smem = gemm_smem_bytes(p.nb, threads);
     if (p.nb < 1 || smem > 220 * 1024) {
         set_error_msg("q6k gemm: blocks per row must be 1..24");
@@ -577,4 +577,22 @@ void llamd::expert_gemm_scatter(const void *wa, const void *wb, const int32_t *g
     p.gstart = gstart; p.gcount = gcount; p.act_map = act_map; p.out_map = pslot;
     p.expert_units = (long long)rows * blocks;
     gemm_launch(p, n_expert);
+}
+
+// One matrix kept folded (expert_prefold with one "expert") against ntok activations: out[ntok][rows]. The grouped kernel
+// with a single group: a CTA copies its row tile's image and multiplies; 2 bytes per weight whatever ntok is, where the
+// matvec repeats its integer work per sequence. Same results as llamd_fwd_gemm_tokens.
+void llamd::gemm_tokens_folded(const void *folded, const void *aq_rm, const float *ad, float *out, int blocks, int rows, int ntok) {
+    if (ntok < 1) return;
+    GemmParams p = {};
+    p.folded[0] = (const uint8_t *)folded;
+    p.fold_tile_bytes = (long long)expert_fold_tile_bytes(blocks);
+    p.out[0] = out;
+    p.rows[0] = rows;
+    p.njobs = 1;
+    p.nb = blocks;
+    p.aq_rm = (const uint32_t *)aq_rm;
+    p.ad = ad;
+    p.n_tokens = ntok;
+    gemm_launch(p, 1);
 }

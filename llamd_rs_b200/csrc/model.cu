@@ -140,6 +140,8 @@ struct Model {
     Buf tok_embd, output_norm, output, rope_tab;
     // scratch (crates/llamd-runtime/src/device.rs:407-434)
     Buf x, xb, xb2, q, k, v, attn, aq, ad, aq2, ad2, router_logits, router_probs, expert_ids, expert_w;
+    Buf head_fold, head_rm;  // the output matrix folded for the integer GEMM (option "head_gemm"), and a batch's activations in its operand order
+    bool head_fold_ready = false, head_fold_failed = false;
     Buf slot_order;          // [max_seq * n_expert_used] a batch's (sequence, slot) pairs sorted by expert (decode pass, 8 sequences and more)
     Buf e_gate, e_up, e_down, logits, amax_v, amax_i, out_token, meta;
     Buf trace_x, trace_ids;  // [n_layer][max_seq][n_embd], [n_layer][max_seq][n_used]
@@ -196,6 +198,9 @@ struct Model {
                                 // LLAMD_MAX_SEQ its large matrices take one launch per LLAMD_MAX_SEQ sequences), larger ones the tile pass.
                                 // Measured at position ~500, tok/s aggregate, matvec / tile: 9 sequences 1109 / 529, 16: 1299 / 776,
                                 // 24: 1374 / 1015, 32: 1424 / 1247, 48: 1479 / 1652, 64: 1529 / 2048
+    int head_gemm = 4;       // option "head_gemm" = n: from n sequences per pass the output projection runs on the integer GEMM over a folded
+                             // copy of the matrix (2 bytes per weight once per pass, where the matvec repeats its integer work per sequence;
+                             // +0.6 GB for a 151936 x 2048 matrix, made at the first such pass); 0: never
     int sort_slots = 8;      // option "sort_slots" = n: from n sequences per pass the expert launches take their slots in expert order (0: never)
     int attn_gqa = 1;        // option "attn_gqa": batches of sequences run attention with one CTA per kv head for all its query heads (the same bits)
     int fuse_attn_quant = 0; // option "fuse_attn_quant": the attention-output launch leaves its result quantized (clusters of the CTAs of a
@@ -620,9 +625,15 @@ void queue_token(Model &m, int nseq) {
                                 m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
     trace_x(hp.n_layer - 1);
     mark(LLAMD_PH_ATTN_NORM);
-    // (the prefetch plan names where the next token starts)
-    matvec_batch(plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v), m.output.p ? m.output.p : m.tok_embd.p,
-                 m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb, hp.n_vocab, nseq);
+    if (m.head_gemm && nseq >= m.head_gemm && m.head_fold_ready) {
+        // a batch: the folded matrix once for all the sequences, on the integer tensor path (the same bits)
+        llamd_fwd_q8k_residue_major(m.aq.as<int8_t>(), m.head_rm.p, (size_t)nseq * eb);
+        gemm_tokens_folded(m.head_fold.p, m.head_rm.p, m.ad.as<float>(), m.logits.as<float>(), eb, hp.n_vocab, nseq);
+    } else {
+        // (the prefetch plan names where the next token starts)
+        matvec_batch(plan_static(m, &m.layers[0].attn_q, &m.layers[0].attn_k, &m.layers[0].attn_v), m.output.p ? m.output.p : m.tok_embd.p,
+                     m.aq.as<int8_t>(), m.ad.as<float>(), m.logits.as<float>(), eb, hp.n_vocab, nseq);
+    }
     mark(LLAMD_PH_LM_HEAD);
     llamd_fwd_argmax(m.logits.as<float>(), hp.n_vocab, m.amax_v.as<float>(), m.amax_i.as<int32_t>(), m.out_token.as<int32_t>(),
                      kArgmaxBlocks, nseq);
@@ -700,6 +711,22 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
     }
     if (!check_ready(m)) return -1;
     if (m.resident) mega_prepare(m);  // (uploads a pointer table: not inside a capture)
+    if (m.head_gemm && nseq >= m.head_gemm && !m.head_fold_ready && !m.head_fold_failed) {
+        // the output matrix folded once for the batched output projection (not inside a capture); without the memory for
+        // it the matvec serves batches as it serves one sequence
+        const int eb = hp.n_embd / 256;
+        const size_t need = expert_fold_bytes(eb, hp.n_vocab, 1);
+        if (need + ((size_t)1 << 30) <= llamd_cuda_free_mem() && m.head_fold.alloc(need) && m.head_rm.alloc((size_t)m.max_seq * eb * 256)) {
+            expert_prefold(m.output.p ? m.output.p : m.tok_embd.p, m.head_fold.p, eb, hp.n_vocab, 1);
+            m.head_fold_ready = llamd_fwd_sync() == 0;
+        }
+        if (!m.head_fold_ready) {
+            m.head_fold.release();
+            m.head_rm.release();
+            m.head_fold_failed = true;
+            if (error_code() != 0) return -1;
+        }
+    }
     // the only per-token host->device traffic: 8 bytes per sequence
     if (cudaMemcpyAsync(m.meta.p, m.h_meta, (size_t)nseq * 8, cudaMemcpyHostToDevice, stream()) != cudaSuccess) {
         set_error(cudaGetLastError(), "meta H2D");
@@ -841,7 +868,7 @@ void llamd_model_free(llamd_model *h) {
                        &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.gate_fold, &l.up_fold, &l.down_fold, &l.kc, &l.vc})
             b->release();
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
-                   &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->slot_order, &m->expert_w, &m->e_gate,
+                   &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->slot_order, &m->head_fold, &m->head_rm, &m->expert_w, &m->e_gate,
                    &m->e_up, &m->e_down, &m->logits, &m->amax_v, &m->amax_i, &m->out_token, &m->meta, &m->trace_x, &m->trace_ids,
                    &m->tok_log, &m->tok_count, &m->router_counter, &m->tail_counter, &m->scores, &m->ids_all, &m->ad_all, &m->aq_all, &m->gate_all,
                    &m->up_all, &m->aq2_all, &m->ad2_all, &m->down_all, &m->recv_all, &m->ep_arrive, &m->ep_status, &m->ep_out_tab,
@@ -882,6 +909,12 @@ int llamd_model_set_tensor(llamd_model *h, int layer, int which, size_t first_bl
     if (which == LLAMD_T_TOK_EMBD || which == LLAMD_T_OUTPUT) {
         total = q6k_blocks_for(hp.n_vocab, E);
         ok = upload_q6k_slice(which == LLAMD_T_TOK_EMBD ? m->tok_embd : m->output, total, first_block, host, count);
+        if (m->head_fold_ready || m->head_fold_failed) {  // the folded copy of the output matrix is of the old bytes
+            if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
+            m->head_fold.release();
+            m->head_rm.release();
+            m->head_fold_ready = m->head_fold_failed = false;
+        }
     } else if (which == LLAMD_T_OUTPUT_NORM) {
         ok = count == E && upload_f32(m->output_norm, host, E);
     } else {
@@ -1000,6 +1033,15 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
             return -1;
         }
         m->matvec_batch_max = value;
+        return 0;
+    }
+    if (!strcmp(name, "head_gemm")) {
+        if (value < 0 || value > LLAMD_MAX_BATCH) {
+            m->err = "option head_gemm: 0 (never) or the number of sequences from which on, up to 256";
+            return -1;
+        }
+        if (m->head_gemm != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->head_gemm = value;
         return 0;
     }
     if (!strcmp(name, "sort_slots")) {
