@@ -134,7 +134,8 @@ size_t llamd_model_weight_bytes(llamd_model *m); /* device.rs:473 */
  * (default 8): from n sequences per pass the expert launches take their (sequence, expert) slots in expert order, so that
  * sequences that chose the same expert read it side by side; "head_gemm" = n (default 4): from n sequences per pass the
  * output projection runs on the integer GEMM over a folded copy of its matrix (made at the first such pass, +2 bytes per
- * weight; the matvec when the memory is not there); "early_loads"
+ * weight; the matvec when the memory is not there); "dense_gemm" = n (default 8): the same for the four attention
+ * projections of every layer; "early_loads"
  * (default 1): the down projection reads its expert ids, and attention its positions and the cached rows of earlier
  * positions, before the launch's dependency wait, so their bytes travel while the launch in front still runs. */
 int llamd_model_set_option(llamd_model *m, const char *name, int value);

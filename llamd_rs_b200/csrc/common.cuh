@@ -256,6 +256,8 @@ size_t expert_fold_tile_bytes(int blocks);
 size_t expert_fold_bytes(int blocks, int rows, int n_expert);
 void expert_prefold(const void *w, void *dst, int blocks, int rows, int n_expert);
 void gemm_tokens_folded(const void *folded, const void *aq_rm, const float *ad, float *out, int blocks, int rows, int ntok);
+void gemm_tokens_folded3(const void *f0, const void *f1, const void *f2, const void *aq_rm, const float *ad, float *o0, float *o1, float *o2,
+                         int blocks, int rows0, int rows1, int rows2, int ntok);
 // expert parallelism, a prefill tile (ep.cu)
 void ep_push_tile(const int32_t *ids, const float *ad, const int8_t *aq, int32_t *const *ids_tab, float *const *ad_tab,
                   int8_t *const *aq_tab, unsigned int *const *disp_tab, unsigned int *epoch, unsigned int *push_done, int T, int cap,

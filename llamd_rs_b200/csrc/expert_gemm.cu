@@ -579,20 +579,24 @@ void llamd::expert_gemm_scatter(const void *wa, const void *wb, const int32_t *g
     gemm_launch(p, n_expert);
 }
 
-// One matrix kept folded (expert_prefold with one "expert") against ntok activations: out[ntok][rows]. The grouped kernel
-// with a single group: a CTA copies its row tile's image and multiplies; 2 bytes per weight whatever ntok is, where the
-// matvec repeats its integer work per sequence. Same results as llamd_fwd_gemm_tokens.
-void llamd::gemm_tokens_folded(const void *folded, const void *aq_rm, const float *ad, float *out, int blocks, int rows, int ntok) {
+// Up to three matrices kept folded (expert_prefold with one "expert" each) against ntok activations: out_i[ntok][rows_i].
+// The grouped kernel with a single group: a CTA copies its row tile's image and multiplies; 2 bytes per weight whatever
+// ntok is, where the matvec repeats its integer work per sequence. Same results as llamd_fwd_gemm_tokens.
+void llamd::gemm_tokens_folded3(const void *f0, const void *f1, const void *f2, const void *aq_rm, const float *ad, float *o0, float *o1,
+                                float *o2, int blocks, int rows0, int rows1, int rows2, int ntok) {
     if (ntok < 1) return;
     GemmParams p = {};
-    p.folded[0] = (const uint8_t *)folded;
+    p.folded[0] = (const uint8_t *)f0; p.folded[1] = (const uint8_t *)f1; p.folded[2] = (const uint8_t *)f2;
     p.fold_tile_bytes = (long long)expert_fold_tile_bytes(blocks);
-    p.out[0] = out;
-    p.rows[0] = rows;
-    p.njobs = 1;
+    p.out[0] = o0; p.out[1] = o1; p.out[2] = o2;
+    p.rows[0] = rows0; p.rows[1] = rows1; p.rows[2] = rows2;
+    p.njobs = f2 ? 3 : (f1 ? 2 : 1);
     p.nb = blocks;
     p.aq_rm = (const uint32_t *)aq_rm;
     p.ad = ad;
     p.n_tokens = ntok;
     gemm_launch(p, 1);
+}
+void llamd::gemm_tokens_folded(const void *folded, const void *aq_rm, const float *ad, float *out, int blocks, int rows, int ntok) {
+    gemm_tokens_folded3(folded, nullptr, nullptr, aq_rm, ad, out, nullptr, nullptr, blocks, rows, 0, 0, ntok);
 }

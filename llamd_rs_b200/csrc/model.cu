@@ -129,6 +129,7 @@ struct Layer {
     Buf attn_norm, attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_out, ffn_norm, ffn_gate_inp;
     Buf gate_exps, up_exps, down_exps;
     Buf gate_fold, up_fold, down_fold;  // option "prefill_prefold": the expert matrices folded once for the prefill GEMM
+    Buf q_fold, k_fold, v_fold, o_fold;  // option "dense_gemm": the attention projections folded for batched decode
     bool has_q_norm = false, has_k_norm = false;
     Buf kc, vc;
 };
@@ -198,6 +199,9 @@ struct Model {
                                 // LLAMD_MAX_SEQ its large matrices take one launch per LLAMD_MAX_SEQ sequences), larger ones the tile pass.
                                 // Measured at position ~500, tok/s aggregate, matvec / tile: 9 sequences 1109 / 529, 16: 1299 / 776,
                                 // 24: 1374 / 1015, 32: 1424 / 1247, 48: 1479 / 1652, 64: 1529 / 2048
+    int dense_gemm = 8;      // option "dense_gemm" = n: from n sequences per pass the attention projections run on the integer GEMM over folded
+                             // copies of their matrices (as "head_gemm"; +2 bytes per weight of the four matrices of every layer); 0: never
+    bool dense_fold_ready = false, dense_fold_failed = false;
     int head_gemm = 4;       // option "head_gemm" = n: from n sequences per pass the output projection runs on the integer GEMM over a folded
                              // copy of the matrix (2 bytes per weight once per pass, where the matvec repeats its integer work per sequence;
                              // +0.6 GB for a 151936 x 2048 matrix, made at the first such pass); 0: never
@@ -392,6 +396,7 @@ void queue_token(Model &m, int nseq) {
         ~PassFlags() { g_pass_flags = 0; }
     } pass_flags((m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0) | (m.early_loads ? kPassEarlyLoads : 0) |
                  (m.attn_gqa ? kPassAttnGqa : 0));
+    const bool dense_gemm = m.dense_gemm && nseq >= m.dense_gemm && m.dense_fold_ready && !m.fuse_norm_qkv;
     size_t n_marks = 0;
     auto mark = [&](int phase) {
         if (!m.profiling) return;
@@ -462,6 +467,12 @@ void queue_token(Model &m, int nseq) {
             trace_x(il - 1);
         }
         mark(LLAMD_PH_ATTN_NORM);
+        if (dense_gemm) {
+            // a batch: the folded matrices once for all the sequences, on the integer tensor path (the same bits)
+            llamd_fwd_q8k_residue_major(m.aq.as<int8_t>(), m.head_rm.p, (size_t)nseq * eb);
+            gemm_tokens_folded3(l.q_fold.p, l.k_fold.p, l.v_fold.p, m.head_rm.p, m.ad.as<float>(), m.q.as<float>(), m.k.as<float>(), m.v.as<float>(),
+                                eb, qd, kvd, kvd, nseq);
+        } else
         matvec_x3_batch(plan_static(m, &l.attn_out), l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
                         m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
         }
@@ -523,6 +534,10 @@ void queue_token(Model &m, int nseq) {
         }
         }
         mark(LLAMD_PH_QUANT);
+        if (dense_gemm) {
+            llamd_fwd_q8k_residue_major(m.aq.as<int8_t>(), m.head_rm.p, (size_t)nseq * (qd / 256));
+            gemm_tokens_folded(l.o_fold.p, m.head_rm.p, m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        } else
         matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
         mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
@@ -711,18 +726,45 @@ int run(Model &m, const int32_t *tokens, const int32_t *positions, int nseq, int
     }
     if (!check_ready(m)) return -1;
     if (m.resident) mega_prepare(m);  // (uploads a pointer table: not inside a capture)
+    if (m.dense_gemm && nseq >= m.dense_gemm && !m.dense_fold_ready && !m.dense_fold_failed) {
+        // the attention projections folded once for batched passes (not inside a capture); the matvec without the memory
+        const int eb = hp.n_embd / 256, qd = hp.n_head * hp.head_dim, kvd = hp.n_head_kv * hp.head_dim;
+        const size_t need = (size_t)hp.n_layer * (expert_fold_bytes(eb, qd, 1) + 2 * expert_fold_bytes(eb, kvd, 1) + expert_fold_bytes(qd / 256, hp.n_embd, 1));
+        bool ok = qd % 256 == 0 && need + ((size_t)1 << 30) <= llamd_cuda_free_mem();
+        for (size_t i = 0; ok && i < m.layers.size(); i++) {
+            Layer &l = m.layers[i];
+            ok = l.q_fold.alloc(expert_fold_bytes(eb, qd, 1)) && l.k_fold.alloc(expert_fold_bytes(eb, kvd, 1)) &&
+                 l.v_fold.alloc(expert_fold_bytes(eb, kvd, 1)) && l.o_fold.alloc(expert_fold_bytes(qd / 256, hp.n_embd, 1));
+            if (!ok) break;
+            expert_prefold(l.attn_q.p, l.q_fold.p, eb, qd, 1);
+            expert_prefold(l.attn_k.p, l.k_fold.p, eb, kvd, 1);
+            expert_prefold(l.attn_v.p, l.v_fold.p, eb, kvd, 1);
+            expert_prefold(l.attn_out.p, l.o_fold.p, qd / 256, hp.n_embd, 1);
+        }
+        const size_t rm_bytes = (size_t)m.max_seq * (size_t)(qd / 256 > eb ? qd / 256 : eb) * 256;
+        if (ok && m.head_rm.bytes < rm_bytes) {
+            m.head_rm.release();
+            ok = m.head_rm.alloc(rm_bytes);
+        }
+        m.dense_fold_ready = ok && llamd_fwd_sync() == 0;
+        if (!m.dense_fold_ready) {
+            for (auto &l : m.layers)
+                for (Buf *b : {&l.q_fold, &l.k_fold, &l.v_fold, &l.o_fold}) b->release();
+            m.dense_fold_failed = true;
+            if (error_code() != 0) return -1;
+        }
+    }
     if (m.head_gemm && nseq >= m.head_gemm && !m.head_fold_ready && !m.head_fold_failed) {
         // the output matrix folded once for the batched output projection (not inside a capture); without the memory for
         // it the matvec serves batches as it serves one sequence
         const int eb = hp.n_embd / 256;
         const size_t need = expert_fold_bytes(eb, hp.n_vocab, 1);
-        if (need + ((size_t)1 << 30) <= llamd_cuda_free_mem() && m.head_fold.alloc(need) && m.head_rm.alloc((size_t)m.max_seq * eb * 256)) {
+        if (need + ((size_t)1 << 30) <= llamd_cuda_free_mem() && m.head_fold.alloc(need) && (m.head_rm.p || m.head_rm.alloc((size_t)m.max_seq * eb * 256))) {
             expert_prefold(m.output.p ? m.output.p : m.tok_embd.p, m.head_fold.p, eb, hp.n_vocab, 1);
             m.head_fold_ready = llamd_fwd_sync() == 0;
         }
         if (!m.head_fold_ready) {
             m.head_fold.release();
-            m.head_rm.release();
             m.head_fold_failed = true;
             if (error_code() != 0) return -1;
         }
@@ -865,7 +907,8 @@ void llamd_model_free(llamd_model *h) {
     }
     for (auto &l : m->layers)
         for (Buf *b : {&l.attn_norm, &l.attn_q, &l.attn_k, &l.attn_v, &l.attn_q_norm, &l.attn_k_norm, &l.attn_out, &l.ffn_norm,
-                       &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.gate_fold, &l.up_fold, &l.down_fold, &l.kc, &l.vc})
+                       &l.ffn_gate_inp, &l.gate_exps, &l.up_exps, &l.down_exps, &l.gate_fold, &l.up_fold, &l.down_fold, &l.q_fold, &l.k_fold,
+                       &l.v_fold, &l.o_fold, &l.kc, &l.vc})
             b->release();
     for (Buf *b : {&m->tok_embd, &m->output_norm, &m->output, &m->rope_tab, &m->x, &m->xb, &m->xb2, &m->q, &m->k, &m->v, &m->attn,
                    &m->aq, &m->ad, &m->aq2, &m->ad2, &m->router_logits, &m->router_probs, &m->expert_ids, &m->slot_order, &m->head_fold, &m->head_rm, &m->expert_w, &m->e_gate,
@@ -912,7 +955,6 @@ int llamd_model_set_tensor(llamd_model *h, int layer, int which, size_t first_bl
         if (m->head_fold_ready || m->head_fold_failed) {  // the folded copy of the output matrix is of the old bytes
             if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
             m->head_fold.release();
-            m->head_rm.release();
             m->head_fold_ready = m->head_fold_failed = false;
         }
     } else if (which == LLAMD_T_OUTPUT_NORM) {
@@ -923,6 +965,13 @@ int llamd_model_set_tensor(llamd_model *h, int layer, int which, size_t first_bl
             return -1;
         }
         Layer &l = m->layers[layer];
+        if ((which == LLAMD_T_ATTN_Q || which == LLAMD_T_ATTN_K || which == LLAMD_T_ATTN_V || which == LLAMD_T_ATTN_OUT) &&
+            (m->dense_fold_ready || m->dense_fold_failed)) {  // the folded copies are of the old bytes
+            if (g_graph_owner == m->id) llamd_fwd_graph_destroy();
+            for (auto &ll : m->layers)
+                for (Buf *b : {&ll.q_fold, &ll.k_fold, &ll.v_fold, &ll.o_fold}) b->release();
+            m->dense_fold_ready = m->dense_fold_failed = false;
+        }
         switch (which) {
         case LLAMD_T_ATTN_NORM: ok = count == E && upload_f32(l.attn_norm, host, E); break;
         case LLAMD_T_FFN_NORM: ok = count == E && upload_f32(l.ffn_norm, host, E); break;
@@ -1033,6 +1082,15 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
             return -1;
         }
         m->matvec_batch_max = value;
+        return 0;
+    }
+    if (!strcmp(name, "dense_gemm")) {
+        if (value < 0 || value > LLAMD_MAX_BATCH) {
+            m->err = "option dense_gemm: 0 (never) or the number of sequences from which on, up to 256";
+            return -1;
+        }
+        if (m->dense_gemm != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->dense_gemm = value;
         return 0;
     }
     if (!strcmp(name, "head_gemm")) {

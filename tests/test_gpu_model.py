@@ -155,14 +155,14 @@ def test_fused_tails_change_nothing(tiny):
         assert t == ref_t and np.array_equal(l.view(np.uint32), ref_l.view(np.uint32))
 
 
-@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv", "fuse_silu_down", "early_loads", "fuse_attn_quant", "sort_slots", "head_gemm"])
+@pytest.mark.parametrize("option", ["fuse_norm_router", "fuse_rope_attn", "fuse_norm_qkv", "fuse_silu_down", "early_loads", "fuse_attn_quant", "sort_slots", "head_gemm", "dense_gemm"])
 def test_fused_launches_change_nothing(tiny, option):
     """The decode pass with the FFN norm and the router as one launch (option fuse_norm_router), with QK-norm, RoPE and
     the KV store inside the attention-scores launch (option fuse_rope_attn), and with the attention norm and the MoE combine
     inside the QKV matvec (option fuse_norm_qkv; off by default), and with the loads that do not depend on the launch in
     front issued before the dependency wait (option early_loads), and with the expert launches taking their slots in expert
-    order (option sort_slots), and with the output projection on the integer GEMM over a folded copy of its matrix (option
-    head_gemm) -- against the separate launches, the late loads, the slots in routing order and the output matvec: same tokens, same hidden states after every layer, same routed experts, same logits and cache rows, bit for
+    order (option sort_slots), and with the output projection, or the attention projections, on the integer GEMM over folded
+    copies of their matrices (options head_gemm, dense_gemm) -- against the separate launches, the late loads, the slots in routing order and the output matvec: same tokens, same hidden states after every layer, same routed experts, same logits and cache rows, bit for
     bit; one and four sequences. (Positions beyond a 64-position tile, where the token's own row moves from tile to tile, are
     covered by the 768-position run against the CPU fixture, which uses the defaults.)"""
     hp, w, gm, om = tiny
@@ -172,6 +172,8 @@ def test_fused_launches_change_nothing(tiny, option):
         default = 8  # (the number of sequences from which the expert launches take their slots in expert order; 1: always)
     if option == "head_gemm":
         default = 4  # (the number of sequences from which the output projection runs on the integer GEMM; 1: always)
+    if option == "dense_gemm":
+        default = 8  # (the same for the attention projections)
     for fuse in (1, 0, 1):
         gm.set_option(option, fuse)
         gm.set_trace(True)
