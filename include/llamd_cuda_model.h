@@ -167,7 +167,7 @@ int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
 /* DeviceModel::forward (device.rs:689-722): one token, greedy next token. */
 int llamd_model_forward(llamd_model *m, int32_t token, int32_t pos, int32_t *out_token);
 /* DeviceModel::forward_batch (device.rs:741-962): nseq independent sequences. Up to LLAMD_MAX_SEQ (8) they share
- * each weight read inside the nseq kernels; up to option "matvec_batch_max" (default 40) the same pass runs with one
+ * each weight read inside the nseq kernels; up to option "matvec_batch_max" (default 56) the same pass runs with one
  * launch per 8 sequences for its large matrices; beyond that, up to max_seq (at most LLAMD_MAX_BATCH), the pass runs as
  * a prefill tile whose tokens belong to different sequences, on the integer GEMM (with sharded experts: from 2 on,
  * through the tile exchange over peer memory). Either way sequence s gets exactly the single-sequence pass's bits. */

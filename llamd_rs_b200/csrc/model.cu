@@ -195,10 +195,10 @@ struct Model {
     int prefill_attn = 1;    // 1: register-tiled attention kernels for a tile; 0: the per-token decode kernels
     int early_loads = 1;     // option "early_loads": the down projection reads its expert ids, and attention its positions and the cached rows
                              // of earlier positions, before the dependency wait (what they read was complete before the launch in front began)
-    int matvec_batch_max = 40;  // option "matvec_batch_max": batches up to this many sequences run the decode pass of matvec launches (beyond
+    int matvec_batch_max = 56;  // option "matvec_batch_max": batches up to this many sequences run the decode pass of matvec launches (beyond
                                 // LLAMD_MAX_SEQ its large matrices take one launch per LLAMD_MAX_SEQ sequences), larger ones the tile pass.
-                                // Measured at position ~500, tok/s aggregate, matvec / tile: 9 sequences 1109 / 529, 16: 1299 / 776,
-                                // 24: 1374 / 1015, 32: 1424 / 1247, 48: 1479 / 1652, 64: 1529 / 2048
+                                // Measured at position ~500, tok/s aggregate, matvec / tile: 9 sequences 1109 / 529, 16: 1547 / 776,
+                                // 32: 1810 / 1247, 40: 1797 / 1446, 48: 1882 / 1649, 64: 1968 / 2048, 80: 1972 / 2330
     int dense_gemm = 8;      // option "dense_gemm" = n: from n sequences per pass the attention projections run on the integer GEMM over folded
                              // copies of their matrices (as "head_gemm"; +2 bytes per weight of the four matrices of every layer); 0: never
     bool dense_fold_ready = false, dense_fold_failed = false;

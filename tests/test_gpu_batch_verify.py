@@ -1,7 +1,7 @@
 """Wide batches and draft verification against single-sequence decode.
 
   - forward_batch with more than 8 sequences (the nseq kernels' limit per launch) runs either as the decode pass of matvec
-    launches, whose large matrices then take one launch per 8 sequences (up to option matvec_batch_max sequences, 40 by
+    launches, whose large matrices then take one launch per 8 sequences (up to option matvec_batch_max sequences, 56 by
     default), or as a tile whose tokens belong to different sequences (beyond); either way every sequence must get
     exactly the tokens and logits of its own single-sequence run
     (crates/llamd-testing/tests/batch_decode.rs:102-125, beyond its 8);
