@@ -458,87 +458,74 @@ void queue_token(Model &m, int nseq) {
             }
             mark(LLAMD_PH_ATTN_NORM);
         } else {
-        if (il == 0) {
-            llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
-        } else {
-            combine_rms_norm_quant_wait(plan_ep_wait(), x_res, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(), nullptr,
-                                        m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
-            x_res = x;
-            trace_x(il - 1);
-        }
-        mark(LLAMD_PH_ATTN_NORM);
-        if (dense_gemm) {
-            // a batch: the folded matrices once for all the sequences, on the integer tensor path (the same bits)
-            llamd_fwd_q8k_residue_major(m.aq.as<int8_t>(), m.head_rm.p, (size_t)nseq * eb);
-            gemm_tokens_folded3(l.q_fold.p, l.k_fold.p, l.v_fold.p, m.head_rm.p, m.ad.as<float>(), m.q.as<float>(), m.k.as<float>(), m.v.as<float>(),
-                                eb, qd, kvd, kvd, nseq);
-        } else
-        matvec_x3_batch(plan_static(m, &l.attn_out), l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.q.as<float>(),
-                        m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+            if (il == 0) {
+                llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+            } else {
+                combine_rms_norm_quant_wait(plan_ep_wait(), x_res, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(),
+                                            nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+                x_res = x;
+                trace_x(il - 1);
+            }
+            mark(LLAMD_PH_ATTN_NORM);
+            if (dense_gemm) {
+                // a batch: the folded matrices once for all the sequences, on the integer tensor path (the same bits)
+                llamd_fwd_q8k_residue_major(m.aq.as<int8_t>(), m.head_rm.p, (size_t)nseq * eb);
+                gemm_tokens_folded3(l.q_fold.p, l.k_fold.p, l.v_fold.p, m.head_rm.p, m.ad.as<float>(), m.q.as<float>(), m.k.as<float>(),
+                                    m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+            } else {
+                matvec_x3_batch(plan_static(m, &l.attn_out), l.attn_q.p, l.attn_k.p, l.attn_v.p, m.aq.as<int8_t>(), m.ad.as<float>(),
+                                m.q.as<float>(), m.k.as<float>(), m.v.as<float>(), eb, qd, kvd, kvd, nseq);
+            }
         }
         mark(LLAMD_PH_QKV);
         // QK-norm per head BEFORE RoPE; K and V go into the cache at pos
         const bool fuse = m.fuse_tails && !m.kv16 && qd % 256 == 0 && hd % 16 == 0 && ffe % 256 == 0;
         const bool fuse_ra = m.fuse_rope_attn && !fuse && hd % 16 == 0 && hd <= 256;
+        const float *wqn = l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, *wkn = l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr;
         if (fuse_ra) {
-            // ... inside the attention-scores launch: one launch fewer, the same bits
-            if (m.fuse_attn_quant) {
-                // ... and the Q8_K form of the result made by the output launch itself (a cluster per 256-element block)
-                attention_rope_quant(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
-                                     l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(),
-                                     m.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, nseq, m.kv16,
-                                     m.aq.as<int8_t>(), m.ad.as<float>());
-                mark(LLAMD_PH_ROPE);
-                mark(LLAMD_PH_ATTENTION);
-            } else {
-            if (m.kv16)
-                llamd_fwd_attention_rope_meta_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
-                                                   l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p,
-                                                   m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(),
-                                                   hp.rms_eps, m.max_kv, nseq);
-            else
-                llamd_fwd_attention_rope_meta(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
-                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
-                                              l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
-                                              m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, nseq);
+            // ... inside the attention-scores launch: one launch fewer, the same bits; with fuse_attn_quant the Q8_K form of the
+            // result is made by the output launch itself (a cluster per 256-element block) where the shape allows
+            const bool quant_in_launch = m.fuse_attn_quant != 0;
+            attention_rope_quant(m.q.as<float>(), wqn, m.k.as<float>(), wkn, m.v.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(),
+                                 m.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, nseq, m.kv16,
+                                 quant_in_launch ? m.aq.as<int8_t>() : nullptr, quant_in_launch ? m.ad.as<float>() : nullptr);
             mark(LLAMD_PH_ROPE);
             mark(LLAMD_PH_ATTENTION);
-            llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
-            }
-        } else {
-        if (m.kv16)
-            llamd_fwd_qk_norm_rope_store_kv16(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
-                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
-                                              m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
-        else
-        llamd_fwd_qk_norm_rope_store(m.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, m.k.as<float>(),
-                                     l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, m.v.as<float>(), l.kc.as<float>(),
-                                     l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
-        mark(LLAMD_PH_ROPE);
-        if (fuse) {
-            // the CTA that finishes a sequence's attention last also writes its Q8_K form
-            llamd_fwd_attention_meta_quant(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
-                                           HKV, hd, meta, m.max_kv, nseq, m.tail_counter.as<unsigned int>(), m.aq.as<int8_t>(),
-                                           m.ad.as<float>());
-            mark(LLAMD_PH_ATTENTION);
+            if (!quant_in_launch) llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
         } else {
             if (m.kv16)
-                llamd_fwd_attention_meta_kv16(m.q.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
-                                              m.max_kv, nseq);
+                llamd_fwd_qk_norm_rope_store_kv16(m.q.as<float>(), wqn, m.k.as<float>(), wkn, m.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
+                                                  m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
             else
-            llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H, HKV,
-                                     hd, meta, m.max_kv, nseq);
-            mark(LLAMD_PH_ATTENTION);
-            // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
-            llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
-        }
+                llamd_fwd_qk_norm_rope_store(m.q.as<float>(), wqn, m.k.as<float>(), wkn, m.v.as<float>(), l.kc.as<float>(), l.vc.as<float>(), H,
+                                             HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, nseq, m.max_kv);
+            mark(LLAMD_PH_ROPE);
+            if (fuse) {
+                // the CTA that finishes a sequence's attention last also writes its Q8_K form
+                llamd_fwd_attention_meta_quant(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
+                                               HKV, hd, meta, m.max_kv, nseq, m.tail_counter.as<unsigned int>(), m.aq.as<int8_t>(),
+                                               m.ad.as<float>());
+                mark(LLAMD_PH_ATTENTION);
+            } else {
+                if (m.kv16)
+                    llamd_fwd_attention_meta_kv16(m.q.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
+                                                  m.max_kv, nseq);
+                else
+                    llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
+                                             HKV, hd, meta, m.max_kv, nseq);
+                mark(LLAMD_PH_ATTENTION);
+                // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
+                llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
+            }
         }
         mark(LLAMD_PH_QUANT);
         if (dense_gemm) {
             llamd_fwd_q8k_residue_major(m.aq.as<int8_t>(), m.head_rm.p, (size_t)nseq * (qd / 256));
             gemm_tokens_folded(l.o_fold.p, m.head_rm.p, m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
-        } else
-        matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E, nseq);
+        } else {
+            matvec_batch(plan_static(m, &l.ffn_gate_inp), l.attn_out.p, m.aq.as<int8_t>(), m.ad.as<float>(), m.xb2.as<float>(), qd / 256, E,
+                         nseq);
+        }
         mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
         if (fuse_nr) {
@@ -548,11 +535,11 @@ void queue_token(Model &m, int nseq) {
             x_res = m.xb.as<float>();
             mark(LLAMD_PH_FFN_NORM);
         } else {
-        llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
-                                     m.ad.as<float>(), E, hp.rms_eps, nseq);
-        mark(LLAMD_PH_FFN_NORM);
-        llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
-                                m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
+            llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
+                                         m.ad.as<float>(), E, hp.rms_eps, nseq);
+            mark(LLAMD_PH_FFN_NORM);
+            llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
+                                    m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
         }
         mark(LLAMD_PH_ROUTER);
         if (m.ep_world > 1) {
@@ -1390,6 +1377,7 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
                                     p.k.as<float>(), p.v.as<float>(), eb, qd, kvd, kvd, T);
         }
         const float *kc_view = l.kc.as<float>(), *vc_view = l.vc.as<float>();  // what the tile's attention reads
+        const float *wqn = l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, *wkn = l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr;
         if (multi_seq && m.fuse_rope_attn && hd % 16 == 0 && hd <= 256) {
             // every token is another sequence at its own position, as in a decode pass: the decode pass's attention launches
             // (QK-norm, RoPE and the K/V store inside the scores launch; one CTA per kv head for all its query heads where
@@ -1398,47 +1386,37 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
                 explicit PassFlags(int v) { g_pass_flags = v; }
                 ~PassFlags() { g_pass_flags = 0; }
             } pass_flags((m.early_loads ? kPassEarlyLoads : 0) | (m.attn_gqa ? kPassAttnGqa : 0));
-            if (m.kv16)
-                llamd_fwd_attention_rope_meta_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
-                                                   l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p,
-                                                   p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(),
-                                                   hp.rms_eps, m.max_kv, T);
-            else
-                llamd_fwd_attention_rope_meta(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
-                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
-                                              l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta,
-                                              m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, T);
+            attention_rope_quant(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.p, l.vc.p, p.attn.as<float>(),
+                                 p.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, T, m.kv16, nullptr, nullptr);
         } else if (multi_seq && m.kv16) {
-            llamd_fwd_qk_norm_rope_store_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
-                                              l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
+            llamd_fwd_qk_norm_rope_store_kv16(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
                                               m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
             llamd_fwd_attention_meta_kv16(p.q.as<float>(), l.kc.p, l.vc.p, p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta, m.max_kv, T);
         } else if (multi_seq) {
-            llamd_fwd_qk_norm_rope_store(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
-                                         l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
-                                         l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
+            llamd_fwd_qk_norm_rope_store(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.as<float>(), l.vc.as<float>(), H, HKV,
+                                         hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);
             llamd_fwd_attention_meta(p.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), p.attn.as<float>(), p.scores.as<float>(), H, HKV,
                                      hd, meta, m.max_kv, T);
         } else if (m.kv16) {
             // one sequence's tile over a binary16 cache: store rounded, then widen the rows the tile attends (exactly) into an
             // f32 view that the tiled kernels read as they read an f32 cache
-            llamd_fwd_qk_norm_rope_store_tile_kv16(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
-                                                   l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd,
-                                                   meta, m.rope_tab.as<float>(), hp.rms_eps, T);
+            llamd_fwd_qk_norm_rope_store_tile_kv16(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
+                                                   m.rope_tab.as<float>(), hp.rms_eps, T);
             llamd_fwd_kv16_expand(l.kc.p, l.vc.p, m.kc32.as<float>(), m.vc32.as<float>(), n_kv_max, kvd);
             kc_view = m.kc32.as<float>();
             vc_view = m.vc32.as<float>();
-        } else
-        llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), l.has_q_norm ? l.attn_q_norm.as<float>() : nullptr, p.k.as<float>(),
-                                          l.has_k_norm ? l.attn_k_norm.as<float>() : nullptr, p.v.as<float>(), l.kc.as<float>(),
-                                          l.vc.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
-        if (multi_seq) {
-        } else if (m.prefill_attn)
-            llamd_fwd_attention_prefill(p.q.as<float>(), kc_view, vc_view, p.attn.as<float>(), p.scores.as<float>(), H,
-                                        HKV, hd, meta, (m.max_kv + 3) & ~3, T, n_kv_max);  // score rows padded to 16 bytes
-        else
-            llamd_fwd_attention_tile(p.q.as<float>(), kc_view, vc_view, p.attn.as<float>(), p.scores.as<float>(), H, HKV,
-                                     hd, meta, m.max_kv, T);
+        } else {
+            llamd_fwd_qk_norm_rope_store_tile(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.as<float>(), l.vc.as<float>(), H,
+                                              HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, T);
+        }
+        if (!multi_seq) {  // (a batch of sequences attended above)
+            if (m.prefill_attn)
+                llamd_fwd_attention_prefill(p.q.as<float>(), kc_view, vc_view, p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta,
+                                            (m.max_kv + 3) & ~3, T, n_kv_max);  // score rows padded to 16 bytes
+            else
+                llamd_fwd_attention_tile(p.q.as<float>(), kc_view, vc_view, p.attn.as<float>(), p.scores.as<float>(), H, HKV, hd, meta,
+                                         m.max_kv, T);
+        }
         llamd_fwd_quantize(p.attn.as<float>(), p.aq.as<int8_t>(), p.ad.as<float>(), T * (qd / 256));
         if (tc) {
             llamd_fwd_act_f16_rm(p.aq.as<int8_t>(), p.ad.as<float>(), p.aq_rm.p, (size_t)T * (qd / 256));
