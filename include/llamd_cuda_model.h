@@ -125,7 +125,8 @@ size_t llamd_model_weight_bytes(llamd_model *m); /* device.rs:473 */
 /* Public knobs of DeviceModel (device.rs:126-143): "use_graph" (default 1),
  * "trace" (record per-layer hidden state and expert ids; disables the graph),
  * "ep_poll_limit" (polls before a device-side wait on another rank gives up).
- * Launch structure of the decode pass, none of which changes a bit of the result: "fuse_norm_router", "fuse_rope_attn"
+ * Launch structure of the decode pass, none of which changes a bit of the result: "fuse_norm_router" (for passes of fewer
+ * than "fuse_norm_router_max" sequences, default 2: single sequences), "fuse_rope_attn"
  * (default 1), "fuse_attn_quant", "fuse_norm_qkv", "fuse_silu_down", "fuse_tails" (default 0: measured no faster):
  * neighbouring launches as one ("fuse_attn_quant": the attention-output launch writes the Q8_K form of its result itself,
  * as thread-block clusters of the eight CTAs of a 256-element block; heads of 128, the separate quantize launch

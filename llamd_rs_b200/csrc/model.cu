@@ -205,6 +205,9 @@ struct Model {
     int head_gemm = 4;       // option "head_gemm" = n: from n sequences per pass the output projection runs on the integer GEMM over a folded
                              // copy of the matrix (2 bytes per weight once per pass, where the matvec repeats its integer work per sequence;
                              // +0.6 GB for a 151936 x 2048 matrix, made at the first such pass); 0: never
+    int fuse_norm_router_max = 2;  // option "fuse_norm_router_max": the fused norm + router launch serves passes of fewer sequences than this.
+                                   // Measured, tok/s aggregate, fused / separate: 1 sequence 281.3 / 275.7 (when it was built), 2: 460.5 / 485.0,
+                                   // 4: 727.1 / 736.8, 8: 1112.5 / 1149.2, 24: 1644.5 / 1718.7, 48: 1876.2 / 1941.4
     int sort_slots = 8;      // option "sort_slots" = n: from n sequences per pass the expert launches take their slots in expert order (0: never)
     int attn_gqa = 1;        // option "attn_gqa": batches of sequences run attention with one CTA per kv head for all its query heads (the same bits)
     int fuse_attn_quant = 0; // option "fuse_attn_quant": the attention-output launch leaves its result quantized (clusters of the CTAs of a
@@ -437,7 +440,11 @@ void queue_token(Model &m, int nseq) {
     // where the residual stream lives: m.x, or m.xb after a fused norm + router launch (which may not write in place: its
     // other CTAs still read the old stream); the combine that opens the next layer moves it back to m.x
     const float *x_res = x;
-    const bool fuse_nr = m.fuse_norm_router && (size_t)6 * E * sizeof(float) <= 200 * 1024 && E % 256 == 0 && hp.n_expert <= 4 * E;
+    // (the fused launch repeats the norm in each of its n_expert / 4 CTAs per sequence; it wins for a single sequence, where a
+    // launch boundary is what it saves, and loses from two sequences on -- m.fuse_norm_router_max -- where the norm as a
+    // launch of its own and the router rows behind it cost less; the `fast` arithmetic's router tree lives in the fused kernel)
+    const bool fuse_nr = m.fuse_norm_router && (size_t)6 * E * sizeof(float) <= 200 * 1024 && E % 256 == 0 && hp.n_expert <= 4 * E &&
+                         (nseq < m.fuse_norm_router_max || m.arith_fast);
     for (int il = 0; il < hp.n_layer; il++) {
         Layer &l = m.layers[il];
         // Attention norm, f32 and Q8_K in one pass (Q, K and V read the same
@@ -1087,6 +1094,15 @@ int llamd_model_set_option(llamd_model *h, const char *name, int value) {
         }
         if (m->head_gemm != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
         m->head_gemm = value;
+        return 0;
+    }
+    if (!strcmp(name, "fuse_norm_router_max")) {
+        if (value < 1 || value > LLAMD_MAX_BATCH + 1) {
+            m->err = "option fuse_norm_router_max: 1..257";
+            return -1;
+        }
+        if (m->fuse_norm_router_max != value && g_graph_owner == m->id) llamd_fwd_graph_destroy();  // recorded with the other setting
+        m->fuse_norm_router_max = value;
         return 0;
     }
     if (!strcmp(name, "sort_slots")) {
