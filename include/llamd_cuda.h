@@ -35,7 +35,7 @@ extern "C" {
 #define LLAMD_Q6K_BLOCK_BYTES 210
 #define LLAMD_Q8_0_BLOCK_BYTES 34
 #define LLAMD_MAX_SEQ 8 /* crates/llamd-rocm/kernels/llamd_batch.hip:41 MAX_SEQ: sequences per launch of the nseq kernels */
-#define LLAMD_MAX_BATCH 256 /* sequences a model can hold; beyond LLAMD_MAX_SEQ a pass runs on the prefill GEMM kernels */
+#define LLAMD_MAX_BATCH 256 /* sequences a model can hold; a pass of more than LLAMD_MAX_SEQ takes several launches for its large matrices, or the prefill GEMM kernels */
 
 /* ---- device discovery: crates/llamd-rocm/src/lib.rs:74-85 ------------- */
 int llamd_cuda_device_count(void);

@@ -160,7 +160,7 @@ int llamd_model_set_option(llamd_model *m, const char *name, int value);
  * dots, the softmax sum and the weighted values of attention as reduction trees instead of walking them in the reference's
  * order. Integers, indices, `exp` and every other float operation are unchanged, so results agree with arith = 0 to the
  * last bits of those sums, NOT bit for bit, and a near-tie in a router can then choose another expert. Deterministic (fixed
- * tree shapes). Honoured by the graph of separate launches (1..8 sequences; needs "fuse_norm_router", the default) and by
+ * tree shapes). Honoured by the graph of separate launches (any batch that takes the matvec pass; needs "fuse_norm_router", the default) and by
  * the resident kernel; refused (-1, message) with expert parallelism. Prefill tiles and wide batches always use the exact
  * arithmetic. */
 int llamd_model_resident_profile(llamd_model *m, unsigned long long *out32);
