@@ -138,7 +138,15 @@ size_t llamd_model_weight_bytes(llamd_model *m); /* device.rs:473 */
  * weight; the matvec when the memory is not there); "dense_gemm" = n (default 8): the same for the four attention
  * projections of every layer; "early_loads"
  * (default 1): the down projection reads its expert ids, and attention its positions and the cached rows of earlier
- * positions, before the launch's dependency wait, so their bytes travel while the launch in front still runs. */
+ * positions, before the launch's dependency wait, so their bytes travel while the launch in front still runs.
+ * Prefill: "prefill_tile" (tokens per tile, 1..4096, default 512), "prefill_gemm" (1: the exact integer tensor path,
+ * default; 0: dp4a, 8 tokens per weight pass, exact; 2: tcgen05 on f16 pairs, tolerance level), "prefill_attn" (1: the
+ * register-tiled attention kernels, default; 0: the per-token decode kernels), "prefill_prefold" (1: keep the expert
+ * matrices a second time, folded for the integer GEMM, +2 bytes per weight; same bits).
+ * Experiments kept for A/B runs, results unchanged: "pdl" (mask of launch classes that use programmatic dependent
+ * launch), "prefetch" (1: matvec launches ask L2 for the next matvec's weights), "batch_group" (sequences per CTA for
+ * small matrices at batch > 1, default 2), "ep_rank_arrive" (expert parallelism: 1 = one arrival per rank and launch on
+ * the return path instead of one per CTA; the same on every rank). An unknown name or a value out of range: -1, message. */
 int llamd_model_set_option(llamd_model *m, const char *name, int value);
 
 /* The resident decode kernel (no counterpart in the reference): option "resident" = 1 runs a single-sequence pass as

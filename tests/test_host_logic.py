@@ -229,3 +229,20 @@ def test_peer_exchange_needs_every_cta_to_arrive():
     with pytest.raises(AssertionError):
         for seed in range(400):
             _simulate_peer_exchange(4, layers=6, ctas=2, seed=seed, mode="owners_only")
+
+
+def test_every_model_option_is_documented():
+    """Every name llamd_model_set_option accepts is described in include/llamd_cuda_model.h and named in INTEGRATION.md."""
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = open(os.path.join(root, "llamd_rs_b200", "csrc", "model.cu")).read()
+    names = sorted(set(re.findall(r'!strcmp\(name, "([a-z0-9_]+)"\)', src)))
+    assert len(names) >= 20
+    hdr = open(os.path.join(root, "include", "llamd_cuda_model.h")).read()
+    integ = open(os.path.join(root, "INTEGRATION.md")).read()
+    missing_h = [n for n in names if f'"{n}"' not in hdr]
+    missing_i = [n for n in names if f"`{n}`" not in integ]
+    assert not missing_h, f"options not described in the header: {missing_h}"
+    assert not missing_i, f"options not named in INTEGRATION.md: {missing_i}"
