@@ -46,15 +46,15 @@ extern unsigned long long g_launches;
 // kernel has completed and flushed, and every kernel calls it, so completion
 // is transitive along the stream. Without the attribute both are no-ops.
 extern int g_pdl;
-// What a model's decode pass asks of the kernels it launches; 0 except while such a pass is being queued, and the launchers
-// pass it to the kernels as an argument. Bits 1 | 2 | 4: the `fast` arithmetic (model option arith) -- the norms' sums of
-// squares, the router's dots, attention's softmax sum and weighted values as reduction trees instead of the reference's
-// ordered sums. kPassEarlyLoads: the attention kernels read the positions and the cached rows of earlier positions before
-// their dependency wait; true only inside a pass whose first launch waits for everything in front of it.
+// What a model's decode pass asks of the kernels it launches: an argument of the internal launch functions (..._flags,
+// attention_rope_quant, combine_rms_norm_quant_wait) that they hand to the kernels; the extern "C" entry points pass 0.
+// Bits 1 | 2 | 4: the `fast` arithmetic (model option arith) -- the norms' sums of squares, the router's dots, attention's
+// softmax sum and weighted values as reduction trees instead of the reference's ordered sums. kPassEarlyLoads: the
+// attention kernels read the positions and the cached rows of earlier positions before their dependency wait; true only
+// inside a pass whose first launch waits for everything in front of it.
 constexpr int kPassEarlyLoads = 8;
 // kPassAttnGqa: a batch of sequences runs attention as one CTA per kv head for all the query heads that share it.
 constexpr int kPassAttnGqa = 16;
-extern int g_pass_flags;
 extern int g_batch_group;  // matvec_q6k.cu: sequences per CTA for small ungrouped matrices at batch > 1
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -219,7 +219,15 @@ void slot_order_launch(const int32_t *ids, int n_slots, int32_t *order);
 // The decode pass's attention (QK-norm, RoPE and the K/V store inside the scores launch) leaving its result quantized as well.
 void attention_rope_quant(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc, float *out,
                           float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int max_kv,
-                          int nseq, bool kv16, int8_t *qs, float *d);
+                          int nseq, bool kv16, int8_t *qs, float *d, int flags);
+void attention_meta_flags(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
+                          const int32_t *meta, int max_kv, int nseq, bool kv16, int flags);
+void norm_router_flags(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm, float *xn_out, int8_t *qs,
+                       float *d, int k, float eps, int n_expert, int n_used, float *logits, int32_t *ids, float *weights, float *probs,
+                       unsigned int *counter, int nseq, int flags);
+void rms_norm_quant_flags(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq, int flags);
+void add_rms_norm_quant_flags(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs, float *d, int n,
+                              float eps, int nseq, int flags);
 // Internal launch functions behind the extern "C" entry points of the same names; the model passes its plans here.
 void launch_matvec(int njobs, const void *const *w, float *const *out, const int *rows, int blocks, const int8_t *aq,
                    const float *ad, int nseq, const int32_t *ids, int n_slots, int n_expert, int act_div, int act_mode = 0,
@@ -266,7 +274,7 @@ void ep_wait_requests(unsigned int *counter, const unsigned int *epoch, int *sta
 void ep_wait_rows(unsigned int *counter, unsigned int target, int *status, unsigned int limit);
 void ep_signal_rows(unsigned int *const *arrive_tab);
 void combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, const float *down, const float *weights, int n_used, float *sum_out,
-                                 const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq);
+                                 const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq, int flags);
 
 // Grow-only device scratch for the host-facing entry points, the counterpart
 // of g_aq/g_ad/g_out in crates/llamd-rocm/kernels/llamd.hip:1027-1051.

@@ -392,13 +392,11 @@ void queue_token(Model &m, int nseq) {
         queue_token_resident(m);
         return;
     }
-    // the `fast` arithmetic (option arith): the decode pass's norm, router and attention launches take the mask as an argument
-    // while this pass is queued (the fused norm + router launch carries the router's tree, so the mask needs it on)
-    struct PassFlags {
-        explicit PassFlags(int v) { g_pass_flags = v; }
-        ~PassFlags() { g_pass_flags = 0; }
-    } pass_flags((m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0) | (m.early_loads ? kPassEarlyLoads : 0) |
-                 (m.attn_gqa ? kPassAttnGqa : 0));
+    // what this pass asks of the norm, router and attention launches (an argument of theirs): the `fast` arithmetic's mask
+    // (option arith; the fused norm + router launch carries the router's tree, so the mask needs it on), the loads before
+    // the dependency wait, the batch form of attention
+    const int pf = (m.arith_fast && m.fuse_norm_router && !m.fuse_tails ? m.arith_fast : 0) | (m.early_loads ? kPassEarlyLoads : 0) |
+                   (m.attn_gqa ? kPassAttnGqa : 0);
     const bool dense_gemm = m.dense_gemm && nseq >= m.dense_gemm && m.dense_fold_ready && !m.fuse_norm_qkv;
     size_t n_marks = 0;
     auto mark = [&](int phase) {
@@ -466,10 +464,10 @@ void queue_token(Model &m, int nseq) {
             mark(LLAMD_PH_ATTN_NORM);
         } else {
             if (il == 0) {
-                llamd_fwd_rms_norm_quant(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+                rms_norm_quant_flags(x, l.attn_norm.as<float>(), nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq, pf);
             } else {
                 combine_rms_norm_quant_wait(plan_ep_wait(), x_res, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, l.attn_norm.as<float>(),
-                                            nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+                                            nullptr, m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq, pf);
                 x_res = x;
                 trace_x(il - 1);
             }
@@ -495,7 +493,7 @@ void queue_token(Model &m, int nseq) {
             const bool quant_in_launch = m.fuse_attn_quant != 0;
             attention_rope_quant(m.q.as<float>(), wqn, m.k.as<float>(), wkn, m.v.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(),
                                  m.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, nseq, m.kv16,
-                                 quant_in_launch ? m.aq.as<int8_t>() : nullptr, quant_in_launch ? m.ad.as<float>() : nullptr);
+                                 quant_in_launch ? m.aq.as<int8_t>() : nullptr, quant_in_launch ? m.ad.as<float>() : nullptr, pf);
             mark(LLAMD_PH_ROPE);
             mark(LLAMD_PH_ATTENTION);
             if (!quant_in_launch) llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
@@ -514,12 +512,8 @@ void queue_token(Model &m, int nseq) {
                                                m.ad.as<float>());
                 mark(LLAMD_PH_ATTENTION);
             } else {
-                if (m.kv16)
-                    llamd_fwd_attention_meta_kv16(m.q.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta,
-                                                  m.max_kv, nseq);
-                else
-                    llamd_fwd_attention_meta(m.q.as<float>(), l.kc.as<float>(), l.vc.as<float>(), m.attn.as<float>(), m.scores.as<float>(), H,
-                                             HKV, hd, meta, m.max_kv, nseq);
+                attention_meta_flags(m.q.as<float>(), l.kc.p, l.vc.p, m.attn.as<float>(), m.scores.as<float>(), H, HKV, hd, meta, m.max_kv, nseq,
+                                     m.kv16, pf);
                 mark(LLAMD_PH_ATTENTION);
                 // (llamd_fwd_matvec_f32act fuses these two; measured 2 % slower per token: every CTA repeats the quantization)
                 llamd_fwd_quantize(m.attn.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), nseq * (qd / 256));
@@ -536,14 +530,14 @@ void queue_token(Model &m, int nseq) {
         mark(LLAMD_PH_ATTN_OUT);
         // residual, then the FFN norm (f32 for the router, Q8_K for the experts)
         if (fuse_nr) {
-            llamd_fwd_norm_router(l.ffn_gate_inp.as<float>(), x, m.xb2.as<float>(), m.xb.as<float>(), l.ffn_norm.as<float>(), nullptr,
-                                  m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, hp.n_expert, nu, m.router_logits.as<float>(),
-                                  m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
+            norm_router_flags(l.ffn_gate_inp.as<float>(), x, m.xb2.as<float>(), m.xb.as<float>(), l.ffn_norm.as<float>(), nullptr,
+                              m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, hp.n_expert, nu, m.router_logits.as<float>(),
+                              m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq, pf);
             x_res = m.xb.as<float>();
             mark(LLAMD_PH_FFN_NORM);
         } else {
-            llamd_fwd_add_rms_norm_quant(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(),
-                                         m.ad.as<float>(), E, hp.rms_eps, nseq);
+            add_rms_norm_quant_flags(x, m.xb2.as<float>(), x, l.ffn_norm.as<float>(), m.xb.as<float>(), m.aq.as<int8_t>(), m.ad.as<float>(), E,
+                                     hp.rms_eps, nseq, pf);
             mark(LLAMD_PH_FFN_NORM);
             llamd_fwd_router_matvec(l.ffn_gate_inp.as<float>(), m.xb.as<float>(), E, hp.n_expert, nu, m.router_logits.as<float>(),
                                     m.expert_ids.as<int32_t>(), m.expert_w.as<float>(), nullptr, m.router_counter.as<unsigned int>(), nseq);
@@ -631,7 +625,7 @@ void queue_token(Model &m, int nseq) {
     }
     // the last layer's combine, fused with the output norm
     combine_rms_norm_quant_wait(plan_ep_wait(), x_res, m.e_down.as<float>(), m.expert_w.as<float>(), nu, x, m.output_norm.as<float>(), nullptr,
-                                m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq);
+                                m.aq.as<int8_t>(), m.ad.as<float>(), E, hp.rms_eps, nseq, pf);
     trace_x(hp.n_layer - 1);
     mark(LLAMD_PH_ATTN_NORM);
     if (m.head_gemm && nseq >= m.head_gemm && m.head_fold_ready) {
@@ -1398,12 +1392,9 @@ static void queue_prefill_tile(Model &m, int T, int n_kv_max, bool last, bool mu
             // every token is another sequence at its own position, as in a decode pass: the decode pass's attention launches
             // (QK-norm, RoPE and the K/V store inside the scores launch; one CTA per kv head for all its query heads where
             // the shape allows; the rows of earlier positions read before the dependency wait -- earlier passes wrote them)
-            struct PassFlags {
-                explicit PassFlags(int v) { g_pass_flags = v; }
-                ~PassFlags() { g_pass_flags = 0; }
-            } pass_flags((m.early_loads ? kPassEarlyLoads : 0) | (m.attn_gqa ? kPassAttnGqa : 0));
             attention_rope_quant(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.p, l.vc.p, p.attn.as<float>(),
-                                 p.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, T, m.kv16, nullptr, nullptr);
+                                 p.scores.as<float>(), H, HKV, hd, meta, m.rope_tab.as<float>(), hp.rms_eps, m.max_kv, T, m.kv16, nullptr, nullptr,
+                                 (m.early_loads ? kPassEarlyLoads : 0) | (m.attn_gqa ? kPassAttnGqa : 0));
         } else if (multi_seq && m.kv16) {
             llamd_fwd_qk_norm_rope_store_kv16(p.q.as<float>(), wqn, p.k.as<float>(), wkn, p.v.as<float>(), l.kc.p, l.vc.p, H, HKV, hd, meta,
                                               m.rope_tab.as<float>(), hp.rms_eps, T, m.max_kv);

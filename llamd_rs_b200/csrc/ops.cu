@@ -1493,7 +1493,7 @@ __global__ void __launch_bounds__(256) attn_out_gqa_kernel(const float *__restri
 // The attention-output launch with a cluster per 256-element block of its result (attn_out_kernel's quantizing tail).
 template <class KVT>
 static void attn_out_cluster_launch(size_t smem, const float *scores, const KVT *vc, float *out, int n_head, int n_head_kv, int hd,
-                                    const int32_t *meta, int max_kv, int nseq, int8_t *qs, float *d) {
+                                    const int32_t *meta, int max_kv, int nseq, int8_t *qs, float *d, int flags) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_head, kSplit, nseq);
     cfg.blockDim = dim3(256);
@@ -1510,7 +1510,7 @@ static void attn_out_cluster_launch(size_t smem, const float *scores, const KVT 
     cfg.numAttrs = (g_pdl & PDL_ATTN) ? 2 : 1;
     g_launches++;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, attn_out_kernel<KVT>, scores, vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv,
-                                             TailPlan{nullptr, qs, d}, g_pass_flags);
+                                             TailPlan{nullptr, qs, d}, flags);
     if (e != cudaSuccess) set_error(e, "attn_out (clusters)");
 }
 // whether the attention output can leave its launch quantized: one cluster = one block
@@ -1758,6 +1758,13 @@ void llamd_fwd_router_matvec(const float *w, const float *x, int k, int n_expert
 void llamd_fwd_norm_router(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm, float *xn_out,
                            int8_t *qs, float *d, int k, float eps, int n_expert, int n_used, float *logits, int32_t *ids, float *weights,
                            float *probs, unsigned int *counter, int nseq) {
+    norm_router_flags(w, x, residual, x_out, w_norm, xn_out, qs, d, k, eps, n_expert, n_used, logits, ids, weights, probs, counter, nseq, 0);
+}
+}  // extern "C"
+// (flags: what a model's decode pass asks of the kernel, see kPass... in common.cuh; 0 = the exact arithmetic)
+void llamd::norm_router_flags(const float *w, const float *x, const float *residual, float *x_out, const float *w_norm, float *xn_out,
+                              int8_t *qs, float *d, int k, float eps, int n_expert, int n_used, float *logits, int32_t *ids, float *weights,
+                              float *probs, unsigned int *counter, int nseq, int flags) {
     const size_t smem = (size_t)6 * k * sizeof(float);
     if (k % 256 || n_expert < 1 || n_used < 1 || n_used > kMaxUsed || n_used > n_expert || (size_t)4 * k < (size_t)n_expert || smem > 200 * 1024 ||
         x_out == x || x_out == residual) {
@@ -1774,8 +1781,9 @@ void llamd_fwd_norm_router(const float *w, const float *x, const float *residual
         configured = smem;
     }
     launch_kc(PDL_ROUTER, "norm_router", norm_router_kernel, dim3((n_expert + 3) / 4, nseq), dim3(128), smem, w, x, residual, x_out, w_norm, xn_out, qs, d,
-              k, eps, n_expert, n_used, logits, ids, weights, probs, counter, g_pass_flags);
+              k, eps, n_expert, n_used, logits, ids, weights, probs, counter, flags);
 }
+extern "C" {
 
 static int g_q80_rows_max_ctas = 148 * 4;
 static int *g_q80_status = nullptr;
@@ -1927,7 +1935,7 @@ void llamd_fwd_kv16_expand(const void *kc16, const void *vc16, float *kc32, floa
 
 static void attention_split_launch(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head,
                                    int n_head_kv, int hd, const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride,
-                                   const TailPlan &tail_in, bool kv16 = false) {
+                                   const TailPlan &tail_in, bool kv16 = false, int flags = 0) {
     const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1)) * sizeof(float);
     const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
     // (the library runs on one device per process: llamd_cuda_set_device is refused once the stream exists, so a
@@ -1964,15 +1972,15 @@ static void attention_split_launch(const float *q, const void *kc, const void *v
     }
     if (kv16)
         launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const __half *)vc, out,
-                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail, g_pass_flags);
+                  n_head, n_head_kv, hd, meta, n_kv, max_kv, kv_stride, tail, flags);
     else
     launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores, (const float *)vc, out, n_head, n_head_kv, hd,
-             meta, n_kv, max_kv, kv_stride, tail, g_pass_flags);
+             meta, n_kv, max_kv, kv_stride, tail, flags);
 }
 
 static void attention_launch(const float *q, const float *kc, const float *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
                              const int32_t *meta, int n_kv, int max_kv, int nseq, int kv_stride, const TailPlan &tail = TailPlan{},
-                             bool kv16 = false) {
+                             bool kv16 = false, int flags = 0) {
     const size_t smem = (size_t)(hd + ((max_kv + 3) & ~3) + 2 * kAttTile * (hd + 1)) * sizeof(float);
     if (hd % 4 || hd > 256 || kAttTile * (hd / 4) > 8 * 256 || n_head_kv <= 0 || n_head % n_head_kv || smem > 200 * 1024) {
         set_error_msg("attention: head_dim % 4, grouping, or context beyond the shared-memory score buffer");
@@ -1981,7 +1989,7 @@ static void attention_launch(const float *q, const float *kc, const float *vc, f
     // With a scores buffer ([nseq][n_head][max_kv] floats) and a head_dim the
     // column split divides, the work is cut over 4x more CTAs.
     if (scores && hd % (4 * kSplit) == 0 && kPvTile * (hd / kSplit) / 4 <= 8 * 256) {
-        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride, tail, kv16);
+        attention_split_launch(q, kc, vc, out, scores, n_head, n_head_kv, hd, meta, n_kv, max_kv, nseq, kv_stride, tail, kv16, flags);
         return;
     }
     if (kv16) {
@@ -2040,7 +2048,7 @@ void llamd_fwd_attention_meta_kv16(const float *q, const void *kc, const void *v
 // llamd_fwd_attention_meta.
 static void attention_rope_launch(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc,
                                   float *out, float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab,
-                                  float eps, int max_kv, int nseq, bool kv16, int8_t *qs = nullptr, float *qd = nullptr) {
+                                  float eps, int max_kv, int nseq, bool kv16, int8_t *qs = nullptr, float *qd = nullptr, int flags = 0) {
     const size_t smem_a = (size_t)(hd + 2 * kAttTile * (hd + 1) + 3 * hd) * sizeof(float);
     const size_t smem_b = (size_t)(((max_kv + 3) & ~3) + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
     if (!scores || !meta || hd % (4 * kSplit) || hd > 256 || hd / 2 > 256 || kAttTile * (hd / 4) > 8 * 256 || kPvTile * (hd / kSplit) / 4 > 8 * 256 ||
@@ -2073,7 +2081,7 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
     const size_t smem_gb = (size_t)((size_t)ratio * cap + 2 * kPvTile * (hd / kSplit)) * sizeof(float);
     // (measured, 48 layers at position ~520: 8 sequences 814.7 -> 1044.8 tok/s, 4 sequences 641.8 -> 717.2, 2 sequences 456.2 -> 439.7,
     // so from four sequences on)
-    if ((g_pass_flags & kPassAttnGqa) && !(g_pass_flags & 4) && nseq >= 4 && ratio == kGqaMax && hd / kSplit == 32 && smem_ga <= 200 * 1024 &&
+    if ((flags & kPassAttnGqa) && !(flags & 4) && nseq >= 4 && ratio == kGqaMax && hd / kSplit == 32 && smem_ga <= 200 * 1024 &&
         smem_gb <= 200 * 1024) {
         static size_t conf_ga[2] = {0, 0}, conf_gb[2] = {0, 0};
         if (smem_ga > conf_ga[kv16]) {
@@ -2096,14 +2104,14 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
         }
         if (kv16) {
             launch_kc(PDL_ATTN, "attn_rope_scores_gqa", attn_rope_scores_gqa_kernel<__half>, dim3(n_head_kv, kSplitT, nseq), dim3(256), smem_ga, q, wq, k,
-                      wk, v, (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
+                      wk, v, (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, flags);
             launch_kc(PDL_ATTN, "attn_out_gqa", attn_out_gqa_kernel<__half>, dim3(n_head_kv, kSplit, nseq), dim3(256), smem_gb, (const float *)scores,
-                      (const __half *)vc, out, n_head, n_head_kv, hd, meta, max_kv, max_kv, g_pass_flags);
+                      (const __half *)vc, out, n_head, n_head_kv, hd, meta, max_kv, max_kv, flags);
         } else {
             launch_kc(PDL_ATTN, "attn_rope_scores_gqa", attn_rope_scores_gqa_kernel<float>, dim3(n_head_kv, kSplitT, nseq), dim3(256), smem_ga, q, wq, k,
-                      wk, v, (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
+                      wk, v, (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, flags);
             launch_kc(PDL_ATTN, "attn_out_gqa", attn_out_gqa_kernel<float>, dim3(n_head_kv, kSplit, nseq), dim3(256), smem_gb, (const float *)scores,
-                      (const float *)vc, out, n_head, n_head_kv, hd, meta, max_kv, max_kv, g_pass_flags);
+                      (const float *)vc, out, n_head, n_head_kv, hd, meta, max_kv, max_kv, flags);
         }
         if (qs && qd) llamd_fwd_quantize(out, qs, qd, nseq * (n_head * hd / 256));
         return;
@@ -2111,20 +2119,20 @@ static void attention_rope_launch(const float *q, const float *wq, const float *
     const bool clusters = qs && qd && attn_out_cluster_ok(n_head, hd);
     if (kv16) {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<__half>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
-                  (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
+                  (__half *)kc, (__half *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, flags);
         if (clusters)
-            attn_out_cluster_launch<__half>(smem_b, scores, (const __half *)vc, out, n_head, n_head_kv, hd, meta, max_kv, nseq, qs, qd);
+            attn_out_cluster_launch<__half>(smem_b, scores, (const __half *)vc, out, n_head, n_head_kv, hd, meta, max_kv, nseq, qs, qd, flags);
         else
             launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<__half>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores,
-                      (const __half *)vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
+                      (const __half *)vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, flags);
     } else {
         launch_kc(PDL_ATTN, "attn_rope_scores", attn_rope_scores_kernel<float>, dim3(n_head, kSplitT, nseq), dim3(256), smem_a, q, wq, k, wk, v,
-                  (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, g_pass_flags);
+                  (float *)kc, (float *)vc, scores, n_head, n_head_kv, hd, meta, max_kv, max_kv, rope_tab, eps, flags);
         if (clusters)
-            attn_out_cluster_launch<float>(smem_b, scores, (const float *)vc, out, n_head, n_head_kv, hd, meta, max_kv, nseq, qs, qd);
+            attn_out_cluster_launch<float>(smem_b, scores, (const float *)vc, out, n_head, n_head_kv, hd, meta, max_kv, nseq, qs, qd, flags);
         else
             launch_kc(PDL_ATTN, "attn_out", attn_out_kernel<float>, dim3(n_head, kSplit, nseq), dim3(256), smem_b, (const float *)scores,
-                      (const float *)vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, g_pass_flags);
+                      (const float *)vc, out, n_head, n_head_kv, hd, meta, 0, max_kv, max_kv, TailPlan{}, flags);
     }
     if (qs && qd && !clusters) llamd_fwd_quantize(out, qs, qd, nseq * (n_head * hd / 256));
 }
@@ -2134,8 +2142,14 @@ namespace llamd {
 // cluster cover a block (the quantize launch otherwise). Same bits as llamd_fwd_attention_rope_meta + llamd_fwd_quantize.
 void attention_rope_quant(const float *q, const float *wq, const float *k, const float *wk, const float *v, void *kc, void *vc, float *out,
                           float *scores, int n_head, int n_head_kv, int hd, const int32_t *meta, const float *rope_tab, float eps, int max_kv,
-                          int nseq, bool kv16, int8_t *qs, float *d) {
-    attention_rope_launch(q, wq, k, wk, v, kc, vc, out, scores, n_head, n_head_kv, hd, meta, rope_tab, eps, max_kv, nseq, kv16, qs, d);
+                          int nseq, bool kv16, int8_t *qs, float *d, int flags) {
+    attention_rope_launch(q, wq, k, wk, v, kc, vc, out, scores, n_head, n_head_kv, hd, meta, rope_tab, eps, max_kv, nseq, kv16, qs, d, flags);
+}
+// llamd_fwd_attention_meta / _kv16 with a decode pass's flags.
+void attention_meta_flags(const float *q, const void *kc, const void *vc, float *out, float *scores, int n_head, int n_head_kv, int hd,
+                          const int32_t *meta, int max_kv, int nseq, bool kv16, int flags) {
+    attention_launch(q, (const float *)kc, (const float *)vc, out, scores, n_head, n_head_kv, hd, meta, 0, max_kv, nseq, max_kv, TailPlan{}, kv16,
+                     flags);
 }
 }  // namespace llamd
 extern "C" {

@@ -275,13 +275,31 @@ static void launch_rms_norm(const char *what, int nseq, int n, Args... args) {
 
 // `wait`: with expert parallelism the rows of `down` are stored by other GPUs; the launch first waits for their arrivals.
 void llamd::combine_rms_norm_quant_wait(const WaitPlan &wait, const float *x, const float *down, const float *weights, int n_used,
-                                        float *sum_out, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
+                                        float *sum_out, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq, int flags) {
     if (n % 256 || (size_t)n * 8 > 48 * 1024) {
         set_error_msg("combine_rms_norm_quant: n must be a multiple of 256 and at most 6144");
         return;
     }
     launch_rms_norm("combine_rms_norm_quant", nseq, n, x, (const float *)nullptr, down, weights, n_used, sum_out, w, out, qs, d, n, eps, wait,
-                    g_pass_flags);
+                    flags);
+}
+// llamd_fwd_rms_norm_quant / llamd_fwd_add_rms_norm_quant with a decode pass's flags (kPass... in common.cuh).
+void llamd::rms_norm_quant_flags(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq, int flags) {
+    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("rms_norm_quant: n must be a multiple of 256 and at most 6144");
+        return;
+    }
+    launch_rms_norm("rms_norm_quant", nseq, n, x, (const float *)nullptr, (const float *)nullptr, (const float *)nullptr, 0, (float *)nullptr, w, out,
+                    qs, d, n, eps, WaitPlan{}, flags);
+}
+void llamd::add_rms_norm_quant_flags(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs, float *d,
+                                     int n, float eps, int nseq, int flags) {
+    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
+        set_error_msg("add_rms_norm_quant: n must be a multiple of 256 and at most 6144");
+        return;
+    }
+    launch_rms_norm("add_rms_norm_quant", nseq, n, x, residual, (const float *)nullptr, (const float *)nullptr, 0, sum_out, w, out, qs, d, n, eps,
+                    WaitPlan{}, flags);
 }
 
 extern "C" {
@@ -300,33 +318,23 @@ void llamd_fwd_rms_norm_mul(const float *x, const float *w, float *out, int n, f
         return;
     }
     launch_rms_norm("rms_norm_mul", nseq, n, x, (const float *)nullptr, (const float *)nullptr, (const float *)nullptr, 0, (float *)nullptr, w, out,
-                    (int8_t *)nullptr, (float *)nullptr, n, eps, WaitPlan{}, g_pass_flags);
+                    (int8_t *)nullptr, (float *)nullptr, n, eps, WaitPlan{}, 0);
 }
 void llamd_fwd_rms_norm_quant(const float *x, const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
-    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
-        set_error_msg("rms_norm_quant: n must be a multiple of 256 and at most 6144");
-        return;
-    }
-    launch_rms_norm("rms_norm_quant", nseq, n, x, (const float *)nullptr, (const float *)nullptr, (const float *)nullptr, 0, (float *)nullptr, w, out,
-                    qs, d, n, eps, WaitPlan{}, g_pass_flags);
+    rms_norm_quant_flags(x, w, out, qs, d, n, eps, nseq, 0);
 }
 // x + residual -> sum_out, then norm*w and its Q8_K form. Fuses the residual
 // add of layer.rs:170 into the norm of :173-174.
 void llamd_fwd_add_rms_norm_quant(const float *x, const float *residual, float *sum_out, const float *w, float *out, int8_t *qs,
                                   float *d, int n, float eps, int nseq) {
-    if (n % 256 || (size_t)n * 8 > 48 * 1024) {
-        set_error_msg("add_rms_norm_quant: n must be a multiple of 256 and at most 6144");
-        return;
-    }
-    launch_rms_norm("add_rms_norm_quant", nseq, n, x, residual, (const float *)nullptr, (const float *)nullptr, 0, sum_out, w, out, qs, d, n, eps,
-                    WaitPlan{}, g_pass_flags);
+    add_rms_norm_quant_flags(x, residual, sum_out, w, out, qs, d, n, eps, nseq, 0);
 }
 // x + sum_e weights[e]*down[e] -> sum_out (the MoE combine and residual,
 // forward.rs:586), then norm*w and its Q8_K form: the tail of one layer fused
 // with the attention norm of the next (or with the output norm).
 void llamd_fwd_combine_rms_norm_quant(const float *x, const float *down, const float *weights, int n_used, float *sum_out,
                                       const float *w, float *out, int8_t *qs, float *d, int n, float eps, int nseq) {
-    combine_rms_norm_quant_wait(WaitPlan{}, x, down, weights, n_used, sum_out, w, out, qs, d, n, eps, nseq);
+    combine_rms_norm_quant_wait(WaitPlan{}, x, down, weights, n_used, sum_out, w, out, qs, d, n, eps, nseq, 0);
 }
 void llamd_fwd_head_rms_norm_mul(const float *x, const float *w, float *out, int n_head, int hd, float eps) {
     if (hd % 4) {

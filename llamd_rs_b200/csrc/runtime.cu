@@ -18,7 +18,6 @@ namespace llamd {
 
 unsigned long long g_launches = 0;
 int g_pdl = 7;  // matvec, grouped matvec and router launches: measured best
-int g_pass_flags = 0;
 static cudaStream_t g_stream = nullptr;
 static int g_err = 0;
 static std::string g_err_msg;
